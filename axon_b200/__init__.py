@@ -1,0 +1,2 @@
+"""axon_b200 — a Blackwell (sm_100a) native RL post-training framework."""
+__version__ = "0.1.0"

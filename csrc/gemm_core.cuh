@@ -1,0 +1,289 @@
+// Persistent warp-specialised tcgen05 GEMM core for sm_100a.
+//
+//   D[M,N] = A[M,K] * B[N,K]^T     (fp32 accumulation in TMEM)
+//
+// One CTA per SM, 192 threads:
+//   warp 0     TMA producer   (cp.async.bulk.tensor 2-D, 128-byte swizzle, no multicast)
+//   warp 1     MMA issuer     (one lane issues tcgen05.mma; owns TMEM alloc/dealloc)
+//   warps 2-5  epilogue       (tcgen05.ld 32x32b: thread t of a warp owns one output row)
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1. Tiles are 128 x BN with BK = 64 (one 128-byte swizzle
+// atom of bf16 along the contiguous dimension).
+//
+// Each operand may be K-major (rows are M/N, K contiguous) or MN-major (rows are K, M/N
+// contiguous), which gives NN/NT/TN/TT products without a transpose pass:
+//   forward   Y = X W^T      : A = X  (K-major),  B = W  (K-major)
+//   dgrad     dX = dY W      : A = dY (K-major),  B = W  (MN-major)
+//   wgrad     dW = dY^T X    : A = dY (MN-major), B = X  (MN-major)
+//
+// The epilogue is a functor so fused consumers (bf16/fp32 store, accumulate, SwiGLU,
+// soft-max statistics for the vocabulary head, ...) share the main loop.
+#pragma once
+#include "ptx.cuh"
+#include <cuda.h>
+
+namespace axb {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_GROUP_M = 8;
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  // Leave room for barriers and the 1024-byte alignment slack inside 227 KB.
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+};
+
+struct GemmShape {
+  int M, N, K;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int group = GEMM_GROUP_M * num_n;
+  const int gid = t / group;
+  const int first_m = gid * GEMM_GROUP_M;
+  const int gm = min(num_m - first_m, GEMM_GROUP_M);
+  const int r = t - gid * group;
+  m_blk = first_m + (r % gm);
+  n_blk = r / gm;
+}
+
+// Epi contract:
+//   struct Params;                                   // POD passed by value
+//   __device__ Epi(const Params&, int m_blk, int n_blk, int row, const GemmShape&);
+//   __device__ void chunk(int col0, const uint32_t (&acc)[32]);   // 32 fp32 columns of `row`
+//   __device__ void finish();
+template <int BN, bool A_MN, bool B_MN, class Epi>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const GemmShape shape, const typename Epi::Params ep, int* status) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES);
+  uint64_t* full = bars;                      // [STAGES]
+  uint64_t* empty = bars + S::STAGES;         // [STAGES]
+  uint64_t* acc_full = bars + 2 * S::STAGES;  // [2]
+  uint64_t* acc_empty = acc_full + 2;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (shape.M + GEMM_BM - 1) / GEMM_BM;
+  const int num_n = (shape.N + BN - 1) / BN;
+  const int num_k = (shape.K + GEMM_BK - 1) / GEMM_BK;
+  const int num_tiles = num_m * num_n;
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1)) {
+            report_error(status, AXB_ERR_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + s * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, &full[s], kb * GEMM_BK, m_blk * GEMM_BM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c)
+              tma_load_2d(sA + c * 8192, &tmA, &full[s], m_blk * GEMM_BM + c * 64, kb * GEMM_BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &tmB, &full[s], kb * GEMM_BK, n_blk * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * 8192, &tmB, &full[s], n_blk * BN + c * 64, kb * GEMM_BK);
+          }
+          if (++s == S::STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(GEMM_BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1)) {
+          report_error(status, AXB_ERR_WAIT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&full[s], ph)) {
+            report_error(status, AXB_ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a0 = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b0 = a0 + S::A_BYTES;
+#pragma unroll
+          for (int j = 0; j < GEMM_BK / 16; ++j) {
+            const uint64_t ad = A_MN ? umma_smem_desc(a0 + j * 2048, 8192, 1024)
+                                     : umma_smem_desc(a0 + j * 32, 16, 1024);
+            const uint64_t bd = B_MN ? umma_smem_desc(b0 + j * 2048, 8192, 1024)
+                                     : umma_smem_desc(b0 + j * 32, 16, 1024);
+            umma_f16_ss(d_tmem, ad, bd, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);
+          if (++s == S::STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int buf = it & 1;
+      if (!mbar_wait(&acc_full[buf], (it >> 1) & 1)) {
+        report_error(status, AXB_ERR_WAIT_TMEM_FULL);
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * GEMM_BM + q * 32 + lane;
+      Epi epi(ep, m_blk, n_blk, row, shape);
+      const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld_32x32(t0 + c * 32, acc);
+        tmem_ld_wait();
+        epi.chunk(n_blk * BN + c * 32, acc);
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+      epi.finish();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------- store epilogue
+// mode 0: bf16 store, 1: fp32 store, 2: fp32 accumulate (C += acc), 3: bf16 accumulate.
+// alpha scales the accumulator first.
+struct StoreEpi {
+  struct Params {
+    void* C;
+    long long ldc;
+    int mode;
+    float alpha;
+  };
+  const Params& p;
+  const GemmShape& sh;
+  int row;
+  __device__ StoreEpi(const Params& p_, int, int, int row_, const GemmShape& sh_)
+      : p(p_), sh(sh_), row(row_) {}
+  __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
+    if (row >= sh.M || col0 >= sh.N) return;
+    const bool full = (col0 + 32 <= sh.N) && ((p.ldc & 7) == 0);
+    const float a = p.alpha;
+    if (p.mode == 0) {
+      __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+      if (full) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(acc[8 * v + 0]) * a, __uint_as_float(acc[8 * v + 1]) * a);
+          o.y = pack_bf16x2(__uint_as_float(acc[8 * v + 2]) * a, __uint_as_float(acc[8 * v + 3]) * a);
+          o.z = pack_bf16x2(__uint_as_float(acc[8 * v + 4]) * a, __uint_as_float(acc[8 * v + 5]) * a);
+          o.w = pack_bf16x2(__uint_as_float(acc[8 * v + 6]) * a, __uint_as_float(acc[8 * v + 7]) * a);
+          reinterpret_cast<uint4*>(c)[v] = o;
+        }
+      } else {
+        for (int j = 0; j < 32 && col0 + j < sh.N; ++j)
+          c[j] = __float2bfloat16(__uint_as_float(acc[j]) * a);
+      }
+    } else if (p.mode == 3) {
+      __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+      for (int j = 0; j < 32 && col0 + j < sh.N; ++j)
+        c[j] = __float2bfloat16(__bfloat162float(c[j]) + __uint_as_float(acc[j]) * a);
+    } else {
+      float* c = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+      const bool accum = p.mode == 2;
+      if (full && (p.ldc & 3) == 0) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          float4 o = make_float4(__uint_as_float(acc[4 * v + 0]) * a, __uint_as_float(acc[4 * v + 1]) * a,
+                                 __uint_as_float(acc[4 * v + 2]) * a, __uint_as_float(acc[4 * v + 3]) * a);
+          if (accum) {
+            const float4 old = reinterpret_cast<float4*>(c)[v];
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          reinterpret_cast<float4*>(c)[v] = o;
+        }
+      } else {
+        for (int j = 0; j < 32 && col0 + j < sh.N; ++j) {
+          const float v = __uint_as_float(acc[j]) * a;
+          c[j] = accum ? c[j] + v : v;
+        }
+      }
+    }
+  }
+  __device__ __forceinline__ void finish() {}
+};
+
+}  // namespace axb
