@@ -75,3 +75,20 @@ def check_status(device: torch.device | None = None) -> None:
         if code != 0:
             buf.zero_()
             raise NativeKernelError(f"device {idx}: kernel status {code}: {_ERR.get(code, 'unknown')}")
+
+
+_WORKSPACE: dict[tuple, torch.Tensor] = {}
+
+
+def workspace(device: torch.device, nbytes: int, tag: str = "default") -> torch.Tensor:
+    """A cached, grow-only uint8 scratch buffer per (device, tag).
+
+    Kernels launched on one stream run in order, so consecutive ops may share a tag; ops that
+    may overlap on different streams must use different tags.
+    """
+    key = (device.index, tag)
+    buf = _WORKSPACE.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACE[key] = buf
+    return buf

@@ -1,0 +1,140 @@
+"""Native sm_100a kernels vs the PyTorch fp32 reference path (same op called on CPU tensors)."""
+import math
+
+import pytest
+import torch
+
+from axon_b200.ops import _common as C
+from axon_b200.ops import activation as A
+from axon_b200.ops import attention as AT
+from axon_b200.ops import norm as N
+from axon_b200.ops import optim as O
+from axon_b200.ops import rope as R
+
+pytestmark = pytest.mark.gpu
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape) * scale).to(torch.bfloat16)
+
+
+def close(a, b, atol, rtol=2e-2):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (tol {atol}); mean err {err.mean().item():.4g}"
+
+
+@pytest.mark.parametrize("T,H", [(7, 256), (300, 4096), (64, 688 + 8), (33, 5120)])
+def test_rmsnorm_fwd_bwd(T, H):
+    torch.manual_seed(0)
+    x, d, w, dy, dres = bf(T, H), bf(T, H), bf(H) * 0.1 + 1, bf(T, H), bf(T, H)
+    y_r, rstd_r, xs_r = N.rmsnorm_fwd(x, w, 1e-6, delta=d)
+    y, rstd, xs = N.rmsnorm_fwd(x.cuda(), w.cuda(), 1e-6, delta=d.cuda())
+    close(y, y_r, 2e-2)
+    close(xs, xs_r, 1e-2)
+    close(rstd, rstd_r, 1e-3)
+    y2, rstd2, _ = N.rmsnorm_fwd(x.cuda(), w.cuda(), 1e-6)
+    close(y2, N.rmsnorm_fwd(x, w, 1e-6)[0], 2e-2)
+    dw_r = torch.zeros(H)
+    dx_r = N.rmsnorm_bwd(dy, xs_r, w, rstd_r, dw_r, dres=dres)
+    dw = torch.zeros(H, device="cuda")
+    dx = N.rmsnorm_bwd(dy.cuda(), xs.cuda(), w.cuda(), rstd, dw, dres=dres.cuda())
+    close(dx, dx_r, 3e-2)
+    close(dw, dw_r, 5e-2 * math.sqrt(T))
+    C.check_status()
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,D,norm", [(50, 8, 2, 128, True), (129, 32, 8, 128, True), (40, 4, 4, 128, False),
+                                           (31, 4, 2, 64, True)])
+def test_qknorm_rope(T, Hq, Hkv, D, norm):
+    torch.manual_seed(1)
+    HT = Hq + 2 * Hkv
+    qkv, dout = bf(T, HT * D), bf(T, HT * D)
+    qw = (bf(D) * 0.1 + 1) if norm else None
+    kw = (bf(D) * 0.1 + 1) if norm else None
+    pos = torch.randint(0, 5000, (T,), dtype=torch.int32)
+    cos, sin = R.rope_tables(8192, D, 1e6, "cpu")
+    out_r = R.qknorm_rope_fwd(qkv, pos, cos, sin, Hq, Hkv, D, qw, kw)
+    cg, sg = R.rope_tables(8192, D, 1e6, torch.device("cuda", 0))
+    cu = lambda t: None if t is None else t.cuda()
+    out = R.qknorm_rope_fwd(qkv.cuda(), pos.cuda(), cg, sg, Hq, Hkv, D, cu(qw), cu(kw))
+    close(out, out_r, 3e-2)
+    dqw_r, dkw_r = torch.zeros(D), torch.zeros(D)
+    d_r = R.qknorm_rope_bwd(dout, qkv, pos, cos, sin, Hq, Hkv, D, qw, kw, dqw_r, dkw_r)
+    dqw, dkw = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    d = R.qknorm_rope_bwd(dout.cuda(), qkv.cuda(), pos.cuda(), cg, sg, Hq, Hkv, D, cu(qw), cu(kw), dqw, dkw)
+    close(d, d_r, 4e-2)
+    if norm:
+        close(dqw, dqw_r, 5e-2 * math.sqrt(T * Hq))
+        close(dkw, dkw_r, 5e-2 * math.sqrt(T * Hkv))
+    C.check_status()
+
+
+def test_swiglu_embedding_add():
+    torch.manual_seed(2)
+    T, F, V, H = 77, 1376, 1000, 256
+    gu, da = bf(T, 2 * F), bf(T, F)
+    close(A.swiglu_fwd(gu.cuda()), A.swiglu_fwd(gu), 2e-2)
+    close(A.swiglu_bwd(da.cuda(), gu.cuda()), A.swiglu_bwd(da, gu), 3e-2)
+    table, ids = bf(V, H), torch.randint(0, V, (T,), dtype=torch.int32)
+    close(A.embedding_fwd(ids.cuda(), table.cuda()), A.embedding_fwd(ids, table), 0)
+    dy = bf(T, H)
+    dt = A.embedding_bwd(ids.cuda(), dy.cuda(), torch.zeros(V, H, device="cuda"))
+    close(dt, A.embedding_bwd(ids, dy, torch.zeros(V, H)), 1e-3)
+    a, b = bf(T, H), bf(T, H)
+    close(A.add(a.cuda(), b.cuda()), A.add(a, b), 1e-2)
+
+
+@pytest.mark.parametrize("lens,Hq,Hkv", [([128], 4, 4), ([256, 128], 4, 2), ([100, 300, 57, 513], 8, 2), ([1000], 32, 8)])
+def test_attention_fwd_bwd(lens, Hq, Hkv):
+    torch.manual_seed(3)
+    D = 128
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    qkv = bf(T, (Hq + 2 * Hkv) * D, scale=0.7)
+    do = bf(T, Hq * D)
+    o_r, lse_r = AT.attn_fwd(qkv, cu, Hq, Hkv, D)
+    o, lse = AT.attn_fwd(qkv.cuda(), cu.cuda(), Hq, Hkv, D)
+    C.check_status()
+    close(o, o_r, 2e-2)
+    close(lse, lse_r, 2e-2)
+    d_r = AT.attn_bwd(do, qkv, o_r, lse_r, cu, Hq, Hkv, D)
+    d = AT.attn_bwd(do.cuda(), qkv.cuda(), o, lse, cu.cuda(), Hq, Hkv, D)
+    C.check_status()
+    close(d, d_r, 6e-2, rtol=5e-2)
+    # run-twice determinism
+    d2 = AT.attn_bwd(do.cuda(), qkv.cuda(), o, lse, cu.cuda(), Hq, Hkv, D)
+    assert torch.equal(d, d2)
+
+
+def test_adamw_and_clip():
+    torch.manual_seed(4)
+    n = 100_003
+    master = torch.randn(n)
+    grad = torch.randn(n) * 3
+    m, v = torch.zeros(n), torch.zeros(n)
+    mg, vg, pg = m.cuda(), v.cuda(), master.cuda()
+    param = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    state_r, state = torch.zeros(4), torch.zeros(4, device="cuda")
+    for g_dtype in (torch.float32, torch.bfloat16):
+        g = grad.to(g_dtype)
+        O.sumsq(g, state_r)
+        O.sumsq(g.cuda(), state)
+        close(state[:1], state_r[:1], 1e-2 * n, rtol=1e-4)
+        O.clip_coef(state_r, 1.0)
+        O.clip_coef(state, 1.0)
+        close(state, state_r, 1e-3, rtol=1e-3)
+        for step in (1, 2):
+            O.adamw_step(master, None, g, m, v, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, state_r)
+            O.adamw_step(pg, param, g.cuda(), mg, vg, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, state)
+        close(pg, master, 1e-4, rtol=1e-4)
+        close(param, master, 1e-2)
+    # non-finite gradient -> step skipped
+    bad = grad.clone()
+    bad[5] = float("inf")
+    O.sumsq(bad.cuda(), state)
+    O.clip_coef(state, 1.0)
+    before = pg.clone()
+    O.adamw_step(pg, param, bad.cuda(), mg, vg, 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, state)
+    assert torch.equal(before, pg) and float(state[3]) == 1.0
