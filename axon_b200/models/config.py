@@ -1,0 +1,133 @@
+"""Model configurations of the in-house decoder family (dense Qwen3 / Llama-3 style).
+
+One definition serves the trainer and the sampler, so their numerics agree by construction.
+Field names follow the HF config keys the reference reads through ``AutoConfig``
+(axon/trainer/fsdp_trainer.py:186-260, axon/utils/hf_model.py).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "qwen3"
+    vocab_size: int = 151936
+    hidden_size: int = 4096
+    num_hidden_layers: int = 36
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 12288
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    qk_norm: bool = True
+    tie_word_embeddings: bool = False
+    max_position_embeddings: int = 40960
+    eos_token_id: int = 151645
+    pad_token_id: int = 151643
+    # MoE (0 experts = dense)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def qkv_size(self) -> int:
+        return self.q_size + 2 * self.kv_size
+
+    def num_params(self) -> int:
+        H, F, L, V = self.hidden_size, self.intermediate_size, self.num_hidden_layers, self.vocab_size
+        per_layer = self.qkv_size * H + H * self.q_size + 2 * H
+        if self.qk_norm:
+            per_layer += 2 * self.head_dim
+        if self.num_experts > 0:
+            per_layer += self.num_experts * H + self.num_experts * 3 * H * self.moe_intermediate_size
+        else:
+            per_layer += 3 * H * F
+        emb = V * H * (1 if self.tie_word_embeddings else 2)
+        return L * per_layer + emb + H
+
+    def to_hf_dict(self) -> dict:
+        d = asdict(self)
+        d.pop("extra")
+        d.update(self.extra)
+        d["architectures"] = [{"qwen3": "Qwen3ForCausalLM", "llama": "LlamaForCausalLM",
+                               "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "Qwen3ForCausalLM")]
+        return d
+
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        known = {f for f in cls.__dataclass_fields__ if f != "extra"}
+        kw = {k: v for k, v in d.items() if k in known}
+        if "head_dim" not in kw and "hidden_size" in d and "num_attention_heads" in d:
+            kw["head_dim"] = d["hidden_size"] // d["num_attention_heads"]
+        mt = d.get("model_type", "qwen3")
+        if "qk_norm" not in kw:
+            kw["qk_norm"] = mt.startswith("qwen3")
+        if isinstance(kw.get("eos_token_id"), list):
+            kw["eos_token_id"] = kw["eos_token_id"][0]
+        if kw.get("pad_token_id") is None:
+            kw["pad_token_id"] = kw.get("eos_token_id", 0)
+        return cls(**kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        return cls.from_hf_dict(json.loads((Path(path) / "config.json").read_text()))
+
+    def save_pretrained(self, path: str) -> None:
+        Path(path).mkdir(parents=True, exist_ok=True)
+        (Path(path) / "config.json").write_text(json.dumps(self.to_hf_dict(), indent=2))
+
+
+def qwen3_8b() -> ModelConfig:
+    return ModelConfig()
+
+
+def llama3_8b() -> ModelConfig:
+    return ModelConfig(model_type="llama", vocab_size=128256, hidden_size=4096, num_hidden_layers=32,
+                       num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+                       rms_norm_eps=1e-5, rope_theta=5e5, qk_norm=False, max_position_embeddings=131072,
+                       eos_token_id=128009, pad_token_id=128009)
+
+
+def qwen3_30b_a3b() -> ModelConfig:
+    return ModelConfig(model_type="qwen3_moe", hidden_size=2048, num_hidden_layers=48, num_attention_heads=32,
+                       num_key_value_heads=4, head_dim=128, intermediate_size=6144, num_experts=128,
+                       num_experts_per_tok=8, moe_intermediate_size=768)
+
+
+def tiny_qwen3() -> ModelConfig:
+    """The 2-layer CPU/gloo configuration: d_model 256, 4 q / 2 kv heads of 64, FFN 688, vocab 4096, tied."""
+    return ModelConfig(vocab_size=4096, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, intermediate_size=688, tie_word_embeddings=True,
+                       max_position_embeddings=4096, eos_token_id=1, pad_token_id=0)
+
+
+def tiny_gpu() -> ModelConfig:
+    """A small head-dim-128 model for GPU smoke tests."""
+    return ModelConfig(vocab_size=8192, hidden_size=512, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=128, intermediate_size=1024, tie_word_embeddings=False,
+                       max_position_embeddings=8192, eos_token_id=1, pad_token_id=0)
+
+
+PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen3-30b-a3b": qwen3_30b_a3b,
+           "tiny-qwen3": tiny_qwen3, "tiny-gpu": tiny_gpu}
+
+
+def get_config(name_or_path: str) -> ModelConfig:
+    key = name_or_path.lower()
+    if key in PRESETS:
+        return PRESETS[key]()
+    return ModelConfig.from_pretrained(name_or_path)

@@ -1,0 +1,184 @@
+"""Dense decoder (Qwen3 / Llama-3 style) with an explicit forward and backward over packed
+sequences.
+
+The backward pass is hand-scheduled instead of recorded by autograd: every layer keeps only its
+input residual stream, recomputes its activations when its backward runs, and accumulates weight
+gradients straight into the flat fp32 main-gradient buffer inside the wgrad GEMM epilogue. All
+heavy ops are the native sm_100a kernels of ``axon_b200.ops`` (tcgen05 GEMM / attention /
+fused vocabulary head); the same calls run PyTorch fp32 math on CPU tensors, which is both the
+test oracle and the CPU/gloo configuration.
+
+Plays the role of the HF model + ``fsdp_model_forward`` in the reference
+(axon/utils/fsdp/forward_utils.py:185-318): packed (remove-padding) inputs, fused head that
+returns per-token log-probs and entropy without materialising logits.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import activation as A
+from ..ops import attention as AT
+from ..ops import gemm as G
+from ..ops import lm_head as LM
+from ..ops import norm as N
+from ..ops import rope as R
+from .config import ModelConfig
+from .params import FlatParams
+
+
+@dataclass
+class PackedBatch:
+    """Packed (padding-free) token batch. labels[t] is the next token inside the same sequence, -100 at
+    the last position of each sequence, so ``head(t)`` scores token t+1."""
+    input_ids: torch.Tensor      # int32 [T]
+    position_ids: torch.Tensor   # int32 [T]
+    cu_seqlens: torch.Tensor     # int32 [B+1]
+    labels: torch.Tensor         # int32 [T]
+    max_seqlen: int = 0
+
+    @staticmethod
+    def from_sequences(seqs: list[torch.Tensor], device) -> "PackedBatch":
+        lens = [int(s.numel()) for s in seqs]
+        ids = torch.cat([s.to(torch.int32) for s in seqs])
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+        labels = torch.cat([torch.cat([s[1:].to(torch.int32), torch.tensor([-100], dtype=torch.int32)]) for s in seqs])
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32)
+        return PackedBatch(ids.to(device), pos.to(device), cu.to(device), labels.to(device), max(lens))
+
+
+class DenseModel:
+    def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params: FlatParams | None = None):
+        assert cfg.num_experts == 0, "use MoEModel for sparse configs"
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.params = params if params is not None else FlatParams(cfg, self.device, dtype)
+        self._saved: dict | None = None
+
+    # ------------------------------------------------------------------ helpers
+    def _p(self, l: int, name: str) -> torch.Tensor:
+        return self.params[f"model.layers.{l}.{name}"]
+
+    def _g(self, l: int, name: str) -> torch.Tensor:
+        return self.params.grads[f"model.layers.{l}.{name}"]
+
+    def head_weight(self) -> torch.Tensor:
+        return self.params["model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight"]
+
+    def head_grad(self) -> torch.Tensor:
+        return self.params.grads["model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight"]
+
+    def _tables(self, max_pos: int):
+        return R.rope_tables(max(max_pos, 8), self.cfg.head_dim, self.cfg.rope_theta, self.device)
+
+    # ------------------------------------------------------------------ one layer
+    def layer_fwd(self, l: int, x, delta, batch: PackedBatch, tables, keep: bool):
+        """x (+ delta) is the residual stream entering the layer. Returns (x1, mlp_out[, cache]):
+        the stream after attention and the not-yet-added MLP output (fused into the next norm)."""
+        c = self.cfg
+        qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
+        kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
+        h, rstd1, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
+        qkv = G.gemm_nt(h, self._p(l, "self_attn.qkv_proj.weight"))
+        qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
+                                  c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
+        o, lse = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+                             need_lse=keep)
+        ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
+        h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
+        gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
+        a = A.swiglu_fwd(gu)
+        mo = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
+        if not keep:
+            return x1, mo, xin
+        cache = dict(xin=xin, h=h, rstd1=rstd1, qkv=qkv, qkv_r=qkv_r, o=o, lse=lse, x1=x1, h2=h2, rstd2=rstd2,
+                     gu=gu, a=a)
+        return x1, mo, cache
+
+    def layer_bwd(self, l: int, xin, dx_out, batch: PackedBatch, tables):
+        """dx_out: grad of the stream leaving the layer (x1 + mlp_out). Returns grad of the stream entering."""
+        c = self.cfg
+        _, _, k = self.layer_fwd(l, xin, None, batch, tables, keep=True)
+        qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
+        kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
+        # MLP
+        da = G.gemm_nn(dx_out, self._p(l, "mlp.down_proj.weight"))
+        G.gemm_tn(dx_out, k["a"], out=self._g(l, "mlp.down_proj.weight"), accumulate=True)
+        dgu = A.swiglu_bwd(da, k["gu"])
+        del da
+        dh2 = G.gemm_nn(dgu, self._p(l, "mlp.gate_up_proj.weight"))
+        G.gemm_tn(dgu, k["h2"], out=self._g(l, "mlp.gate_up_proj.weight"), accumulate=True)
+        del dgu
+        dx1 = N.rmsnorm_bwd(dh2, k["x1"], self._p(l, "post_attention_layernorm.weight"), k["rstd2"],
+                            self._g(l, "post_attention_layernorm.weight"), dres=dx_out)
+        del dh2
+        # attention
+        do = G.gemm_nn(dx1, self._p(l, "self_attn.o_proj.weight"))
+        G.gemm_tn(dx1, k["o"], out=self._g(l, "self_attn.o_proj.weight"), accumulate=True)
+        dqkv_r = AT.attn_bwd(do, k["qkv_r"], k["o"], k["lse"], batch.cu_seqlens, c.num_attention_heads,
+                             c.num_key_value_heads, c.head_dim)
+        del do
+        dqkv = R.qknorm_rope_bwd(dqkv_r, k["qkv"], batch.position_ids, tables[0], tables[1], c.num_attention_heads,
+                                 c.num_key_value_heads, c.head_dim, qw, kw,
+                                 self._g(l, "self_attn.q_norm.weight") if c.qk_norm else None,
+                                 self._g(l, "self_attn.k_norm.weight") if c.qk_norm else None, c.rms_norm_eps)
+        del dqkv_r
+        dh = G.gemm_nn(dqkv, self._p(l, "self_attn.qkv_proj.weight"))
+        G.gemm_tn(dqkv, k["h"], out=self._g(l, "self_attn.qkv_proj.weight"), accumulate=True)
+        del dqkv
+        dx = N.rmsnorm_bwd(dh, k["xin"], self._p(l, "input_layernorm.weight"), k["rstd1"],
+                           self._g(l, "input_layernorm.weight"), dres=dx1)
+        return dx
+
+    # ------------------------------------------------------------------ whole model
+    def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
+        """Returns (logprob[T], entropy[T]) of the next token at every packed position (fp32)."""
+        c = self.cfg
+        tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
+        x = A.embedding_fwd(batch.input_ids, self.params["model.embed_tokens.weight"])
+        delta = None
+        layer_inputs = []
+        for l in range(c.num_hidden_layers):
+            x, delta, xin = self.layer_fwd(l, x, delta, batch, tables, keep=False)
+            if save_for_backward:
+                layer_inputs.append(xin)
+        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), batch.labels, temperature)
+        if save_for_backward:
+            self._saved = dict(batch=batch, tables=tables, layer_inputs=layer_inputs, xf=xf, hf=hf, rstd_f=rstd_f,
+                               lse=lse, ent=ent, temperature=temperature)
+        return lp, ent
+
+    def backward(self, g_logprob: torch.Tensor | None, g_entropy: torch.Tensor | None = None) -> None:
+        """Backward from per-position grads of (logprob, entropy); accumulates into params.grads."""
+        s = self._saved
+        assert s is not None, "call forward(save_for_backward=True) first"
+        self._saved = None
+        c = self.cfg
+        self.params.alloc_grads()
+        batch, tables = s["batch"], s["tables"]
+        g_lp = None if g_logprob is None else g_logprob.float().contiguous()
+        g_ent = None if g_entropy is None else g_entropy.float().contiguous()
+        dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), batch.labels, s["lse"], s["ent"], g_lp, g_ent,
+                            s["temperature"], dweight=self.head_grad())
+        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"],
+                           self.params.grads["model.norm.weight"])
+        del dhf
+        inputs = s["layer_inputs"]
+        for l in reversed(range(c.num_hidden_layers)):
+            xin = inputs.pop()
+            dx = self.layer_bwd(l, xin, dx, batch, tables)
+            del xin
+        A.embedding_bwd(batch.input_ids, dx, self.params.grads["model.embed_tokens.weight"])
+
+    # ------------------------------------------------------------------ analytic FLOPs (for MFU)
+    def flops_per_token(self, seqlen: int) -> float:
+        """Forward+backward FLOPs per token (6 x matmul params + attention), as the reference's
+        FlopsCounter estimates for dense models (axon/utils/profiler/flops_counter.py)."""
+        c = self.cfg
+        dense = c.num_hidden_layers * (c.qkv_size * c.hidden_size + c.hidden_size * c.q_size
+                                       + 3 * c.hidden_size * c.intermediate_size) + c.vocab_size * c.hidden_size
+        attn = 12 * c.num_hidden_layers * c.q_size * seqlen / 2  # causal
+        return 6 * dense + attn

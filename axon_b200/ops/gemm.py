@@ -31,13 +31,13 @@ def _native_gemm(a, b, out, M, N, K, a_mn, b_mn, mode, alpha=1.0, bn_hint=0, max
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
-            out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0,
+            out_dtype=None, accumulate: bool = False, alpha: float = 1.0,
             bn_hint: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """``out[M,N] (+)= alpha * a[M,K] @ b[N,K]^T``."""
     M, K = a.shape
     N = b.shape[0]
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
         assert not accumulate
     if not C.use_native(a):
         r = alpha * (a.float() @ b.float().t())
@@ -49,12 +49,12 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
 
 
 def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
-            out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0) -> torch.Tensor:
+            out_dtype=None, accumulate: bool = False, alpha: float = 1.0) -> torch.Tensor:
     """``out[M,N] (+)= alpha * a[M,K] @ b[K,N]`` (b is read MN-major, no transpose)."""
     M, K = a.shape
     N = b.shape[1]
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
         assert not accumulate
     if not C.use_native(a):
         r = alpha * (a.float() @ b.float())
@@ -66,12 +66,12 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
-            out_dtype=torch.bfloat16, accumulate: bool = False, alpha: float = 1.0) -> torch.Tensor:
+            out_dtype=None, accumulate: bool = False, alpha: float = 1.0) -> torch.Tensor:
     """``out[M,N] (+)= alpha * a[K,M]^T @ b[K,N]`` (both operands read MN-major)."""
     K, M = a.shape
     N = b.shape[1]
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
         assert not accumulate
     if not C.use_native(a):
         r = alpha * (a.float().t() @ b.float())
@@ -82,7 +82,7 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
     return _native_gemm(a, b, out, M, N, K, 1, 1, mode, alpha)
 
 
-def linear_fwd(x, w, out=None, out_dtype=torch.bfloat16):
+def linear_fwd(x, w, out=None, out_dtype=None):
     """y[T,out] = x[T,in] @ w[out,in]^T."""
     return gemm_nt(x, w, out=out, out_dtype=out_dtype)
 

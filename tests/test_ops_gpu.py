@@ -138,3 +138,48 @@ def test_adamw_and_clip():
     before = pg.clone()
     O.adamw_step(pg, param, bad.cuda(), mg, vg, 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, state)
     assert torch.equal(before, pg) and float(state[3]) == 1.0
+
+
+@pytest.mark.parametrize("T,H,V,temp", [(100, 256, 1000, 1.0), (300, 512, 4096 + 24, 0.7), (513, 1024, 20000, 1.3)])
+def test_lmhead_logprob_entropy(T, H, V, temp):
+    from axon_b200.ops import lm_head as L
+    torch.manual_seed(5)
+    hidden, w = bf(T, H), bf(V, H, scale=0.05)
+    labels = torch.randint(0, V, (T,), dtype=torch.int32)
+    labels[3] = -100
+    lp_r, ent_r, lse_r = L.lmhead_fwd(hidden, w, labels, temp)
+    lp, ent, lse = L.lmhead_fwd(hidden.cuda(), w.cuda(), labels.cuda(), temp)
+    C.check_status()
+    close(lp, lp_r, 2e-2)
+    close(ent, ent_r, 2e-2)
+    close(lse, lse_r, 2e-2)
+    g_lp, g_ent = torch.randn(T), torch.randn(T) * 0.1
+    dw_r = torch.zeros(V, H)
+    dh_r = L.lmhead_bwd(hidden, w, labels, lse_r, ent_r, g_lp, g_ent, temp, dweight=dw_r)
+    dw = torch.zeros(V, H, device="cuda")
+    dh = L.lmhead_bwd(hidden.cuda(), w.cuda(), labels.cuda(), lse, ent, g_lp.cuda(), g_ent.cuda(), temp, dweight=dw)
+    C.check_status()
+    close(dh, dh_r, 2e-2 * max(1.0, float(dh_r.abs().max())), rtol=5e-2)
+    close(dw, dw_r, 2e-2 * max(1.0, float(dw_r.abs().max())), rtol=5e-2)
+
+
+def test_lmhead_autograd_matches_torch():
+    from axon_b200.ops import lm_head as L
+    torch.manual_seed(6)
+    T, H, V = 64, 256, 777 + 7
+    hidden = bf(T, H).cuda().requires_grad_(True)
+    w = bf(V, H, scale=0.05).cuda().requires_grad_(True)
+    labels = torch.randint(0, V, (T,), dtype=torch.int32, device="cuda")
+    lp, ent = L.linear_logprob_entropy(hidden, w, labels, 1.0)
+    (lp.sum() * 0.5 - 0.01 * ent.sum()).backward()
+    h2 = hidden.detach().float().requires_grad_(True)
+    w2 = w.detach().float().requires_grad_(True)
+    z = h2 @ w2.t()
+    lsm = torch.log_softmax(z, -1)
+    lp2 = lsm.gather(1, labels.long()[:, None])[:, 0]
+    ent2 = -(lsm.exp() * lsm).sum(-1)
+    (lp2.sum() * 0.5 - 0.01 * ent2.sum()).backward()
+    close(lp, lp2, 2e-2)
+    close(ent, ent2, 2e-2)
+    close(hidden.grad, h2.grad, 2e-2, rtol=5e-2)
+    close(w.grad, w2.grad, 3e-2, rtol=5e-2)
