@@ -182,3 +182,76 @@ class DenseModel:
                                        + 3 * c.hidden_size * c.intermediate_size) + c.vocab_size * c.hidden_size
         attn = 12 * c.num_hidden_layers * c.q_size * seqlen / 2  # causal
         return 6 * dense + attn
+
+
+# ---------------------------------------------------------------------------------------------
+# Sampler-side forward passes (same weights, same kernels as training)
+# ---------------------------------------------------------------------------------------------
+class _DenseInference:
+    """Mixed into DenseModel: prefill over packed prompts and single-token decode against a paged
+    KV cache. Both write rotated K / V into the cache and return fp32 logits for sampling."""
+
+    def prefill(self, batch: PackedBatch, cache, tok_seq, tok_pos, block_table, last_index):
+        """batch: packed prompts (whole sequences, no cached prefix). tok_seq/tok_pos: per packed token
+        cache row and position. last_index: int64 [B] packed index of each prompt's last token.
+        Returns fp32 logits [B, V] of the next token."""
+        from ..ops import paged as P
+        c = self.cfg
+        tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
+        x = A.embedding_fwd(batch.input_ids, self.params["model.embed_tokens.weight"])
+        delta = None
+        for l in range(c.num_hidden_layers):
+            qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
+            kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
+            h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
+            qkv = G.gemm_nt(h, self._p(l, "self_attn.qkv_proj.weight"))
+            qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
+                                      c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
+            P.kv_write(qkv_r, cache.k[l], cache.v[l], tok_seq, tok_pos, block_table, c.num_attention_heads,
+                       c.num_key_value_heads, c.head_dim)
+            o, _ = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+                               need_lse=False)
+            ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
+            h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
+            gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
+            a = A.swiglu_fwd(gu)
+            delta = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
+            x = x1
+        xl = x[last_index]
+        dl = delta[last_index]
+        hf, _, _ = N.rmsnorm_fwd(xl, self.params["model.norm.weight"], c.rms_norm_eps, delta=dl)
+        return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)
+
+    def decode(self, tokens, positions, cache, block_table, seq_lens):
+        """tokens/positions: int32 [B] (the token to feed and its position); seq_lens = positions + 1.
+        Returns fp32 logits [B, V]."""
+        from ..ops import paged as P
+        c = self.cfg
+        B = tokens.numel()
+        tables = self._tables(c.max_position_embeddings)
+        x = A.embedding_fwd(tokens, self.params["model.embed_tokens.weight"])
+        delta = None
+        slots = cache.arange(B)
+        for l in range(c.num_hidden_layers):
+            qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
+            kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
+            h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
+            qkv = G.gemm_nt(h, self._p(l, "self_attn.qkv_proj.weight"))
+            qkv_r = R.qknorm_rope_fwd(qkv, positions, tables[0], tables[1], c.num_attention_heads,
+                                      c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
+            P.kv_write(qkv_r, cache.k[l], cache.v[l], slots, positions, block_table, c.num_attention_heads,
+                       c.num_key_value_heads, c.head_dim)
+            o = P.paged_decode(qkv_r, cache.k[l], cache.v[l], block_table, seq_lens, c.num_attention_heads,
+                               c.num_key_value_heads, c.head_dim)
+            ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
+            h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
+            gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
+            a = A.swiglu_fwd(gu)
+            delta = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
+            x = x1
+        hf, _, _ = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)
+
+
+DenseModel.prefill = _DenseInference.prefill
+DenseModel.decode = _DenseInference.decode

@@ -1,0 +1,130 @@
+"""Sampler-side ops: paged KV-cache write, paged decode attention, token sampling with log-probs.
+
+Native sm_100a kernels on CUDA; straightforward PyTorch on CPU (the oracle and the CPU config).
+Cache layout per layer: ``K, V: [num_pages, Hkv, 128, D]``; ``block_table[seq, i]`` is the page
+that holds positions ``[128*i, 128*i+128)`` of sequence ``seq``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _common as C
+
+PAGE = 128
+
+
+def kv_write(qkv_r, kcache, vcache, tok_seq, tok_pos, block_table, Hq, Hkv, D):
+    """Copy the (rotated) K and V head rows of every packed token into its cache page."""
+    T = qkv_r.shape[0]
+    if not C.use_native(qkv_r):
+        x = qkv_r.view(T, Hq + 2 * Hkv, D)
+        pages = block_table[tok_seq.long(), (tok_pos // PAGE).long()].long()
+        off = (tok_pos % PAGE).long()
+        kcache[pages, :, off] = x[:, Hq:Hq + Hkv].to(kcache.dtype)
+        vcache[pages, :, off] = x[:, Hq + Hkv:].to(vcache.dtype)
+        return
+    rc = C.lib().axb_kv_write(C.ptr(qkv_r), C.ptr(kcache), C.ptr(vcache), C.ptr(tok_seq), C.ptr(tok_pos),
+                              C.ptr(block_table), block_table.shape[1], ctypes.c_longlong(T), Hq, Hkv, D,
+                              kcache.shape[0], C.stream())
+    C.launched(rc, "kv_write")
+
+
+def paged_decode(qkv_r, kcache, vcache, block_table, seq_lens, Hq, Hkv, D, scale=None):
+    """One query token per sequence against its paged KV (which already includes that token).
+    qkv_r: [B, (Hq+2Hkv)*D]; returns o [B, Hq*D]."""
+    B = qkv_r.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not C.use_native(qkv_r):
+        q = qkv_r.view(B, Hq + 2 * Hkv, D)[:, :Hq].float()
+        out = torch.zeros(B, Hq, D)
+        rep = Hq // Hkv
+        for b in range(B):
+            n = int(seq_lens[b])
+            if n == 0:
+                continue
+            npg = (n + PAGE - 1) // PAGE
+            pg = block_table[b, :npg].long()
+            k = kcache[pg].float().permute(1, 0, 2, 3).reshape(Hkv, npg * PAGE, D)[:, :n]
+            v = vcache[pg].float().permute(1, 0, 2, 3).reshape(Hkv, npg * PAGE, D)[:, :n]
+            k = k.repeat_interleave(rep, 0)
+            v = v.repeat_interleave(rep, 0)
+            s = torch.einsum("hd,hnd->hn", q[b], k) * scale
+            out[b] = torch.einsum("hn,hnd->hd", s.softmax(-1), v)
+        return out.reshape(B, Hq * D).to(qkv_r.dtype)
+    lib = C.lib()
+    max_pages = block_table.shape[1]
+    ns = lib.axb_paged_decode_splits(B, Hkv, max_pages)
+    scratch = C.workspace(qkv_r.device, B * Hq * ns * (D + 2) * 4, "paged") if ns > 1 else None
+    out = torch.empty(B, Hq * D, dtype=qkv_r.dtype, device=qkv_r.device)
+    rc = lib.axb_paged_decode(C.ptr(qkv_r), ctypes.c_longlong(qkv_r.stride(0)), C.ptr(kcache), C.ptr(vcache),
+                              kcache.shape[0], C.ptr(block_table), max_pages, C.ptr(seq_lens), C.ptr(out), B,
+                              Hq, Hkv, D, ctypes.c_float(scale), ns, C.ptr(scratch),
+                              C.ptr(C.status(qkv_r.device)), C.stream())
+    C.launched(rc, "paged_decode", 2 if ns > 1 else 1)
+    return out
+
+
+def _ref_process(logits, temperature, top_k, top_p):
+    """Processed log-probs (after temperature / top-k / top-p), fp32 [B,V]; rows with T<=0 get argmax one-hot."""
+    B, V = logits.shape
+    z = logits.float().clone()
+    out = torch.empty_like(z)
+    for b in range(B):
+        t = float(temperature[b]) if temperature is not None else 1.0
+        if t <= 0:
+            out[b] = torch.log_softmax(z[b], -1)
+            continue
+        zb = z[b] / t
+        k = int(top_k[b]) if top_k is not None else 0
+        if 0 < k < V:
+            kth = torch.topk(zb, k).values[-1]
+            zb = zb.masked_fill(zb < kth, float("-inf"))
+        p = float(top_p[b]) if top_p is not None else 1.0
+        if p < 1.0:
+            probs = torch.softmax(zb, -1)
+            sp, si = probs.sort(descending=True)
+            keep_sorted = (sp.cumsum(0) - sp) < p
+            thr = sp[keep_sorted].min()
+            zb = zb.masked_fill(probs < thr, float("-inf"))
+        out[b] = torch.log_softmax(zb, -1)
+    return out
+
+
+def sample(logits, temperature=None, top_k=None, top_p=None, seed: int = 0, counters=None):
+    """Returns (tokens int32 [B], logprobs fp32 [B]) with log-probs under the processed distribution."""
+    B, V = logits.shape
+    if not C.use_native(logits):
+        lp = _ref_process(logits, temperature, top_k, top_p)
+        toks = torch.empty(B, dtype=torch.int32)
+        for b in range(B):
+            t = float(temperature[b]) if temperature is not None else 1.0
+            if t <= 0:
+                toks[b] = int(lp[b].argmax())
+            else:
+                g = torch.Generator().manual_seed((seed * 1000003 + b * 7919 + (int(counters[b]) if counters is not None else 0)) % (2 ** 63))
+                toks[b] = int(torch.multinomial(lp[b].exp(), 1, generator=g))
+        return toks, lp.gather(1, toks.long()[:, None])[:, 0]
+    toks = torch.empty(B, dtype=torch.int32, device=logits.device)
+    lps = torch.empty(B, dtype=torch.float32, device=logits.device)
+    rc = C.lib().axb_sample(C.ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V, C.ptr(temperature),
+                            C.ptr(top_k), C.ptr(top_p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), C.ptr(counters),
+                            C.ptr(toks), C.ptr(lps), C.stream())
+    C.launched(rc, "sample")
+    return toks, lps
+
+
+def repetition_penalty_(logits, seen, penalty):
+    """In place: logits of already-seen tokens are divided (if > 0) or multiplied (if < 0) by the penalty."""
+    B, V = logits.shape
+    if not C.use_native(logits):
+        pen = penalty[:, None]
+        adj = torch.where(logits > 0, logits / pen, logits * pen)
+        logits.copy_(torch.where(seen.bool(), adj, logits))
+        return logits
+    rc = C.lib().axb_repetition_penalty(C.ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V, C.ptr(seen),
+                                        C.ptr(penalty), C.stream())
+    C.launched(rc, "repetition_penalty")
+    return logits

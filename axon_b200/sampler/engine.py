@@ -1,0 +1,242 @@
+"""In-process generation engine with continuous batching over a paged KV cache.
+
+One ``GenerationEngine`` drives one model replica on one device: requests wait in a queue, are
+admitted while KV pages are free, prefilled in packed batches under a token budget, and decoded
+one token per running sequence per step. Log-probs are captured under the processed distribution
+(after temperature / top-k / top-p). Supports pause / continue with the reference's strategies
+(``drain | hold | continue | reset``: axon/sampler/vllm/server.py:653-744), sleep / wake (free and
+re-create the KV pool: axon/sampler/vllm/engine.py:240-303) and in-place weight refresh.
+
+The engine shares the model definition — and, when colocated, the very weight buffer — with the
+trainer, so sampler and trainer log-probs agree by construction.
+"""
+from __future__ import annotations
+
+import itertools
+from collections import deque
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..models.dense import PackedBatch
+from .kv_cache import PAGE, PagedKVCache
+from .params import SamplingParams, TokenOutput
+
+
+@dataclass
+class _Seq:
+    rid: int
+    prompt: list
+    params: SamplingParams
+    out: TokenOutput = field(default_factory=TokenOutput)
+    pages: list = field(default_factory=list)
+    length: int = 0            # tokens currently in the KV cache
+    last_token: int = 0
+    done: bool = False
+
+
+class GenerationEngine:
+    def __init__(self, model, num_pages: int | None = None, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 32768, kv_memory_bytes: int | None = None, seed: int = 0):
+        self.model = model
+        self.cfg = model.cfg
+        self.device = model.device
+        self.max_num_seqs = max_num_seqs
+        self.max_num_batched_tokens = max_num_batched_tokens
+        if num_pages is None:
+            budget = kv_memory_bytes if kv_memory_bytes is not None else 4 << 30
+            num_pages = max(8, budget // PagedKVCache.bytes_per_page(self.cfg, model.params.flat.element_size()))
+        self._num_pages = int(num_pages)
+        self.cache: PagedKVCache | None = PagedKVCache(self.cfg, self._num_pages, self.device, model.params.dtype)
+        self.waiting: deque[_Seq] = deque()
+        self.running: list[_Seq] = []
+        self.finished: dict[int, TokenOutput] = {}
+        self._rid = itertools.count()
+        self.seed = seed
+        self.step_count = 0
+        self.paused = False
+        self.pause_strategy = "drain"
+        self.stats = dict(prefill_tokens=0, decode_tokens=0, decode_steps=0, preempted=0)
+
+    # ------------------------------------------------------------------ request API
+    def add_request(self, prompt_ids, params: SamplingParams) -> int:
+        rid = next(self._rid)
+        seq = _Seq(rid, list(map(int, prompt_ids)), params)
+        seq.out.prompt_len = len(seq.prompt)
+        self.waiting.append(seq)
+        return rid
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def generate(self, prompts, params) -> list[TokenOutput]:
+        """Blocking helper: run all prompts to completion; ``params`` is one SamplingParams or a list."""
+        plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        rids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        while self.has_unfinished():
+            self.step()
+        return [self.finished.pop(r) for r in rids]
+
+    # ------------------------------------------------------------------ control
+    def pause(self, strategy: str = "drain") -> None:
+        """drain: finish running sequences, admit nothing new. hold: freeze everything in place.
+        continue: keep generating (no-op marker). reset: abort running sequences (their partial
+        outputs are returned with finish_reason 'abort') and requeue nothing."""
+        assert strategy in ("drain", "hold", "continue", "reset")
+        self.pause_strategy = strategy
+        self.paused = strategy != "continue"
+        if strategy == "drain":
+            while self.running:
+                self.step()
+        elif strategy == "reset":
+            for s in self.running:
+                self._finish(s, "abort")
+            self.running = []
+
+    def resume(self) -> None:
+        self.paused = False
+
+    def sleep(self) -> None:
+        """Free the KV pool (running sequences are aborted, as a level-1 sleep discards the cache)."""
+        for s in self.running:
+            self._finish(s, "abort")
+        self.running = []
+        if self.cache is not None:
+            self.cache.drop()
+        self.cache = None
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def wake_up(self, num_pages: int | None = None) -> None:
+        if self.cache is None:
+            if num_pages is not None:
+                self._num_pages = int(num_pages)
+            self.cache = PagedKVCache(self.cfg, self._num_pages, self.device, self.model.params.dtype)
+
+    # ------------------------------------------------------------------ internals
+    def _finish(self, s: _Seq, reason: str, stop=None) -> None:
+        s.done = True
+        s.out.finish_reason = reason
+        s.out.stop_reason = stop
+        if self.cache is not None:
+            self.cache.release(s.pages)
+        s.pages = []
+        self.finished[s.rid] = s.out
+
+    def _admit(self) -> list[_Seq]:
+        """Pick waiting sequences that fit the page pool and the token budget."""
+        batch, tokens = [], 0
+        while self.waiting and len(self.running) + len(batch) < self.max_num_seqs:
+            s = self.waiting[0]
+            n = len(s.prompt) + len(s.out.token_ids)  # a preempted sequence re-prefills its output too
+            need = (n + 1 + PAGE - 1) // PAGE
+            # keep one page of head-room per running sequence so decode can always advance
+            if need > self.cache.num_free() - len(self.running) - len(batch):
+                break
+            if batch and tokens + n > self.max_num_batched_tokens:
+                break
+            self.waiting.popleft()
+            s.pages = self.cache.alloc(need)
+            batch.append(s)
+            tokens += n
+        return batch
+
+    def _block_table(self, seqs) -> torch.Tensor:
+        width = max(len(s.pages) for s in seqs)
+        bt = np.full((len(seqs), width), -1, dtype=np.int32)
+        for i, s in enumerate(seqs):
+            bt[i, : len(s.pages)] = s.pages
+        return torch.from_numpy(bt).to(self.device, non_blocking=True)
+
+    def _sampling_tensors(self, seqs):
+        t = torch.tensor([s.params.temperature for s in seqs], dtype=torch.float32).to(self.device)
+        ks = [s.params.top_k for s in seqs]
+        ps = [s.params.top_p for s in seqs]
+        k = torch.tensor(ks, dtype=torch.int32).to(self.device) if any(x > 0 for x in ks) else None
+        p = torch.tensor(ps, dtype=torch.float32).to(self.device) if any(x < 1.0 for x in ps) else None
+        ctr = torch.tensor([len(s.out.token_ids) + 7919 * (s.rid + 1) for s in seqs], dtype=torch.int32).to(self.device)
+        return t, k, p, ctr
+
+    def _sample_and_record(self, seqs, logits) -> None:
+        from ..ops import paged as P
+        pens = [s.params.repetition_penalty for s in seqs]
+        if any(x != 1.0 for x in pens):
+            V = logits.shape[1]
+            seen = torch.zeros(len(seqs), V, dtype=torch.uint8)
+            for i, s in enumerate(seqs):
+                seen[i, torch.tensor(s.prompt + s.out.token_ids, dtype=torch.long).clamp(0, V - 1)] = 1
+            P.repetition_penalty_(logits, seen.to(self.device), torch.tensor(pens, dtype=torch.float32).to(self.device))
+        t, k, p, ctr = self._sampling_tensors(seqs)
+        toks, lps = P.sample(logits, t, k, p, seed=self.seed, counters=ctr)
+        toks_h = toks.cpu().tolist()   # the one host sync of a step: finish detection needs the ids
+        lps_h = lps.cpu().tolist()
+        eos = self.cfg.eos_token_id
+        for s, tok, lp in zip(seqs, toks_h, lps_h):
+            s.out.token_ids.append(tok)
+            s.out.logprobs.append(lp)
+            s.last_token = tok
+            sp = s.params
+            if not sp.ignore_eos and (tok == eos or tok in sp.stop_token_ids):
+                self._finish(s, "stop", tok)
+            elif len(s.out.token_ids) >= sp.max_tokens:
+                self._finish(s, "length")
+
+    def _prefill(self, seqs) -> None:
+        toks = [torch.tensor(s.prompt + s.out.token_ids, dtype=torch.int32) for s in seqs]
+        batch = PackedBatch.from_sequences(toks, self.device)
+        lens = [int(t.numel()) for t in toks]
+        tok_seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(lens)]).to(self.device)
+        last = (torch.tensor(lens).cumsum(0) - 1).to(self.device)
+        bt = self._block_table(seqs)
+        logits = self.model.prefill(batch, self.cache, tok_seq, batch.position_ids, bt, last)
+        for s, n in zip(seqs, lens):
+            s.length = n
+        self.stats["prefill_tokens"] += sum(lens)
+        self._sample_and_record(seqs, logits)
+        self.running.extend(s for s in seqs if not s.done)
+
+    def _decode(self) -> None:
+        seqs = self.running
+        # make room for the token about to be written
+        for s in seqs:
+            if s.length + 1 > len(s.pages) * PAGE:
+                if self.cache.num_free() == 0:
+                    self._preempt_one()
+                    return
+                s.pages.extend(self.cache.alloc(1))
+        tokens = torch.tensor([s.last_token for s in seqs], dtype=torch.int32).to(self.device)
+        pos = torch.tensor([s.length for s in seqs], dtype=torch.int32).to(self.device)
+        bt = self._block_table(seqs)
+        logits = self.model.decode(tokens, pos, self.cache, bt, pos + 1)
+        for s in seqs:
+            s.length += 1
+        self.stats["decode_tokens"] += len(seqs)
+        self.stats["decode_steps"] += 1
+        self._sample_and_record(seqs, logits)
+        self.running = [s for s in seqs if not s.done]
+
+    def _preempt_one(self) -> None:
+        """Out of pages: push the youngest running sequence back to the queue (recompute later)."""
+        s = self.running.pop()
+        self.cache.release(s.pages)
+        s.pages, s.length = [], 0
+        self.waiting.appendleft(s)
+        self.stats["preempted"] += 1
+
+    @torch.no_grad()
+    def step(self) -> None:
+        """One scheduler iteration: admit + prefill new sequences if possible, else decode."""
+        assert self.cache is not None, "engine is asleep; call wake_up() first"
+        self.step_count += 1
+        if self.paused and self.pause_strategy == "hold":
+            return
+        if not (self.paused and self.pause_strategy in ("drain", "reset")):
+            new = self._admit()
+            if new:
+                self._prefill(new)
+                return
+        if self.running:
+            self._decode()
+        elif self.waiting and not self.paused:
+            raise MemoryError("a waiting request does not fit the KV pool even when it is empty")

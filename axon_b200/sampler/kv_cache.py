@@ -1,0 +1,46 @@
+"""Paged KV cache: per-layer ``[num_pages, Hkv, 128, D]`` K and V pools, a host-side free list,
+and per-sequence block tables. Page = 128 tokens (one TMA tile of the decode kernel)."""
+from __future__ import annotations
+
+import torch
+
+from ..models.config import ModelConfig
+
+PAGE = 128
+
+
+class PagedKVCache:
+    def __init__(self, cfg: ModelConfig, num_pages: int, device, dtype=torch.bfloat16):
+        self.cfg = cfg
+        self.num_pages = int(num_pages)
+        self.device = torch.device(device)
+        shape = (self.num_pages, cfg.num_key_value_heads, PAGE, cfg.head_dim)
+        self.k = [torch.zeros(shape, dtype=dtype, device=self.device) for _ in range(cfg.num_hidden_layers)]
+        self.v = [torch.zeros(shape, dtype=dtype, device=self.device) for _ in range(cfg.num_hidden_layers)]
+        self.free = list(range(self.num_pages - 1, -1, -1))
+        self._arange = torch.arange(4096, dtype=torch.int32, device=self.device)
+
+    @staticmethod
+    def bytes_per_page(cfg: ModelConfig, dtype_bytes: int = 2) -> int:
+        return 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * PAGE * cfg.head_dim * dtype_bytes
+
+    def arange(self, n: int) -> torch.Tensor:
+        if n > self._arange.numel():
+            self._arange = torch.arange(2 * n, dtype=torch.int32, device=self.device)
+        return self._arange[:n]
+
+    def num_free(self) -> int:
+        return len(self.free)
+
+    def alloc(self, n: int) -> list[int]:
+        if n > len(self.free):
+            raise MemoryError(f"KV cache exhausted: want {n} pages, {len(self.free)} free")
+        out = [self.free.pop() for _ in range(n)]
+        return out
+
+    def release(self, pages: list[int]) -> None:
+        self.free.extend(pages)
+
+    def drop(self) -> None:
+        """Release the device memory (sleep); the cache must be rebuilt before the next use."""
+        self.k, self.v = [], []

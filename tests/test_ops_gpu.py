@@ -183,3 +183,64 @@ def test_lmhead_autograd_matches_torch():
     close(ent, ent2, 2e-2)
     close(hidden.grad, h2.grad, 2e-2, rtol=5e-2)
     close(w.grad, w2.grad, 3e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("lens,Hq,Hkv", [([5, 130, 257], 8, 2), ([1000, 40], 32, 8), ([3000], 8, 8)])
+def test_paged_decode_and_kv_write(lens, Hq, Hkv):
+    from axon_b200.ops import paged as P
+    torch.manual_seed(7)
+    D, B = 128, len(lens)
+    max_pages = max((n + 127) // 128 for n in lens) + 1
+    num_pages = sum((n + 127) // 128 for n in lens) + 3
+    perm = torch.randperm(num_pages)
+    bt = torch.full((B, max_pages), -1, dtype=torch.int32)
+    nxt = 0
+    for b, n in enumerate(lens):
+        for i in range((n + 127) // 128):
+            bt[b, i] = perm[nxt]
+            nxt += 1
+    HT = Hq + 2 * Hkv
+    T = sum(lens)
+    qkv = bf(T, HT * D, scale=0.7)
+    tok_seq = torch.cat([torch.full((n,), b, dtype=torch.int32) for b, n in enumerate(lens)])
+    tok_pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+    kc, vc = torch.zeros(num_pages, Hkv, 128, D, dtype=torch.bfloat16), torch.zeros(num_pages, Hkv, 128, D, dtype=torch.bfloat16)
+    P.kv_write(qkv, kc, vc, tok_seq, tok_pos, bt, Hq, Hkv, D)
+    kg, vg = torch.zeros_like(kc).cuda(), torch.zeros_like(vc).cuda()
+    P.kv_write(qkv.cuda(), kg, vg, tok_seq.cuda(), tok_pos.cuda(), bt.cuda(), Hq, Hkv, D)
+    assert torch.equal(kg.cpu(), kc) and torch.equal(vg.cpu(), vc)
+    last = torch.tensor(lens).cumsum(0) - 1
+    qlast = qkv[last]
+    sl = torch.tensor(lens, dtype=torch.int32)
+    o_r = P.paged_decode(qlast, kc, vc, bt, sl, Hq, Hkv, D)
+    o = P.paged_decode(qlast.cuda(), kg, vg, bt.cuda(), sl.cuda(), Hq, Hkv, D)
+    C.check_status()
+    close(o, o_r, 2e-2)
+
+
+def test_sampling_distribution_and_logprobs():
+    from axon_b200.ops import paged as P
+    torch.manual_seed(8)
+    B, V = 6, 5000
+    logits = (torch.randn(B, V) * 3).cuda()
+    temp = torch.tensor([1.0, 0.7, 0.0, 1.0, 1.3, 1.0]).cuda()
+    top_k = torch.tensor([0, 50, 0, 0, 20, 5], dtype=torch.int32).cuda()
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.8, 0.9, 1.0]).cuda()
+    ref_lp = P._ref_process(logits.cpu(), temp.cpu(), top_k.cpu(), top_p.cpu())
+    counts = torch.zeros(B, V)
+    n_draws = 300
+    for it in range(n_draws):
+        ctr = torch.full((B,), it, dtype=torch.int32, device="cuda")
+        toks, lps = P.sample(logits, temp, top_k, top_p, seed=123, counters=ctr)
+        toks, lps = toks.cpu().long(), lps.cpu()
+        want = ref_lp.gather(1, toks[:, None])[:, 0]
+        assert torch.isfinite(want).all(), "sampled a token outside the kept set"
+        assert (lps - want).abs().max() < 2e-3, (lps, want)
+        counts[torch.arange(B), toks] += 1
+    assert counts[2].argmax() == logits[2].argmax().cpu() and counts[2].max() == n_draws
+    assert (counts[5] > 0).sum() <= 5 and (counts[4] > 0).sum() <= 20
+    # empirical frequency of the most likely token tracks its probability
+    for b in (0, 3):
+        top = ref_lp[b].argmax()
+        pr = ref_lp[b, top].exp().item()
+        assert abs(counts[b, top].item() / n_draws - pr) < 4 * (pr * (1 - pr) / n_draws) ** 0.5 + 0.02
