@@ -1,0 +1,213 @@
+"""Colocated (hybrid-engine) RL step on one process per GPU.
+
+Each rank hosts the policy trainer and the sampler on the SAME device and the SAME bf16 weight
+buffer (the sampler reads the trainer's flat parameters in place), so the trainer->sampler weight
+sync of the hybrid topology is a stream-ordered hand-over with no copy. One ``step``:
+
+    prompts (pinned host) --H2D--> rollout (continuous batching, n samples per prompt)
+      -> rewards -> training batch (reference schema) -> group-relative advantages
+      -> old log-probs (forward) -> mini-batches: forward_backward + optim_step
+      -> weight hand-over to the sampler -> scalar metrics (D2H)
+
+Memory phases follow the reference's hybrid engine (sleep / wake, optimizer offload:
+axon/driver/sync_ppo.py:285-454, axon/sampler/mixins/sync_mixin.py:86-168): the KV pool exists only
+during rollout; gradient and (optionally) optimizer buffers exist only during training.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..models.dense import DenseModel
+from ..protocol import DataProto
+from ..sampler.engine import GenerationEngine
+from ..sampler.kv_cache import PagedKVCache
+from ..sampler.params import SamplingParams
+from ..trainer.algos import compute_advantage
+from ..trainer.policy import OptimConfig, PolicyEngine
+
+
+@dataclass
+class RLStepConfig:
+    n_samples: int = 8                   # group size
+    max_prompt_length: int = 1024
+    max_response_length: int = 4096
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    loss: str = "ppo"
+    loss_args: dict = field(default_factory=lambda: {"clip_ratio": 0.2})
+    advantage: str = "grpo"
+    advantage_args: dict = field(default_factory=dict)
+    mini_batch_size: int = 64            # prompts per optimizer step (x n_samples rows)
+    ppo_epochs: int = 1
+    max_token_len_per_gpu: int = 8192
+    use_sampler_logprobs: bool = False
+    kv_memory_fraction: float = 0.85     # of the memory free at rollout time
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 32768
+    offload_optimizer: bool | None = None  # None: decide from free memory
+    optim: OptimConfig = field(default_factory=OptimConfig)
+
+
+def build_training_batch(prompts: list[list[int]], outputs, rewards, group_ids, pad_id: int, max_len: int) -> DataProto:
+    """Rows in the reference's training schema: right-padded full sequences, ``responses == input_ids``,
+    ``response_mask`` on generated tokens, the scalar reward on the last generated token."""
+    B = len(outputs)
+    T = min(max_len, max(len(p) + len(o.token_ids) for p, o in zip(prompts, outputs)))
+    ids = np.full((B, T), pad_id, dtype=np.int64)
+    att = np.zeros((B, T), dtype=np.int64)
+    resp = np.zeros((B, T), dtype=np.float32)
+    slp = np.zeros((B, T), dtype=np.float32)
+    score = np.zeros((B, T), dtype=np.float32)
+    for i, (p, o) in enumerate(zip(prompts, outputs)):
+        seq = (p + o.token_ids)[:T]
+        n, lp = len(seq), len(p)
+        ids[i, :n] = seq
+        att[i, :n] = 1
+        resp[i, lp:n] = 1
+        slp[i, lp:n] = o.logprobs[: n - lp]
+        if n > lp:
+            score[i, n - 1] = rewards[i]
+    pos = np.broadcast_to(np.arange(T), (B, T)) * att
+    tensors = {"input_ids": torch.from_numpy(ids), "attention_mask": torch.from_numpy(att),
+               "position_ids": torch.from_numpy(pos.copy()), "responses": torch.from_numpy(ids.copy()),
+               "response_mask": torch.from_numpy(resp), "sampler_log_probs": torch.from_numpy(slp),
+               "token_level_scores": torch.from_numpy(score), "token_level_rewards": torch.from_numpy(score.copy())}
+    nt = {"uid": np.array(group_ids, dtype=object)}
+    return DataProto.from_dict(tensors, nt)
+
+
+def attach_valid_counts(mini: DataProto, process_group=None) -> None:
+    """Mini-batch-global denominators so every micro-batch / rank divides by the same numbers
+    (``process_mini_batch`` in the reference: axon/driver/driver_utils.py:436)."""
+    rm = mini.batch["response_mask"]
+    tok = rm.sum().float()
+    rows = (rm.sum(-1) > 0).sum().float()
+    cnt = torch.stack([tok, rows])
+    if process_group is not None or (dist.is_initialized() and dist.get_world_size() > 1):
+        dev = "cuda" if dist.get_backend(process_group) == "nccl" else "cpu"
+        c = cnt.to(dev)
+        dist.all_reduce(c, group=process_group)
+        cnt = c.cpu()
+    B = len(mini)
+    mini.batch["valid_token_count"] = cnt[0].expand(B).clone()
+    mini.batch["valid_batch_size"] = cnt[1].expand(B).clone()
+    mini.batch["valid_program_count"] = cnt[1].expand(B).clone()
+    mini.batch["per_row_token_count"] = rm.sum(-1)
+
+
+class ColocatedRLRunner:
+    """One GRPO/PPO-style RL step per ``step()`` call on this rank's GPU (data parallel across ranks)."""
+
+    def __init__(self, model: DenseModel, cfg: RLStepConfig, process_group=None, reward_fn=None, seed: int = 0):
+        self.model, self.cfg, self.pg = model, cfg, process_group
+        self.device = model.device
+        self.policy = PolicyEngine(model, cfg.optim, process_group, cfg.max_token_len_per_gpu, cfg.temperature)
+        self.engine: GenerationEngine | None = None
+        self.reward_fn = reward_fn
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rng = np.random.default_rng(seed + 7919 * self.rank)
+        self.seed = seed
+        self.global_step = 0
+        self.timing: dict[str, float] = {}
+
+    # ------------------------------------------------------------------ memory phases
+    def _free_bytes(self) -> int:
+        if self.device.type != "cuda":
+            return 2 << 30
+        torch.cuda.empty_cache()
+        return torch.cuda.mem_get_info(self.device)[0]
+
+    def _enter_rollout(self) -> None:
+        self.model.params.free_grads()
+        need = PagedKVCache.bytes_per_page(self.model.cfg, self.model.params.flat.element_size())
+        want_pages = self.cfg.max_num_seqs * ((self.cfg.max_prompt_length + self.cfg.max_response_length) // 128 + 1)
+        off = self.cfg.offload_optimizer
+        if off is None:
+            off = self._free_bytes() * self.cfg.kv_memory_fraction < want_pages * need * 0.5
+        if off:
+            self.policy.offload_optimizer()
+        pages = int(min(want_pages, self._free_bytes() * self.cfg.kv_memory_fraction // need))
+        if self.engine is None:
+            self.engine = GenerationEngine(self.model, num_pages=pages, max_num_seqs=self.cfg.max_num_seqs,
+                                           max_num_batched_tokens=self.cfg.max_num_batched_tokens,
+                                           seed=self.seed + self.rank)
+        else:
+            self.engine.wake_up(pages)
+
+    def _enter_training(self) -> None:
+        self.engine.sleep()
+        self.policy.load_optimizer()
+
+    # ------------------------------------------------------------------ one RL step
+    def step(self, prompt_ids: torch.Tensor, prompt_lens: torch.Tensor | None = None,
+             response_caps: np.ndarray | None = None, rewards: np.ndarray | None = None) -> dict:
+        """prompt_ids: int32 [P, Lp] (pinned host or device). response_caps: optional per-sample
+        ``max_tokens`` [P * n] (synthetic length control; EOS is ignored for those rows). rewards:
+        optional precomputed per-sample rewards [P * n]; otherwise ``reward_fn(prompt, output)``."""
+        c = self.cfg
+        t0 = time.perf_counter()
+        prompts_dev = prompt_ids.to(self.device, non_blocking=True)
+        P = prompts_dev.shape[0]
+        lens = prompt_lens.tolist() if prompt_lens is not None else [prompts_dev.shape[1]] * P
+        prompts_h = prompts_dev.cpu().tolist()   # the engine's scheduler keeps token lists on the host
+        prompts, groups, params = [], [], []
+        for i in range(P):
+            for j in range(c.n_samples):
+                prompts.append(prompts_h[i][: lens[i]])
+                groups.append(f"{self.global_step}-{self.rank}-{i}")
+                cap = int(response_caps[i * c.n_samples + j]) if response_caps is not None else c.max_response_length
+                params.append(SamplingParams(temperature=c.temperature, top_k=c.top_k, top_p=c.top_p,
+                                             max_tokens=cap, ignore_eos=response_caps is not None))
+        self._enter_rollout()
+        t1 = time.perf_counter()
+        outs = self.engine.generate(prompts, params)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        t2 = time.perf_counter()
+        self._enter_training()
+        if rewards is None:
+            rewards = np.array([self.reward_fn(p, o) for p, o in zip(prompts, outs)], dtype=np.float32) \
+                if self.reward_fn is not None else self.rng.binomial(1, 0.5, len(outs)).astype(np.float32)
+        data = build_training_batch(prompts, outs, rewards, groups, self.model.cfg.pad_token_id,
+                                    c.max_prompt_length + c.max_response_length)
+        data.meta_info.update(temperature=c.temperature, global_steps=self.global_step)
+        compute_advantage(data, {"advantage": c.advantage, "advantage_args": c.advantage_args})
+        if c.use_sampler_logprobs:
+            data.batch["old_log_probs"] = data.batch["sampler_log_probs"].clone()
+        else:
+            old = self.policy.forward(data, want_entropy=False)
+            data.batch["old_log_probs"] = old.batch["log_probs"].cpu()
+        rm = data.batch["response_mask"]
+        gap = ((data.batch["old_log_probs"].exp() - data.batch["sampler_log_probs"].exp()).abs() * rm).sum() / rm.sum().clamp_min(1)
+        t3 = time.perf_counter()
+        rows_per_mini = min(len(data), c.mini_batch_size * c.n_samples)
+        metrics: dict[str, list] = {}
+        opt = {}
+        for _ in range(c.ppo_epochs):
+            for s in range(0, len(data), rows_per_mini):
+                mini = data.slice(s, s + rows_per_mini)
+                mini.meta_info = data.meta_info
+                attach_valid_counts(mini, self.pg if self.world > 1 else None)
+                m = self.policy.forward_backward(mini, c.loss, c.loss_args)
+                opt = self.policy.optim_step()
+                for k, v in m.items():
+                    metrics.setdefault(k, []).extend(v)
+        # hand the updated weights to the sampler: same buffer, ordered on the compute stream
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        t4 = time.perf_counter()
+        self.global_step += 1
+        n_tok = int(data.batch["attention_mask"].sum())
+        n_resp = int(rm.sum())
+        self.timing = dict(setup=t1 - t0, rollout=t2 - t1, prepare_and_old_logprob=t3 - t2, train=t4 - t3, total=t4 - t0)
+        return {"loss": float(np.sum(metrics.get("loss", [0.0]))), "grad_norm": opt.get("grad_norm", 0.0),
+                "tokens": n_tok, "response_tokens": n_resp, "sequences": len(data),
+                "reward_mean": float(np.mean(rewards)), "sampler_probs_diff_mean": float(gap),
+                "entropy": float(np.mean(metrics.get("entropy", [0.0]))), **{f"time/{k}": v for k, v in self.timing.items()}}

@@ -64,7 +64,7 @@ class FlatParams:
             n = _numel(shape)
             self.offsets[name] = (off, n)
             off += (n + ALIGN - 1) // ALIGN * ALIGN
-        self.numel = off
+        self.numel = (off + 8191) // 8192 * 8192   # divisible by any power-of-two data-parallel size <= 64
         self.device = torch.device(device)
         self.dtype = dtype
         self.flat = flat if flat is not None else torch.zeros(self.numel, dtype=dtype, device=self.device)

@@ -30,6 +30,20 @@ def _native_gemm(a, b, out, M, N, K, a_mn, b_mn, mode, alpha=1.0, bn_hint=0, max
     return out
 
 
+SMALL_M = 256  # token batches up to this size take the swap-AB + split-K path (decode)
+
+
+def _native_gemm_smallm(x, w, out, M, N, K):
+    lib = C.lib()
+    splits = lib.axb_gemm_smallm_splits(M, N, K)
+    ws = C.workspace(x.device, splits * M * N * 4, "gemm_splitk") if splits > 1 else None
+    rc = lib.axb_gemm_bf16_smallm(C.ptr(x), C.ptr(w), C.ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),
+                                  ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(out.stride(0)),
+                                  int(out.dtype == torch.float32), C.ptr(ws), C.ptr(C.status(x.device)), C.stream())
+    C.launched(rc, "gemm_bf16_smallm", 2 if splits > 1 else 1)
+    return out
+
+
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
             out_dtype=None, accumulate: bool = False, alpha: float = 1.0,
             bn_hint: int = 0, max_ctas: int = 0) -> torch.Tensor:
@@ -43,6 +57,8 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
         r = alpha * (a.float() @ b.float().t())
         out.copy_(out.float() + r if accumulate else r)
         return out
+    if M <= SMALL_M and not accumulate and alpha == 1.0 and bn_hint == 0 and N >= 512:
+        return _native_gemm_smallm(a, b, out, M, N, K)
     mode = {torch.bfloat16: ACC_BF16 if accumulate else OUT_BF16,
             torch.float32: ACC_F32 if accumulate else OUT_F32}[out.dtype]
     return _native_gemm(a, b, out, M, N, K, 0, 0, mode, alpha, bn_hint, max_ctas)

@@ -58,6 +58,11 @@ class GenerationEngine:
         self.paused = False
         self.pause_strategy = "drain"
         self.stats = dict(prefill_tokens=0, decode_tokens=0, decode_steps=0, preempted=0)
+        # CUDA-graph decode: one captured graph per batch-size bucket (re-captured after every wake_up,
+        # because the KV pool moves). Disabled on CPU.
+        self.use_cuda_graph = self.device.type == "cuda"
+        self._graphs: dict[int, dict] = {}
+        self.max_pages_per_seq = (self.cfg.max_position_embeddings + PAGE - 1) // PAGE
 
     # ------------------------------------------------------------------ request API
     def add_request(self, prompt_ids, params: SamplingParams) -> int:
@@ -105,6 +110,7 @@ class GenerationEngine:
         if self.cache is not None:
             self.cache.drop()
         self.cache = None
+        self._graphs.clear()
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
 
@@ -169,18 +175,8 @@ class GenerationEngine:
             P.repetition_penalty_(logits, seen.to(self.device), torch.tensor(pens, dtype=torch.float32).to(self.device))
         t, k, p, ctr = self._sampling_tensors(seqs)
         toks, lps = P.sample(logits, t, k, p, seed=self.seed, counters=ctr)
-        toks_h = toks.cpu().tolist()   # the one host sync of a step: finish detection needs the ids
-        lps_h = lps.cpu().tolist()
-        eos = self.cfg.eos_token_id
-        for s, tok, lp in zip(seqs, toks_h, lps_h):
-            s.out.token_ids.append(tok)
-            s.out.logprobs.append(lp)
-            s.last_token = tok
-            sp = s.params
-            if not sp.ignore_eos and (tok == eos or tok in sp.stop_token_ids):
-                self._finish(s, "stop", tok)
-            elif len(s.out.token_ids) >= sp.max_tokens:
-                self._finish(s, "length")
+        # the one host sync of a step: finish detection needs the ids
+        self._record(seqs, toks.cpu().tolist(), lps.cpu().tolist())
 
     def _prefill(self, seqs) -> None:
         toks = [torch.tensor(s.prompt + s.out.token_ids, dtype=torch.int32) for s in seqs]
@@ -196,6 +192,83 @@ class GenerationEngine:
         self._sample_and_record(seqs, logits)
         self.running.extend(s for s in seqs if not s.done)
 
+    # ------------------------------------------------------------------ CUDA-graph decode
+    def set_max_model_len(self, n: int) -> None:
+        """Upper bound on prompt + response length; fixes the block-table width of the decode graphs."""
+        self.max_pages_per_seq = (n + PAGE - 1) // PAGE + 1
+        self._graphs.clear()
+
+    def _capture(self, bucket: int) -> dict:
+        from ..ops import paged as P
+        dev = self.device
+        g = dict(tokens=torch.zeros(bucket, dtype=torch.int32, device=dev),
+                 pos=torch.zeros(bucket, dtype=torch.int32, device=dev),
+                 lens=torch.zeros(bucket, dtype=torch.int32, device=dev),
+                 bt=torch.full((bucket, self.max_pages_per_seq), -1, dtype=torch.int32, device=dev),
+                 temp=torch.ones(bucket, dtype=torch.float32, device=dev),
+                 top_k=torch.zeros(bucket, dtype=torch.int32, device=dev),
+                 top_p=torch.ones(bucket, dtype=torch.float32, device=dev),
+                 ctr=torch.zeros(bucket, dtype=torch.int32, device=dev))
+
+        def run():
+            logits = self.model.decode(g["tokens"], g["pos"], self.cache, g["bt"], g["lens"])
+            return P.sample(logits, g["temp"], g["top_k"], g["top_p"], seed=self.seed, counters=g["ctr"])
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):        # warm-up: sizes every cached workspace before capture
+                run()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        from ..ops import _common as C
+        graph = torch.cuda.CUDAGraph()
+        n0 = C.LAUNCH_COUNT
+        with torch.cuda.graph(graph):
+            g["out_tokens"], g["out_lps"] = run()
+        g["launches"] = C.LAUNCH_COUNT - n0      # kernels each replay launches
+        g["graph"] = graph
+        g["host"] = {k: torch.empty(g[k].shape, dtype=g[k].dtype, pin_memory=True)
+                     for k in ("tokens", "pos", "lens", "bt", "temp", "top_k", "top_p", "ctr")}
+        return g
+
+    def _decode_graph(self, seqs) -> tuple[list, list]:
+        B = len(seqs)
+        bucket = 8
+        while bucket < B:
+            bucket *= 2
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._graphs[bucket] = self._capture(bucket)
+        h = g["host"]
+        h["tokens"].zero_(); h["pos"].zero_(); h["lens"].zero_(); h["bt"].fill_(-1)
+        h["temp"].fill_(1.0); h["top_k"].zero_(); h["top_p"].fill_(1.0); h["ctr"].zero_()
+        tok, pos, lens, bt = h["tokens"].numpy(), h["pos"].numpy(), h["lens"].numpy(), h["bt"].numpy()
+        temp, tk, tp, ctr = h["temp"].numpy(), h["top_k"].numpy(), h["top_p"].numpy(), h["ctr"].numpy()
+        for i, s in enumerate(seqs):
+            tok[i], pos[i], lens[i] = s.last_token, s.length, s.length + 1
+            bt[i, : len(s.pages)] = s.pages
+            temp[i], tk[i], tp[i] = s.params.temperature, max(0, s.params.top_k), s.params.top_p
+            ctr[i] = len(s.out.token_ids) + 7919 * (s.rid + 1)
+        for k in h:
+            g[k].copy_(h[k], non_blocking=True)
+        g["graph"].replay()
+        from ..ops import _common as C
+        C.LAUNCH_COUNT += g["launches"]
+        return g["out_tokens"][:B].cpu().tolist(), g["out_lps"][:B].cpu().tolist()
+
+    def _record(self, seqs, toks_h, lps_h) -> None:
+        eos = self.cfg.eos_token_id
+        for s, tok, lp in zip(seqs, toks_h, lps_h):
+            s.out.token_ids.append(tok)
+            s.out.logprobs.append(lp)
+            s.last_token = tok
+            sp = s.params
+            if not sp.ignore_eos and (tok == eos or tok in sp.stop_token_ids):
+                self._finish(s, "stop", tok)
+            elif len(s.out.token_ids) >= sp.max_tokens:
+                self._finish(s, "length")
+
     def _decode(self) -> None:
         seqs = self.running
         # make room for the token about to be written
@@ -205,6 +278,16 @@ class GenerationEngine:
                     self._preempt_one()
                     return
                 s.pages.extend(self.cache.alloc(1))
+        if (self.use_cuda_graph and all(s.params.repetition_penalty == 1.0 for s in seqs)
+                and max(len(s.pages) for s in seqs) <= self.max_pages_per_seq):
+            toks_h, lps_h = self._decode_graph(seqs)
+            for s in seqs:
+                s.length += 1
+            self.stats["decode_tokens"] += len(seqs)
+            self.stats["decode_steps"] += 1
+            self._record(seqs, toks_h, lps_h)
+            self.running = [s for s in seqs if not s.done]
+            return
         tokens = torch.tensor([s.last_token for s in seqs], dtype=torch.int32).to(self.device)
         pos = torch.tensor([s.length for s in seqs], dtype=torch.int32).to(self.device)
         bt = self._block_table(seqs)

@@ -7,7 +7,7 @@ namespace axb {
 template <int BN, bool A_MN, bool B_MN, class Epi>
 static int launch_gemm_inst(const void* A, const void* B, int M, int N, int K, long long lda,
                             long long ldb, const typename Epi::Params& ep, int* status,
-                            cudaStream_t stream, int max_ctas) {
+                            cudaStream_t stream, int max_ctas, int k_splits = 1) {
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN)
@@ -30,10 +30,11 @@ static int launch_gemm_inst(const void* A, const void* B, int M, int N, int K, l
     attr_set = true;
   }
   const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  const int num_tiles_k = num_tiles * (k_splits < 1 ? 1 : k_splits);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (num_tiles < grid) grid = num_tiles;
-  GemmShape sh{M, N, K};
+  if (num_tiles_k < grid) grid = num_tiles_k;
+  GemmShape sh{M, N, K, k_splits < 1 ? 1 : k_splits};
   kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, sh, ep, status);
   return check_launch();
 }
@@ -69,6 +70,20 @@ static int launch_gemm(const void* A, const void* B, int M, int N, int K, long l
 #undef AXB_DISPATCH
 }
 
+// out[t][f] = sum_s ws[s][t][f]  (fp32 partials of a split-K product), bf16 or fp32 result
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, long long ldc,
+                                     int tokens, int feats, int splits, int out_fp32) {
+  const long long n = (long long)tokens * feats;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += ws[(long long)s * n + i];
+    const long long t = i / feats, f = i - t * feats;
+    if (out_fp32) reinterpret_cast<float*>(out)[t * ldc + f] = acc;
+    else reinterpret_cast<__nv_bfloat16*>(out)[t * ldc + f] = __float2bfloat16(acc);
+  }
+}
+
 }  // namespace axb
 
 // C[M,N] (=|+=) alpha * op(A) op(B)^T.
@@ -86,4 +101,48 @@ extern "C" int axb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   StoreEpi::Params ep{C, ldc, out_mode, alpha};
   return launch_gemm<StoreEpi>(A, B, M, N, K, lda, ldb, a_mn, b_mn, ep, status,
                                static_cast<cudaStream_t>(stream), bn_hint, max_ctas);
+}
+
+// Number of K splits the small-batch product will use (the caller sizes the workspace with it).
+extern "C" int axb_gemm_smallm_splits(int tokens, int feats, int K) {
+  using namespace axb;
+  const int bn = tokens <= 64 ? 64 : (tokens <= 128 ? 128 : 256);
+  const int tiles = ((feats + GEMM_BM - 1) / GEMM_BM) * ((tokens + bn - 1) / bn);
+  const int num_k = (K + GEMM_BK - 1) / GEMM_BK;
+  const int sms = sm_count();
+  if (tiles >= sms) return 1;
+  int splits = (sms + tiles - 1) / tiles;
+  const int max_splits = num_k / 8 > 0 ? num_k / 8 : 1;  // keep at least 8 K blocks per split
+  if (splits > max_splits) splits = max_splits;
+  if (splits > 16) splits = 16;
+  return splits < 1 ? 1 : splits;
+}
+
+// Small token batch ("swap-AB"): out[tokens][feats] = X[tokens][K] * W[feats][K]^T with the weight
+// rows on the 128-wide MMA M side, so the weights stream once at full tile efficiency, plus split-K
+// to occupy every SM. ws: fp32 [splits][tokens][feats] (splits from axb_gemm_smallm_splits), may be
+// null when that returns 1. out_fp32 selects fp32 (logits) or bf16 output.
+extern "C" int axb_gemm_bf16_smallm(const void* X, const void* W, void* out, int tokens, int feats, int K,
+                                    long long ldx, long long ldw, long long ldc, int out_fp32, float* ws,
+                                    int* status, void* stream) {
+  using namespace axb;
+  if (tokens <= 0 || feats <= 0 || K <= 0 || (ldx & 7) || (ldw & 7)) return AXB_LAUNCH_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int splits = axb_gemm_smallm_splits(tokens, feats, K);
+  if (splits > 1 && ws == nullptr) return AXB_LAUNCH_BAD_ARG;
+  TransposedEpi::Params ep{out, ldc, out_fp32 ? 1 : 0, ws};
+  int rc;
+  if (tokens <= 64)
+    rc = launch_gemm_inst<64, false, false, TransposedEpi>(W, X, feats, tokens, K, ldw, ldx, ep, status, s, 0, splits);
+  else if (tokens <= 128)
+    rc = launch_gemm_inst<128, false, false, TransposedEpi>(W, X, feats, tokens, K, ldw, ldx, ep, status, s, 0, splits);
+  else
+    rc = launch_gemm_inst<256, false, false, TransposedEpi>(W, X, feats, tokens, K, ldw, ldx, ep, status, s, 0, splits);
+  if (rc || splits == 1) return rc;
+  const long long n = (long long)tokens * feats;
+  long long blocks = (n + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  splitk_reduce_kernel<<<(int)blocks, 256, 0, s>>>(ws, out, ldc, tokens, feats, splits, out_fp32);
+  return check_launch();
 }

@@ -42,9 +42,13 @@ struct GemmSmem {
 
 struct GemmShape {
   int M, N, K;
+  int k_splits;  // >= 1; split s handles K blocks [s*kper, (s+1)*kper) and the epilogue receives s
 };
 
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int k_splits, int& m_blk,
+                                            int& n_blk, int& split) {
+  split = t % k_splits;  // splits of one output tile run side by side
+  t /= k_splits;
   const int group = GEMM_GROUP_M * num_n;
   const int gid = t / group;
   const int first_m = gid * GEMM_GROUP_M;
@@ -56,7 +60,7 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
 
 // Epi contract:
 //   struct Params;                                   // POD passed by value
-//   __device__ Epi(const Params&, int m_blk, int n_blk, int row, const GemmShape&);
+//   __device__ Epi(const Params&, int m_blk, int n_blk, int row, const GemmShape&, int split);
 //   __device__ void chunk(int col0, const uint32_t (&acc)[32]);   // 32 fp32 columns of `row`
 //   __device__ void finish();
 template <int BN, bool A_MN, bool B_MN, class Epi>
@@ -78,8 +82,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int num_m = (shape.M + GEMM_BM - 1) / GEMM_BM;
   const int num_n = (shape.N + BN - 1) / BN;
-  const int num_k = (shape.K + GEMM_BK - 1) / GEMM_BK;
-  const int num_tiles = num_m * num_n;
+  const int num_k_total = (shape.K + GEMM_BK - 1) / GEMM_BK;
+  const int k_splits = shape.k_splits < 1 ? 1 : shape.k_splits;
+  const int k_per = (num_k_total + k_splits - 1) / k_splits;
+  const int num_tiles = num_m * num_n * k_splits;
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 
   if (threadIdx.x == 0) {
@@ -111,9 +117,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int m_blk, n_blk;
-        tile_coords(t, num_m, num_n, m_blk, n_blk);
-        for (int kb = 0; kb < num_k; ++kb) {
+        int m_blk, n_blk, split;
+        tile_coords(t, num_m, num_n, k_splits, m_blk, n_blk, split);
+        const int kb0 = split * k_per, kb1 = min(num_k_total, kb0 + k_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1)) {
             report_error(status, AXB_ERR_WAIT_EMPTY);
             ok = false;
@@ -159,7 +166,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        const int split = t % k_splits;
+        const int kb0 = split * k_per, kb1 = min(num_k_total, kb0 + k_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph)) {
             report_error(status, AXB_ERR_WAIT_FULL);
             ok = false;
@@ -174,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                      : umma_smem_desc(a0 + j * 32, 16, 1024);
             const uint64_t bd = B_MN ? umma_smem_desc(b0 + j * 2048, 8192, 1024)
                                      : umma_smem_desc(b0 + j * 32, 16, 1024);
-            umma_f16_ss(d_tmem, ad, bd, idesc, (kb | j) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, ad, bd, idesc, (kb != kb0 || j != 0) ? 1u : 0u);
           }
           tc_commit(&empty[s]);
           if (++s == S::STAGES) {
@@ -190,8 +199,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
-      int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      int m_blk, n_blk, split;
+      tile_coords(t, num_m, num_n, k_splits, m_blk, n_blk, split);
       const int buf = it & 1;
       if (!mbar_wait(&acc_full[buf], (it >> 1) & 1)) {
         report_error(status, AXB_ERR_WAIT_TMEM_FULL);
@@ -199,7 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tc_fence_after();
       const int row = m_blk * GEMM_BM + q * 32 + lane;
-      Epi epi(ep, m_blk, n_blk, row, shape);
+      Epi epi(ep, m_blk, n_blk, row, shape, split);
       const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -235,7 +244,7 @@ struct StoreEpi {
   const Params& p;
   const GemmShape& sh;
   int row;
-  __device__ StoreEpi(const Params& p_, int, int, int row_, const GemmShape& sh_)
+  __device__ StoreEpi(const Params& p_, int, int, int row_, const GemmShape& sh_, int)
       : p(p_), sh(sh_), row(row_) {}
   __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
     if (row >= sh.M || col0 >= sh.N) return;
@@ -281,6 +290,46 @@ struct StoreEpi {
           c[j] = accum ? c[j] + v : v;
         }
       }
+    }
+  }
+  __device__ __forceinline__ void finish() {}
+};
+
+// ------------------------------------------------------------------------- transposed epilogue
+// For "swap-AB" products (weights as the 128-row operand, a small token batch as the N operand):
+// the accumulator row is an output FEATURE and the column a TOKEN, so element (row, col) goes to
+// C[col][row]. Lanes of a warp hold consecutive rows, hence each store instruction writes 32
+// consecutive elements of one token row. With k_splits > 1 fp32 partials go to
+// ws[split][token][feature] and a reduce kernel finishes; with one split the final dtype is written.
+struct TransposedEpi {
+  struct Params {
+    void* C;          // [tokens][ldc] bf16 (mode 0) or fp32 (mode 1)
+    long long ldc;
+    int mode;
+    float* ws;        // [k_splits][tokens][features] fp32, used when k_splits > 1
+  };
+  const Params& p;
+  const GemmShape& sh;
+  int row, split;
+  __device__ TransposedEpi(const Params& p_, int, int, int row_, const GemmShape& sh_, int split_)
+      : p(p_), sh(sh_), row(row_), split(split_) {}
+  __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
+    if (row >= sh.M || col0 >= sh.N) return;
+    if (sh.k_splits > 1) {
+      float* w = p.ws + ((long long)split * sh.N + col0) * sh.M + row;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < sh.N) w[(long long)j * sh.M] = __uint_as_float(acc[j]);
+    } else if (p.mode == 0) {
+      __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)col0 * p.ldc + row;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < sh.N) c[(long long)j * p.ldc] = __float2bfloat16(__uint_as_float(acc[j]));
+    } else {
+      float* c = reinterpret_cast<float*>(p.C) + (long long)col0 * p.ldc + row;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < sh.N) c[(long long)j * p.ldc] = __uint_as_float(acc[j]);
     }
   }
   __device__ __forceinline__ void finish() {}

@@ -28,7 +28,7 @@ struct StatsEpi {
   int row, n_blk;
   float m, s, sx;
   int label;
-  __device__ StatsEpi(const Params& p_, int, int n_blk_, int row_, const GemmShape& sh_)
+  __device__ StatsEpi(const Params& p_, int, int n_blk_, int row_, const GemmShape& sh_, int)
       : p(p_), sh(sh_), row(row_), n_blk(n_blk_), m(-INFINITY), s(0.f), sx(0.f) {
     label = row < sh.M ? p.labels[row] : -1;
   }
@@ -121,7 +121,7 @@ struct DLogitsEpi {
   const GemmShape& sh;
   int row, label;
   float lse, ent, glp, gent;
-  __device__ DLogitsEpi(const Params& p_, int, int, int row_, const GemmShape& sh_)
+  __device__ DLogitsEpi(const Params& p_, int, int, int row_, const GemmShape& sh_, int)
       : p(p_), sh(sh_), row(row_) {
     const bool v = row < sh.M;
     label = v ? p.labels[row] : -1;
@@ -179,7 +179,7 @@ static int launch_head(const void* hidden, const void* W, int M, int V, int H, l
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((V + 255) / 256);
   int grid = sm_count();
   if (tiles < grid) grid = tiles;
-  GemmShape sh{M, V, H};
+  GemmShape sh{M, V, H, 1};
   kern<<<grid, GEMM_THREADS, GemmSmem<256>::TOTAL, stream>>>(tmA, tmB, sh, ep, status);
   return check_launch();
 }

@@ -58,3 +58,15 @@ def test_gemm_accumulate_and_alpha():
 def test_gemm_deterministic():
     a, b = _rand(512, 1024), _rand(768, 1024)
     assert torch.equal(G.gemm_nt(a, b), G.gemm_nt(a, b))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (17, 1024, 4096), (64, 6144, 4096), (100, 4096, 12288),
+                                   (256, 24576 // 4, 4096), (200, 8192 + 40, 1024)])
+def test_gemm_small_m_swap_ab(M, N, K):
+    a, b = _rand(M, K), _rand(N, K)
+    ref = a.float() @ b.float().t()
+    _check(G.gemm_nt(a, b), ref, K)
+    _check(G.gemm_nt(a, b, out_dtype=torch.float32), ref, K)
+    assert torch.equal(G.gemm_nt(a, b), G.gemm_nt(a, b))
+    C.check_status()
