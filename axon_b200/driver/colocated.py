@@ -125,6 +125,7 @@ class ColocatedRLRunner:
         return torch.cuda.mem_get_info(self.device)[0]
 
     def _enter_rollout(self) -> None:
+        ta = time.perf_counter()
         self.model.params.free_grads()
         need = PagedKVCache.bytes_per_page(self.model.cfg, self.model.params.flat.element_size())
         want_pages = self.cfg.max_num_seqs * ((self.cfg.max_prompt_length + self.cfg.max_response_length) // 128 + 1)
@@ -133,6 +134,7 @@ class ColocatedRLRunner:
             off = self._free_bytes() * self.cfg.kv_memory_fraction < want_pages * need * 0.5
         if off:
             self.policy.offload_optimizer()
+        tb = time.perf_counter()
         pages = int(min(want_pages, self._free_bytes() * self.cfg.kv_memory_fraction // need))
         if self.engine is None:
             self.engine = GenerationEngine(self.model, num_pages=pages, max_num_seqs=self.cfg.max_num_seqs,
@@ -140,6 +142,8 @@ class ColocatedRLRunner:
                                            seed=self.seed + self.rank)
         else:
             self.engine.wake_up(pages)
+        self.engine.set_max_model_len(self.cfg.max_prompt_length + self.cfg.max_response_length)
+        self.phase_detail = dict(offload=tb - ta, kv_alloc=time.perf_counter() - tb, kv_pages=pages, offloaded=bool(off))
 
     def _enter_training(self) -> None:
         self.engine.sleep()
