@@ -1,0 +1,281 @@
+"""Sampler server: runs one ``GenerationEngine`` on its own thread and serves concurrent generation
+requests with continuous batching. Callers get futures (in-process) or use the OpenAI-compatible
+HTTP routes. Control surface follows the reference's vLLM server wrapper
+(axon/sampler/vllm/server.py:379-845, axon/sampler/base/server.py:35-181): ``/v1/completions`` with
+prompt token ids in and ``token_ids`` / ``logprobs`` / ``routed_experts`` out, ``/pause_generation``
+with strategy ``drain | hold | continue | reset``, ``/continue_generation``, sleep and wake.
+"""
+from __future__ import annotations
+
+import asyncio
+import base64
+import queue
+import threading
+import time
+from concurrent.futures import Future
+from enum import Enum
+
+import numpy as np
+
+from .params import SamplingParams, TokenOutput
+
+
+class SamplerMode(Enum):
+    HYBRID = "hybrid"          # shares GPUs and weights with the trainer, alternates with it
+    COLOCATED = "colocated"    # same node, own GPUs
+    STANDALONE = "standalone"  # separate sampler pool (disaggregated)
+
+
+SERVER_REGISTRY: dict[str, type] = {}
+
+
+def register_server(name: str):
+    def deco(cls):
+        SERVER_REGISTRY[name] = cls
+        return cls
+    return deco
+
+
+def params_from_dict(d: dict | None, default_max_tokens: int = 1024) -> SamplingParams:
+    d = dict(d or {})
+    return SamplingParams(
+        temperature=float(d.get("temperature", 1.0)), top_k=int(d.get("top_k", 0) or 0) if int(d.get("top_k", 0) or 0) > 0 else 0,
+        top_p=float(d.get("top_p", 1.0)), repetition_penalty=float(d.get("repetition_penalty", 1.0)),
+        max_tokens=int(d.get("max_tokens", default_max_tokens)), n=int(d.get("n", 1)),
+        stop_token_ids=tuple(d.get("stop_token_ids", ()) or ()), ignore_eos=bool(d.get("ignore_eos", False)),
+        seed=d.get("seed"))
+
+
+def encode_routed_experts(rm) -> dict | None:
+    """int16 routing record -> {data: base64, shape} (the wire format of ``routed_experts``)."""
+    if rm is None:
+        return None
+    arr = np.asarray(rm, dtype=np.int16)
+    return {"data": base64.b64encode(arr.tobytes()).decode("ascii"), "shape": list(arr.shape)}
+
+
+def decode_routed_experts(obj):
+    if not obj:
+        return None
+    arr = np.frombuffer(base64.b64decode(obj["data"]), dtype=np.int16)
+    return arr.reshape(obj["shape"]).copy()
+
+
+@register_server("native")
+class SamplerServer:
+    def __init__(self, engine, tokenizer=None, name: str = "sampler-0", mode: SamplerMode = SamplerMode.HYBRID):
+        self.engine, self.tokenizer, self.name, self.mode = engine, tokenizer, name, mode
+        self._inbox: "queue.Queue[tuple]" = queue.Queue()
+        self._futures: dict[int, Future] = {}
+        self._thread: threading.Thread | None = None
+        self._stop = threading.Event()
+        self._wake = threading.Event()
+        self._idle = threading.Event()
+        self._idle.set()
+        self._ctl_lock = threading.Lock()
+        self._paused_hold = False
+        self.error: BaseException | None = None
+
+    # ------------------------------------------------------------------ lifecycle
+    def start(self) -> "SamplerServer":
+        if self._thread is None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._loop, daemon=True, name=self.name)
+            self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._wake.set()
+        if self._thread is not None:
+            self._thread.join(timeout=30)
+            self._thread = None
+
+    def _loop(self) -> None:
+        eng = self.engine
+        try:
+            if eng.device.type == "cuda":
+                import torch
+                torch.cuda.set_device(eng.device)
+            while not self._stop.is_set():
+                self._drain_inbox()
+                busy = eng.has_unfinished() and eng.cache is not None and not self._paused_hold
+                if busy:
+                    self._idle.clear()
+                    with self._ctl_lock:
+                        eng.step()
+                    self._resolve()
+                else:
+                    self._resolve()
+                    self._idle.set()
+                    self._wake.wait(0.005)
+                    self._wake.clear()
+        except BaseException as e:  # noqa: BLE001
+            self.error = e
+            for f in self._futures.values():
+                if not f.done():
+                    f.set_exception(e)
+            self._futures.clear()
+            self._idle.set()
+
+    def _drain_inbox(self) -> None:
+        while True:
+            try:
+                prompt, params, fut = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+            rid = self.engine.add_request(prompt, params)
+            self._futures[rid] = fut
+
+    def _resolve(self) -> None:
+        fin = self.engine.finished
+        for rid in list(fin):
+            fut = self._futures.pop(rid, None)
+            out = fin.pop(rid)
+            if fut is not None and not fut.done():
+                fut.set_result(out)
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, prompt_ids, params: SamplingParams | dict | None = None) -> Future:
+        if self.error is not None:
+            raise RuntimeError(f"sampler server '{self.name}' has failed") from self.error
+        if not isinstance(params, SamplingParams):
+            params = params_from_dict(params)
+        fut: Future = Future()
+        self._inbox.put((list(prompt_ids), params, fut))
+        self._wake.set()
+        return fut
+
+    async def generate(self, prompt_ids, params=None) -> TokenOutput:
+        return await asyncio.wrap_future(self.submit(prompt_ids, params))
+
+    def num_pending(self) -> int:
+        return len(self._futures) + self._inbox.qsize()
+
+    # ------------------------------------------------------------------ control
+    def pause_generation(self, strategy: str = "drain", timeout: float = 600.0) -> None:
+        """drain: wait for in-flight requests to finish (new ones queue). hold: freeze in place.
+        continue: do nothing (in-flight requests keep running across the weight update).
+        reset: abort in-flight requests; they resolve with finish_reason 'abort' and their partial text."""
+        if strategy == "continue":
+            return
+        if strategy == "hold":
+            self._paused_hold = True
+            self._wait_idle(timeout)
+            return
+        if strategy == "drain":
+            deadline = time.monotonic() + timeout
+            while self.num_pending() and time.monotonic() < deadline:
+                time.sleep(0.005)
+            return
+        if strategy == "reset":
+            with self._ctl_lock:
+                self.engine.pause("reset")
+                self.engine.resume()
+            self._wake.set()
+            return
+        raise ValueError(f"unknown pause strategy '{strategy}'")
+
+    def continue_generation(self) -> None:
+        self._paused_hold = False
+        self._wake.set()
+
+    def _wait_idle(self, timeout: float) -> None:
+        self._wake.set()
+        self._idle.wait(timeout)
+
+    def sleep(self) -> None:
+        self._paused_hold = True
+        self._wait_idle(60.0)
+        with self._ctl_lock:
+            self.engine.sleep()
+
+    def wake_up(self, num_pages: int | None = None) -> None:
+        with self._ctl_lock:
+            self.engine.wake_up(num_pages)
+        self._paused_hold = False
+        self._wake.set()
+
+    def update_weights(self, named_tensors) -> int:
+        """Copy (name, tensor) pairs into the engine's parameter views while generation is held."""
+        n = 0
+        with self._ctl_lock:
+            views = self.engine.model.params.views
+            hf_views = None
+            for name, t in named_tensors:
+                dst = views.get(name)
+                if dst is None:
+                    if hf_views is None:
+                        hf_views = self.engine.model.params.to_hf_state_dict()
+                    dst = hf_views.get(name)
+                if dst is None:
+                    raise KeyError(f"unknown parameter '{name}'")
+                dst.copy_(t.to(dst.dtype))
+                n += 1
+        return n
+
+    # ------------------------------------------------------------------ OpenAI-compatible HTTP app
+    def build_app(self):
+        from fastapi import FastAPI, HTTPException
+        app = FastAPI(title=f"axon_b200 sampler {self.name}")
+        server = self
+
+        @app.get("/health")
+        async def health():
+            return {"status": "ok" if server.error is None else "failed", "pending": server.num_pending()}
+
+        @app.get("/v1/models")
+        async def models():
+            return {"object": "list", "data": [{"id": server.name, "object": "model"}]}
+
+        @app.post("/v1/completions")
+        async def completions(body: dict):
+            prompt = body.get("prompt")
+            if isinstance(prompt, str):
+                if server.tokenizer is None:
+                    raise HTTPException(400, "text prompts need a tokenizer; send token ids")
+                prompt = server.tokenizer.encode(prompt)
+            if not isinstance(prompt, list) or (prompt and not isinstance(prompt[0], int)):
+                raise HTTPException(400, "prompt must be a list of token ids")
+            n = int(body.get("n", 1))
+            outs = await asyncio.gather(*(server.generate(prompt, body) for _ in range(n)))
+            choices = []
+            for i, o in enumerate(outs):
+                text = server.tokenizer.decode(o.token_ids) if server.tokenizer is not None else ""
+                strs = server.tokenizer.token_strs(o.token_ids) if hasattr(server.tokenizer, "token_strs") else []
+                choices.append({"index": i, "text": text, "token_ids": o.token_ids, "finish_reason": o.finish_reason,
+                                "stop_reason": o.stop_reason,
+                                "logprobs": {"token_logprobs": o.logprobs, "tokens": strs},
+                                "routed_experts": encode_routed_experts(o.moe_routermap)})
+            return {"object": "text_completion", "model": server.name, "choices": choices,
+                    "usage": {"prompt_tokens": len(prompt), "completion_tokens": sum(len(o.token_ids) for o in outs)}}
+
+        @app.post("/tokenize")
+        async def tokenize(body: dict):
+            if server.tokenizer is None:
+                raise HTTPException(400, "no tokenizer")
+            ids = server.tokenizer.encode(body.get("prompt", ""))
+            return {"tokens": ids, "count": len(ids)}
+
+        @app.post("/pause_generation")
+        async def pause(body: dict | None = None):
+            strategy = (body or {}).get("strategy", "drain")
+            await asyncio.get_running_loop().run_in_executor(None, server.pause_generation, strategy)
+            return {"status": "paused", "strategy": strategy}
+
+        @app.post("/continue_generation")
+        async def cont():
+            server.continue_generation()
+            return {"status": "running"}
+
+        @app.post("/sleep")
+        async def sleep():
+            await asyncio.get_running_loop().run_in_executor(None, server.sleep)
+            return {"status": "asleep"}
+
+        @app.post("/wake_up")
+        async def wake():
+            await asyncio.get_running_loop().run_in_executor(None, server.wake_up)
+            return {"status": "awake"}
+
+        return app
