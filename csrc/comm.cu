@@ -1,0 +1,364 @@
+// Kernels that move data between GPUs through NVLink peer memory (plain peer loads / stores on
+// pointers obtained from symmetric-memory or CUDA-IPC mappings; no NCCL, no TMA multicast).
+//
+//   peer_barrier        device-side barrier over per-rank signal pads, bounded wait + status word
+//   zero1_reduce        gradient reduce-scatter: sum this rank's shard over all ranks' fp32 grad
+//                       buffers (peer loads), emit the reduced shard and sum-of-squares partials
+//   zero1_adamw_bcast   sharded AdamW on the reduced shard (clip coefficient / skip flag read on the
+//                       device) + all-gather fused as peer STORES of the new bf16 values into every
+//                       rank's parameter buffer
+//   p2p_copy_plan       trainer -> sampler weight sync: executes a compiled RoutingTable plan (strided
+//                       2-D slice copies between arbitrary ranks) in ONE launch; optional fused
+//                       bf16 -> fp8(e4m3) 128x128 block-scaled quantisation on the way
+//
+// Every wait on another rank is bounded (AXB_PEER_WAIT_CYCLES) and reports AXB_ERR_WAIT_PEER in the
+// status word instead of spinning forever.
+#include "ptx.cuh"
+#include "host_utils.h"
+#include <cuda_fp8.h>
+
+namespace axb {
+
+#ifndef AXB_PEER_WAIT_CYCLES
+#define AXB_PEER_WAIT_CYCLES (1ll << 32)   // ~2 s
+#endif
+
+constexpr int MAX_RANKS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* addr, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* addr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// Each rank owns a pad of `world` 32-bit slots. Arriving at the barrier with epoch e means writing e
+// into slot[rank] of every peer's pad, then waiting until every slot of the own pad holds >= e.
+// One block, >= world threads. Epochs must increase by one per barrier on every rank.
+__global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int world, unsigned int epoch, int* status) {
+  const int t = threadIdx.x;
+  __threadfence_system();
+  if (t < world) {
+    st_release_sys(reinterpret_cast<unsigned int*>(pads.p[t]) + rank, epoch);
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(pads.p[rank]) + t;
+    const long long t0 = clock64();
+    while (static_cast<int>(ld_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - t0 > AXB_PEER_WAIT_CYCLES) {
+        report_error(status, AXB_ERR_WAIT_PEER);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  __threadfence_system();
+}
+
+// out[i] = sum_r grads[r][lo + i] for i in [0, n); partial[block] = sum of out^2 over the block's slice.
+// The own rank is read first so local traffic overlaps the remote request latency.
+__global__ void __launch_bounds__(256)
+zero1_reduce_kernel(PeerPtrs grads, int rank, int world, long long lo, long long n, float* __restrict__ out,
+                    float* __restrict__ partial) {
+  __shared__ float red[8];
+  float ss = 0.f;
+  const long long n4 = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[rank]) + lo)[i];
+#pragma unroll 1
+    for (int k = 1; k < world; ++k) {
+      const int r = (rank + k) % world;
+      const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  for (long long i = n4 * 4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < world; ++k) acc += reinterpret_cast<const float*>(grads.p[(rank + k) % world])[lo + i];
+    out[i] = acc;
+    ss += acc * acc;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float r = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+    r = warp_sum(r);
+    if (threadIdx.x == 0) partial[blockIdx.x] = r;
+  }
+}
+
+// AdamW on the reduced shard; the new bf16 value of element lo + i is stored into EVERY rank's
+// parameter buffer (the all-gather). state: [sumsq, norm, clip coef, skip flag] as in optim.cu.
+__global__ void __launch_bounds__(256)
+zero1_adamw_bcast_kernel(float* __restrict__ master, const float* __restrict__ grad, float* __restrict__ m,
+                         float* __restrict__ v, PeerPtrs params, int world, long long lo, long long n, float lr,
+                         float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                         const float* __restrict__ state) {
+  if (state != nullptr && state[3] != 0.f) return;
+  const float coef = state != nullptr ? state[2] : 1.f;
+  const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
+  const long long n8 = n / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float p[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const long long j = i * 8 + k;
+      const float g = grad[j] * coef;
+      const float mi = beta1 * m[j] + (1.f - beta1) * g;
+      const float vi = beta2 * v[j] + (1.f - beta2) * g * g;
+      m[j] = mi;
+      v[j] = vi;
+      float w = master[j];
+      w -= lr * wd * w;
+      w -= lr * (mi * inv_bc1) / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+      master[j] = w;
+      p[k] = w;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(p[0], p[1]);
+    o.y = pack_bf16x2(p[2], p[3]);
+    o.z = pack_bf16x2(p[4], p[5]);
+    o.w = pack_bf16x2(p[6], p[7]);
+#pragma unroll 1
+    for (int r = 0; r < world; ++r)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + lo)[i] = o;
+  }
+  for (long long j = n8 * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; j < n;
+       j += (long long)gridDim.x * blockDim.x) {
+    const float g = grad[j] * coef;
+    const float mi = beta1 * m[j] + (1.f - beta1) * g;
+    const float vi = beta2 * v[j] + (1.f - beta2) * g * g;
+    m[j] = mi;
+    v[j] = vi;
+    float w = master[j];
+    w -= lr * wd * w;
+    w -= lr * (mi * inv_bc1) / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+    master[j] = w;
+    for (int r = 0; r < world; ++r) reinterpret_cast<__nv_bfloat16*>(params.p[r])[lo + j] = __float2bfloat16(w);
+  }
+}
+
+// ------------------------------------------------------------------------------ weight-sync plan
+// One descriptor = one strided 2-D slice copy src[rows][cols] -> dst[rows][cols] (element offsets and
+// row strides in elements of the bf16 source / destination buffers). quant: 0 = bf16 copy,
+// 1 = quantise to fp8 e4m3 with one fp32 scale per 128x128 block (dst buffers are then fp8 bytes and
+// dst_scale_off indexes the fp32 scale buffer of the destination rank, row-major over blocks).
+struct CopyDesc {
+  long long src_off, dst_off;
+  int rows, cols;
+  long long src_stride, dst_stride;
+  int dst_rank, quant;
+  long long dst_scale_off;
+  int scale_cols, pad;
+};
+
+__global__ void __launch_bounds__(256)
+p2p_copy_plan_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, PeerPtrs dst_scales,
+                     const CopyDesc* __restrict__ descs, const long long* __restrict__ work_prefix, int n_desc,
+                     long long total_work) {
+  // Work items: 16-byte vectors (bf16 copy) laid out descriptor after descriptor; work_prefix[d] is
+  // the first item of descriptor d. Each block claims a contiguous span so its stores stay sequential.
+  __shared__ int s_desc;
+  const long long per_block = (total_work + gridDim.x - 1) / gridDim.x;
+  const long long w0 = (long long)blockIdx.x * per_block;
+  const long long w1 = min(total_work, w0 + per_block);
+  if (w0 >= w1) return;
+  if (threadIdx.x == 0) {
+    int lo = 0, hi = n_desc - 1;            // last descriptor whose prefix <= w0
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (work_prefix[mid] <= w0) lo = mid; else hi = mid - 1;
+    }
+    s_desc = lo;
+  }
+  __syncthreads();
+  int d = s_desc;
+  for (long long w = w0 + threadIdx.x; w < w1; w += blockDim.x) {
+    while (d + 1 < n_desc && work_prefix[d + 1] <= w) ++d;
+    const CopyDesc& c = descs[d];
+    const long long local = w - work_prefix[d];
+    const int vec_per_row = (c.cols + 7) / 8;
+    const int r = (int)(local / vec_per_row);
+    const int cv = (int)(local - (long long)r * vec_per_row);
+    const __nv_bfloat16* s = src + c.src_off + (long long)r * c.src_stride + cv * 8;
+    __nv_bfloat16* t = reinterpret_cast<__nv_bfloat16*>(dst.p[c.dst_rank]) + c.dst_off + (long long)r * c.dst_stride + cv * 8;
+    const int left = c.cols - cv * 8;
+    if (left >= 8 && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(t)) & 15) == 0) {
+      *reinterpret_cast<uint4*>(t) = *reinterpret_cast<const uint4*>(s);
+    } else {
+      for (int k = 0; k < left && k < 8; ++k) t[k] = s[k];
+    }
+  }
+}
+
+// Quantising variant: one CTA per 128x128 block of a descriptor. amax over the block, scale =
+// amax / 448 (1 when amax is 0 or not finite), fp8 = sat(x / scale); the scale is what the consumer
+// multiplies by (the "weight_scale_inv" of block-scaled fp8 checkpoints).
+struct QuantTile {
+  int desc, block_row, block_col, pad;
+};
+__global__ void __launch_bounds__(256)
+p2p_quant_plan_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, PeerPtrs dst_scales,
+                      const CopyDesc* __restrict__ descs, const QuantTile* __restrict__ tiles, int n_tiles) {
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  for (int ti = blockIdx.x; ti < n_tiles; ti += gridDim.x) {
+    const QuantTile q = tiles[ti];
+    const CopyDesc& c = descs[q.desc];
+    const int r0 = q.block_row * 128, c0 = q.block_col * 128;
+    const int nr = min(128, c.rows - r0), nc = min(128, c.cols - c0);
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < nr * 16; i += blockDim.x) {   // 16 vectors of 8 per 128-wide row
+      const int r = i >> 4, cv = (i & 15) * 8;
+      const __nv_bfloat16* s = src + c.src_off + (long long)(r0 + r) * c.src_stride + c0 + cv;
+      for (int k = 0; k < 8 && cv + k < nc; ++k) amax = fmaxf(amax, fabsf(__bfloat162float(s[k])));
+    }
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float a = red[0];
+      for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
+      const float scale = (a > 0.f && isfinite(a)) ? a / 448.f : 1.f;
+      s_scale = scale;
+      reinterpret_cast<float*>(dst_scales.p[c.dst_rank])[c.dst_scale_off + (long long)q.block_row * c.scale_cols + q.block_col] = scale;
+    }
+    __syncthreads();
+    const float inv = 1.f / s_scale;
+    unsigned char* t0 = reinterpret_cast<unsigned char*>(dst.p[c.dst_rank]);
+    for (int i = threadIdx.x; i < nr * 16; i += blockDim.x) {
+      const int r = i >> 4, cv = (i & 15) * 8;
+      const __nv_bfloat16* s = src + c.src_off + (long long)(r0 + r) * c.src_stride + c0 + cv;
+      unsigned char* t = t0 + c.dst_off + (long long)(r0 + r) * c.dst_stride + c0 + cv;
+      for (int k = 0; k < 8 && cv + k < nc; ++k) {
+        const __nv_fp8_e4m3 f(__bfloat162float(s[k]) * inv);
+        t[k] = *reinterpret_cast<const unsigned char*>(&f);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Stand-alone bf16 -> fp8 e4m3 128x128 block quantisation of a local [rows][cols] matrix.
+__global__ void __launch_bounds__(256)
+fp8_block_quant_kernel(const __nv_bfloat16* __restrict__ x, unsigned char* __restrict__ y, float* __restrict__ scales,
+                       int rows, int cols, long long ldx, long long ldy) {
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  const int bc = (cols + 127) / 128;
+  const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 128;
+  const int nr = min(128, rows - r0), nc = min(128, cols - c0);
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < nr * 128; i += blockDim.x) {
+    const int r = i >> 7, cc = i & 127;
+    if (cc < nc) amax = fmaxf(amax, fabsf(__bfloat162float(x[(long long)(r0 + r) * ldx + c0 + cc])));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = red[0];
+    for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
+    s_scale = (a > 0.f && isfinite(a)) ? a / 448.f : 1.f;
+    scales[(long long)blockIdx.y * bc + blockIdx.x] = s_scale;
+  }
+  __syncthreads();
+  const float inv = 1.f / s_scale;
+  for (int i = threadIdx.x; i < nr * 128; i += blockDim.x) {
+    const int r = i >> 7, cc = i & 127;
+    if (cc < nc) {
+      const __nv_fp8_e4m3 f(__bfloat162float(x[(long long)(r0 + r) * ldx + c0 + cc]) * inv);
+      y[(long long)(r0 + r) * ldy + c0 + cc] = *reinterpret_cast<const unsigned char*>(&f);
+    }
+  }
+}
+
+}  // namespace axb
+
+using namespace axb;
+
+static int fill_ptrs(PeerPtrs& out, const unsigned long long* ptrs, int world) {
+  if (world < 1 || world > MAX_RANKS) return AXB_LAUNCH_BAD_ARG;
+  for (int i = 0; i < MAX_RANKS; ++i) out.p[i] = i < world ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return AXB_LAUNCH_OK;
+}
+
+extern "C" int axb_peer_barrier(const unsigned long long* pad_ptrs, int rank, int world, unsigned int epoch,
+                                int* status, void* stream) {
+  PeerPtrs pads;
+  if (int rc = fill_ptrs(pads, pad_ptrs, world)) return rc;
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pads, rank, world, epoch, status);
+  return check_launch();
+}
+
+extern "C" int axb_zero1_partials(void) { return sm_count() * 4; }
+
+// out: fp32 [n] reduced shard; partial: fp32 [axb_zero1_partials()].
+extern "C" int axb_zero1_reduce(const unsigned long long* grad_ptrs, int rank, int world, long long lo, long long n,
+                                float* out, float* partial, void* stream) {
+  PeerPtrs g;
+  if (int rc = fill_ptrs(g, grad_ptrs, world)) return rc;
+  if (n <= 0 || (lo & 3) != 0) return AXB_LAUNCH_BAD_ARG;
+  zero1_reduce_kernel<<<axb_zero1_partials(), 256, 0, (cudaStream_t)stream>>>(g, rank, world, lo, n, out, partial);
+  return check_launch();
+}
+
+extern "C" int axb_zero1_adamw_bcast(float* master, const float* grad, float* m, float* v,
+                                     const unsigned long long* param_ptrs, int world, long long lo, long long n,
+                                     float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                                     const float* state, void* stream) {
+  PeerPtrs p;
+  if (int rc = fill_ptrs(p, param_ptrs, world)) return rc;
+  if (n <= 0 || (lo & 7) != 0) return AXB_LAUNCH_BAD_ARG;
+  zero1_adamw_bcast_kernel<<<sm_count() * 4, 256, 0, (cudaStream_t)stream>>>(master, grad, m, v, p, world, lo, n, lr,
+                                                                            beta1, beta2, eps, wd, bc1, bc2, state);
+  return check_launch();
+}
+
+// descs / work_prefix / tiles live on the device. total_work = number of 16-byte vectors (copy mode).
+extern "C" int axb_p2p_copy_plan(const void* src, const unsigned long long* dst_ptrs, int world, const void* descs,
+                                 const long long* work_prefix, int n_desc, long long total_work, void* stream) {
+  PeerPtrs d, s;
+  if (int rc = fill_ptrs(d, dst_ptrs, world)) return rc;
+  fill_ptrs(s, dst_ptrs, world);
+  if (n_desc <= 0 || total_work <= 0) return AXB_LAUNCH_BAD_ARG;
+  long long blocks = (total_work + 2047) / 2048;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  p2p_copy_plan_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)src, d, s, (const CopyDesc*)descs, work_prefix, n_desc, total_work);
+  return check_launch();
+}
+
+extern "C" int axb_p2p_quant_plan(const void* src, const unsigned long long* dst_ptrs,
+                                  const unsigned long long* scale_ptrs, int world, const void* descs,
+                                  const void* tiles, int n_tiles, void* stream) {
+  PeerPtrs d, s;
+  if (int rc = fill_ptrs(d, dst_ptrs, world)) return rc;
+  if (int rc = fill_ptrs(s, scale_ptrs, world)) return rc;
+  if (n_tiles <= 0) return AXB_LAUNCH_BAD_ARG;
+  int blocks = n_tiles < sm_count() * 8 ? n_tiles : sm_count() * 8;
+  p2p_quant_plan_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, d, s,
+                                                                 (const CopyDesc*)descs, (const QuantTile*)tiles, n_tiles);
+  return check_launch();
+}
+
+extern "C" int axb_fp8_block_quant(const void* x, void* y, float* scales, int rows, int cols, long long ldx,
+                                   long long ldy, void* stream) {
+  if (rows <= 0 || cols <= 0) return AXB_LAUNCH_BAD_ARG;
+  dim3 grid((cols + 127) / 128, (rows + 127) / 128);
+  fp8_block_quant_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (unsigned char*)y, scales,
+                                                                rows, cols, ldx, ldy);
+  return check_launch();
+}
