@@ -1,0 +1,167 @@
+"""Named single-kernel workloads for timing and for ``ncu`` captures.
+
+    python -m axon_b200.utils.profiler.kernel_cases <case> [--iters N] [--small]
+
+Each case builds inputs larger than L2 where the kernel is memory-bound, runs warm-up iterations,
+times ``iters`` launches with CUDA events (L2 is flushed between timed launches by writing a 256 MB
+buffer) and prints one JSON line with the achieved rate and its fraction of the measured peaks
+(``MEASURED_PEAKS.json`` at the repository root when present, else 6650 GB/s and 1590 TFLOP/s).
+``--small`` shrinks the case so that a full-metric ``ncu`` capture of a few launches ends quickly.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+PEAK_GBS, PEAK_TFLOPS = 6650.0, 1590.0
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d.get("hbm_gbs", PEAK_GBS)), float(d.get("bf16_tflops", PEAK_TFLOPS)), "measured"
+    return PEAK_GBS, PEAK_TFLOPS, "fallback"
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def case_gemm_train(small):
+    from ...ops import gemm as G
+    M, N, K = (2048, 6144, 4096) if small else (8192, 6144, 4096)
+    a, b = bf(M, K), bf(N, K)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    return (lambda: G.gemm_nt(a, b, out=out)), dict(flops=2.0 * M * N * K, bytes=2.0 * (M * K + N * K + M * N), shape=[M, N, K])
+
+
+def case_gemm_wgrad(small):
+    from ...ops import gemm as G
+    T, N, K = (2048, 4096, 4096) if small else (8192, 12288, 4096)
+    dy, x = bf(T, N), bf(T, K)
+    out = torch.zeros(N, K, device="cuda", dtype=torch.float32)
+    return (lambda: G.gemm_tn(dy, x, out=out, accumulate=True)), dict(flops=2.0 * T * N * K, bytes=2.0 * T * (N + K) + 8.0 * N * K, shape=[T, N, K])
+
+
+def case_gemm_decode(small):
+    from ...ops import gemm as G
+    M, N, K = 256, 6144, 4096
+    a = bf(M, K)
+    ws = [bf(N, K) for _ in range(2 if small else 8)]       # rotate weights: 8 x 50 MB exceeds L2
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    st = {"i": 0}
+
+    def run():
+        st["i"] = (st["i"] + 1) % len(ws)
+        G.gemm_nt(a, ws[st["i"]], out=out)
+    return run, dict(flops=2.0 * M * N * K, bytes=2.0 * (M * K + N * K + M * N), shape=[M, N, K])
+
+
+def _qkv(lens, Hq, Hkv, D=128):
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    return bf(T, (Hq + 2 * Hkv) * D, scale=0.5), cu, T
+
+
+def _attn_flops(lens, Hq, D=128):
+    return sum(4.0 * L * L / 2 * Hq * D for L in lens)
+
+
+def case_attn_fwd(small):
+    from ...ops import attention as AT
+    lens = [1024] * 2 if small else [2731, 2731, 2730]
+    qkv, cu, T = _qkv(lens, 32, 8)
+    return (lambda: AT.attn_fwd(qkv, cu, 32, 8, 128)), dict(flops=_attn_flops(lens, 32), bytes=2.0 * T * (48 + 32) * 128, shape=lens)
+
+
+def case_attn_bwd(small):
+    from ...ops import attention as AT
+    lens = [1024] * 2 if small else [2731, 2731, 2730]
+    qkv, cu, T = _qkv(lens, 32, 8)
+    o, lse = AT.attn_fwd(qkv, cu, 32, 8, 128)
+    do = bf(T, 32 * 128)
+    return (lambda: AT.attn_bwd(do, qkv, o, lse, cu, 32, 8, 128)), dict(flops=3.5 * _attn_flops(lens, 32), bytes=2.0 * T * (48 * 2 + 64) * 128, shape=lens)
+
+
+def case_paged_decode(small):
+    from ...ops import paged as P
+    B, ctx, Hq, Hkv, D = (32, 1024, 32, 8, 128) if small else (256, 1536, 32, 8, 128)
+    pages_per = (ctx + 127) // 128
+    n_pages = B * pages_per
+    kc, vc = bf(n_pages, Hkv, 128, D, scale=0.3), bf(n_pages, Hkv, 128, D, scale=0.3)
+    bt = torch.randperm(n_pages, device="cuda").to(torch.int32).view(B, pages_per)
+    lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    q = bf(B, (Hq + 2 * Hkv) * D, scale=0.3)
+    return (lambda: P.paged_decode(q, kc, vc, bt, lens, Hq, Hkv, D)), dict(flops=4.0 * B * ctx * Hq * D, bytes=4.0 * B * ctx * Hkv * D, shape=[B, ctx])
+
+
+def case_lmhead_fwd(small):
+    from ...ops import lm_head as L
+    T, H, V = (1024, 4096, 151936) if small else (8192, 4096, 151936)
+    h, w = bf(T, H), bf(V, H, scale=0.02)
+    lab = torch.randint(0, V, (T,), dtype=torch.int32, device="cuda")
+    return (lambda: L.lmhead_fwd(h, w, lab, 1.0)), dict(flops=2.0 * T * H * V, bytes=2.0 * (T * H + V * H), shape=[T, H, V])
+
+
+def case_rmsnorm(small):
+    from ...ops import norm as N
+    T, H = (16384, 4096) if small else (65536, 4096)
+    x, d, w = bf(T, H), bf(T, H), bf(H)
+    return (lambda: N.rmsnorm_fwd(x, w, 1e-6, delta=d)), dict(flops=0.0, bytes=2.0 * T * H * 4, shape=[T, H])
+
+
+def case_adamw(small):
+    from ...ops import optim as O
+    n = (1 << 26) if small else (1 << 28)
+    master, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    p = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    return (lambda: O.adamw_step(master, p, g, m, v, 1e-5, 0.9, 0.95, 1e-8, 0.1, 3)), dict(flops=0.0, bytes=n * (4 * 7 + 2.0), shape=[n])
+
+
+CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode,
+         "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode,
+         "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=sorted(CASES) + ["all"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--small", action="store_true")
+    args = ap.parse_args()
+    from ...ops import _common as C
+    gbs, tfl, src = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in (sorted(CASES) if args.case == "all" else [args.case]):
+        fn, info = CASES[name](args.small)
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(args.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        C.check_status()
+        t = sorted(ms)[len(ms) // 2] * 1e-3
+        out = {"case": name, "shape": info["shape"], "ms": t * 1e3, "tflops": info["flops"] / t / 1e12,
+               "gbs": info["bytes"] / t / 1e9, "frac_of_" + src + "_tflops": info["flops"] / t / 1e12 / tfl,
+               "frac_of_" + src + "_hbm": info["bytes"] / t / 1e9 / gbs, "l2": "flushed between timed launches"}
+        print(json.dumps(out))
+        del fn
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
