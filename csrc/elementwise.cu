@@ -521,3 +521,73 @@ extern "C" int axb_add_bf16(const void* a, const void* b, void* y, long long n, 
       (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n / 8);
   return check_launch();
 }
+
+// --------------------------------------------------------- RMSNorm backward, workspace built in
+#include "rmsnorm_bwd_static.h"
+#include <cstdio>
+
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[AXB_RMSNORM_BWD_STATIC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices] = {};
+thread_local char g_static_err[192] = "";
+
+int static_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_static_err, sizeof(g_static_err), "rmsnorm_bwd_static: no usable current device (%s)",
+             cudaGetErrorString(e));
+    return AXB_LAUNCH_CUDA_ERROR;
+  }
+  if (g_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_rmsnorm_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_static_err, sizeof(g_static_err),
+               "rmsnorm_bwd_static: cudaGetSymbolAddress failed on device %d (%s)", dev,
+               cudaGetErrorString(e));
+      return AXB_LAUNCH_CUDA_ERROR;
+    }
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return AXB_LAUNCH_OK;
+}
+}  // namespace
+
+extern "C" const char* axb_rmsnorm_bwd_static_error(void) { return g_static_err; }
+
+extern "C" int axb_rmsnorm_bwd_static_setup(void) {
+  float* p = nullptr;
+  g_static_err[0] = 0;
+  return static_scratch(&p);
+}
+
+extern "C" int axb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd,
+                                      const void* dres, void* dx, float* dw, int dw_accumulate,
+                                      long long T, int H, void* stream) {
+  g_static_err[0] = 0;
+  if (H % 8 != 0 || H <= 0 || T <= 0 || H > NORM_THREADS * 8 * 4) {
+    snprintf(g_static_err, sizeof(g_static_err),
+             "rmsnorm_bwd_static: need T > 0 and H a multiple of 8 up to %d (got T=%lld H=%d)",
+             NORM_THREADS * 8 * 4, T, H);
+    return AXB_LAUNCH_BAD_ARG;
+  }
+  const long long need = (long long)axb_rmsnorm_bwd_partials(T) * H;
+  if (need > (long long)AXB_RMSNORM_BWD_STATIC_MAX_FLOATS) {
+    snprintf(g_static_err, sizeof(g_static_err),
+             "rmsnorm_bwd_static: T=%lld H=%d needs %lld workspace floats, the built-in workspace "
+             "holds %d; use axb_rmsnorm_bwd with a caller-owned workspace",
+             T, H, need, AXB_RMSNORM_BWD_STATIC_MAX_FLOATS);
+    return AXB_LAUNCH_TOO_LARGE;
+  }
+  float* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc) return rc;
+  rc = axb_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw, dw_accumulate, scratch, T, H, stream);
+  if (rc)
+    snprintf(g_static_err, sizeof(g_static_err), "rmsnorm_bwd_static: launch failed with code %d", rc);
+  return rc;
+}
