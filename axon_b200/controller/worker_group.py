@@ -36,6 +36,31 @@ class ClassWithInitArgs:
     def __call__(self):
         return self.cls(*self.args, **self.kwargs)
 
+    # A class assembled at run time (``synthesize_class``) cannot be pickled by reference; its recipe
+    # (name, base, mixins) travels instead and the worker process assembles it again.
+    def __getstate__(self):
+        state = dict(self.__dict__)
+        spec = getattr(self.cls, "_synth_spec", None)
+        if spec is not None:
+            state["cls"] = None
+            state["_spec"] = spec
+        return state
+
+    def __setstate__(self, state):
+        spec = state.pop("_spec", None)
+        self.__dict__.update(state)
+        if spec is not None:
+            self.cls = synthesize_class(*spec)
+
+
+def synthesize_class(name: str, base: type, mixins: tuple = ()) -> type:
+    """``type(name, (*mixins, base), {})`` that remembers its recipe (see ``ClassWithInitArgs``)."""
+    if not mixins:
+        return base
+    cls = type(name, (*mixins, base), {})
+    cls._synth_spec = (name, base, tuple(mixins))
+    return cls
+
 
 class WorkerDiedError(RuntimeError):
     pass
@@ -139,85 +164,140 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker_main(conn, factory: ClassWithInitArgs, env: dict) -> None:
+def _worker_main(conn, factory: ClassWithInitArgs, env: dict, max_concurrency: int = 4) -> None:
+    """Worker process body. Calls run on a small thread pool so that a long call (a rollout) does not
+    block a short one that must overlap with it (pause, weight receive); replies carry the call id."""
     os.environ.update(env)
     try:
         obj = factory()
-        conn.send(("ready", None))
+        conn.send(("ready", None, None))
     except BaseException:  # noqa: BLE001
-        conn.send(("error", traceback.format_exc()))
+        conn.send(("error", None, traceback.format_exc()))
         return
-    while True:
-        try:
-            msg = conn.recv()
-        except (EOFError, OSError):
-            return
-        if msg is None:
-            return
-        name, args, kwargs = msg
+    send_lock = threading.Lock()
+    pool = ThreadPoolExecutor(max_workers=max(1, max_concurrency), thread_name_prefix="rpc-exec")
+
+    def execute(call_id, name, args, kwargs):
         try:
             res = getattr(obj, name)(*args, **kwargs)
             if hasattr(res, "__await__"):
                 import asyncio
                 res = asyncio.run(res)
-            conn.send(("ok", res))
+            reply = ("ok", call_id, res)
         except BaseException:  # noqa: BLE001
-            conn.send(("error", traceback.format_exc()))
+            reply = ("error", call_id, traceback.format_exc())
+        with send_lock:
+            try:
+                conn.send(reply)
+            except Exception:  # noqa: BLE001 - result not picklable
+                conn.send(("error", call_id, "result could not be pickled:\n" + traceback.format_exc()))
+
+    while True:
+        try:
+            msg = conn.recv()
+        except (EOFError, OSError):
+            break
+        if msg is None:
+            break
+        call_id, name, args, kwargs = msg
+        pool.submit(execute, call_id, name, args, kwargs)
+    pool.shutdown(wait=False, cancel_futures=True)
+    os._exit(0)
 
 
 class _ProcessWorker:
-    def __init__(self, rank: int, factory: ClassWithInitArgs, env: dict, ctx):
+    def __init__(self, rank: int, factory: ClassWithInitArgs, env: dict, ctx, max_concurrency: int = 4):
         self.rank = rank
         self.conn, child = ctx.Pipe()
-        self.proc = ctx.Process(target=_worker_main, args=(child, factory, env), daemon=True)
+        self.proc = ctx.Process(target=_worker_main, args=(child, factory, env, max_concurrency), daemon=True)
         self.proc.start()
         child.close()
-        self.pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix=f"rpc-{rank}")
+        self._send_lock = threading.Lock()
+        self._pending: dict[int, Future] = {}
+        self._pending_lock = threading.Lock()
+        self._next_id = 0
+        self._reader: threading.Thread | None = None
 
     def wait_ready(self, timeout: float) -> None:
         if not self.conn.poll(timeout):
             raise RPCTimeoutError(f"worker {self.rank} did not start within {timeout}s")
-        tag, payload = self.conn.recv()
+        tag, _, payload = self.conn.recv()
         if tag != "ready":
             raise RuntimeError(f"worker {self.rank} failed to start:\n{payload}")
+        self._reader = threading.Thread(target=self._read_loop, daemon=True, name=f"rpc-read-{self.rank}")
+        self._reader.start()
 
-    def call(self, name, args, kwargs, timeout):
-        def run():
+    def _fail_all(self, exc: BaseException) -> None:
+        with self._pending_lock:
+            pend, self._pending = self._pending, {}
+        for fut in pend.values():
+            if not fut.done():
+                fut.set_exception(exc)
+
+    def _read_loop(self) -> None:
+        while True:
             try:
-                self.conn.send((name, args, kwargs))
-            except (BrokenPipeError, OSError) as e:
-                raise WorkerDiedError(f"worker {self.rank} is gone") from e
-            deadline = None if timeout is None else time.monotonic() + timeout
-            while True:
-                if self.conn.poll(0.2):
-                    try:
-                        tag, payload = self.conn.recv()
-                    except (EOFError, OSError) as e:
-                        raise WorkerDiedError(f"worker {self.rank} died during '{name}'") from e
-                    if tag == "ok":
-                        return payload
-                    raise RuntimeError(f"worker {self.rank} raised in '{name}':\n{payload}")
-                if not self.proc.is_alive():
-                    raise WorkerDiedError(f"worker {self.rank} died during '{name}'")
-                if deadline is not None and time.monotonic() > deadline:
-                    raise RPCTimeoutError(f"worker {self.rank}: '{name}' exceeded {timeout}s")
-        return self.pool.submit(run)
+                if not self.conn.poll(0.2):
+                    if not self.proc.is_alive():
+                        self._fail_all(WorkerDiedError(f"worker {self.rank} died"))
+                        return
+                    continue
+                tag, call_id, payload = self.conn.recv()
+            except (EOFError, OSError):
+                self._fail_all(WorkerDiedError(f"worker {self.rank} is gone"))
+                return
+            with self._pending_lock:
+                fut = self._pending.pop(call_id, None)
+            if fut is None or fut.done():
+                continue
+            if tag == "ok":
+                fut.set_result(payload)
+            else:
+                fut.set_exception(RuntimeError(f"worker {self.rank} raised:\n{payload}"))
+
+    def call(self, name, args, kwargs, timeout) -> Future:
+        fut: Future = Future()
+        with self._pending_lock:
+            call_id = self._next_id
+            self._next_id += 1
+            self._pending[call_id] = fut
+        try:
+            with self._send_lock:
+                self.conn.send((call_id, name, args, kwargs))
+        except (BrokenPipeError, OSError) as e:
+            with self._pending_lock:
+                self._pending.pop(call_id, None)
+            fut.set_exception(WorkerDiedError(f"worker {self.rank} is gone"))
+            fut.__cause__ = e
+            return fut
+        if timeout is not None:
+            def expire():
+                with self._pending_lock:
+                    f = self._pending.pop(call_id, None)
+                if f is not None and not f.done():
+                    f.set_exception(RPCTimeoutError(f"worker {self.rank}: '{name}' exceeded {timeout}s"))
+            t = threading.Timer(timeout, expire)
+            t.daemon = True
+            t.start()
+            fut.add_done_callback(lambda _f: t.cancel())
+        return fut
 
     def shutdown(self) -> None:
         try:
-            self.conn.send(None)
+            with self._send_lock:
+                self.conn.send(None)
         except (BrokenPipeError, OSError):
             pass
         self.proc.join(timeout=5)
         if self.proc.is_alive():
             self.proc.terminate()
-        self.pool.shutdown(wait=False)
+        self._fail_all(WorkerDiedError(f"worker {self.rank} was shut down"))
 
 
 class LocalWorkerGroup(WorkerGroup):
     def __init__(self, resource_pool=None, cls_with_init: ClassWithInitArgs | None = None, backend: str = "process",
                  world_size: int | None = None, env: dict | None = None, rpc_timeout: float | None = 600.0,
-                 start_timeout: float = 300.0, bind: bool = True):
+                 start_timeout: float = 300.0, bind: bool = True, max_concurrency: int = 4):
         super().__init__()
         assert backend in ("process", "inline")
         self.backend = backend
@@ -242,7 +322,7 @@ class LocalWorkerGroup(WorkerGroup):
                         else:
                             os.environ[k] = v
             else:
-                self._workers.append(_ProcessWorker(rank, cls_with_init, wenv, mp.get_context("spawn")))
+                self._workers.append(_ProcessWorker(rank, cls_with_init, wenv, mp.get_context("spawn"), max_concurrency))
         if backend == "process":
             for w in self._workers:
                 w.wait_ready(start_timeout)

@@ -133,6 +133,56 @@ class DenseModel:
         return dx
 
     # ------------------------------------------------------------------ whole model
+    def _trunk_fwd(self, batch: PackedBatch, save_for_backward: bool):
+        """Embedding + all layers + final norm. Returns (hf, state) with state holding what backward needs."""
+        c = self.cfg
+        tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
+        x = A.embedding_fwd(batch.input_ids, self.params["model.embed_tokens.weight"])
+        delta = None
+        layer_inputs = []
+        for l in range(c.num_hidden_layers):
+            x, delta, xin = self.layer_fwd(l, x, delta, batch, tables, keep=False)
+            if save_for_backward:
+                layer_inputs.append(xin)
+        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        state = dict(batch=batch, tables=tables, layer_inputs=layer_inputs, xf=xf, hf=hf, rstd_f=rstd_f) \
+            if save_for_backward else None
+        return hf, state
+
+    def _trunk_bwd(self, s: dict, dhf: torch.Tensor) -> None:
+        c = self.cfg
+        batch, tables = s["batch"], s["tables"]
+        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"],
+                           self.params.grads["model.norm.weight"])
+        del dhf
+        inputs = s["layer_inputs"]
+        for l in reversed(range(c.num_hidden_layers)):
+            xin = inputs.pop()
+            dx = self.layer_bwd(l, xin, dx, batch, tables)
+            del xin
+        A.embedding_bwd(batch.input_ids, dx, self.params.grads["model.embed_tokens.weight"])
+
+    def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
+        """Scalar value per packed position from the value head (fp32 [T]); needs ``value_head`` in the config."""
+        hf, state = self._trunk_fwd(batch, save_for_backward)
+        w = self.params["v_head.weight"]
+        values = (hf.float() @ w.float().t()).squeeze(-1)
+        if save_for_backward:
+            state["kind"] = "values"
+            self._saved = state
+        return values
+
+    def backward_values(self, g_values: torch.Tensor) -> None:
+        s = self._saved
+        assert s is not None and s.get("kind") == "values", "call forward_values(save_for_backward=True) first"
+        self._saved = None
+        self.params.alloc_grads()
+        g = g_values.float().contiguous()
+        w = self.params["v_head.weight"]
+        self.params.grads["v_head.weight"].add_((g[None, :] @ s["hf"].float()))
+        dhf = (g[:, None] * w.float()).to(s["hf"].dtype)
+        self._trunk_bwd(s, dhf)
+
     def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
         """Returns (logprob[T], entropy[T]) of the next token at every packed position (fp32)."""
         c = self.cfg

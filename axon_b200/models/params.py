@@ -42,6 +42,8 @@ def param_layout(cfg: ModelConfig) -> "OrderedDict[str, tuple[int, ...]]":
     lay["model.norm.weight"] = (H,)
     if not cfg.tie_word_embeddings:
         lay["lm_head.weight"] = (cfg.vocab_size, H)
+    if cfg.extra.get("value_head", False):          # critic / reward model: scalar head on the final hidden state
+        lay["v_head.weight"] = (1, H)
     return lay
 
 
@@ -75,6 +77,15 @@ class FlatParams:
 
     def __getitem__(self, name: str) -> torch.Tensor:
         return self.views[name]
+
+    def rebind(self, flat: torch.Tensor) -> None:
+        """Point every named view at a new flat buffer (an empty one drops the views: parameters
+        parked on the host). Consumers that cached views must fetch them again."""
+        self.flat = flat
+        if flat.numel() >= self.numel:
+            self.views = {n: flat[o:o + k].view(self.layout[n]) for n, (o, k) in self.offsets.items()}
+        else:
+            self.views = {}
 
     def names(self):
         return list(self.layout.keys())

@@ -1,0 +1,182 @@
+"""Sampler worker: one generation engine + server per GPU (reference: axon/sampler/sampler.py:35-164).
+
+In the colocated ("hybrid") deployment the worker lives in the same process as the trainer role and
+binds its engine to the trainer's flat parameter buffer, so a weight update needs no copy at all; in
+the disaggregated deployment it owns its parameters and receives updates either as named tensors
+(``update_weights``) or through the P2P push path. The server is reachable in-process (the object)
+and, when ``serve_http`` is set, over an OpenAI-compatible HTTP endpoint.
+"""
+from __future__ import annotations
+
+import datetime
+import threading
+
+import torch
+import torch.distributed as dist
+
+from ..controller.decorator import Dispatch, register
+from ..core.worker import Worker
+from ..utils.profiler import DistProfiler, DistProfilerExtension, ProfilerConfig
+from .engine import GenerationEngine
+from .server import SERVER_REGISTRY, SamplerMode, SamplerServer
+
+
+def _get(cfg, key, default=None):
+    cur = cfg
+    for part in key.split("."):
+        if isinstance(cur, dict) and part in cur:
+            cur = cur[part]
+        elif cur is not None and not isinstance(cur, dict) and hasattr(cur, part):
+            cur = getattr(cur, part)
+        else:
+            return default
+    return default if cur is None else cur
+
+
+class SamplerWorker(Worker, DistProfilerExtension):
+    def __init__(self, config, name: str = "sampler", **kwargs):
+        Worker.__init__(self)
+        self.config = config
+        self.name = name
+        scfg = _get(config, "sampler", config)
+        self.scfg = scfg
+        use_cuda = torch.cuda.is_available() and not _get(config, "force_cpu", False)
+        if use_cuda:
+            torch.cuda.set_device(self.local_rank % torch.cuda.device_count())
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        else:
+            self.device = torch.device("cpu")
+        self.tp = int(_get(scfg, "tensor_model_parallel_size", 1))
+        self.pp = int(_get(scfg, "pipeline_model_parallel_size", 1))
+        assert self.world_size % (self.tp * self.pp) == 0
+        self.dp_rank = self.rank // (self.tp * self.pp)
+        self._register_dispatch_collect_info("sampler", dp_rank=self.dp_rank, is_collect=self.rank % (self.tp * self.pp) == 0)
+        if self.world_size > 1 and self.tp * self.pp > 1 and not dist.is_initialized():
+            dist.init_process_group(backend="nccl" if use_cuda else "gloo", rank=self.rank, world_size=self.world_size,
+                                    init_method=f"tcp://{self._master_addr}:{self._master_port}",
+                                    timeout=datetime.timedelta(seconds=600))
+        DistProfilerExtension.__init__(self, DistProfiler(self.rank, ProfilerConfig.from_config(
+            _get(scfg, "profiler", {}), _get(config, "global_profiler", None))))
+        self.model = None
+        self.engine: GenerationEngine | None = None
+        self.server: SamplerServer | None = None
+        self.tokenizer = None
+        self._http_thread: threading.Thread | None = None
+        self._http_server = None
+        self.address: str | None = None
+        self.shares_trainer_weights = False
+
+    # ------------------------------------------------------------------ set-up
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def init_model(self):
+        from ..utils.hf_model import build_model
+        from ..utils.tokenizer import hf_tokenizer
+        cfg, scfg = self.config, self.scfg
+        peers = getattr(self, "_fused_peers", None) or {}
+        trainer = next((p for r, p in peers.items() if r != self.name and getattr(p, "model", None) is not None
+                        and hasattr(p, "engine") and not getattr(p, "_forward_only", False)), None)
+        if trainer is not None:
+            self.model = trainer.model                  # zero-copy: generation reads the trainer's live parameters
+            self.shares_trainer_weights = True
+        else:
+            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            self.model = build_model(_get(cfg, "model_path"), device=self.device, dtype=dtype, seed=int(_get(cfg, "seed", 42)),
+                                     load_weights=True)
+        try:
+            self.tokenizer = hf_tokenizer(_get(cfg, "model_path"))
+        except Exception:
+            self.tokenizer = None
+        kv_bytes = None
+        if self.device.type == "cuda":
+            free, total = torch.cuda.mem_get_info()
+            util = float(_get(scfg, "gpu_memory_utilization", 0.85))
+            kv_bytes = max(1 << 28, int(free - (1.0 - util) * total))
+        num_pages = _get(scfg, "num_kv_pages", None)
+        self.engine = GenerationEngine(self.model, num_pages=num_pages, max_num_seqs=int(_get(scfg, "max_num_seqs", 256)),
+                                       max_num_batched_tokens=int(_get(scfg, "max_num_batched_tokens", 32768)),
+                                       kv_memory_bytes=kv_bytes, seed=int(_get(cfg, "seed", 42)) + self.rank)
+        if _get(scfg, "enforce_eager", False):
+            self.engine.use_cuda_graph = False
+        max_len = _get(scfg, "max_model_len", None)
+        if max_len:
+            self.engine.set_max_model_len(int(max_len))
+        mode = SamplerMode.HYBRID if self.shares_trainer_weights else SamplerMode.STANDALONE
+        server_cls = SERVER_REGISTRY.get(str(_get(scfg, "name", "native")), SamplerServer)
+        self.server = server_cls(self.engine, tokenizer=self.tokenizer, name=f"{self.name}-{self.rank}", mode=mode).start()
+        if _get(scfg, "serve_http", False):
+            self._start_http()
+        if self.shares_trainer_weights and _get(scfg, "offload_sampler", True):
+            self.server.sleep()                          # training starts with the KV pool released
+        return {"address": self.address, "shares_trainer_weights": self.shares_trainer_weights,
+                "kv_pages": self.engine._num_pages}
+
+    def _start_http(self) -> None:
+        import socket
+
+        import uvicorn
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        cfg = uvicorn.Config(self.server.build_app(), host="127.0.0.1", port=port, log_level="warning")
+        self._http_server = uvicorn.Server(cfg)
+        self._http_thread = threading.Thread(target=self._http_server.run, daemon=True, name="sampler-http")
+        self._http_thread.start()
+        self.address = f"http://127.0.0.1:{port}"
+
+    # ------------------------------------------------------------------ direct methods
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def get_server_address(self):
+        """HTTP address when serving over HTTP, else None (callers in the same process use ``get_server``)."""
+        return self.address
+
+    get_zeromq_address = get_server_address      # name used by the reference's executor-facing API
+
+    def get_server(self) -> SamplerServer:
+        return self.server
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def wake_up(self):
+        self.server.wake_up()
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def sleep(self):
+        self.server.sleep()
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def pause_generation(self, strategy: str = "drain"):
+        self.server.pause_generation(strategy)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def continue_generation(self):
+        self.server.continue_generation()
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def update_weights(self, named_tensors=None):
+        """Hybrid deployment: nothing to move (shared buffer) — only cached state that depends on the
+        old weights is dropped. Otherwise copy the given (name, tensor) pairs in."""
+        if self.shares_trainer_weights or named_tensors is None:
+            return 0
+        return self.server.update_weights(named_tensors)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def params_checksum(self) -> float:
+        return float(self.model.params.flat.double().sum().item())
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def engine_stats(self) -> dict:
+        return dict(self.engine.stats)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def shutdown(self):
+        if self._http_server is not None:
+            self._http_server.should_exit = True
+        if self.server is not None:
+            self.server.stop()
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def start_profile(self, **kw):
+        DistProfilerExtension.start_profile(self, role=self.name, **kw)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def stop_profile(self):
+        DistProfilerExtension.stop_profile(self)

@@ -50,10 +50,14 @@ class SamplingClient:
         return self._sems[key]
 
     def _client(self):
+        # one HTTP client per running event loop (connections are bound to the loop that opened them)
+        import httpx
         if self._http is None:
-            import httpx
-            self._http = httpx.AsyncClient(timeout=httpx.Timeout(self.request_timeout, connect=5.0))
-        return self._http
+            self._http = {}
+        key = id(asyncio.get_running_loop())
+        if key not in self._http:
+            self._http[key] = httpx.AsyncClient(timeout=httpx.Timeout(self.request_timeout, connect=5.0))
+        return self._http[key]
 
     # ------------------------------------------------------------------ sampling
     async def _one(self, addr, prompt_ids, params: dict) -> dict:
@@ -140,6 +144,8 @@ class SamplingClient:
         return {"inflight": list(self._inflight), "sessions": len(self._session_addr)}
 
     async def close(self) -> None:
-        if self._http is not None:
-            await self._http.aclose()
+        if self._http:
+            mine = self._http.pop(id(asyncio.get_running_loop()), None)
+            if mine is not None:
+                await mine.aclose()
             self._http = None

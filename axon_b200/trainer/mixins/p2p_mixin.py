@@ -1,0 +1,77 @@
+"""Trainer side of the disaggregated weight push
+(reference: axon/trainer/mixins/p2p_mixin.py:58-703).
+
+``get_parameter_mapping`` describes what this rank holds (every trainer rank holds the full fused
+parameters, so any rank can serve any sampler shard and the routing table spreads the load).
+``send_trainer_to_sampler_weights`` compiles the routing table into a copy plan once (cached across
+steps) and executes it: on CUDA within a node through the sampler's symmetric-memory buffers with
+the fused peer-store kernel (optionally quantising to fp8 blocks on the way), otherwise as one
+packed message per destination over the bridge process group.
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+import torch.distributed as dist
+
+from ...controller.decorator import Dispatch, register
+from ...utils.p2p.distributed import init_trainer_sampler_process_group
+from ...utils.p2p.param_mapper import get_param_metadata
+from ...utils.p2p.plan import compile_plan
+from ...utils.p2p.transport import send_plan
+
+
+def slice_for_tp(t: torch.Tensor, dim: int, tp_rank: int, tp_size: int) -> torch.Tensor:
+    """The ``tp_rank``-th of ``tp_size`` equal slices along ``dim`` (``dim`` < 0: replicated)."""
+    if dim < 0 or tp_size == 1:
+        return t
+    n = t.shape[dim] // tp_size
+    return t.narrow(dim, tp_rank * n, n)
+
+
+class TrainerP2PMixin:
+    bridge_pg = None
+    _p2p_plan = None
+    _p2p_stage: dict | None = None
+    _bridge_offset = 0
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def connect_trainer_to_sampler(self, master_addr: str, master_port: int, world_size: int, rank_offset: int = 0):
+        self._bridge_world = world_size
+        self._n_trainers = self.world_size
+        self.bridge_pg = init_trainer_sampler_process_group(master_addr, master_port, rank_offset + self.rank, world_size,
+                                                            backend="nccl" if self.device.type == "cuda" else "gloo")
+        t = torch.zeros(1, device=self.device)
+        dist.all_reduce(t, group=self.bridge_pg)          # warm-up: connections exist before the first push
+        return self.bridge_pg.rank()
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def get_parameter_mapping(self):
+        return get_param_metadata(self.model.cfg, rank=self.rank, dtype=self.model.params.dtype)
+
+    def _local_offsets(self) -> dict:
+        return {n: o for n, (o, _) in self.model.params.offsets.items()}
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def send_trainer_to_sampler_weights(self, routing_table=None):
+        if routing_table is not None:
+            self.routing_table = routing_table
+            self._p2p_plan = None
+        assert getattr(self, "routing_table", None) is not None, "no routing table: the first push must carry it"
+        t0 = time.monotonic()
+        if self._p2p_plan is None:
+            from ...sampler.mixins.p2p_mixin import _Zero
+            dsts = {s for (a, s) in self.routing_table.routing_map if a == self.rank}
+            # message path: only source offsets matter to the sender (the receiver owns its layout)
+            self._p2p_plan = compile_plan(self.routing_table, self.rank, self._local_offsets(), {s: _Zero() for s in dsts},
+                                          elem_bytes=self.model.params.flat.element_size())
+            self._p2p_stage = {}
+        sent = send_plan(self._p2p_plan, self.model.params.flat, self.bridge_pg, self._n_trainers, self._p2p_stage)
+        if getattr(self, "offload_p2p_buffer", False):
+            self._p2p_stage = {}
+        return {"bytes": sent, "seconds": time.monotonic() - t0}
+
+
+FSDPTrainerP2PMixin = TrainerP2PMixin
+MegatronTrainerP2PMixin = TrainerP2PMixin

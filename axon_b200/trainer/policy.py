@@ -106,7 +106,8 @@ class PolicyEngine:
         self.shard = (min(n, self.rank * per), min(n, (self.rank + 1) * per))
         self.shard_size = per
         self.master = self.exp_avg = self.exp_avg_sq = None
-        self.opt_step = 0
+        self.opt_step = 0                     # optimizer updates so far (Adam bias correction)
+        self.sched_step = 0                   # learning-rate schedule position (advances once per RL step)
         self.state = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._host_state: dict | None = None
 
@@ -205,8 +206,64 @@ class PolicyEngine:
                 metrics.setdefault(k, []).append(v)
         return metrics
 
+    # ------------------------------------------------------------------ value head (critic / reward model)
+    @torch.no_grad()
+    def forward_values(self, data: DataProto) -> DataProto:
+        """``values[b, t]`` = value head on the hidden state BEFORE token t (0 at t = 0), masked by
+        ``response_mask`` when present (reference: axon/models/fsdp_models.py:299-372)."""
+        mbs, idx = prepare_dynamic_batch(data, self.max_tokens, dp_group=None)
+        outs = []
+        for mb in mbs:
+            pk = _Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device)
+            outs.append(pk.to_padded(self.model.forward_values(pk.batch)))
+        order = torch.tensor([i for p in idx for i in p], dtype=torch.long, device=self.device)
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=self.device)
+        values = torch.cat(outs)[inv]
+        if "response_mask" in data.batch:
+            values = values * data.batch["response_mask"].to(values.device)
+        return DataProto.from_dict({"values": values})
+
+    @torch.no_grad()
+    def forward_rewards(self, data: DataProto) -> DataProto:
+        """Sequence reward = value head on the LAST real token's hidden state, placed at that token."""
+        mbs, idx = prepare_dynamic_batch(data, self.max_tokens, dp_group=None)
+        outs = []
+        for mb in mbs:
+            am = mb.batch["attention_mask"].to(self.device)
+            pk = _Packing(mb.batch["input_ids"], am, self.device)
+            v = self.model.forward_values(pk.batch)
+            last_packed = torch.from_numpy(np.cumsum(pk.lens) - 1).to(self.device)
+            scores = torch.zeros(am.shape, dtype=torch.float32, device=self.device)
+            rows = torch.nonzero(torch.from_numpy(pk.lens > 0).to(self.device)).flatten()
+            scores[rows, (am.sum(1) - 1)[rows]] = v[last_packed[rows]]
+            outs.append(scores)
+        order = torch.tensor([i for p in idx for i in p], dtype=torch.long, device=self.device)
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=self.device)
+        return DataProto.from_dict({"rm_scores": torch.cat(outs)[inv]})
+
+    def forward_backward_values(self, data: DataProto, loss_fn: str = "value", loss_args: dict | None = None) -> dict:
+        """Critic update: value-head predictions against ``returns`` with the registered value loss."""
+        args = dict(loss_args or {})
+        self.model.params.alloc_grads()
+        mbs, _ = prepare_dynamic_batch(data, self.max_tokens, dp_group=None)
+        metrics: dict[str, list] = {}
+        for mb in mbs:
+            mb = mb.to(self.device)
+            pk = _Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device)
+            v_packed = self.model.forward_values(pk.batch, save_for_backward=True)
+            leaf = v_packed.detach().requires_grad_(True)
+            mb.batch["vpreds"] = pk.to_padded(leaf) * mb.batch["response_mask"]
+            loss, m = compute_loss_fn(mb, loss_fn, args)
+            loss.backward()
+            self.model.backward_values(leaf.grad if leaf.grad is not None else torch.zeros_like(leaf))
+            for k, v in m.items():
+                metrics.setdefault(k, []).append(v)
+        return metrics
+
     # ------------------------------------------------------------------ optimizer step
-    def optim_step(self) -> dict:
+    def optim_step(self, step_lr: bool = True) -> dict:
         """Reduce gradients over the data-parallel group, clip by global norm, fused AdamW on the local
         shard, gather the updated bf16 parameters. Skips the update when the norm is not finite."""
         p = self.model.params
@@ -225,7 +282,9 @@ class PolicyEngine:
             dist.all_reduce(self.state[:1], group=self.pg)
         OPT.clip_coef(self.state, self.cfg.grad_clip, self.cfg.grad_norm_threshold)
         self.opt_step += 1
-        lr = lr_at(self.cfg, self.opt_step)
+        lr = lr_at(self.cfg, self.sched_step + 1)
+        if step_lr:
+            self.sched_step += 1
         OPT.adamw_step(self.master, p.flat[lo:hi], grad_shard, self.exp_avg, self.exp_avg_sq, lr, self.cfg.beta1,
                        self.cfg.beta2, self.cfg.eps, self.cfg.weight_decay, self.opt_step, self.state)
         if self.world > 1:

@@ -8,6 +8,23 @@ import os
 import sys
 
 
+def load_module(mod_path: str):
+    """Import a module given a dotted name (optionally ``pkg://`` prefixed) or a ``.py`` file path
+    (optionally ``file://`` prefixed)."""
+    mod_path = mod_path.removeprefix("pkg://").removeprefix("file://")
+    if mod_path.endswith(".py") or os.path.sep in mod_path:
+        path = os.path.abspath(mod_path)
+        name = "_axon_dyn_" + str(abs(hash(path)))
+        if name in sys.modules:
+            return sys.modules[name]
+        s = importlib.util.spec_from_file_location(name, path)
+        module = importlib.util.module_from_spec(s)
+        sys.modules[name] = module
+        s.loader.exec_module(module)
+        return module
+    return importlib.import_module(mod_path)
+
+
 def load_class(spec: str):
     spec = spec.removeprefix("pkg://")
     mod_path, _, cls_name = spec.rpartition(":")

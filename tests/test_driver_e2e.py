@@ -1,0 +1,91 @@
+"""End-to-end RL runs of all three driver modes on CPU with the tiny model: colocated synchronous
+(in-process workers, checkpoint + resume), disaggregated asynchronous and the one-off pipelined
+synchronous mode (worker processes, gloo bridge group, P2P weight push)."""
+import json
+import os
+
+import pytest
+import torch
+
+from axon_b200.driver.train_agent_ppo import train_agent
+from axon_b200.utils.config import compose_config
+from axon_b200.utils.state import find_latest_ckpt_path, is_valid_checkpoint
+
+
+def _config(tmp_path, extra):
+    rows = [{"question": f"What is {i}+{i}?", "ground_truth": str(2 * i), "data_source": "toy", "reward_fn": "bernoulli"}
+            for i in range(8)]
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as f:
+        for r in rows:
+            f.write(json.dumps(r) + "\n")
+    ov = [f"train_files={data}", "model_path=tiny-qwen3", "+force_cpu=true", "train_batch_size=2", "decoding.n=2",
+          "mini_batch_size=2", "max_seq_length=256", "max_prompt_length=200", f"output_dir={tmp_path}/out",
+          "advantage=grpo", "validation.before_train=false", "+sampler.num_kv_pages=64", "sampler.max_num_seqs=8",
+          "max_tokens_per_step=12", "drop_zero_advantage_samples=false", "actor.max_token_len_per_gpu=512",
+          "save_programs_flag=false", "logger=[file]", "resume_from_checkpoint=true"] + extra
+    os.environ["AXON_FILE_LOGGER_ROOT"] = str(tmp_path)
+    return compose_config(ov)
+
+
+def _logged_steps(tmp_path):
+    path = tmp_path / "axon-agent_ppo.jsonl"
+    return [json.loads(line) for line in open(path)]
+
+
+@pytest.mark.timeout(600)
+def test_sync_colocated_train_checkpoint_resume(tmp_path):
+    cfg = _config(tmp_path, ["num_gpus_per_node=1", "total_training_steps=2", "save_steps=1", "checkpoint_format=both",
+                             f"val_files={tmp_path}/train.jsonl"])
+    drv = train_agent(cfg, backend="inline", keep_alive=True)
+    try:
+        assert drv.global_steps == 3
+        # colocated sampler generates from the trainer's own parameter buffer
+        s_worker = drv.sampler_wg.workers[0].role_objects["sampler"]
+        a_worker = drv.sampler_wg.workers[0].role_objects["actor"]
+        assert s_worker.shares_trainer_weights and s_worker.model is a_worker.model
+        sum_after = a_worker.params_checksum()
+        sched = a_worker.engine.sched_step
+    finally:
+        drv.shutdown()
+    logs = _logged_steps(tmp_path)
+    assert [r["step"] for r in logs][:2] == [1, 2] and "val/reward" in logs[-1]["data"]
+    first = logs[0]["data"]
+    for key in ("actor/loss", "actor/grad_norm", "batch/sampler_logprobs_diff_mean", "critic/rewards/mean", "timing_s/gen",
+                "timing_s/forward_backward", "response_length/mean", "perf/throughput_tokens_per_s", "engine/returned_programs"):
+        assert key in first, key
+    assert first["batch/sampler_logprobs_diff_mean"] < 1e-4            # sampler and trainer agree on log-probs
+    ckpt_root = tmp_path / "out" / "axon" / "agent_ppo" / "checkpoints"
+    latest = find_latest_ckpt_path(str(ckpt_root))
+    assert latest.endswith("step_2") and is_valid_checkpoint(latest)
+    assert os.path.exists(os.path.join(latest, "actor", "huggingface", "model.safetensors"))
+    # resume: one more step; parameters and schedule continue from the checkpoint
+    cfg2 = _config(tmp_path, ["num_gpus_per_node=1", "total_training_steps=3", "save_steps=-1", "checkpoint_format=both"])
+    drv2 = train_agent(cfg2, backend="inline", keep_alive=True)
+    try:
+        a2 = drv2.sampler_wg.workers[0].role_objects["actor"]
+        assert drv2.global_steps == 4 and a2.engine.sched_step == sched + 1 and a2.engine.opt_step >= 3
+        assert abs(a2.params_checksum() - sum_after) < 1.0 and a2.params_checksum() != sum_after
+    finally:
+        drv2.shutdown()
+    assert [r["step"] for r in _logged_steps(tmp_path)][-1] == 3
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("mode", ["async", "oneoff"])
+def test_disaggregated_modes_push_weights(tmp_path, mode):
+    extra = ["num_gpus_per_node=2", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1"]
+    if mode == "oneoff":
+        extra += ["enable_one_off_pipeline=true", "driver_mode=sync"]
+    drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
+    try:
+        assert drv.global_steps == 3
+        a, s = drv.actor_wg.params_checksum()[0], drv.sampler_wg.params_checksum()[0]
+        assert a == s                                   # the last push made the sampler's weights bit-identical
+    finally:
+        drv.shutdown()
+    logs = _logged_steps(tmp_path)
+    assert [r["step"] for r in logs] == [1, 2]
+    assert "timing_s/sync_weights" in logs[0]["data"] and "actor/loss" in logs[1]["data"]
+    if mode == "async":
+        assert "async/staleness_steps" in logs[0]["data"]
