@@ -180,7 +180,7 @@ def test_agg_loss_modes():
 
 
 @pytest.mark.parametrize("token_reduce,batch_reduce,dp", list(itertools.product(
-    ["sum", "mean", "mean-norm", "mean-program"], ["token-mean", "step-mean", "program-mean"], [2, 4]))
+    ["sum", "mean", "mean-norm", "mean-program"], ["token-mean", "step-mean", "program-mean"], [2, 4])))
 def test_multi_rank_gradient_equals_single_process(token_reduce, batch_reduce, dp):
     """Simulate ``dp`` data-parallel ranks on CPU. With mini-batch-global valid counts, SUM-reduced rank
     gradients (or AVG-reduced ones pre-multiplied by dp, the FSDP convention) equal the 1-process gradient."""
