@@ -51,6 +51,7 @@ class RLStepConfig:
     max_num_seqs: int = 256
     max_num_batched_tokens: int = 32768
     offload_optimizer: bool | None = None  # None: decide from free memory
+    recompute: str = "auto"                # activation recomputation: auto | full | selective | none
     optim: OptimConfig = field(default_factory=OptimConfig)
 
 
@@ -148,6 +149,18 @@ class ColocatedRLRunner:
     def _enter_training(self) -> None:
         self.engine.sleep()
         self.policy.load_optimizer()
+        if self.cfg.recompute == "auto" and self.device.type == "cuda":
+            # keep as many activations as the memory left after parameters, gradients and optimizer
+            # state allows (per token and layer: selective 2(3H + qkv) bytes, none adds 4F bytes)
+            c = self.model.cfg
+            tok = self.policy.max_tokens
+            grads = 0 if self.model.params.grad_flat is not None else self.model.params.numel * 4
+            free = self._free_bytes() - grads - (6 << 30)
+            sel = 2 * (3 * c.hidden_size + c.qkv_size) * tok * c.num_hidden_layers
+            non = sel + 4 * c.intermediate_size * tok * c.num_hidden_layers
+            self.model.recompute = "none" if free > 1.25 * non else "selective" if free > 1.25 * sel else "full"
+        elif self.cfg.recompute != "auto":
+            self.model.recompute = self.cfg.recompute
 
     # ------------------------------------------------------------------ one RL step
     def step(self, prompt_ids: torch.Tensor, prompt_lens: torch.Tensor | None = None,
@@ -176,6 +189,9 @@ class ColocatedRLRunner:
             torch.cuda.synchronize(self.device)
         t2 = time.perf_counter()
         self._enter_training()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        t2a = time.perf_counter()
         if rewards is None:
             rewards = np.array([self.reward_fn(p, o) for p, o in zip(prompts, outs)], dtype=np.float32) \
                 if self.reward_fn is not None else self.rng.binomial(1, 0.5, len(outs)).astype(np.float32)
@@ -183,6 +199,7 @@ class ColocatedRLRunner:
                                     c.max_prompt_length + c.max_response_length)
         data.meta_info.update(temperature=c.temperature, global_steps=self.global_step)
         compute_advantage(data, {"advantage": c.advantage, "advantage_args": c.advantage_args})
+        t2b = time.perf_counter()
         if c.use_sampler_logprobs:
             data.batch["old_log_probs"] = data.batch["sampler_log_probs"].clone()
         else:
@@ -210,7 +227,10 @@ class ColocatedRLRunner:
         self.global_step += 1
         n_tok = int(data.batch["attention_mask"].sum())
         n_resp = int(rm.sum())
-        self.timing = dict(setup=t1 - t0, rollout=t2 - t1, prepare_and_old_logprob=t3 - t2, train=t4 - t3, total=t4 - t0)
+        self.timing = dict(setup=t1 - t0, rollout=t2 - t1, prepare_and_old_logprob=t3 - t2, train=t4 - t3, total=t4 - t0,
+                           enter_training=t2a - t2, build_batch=t2b - t2a, old_logprob=t3 - t2b,
+                           offload=self.phase_detail.get("offload", 0.0), kv_alloc=self.phase_detail.get("kv_alloc", 0.0))
+        self.phase_detail["recompute"] = self.model.recompute
         return {"loss": float(np.sum(metrics.get("loss", [0.0]))), "grad_norm": opt.get("grad_norm", 0.0),
                 "tokens": n_tok, "response_tokens": n_resp, "sequences": len(data),
                 "reward_mean": float(np.mean(rewards)), "sampler_probs_diff_mean": float(gap),

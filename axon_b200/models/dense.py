@@ -56,6 +56,7 @@ class DenseModel:
         self.dtype = dtype
         self.params = params if params is not None else FlatParams(cfg, self.device, dtype)
         self._saved: dict | None = None
+        self.recompute = "selective"          # activation recomputation in backward: full | selective | none
 
     # ------------------------------------------------------------------ helpers
     def _p(self, l: int, name: str) -> torch.Tensor:
@@ -74,9 +75,17 @@ class DenseModel:
         return R.rope_tables(max(max_pos, 8), self.cfg.head_dim, self.cfg.rope_theta, self.device)
 
     # ------------------------------------------------------------------ one layer
+    # What the forward pass keeps per layer for backward, by ``self.recompute``:
+    #   "full"       xin only: backward re-runs the layer up to the SwiGLU (everything but the down GEMM)
+    #   "selective"  xin, qkv, o, lse, x1: backward re-runs the two norms, RoPE, the gate/up GEMM and SwiGLU
+    #   "none"       additionally gu: backward re-runs only norms, RoPE and SwiGLU (no GEMM, no attention)
+    # Bytes kept per token and layer (bf16, H = hidden): full 2H; selective 2(3H + qkv); none adds 4F.
+    _KEEP = {"full": ("xin",), "selective": ("xin", "qkv", "o", "lse", "x1"), "none": ("xin", "qkv", "o", "lse", "x1", "gu")}
+
     def layer_fwd(self, l: int, x, delta, batch: PackedBatch, tables, keep: bool):
-        """x (+ delta) is the residual stream entering the layer. Returns (x1, mlp_out[, cache]):
-        the stream after attention and the not-yet-added MLP output (fused into the next norm)."""
+        """x (+ delta) is the residual stream entering the layer. Returns (x1, mlp_out, saved): the
+        stream after attention, the not-yet-added MLP output (fused into the next norm) and, with
+        ``keep``, the tensors backward wants (see ``_KEEP``)."""
         c = self.cfg
         qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
         kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
@@ -84,23 +93,48 @@ class DenseModel:
         qkv = G.gemm_nt(h, self._p(l, "self_attn.qkv_proj.weight"))
         qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
                                   c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
+        want = self._KEEP[self.recompute] if keep else ()
         o, lse = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-                             need_lse=keep)
+                             need_lse="lse" in want)
         ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
         h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
         gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
         a = A.swiglu_fwd(gu)
         mo = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
-        if not keep:
-            return x1, mo, xin
-        cache = dict(xin=xin, h=h, rstd1=rstd1, qkv=qkv, qkv_r=qkv_r, o=o, lse=lse, x1=x1, h2=h2, rstd2=rstd2,
-                     gu=gu, a=a)
-        return x1, mo, cache
+        local = dict(xin=xin, qkv=qkv, o=o, lse=lse, x1=x1, gu=gu)
+        return x1, mo, ({k: local[k] for k in want} if keep else xin)
 
-    def layer_bwd(self, l: int, xin, dx_out, batch: PackedBatch, tables):
+    def _rebuild(self, l: int, saved: dict, batch: PackedBatch, tables) -> dict:
+        """Recompute, from what forward kept, every tensor backward reads."""
+        c = self.cfg
+        qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
+        kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
+        k = dict(saved)
+        k["h"], k["rstd1"], _ = N.rmsnorm_fwd(k["xin"], self._p(l, "input_layernorm.weight"), c.rms_norm_eps)
+        if "qkv" not in k:
+            k["qkv"] = G.gemm_nt(k["h"], self._p(l, "self_attn.qkv_proj.weight"))
+        k["qkv_r"] = R.qknorm_rope_fwd(k["qkv"], batch.position_ids, tables[0], tables[1], c.num_attention_heads,
+                                       c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
+        if "o" not in k:
+            k["o"], k["lse"] = AT.attn_fwd(k["qkv_r"], batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads,
+                                           c.head_dim, need_lse=True)
+        if "x1" not in k:
+            ao = G.gemm_nt(k["o"], self._p(l, "self_attn.o_proj.weight"))
+            k["h2"], k["rstd2"], k["x1"] = N.rmsnorm_fwd(k["xin"], self._p(l, "post_attention_layernorm.weight"),
+                                                         c.rms_norm_eps, delta=ao)
+        else:
+            k["h2"], k["rstd2"], _ = N.rmsnorm_fwd(k["x1"], self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps)
+        if "gu" not in k:
+            k["gu"] = G.gemm_nt(k["h2"], self._p(l, "mlp.gate_up_proj.weight"))
+        k["a"] = A.swiglu_fwd(k["gu"])
+        return k
+
+    def layer_bwd(self, l: int, saved, dx_out, batch: PackedBatch, tables):
         """dx_out: grad of the stream leaving the layer (x1 + mlp_out). Returns grad of the stream entering."""
         c = self.cfg
-        _, _, k = self.layer_fwd(l, xin, None, batch, tables, keep=True)
+        if not isinstance(saved, dict):
+            saved = {"xin": saved}
+        k = self._rebuild(l, saved, batch, tables)
         qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
         kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
         # MLP
@@ -141,9 +175,9 @@ class DenseModel:
         delta = None
         layer_inputs = []
         for l in range(c.num_hidden_layers):
-            x, delta, xin = self.layer_fwd(l, x, delta, batch, tables, keep=False)
+            x, delta, saved = self.layer_fwd(l, x, delta, batch, tables, keep=save_for_backward)
             if save_for_backward:
-                layer_inputs.append(xin)
+                layer_inputs.append(saved)
         hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
         state = dict(batch=batch, tables=tables, layer_inputs=layer_inputs, xf=xf, hf=hf, rstd_f=rstd_f) \
             if save_for_backward else None
@@ -157,9 +191,9 @@ class DenseModel:
         del dhf
         inputs = s["layer_inputs"]
         for l in reversed(range(c.num_hidden_layers)):
-            xin = inputs.pop()
-            dx = self.layer_bwd(l, xin, dx, batch, tables)
-            del xin
+            saved = inputs.pop()
+            dx = self.layer_bwd(l, saved, dx, batch, tables)
+            del saved
         A.embedding_bwd(batch.input_ids, dx, self.params.grads["model.embed_tokens.weight"])
 
     def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
@@ -185,43 +219,24 @@ class DenseModel:
 
     def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
         """Returns (logprob[T], entropy[T]) of the next token at every packed position (fp32)."""
-        c = self.cfg
-        tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
-        x = A.embedding_fwd(batch.input_ids, self.params["model.embed_tokens.weight"])
-        delta = None
-        layer_inputs = []
-        for l in range(c.num_hidden_layers):
-            x, delta, xin = self.layer_fwd(l, x, delta, batch, tables, keep=False)
-            if save_for_backward:
-                layer_inputs.append(xin)
-        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        hf, state = self._trunk_fwd(batch, save_for_backward)
         lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), batch.labels, temperature)
         if save_for_backward:
-            self._saved = dict(batch=batch, tables=tables, layer_inputs=layer_inputs, xf=xf, hf=hf, rstd_f=rstd_f,
-                               lse=lse, ent=ent, temperature=temperature)
+            state.update(kind="lm", lse=lse, ent=ent, temperature=temperature)
+            self._saved = state
         return lp, ent
 
     def backward(self, g_logprob: torch.Tensor | None, g_entropy: torch.Tensor | None = None) -> None:
         """Backward from per-position grads of (logprob, entropy); accumulates into params.grads."""
         s = self._saved
-        assert s is not None, "call forward(save_for_backward=True) first"
+        assert s is not None and s.get("kind") == "lm", "call forward(save_for_backward=True) first"
         self._saved = None
-        c = self.cfg
         self.params.alloc_grads()
-        batch, tables = s["batch"], s["tables"]
         g_lp = None if g_logprob is None else g_logprob.float().contiguous()
         g_ent = None if g_entropy is None else g_entropy.float().contiguous()
-        dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), batch.labels, s["lse"], s["ent"], g_lp, g_ent,
+        dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["batch"].labels, s["lse"], s["ent"], g_lp, g_ent,
                             s["temperature"], dweight=self.head_grad())
-        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"],
-                           self.params.grads["model.norm.weight"])
-        del dhf
-        inputs = s["layer_inputs"]
-        for l in reversed(range(c.num_hidden_layers)):
-            xin = inputs.pop()
-            dx = self.layer_bwd(l, xin, dx, batch, tables)
-            del xin
-        A.embedding_bwd(batch.input_ids, dx, self.params.grads["model.embed_tokens.weight"])
+        self._trunk_bwd(s, dhf)
 
     # ------------------------------------------------------------------ analytic FLOPs (for MFU)
     def flops_per_token(self, seqlen: int) -> float:

@@ -33,8 +33,17 @@ def _native_gemm(a, b, out, M, N, K, a_mn, b_mn, mode, alpha=1.0, bn_hint=0, max
 SMALL_M = 256  # token batches up to this size take the swap-AB + split-K path (decode)
 
 
+USE_CLUSTER_DECODE = True   # cluster split-K kernel (partials reduced through distributed shared memory)
+
+
 def _native_gemm_smallm(x, w, out, M, N, K):
     lib = C.lib()
+    if USE_CLUSTER_DECODE and lib.axb_gemm_decode_cluster_size(M, N, K) >= 2:
+        rc = lib.axb_gemm_decode_cluster(C.ptr(x), C.ptr(w), C.ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),
+                                         ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(out.stride(0)),
+                                         int(out.dtype == torch.float32), C.ptr(C.status(x.device)), C.stream())
+        C.launched(rc, "gemm_decode_cluster", 1)
+        return out
     splits = lib.axb_gemm_smallm_splits(M, N, K)
     ws = C.workspace(x.device, splits * M * N * 4, "gemm_splitk") if splits > 1 else None
     rc = lib.axb_gemm_bf16_smallm(C.ptr(x), C.ptr(w), C.ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),

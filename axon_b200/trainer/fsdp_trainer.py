@@ -173,6 +173,7 @@ class TrainerWorker(Worker, DistProfilerExtension):
         if self.model_kind.value_head:
             mcfg.extra = {**mcfg.extra, "value_head": True}
         model = DenseModel(mcfg, device=self.device, dtype=dtype)
+        model.recompute = str(_get(self.config, "recompute", "selective"))
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
             load_hf_weights(model, model_path, strict=not self.model_kind.value_head)
             if self.model_kind.value_head:

@@ -70,3 +70,44 @@ def test_gemm_small_m_swap_ab(M, N, K):
     _check(G.gemm_nt(a, b, out_dtype=torch.float32), ref, K)
     assert torch.equal(G.gemm_nt(a, b), G.gemm_nt(a, b))
     C.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (5, 1024, 512), (17, 1024, 4096), (64, 6144, 4096), (65, 4096, 4096),
+                                   (128, 4096, 12288), (129, 6144, 4096), (256, 6144, 4096), (256, 4096, 12288),
+                                   (200, 2048 + 40, 1024), (256, 1000, 576)])
+def test_gemm_decode_cluster_matches_reference_and_split_kernel(M, N, K):
+    """Cluster split-K kernel (partials reduced through distributed shared memory): against fp32
+    PyTorch, against the global-workspace split-K kernel, run-to-run bit identical, and the batch
+    rows do not depend on the batch size (row i of a 1-row and an M-row product agree)."""
+    lib = C.lib()
+    a, b = _rand(M, K), _rand(N, K)
+    ref = a.float() @ b.float().t()
+    cs = lib.axb_gemm_decode_cluster_size(M, N, K)
+    assert 0 <= cs <= 8
+    G.USE_CLUSTER_DECODE = True
+    try:
+        out = G.gemm_nt(a, b)
+        out32 = G.gemm_nt(a, b, out_dtype=torch.float32)
+        again = G.gemm_nt(a, b)
+    finally:
+        G.USE_CLUSTER_DECODE = True
+    _check(out, ref, K)
+    _check(out32, ref, K)
+    assert torch.equal(out, again)
+    G.USE_CLUSTER_DECODE = False
+    try:
+        old32 = G.gemm_nt(a, b, out_dtype=torch.float32)
+    finally:
+        G.USE_CLUSTER_DECODE = True
+    torch.testing.assert_close(out32, old32, rtol=1e-4, atol=1e-3 * (K ** 0.5) / 16)
+    C.check_status()
+
+
+@pytest.mark.gpu
+def test_gemm_decode_cluster_selection():
+    lib = C.lib()
+    assert lib.axb_gemm_decode_cluster_size(256, 6144, 4096) == 3        # 48 tiles x 3 = 144 CTAs
+    assert lib.axb_gemm_decode_cluster_size(256, 4096, 4096) == 4        # 32 tiles x 4
+    assert lib.axb_gemm_decode_cluster_size(256, 24576, 4096) == 0       # enough tiles without splitting
+    assert lib.axb_gemm_decode_cluster_size(8, 512, 256) in (0, 1, 2, 4)  # 4 K blocks: at most 1 split of >= 4
