@@ -122,8 +122,24 @@ def tiny_gpu() -> ModelConfig:
                        max_position_embeddings=8192, eos_token_id=1, pad_token_id=0)
 
 
+def tiny_moe() -> ModelConfig:
+    """A small sparse model (8 experts, top-2, head dim 64) for CPU tests."""
+    return ModelConfig(model_type="qwen3_moe", vocab_size=2048, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, intermediate_size=256, tie_word_embeddings=False,
+                       max_position_embeddings=2048, eos_token_id=1, pad_token_id=0, num_experts=8,
+                       num_experts_per_tok=2, moe_intermediate_size=128, norm_topk_prob=True)
+
+
+def tiny_moe_gpu() -> ModelConfig:
+    """Sparse GPU smoke model: head dim 128, 16 experts top-4, expert FFN 256."""
+    return ModelConfig(model_type="qwen3_moe", vocab_size=8192, hidden_size=512, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=128, intermediate_size=1024, tie_word_embeddings=False,
+                       max_position_embeddings=8192, eos_token_id=1, pad_token_id=0, num_experts=16,
+                       num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
+
+
 PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen3-30b-a3b": qwen3_30b_a3b,
-           "tiny-qwen3": tiny_qwen3, "tiny-gpu": tiny_gpu}
+           "tiny-qwen3": tiny_qwen3, "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
 
 
 def get_config(name_or_path: str) -> ModelConfig:

@@ -37,6 +37,7 @@ class PackedBatch:
     cu_seqlens: torch.Tensor     # int32 [B+1]
     labels: torch.Tensor         # int32 [T]
     max_seqlen: int = 0
+    routermap: torch.Tensor | None = None   # int [T, n_moe_layers, top_k] expert ids chosen by the sampler (-1: none)
 
     @staticmethod
     def from_sequences(seqs: list[torch.Tensor], device) -> "PackedBatch":
@@ -50,7 +51,7 @@ class PackedBatch:
 
 class DenseModel:
     def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params: FlatParams | None = None):
-        assert cfg.num_experts == 0, "use MoEModel for sparse configs"
+        assert cfg.num_experts == 0 or type(self) is not DenseModel, "use MoEModel for sparse configs"
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype
@@ -98,11 +99,36 @@ class DenseModel:
                              need_lse="lse" in want)
         ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
         h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
+        mo, mlp_saved = self.mlp_fwd(l, h2, batch, want)
+        local = dict(xin=xin, qkv=qkv, o=o, lse=lse, x1=x1, **mlp_saved)
+        return x1, mo, ({k: local[k] for k in local if k in want or k in mlp_saved} if keep else xin)
+
+    # ---- MLP hooks (dense SwiGLU here; the mixture-of-experts model overrides the three of them)
+    def mlp_fwd(self, l: int, h2, batch: PackedBatch, want=()):
+        """Returns (mlp output, tensors to keep for backward)."""
         gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
         a = A.swiglu_fwd(gu)
         mo = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
-        local = dict(xin=xin, qkv=qkv, o=o, lse=lse, x1=x1, gu=gu)
-        return x1, mo, ({k: local[k] for k in want} if keep else xin)
+        return mo, ({"gu": gu} if "gu" in want else {})
+
+    def mlp_infer(self, l: int, h2):
+        """MLP of the sampler path (no state kept)."""
+        return self.mlp_fwd(l, h2, None, ())[0]
+
+    def mlp_rebuild(self, l: int, k: dict, batch: PackedBatch) -> None:
+        if "gu" not in k:
+            k["gu"] = G.gemm_nt(k["h2"], self._p(l, "mlp.gate_up_proj.weight"))
+        k["a"] = A.swiglu_fwd(k["gu"])
+
+    def mlp_bwd(self, l: int, k: dict, dx_out):
+        """Grad wrt the MLP input h2; accumulates the MLP weight gradients."""
+        da = G.gemm_nn(dx_out, self._p(l, "mlp.down_proj.weight"))
+        G.gemm_tn(dx_out, k["a"], out=self._g(l, "mlp.down_proj.weight"), accumulate=True)
+        dgu = A.swiglu_bwd(da, k["gu"])
+        del da
+        dh2 = G.gemm_nn(dgu, self._p(l, "mlp.gate_up_proj.weight"))
+        G.gemm_tn(dgu, k["h2"], out=self._g(l, "mlp.gate_up_proj.weight"), accumulate=True)
+        return dh2
 
     def _rebuild(self, l: int, saved: dict, batch: PackedBatch, tables) -> dict:
         """Recompute, from what forward kept, every tensor backward reads."""
@@ -124,9 +150,7 @@ class DenseModel:
                                                          c.rms_norm_eps, delta=ao)
         else:
             k["h2"], k["rstd2"], _ = N.rmsnorm_fwd(k["x1"], self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps)
-        if "gu" not in k:
-            k["gu"] = G.gemm_nt(k["h2"], self._p(l, "mlp.gate_up_proj.weight"))
-        k["a"] = A.swiglu_fwd(k["gu"])
+        self.mlp_rebuild(l, k, batch)
         return k
 
     def layer_bwd(self, l: int, saved, dx_out, batch: PackedBatch, tables):
@@ -137,14 +161,7 @@ class DenseModel:
         k = self._rebuild(l, saved, batch, tables)
         qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
         kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
-        # MLP
-        da = G.gemm_nn(dx_out, self._p(l, "mlp.down_proj.weight"))
-        G.gemm_tn(dx_out, k["a"], out=self._g(l, "mlp.down_proj.weight"), accumulate=True)
-        dgu = A.swiglu_bwd(da, k["gu"])
-        del da
-        dh2 = G.gemm_nn(dgu, self._p(l, "mlp.gate_up_proj.weight"))
-        G.gemm_tn(dgu, k["h2"], out=self._g(l, "mlp.gate_up_proj.weight"), accumulate=True)
-        del dgu
+        dh2 = self.mlp_bwd(l, k, dx_out)
         dx1 = N.rmsnorm_bwd(dh2, k["x1"], self._p(l, "post_attention_layernorm.weight"), k["rstd2"],
                             self._g(l, "post_attention_layernorm.weight"), dres=dx_out)
         del dh2
@@ -278,9 +295,7 @@ class _DenseInference:
                                need_lse=False)
             ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
-            gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
-            a = A.swiglu_fwd(gu)
-            delta = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
+            delta = self.mlp_infer(l, h2)
             x = x1
         xl = x[last_index]
         dl = delta[last_index]
@@ -310,9 +325,7 @@ class _DenseInference:
                                c.num_key_value_heads, c.head_dim)
             ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
-            gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
-            a = A.swiglu_fwd(gu)
-            delta = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
+            delta = self.mlp_infer(l, h2)
             x = x1
         hf, _, _ = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
         return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)

@@ -1,0 +1,129 @@
+"""Sparse mixture-of-experts decoder (Qwen3-MoE family: softmax router, top-k, optional weight
+renormalisation, SwiGLU experts, no shared expert).
+
+Attention, norms, embedding and the vocabulary head are the dense model's; only the MLP differs:
+
+    logits = h2 @ gate^T                     (fp32)
+    ids, w = route(logits)                   top-k of softmax; with routing replay the ids come from
+                                             the sampler's record and only the weights are recomputed
+    xs     = gather(h2)                      expert-sorted, 128-row padded
+    ys     = W2_e . swiglu(W13_e . xs)       two grouped tcgen05 GEMMs
+    out    = sum_j w_j * ys[row(t, j)]       weights applied AFTER the second projection, as the
+                                             sampler does, so trainer and sampler agree bit-for-bit
+                                             on the order of operations
+
+Backward recomputes the expert activations from what forward kept (``recompute`` as in the dense
+model; "none" also keeps the gate/up output). Router gradients flow through the softmax weights of
+the selected experts; the selection itself is not differentiated. Replaces the reference's fused-MoE
+autograd functions (axon/utils/kernel/fused_moe.py:66-352), the Megatron MoE layer with its routing
+replay and probability-placement patches (axon/monkey_patches/megatron/moe_replay.py,
+moe_prob_placement.py) and the HF fused block (axon/models/transformers/qwen3_moe.py).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import activation as A
+from ..ops import gemm as G
+from ..ops import moe as M
+from .config import ModelConfig
+from .dense import DenseModel, PackedBatch
+
+
+class MoEModel(DenseModel):
+    def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params=None):
+        assert cfg.num_experts > 0 and cfg.num_experts_per_tok > 0, "MoEModel needs num_experts / num_experts_per_tok"
+        super().__init__(cfg, device, dtype, params)
+        self.last_routing: list | None = None       # per layer ids of the latest sampler forward (routed-experts capture)
+        self.capture_routing = False
+
+    # ------------------------------------------------------------------ routing
+    def _route(self, l: int, h2, replay):
+        c = self.cfg
+        logits = G.gemm_nt(h2, self._p(l, "mlp.gate.weight"), out_dtype=torch.float32)
+        ids, w = M.route(logits, c.num_experts_per_tok, c.norm_topk_prob, replay)
+        return logits, ids, w
+
+    def _experts(self, l: int, h2, ids, w, keep_gu: bool):
+        c = self.cfg
+        lay = M.align(ids, c.num_experts)
+        xs = M.gather(h2, lay)
+        gu = M.grouped_fwd(xs, self._p(l, "mlp.experts.w13_weight"), lay)
+        a = A.swiglu_fwd(gu)
+        ys = M.grouped_fwd(a, self._p(l, "mlp.experts.w2_weight"), lay)
+        return lay, xs, gu, a, ys
+
+    def _replay_for(self, l: int, batch):
+        rm = getattr(batch, "routermap", None) if batch is not None else None
+        if rm is None:
+            return None
+        return rm[:, l, :].contiguous()
+
+    # ------------------------------------------------------------------ hooks
+    def mlp_fwd(self, l: int, h2, batch: PackedBatch, want=()):
+        logits, ids, w = self._route(l, h2, self._replay_for(l, batch))
+        lay, xs, gu, a, ys = self._experts(l, h2, ids, w, "gu" in want)
+        out = M.combine(ys, w, lay)
+        if self.capture_routing:
+            if self.last_routing is None:
+                self.last_routing = []
+            self.last_routing.append(ids)
+        saved = {"moe_ids": ids} if want else {}
+        if "gu" in want:
+            saved.update(moe_gu=gu, moe_lay=lay, moe_xs=xs)
+        return out, saved
+
+    def mlp_infer(self, l: int, h2):
+        return self.mlp_fwd(l, h2, None, ())[0]
+
+    def mlp_rebuild(self, l: int, k: dict, batch: PackedBatch) -> None:
+        c = self.cfg
+        h2 = k["h2"]
+        logits = G.gemm_nt(h2, self._p(l, "mlp.gate.weight"), out_dtype=torch.float32)
+        ids = k["moe_ids"]
+        k["moe_logits"] = logits
+        k["moe_w"] = M.route_weights_from_probs(logits, ids, c.norm_topk_prob)
+        if "moe_gu" in k:
+            lay, xs, gu = k["moe_lay"], k["moe_xs"], k["moe_gu"]
+        else:
+            lay = M.align(ids, c.num_experts)
+            xs = M.gather(h2, lay)
+            gu = M.grouped_fwd(xs, self._p(l, "mlp.experts.w13_weight"), lay)
+        a = A.swiglu_fwd(gu)
+        ys = M.grouped_fwd(a, self._p(l, "mlp.experts.w2_weight"), lay)
+        k.update(moe_lay=lay, moe_xs=xs, moe_gu=gu, moe_a=a, moe_ys=ys)
+
+    def mlp_bwd(self, l: int, k: dict, dx_out):
+        c = self.cfg
+        lay, xs, gu, a, ys = k["moe_lay"], k["moe_xs"], k["moe_gu"], k["moe_a"], k["moe_ys"]
+        w = k["moe_w"]
+        dys, dw = M.combine_bwd(dx_out, ys, w.detach(), lay)
+        M.grouped_wgrad(dys, a, self._g(l, "mlp.experts.w2_weight"), lay, accumulate=True)
+        da = M.grouped_dgrad(dys, self._p(l, "mlp.experts.w2_weight"), lay)
+        dgu = A.swiglu_bwd(da, gu)
+        del da, dys
+        M.grouped_wgrad(dgu, xs, self._g(l, "mlp.experts.w13_weight"), lay, accumulate=True)
+        dxs = M.grouped_dgrad(dgu, self._p(l, "mlp.experts.w13_weight"), lay)
+        del dgu
+        dh2 = M.scatter_sum(dxs, lay)
+        # router: d logits from d weights (softmax over all experts, renormalised over the chosen k)
+        logits = k["moe_logits"].detach().requires_grad_(True)
+        with torch.enable_grad():
+            wt = M.route_weights_from_probs(logits, k["moe_ids"], c.norm_topk_prob)
+            (wt * dw).sum().backward()
+        dlog = logits.grad.to(k["h2"].dtype)
+        G.gemm_tn(dlog, k["h2"], out=self._g(l, "mlp.gate.weight"), accumulate=True)
+        dh2 = dh2 + G.gemm_nn(dlog, self._p(l, "mlp.gate.weight"))
+        return dh2
+
+    # ------------------------------------------------------------------ FLOPs
+    def flops_per_token(self, seqlen: int) -> float:
+        c = self.cfg
+        moe = 3 * c.hidden_size * c.moe_intermediate_size * c.num_experts_per_tok + c.hidden_size * c.num_experts
+        dense = c.num_hidden_layers * (c.qkv_size * c.hidden_size + c.hidden_size * c.q_size + moe) + c.vocab_size * c.hidden_size
+        return 6 * dense + 12 * c.num_hidden_layers * c.q_size * seqlen / 2
+
+
+def build_model_for(cfg: ModelConfig, device="cuda", dtype=torch.bfloat16):
+    """Dense or sparse model class by configuration."""
+    return (MoEModel if cfg.num_experts > 0 else DenseModel)(cfg, device=device, dtype=dtype)

@@ -112,6 +112,8 @@ class FlatParams:
             self.grads = {n: self.grad_flat[o:o + k].view(self.layout[n]) for n, (o, k) in self.offsets.items()}
 
     def free_grads(self) -> None:
+        if getattr(self, "grads_persistent", False):      # buffer lives in symmetric memory: keep the mapping
+            return
         self.grad_flat = None
         self.grads = {}
 

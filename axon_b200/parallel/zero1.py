@@ -42,11 +42,18 @@ class FusedZero1:
         self.lo, self.n = self.rank * per, per
         self.reduced = torch.empty(per, dtype=torch.float32, device=self.device)
         self.grads.tensor.zero_()
+        self._sync_token = torch.zeros(1, dtype=torch.float32, device=self.device)
 
     def step(self, master, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, wd, step, max_norm, skip_threshold=0.0):
         """Consumes ``grads.tensor`` (this rank's full local gradient), updates this rank's shard of the
         optimizer state and every rank's ``params.tensor``. Returns the device state [sumsq, norm, coef, skip]."""
         lib = C.lib()
+        if self.world > 1:
+            # Ranks can reach the optimizer step seconds apart (uneven micro-batches); the device
+            # barrier's wait is bounded to about two seconds by design, so first line the streams up
+            # with a stream-ordered NCCL all-reduce of one element (plumbing, not data).
+            import torch.distributed as dist
+            dist.all_reduce(self._sync_token, group=self.grads.group)
         self.barrier()                                                        # all backward passes are done
         rc = lib.axb_zero1_reduce(self.grads.ptr_array(), self.rank, self.world, ctypes.c_longlong(self.lo),
                                   ctypes.c_longlong(self.n), C.ptr(self.reduced), C.ptr(self.partials), C.stream())
@@ -55,10 +62,8 @@ class FusedZero1:
         mine = self.stats.tensor[self.rank:self.rank + 1]
         torch.sum(self.partials, dim=0, keepdim=True, out=mine)
         self.barrier()
-        total = torch.zeros(1, dtype=torch.float32, device=self.device)
-        for r in range(self.world):                                           # fixed order: identical on every rank
-            total += self.stats.peer_tensor(r)[r:r + 1]
-        self.state[0:1] = total
+        rc = lib.axb_zero1_total(self.stats.ptr_array(), self.world, C.ptr(self.state), C.stream())   # fixed rank order
+        C.launched(rc, "zero1_total")
         OPT.clip_coef(self.state, max_norm, skip_threshold)
         bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
         rc = lib.axb_zero1_adamw_bcast(C.ptr(master), C.ptr(self.reduced), C.ptr(exp_avg), C.ptr(exp_avg_sq),

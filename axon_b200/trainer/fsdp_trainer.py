@@ -167,12 +167,12 @@ class TrainerWorker(Worker, DistProfilerExtension):
 
     def _build(self, model_path, dtype, seed):
         from ..models.config import get_config
-        from ..models.dense import DenseModel
+        from ..models.moe import build_model_for
         from ..utils.hf_model import has_hf_weights, load_hf_weights
         mcfg = get_config(model_path)
         if self.model_kind.value_head:
             mcfg.extra = {**mcfg.extra, "value_head": True}
-        model = DenseModel(mcfg, device=self.device, dtype=dtype)
+        model = build_model_for(mcfg, device=self.device, dtype=dtype)
         model.recompute = str(_get(self.config, "recompute", "selective"))
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
             load_hf_weights(model, model_path, strict=not self.model_kind.value_head)

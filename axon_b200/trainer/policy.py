@@ -91,7 +91,7 @@ class _Packing:
 
 class PolicyEngine:
     def __init__(self, model: DenseModel, optim: OptimConfig | None = None, process_group=None,
-                 max_token_len_per_gpu: int = 8192, temperature: float = 1.0):
+                 max_token_len_per_gpu: int = 8192, temperature: float = 1.0, fused_zero1: bool | None = None):
         self.model = model
         self.cfg = optim or OptimConfig()
         self.pg = process_group
@@ -110,6 +110,34 @@ class PolicyEngine:
         self.sched_step = 0                   # learning-rate schedule position (advances once per RL step)
         self.state = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._host_state: dict | None = None
+        self.fused = None
+        if fused_zero1 is None:
+            fused_zero1 = self.world > 1 and self.device.type == "cuda" and n % (self.world * 128) == 0 and \
+                dist.get_backend(process_group) == "nccl"
+        if fused_zero1:
+            self._enable_fused_zero1()
+
+    def _enable_fused_zero1(self) -> None:
+        """Move the parameters and the main-gradient buffer into symmetric memory and route the
+        optimizer step through the peer-memory kernels (reduce via peer loads, AdamW whose epilogue
+        stores the new bf16 values into every rank's parameters). Falls back to NCCL collectives when
+        symmetric memory cannot be set up."""
+        from ..parallel.zero1 import FusedZero1
+        p = self.model.params
+        try:
+            fz = FusedZero1(p.flat.numel(), group=self.pg, device=self.device)
+        except Exception as e:          # noqa: BLE001 - no peer access / unsupported driver
+            import warnings
+            warnings.warn(f"fused ZeRO-1 unavailable ({type(e).__name__}: {e}); using NCCL collectives", stacklevel=2)
+            return
+        fz.params.tensor.copy_(p.flat)
+        p.rebind(fz.params.tensor)
+        p.grad_flat, p.grads = None, {}
+        p.alloc_grads(grad_flat=fz.grads.tensor)
+        p.grads_persistent = True       # symmetric memory is mapped once; rollouts must not free it
+        self.fused = fz
+        lo, hi = self.shard
+        assert (fz.lo, fz.lo + fz.n) == (lo, hi), "shard boundaries of the fused path and the engine differ"
 
     # ------------------------------------------------------------------ optimizer state
     def init_optimizer(self) -> None:
@@ -273,6 +301,17 @@ class PolicyEngine:
             if self.master is None:
                 self.init_optimizer()
         lo, hi = self.shard
+        if self.fused is not None:
+            self.opt_step += 1
+            lr = lr_at(self.cfg, self.sched_step + 1)
+            if step_lr:
+                self.sched_step += 1
+            state = self.fused.step(self.master, self.exp_avg, self.exp_avg_sq, lr, self.cfg.beta1, self.cfg.beta2,
+                                    self.cfg.eps, self.cfg.weight_decay, self.opt_step, self.cfg.grad_clip,
+                                    self.cfg.grad_norm_threshold)
+            p.zero_grads()
+            st = state.tolist()
+            return {"grad_norm": st[1], "lr": lr, "skipped": st[3]}
         if self.world > 1:
             grad_shard = self._reduce_scatter_grads()
         else:

@@ -63,10 +63,9 @@ def load_hf_weights(model, path: str, strict: bool = True) -> list[str]:
 def build_model(model_path: str, device="cuda", dtype=torch.bfloat16, seed: int = 0, load_weights: bool = True,
                 model_cls=None):
     """Preset name -> random init (seeded); HF directory -> its config, and its weights when present."""
-    from ..models.dense import DenseModel
+    from ..models.moe import build_model_for
     cfg = get_config(model_path)
-    cls = model_cls or DenseModel
-    model = cls(cfg, device=device, dtype=dtype)
+    model = model_cls(cfg, device=device, dtype=dtype) if model_cls is not None else build_model_for(cfg, device, dtype)
     if load_weights and os.path.isdir(str(model_path)) and has_hf_weights(model_path):
         load_hf_weights(model, model_path)
     else:

@@ -314,6 +314,23 @@ extern "C" int axb_zero1_reduce(const unsigned long long* grad_ptrs, int rank, i
   return check_launch();
 }
 
+// state[0] = sum over ranks of stats_r[r] (rank r's sum-of-squares partial, read from rank r's own
+// buffer with plain peer loads, in rank order so every rank derives the same total).
+__global__ void zero1_total_kernel(PeerPtrs stats, int world, float* __restrict__ state) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float t = 0.f;
+    for (int r = 0; r < world; ++r) t += reinterpret_cast<const volatile float*>(stats.p[r])[r];
+    state[0] = t;
+  }
+}
+
+extern "C" int axb_zero1_total(const unsigned long long* stats_ptrs, int world, float* state, void* stream) {
+  PeerPtrs s;
+  if (int rc = fill_ptrs(s, stats_ptrs, world)) return rc;
+  zero1_total_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(s, world, state);
+  return check_launch();
+}
+
 extern "C" int axb_zero1_adamw_bcast(float* master, const float* grad, float* m, float* v,
                                      const unsigned long long* param_ptrs, int world, long long lo, long long n,
                                      float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,

@@ -4,24 +4,31 @@
 
 namespace axb {
 
-template <int BN, bool A_MN, bool B_MN, class Epi>
+// b_rows / a_rows: outer extents of the tensor maps (rows of the operand matrices as stored); they
+// differ from N / M for stacked expert weights and expert-sorted activations.
+template <int BN, bool A_MN, bool B_MN, class Epi, class TM = DenseTiles>
 static int launch_gemm_inst(const void* A, const void* B, int M, int N, int K, long long lda,
                             long long ldb, const typename Epi::Params& ep, int* status,
-                            cudaStream_t stream, int max_ctas, int k_splits = 1) {
+                            cudaStream_t stream, int max_ctas, int k_splits = 1,
+                            const typename TM::Params& tp = typename TM::Params{}, long long a_rows = -1,
+                            long long b_rows = -1, int tiles_hint = -1) {
   CUtensorMap tmA, tmB;
   int rc;
+  // K-major operand: tensor [rows][K]; MN-major operand: tensor [K rows][M or N]
+  const long long a_outer = a_rows >= 0 ? a_rows : (A_MN ? K : M);
+  const long long b_outer = b_rows >= 0 ? b_rows : (B_MN ? K : N);
   if (!A_MN)
-    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda * 2, GEMM_BK, GEMM_BM, true);
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, a_outer, lda * 2, GEMM_BK, GEMM_BM, true);
   else
-    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, 64, GEMM_BK, true);
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, a_outer, lda * 2, 64, GEMM_BK, true);
   if (rc != AXB_LAUNCH_OK) return rc;
   if (!B_MN)
-    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb * 2, GEMM_BK, BN, true);
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, b_outer, ldb * 2, GEMM_BK, BN, true);
   else
-    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2, 64, GEMM_BK, true);
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, b_outer, ldb * 2, 64, GEMM_BK, true);
   if (rc != AXB_LAUNCH_OK) return rc;
 
-  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, Epi>;
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, Epi, TM>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -30,12 +37,12 @@ static int launch_gemm_inst(const void* A, const void* B, int M, int N, int K, l
     attr_set = true;
   }
   const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
-  const int num_tiles_k = num_tiles * (k_splits < 1 ? 1 : k_splits);
+  const int num_tiles_k = tiles_hint > 0 ? tiles_hint : num_tiles * (k_splits < 1 ? 1 : k_splits);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (num_tiles_k < grid) grid = num_tiles_k;
   GemmShape sh{M, N, K, k_splits < 1 ? 1 : k_splits};
-  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, sh, ep, status);
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, sh, ep, status, tp);
   return check_launch();
 }
 
@@ -145,4 +152,62 @@ extern "C" int axb_gemm_bf16_smallm(const void* X, const void* W, void* out, int
   if (blocks > cap) blocks = cap;
   splitk_reduce_kernel<<<(int)blocks, 256, 0, s>>>(ws, out, ldc, tokens, feats, splits, out_fp32);
   return check_launch();
+}
+
+
+// ------------------------------------------------------------------ grouped (mixture-of-experts)
+// Rows of X / Y are sorted by expert and padded to 128 per expert (see moe.cu):
+//   tile_expert[m]  expert of 128-row block m (-1 past the end);  total_rows = padded rows in use.
+// forward   Y[P][N]  = X[P][K]  * W_e[N][K]^T          (W stacked [E*N][K])
+// dgrad     dX[P][K] = dY[P][N] * W_e[N][K]            (same W, read MN-major)
+// wgrad     dW_e[N][K] += dY_e^T X_e  in fp32          (contraction over the expert's rows)
+// P = max_rows (capacity of the sorted buffers). N and K of the weights must be multiples of 128.
+extern "C" int axb_gemm_grouped_fwd(const void* X, const void* W, void* Y, int max_rows, int N, int K, int E,
+                                    long long ldx, long long ldw, long long ldy, const int* tile_expert,
+                                    const int* total_rows, int* status, void* stream) {
+  using namespace axb;
+  if (max_rows <= 0 || N % 128 != 0 || K % 64 != 0 || E <= 0 || (ldx & 7) || (ldw & 7)) return AXB_LAUNCH_BAD_ARG;
+  StoreEpi::Params ep{Y, ldy, 0, 1.0f};
+  RowGroupedTiles::Params tp{tile_expert, total_rows, N};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (N % 256 == 0)
+    return launch_gemm_inst<256, false, false, StoreEpi, RowGroupedTiles>(X, W, max_rows, N, K, ldx, ldw, ep, status, s,
+                                                                           0, 1, tp, max_rows, (long long)E * N);
+  return launch_gemm_inst<128, false, false, StoreEpi, RowGroupedTiles>(X, W, max_rows, N, K, ldx, ldw, ep, status, s, 0,
+                                                                         1, tp, max_rows, (long long)E * N);
+}
+
+// dX[P][Kw] = dY[P][Nw] * W_e[Nw][Kw]: GEMM with N_gemm = Kw, K_gemm = Nw, B MN-major, rows of B offset by e*Nw.
+extern "C" int axb_gemm_grouped_dgrad(const void* dY, const void* W, void* dX, int max_rows, int Nw, int Kw, int E,
+                                      long long lddy, long long ldw, long long lddx, const int* tile_expert,
+                                      const int* total_rows, int* status, void* stream) {
+  using namespace axb;
+  if (max_rows <= 0 || Nw % 64 != 0 || Kw % 128 != 0 || E <= 0 || (lddy & 7) || (ldw & 7)) return AXB_LAUNCH_BAD_ARG;
+  StoreEpi::Params ep{dX, lddx, 0, 1.0f};
+  RowGroupedTiles::Params tp{tile_expert, total_rows, Nw};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (Kw % 256 == 0)
+    return launch_gemm_inst<256, false, true, StoreEpi, RowGroupedTiles>(dY, W, max_rows, Kw, Nw, lddy, ldw, ep, status, s,
+                                                                          0, 1, tp, max_rows, (long long)E * Nw);
+  return launch_gemm_inst<128, false, true, StoreEpi, RowGroupedTiles>(dY, W, max_rows, Kw, Nw, lddy, ldw, ep, status, s, 0,
+                                                                        1, tp, max_rows, (long long)E * Nw);
+}
+
+// dW[E][Nw][Kw] (fp32) += dY_e^T X_e. offsets: [E+1] row offsets of the experts (device).
+extern "C" int axb_gemm_grouped_wgrad(const void* dY, const void* X, float* dW, int max_rows, int Nw, int Kw, int E,
+                                      long long lddy, long long ldx, const int* offsets, int accumulate, int* status,
+                                      void* stream) {
+  using namespace axb;
+  if (max_rows <= 0 || Nw % 128 != 0 || Kw % 128 != 0 || E <= 0 || (lddy & 7) || (ldx & 7)) return AXB_LAUNCH_BAD_ARG;
+  StoreEpi::Params ep{dW, Kw, accumulate ? 2 : 1, 1.0f};
+  KGroupedTiles::Params tp{offsets, E};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int bn = Kw % 256 == 0 ? 256 : 128;
+  const int tiles = E * (Nw / 128) * (Kw / bn);
+  // GEMM: M = Nw (A = dY MN-major [rows][Nw]), N = Kw (B = X MN-major [rows][Kw]), K = rows
+  if (bn == 256)
+    return launch_gemm_inst<256, true, true, StoreEpi, KGroupedTiles>(dY, X, Nw, Kw, max_rows, lddy, ldx, ep, status, s, 0,
+                                                                       1, tp, max_rows, max_rows, tiles);
+  return launch_gemm_inst<128, true, true, StoreEpi, KGroupedTiles>(dY, X, Nw, Kw, max_rows, lddy, ldx, ep, status, s, 0, 1,
+                                                                     tp, max_rows, max_rows, tiles);
 }

@@ -58,15 +58,98 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int k_s
   n_blk = r / gm;
 }
 
+// Tile maps: which (m, n, split) tile a linear tile index denotes, which K blocks it covers and
+// where its B rows and output rows start. The dense map is the plain rasterisation above; the two
+// grouped maps serve mixture-of-experts layers whose rows are sorted by expert and padded to 128.
+struct TileInfo {
+  int m_blk, n_blk, split;
+  int kb0, kb1;     // K blocks [kb0, kb1)
+  int b_off;        // added to B's outer (row) coordinate: expert * rows-per-expert
+  int epi_m_blk;    // row block the epilogue writes
+  bool valid;
+};
+
+struct DenseTiles {
+  struct Params {};
+  __device__ static int rows(const Params&, const GemmShape& sh) { return sh.M; }
+  __device__ static int epi_rows(const Params&, const GemmShape& sh) { return sh.M; }
+  __device__ static int num_tiles(const Params&, const GemmShape& sh, int num_m, int num_n) {
+    return num_m * num_n * (sh.k_splits < 1 ? 1 : sh.k_splits);
+  }
+  __device__ static TileInfo decode(const Params&, const GemmShape& sh, int t, int num_m, int num_n, int num_k) {
+    TileInfo ti;
+    const int ks = sh.k_splits < 1 ? 1 : sh.k_splits;
+    tile_coords(t, num_m, num_n, ks, ti.m_blk, ti.n_blk, ti.split);
+    const int k_per = (num_k + ks - 1) / ks;
+    ti.kb0 = ti.split * k_per;
+    ti.kb1 = min(num_k, ti.kb0 + k_per);
+    ti.b_off = 0;
+    ti.epi_m_blk = ti.m_blk;
+    ti.valid = true;
+    return ti;
+  }
+};
+
+// Rows of A / C are sorted by expert (128-row aligned); B holds E stacked weight matrices. Every
+// 128-row block belongs to one expert (tile_expert[m]); the number of live rows is read on the device.
+struct RowGroupedTiles {
+  struct Params {
+    const int* tile_expert;
+    const int* total_rows;     // offsets[E]: padded row count actually in use
+    int b_rows_per_expert;
+  };
+  __device__ static int rows(const Params& p, const GemmShape& sh) { return min(sh.M, *p.total_rows); }
+  __device__ static int epi_rows(const Params& p, const GemmShape& sh) { return min(sh.M, *p.total_rows); }
+  __device__ static int num_tiles(const Params&, const GemmShape&, int num_m, int num_n) { return num_m * num_n; }
+  __device__ static TileInfo decode(const Params& p, const GemmShape&, int t, int num_m, int num_n, int num_k) {
+    TileInfo ti;
+    tile_coords(t, num_m, num_n, 1, ti.m_blk, ti.n_blk, ti.split);
+    const int e = p.tile_expert[ti.m_blk];
+    ti.kb0 = 0;
+    ti.kb1 = num_k;
+    ti.b_off = (e < 0 ? 0 : e) * p.b_rows_per_expert;
+    ti.epi_m_blk = ti.m_blk;
+    ti.valid = e >= 0;
+    return ti;
+  }
+};
+
+// Per-expert weight gradients: the contraction runs over the rows of one expert (a K range), the
+// output is that expert's [M, N] slice of a stacked [E*M, N] tensor.
+struct KGroupedTiles {
+  struct Params {
+    const int* offsets;        // [E + 1] row offsets (multiples of 128)
+    int num_experts;
+  };
+  __device__ static int rows(const Params&, const GemmShape& sh) { return sh.M; }
+  __device__ static int epi_rows(const Params& p, const GemmShape& sh) { return sh.M * p.num_experts; }
+  __device__ static int num_tiles(const Params& p, const GemmShape&, int num_m, int num_n) {
+    return p.num_experts * num_m * num_n;
+  }
+  __device__ static TileInfo decode(const Params& p, const GemmShape&, int t, int num_m, int num_n, int) {
+    TileInfo ti;
+    const int per = num_m * num_n;
+    const int e = t / per;
+    tile_coords(t - e * per, num_m, num_n, 1, ti.m_blk, ti.n_blk, ti.split);
+    ti.kb0 = p.offsets[e] / GEMM_BK;
+    ti.kb1 = p.offsets[e + 1] / GEMM_BK;
+    ti.b_off = 0;
+    ti.epi_m_blk = e * num_m + ti.m_blk;
+    ti.valid = ti.kb1 > ti.kb0;
+    return ti;
+  }
+};
+
 // Epi contract:
 //   struct Params;                                   // POD passed by value
 //   __device__ Epi(const Params&, int m_blk, int n_blk, int row, const GemmShape&, int split);
 //   __device__ void chunk(int col0, const uint32_t (&acc)[32]);   // 32 fp32 columns of `row`
 //   __device__ void finish();
-template <int BN, bool A_MN, bool B_MN, class Epi>
+template <int BN, bool A_MN, bool B_MN, class Epi, class TM = DenseTiles>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const GemmShape shape, const typename Epi::Params ep, int* status) {
+               const GemmShape shape, const typename Epi::Params ep, int* status,
+               const typename TM::Params tp = typename TM::Params{}) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -80,12 +163,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (shape.M + GEMM_BM - 1) / GEMM_BM;
+  const int num_m = (TM::rows(tp, shape) + GEMM_BM - 1) / GEMM_BM;
   const int num_n = (shape.N + BN - 1) / BN;
   const int num_k_total = (shape.K + GEMM_BK - 1) / GEMM_BK;
-  const int k_splits = shape.k_splits < 1 ? 1 : shape.k_splits;
-  const int k_per = (num_k_total + k_splits - 1) / k_splits;
-  const int num_tiles = num_m * num_n * k_splits;
+  const int num_tiles = TM::num_tiles(tp, shape, num_m, num_n);
+  GemmShape epi_shape = shape;
+  epi_shape.M = TM::epi_rows(tp, shape);
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 
   if (threadIdx.x == 0) {
@@ -117,9 +200,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int m_blk, n_blk, split;
-        tile_coords(t, num_m, num_n, k_splits, m_blk, n_blk, split);
-        const int kb0 = split * k_per, kb1 = min(num_k_total, kb0 + k_per);
+        const TileInfo ti = TM::decode(tp, shape, t, num_m, num_n, num_k_total);
+        if (!ti.valid) continue;
+        const int m_blk = ti.m_blk, n_blk = ti.n_blk;
+        const int kb0 = ti.kb0, kb1 = ti.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1)) {
             report_error(status, AXB_ERR_WAIT_EMPTY);
@@ -137,11 +221,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               tma_load_2d(sA + c * 8192, &tmA, &full[s], m_blk * GEMM_BM + c * 64, kb * GEMM_BK);
           }
           if (!B_MN) {
-            tma_load_2d(sB, &tmB, &full[s], kb * GEMM_BK, n_blk * BN);
+            tma_load_2d(sB, &tmB, &full[s], kb * GEMM_BK, n_blk * BN + ti.b_off);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sB + c * 8192, &tmB, &full[s], n_blk * BN + c * 64, kb * GEMM_BK);
+              tma_load_2d(sB + c * 8192, &tmB, &full[s], n_blk * BN + c * 64, kb * GEMM_BK + ti.b_off);
           }
           if (++s == S::STAGES) {
             s = 0;
@@ -158,7 +242,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileInfo ti = TM::decode(tp, shape, t, num_m, num_n, num_k_total);
+        if (!ti.valid) continue;
         const int buf = it & 1;
         if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1)) {
           report_error(status, AXB_ERR_WAIT_TMEM_EMPTY);
@@ -166,8 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        const int split = t % k_splits;
-        const int kb0 = split * k_per, kb1 = min(num_k_total, kb0 + k_per);
+        const int kb0 = ti.kb0, kb1 = ti.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph)) {
             report_error(status, AXB_ERR_WAIT_FULL);
@@ -192,15 +277,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         if (ok) tc_commit(&acc_full[buf]);
+        ++it;
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
-      int m_blk, n_blk, split;
-      tile_coords(t, num_m, num_n, k_splits, m_blk, n_blk, split);
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const TileInfo ti = TM::decode(tp, shape, t, num_m, num_n, num_k_total);
+      if (!ti.valid) continue;
+      const int m_blk = ti.epi_m_blk, n_blk = ti.n_blk, split = ti.split;
       const int buf = it & 1;
       if (!mbar_wait(&acc_full[buf], (it >> 1) & 1)) {
         report_error(status, AXB_ERR_WAIT_TMEM_FULL);
@@ -208,7 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tc_fence_after();
       const int row = m_blk * GEMM_BM + q * 32 + lane;
-      Epi epi(ep, m_blk, n_blk, row, shape, split);
+      Epi epi(ep, m_blk, n_blk, row, epi_shape, split);
       const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -220,6 +307,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(&acc_empty[buf]);
       epi.finish();
+      ++it;
     }
   }
 

@@ -17,6 +17,21 @@
 
 namespace axb {
 
+#ifdef AXB_TIMELINE
+// Development aid (compiled only with -DAXB_TIMELINE): per-CTA timestamps of the kernel's phases.
+__device__ unsigned long long* g_timeline = nullptr;
+__device__ __forceinline__ void tl_mark(int slot) {
+  if (g_timeline != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_timeline[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t;
+  }
+}
+#define AXB_TL(slot, cond) do { if (cond) tl_mark(slot); } while (0)
+#else
+#define AXB_TL(slot, cond) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -63,6 +78,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  AXB_TL(0, threadIdx.x == 0);
   const int split = static_cast<int>(cluster_ctarank());
   const int csize = static_cast<int>(cluster_nctarank());
   const int num_m = (feats + GEMM_BM - 1) / GEMM_BM;
@@ -74,6 +90,8 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
   const int kb1 = min(num_k, kb0 + k_per);
   const bool has_work = kb0 < kb1;
   const int max_own = (NCHUNK + csize - 1) / csize;
+  // the exchange buffer (csize x max_own slots of 16 KB) must fit in the pipeline stages
+  const bool fits = csize * max_own * (GEMM_BM * 128) <= S::STAGES * S::STAGE_BYTES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
@@ -94,6 +112,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  AXB_TL(1, threadIdx.x == 0);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -140,6 +159,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
         }
       }
       if (issued) tc_commit(acc_full);
+      AXB_TL(2, true);
     }
   } else {
     // The accumulator is complete (and with it every read of this CTA's pipeline stages) once
@@ -149,13 +169,17 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
       ok = false;
     }
     tc_fence_after();
+    AXB_TL(3, threadIdx.x == 64);
   }
 
   __syncwarp();
   cluster_sync_all();   // #1: every CTA of the cluster is done with its stages
+  AXB_TL(4, threadIdx.x == 64);
 
   const uint32_t xbuf = smem_u32(smem);
-  if (warp >= 2) {
+  if (!fits) {
+    if (threadIdx.x == 0) report_error(status, AXB_ERR_BAD_ARG);
+  } else if (warp >= 2) {
     tc_fence_after();
     const int q = warp & 3;
     const int row = q * 32 + lane;   // feature row inside the tile
@@ -183,10 +207,12 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
     tc_fence_before();
   }
 
+  AXB_TL(5, threadIdx.x == 64);
   __syncwarp();
   cluster_sync_all();   // #2: all partial tiles have landed
+  AXB_TL(6, threadIdx.x == 64);
 
-  if (warp >= 2) {
+  if (warp >= 2 && fits) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const int f = m_blk * GEMM_BM + row;
@@ -227,6 +253,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
 
   tc_fence_before();
   __syncthreads();
+  AXB_TL(7, threadIdx.x == 0);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, BN);
@@ -270,8 +297,20 @@ static int launch_decode(const void* X, const void* W, void* out, int tokens, in
 
 }  // namespace axb
 
+#ifdef AXB_TIMELINE
+extern "C" int axb_gemm_decode_set_timeline(unsigned long long* buf) {
+  return cudaMemcpyToSymbol(axb::g_timeline, &buf, sizeof(buf)) == cudaSuccess ? 0 : -4;
+}
+#endif
+
+static int g_forced_cluster = 0;
+// Experiments only: force the cluster size of the next launches (0 restores the heuristic).
+extern "C" void axb_gemm_decode_force_cluster(int cs) { g_forced_cluster = cs; }
+
 // Cluster size (= K splits) the cluster kernel would use for this shape, or 0 when the shape is
 // better served by the persistent kernel (enough output tiles to fill the GPU on their own).
+extern "C" int axb_gemm_decode_max_active_clusters(int bn, int csize);
+
 extern "C" int axb_gemm_decode_cluster_size(int tokens, int feats, int K) {
   using namespace axb;
   const int bn = tokens <= 64 ? 64 : (tokens <= 128 ? 128 : 256);
@@ -284,7 +323,57 @@ extern "C" int axb_gemm_decode_cluster_size(int tokens, int feats, int K) {
   while (s > 1 && num_k / s < 4) --s;   // at least four K blocks per CTA
   // every split must own at least one K block (k_per = ceil(num_k / s))
   while (s > 1 && (s - 1) * ((num_k + s - 1) / s) >= num_k) --s;
+  // exchange buffer: s * ceil(chunks / s) slots of 16 KB must fit in the 192 KB of pipeline stages
+  const int chunks = bn / 32;
+  while (s > 1 && s * ((chunks + s - 1) / s) > 12) --s;
+  // one wave: a cluster lives inside one GPC, so fewer clusters fit than sms / s suggests
+  static int fit[3][9];
+  static bool have[3][9];
+  const int bi = bn == 64 ? 0 : (bn == 128 ? 1 : 2);
+  while (s > 1) {
+    if (!have[bi][s]) {
+      fit[bi][s] = axb_gemm_decode_max_active_clusters(bn, s);
+      have[bi][s] = true;
+    }
+    if (fit[bi][s] < 0 || fit[bi][s] >= tiles) break;
+    --s;
+  }
   return s < 2 ? 0 : s;
+}
+
+// Diagnostics: how many clusters of `csize` CTAs of the BN-wide kernel the device can hold at once.
+extern "C" int axb_gemm_decode_max_active_clusters(int bn, int csize) {
+  using namespace axb;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(csize, 64, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = -1;
+  cudaError_t e;
+  if (bn == 64) {
+    cfg.dynamicSmemBytes = GemmSmem<64>::TOTAL;
+    cudaFuncSetAttribute(gemm_decode_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<64>::TOTAL);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_decode_cluster_kernel<64>, &cfg);
+  } else if (bn == 128) {
+    cfg.dynamicSmemBytes = GemmSmem<128>::TOTAL;
+    cudaFuncSetAttribute(gemm_decode_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::TOTAL);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_decode_cluster_kernel<128>, &cfg);
+  } else {
+    cfg.dynamicSmemBytes = GemmSmem<256>::TOTAL;
+    cudaFuncSetAttribute(gemm_decode_cluster_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::TOTAL);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_decode_cluster_kernel<256>, &cfg);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return n;
 }
 
 // out[tokens][ldc] = X[tokens][ldx] * W[feats][ldw]^T, bf16 inputs, bf16 or fp32 output.
@@ -294,7 +383,8 @@ extern "C" int axb_gemm_decode_cluster(const void* X, const void* W, void* out, 
                                        void* stream) {
   using namespace axb;
   if (tokens <= 0 || feats <= 0 || K <= 0 || (ldx & 7) || (ldw & 7)) return AXB_LAUNCH_BAD_ARG;
-  const int cs = axb_gemm_decode_cluster_size(tokens, feats, K);
+  int cs = axb_gemm_decode_cluster_size(tokens, feats, K);
+  if (g_forced_cluster > 0) cs = g_forced_cluster;
   if (cs < 2) return AXB_LAUNCH_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (tokens <= 64) return launch_decode<64>(X, W, out, tokens, feats, K, ldx, ldw, ldc, out_fp32, cs, status, s);

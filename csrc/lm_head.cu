@@ -180,7 +180,7 @@ static int launch_head(const void* hidden, const void* W, int M, int V, int H, l
   int grid = sm_count();
   if (tiles < grid) grid = tiles;
   GemmShape sh{M, V, H, 1};
-  kern<<<grid, GEMM_THREADS, GemmSmem<256>::TOTAL, stream>>>(tmA, tmB, sh, ep, status);
+  kern<<<grid, GEMM_THREADS, GemmSmem<256>::TOTAL, stream>>>(tmA, tmB, sh, ep, status, DenseTiles::Params{});
   return check_launch();
 }
 

@@ -114,6 +114,44 @@ def main(out_path: str) -> None:
     t = torch.tensor([e0.elapsed_time(e1) / 5], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     res["sync_push_gbs"] = big / (float(t) * 1e-3) / 1e9
+    # 4. policy engine: optimizer step through the fused peer-memory path vs the NCCL path
+    from axon_b200.models.config import get_config
+    from axon_b200.models.dense import DenseModel
+    from axon_b200.protocol import DataProto
+    from axon_b200.trainer.policy import OptimConfig, PolicyEngine
+    mcfg = get_config("tiny-gpu")
+    engines = []
+    for fused in (True, False):
+        mdl = DenseModel(mcfg, device=dev, dtype=torch.bfloat16)
+        mdl.params.init_random(seed=5)
+        engines.append(PolicyEngine(mdl, OptimConfig(lr=1e-3, grad_clip=1.0), process_group=dist.group.WORLD,
+                                    max_token_len_per_gpu=512, fused_zero1=fused))
+    res["engine_fused_active"] = engines[0].fused is not None and engines[1].fused is None
+    gen = torch.Generator().manual_seed(50 + rank)
+    B, T = 4, 96
+    ids = torch.randint(0, mcfg.vocab_size, (B, T), generator=gen)
+    att = torch.ones(B, T, dtype=torch.long)
+    att[0, 70:] = 0
+    rmask = att.clone().float()
+    rmask[:, :16] = 0
+    for step in range(2):
+        for e in engines:
+            data = DataProto.from_dict({"input_ids": ids, "attention_mask": att, "response_mask": rmask,
+                                        "advantages": torch.randn(B, T, generator=torch.Generator().manual_seed(step)) * rmask,
+                                        "old_log_probs": torch.zeros(B, T)})
+            data.batch["old_log_probs"] = e.forward(data, want_entropy=False).batch["log_probs"].cpu()
+            data.meta_info["temperature"] = 1.0
+            e.forward_backward(data, "ppo", {"clip_ratio": 0.2})
+            out = e.optim_step()
+            res.setdefault("engine_norms", []).append(out["grad_norm"])
+    torch.cuda.synchronize()
+    a, b = engines[0].model.params.flat.float(), engines[1].model.params.flat.float()
+    res["engine_param_diff"] = float((a - b).abs().max())
+    res["engine_param_moved"] = float((a - DenseModel(mcfg, device=dev).params.flat.float()).abs().max()) > 0
+    chk = a.double().sum().reshape(1)
+    allc = [torch.zeros_like(chk) for _ in range(world)]
+    dist.all_gather(allc, chk)
+    res["engine_replicas_equal"] = all(float(c) == float(allc[0]) for c in allc)
     bar()
     torch.cuda.synchronize()
     C.check_status()

