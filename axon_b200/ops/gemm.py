@@ -33,6 +33,7 @@ def _native_gemm(a, b, out, M, N, K, a_mn, b_mn, mode, alpha=1.0, bn_hint=0, max
 SMALL_M = 256  # token batches up to this size take the swap-AB + split-K path (decode)
 
 
+FIXED_CONFIG = False        # batch-invariant mode: one tile width, no K split, whatever the batch size
 USE_CLUSTER_DECODE = True   # cluster split-K kernel (partials reduced through distributed shared memory)
 
 
@@ -66,7 +67,9 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
         r = alpha * (a.float() @ b.float().t())
         out.copy_(out.float() + r if accumulate else r)
         return out
-    if M <= SMALL_M and not accumulate and alpha == 1.0 and bn_hint == 0 and N >= 512:
+    if FIXED_CONFIG:
+        bn_hint = bn_hint or 128
+    elif M <= SMALL_M and not accumulate and alpha == 1.0 and bn_hint == 0 and N >= 512:
         return _native_gemm_smallm(a, b, out, M, N, K)
     mode = {torch.bfloat16: ACC_BF16 if accumulate else OUT_BF16,
             torch.float32: ACC_F32 if accumulate else OUT_F32}[out.dtype]
