@@ -117,6 +117,27 @@ class ColocatedRLRunner:
         self.seed = seed
         self.global_step = 0
         self.timing: dict[str, float] = {}
+        self.phase_detail: dict = {}
+        if self.device.type == "cuda":
+            # Make step 1 look like every later step: the optimizer state exists from the start, and if
+            # rollouts will need its memory the pinned host buffers it moves to are allocated now
+            # (pinning tens of GB takes tens of seconds and must not land inside a step).
+            self.policy.init_optimizer()
+            if self._will_offload():
+                self.policy.prepare_offload_buffers()
+
+    def _kv_need(self) -> tuple[int, int]:
+        need = PagedKVCache.bytes_per_page(self.model.cfg, self.model.params.flat.element_size())
+        want_pages = self.cfg.max_num_seqs * ((self.cfg.max_prompt_length + self.cfg.max_response_length) // 128 + 1)
+        return need, want_pages
+
+    def _will_offload(self) -> bool:
+        if self.cfg.offload_optimizer is not None:
+            return bool(self.cfg.offload_optimizer)
+        need, want_pages = self._kv_need()
+        grads = 0 if self.model.params.grad_flat is None or getattr(self.model.params, "grads_persistent", False) \
+            else self.model.params.grad_flat.numel() * 4
+        return (self._free_bytes() + grads) * self.cfg.kv_memory_fraction < want_pages * need * 0.5
 
     # ------------------------------------------------------------------ memory phases
     def _free_bytes(self) -> int:
@@ -128,11 +149,8 @@ class ColocatedRLRunner:
     def _enter_rollout(self) -> None:
         ta = time.perf_counter()
         self.model.params.free_grads()
-        need = PagedKVCache.bytes_per_page(self.model.cfg, self.model.params.flat.element_size())
-        want_pages = self.cfg.max_num_seqs * ((self.cfg.max_prompt_length + self.cfg.max_response_length) // 128 + 1)
-        off = self.cfg.offload_optimizer
-        if off is None:
-            off = self._free_bytes() * self.cfg.kv_memory_fraction < want_pages * need * 0.5
+        need, want_pages = self._kv_need()
+        off = self._will_offload()
         if off:
             self.policy.offload_optimizer()
         tb = time.perf_counter()

@@ -57,9 +57,10 @@ def _numel(shape) -> int:
 class FlatParams:
     """Named views over one flat buffer (+ optional fp32 main grads with the same offsets)."""
 
-    def __init__(self, cfg: ModelConfig, device, dtype=torch.bfloat16, flat: torch.Tensor | None = None):
+    def __init__(self, cfg: ModelConfig, device, dtype=torch.bfloat16, flat: torch.Tensor | None = None,
+                 layout: "OrderedDict[str, tuple[int, ...]] | None" = None):
         self.cfg = cfg
-        self.layout = param_layout(cfg)
+        self.layout = layout if layout is not None else param_layout(cfg)
         self.offsets: dict[str, tuple[int, int]] = {}
         off = 0
         for name, shape in self.layout.items():

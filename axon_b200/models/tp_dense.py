@@ -1,0 +1,274 @@
+"""Tensor-parallel dense decoder with sequence-parallel activations (Megatron-style layout).
+
+Each of the W ranks of a tensor-parallel group holds, per layer, the rows of the fused QKV and
+gate/up projections for its share of the heads / FFN units (column-parallel) and the matching
+columns of the attention-output and down projections (row-parallel). Norm weights, the embedding and
+the vocabulary head are replicated. The residual stream is sharded along the token dimension: every
+rank owns T/W packed tokens, norms and the vocabulary head run on those rows only, and full-length
+activations exist only between an all-gather -> GEMM and the following GEMM -> reduce-scatter
+(``parallel/tp.TPContext``: both fused with the GEMM over NVLink peer memory on CUDA).
+
+Backward recomputes a layer from its saved local input; there the gathered activations are needed
+twice (input gradient and weight gradient), so they are gathered once explicitly. Gradients of the
+replicated parameters are partial per rank (local tokens) and are summed over the group by
+``sync_replicated_grads`` before the optimizer step.
+
+(reference: axon/trainer/megatron_trainer.py:164-173 with Megatron-Core column/row-parallel linears
+and ``sequence_parallel: true``; parameter sharding as in axon/utils/p2p/param_mapper.py.)
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import torch
+
+from ..ops import activation as A
+from ..ops import attention as AT
+from ..ops import gemm as G
+from ..ops import lm_head as LM
+from ..ops import norm as N
+from ..ops import rope as R
+from ..parallel.tp import TPContext
+from ..utils.p2p.param_mapper import shard_rows, split_kind
+from .config import ModelConfig
+from .dense import PackedBatch
+from .params import FlatParams, param_layout
+
+REPLICATED_KINDS = ("replicated", "vocab")
+
+
+def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int) -> "OrderedDict[str, tuple[int, ...]]":
+    out: OrderedDict[str, tuple[int, ...]] = OrderedDict()
+    for name, full in param_layout(cfg).items():
+        if split_kind(name) in REPLICATED_KINDS or tp == 1:
+            out[name] = tuple(full)
+            continue
+        boxes = shard_rows(cfg, name, tp, tp_rank)
+        rows = sum(b[1] - b[0] for b in boxes)
+        out[name] = (rows, boxes[0][3] - boxes[0][2])
+    return out
+
+
+def slice_full_param(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, tp_rank: int) -> torch.Tensor:
+    if split_kind(name) in REPLICATED_KINDS or tp == 1:
+        return full
+    return torch.cat([full[a:b, c:d] for a, b, c, d in shard_rows(cfg, name, tp, tp_rank)], 0)
+
+
+def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, int]:
+    """Append a dummy sequence so that the token count is a multiple of ``multiple`` (labels -100)."""
+    T = batch.input_ids.numel()
+    pad = (-T) % multiple
+    if pad == 0:
+        return batch, T
+    dev = batch.input_ids.device
+    z = lambda n, v, dt: torch.full((n,), v, dtype=dt, device=dev)      # noqa: E731
+    return PackedBatch(torch.cat([batch.input_ids, z(pad, 0, batch.input_ids.dtype)]),
+                       torch.cat([batch.position_ids, torch.arange(pad, dtype=batch.position_ids.dtype, device=dev)]),
+                       torch.cat([batch.cu_seqlens, torch.tensor([T + pad], dtype=batch.cu_seqlens.dtype, device=dev)]),
+                       torch.cat([batch.labels, z(pad, -100, batch.labels.dtype)]),
+                       max(batch.max_seqlen, pad)), T
+
+
+class TPDenseModel:
+    def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16):
+        assert cfg.num_experts == 0
+        assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
+        self.cfg, self.tp = cfg, tp
+        self.device, self.dtype = torch.device(device), dtype
+        self.params = FlatParams(cfg, self.device, dtype, layout=tp_param_layout(cfg, tp.world, tp.rank))
+        self.hq, self.hkv = cfg.num_attention_heads // tp.world, cfg.num_key_value_heads // tp.world
+        self._saved = None
+
+    # ------------------------------------------------------------------ parameters
+    def load_full_state(self, full_views: dict) -> None:
+        for name, dst in self.params.views.items():
+            dst.copy_(slice_full_param(self.cfg, name, full_views[name].to(dst.device), self.tp.world, self.tp.rank).to(dst.dtype))
+
+    def init_random(self, std: float = 0.02, seed: int = 0) -> None:
+        """Same values as ``FlatParams.init_random`` of the unsharded model with this seed."""
+        ref = FlatParams(self.cfg, self.device, self.dtype)
+        ref.init_random(std=std, seed=seed)
+        self.load_full_state(ref.views)
+
+    def replicated_names(self) -> list[str]:
+        return [n for n in self.params.layout if split_kind(n) in REPLICATED_KINDS]
+
+    def sync_replicated_grads(self) -> None:
+        """Sum the partial gradients of replicated parameters over the tensor-parallel group."""
+        if self.tp.world == 1 or self.params.grad_flat is None:
+            return
+        names = self.replicated_names()
+        flat = torch.cat([self.params.grads[n].reshape(-1) for n in names])
+        self.tp.all_reduce_(flat)
+        off = 0
+        for n in names:
+            g = self.params.grads[n]
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+
+    def grad_sumsq(self) -> torch.Tensor:
+        """This rank's contribution to the global squared gradient norm: sharded parameters in full,
+        replicated ones (identical on every rank after ``sync_replicated_grads``) divided by W."""
+        g = self.params.grad_flat
+        total = g.double().pow(2).sum()
+        if self.tp.world > 1:
+            rep = sum(self.params.grads[n].double().pow(2).sum() for n in self.replicated_names())
+            total = total - rep * (1.0 - 1.0 / self.tp.world)
+        return total
+
+    def _p(self, l, name):
+        return self.params[f"model.layers.{l}.{name}"]
+
+    def _g(self, l, name):
+        return self.params.grads[f"model.layers.{l}.{name}"]
+
+    def head_weight(self):
+        return self.params["model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight"]
+
+    def head_grad(self):
+        return self.params.grads["model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight"]
+
+    # ------------------------------------------------------------------ one layer
+    def _attn(self, l, qkv, batch, tables, need_lse):
+        c = self.cfg
+        qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
+        kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
+        qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], self.hq, self.hkv, c.head_dim, qw, kw, c.rms_norm_eps)
+        o, lse = AT.attn_fwd(qkv_r, batch.cu_seqlens, self.hq, self.hkv, c.head_dim, need_lse=need_lse)
+        return qkv_r, o, lse
+
+    def layer_fwd(self, l, x, delta, batch, tables):
+        """x (+ delta): local rows [T/W, H] of the stream entering the layer -> (x1, mlp_out, xin), all local rows."""
+        c, tp = self.cfg, self.tp
+        h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
+        qkv = tp.allgather_gemm(h, self._p(l, "self_attn.qkv_proj.weight"))
+        _, o, _ = self._attn(l, qkv, batch, tables, need_lse=False)
+        ao = tp.gemm_reduce_scatter(o, self._p(l, "self_attn.o_proj.weight"))
+        h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
+        gu = tp.allgather_gemm(h2, self._p(l, "mlp.gate_up_proj.weight"))
+        a = A.swiglu_fwd(gu)
+        mo = tp.gemm_reduce_scatter(a, self._p(l, "mlp.down_proj.weight"))
+        return x1, mo, xin
+
+    def layer_bwd(self, l, xin, dx_out, batch, tables):
+        c, tp = self.cfg, self.tp
+        qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
+        kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
+        # ---- recompute with explicit gathers (the gathered tensors feed both dgrad and wgrad)
+        h, rstd1, _ = N.rmsnorm_fwd(xin, self._p(l, "input_layernorm.weight"), c.rms_norm_eps)
+        h_full = tp.all_gather_rows(h)
+        qkv = G.gemm_nt(h_full, self._p(l, "self_attn.qkv_proj.weight"))
+        qkv_r, o, lse = self._attn(l, qkv, batch, tables, need_lse=True)
+        ao = tp.gemm_reduce_scatter(o, self._p(l, "self_attn.o_proj.weight"))
+        h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
+        h2_full = tp.all_gather_rows(h2)
+        gu = G.gemm_nt(h2_full, self._p(l, "mlp.gate_up_proj.weight"))
+        a = A.swiglu_fwd(gu)
+        # ---- MLP backward
+        dy_full = tp.all_gather_rows(dx_out)                                   # grad of the row-parallel output, all rows
+        da = G.gemm_nn(dy_full, self._p(l, "mlp.down_proj.weight"))
+        G.gemm_tn(dy_full, a, out=self._g(l, "mlp.down_proj.weight"), accumulate=True)
+        dgu = A.swiglu_bwd(da, gu)
+        del da, a, gu
+        G.gemm_tn(dgu, h2_full, out=self._g(l, "mlp.gate_up_proj.weight"), accumulate=True)
+        dh2 = tp.gemm_reduce_scatter(dgu, self._p(l, "mlp.gate_up_proj.weight"), w_is_kn=True)
+        del dgu, h2_full, dy_full
+        dx1 = N.rmsnorm_bwd(dh2, x1, self._p(l, "post_attention_layernorm.weight"), rstd2,
+                            self._g(l, "post_attention_layernorm.weight"), dres=dx_out)
+        # ---- attention backward
+        dao_full = tp.all_gather_rows(dx1)
+        do = G.gemm_nn(dao_full, self._p(l, "self_attn.o_proj.weight"))
+        G.gemm_tn(dao_full, o, out=self._g(l, "self_attn.o_proj.weight"), accumulate=True)
+        dqkv_r = AT.attn_bwd(do, qkv_r, o, lse, batch.cu_seqlens, self.hq, self.hkv, c.head_dim)
+        dqkv = R.qknorm_rope_bwd(dqkv_r, qkv, batch.position_ids, tables[0], tables[1], self.hq, self.hkv, c.head_dim, qw, kw,
+                                 self._g(l, "self_attn.q_norm.weight") if c.qk_norm else None,
+                                 self._g(l, "self_attn.k_norm.weight") if c.qk_norm else None, c.rms_norm_eps)
+        G.gemm_tn(dqkv, h_full, out=self._g(l, "self_attn.qkv_proj.weight"), accumulate=True)
+        dh = tp.gemm_reduce_scatter(dqkv, self._p(l, "self_attn.qkv_proj.weight"), w_is_kn=True)
+        return N.rmsnorm_bwd(dh, xin, self._p(l, "input_layernorm.weight"), rstd1, self._g(l, "input_layernorm.weight"), dres=dx1)
+
+    # ------------------------------------------------------------------ whole model
+    def local_slice(self, T: int) -> slice:
+        n = T // self.tp.world
+        return slice(self.tp.rank * n, (self.tp.rank + 1) * n)
+
+    def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
+        """``batch`` is the full packed batch, its length a multiple of 128 * W (``pad_packed_batch``).
+        Returns (log-prob, entropy) of THIS rank's tokens [T/W]."""
+        c = self.cfg
+        T = batch.input_ids.numel()
+        assert T % (128 * self.tp.world) == 0, "pad the batch with pad_packed_batch(batch, 128 * tp)"
+        sl = self.local_slice(T)
+        tables = R.rope_tables(max(int(batch.max_seqlen) or c.max_position_embeddings, 8), c.head_dim, c.rope_theta, self.device)
+        x = A.embedding_fwd(batch.input_ids[sl].contiguous(), self.params["model.embed_tokens.weight"])
+        delta, inputs = None, []
+        for l in range(c.num_hidden_layers):
+            x, delta, xin = self.layer_fwd(l, x, delta, batch, tables)
+            if save_for_backward:
+                inputs.append(xin)
+        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        # the parameter gradient of a qk-norm weight is partial per rank (local heads); norms over the
+        # hidden size see local tokens only — both are summed by sync_replicated_grads
+        labels = batch.labels[sl].contiguous()
+        lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), labels, temperature)
+        if save_for_backward:
+            self._saved = dict(batch=batch, tables=tables, inputs=inputs, xf=xf, hf=hf, rstd_f=rstd_f, lse=lse, ent=ent,
+                               labels=labels, temperature=temperature, sl=sl)
+        return lp, ent
+
+    def backward(self, g_logprob, g_entropy=None) -> None:
+        s = self._saved
+        assert s is not None
+        self._saved = None
+        c = self.cfg
+        self.params.alloc_grads()
+        g_lp = None if g_logprob is None else g_logprob.float().contiguous()
+        g_ent = None if g_entropy is None else g_entropy.float().contiguous()
+        dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
+                            dweight=self.head_grad())
+        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"])
+        for l in reversed(range(c.num_hidden_layers)):
+            dx = self.layer_bwd(l, s["inputs"].pop(), dx, s["batch"], s["tables"])
+        A.embedding_bwd(s["batch"].input_ids[s["sl"]].contiguous(), dx, self.params.grads["model.embed_tokens.weight"])
+
+
+class TPModelAdapter:
+    """Gives a tensor-parallel model the interface of ``DenseModel`` (full-batch log-probs in, full-batch
+    gradients out), so the policy engine and the loss code run unchanged on every TP rank: local
+    log-probs are all-gathered over the group, incoming gradients are cut back to the local rows."""
+
+    def __init__(self, model: TPDenseModel):
+        self.inner, self.tp = model, model.tp
+        self.cfg, self.params, self.device, self.dtype = model.cfg, model.params, model.device, model.dtype
+        self.recompute = "full"
+        self._T = self._T_real = 0
+
+    def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
+        padded, self._T_real = pad_packed_batch(batch, 128 * self.tp.world)
+        self._T = padded.input_ids.numel()
+        lp, ent = self.inner.forward(padded, temperature, save_for_backward)
+        lp_full = self.tp.all_gather_rows(lp.contiguous())[: self._T_real]
+        ent_full = self.tp.all_gather_rows(ent.contiguous())[: self._T_real]
+        return lp_full, ent_full
+
+    def backward(self, g_logprob, g_entropy=None) -> None:
+        sl = self.inner.local_slice(self._T)
+
+        def cut(g):
+            if g is None:
+                return None
+            full = torch.zeros(self._T, dtype=torch.float32, device=g.device)
+            full[: self._T_real] = g.float()
+            return full[sl].contiguous()
+        self.inner.backward(cut(g_logprob), cut(g_entropy))
+
+    def sync_replicated_grads(self) -> None:
+        self.inner.sync_replicated_grads()
+
+    def replicated_ranges(self) -> list[tuple[int, int]]:
+        return [(o, o + n) for name, (o, n) in self.params.offsets.items() if name in set(self.inner.replicated_names())]
+
+    def flops_per_token(self, seqlen: int) -> float:
+        from .dense import DenseModel
+        return DenseModel.flops_per_token(self, seqlen) / self.tp.world

@@ -1,0 +1,133 @@
+"""Tensor parallelism with sequence-parallel activations: the two collectives that bracket every
+sharded linear layer, fused with the GEMM through NVLink peer memory.
+
+    all-gather -> GEMM     column-parallel layers (QKV, gate/up): the [T/W, K] activation shards stay
+                           where they are; each rank's GEMM streams the A tiles of the other ranks with
+                           TMA directly out of their memory (``axb_gemm_allgather_a``). No gathered
+                           copy, no separate collective.
+    GEMM -> reduce-scatter row-parallel layers (attention output, down projection) and the dgrad of
+                           column-parallel layers: the GEMM epilogue stores every finished tile into the
+                           staging slot of the rank that owns those rows (``axb_gemm_scatter``), a device
+                           barrier follows, and a fixed-order sum over the W slots produces the local
+                           [T/W, N] rows (``axb_rs_reduce``) — deterministic, bf16 on the wire like the
+                           NCCL reduce-scatter it replaces.
+
+(reference: Megatron-Core tensor/sequence parallel linears used through
+axon/trainer/megatron_trainer.py:164-173 and axon/utils/megatron/tensor_parallel.py:52-94.)
+CPU tensors and single-rank groups fall back to ``torch.distributed`` collectives + plain GEMMs.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _common as C
+from ..ops import gemm as G
+from .symm import PeerBarrier, SymmetricBuffer
+
+
+class TPContext:
+    """Per-process state of one tensor-parallel group: symmetric workspaces and the device barrier."""
+
+    def __init__(self, group=None, device=None, max_rows_per_rank: int = 0, max_width: int = 0, fused: bool | None = None):
+        self.group = group
+        live = dist.is_initialized() and group is not None
+        self.world = dist.get_world_size(group) if live else 1
+        self.rank = dist.get_rank(group) if live else 0
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        if fused is None:
+            fused = self.world > 1 and self.device.type == "cuda" and dist.get_backend(group) == "nccl"
+        self.fused = bool(fused)
+        self.rows, self.width = max_rows_per_rank, max_width
+        self._ag = self._st = None
+        self._turn = 0
+        if self.fused:
+            assert max_rows_per_rank % 128 == 0 and max_rows_per_rank > 0 and max_width > 0
+            # two rotating sets so that a buffer is never rewritten while a slower peer may still read it
+            self._ag = [SymmetricBuffer(max_rows_per_rank * max_width, torch.bfloat16, group, self.device) for _ in range(2)]
+            self._st = [SymmetricBuffer(self.world * max_rows_per_rank * max_width, torch.bfloat16, group, self.device)
+                        for _ in range(2)]
+            self.barrier = PeerBarrier(group, self.device)
+            self._sync = torch.zeros(1, device=self.device)
+
+    # ------------------------------------------------------------------ plain collectives (fallback, backward gathers)
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x
+        out = torch.empty(self.world * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+        if dist.get_backend(self.group) == "gloo":
+            parts = [torch.empty_like(x) for _ in range(self.world)]
+            dist.all_gather(parts, x.contiguous(), group=self.group)
+            return torch.cat(parts, 0)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out
+
+    def reduce_scatter_rows(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x
+        n = x.shape[0] // self.world
+        if dist.get_backend(self.group) == "gloo":
+            y = x.float().contiguous()
+            dist.all_reduce(y, group=self.group)
+            return y[self.rank * n:(self.rank + 1) * n].to(x.dtype)
+        out = torch.empty(n, *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x.contiguous(), group=self.group)
+        return out
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    # ------------------------------------------------------------------ fused paths
+    def _align_streams(self) -> None:
+        # device barriers wait a bounded ~2 s; a stream-ordered NCCL all-reduce of one element first
+        # removes host-side skew between the ranks (plumbing, not data)
+        dist.all_reduce(self._sync, group=self.group)
+
+    def allgather_gemm(self, x_local: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False, out_dtype=None) -> torch.Tensor:
+        """x_local [T/W, K] (this rank's rows) -> concat(x)[T, K] @ (w [N, K]^T, or w [K, N] when ``w_is_kn``)."""
+        out_dtype = out_dtype or x_local.dtype
+        if not self.fused:
+            xf = self.all_gather_rows(x_local)
+            return G.gemm_nn(xf, w, out_dtype=out_dtype) if w_is_kn else G.gemm_nt(xf, w, out_dtype=out_dtype)
+        rows, K = x_local.shape
+        N = w.shape[1] if w_is_kn else w.shape[0]
+        assert rows % 128 == 0 and rows * K <= self.rows * self.width, "activation shard exceeds the TP workspace"
+        buf = self._ag[self._turn & 1]
+        self._turn += 1
+        buf.tensor[: rows * K].view(rows, K).copy_(x_local)
+        self._align_streams()
+        self.barrier()                                           # every rank's shard is in place
+        out = torch.empty(self.world * rows, N, dtype=out_dtype, device=x_local.device)
+        rc = C.lib().axb_gemm_allgather_a(buf.ptr_array(), self.world, self.rank, C.ptr(w), C.ptr(out), rows, N, K,
+                                          ctypes.c_longlong(K), ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(N),
+                                          int(w_is_kn), int(out_dtype == torch.float32), C.ptr(C.status(self.device)), C.stream())
+        C.launched(rc, "gemm_allgather_a")
+        return out
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False, residual: torch.Tensor | None = None):
+        """x [T, K_local] @ op(w) summed over the group, rows scattered: returns this rank's [T/W, N] (+ residual)."""
+        if not self.fused:
+            y = G.gemm_nn(x, w) if w_is_kn else G.gemm_nt(x, w)
+            out = self.reduce_scatter_rows(y)
+            return out if residual is None else (out.float() + residual.float()).to(out.dtype)
+        T, K = x.shape
+        N = w.shape[1] if w_is_kn else w.shape[0]
+        rows = T // self.world
+        assert T % self.world == 0 and rows * N <= self.rows * self.width and N % 8 == 0
+        st = self._st[self._turn & 1]
+        self._turn += 1
+        rc = C.lib().axb_gemm_scatter(C.ptr(x), C.ptr(w), st.ptr_array(), self.world, self.rank, T, N, K,
+                                      ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(N),
+                                      int(w_is_kn), C.ptr(C.status(self.device)), C.stream())
+        C.launched(rc, "gemm_scatter")
+        self._align_streams()
+        self.barrier()                                           # all partial tiles have landed in every owner
+        out = torch.empty(rows, N, dtype=x.dtype, device=x.device)
+        rc = C.lib().axb_rs_reduce(C.ptr(st.tensor), C.ptr(residual), C.ptr(out), self.world, ctypes.c_longlong(rows), N,
+                                   ctypes.c_longlong(N), ctypes.c_longlong(N), C.stream())
+        C.launched(rc, "rs_reduce")
+        return out

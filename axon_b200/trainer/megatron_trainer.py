@@ -1,0 +1,83 @@
+"""Model-parallel trainer worker (the reference's Megatron personality:
+axon/trainer/megatron_trainer.py:120-932, model functions axon/models/megatron_models.py).
+
+World layout: ``world = dp x tp`` with tensor-parallel groups of consecutive ranks (one NVLink domain)
+and data-parallel groups strided across them, as ``mpu.initialize_model_parallel`` lays them out.
+Tensor parallelism uses sequence-parallel activations with the fused all-gather->GEMM and
+GEMM->reduce-scatter kernels (``parallel/tp.py``); the optimizer is the sharded (distributed)
+AdamW of the policy engine over the data-parallel group. Data is dispatched per data-parallel rank
+and collected from tensor-parallel rank 0. Pipeline, context and expert parallel sizes other than 1
+are refused with an explicit error until their schedules land here.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .fsdp_trainer import CausalLM, RewardModel, TrainerWorker as _Base, ValueModel, _get  # noqa: F401
+
+
+class TrainerWorker(_Base):
+    def __init__(self, config, model=None, name: str = "trainer", **kwargs):
+        m = _get(config, "megatron", {}) or {}
+        self.tp_size = int(_get(m, "tensor_model_parallel_size", 1) or 1)
+        for key, label in (("pipeline_model_parallel_size", "pipeline"), ("context_parallel_size", "context"),
+                           ("expert_model_parallel_size", "expert")):
+            if int(_get(m, key, 1) or 1) != 1:
+                raise NotImplementedError(f"{label} parallelism > 1 is not available in this trainer yet "
+                                          f"(megatron.{key}={_get(m, key)}); use tensor and data parallelism")
+        self._pending_dispatch = True
+        super().__init__(config, model=model, name=name, **kwargs)
+
+    # the base class registers dp_rank = rank // sp; with TP the data shard is rank // tp
+    def _register_dispatch_collect_info(self, mesh_name: str, dp_rank: int, is_collect: bool) -> None:
+        if mesh_name == "trainer" and getattr(self, "_pending_dispatch", False):
+            self._pending_dispatch = False
+            assert self.world_size % self.tp_size == 0, f"world size {self.world_size} not divisible by tp {self.tp_size}"
+            return super()._register_dispatch_collect_info(mesh_name, self.rank // self.tp_size, self.rank % self.tp_size == 0)
+        return super()._register_dispatch_collect_info(mesh_name, dp_rank, is_collect)
+
+    def _make_groups(self):
+        """(tp group, dp group) of this rank; every rank creates every group (collective contract)."""
+        tp, world = self.tp_size, self.world_size
+        tp_group = dp_group = None
+        if world == 1:
+            return None, None
+        for i in range(world // tp):
+            ranks = list(range(i * tp, (i + 1) * tp))
+            g = dist.new_group(ranks)
+            if self.rank in ranks:
+                tp_group = g
+        for j in range(tp):
+            ranks = list(range(j, world, tp))
+            g = dist.new_group(ranks)          # also for a single rank: the optimizer needs a group of its own
+            if self.rank in ranks:
+                dp_group = g
+        return tp_group, dp_group
+
+    def _build(self, model_path, dtype, seed):
+        if self.tp_size == 1:
+            return super()._build(model_path, dtype, seed)
+        if self.model_kind.value_head:
+            raise NotImplementedError("value-head models are not tensor-parallel yet; run the critic with tp=1")
+        from ..models.config import get_config
+        from ..models.tp_dense import TPDenseModel, TPModelAdapter
+        from ..parallel.tp import TPContext
+        mcfg = get_config(model_path)
+        tp_group, dp_group = self._make_groups()
+        self.pg = dp_group                          # the optimizer shards over the data-parallel group
+        rows = int(_get(self.config, "max_token_len_per_gpu", 16384))
+        rows = (rows // self.tp_size + 127) // 128 * 128 + 128
+        width = max(mcfg.qkv_size, 2 * mcfg.intermediate_size, mcfg.hidden_size) // 1
+        ctx = TPContext(tp_group, self.device, max_rows_per_rank=rows, max_width=width)
+        inner = TPDenseModel(mcfg, ctx, device=self.device, dtype=dtype)
+        import os
+        from ..utils.hf_model import has_hf_weights, iter_hf_weights
+        if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+            from ..models.params import FlatParams
+            ref = FlatParams(mcfg, "cpu", dtype)
+            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+            inner.load_full_state(ref.views)
+        else:
+            inner.init_random(seed=seed)
+        return TPModelAdapter(inner)

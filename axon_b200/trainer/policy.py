@@ -146,6 +146,12 @@ class PolicyEngine:
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
 
+    def prepare_offload_buffers(self) -> None:
+        """Allocate the pinned host buffers of ``offload_optimizer`` ahead of time."""
+        if self._host_state is None and self.master is not None and self.device.type == "cuda":
+            self._host_state = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
+                                for k, v in (("master", self.master), ("m", self.exp_avg), ("v", self.exp_avg_sq))}
+
     def offload_optimizer(self) -> None:
         """Move master / moments to pinned host memory (frees HBM for the KV pool during rollout)."""
         if self.master is None or self.device.type != "cuda":
@@ -296,6 +302,8 @@ class PolicyEngine:
         shard, gather the updated bf16 parameters. Skips the update when the norm is not finite."""
         p = self.model.params
         assert p.grad_flat is not None, "no gradients accumulated"
+        if hasattr(self.model, "sync_replicated_grads"):
+            self.model.sync_replicated_grads()
         if self.master is None:
             self.load_optimizer()
             if self.master is None:
@@ -316,9 +324,12 @@ class PolicyEngine:
             grad_shard = self._reduce_scatter_grads()
         else:
             grad_shard = p.grad_flat[lo:hi]
+        if hasattr(self.model, "sync_replicated_grads") and self.world == 1:
+            pass        # single data-parallel rank: replicated gradients were summed before the reduce below
         OPT.sumsq(grad_shard, self.state)
         if self.world > 1:
             dist.all_reduce(self.state[:1], group=self.pg)
+        self._tensor_parallel_norm(grad_shard, lo)
         OPT.clip_coef(self.state, self.cfg.grad_clip, self.cfg.grad_norm_threshold)
         self.opt_step += 1
         lr = lr_at(self.cfg, self.sched_step + 1)
@@ -331,6 +342,24 @@ class PolicyEngine:
         p.zero_grads()
         st = self.state.tolist()
         return {"grad_norm": st[1], "lr": lr, "skipped": st[3]}
+
+    def _tensor_parallel_norm(self, grad_shard: torch.Tensor, lo: int) -> None:
+        """With a tensor-parallel model the squared norm is the sum over the TP ranks of their sharded
+        parameters plus the replicated parameters ONCE: sum_r S_r - (W - 1) * rep, where S_r is rank r's
+        full-buffer value and rep the replicated part (equal on every rank)."""
+        tp = getattr(self.model, "tp", None)
+        if tp is None or tp.world == 1:
+            return
+        rep = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for a, b in self.model.replicated_ranges():
+            a2, b2 = max(a, lo) - lo, min(b, lo + grad_shard.numel()) - lo
+            if b2 > a2:
+                rep += grad_shard[a2:b2].float().pow(2).sum()
+        if self.world > 1:
+            dist.all_reduce(rep, group=self.pg)
+        tot = self.state[:1].clone()
+        tp.all_reduce_(tot)
+        self.state[:1] = tot - (tp.world - 1) * rep
 
     def _padded_flat(self, t: torch.Tensor) -> torch.Tensor:
         need = self.shard_size * self.world

@@ -211,3 +211,122 @@ extern "C" int axb_gemm_grouped_wgrad(const void* dY, const void* X, float* dW, 
   return launch_gemm_inst<128, true, true, StoreEpi, KGroupedTiles>(dY, X, Nw, Kw, max_rows, lddy, ldx, ep, status, s, 0, 1,
                                                                      tp, max_rows, max_rows, tiles);
 }
+
+// ------------------------------------------------------------------ tensor-parallel fused GEMMs
+// All-gather -> GEMM: Y[T][N] = concat_r(X_r)[T][K] * op(W), X_r = rank r's [rows_per_rank][K] shard in
+// symmetric memory (x_ptrs[r] = its address mapped into this process). T = world * rows_per_rank,
+// rows_per_rank % 128 == 0. b_mn = 0: W is [N][K] (forward); b_mn = 1: W is [K][N] (dgrad through a
+// row-parallel layer). The caller has made sure (device barrier) that every rank's shard is complete.
+extern "C" int axb_gemm_allgather_a(const unsigned long long* x_ptrs, int world, int rank, const void* W, void* Y,
+                                    int rows_per_rank, int N, int K, long long ldx, long long ldw, long long ldy,
+                                    int b_mn, int out_fp32, int* status, void* stream) {
+  using namespace axb;
+  if (world < 1 || world > PeerGatherTiles::MAX_RANKS || rank < 0 || rank >= world || rows_per_rank <= 0 ||
+      rows_per_rank % GEMM_BM != 0 || (ldx & 7) || (ldw & 7))
+    return AXB_LAUNCH_BAD_ARG;
+  PeerGatherTiles::Params tp;
+  for (int r = 0; r < PeerGatherTiles::MAX_RANKS; ++r) {
+    const void* base = reinterpret_cast<const void*>(x_ptrs[r < world ? r : rank]);
+    int rc = make_tmap_2d(&tp.maps[r], base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, rows_per_rank, ldx * 2, GEMM_BK,
+                          GEMM_BM, true);
+    if (rc != AXB_LAUNCH_OK) return rc;
+  }
+  tp.world = world;
+  tp.rank = rank;
+  tp.blocks_per_rank = rows_per_rank / GEMM_BM;
+  const int T = world * rows_per_rank;
+  StoreEpi::Params ep{Y, ldy, out_fp32 ? 1 : 0, 1.0f};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const void* own = reinterpret_cast<const void*>(x_ptrs[rank]);
+  const int bn = (N % 256 == 0 || N > 2048) ? 256 : 128;
+#define AXB_AG(BN_, BMN_)                                                                                     \
+  return launch_gemm_inst<BN_, false, BMN_, StoreEpi, PeerGatherTiles>(own, W, T, N, K, ldx, ldw, ep, status, s, 0, 1, tp, \
+                                                                      rows_per_rank, -1)
+  if (bn == 256) {
+    if (b_mn) AXB_AG(256, true);
+    AXB_AG(256, false);
+  }
+  if (b_mn) AXB_AG(128, true);
+  AXB_AG(128, false);
+#undef AXB_AG
+}
+
+// GEMM -> reduce-scatter, part 1: partial[T][N] = X[T][K] * op(W); the epilogue stores every tile into the
+// staging slot [rank][local row][N] of the rank that owns the rows (staging_ptrs[r], bf16, row pitch ld).
+extern "C" int axb_gemm_scatter(const void* X, const void* W, const unsigned long long* staging_ptrs, int world, int rank,
+                                int T, int N, int K, long long ldx, long long ldw, long long ld, int b_mn, int* status,
+                                void* stream) {
+  using namespace axb;
+  if (world < 1 || world > PeerScatterEpi::MAX_RANKS || rank < 0 || rank >= world || T <= 0 || T % world != 0 ||
+      (ldx & 7) || (ldw & 7))
+    return AXB_LAUNCH_BAD_ARG;
+  PeerScatterEpi::Params ep;
+  for (int r = 0; r < PeerScatterEpi::MAX_RANKS; ++r) ep.staging[r] = reinterpret_cast<void*>(staging_ptrs[r < world ? r : rank]);
+  ep.ld = ld;
+  ep.rows_per_rank = T / world;
+  ep.rank = rank;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int bn = (N % 256 == 0 || N > 2048) ? 256 : 128;
+  if (bn == 256) {
+    if (b_mn) return launch_gemm_inst<256, false, true, PeerScatterEpi>(X, W, T, N, K, ldx, ldw, ep, status, s, 0);
+    return launch_gemm_inst<256, false, false, PeerScatterEpi>(X, W, T, N, K, ldx, ldw, ep, status, s, 0);
+  }
+  if (b_mn) return launch_gemm_inst<128, false, true, PeerScatterEpi>(X, W, T, N, K, ldx, ldw, ep, status, s, 0);
+  return launch_gemm_inst<128, false, false, PeerScatterEpi>(X, W, T, N, K, ldx, ldw, ep, status, s, 0);
+}
+
+namespace axb {
+// out[r][c] = sum over source ranks (in rank order) of staging[src][r][c] (+ residual), bf16 in / out.
+__global__ void rs_reduce_kernel(const __nv_bfloat16* __restrict__ staging, const __nv_bfloat16* __restrict__ residual,
+                                 __nv_bfloat16* __restrict__ out, int world, long long rows, int N, long long ld,
+                                 long long ldo) {
+  const long long vec_per_row = N / 8;
+  const long long total = rows * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row, v = i - r * vec_per_row;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < world; ++s) {
+      const uint4 q = reinterpret_cast<const uint4*>(staging + (static_cast<long long>(s) * rows + r) * ld)[v];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    if (residual != nullptr) {
+      const uint4 q = reinterpret_cast<const uint4*>(residual + r * ldo)[v];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + r * ldo)[v] = o;
+  }
+}
+}  // namespace axb
+
+// GEMM -> reduce-scatter, part 2 (after a barrier): sum this rank's staging slots in rank order.
+extern "C" int axb_rs_reduce(const void* staging, const void* residual, void* out, int world, long long rows, int N,
+                             long long ld, long long ldo, void* stream) {
+  using namespace axb;
+  if (world < 1 || rows <= 0 || N % 8 != 0 || (ld & 7) || (ldo & 7)) return AXB_LAUNCH_BAD_ARG;
+  const long long total = rows * (N / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  rs_reduce_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(staging), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<__nv_bfloat16*>(out), world, rows, N, ld, ldo);
+  return check_launch();
+}

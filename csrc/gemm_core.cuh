@@ -70,6 +70,7 @@ struct TileInfo {
 };
 
 struct DenseTiles {
+  static constexpr bool PEER_A = false;
   struct Params {};
   __device__ static int rows(const Params&, const GemmShape& sh) { return sh.M; }
   __device__ static int epi_rows(const Params&, const GemmShape& sh) { return sh.M; }
@@ -93,6 +94,7 @@ struct DenseTiles {
 // Rows of A / C are sorted by expert (128-row aligned); B holds E stacked weight matrices. Every
 // 128-row block belongs to one expert (tile_expert[m]); the number of live rows is read on the device.
 struct RowGroupedTiles {
+  static constexpr bool PEER_A = false;
   struct Params {
     const int* tile_expert;
     const int* total_rows;     // offsets[E]: padded row count actually in use
@@ -117,6 +119,7 @@ struct RowGroupedTiles {
 // Per-expert weight gradients: the contraction runs over the rows of one expert (a K range), the
 // output is that expert's [M, N] slice of a stacked [E*M, N] tensor.
 struct KGroupedTiles {
+  static constexpr bool PEER_A = false;
   struct Params {
     const int* offsets;        // [E + 1] row offsets (multiples of 128)
     int num_experts;
@@ -140,6 +143,36 @@ struct KGroupedTiles {
   }
 };
 
+// All-gather fused into the GEMM: A is row-sharded over `world` ranks (sequence-parallel activations in
+// symmetric memory); row block m lives on rank m / blocks_per_rank. Each A tile is fetched by TMA
+// straight from its owner's buffer (plain, non-multicast loads over NVLink) — no gathered copy exists.
+// Blocks are visited starting with this rank's own rows, then the next rank's, so the ranks do not all
+// pull from the same peer at the same time.
+struct PeerGatherTiles {
+  static constexpr bool PEER_A = true;
+  static constexpr int MAX_RANKS = 8;
+  struct Params {
+    CUtensorMap maps[MAX_RANKS];   // map r describes rank r's shard [rows_per_rank][K]
+    int world, rank, blocks_per_rank;
+  };
+  __device__ static int rows(const Params&, const GemmShape& sh) { return sh.M; }
+  __device__ static int epi_rows(const Params&, const GemmShape& sh) { return sh.M; }
+  __device__ static int num_tiles(const Params&, const GemmShape&, int num_m, int num_n) { return num_m * num_n; }
+  __device__ static TileInfo decode(const Params& p, const GemmShape&, int t, int num_m, int num_n, int num_k) {
+    TileInfo ti;
+    tile_coords(t, num_m, num_n, 1, ti.m_blk, ti.n_blk, ti.split);
+    ti.m_blk = (ti.m_blk + p.rank * p.blocks_per_rank) % num_m;      // own rows first
+    ti.kb0 = 0;
+    ti.kb1 = num_k;
+    ti.b_off = 0;
+    ti.epi_m_blk = ti.m_blk;
+    ti.valid = true;
+    return ti;
+  }
+  __device__ static const CUtensorMap* a_map(const Params& p, int m_blk) { return &p.maps[m_blk / p.blocks_per_rank]; }
+  __device__ static int a_row(const Params& p, int m_blk) { return (m_blk % p.blocks_per_rank) * GEMM_BM; }
+};
+
 // Epi contract:
 //   struct Params;                                   // POD passed by value
 //   __device__ Epi(const Params&, int m_blk, int n_blk, int row, const GemmShape&, int split);
@@ -149,7 +182,7 @@ template <int BN, bool A_MN, bool B_MN, class Epi, class TM = DenseTiles>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const GemmShape shape, const typename Epi::Params ep, int* status,
-               const typename TM::Params tp = typename TM::Params{}) {
+               const __grid_constant__ typename TM::Params tp) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -213,7 +246,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* sA = smem + s * S::STAGE_BYTES;
           uint8_t* sB = sA + S::A_BYTES;
           mbar_expect_tx(&full[s], S::STAGE_BYTES);
-          if (!A_MN) {
+          if constexpr (TM::PEER_A) {
+            static_assert(!TM::PEER_A || !A_MN, "peer-gathered A operands are K-major");
+            tma_load_2d(sA, TM::a_map(tp, m_blk), &full[s], kb * GEMM_BK, TM::a_row(tp, m_blk));
+          } else if (!A_MN) {
             tma_load_2d(sA, &tmA, &full[s], kb * GEMM_BK, m_blk * GEMM_BM);
           } else {
 #pragma unroll
@@ -378,6 +414,46 @@ struct StoreEpi {
           c[j] = accum ? c[j] + v : v;
         }
       }
+    }
+  }
+  __device__ __forceinline__ void finish() {}
+};
+
+// ------------------------------------------------------------------------- peer scatter epilogue
+// Reduce-scatter fused into the GEMM: every rank computes a partial [T][N]; the rows are owned by
+// rank row / rows_per_rank. The epilogue stores each 128 x 32 piece, as bf16, straight into the owner's
+// staging area slot [source rank][local row][N] with plain peer stores, so the NVLink transfer runs tile
+// by tile underneath the remaining MMAs. A barrier and a fixed-order sum over the slots finish it.
+struct PeerScatterEpi {
+  static constexpr int MAX_RANKS = 8;
+  struct Params {
+    void* staging[MAX_RANKS];   // rank r's staging buffer: [world][rows_per_rank][ld] bf16
+    long long ld;
+    int rows_per_rank, rank;
+  };
+  const Params& p;
+  const GemmShape& sh;
+  int row;
+  __device__ PeerScatterEpi(const Params& p_, int, int, int row_, const GemmShape& sh_, int)
+      : p(p_), sh(sh_), row(row_) {}
+  __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
+    if (row >= sh.M || col0 >= sh.N) return;
+    const int owner = row / p.rows_per_rank;
+    const int local = row - owner * p.rows_per_rank;
+    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.staging[owner]) +
+                       (static_cast<long long>(p.rank) * p.rows_per_rank + local) * p.ld + col0;
+    if (col0 + 32 <= sh.N && (p.ld & 7) == 0) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 o;
+        o.x = pack_bf16x2(__uint_as_float(acc[8 * v + 0]), __uint_as_float(acc[8 * v + 1]));
+        o.y = pack_bf16x2(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
+        o.z = pack_bf16x2(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
+        o.w = pack_bf16x2(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
+        reinterpret_cast<uint4*>(c)[v] = o;
+      }
+    } else {
+      for (int j = 0; j < 32 && col0 + j < sh.N; ++j) c[j] = __float2bfloat16(__uint_as_float(acc[j]));
     }
   }
   __device__ __forceinline__ void finish() {}
