@@ -35,12 +35,19 @@ from .dense import PackedBatch
 from .params import FlatParams, param_layout
 
 REPLICATED_KINDS = ("replicated", "vocab")
+_SHARD_HEAD = False      # set per model: the untied output head split by vocabulary rows
 
 
-def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int) -> "OrderedDict[str, tuple[int, ...]]":
+def _replicated(name: str, shard_head: bool) -> bool:
+    if shard_head and name == "lm_head.weight":
+        return False
+    return split_kind(name) in REPLICATED_KINDS
+
+
+def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = False) -> "OrderedDict[str, tuple[int, ...]]":
     out: OrderedDict[str, tuple[int, ...]] = OrderedDict()
     for name, full in param_layout(cfg).items():
-        if split_kind(name) in REPLICATED_KINDS or tp == 1:
+        if _replicated(name, shard_head) or tp == 1:
             out[name] = tuple(full)
             continue
         boxes = shard_rows(cfg, name, tp, tp_rank)
@@ -49,8 +56,8 @@ def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int) -> "OrderedDict[str
     return out
 
 
-def slice_full_param(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, tp_rank: int) -> torch.Tensor:
-    if split_kind(name) in REPLICATED_KINDS or tp == 1:
+def slice_full_param(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, tp_rank: int, shard_head: bool = False) -> torch.Tensor:
+    if _replicated(name, shard_head) or tp == 1:
         return full
     return torch.cat([full[a:b, c:d] for a, b, c, d in shard_rows(cfg, name, tp, tp_rank)], 0)
 
@@ -71,19 +78,25 @@ def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, in
 
 
 class TPDenseModel:
-    def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16):
+    def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False):
         assert cfg.num_experts == 0
         assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
-        self.params = FlatParams(cfg, self.device, dtype, layout=tp_param_layout(cfg, tp.world, tp.rank))
+        self.shard_head = bool(vocab_parallel_head) and not cfg.tie_word_embeddings and tp.world > 1
+        self.params = FlatParams(cfg, self.device, dtype, layout=tp_param_layout(cfg, tp.world, tp.rank, self.shard_head))
+        self.vp_head = None
+        if self.shard_head:
+            from ..parallel.vocab_parallel import VocabParallelHead
+            self.vp_head = VocabParallelHead(tp, cfg.vocab_size)
         self.hq, self.hkv = cfg.num_attention_heads // tp.world, cfg.num_key_value_heads // tp.world
         self._saved = None
 
     # ------------------------------------------------------------------ parameters
     def load_full_state(self, full_views: dict) -> None:
         for name, dst in self.params.views.items():
-            dst.copy_(slice_full_param(self.cfg, name, full_views[name].to(dst.device), self.tp.world, self.tp.rank).to(dst.dtype))
+            dst.copy_(slice_full_param(self.cfg, name, full_views[name].to(dst.device), self.tp.world, self.tp.rank,
+                                       self.shard_head).to(dst.dtype))
 
     def init_random(self, std: float = 0.02, seed: int = 0) -> None:
         """Same values as ``FlatParams.init_random`` of the unsharded model with this seed."""
@@ -92,7 +105,7 @@ class TPDenseModel:
         self.load_full_state(ref.views)
 
     def replicated_names(self) -> list[str]:
-        return [n for n in self.params.layout if split_kind(n) in REPLICATED_KINDS]
+        return [n for n in self.params.layout if _replicated(n, self.shard_head)]
 
     def sync_replicated_grads(self) -> None:
         """Sum the partial gradients of replicated parameters over the tensor-parallel group."""
@@ -211,10 +224,15 @@ class TPDenseModel:
         # the parameter gradient of a qk-norm weight is partial per rank (local heads); norms over the
         # hidden size see local tokens only — both are summed by sync_replicated_grads
         labels = batch.labels[sl].contiguous()
-        lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), labels, temperature)
+        if self.vp_head is not None:
+            lp, ent, head_ctx = self.vp_head.forward(hf, self.head_weight(), batch.labels, temperature)
+            lse = None
+        else:
+            lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), labels, temperature)
+            head_ctx = None
         if save_for_backward:
             self._saved = dict(batch=batch, tables=tables, inputs=inputs, xf=xf, hf=hf, rstd_f=rstd_f, lse=lse, ent=ent,
-                               labels=labels, temperature=temperature, sl=sl)
+                               labels=labels, temperature=temperature, sl=sl, head_ctx=head_ctx)
         return lp, ent
 
     def backward(self, g_logprob, g_entropy=None) -> None:
@@ -225,8 +243,11 @@ class TPDenseModel:
         self.params.alloc_grads()
         g_lp = None if g_logprob is None else g_logprob.float().contiguous()
         g_ent = None if g_entropy is None else g_entropy.float().contiguous()
-        dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
-                            dweight=self.head_grad())
+        if s["head_ctx"] is not None:
+            dhf = self.vp_head.backward(s["head_ctx"], g_lp, g_ent, dweight=self.head_grad())
+        else:
+            dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
+                                dweight=self.head_grad())
         dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"])
         for l in reversed(range(c.num_hidden_layers)):
             dx = self.layer_bwd(l, s["inputs"].pop(), dx, s["batch"], s["tables"])

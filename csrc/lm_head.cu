@@ -127,7 +127,7 @@ struct DLogitsEpi {
     label = v ? p.labels[row] : -1;
     lse = v ? p.lse[row] : 0.f;
     ent = v ? p.entropy[row] : 0.f;
-    glp = (v && p.g_logprob && label >= 0) ? p.g_logprob[row] : 0.f;
+    glp = (v && p.g_logprob && label != -1) ? p.g_logprob[row] : 0.f;   // -1: ignored token; <= -2: label in another shard
     gent = (v && p.g_entropy) ? p.g_entropy[row] : 0.f;
   }
   __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
@@ -161,15 +161,16 @@ struct DLogitsEpi {
   __device__ __forceinline__ void finish() {}
 };
 
-template <class Epi>
+template <class Epi, class TM = DenseTiles>
 static int launch_head(const void* hidden, const void* W, int M, int V, int H, long long ldh, long long ldw,
-                       const typename Epi::Params& ep, int* status, cudaStream_t stream) {
+                       const typename Epi::Params& ep, int* status, cudaStream_t stream,
+                       const typename TM::Params& tp = typename TM::Params{}) {
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, hidden, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, H, M, ldh * 2, GEMM_BK, GEMM_BM, true);
   if (rc) return rc;
   rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, H, V, ldw * 2, GEMM_BK, 256, true);
   if (rc) return rc;
-  auto kern = gemm_tc_kernel<256, false, false, Epi>;
+  auto kern = gemm_tc_kernel<256, false, false, Epi, TM>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::TOTAL) != cudaSuccess)
@@ -180,8 +181,72 @@ static int launch_head(const void* hidden, const void* W, int M, int V, int H, l
   int grid = sm_count();
   if (tiles < grid) grid = tiles;
   GemmShape sh{M, V, H, 1};
-  kern<<<grid, GEMM_THREADS, GemmSmem<256>::TOTAL, stream>>>(tmA, tmB, sh, ep, status, DenseTiles::Params{});
+  kern<<<grid, GEMM_THREADS, GemmSmem<256>::TOTAL, stream>>>(tmA, tmB, sh, ep, status, tp);
   return check_launch();
+}
+
+// Vocabulary-parallel variant of the merge: one warp per row merges this rank's vocabulary tiles and
+// stores (max, sum exp, sum z*exp, label logit or 0) as one float4 into slot [this rank][local row] of the
+// statistics buffer of the rank that owns the row (peer store over NVLink; 16 bytes per token and rank).
+struct PeerStats {
+  float4* p[8];
+};
+__global__ void lmhead_reduce_to_peers_kernel(const float* __restrict__ partials, const float* __restrict__ label_logit,
+                                              const int* __restrict__ labels_local, PeerStats stats, int rank,
+                                              int rows_per_rank, int M, int num_n) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= M) return;
+  float m = -INFINITY, s = 0.f, sx = 0.f;
+  for (int i = lane; i < num_n; i += 32) {
+    const float* o = partials + ((long long)row * num_n + i) * 3;
+    const float pm = o[0], ps = o[1], px = o[2];
+    const float nm = fmaxf(m, pm);
+    const float a = (m == -INFINITY) ? 0.f : __expf(m - nm);
+    const float b = (pm == -INFINITY) ? 0.f : __expf(pm - nm);
+    s = s * a + ps * b;
+    sx = sx * a + px * b;
+    m = nm;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float pm = __shfl_xor_sync(0xffffffffu, m, o);
+    const float ps = __shfl_xor_sync(0xffffffffu, s, o);
+    const float px = __shfl_xor_sync(0xffffffffu, sx, o);
+    const float nm = fmaxf(m, pm);
+    const float a = (m == -INFINITY) ? 0.f : __expf(m - nm);
+    const float b = (pm == -INFINITY) ? 0.f : __expf(pm - nm);
+    s = s * a + ps * b;
+    sx = sx * a + px * b;
+    m = nm;
+  }
+  if (lane == 0) {
+    const int owner = row / rows_per_rank, local = row - owner * rows_per_rank;
+    const float lab = labels_local[row] >= 0 ? label_logit[row] : 0.f;
+    stats.p[owner][(long long)rank * rows_per_rank + local] = make_float4(m, s, sx, lab);
+  }
+}
+
+// After the barrier: merge the W slots of every local row in rank order (identical result on any schedule).
+__global__ void lmhead_vp_finish_kernel(const float4* __restrict__ stats, const int* __restrict__ labels,
+                                        float* __restrict__ logprob, float* __restrict__ entropy,
+                                        float* __restrict__ lse_out, int world, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float m = -INFINITY;
+  for (int w = 0; w < world; ++w) m = fmaxf(m, stats[(long long)w * rows + r].x);
+  float s = 0.f, sx = 0.f, lab = 0.f;
+  for (int w = 0; w < world; ++w) {
+    const float4 v = stats[(long long)w * rows + r];
+    const float sc = (v.x == -INFINITY) ? 0.f : __expf(v.x - m);
+    s += v.y * sc;
+    sx += v.z * sc;
+    lab += v.w;
+  }
+  const float lse = m + logf(s);
+  lse_out[r] = lse;
+  entropy[r] = lse - sx / s;
+  logprob[r] = labels[r] >= 0 ? lab - lse : 0.f;
 }
 
 }  // namespace axb
@@ -218,4 +283,51 @@ extern "C" int axb_lmhead_dlogits(const void* hidden, const void* W, const int* 
   if (M <= 0 || V <= 0 || H <= 0 || (ldh & 7) || (ldw & 7) || temperature <= 0.f) return AXB_LAUNCH_BAD_ARG;
   DLogitsEpi::Params ep{(__nv_bfloat16*)dlogits, ld, labels, lse, entropy, g_logprob, g_entropy, 1.f / temperature};
   return launch_head<DLogitsEpi>(hidden, W, M, V, H, ldh, ldw, ep, status, (cudaStream_t)stream);
+}
+
+
+// Vocabulary-parallel forward, part 1. This rank holds W_shard [Vl][H] (vocabulary rows [v0, v0 + Vl)); the
+// hidden states are row-sharded over the ranks (h_ptrs[r] = rank r's [rows_per_rank][H] shard in symmetric
+// memory) and are read in place by the GEMM (all-gather fused, no gathered copy). labels_local: int32 [T],
+// the label minus v0 where this shard owns it, otherwise negative. The per-token statistics go to the
+// owners' buffers (stats_ptrs[r]: float4 [world][rows_per_rank]). scratch as for axb_lmhead_fwd(T, Vl).
+extern "C" int axb_lmhead_vp_stats(const unsigned long long* h_ptrs, int world, int rank, const void* W_shard,
+                                   const int* labels_local, int rows_per_rank, int Vl, int H, long long ldh,
+                                   long long ldw, float temperature, void* scratch,
+                                   const unsigned long long* stats_ptrs, int* status, void* stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_rank <= 0 || rows_per_rank % GEMM_BM != 0 ||
+      Vl <= 0 || (ldh & 7) || (ldw & 7) || temperature <= 0.f)
+    return AXB_LAUNCH_BAD_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int M = world * rows_per_rank;
+  const int num_n = (Vl + 255) / 256;
+  float* partials = reinterpret_cast<float*>(scratch);
+  float* label_logit = partials + (long long)M * num_n * 3;
+  StatsEpi::Params ep{partials, label_logit, labels_local, num_n, 1.f / temperature};
+  PeerGatherTiles::Params tp;
+  for (int r = 0; r < PeerGatherTiles::MAX_RANKS; ++r) {
+    int rc = make_tmap_2d(&tp.maps[r], reinterpret_cast<const void*>(h_ptrs[r < world ? r : rank]),
+                          CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, H, rows_per_rank, ldh * 2, GEMM_BK, GEMM_BM, true);
+    if (rc) return rc;
+  }
+  tp.world = world;
+  tp.rank = rank;
+  tp.blocks_per_rank = rows_per_rank / GEMM_BM;
+  int rc = launch_head<StatsEpi, PeerGatherTiles>(reinterpret_cast<const void*>(h_ptrs[rank]), W_shard, M, Vl, H, ldh, ldw,
+                                                  ep, status, s, tp);
+  if (rc) return rc;
+  PeerStats st;
+  for (int r = 0; r < 8; ++r) st.p[r] = reinterpret_cast<float4*>(stats_ptrs[r < world ? r : rank]);
+  lmhead_reduce_to_peers_kernel<<<(M + 7) / 8, 256, 0, s>>>(partials, label_logit, labels_local, st, rank,
+                                                           rows_per_rank, M, num_n);
+  return check_launch();
+}
+
+// Part 2, after a device barrier: stats = this rank's buffer; labels = GLOBAL labels of the local rows.
+extern "C" int axb_lmhead_vp_finish(const void* stats, const int* labels, float* logprob, float* entropy, float* lse,
+                                    int world, int rows, void* stream) {
+  if (world < 1 || rows <= 0) return AXB_LAUNCH_BAD_ARG;
+  lmhead_vp_finish_kernel<<<(rows + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const float4*>(stats), labels, logprob, entropy, lse, world, rows);
+  return check_launch();
 }

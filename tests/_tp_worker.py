@@ -39,7 +39,8 @@ def main(out_path: str, device_kind: str) -> None:
     lp_f, ent_f = full.forward(pb, 1.0, save_for_backward=True)
     full.backward(glp, gent)
     tp = TPContext(dist.group.WORLD, dev, max_rows_per_rank=T // world, max_width=max(cfg.qkv_size, 2 * cfg.intermediate_size, cfg.hidden_size))
-    m = TPDenseModel(cfg, tp, device=dev, dtype=dtype)
+    vp = len(sys.argv) > 3 and sys.argv[3] == "vp"
+    m = TPDenseModel(cfg, tp, device=dev, dtype=dtype, vocab_parallel_head=vp)
     m.load_full_state(full.params.views)
     m.params.alloc_grads()
     lp, ent = m.forward(pb, 1.0, save_for_backward=True)
@@ -54,7 +55,7 @@ def main(out_path: str, device_kind: str) -> None:
     res = {"fused": tp.fused, "lp_err": float((lp.float() - lp_f[sl].float()).abs().max()),
            "ent_err": float((ent.float() - ent_f[sl].float()).abs().max()), "grad_rel": {}}
     for name, gsh in m.params.grads.items():
-        ref = slice_full_param(cfg, name, full.params.grads[name], world, rank).float()
+        ref = slice_full_param(cfg, name, full.params.grads[name], world, rank, m.shard_head).float()
         res["grad_rel"][name] = float((gsh.float() - ref).norm() / (ref.norm() + 1e-12))
     ss = m.grad_sumsq().reshape(1).to(dev)
     dist.all_reduce(ss)

@@ -13,18 +13,19 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(tmp_path, n, kind, port):
+def _run(tmp_path, n, kind, port, head="rep"):
     out = tmp_path / "tp.json"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_worker.py"), str(out), kind]
+           "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_worker.py"), str(out), kind, head]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.loads(out.read_text())
 
 
 @pytest.mark.timeout(600)
-def test_tp2_matches_unsharded_model_cpu(tmp_path):
-    res = _run(tmp_path, 2, "cpu", 29641)
+@pytest.mark.parametrize("head", ["rep", "vp"])
+def test_tp2_matches_unsharded_model_cpu(tmp_path, head):
+    res = _run(tmp_path, 2, "cpu", 29641, head)
     for x in res:
         assert not x["fused"] and x["lp_err"] < 1e-4 and x["ent_err"] < 1e-4 and x["norm_rel"] < 1e-5, x
         assert max(x["grad_rel"].values()) < 1e-4, sorted(x["grad_rel"].items(), key=lambda kv: -kv[1])[:3]
@@ -32,8 +33,9 @@ def test_tp2_matches_unsharded_model_cpu(tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_tp2_fused_kernels_match_unsharded_model_gpu(tmp_path):
-    res = _run(tmp_path, 2, "cuda", 29642)
+@pytest.mark.parametrize("head", ["rep", "vp"])
+def test_tp2_fused_kernels_match_unsharded_model_gpu(tmp_path, head):
+    res = _run(tmp_path, 2, "cuda", 29642, head)
     for x in res:
         assert x["fused"] and x["lp_err"] < 0.2 and x["ent_err"] < 0.15 and x["norm_rel"] < 0.05, x
         worst = sorted(x["grad_rel"].items(), key=lambda kv: -kv[1])[:3]
