@@ -31,11 +31,34 @@ from .dense import DenseModel, PackedBatch
 
 
 class MoEModel(DenseModel):
-    def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params=None):
+    def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params=None, ep=None):
+        """``ep``: an ``EPContext`` — every rank then holds only its E/W experts (``w13`` / ``w2`` have a
+        leading dimension of E/W) and tokens reach their experts through peer memory."""
         assert cfg.num_experts > 0 and cfg.num_experts_per_tok > 0, "MoEModel needs num_experts / num_experts_per_tok"
+        self.ep = ep if (ep is not None and ep.world > 1) else None
+        if self.ep is not None and params is None:
+            from .params import FlatParams, param_layout
+            lay = param_layout(cfg)
+            for n, shp in list(lay.items()):
+                if n.endswith("w13_weight") or n.endswith("w2_weight"):
+                    lay[n] = (shp[0] // self.ep.world, *shp[1:])
+            params = FlatParams(cfg, torch.device(device), dtype, layout=lay)
         super().__init__(cfg, device, dtype, params)
         self.last_routing: list | None = None       # per layer ids of the latest sampler forward (routed-experts capture)
         self.capture_routing = False
+
+    def load_full_state(self, full_views: dict) -> None:
+        """Copy from an unsharded model's views, keeping only this rank's experts."""
+        for name, dst in self.params.views.items():
+            src = full_views[name]
+            if self.ep is not None and (name.endswith("w13_weight") or name.endswith("w2_weight")):
+                src = src[self.ep.local_experts()]
+            dst.copy_(src.to(dst.device).to(dst.dtype))
+
+    def replicated_names(self) -> list[str]:
+        """Parameters every expert-parallel rank holds in full (everything but the experts): their
+        gradients are partial per rank (local tokens) and are summed over the group before the step."""
+        return [n for n in self.params.layout if not (n.endswith("w13_weight") or n.endswith("w2_weight"))]
 
     # ------------------------------------------------------------------ routing
     def _route(self, l: int, h2, replay):
@@ -46,12 +69,22 @@ class MoEModel(DenseModel):
 
     def _experts(self, l: int, h2, ids, w, keep_gu: bool):
         c = self.cfg
+        if self.ep is not None:
+            lay = self.ep.align(ids)
+            xs = self.ep.dispatch(h2, lay)
+            gu = M.grouped_fwd(xs, self._p(l, "mlp.experts.w13_weight"), lay.owner)
+            a = A.swiglu_fwd(gu)
+            ys = M.grouped_fwd(a, self._p(l, "mlp.experts.w2_weight"), lay.owner)
+            return lay, xs, gu, a, ys
         lay = M.align(ids, c.num_experts)
         xs = M.gather(h2, lay)
         gu = M.grouped_fwd(xs, self._p(l, "mlp.experts.w13_weight"), lay)
         a = A.swiglu_fwd(gu)
         ys = M.grouped_fwd(a, self._p(l, "mlp.experts.w2_weight"), lay)
         return lay, xs, gu, a, ys
+
+    def _combine(self, ys, w, lay):
+        return self.ep.combine(ys, w, lay) if self.ep is not None else M.combine(ys, w, lay)
 
     def _replay_for(self, l: int, batch):
         rm = getattr(batch, "routermap", None) if batch is not None else None
@@ -63,13 +96,13 @@ class MoEModel(DenseModel):
     def mlp_fwd(self, l: int, h2, batch: PackedBatch, want=()):
         logits, ids, w = self._route(l, h2, self._replay_for(l, batch))
         lay, xs, gu, a, ys = self._experts(l, h2, ids, w, "gu" in want)
-        out = M.combine(ys, w, lay)
+        out = self._combine(ys, w, lay)
         if self.capture_routing:
             if self.last_routing is None:
                 self.last_routing = []
             self.last_routing.append(ids)
         saved = {"moe_ids": ids} if want else {}
-        if "gu" in want:
+        if "gu" in want and self.ep is None:       # with expert parallelism the buffers are shared workspaces: recompute
             saved.update(moe_gu=gu, moe_lay=lay, moe_xs=xs)
         return out, saved
 
@@ -85,27 +118,32 @@ class MoEModel(DenseModel):
         k["moe_w"] = M.route_weights_from_probs(logits, ids, c.norm_topk_prob)
         if "moe_gu" in k:
             lay, xs, gu = k["moe_lay"], k["moe_xs"], k["moe_gu"]
+            a = A.swiglu_fwd(gu)
+            ys = M.grouped_fwd(a, self._p(l, "mlp.experts.w2_weight"), lay)
         else:
-            lay = M.align(ids, c.num_experts)
-            xs = M.gather(h2, lay)
-            gu = M.grouped_fwd(xs, self._p(l, "mlp.experts.w13_weight"), lay)
-        a = A.swiglu_fwd(gu)
-        ys = M.grouped_fwd(a, self._p(l, "mlp.experts.w2_weight"), lay)
+            lay, xs, gu, a, ys = self._experts(l, h2, ids, None, False)
+            if self.ep is not None:
+                xs = xs.clone()            # the dispatch buffer is reused before the weight gradient needs it
         k.update(moe_lay=lay, moe_xs=xs, moe_gu=gu, moe_a=a, moe_ys=ys)
 
     def mlp_bwd(self, l: int, k: dict, dx_out):
         c = self.cfg
         lay, xs, gu, a, ys = k["moe_lay"], k["moe_xs"], k["moe_gu"], k["moe_a"], k["moe_ys"]
         w = k["moe_w"]
-        dys, dw = M.combine_bwd(dx_out, ys, w.detach(), lay)
-        M.grouped_wgrad(dys, a, self._g(l, "mlp.experts.w2_weight"), lay, accumulate=True)
-        da = M.grouped_dgrad(dys, self._p(l, "mlp.experts.w2_weight"), lay)
+        if self.ep is not None:
+            dys, dw = self.ep.combine_bwd(dx_out, ys, w.detach(), lay)
+            glay = lay.owner
+        else:
+            dys, dw = M.combine_bwd(dx_out, ys, w.detach(), lay)
+            glay = lay
+        M.grouped_wgrad(dys, a, self._g(l, "mlp.experts.w2_weight"), glay, accumulate=True)
+        da = M.grouped_dgrad(dys, self._p(l, "mlp.experts.w2_weight"), glay)
         dgu = A.swiglu_bwd(da, gu)
         del da, dys
-        M.grouped_wgrad(dgu, xs, self._g(l, "mlp.experts.w13_weight"), lay, accumulate=True)
-        dxs = M.grouped_dgrad(dgu, self._p(l, "mlp.experts.w13_weight"), lay)
+        M.grouped_wgrad(dgu, xs, self._g(l, "mlp.experts.w13_weight"), glay, accumulate=True)
+        dxs = M.grouped_dgrad(dgu, self._p(l, "mlp.experts.w13_weight"), glay)
         del dgu
-        dh2 = M.scatter_sum(dxs, lay)
+        dh2 = self.ep.collect(dxs, lay) if self.ep is not None else M.scatter_sum(dxs, lay)
         # router: d logits from d weights (softmax over all experts, renormalised over the chosen k)
         logits = k["moe_logits"].detach().requires_grad_(True)
         with torch.enable_grad():

@@ -192,7 +192,7 @@ class VocabParallelHead:
             lse, ent = ctx["lse"], ctx["ent"]
             zlog = (h_full.float() @ w.float().t()) / temp
             p = torch.exp(zlog - lse[:, None])
-            glp = torch.where(lab_loc != -1, g_lp_full, torch.zeros_like(g_lp_full))
+            glp = torch.where((lab_loc >= 0) | (lab_loc == -2), g_lp_full, torch.zeros_like(g_lp_full))
             d = -glp[:, None] * p - g_ent_full[:, None] * p * (zlog - lse[:, None] + ent[:, None])
             own = torch.nonzero(lab_loc >= 0).flatten()
             d[own, lab_loc[own].long()] += glp[own]

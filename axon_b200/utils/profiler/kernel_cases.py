@@ -124,9 +124,64 @@ def case_adamw(small):
     return (lambda: O.adamw_step(master, p, g, m, v, 1e-5, 0.9, 0.95, 1e-8, 0.1, 3)), dict(flops=0.0, bytes=n * (4 * 7 + 2.0), shape=[n])
 
 
+def case_gemm_ag(small):
+    """All-gather -> GEMM kernel with both "ranks" on this GPU (two local shards stand in for the peers):
+    same kernel, same TMA traffic pattern, no NVLink."""
+    import ctypes
+    from ...ops import _common as C
+    rows, N, K, W = (1024, 6144, 4096, 2) if small else (4096, 6144, 4096, 2)
+    shards = [bf(rows, K) for _ in range(W)]
+    w = bf(N, K)
+    out = torch.empty(W * rows, N, device="cuda", dtype=torch.bfloat16)
+    ptrs = (ctypes.c_ulonglong * W)(*[t.data_ptr() for t in shards])
+    lib = C.lib()
+
+    def run():
+        rc = lib.axb_gemm_allgather_a(ptrs, W, 0, C.ptr(w), C.ptr(out), rows, N, K, ctypes.c_longlong(K), ctypes.c_longlong(K),
+                                      ctypes.c_longlong(N), 0, 0, C.ptr(C.status(w.device)), C.stream())
+        C.launched(rc, "gemm_allgather_a")
+    T = W * rows
+    return run, dict(flops=2.0 * T * N * K, bytes=2.0 * (T * K + N * K + T * N), shape=[T, N, K])
+
+
+def case_gemm_rs(small):
+    """GEMM -> reduce-scatter (scatter part) with both staging areas on this GPU."""
+    import ctypes
+    from ...ops import _common as C
+    T, N, K, W = (2048, 4096, 2048, 2) if small else (8192, 4096, 2048, 2)
+    x, w = bf(T, K), bf(N, K)
+    stage = [torch.empty(W * (T // W) * N, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    ptrs = (ctypes.c_ulonglong * W)(*[t.data_ptr() for t in stage])
+    out = torch.empty(T // W, N, device="cuda", dtype=torch.bfloat16)
+    lib = C.lib()
+
+    def run():
+        rc = lib.axb_gemm_scatter(C.ptr(x), C.ptr(w), ptrs, W, 0, T, N, K, ctypes.c_longlong(K), ctypes.c_longlong(K),
+                                  ctypes.c_longlong(N), 0, C.ptr(C.status(w.device)), C.stream())
+        C.launched(rc, "gemm_scatter")
+        rc = lib.axb_rs_reduce(C.ptr(stage[0]), None, C.ptr(out), W, ctypes.c_longlong(T // W), N, ctypes.c_longlong(N),
+                               ctypes.c_longlong(N), C.stream())
+        C.launched(rc, "rs_reduce")
+    return run, dict(flops=2.0 * T * N * K, bytes=2.0 * (T * K + N * K + T * N), shape=[T, N, K])
+
+
+def case_moe_grouped(small):
+    from ...ops import moe as M
+    T, E, k, H, F = (2048, 128, 8, 2048, 768) if small else (8192, 128, 8, 2048, 768)
+    logits = torch.randn(T, E, device="cuda")
+    x = bf(T, H)
+    w13 = bf(E, 2 * F, H, scale=0.05)
+    ids, w = M.route(logits, k)
+    lay = M.align(ids, E)
+    xs = M.gather(x, lay)
+    return (lambda: M.grouped_fwd(xs, w13, lay)), dict(flops=2.0 * T * k * 2 * F * H, bytes=2.0 * (T * k * H + E * 2 * F * H + T * k * 2 * F),
+                                                     shape=[T * k, 2 * F, H, E])
+
+
 CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode,
          "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode,
-         "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw}
+         "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "gemm_ag": case_gemm_ag,
+         "gemm_rs": case_gemm_rs, "moe_grouped": case_moe_grouped}
 
 
 def main() -> None:

@@ -127,7 +127,9 @@ struct DLogitsEpi {
     label = v ? p.labels[row] : -1;
     lse = v ? p.lse[row] : 0.f;
     ent = v ? p.entropy[row] : 0.f;
-    glp = (v && p.g_logprob && label != -1) ? p.g_logprob[row] : 0.f;   // -1: ignored token; <= -2: label in another shard
+    // label < 0: ignored token (no gradient) — except -2, which marks a valid token whose label lives in
+    // another rank's vocabulary shard: it keeps the -g*p term and only drops the one-hot
+    glp = (v && p.g_logprob && (label >= 0 || label == -2)) ? p.g_logprob[row] : 0.f;
     gent = (v && p.g_entropy) ? p.g_entropy[row] : 0.f;
   }
   __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {

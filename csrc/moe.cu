@@ -328,3 +328,212 @@ extern "C" int axb_moe_scatter_sum(const void* dxs, const int* row_of, void* dx,
                                                                              (__nv_bfloat16*)dx, T, k, H, accumulate);
   return check_launch();
 }
+
+// ------------------------------------------------------------------ expert parallelism over peer memory
+// W ranks, each with its own tokens and E/W of the experts. Tokens travel to the rank that owns their
+// expert and back through NVLink peer memory, written and read directly by these kernels — there is no
+// all-to-all collective and no staging copy:
+//   layout     from the W x E matrix of per-rank expert counts (every rank's row sits in its symmetric
+//              buffer) each rank derives, identically, where its assignments land on the owners
+//              (expert-major, then source rank, then token order; 128-row padded per expert) and, for
+//              the experts it owns, the row offsets / tile map of its grouped GEMMs.
+//   dispatch   xs_owner[row] = x[token]                     (peer store)
+//   combine    out[token] = sum_j w_j * ys_owner(j)[row_j]   (peer load)
+//   combine_bwd  dys_owner[row] = w * dout[token] (peer store); dw = <dout[token], ys_owner[row]> (peer load)
+//   collect    dx[token] = sum_j dxs_owner(j)[row_j]         (peer load)
+namespace axb {
+
+struct EpPeers {
+  void* p[8];
+};
+
+// One block. counts[s] = rank s's int32 [E] (peer pointers). Outputs (all local):
+//   my_base[e]      first row, on the owner of e, of THIS rank's assignments to e
+//   offsets[le]     row offsets of the local experts (le = 0..E/W), offsets[E/W] = rows in use
+//   tile_expert[m]  local expert of 128-row tile m (-1 past the end)
+__global__ void moe_ep_layout_kernel(EpPeers counts, int world, int rank, int E, int* __restrict__ my_base,
+                                     int* __restrict__ offsets, int* __restrict__ tile_expert, int max_tiles) {
+  const int epr = E / world;
+  __shared__ int exp_rows[MOE_MAX_EXPERTS];     // padded rows of every expert
+  __shared__ int before_me[MOE_MAX_EXPERTS];    // rows of lower-ranked sources inside the expert
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, pre = 0;
+    for (int s = 0; s < world; ++s) {
+      const int c = reinterpret_cast<const volatile int*>(counts.p[s])[e];
+      if (s < rank) pre += c;
+      tot += c;
+    }
+    exp_rows[e] = (tot + MOE_PAD - 1) / MOE_PAD * MOE_PAD;
+    before_me[e] = pre;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int o = 0; o < world; ++o) {          // owner o: its experts are laid out from row 0
+      int off = 0;
+      for (int le = 0; le < epr; ++le) {
+        const int e = o * epr + le;
+        my_base[e] = off + before_me[e];
+        if (o == rank) {
+          offsets[le] = off;
+          for (int m = off / MOE_PAD; m < (off + exp_rows[e]) / MOE_PAD && m < max_tiles; ++m) tile_expert[m] = le;
+        }
+        off += exp_rows[e];
+      }
+      if (o == rank) {
+        offsets[epr] = off;
+        for (int m = off / MOE_PAD; m < max_tiles; ++m) tile_expert[m] = -1;
+      }
+    }
+  }
+}
+
+// One warp per assignment i = t*k + j.
+__global__ void moe_ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
+                                       const int* __restrict__ row_of, EpPeers xs, long long n, int k, int H, int epr) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= n) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (i / k) * H);
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(xs.p[ids[i] / epr]) +
+                                        static_cast<long long>(row_of[i]) * H);
+  for (int c = lane; c < H / 8; c += 32) dst[c] = src[c];
+}
+
+__global__ void moe_ep_combine_kernel(EpPeers ys, const int* __restrict__ ids, const int* __restrict__ row_of,
+                                      const float* __restrict__ w, __nv_bfloat16* __restrict__ out, long long T, int k,
+                                      int H, int epr) {
+  const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  for (int c = lane; c < H / 8; c += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const long long i = t * k + j;
+      const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(ys.p[ids[i] / epr]);
+      float v[8];
+      unpack8f(reinterpret_cast<const uint4*>(base + static_cast<long long>(row_of[i]) * H)[c], v);
+      const float wj = w[i];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] += wj * v[q];
+    }
+    reinterpret_cast<uint4*>(out + t * H)[c] = pack8f(acc);
+  }
+}
+
+__global__ void moe_ep_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, EpPeers ys, EpPeers dys,
+                                          const int* __restrict__ ids, const int* __restrict__ row_of,
+                                          const float* __restrict__ w, float* __restrict__ dw, long long n, int k, int H,
+                                          int epr) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= n) return;
+  const int o = ids[i] / epr;
+  const long long r = row_of[i];
+  const __nv_bfloat16* y = reinterpret_cast<const __nv_bfloat16*>(ys.p[o]) + r * H;
+  __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(dys.p[o]) + r * H;
+  const float wj = w[i];
+  float dot = 0.f;
+  for (int c = lane; c < H / 8; c += 32) {
+    float g[8], yv[8], ov[8];
+    unpack8f(reinterpret_cast<const uint4*>(dout + (i / k) * H)[c], g);
+    unpack8f(reinterpret_cast<const uint4*>(y)[c], yv);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      dot += g[q] * yv[q];
+      ov[q] = wj * g[q];
+    }
+    reinterpret_cast<uint4*>(d)[c] = pack8f(ov);
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) dw[i] = dot;
+}
+
+__global__ void moe_ep_collect_kernel(EpPeers dxs, const int* __restrict__ ids, const int* __restrict__ row_of,
+                                      __nv_bfloat16* __restrict__ dx, long long T, int k, int H, int epr) {
+  const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  for (int c = lane; c < H / 8; c += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const long long i = t * k + j;
+      const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(dxs.p[ids[i] / epr]);
+      float v[8];
+      unpack8f(reinterpret_cast<const uint4*>(base + static_cast<long long>(row_of[i]) * H)[c], v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] += v[q];
+    }
+    reinterpret_cast<uint4*>(dx + t * H)[c] = pack8f(acc);
+  }
+}
+
+static int fill_peers(EpPeers& out, const unsigned long long* ptrs, int world) {
+  if (world < 1 || world > 8) return AXB_LAUNCH_BAD_ARG;
+  for (int i = 0; i < 8; ++i) out.p[i] = reinterpret_cast<void*>(ptrs[i < world ? i : 0]);
+  return AXB_LAUNCH_OK;
+}
+
+}  // namespace axb
+
+// Step 1 (before the barrier): counts of this rank's assignments per expert into its symmetric slot.
+extern "C" int axb_moe_ep_count(const int* ids, long long T, int k, int E, int* counts, void* stream) {
+  if (T <= 0 || E <= 0 || E > MOE_MAX_EXPERTS) return AXB_LAUNCH_BAD_ARG;
+  moe_count_kernel<<<E, 256, 0, (cudaStream_t)stream>>>(ids, T * k, counts);
+  return check_launch();
+}
+
+// Step 2 (after the barrier): layout from all ranks' counts, then this rank's destination rows.
+// scratch_token_of: int32 [>= max rows any owner can hold] (written, not used by the caller).
+extern "C" int axb_moe_ep_layout(const unsigned long long* count_ptrs, int world, int rank, const int* ids, long long T,
+                                 int k, int E, int* my_base, int* offsets, int* tile_expert, int max_tiles, int* row_of,
+                                 int* scratch_token_of, void* stream) {
+  EpPeers c;
+  if (int rc = fill_peers(c, count_ptrs, world)) return rc;
+  if (E % world != 0 || E > MOE_MAX_EXPERTS || T <= 0) return AXB_LAUNCH_BAD_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  moe_ep_layout_kernel<<<1, 256, 0, s>>>(c, world, rank, E, my_base, offsets, tile_expert, max_tiles);
+  moe_positions_kernel<<<E, 256, 0, s>>>(ids, T * k, k, my_base, row_of, scratch_token_of);
+  return check_launch();
+}
+
+extern "C" int axb_moe_ep_dispatch(const void* x, const int* ids, const int* row_of, const unsigned long long* xs_ptrs,
+                                   int world, long long T, int k, int H, int E, void* stream) {
+  EpPeers p;
+  if (int rc = fill_peers(p, xs_ptrs, world)) return rc;
+  if (H % 8 != 0 || T <= 0) return AXB_LAUNCH_BAD_ARG;
+  moe_ep_dispatch_kernel<<<warp_grid(T * k, 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ids, row_of, p,
+                                                                                 T * k, k, H, E / world);
+  return check_launch();
+}
+
+extern "C" int axb_moe_ep_combine(const unsigned long long* ys_ptrs, int world, const int* ids, const int* row_of,
+                                  const float* w, void* out, long long T, int k, int H, int E, void* stream) {
+  EpPeers p;
+  if (int rc = fill_peers(p, ys_ptrs, world)) return rc;
+  if (H % 8 != 0 || T <= 0) return AXB_LAUNCH_BAD_ARG;
+  moe_ep_combine_kernel<<<warp_grid(T, 256), 256, 0, (cudaStream_t)stream>>>(p, ids, row_of, w, (__nv_bfloat16*)out, T, k, H,
+                                                                            E / world);
+  return check_launch();
+}
+
+extern "C" int axb_moe_ep_combine_bwd(const void* dout, const unsigned long long* ys_ptrs,
+                                      const unsigned long long* dys_ptrs, int world, const int* ids, const int* row_of,
+                                      const float* w, float* dw, long long T, int k, int H, int E, void* stream) {
+  EpPeers y, d;
+  if (int rc = fill_peers(y, ys_ptrs, world)) return rc;
+  if (int rc = fill_peers(d, dys_ptrs, world)) return rc;
+  if (H % 8 != 0 || T <= 0) return AXB_LAUNCH_BAD_ARG;
+  moe_ep_combine_bwd_kernel<<<warp_grid(T * k, 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dout, y, d, ids,
+                                                                                    row_of, w, dw, T * k, k, H, E / world);
+  return check_launch();
+}
+
+extern "C" int axb_moe_ep_collect(const unsigned long long* dxs_ptrs, int world, const int* ids, const int* row_of,
+                                  void* dx, long long T, int k, int H, int E, void* stream) {
+  EpPeers p;
+  if (int rc = fill_peers(p, dxs_ptrs, world)) return rc;
+  if (H % 8 != 0 || T <= 0) return AXB_LAUNCH_BAD_ARG;
+  moe_ep_collect_kernel<<<warp_grid(T, 256), 256, 0, (cudaStream_t)stream>>>(p, ids, row_of, (__nv_bfloat16*)dx, T, k, H,
+                                                                            E / world);
+  return check_launch();
+}
