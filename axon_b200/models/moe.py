@@ -60,6 +60,29 @@ class MoEModel(DenseModel):
         gradients are partial per rank (local tokens) and are summed over the group before the step."""
         return [n for n in self.params.layout if not (n.endswith("w13_weight") or n.endswith("w2_weight"))]
 
+    def replicated_ranges(self) -> list[tuple[int, int]]:
+        """Contiguous [a, b) ranges of the flat buffers that hold replicated parameters (merged)."""
+        if self.ep is None:
+            return []
+        keep = set(self.replicated_names())
+        spans = sorted((o, o + n) for name, (o, n) in self.params.offsets.items() if name in keep)
+        out: list[list[int]] = []
+        for a, b in spans:
+            if out and out[-1][1] == a:
+                out[-1][1] = b
+            else:
+                out.append([a, b])
+        return [(a, b) for a, b in out]
+
+    def sync_replicated_grads(self) -> None:
+        """Sum the gradients of the replicated parameters over the expert-parallel group (each rank saw
+        only its own tokens); expert gradients are already complete for the group, since every token
+        routed to an expert was computed on the expert's owner."""
+        if self.ep is None or self.params.grad_flat is None:
+            return
+        for a, b in self.replicated_ranges():
+            self.ep.all_reduce_(self.params.grad_flat[a:b])
+
     # ------------------------------------------------------------------ routing
     def _route(self, l: int, h2, replay):
         c = self.cfg

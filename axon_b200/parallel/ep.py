@@ -64,6 +64,11 @@ class EPContext:
             dist.all_reduce(self._sync, group=self.group)     # line the streams up (bounded device wait follows)
             self.barrier()
 
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
     def local_experts(self) -> slice:
         return slice(self.rank * self.epr, (self.rank + 1) * self.epr)
 

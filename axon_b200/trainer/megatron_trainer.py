@@ -6,8 +6,16 @@ and data-parallel groups strided across them, as ``mpu.initialize_model_parallel
 Tensor parallelism uses sequence-parallel activations with the fused all-gather->GEMM and
 GEMM->reduce-scatter kernels (``parallel/tp.py``); the optimizer is the sharded (distributed)
 AdamW of the policy engine over the data-parallel group. Data is dispatched per data-parallel rank
-and collected from tensor-parallel rank 0. Pipeline, context and expert parallel sizes other than 1
-are refused with an explicit error until their schedules land here.
+and collected from tensor-parallel rank 0.
+
+Expert parallelism (``expert_model_parallel_size``, with tp = 1): ``world = edp x ep``; expert-parallel
+groups are consecutive ranks, every rank is a data-parallel rank of its own (different rows), tokens
+reach their experts through peer memory (``parallel/ep.py``). Non-expert gradients are summed over the
+expert-parallel group and then reduced with the expert gradients over the strided "expert data
+parallel" group, which is also the group the optimizer state is sharded over.
+
+Pipeline and context parallel sizes other than 1, and tensor x expert parallelism together, are
+refused with an explicit error until their schedules land here.
 """
 from __future__ import annotations
 
@@ -21,8 +29,11 @@ class TrainerWorker(_Base):
     def __init__(self, config, model=None, name: str = "trainer", **kwargs):
         m = _get(config, "megatron", {}) or {}
         self.tp_size = int(_get(m, "tensor_model_parallel_size", 1) or 1)
-        for key, label in (("pipeline_model_parallel_size", "pipeline"), ("context_parallel_size", "context"),
-                           ("expert_model_parallel_size", "expert")):
+        self.ep_size = int(_get(m, "expert_model_parallel_size", 1) or 1)
+        if self.ep_size > 1 and self.tp_size > 1:
+            raise NotImplementedError("tensor and expert parallelism together are not available in this trainer yet; "
+                                      "use one of megatron.tensor_model_parallel_size / expert_model_parallel_size")
+        for key, label in (("pipeline_model_parallel_size", "pipeline"), ("context_parallel_size", "context")):
             if int(_get(m, key, 1) or 1) != 1:
                 raise NotImplementedError(f"{label} parallelism > 1 is not available in this trainer yet "
                                           f"(megatron.{key}={_get(m, key)}); use tensor and data parallelism")
@@ -37,9 +48,10 @@ class TrainerWorker(_Base):
             return super()._register_dispatch_collect_info(mesh_name, self.rank // self.tp_size, self.rank % self.tp_size == 0)
         return super()._register_dispatch_collect_info(mesh_name, dp_rank, is_collect)
 
-    def _make_groups(self):
-        """(tp group, dp group) of this rank; every rank creates every group (collective contract)."""
-        tp, world = self.tp_size, self.world_size
+    def _make_groups(self, tp: int | None = None):
+        """(model-parallel group of ``tp`` consecutive ranks, strided data-parallel group) of this rank;
+        every rank creates every group (collective contract)."""
+        tp, world = tp or self.tp_size, self.world_size
         tp_group = dp_group = None
         if world == 1:
             return None, None
@@ -55,7 +67,34 @@ class TrainerWorker(_Base):
                 dp_group = g
         return tp_group, dp_group
 
+    def _build_expert_parallel(self, model_path, dtype, seed):
+        import os
+        from ..models.config import get_config
+        from ..models.moe import MoEModel
+        from ..parallel.ep import EPContext
+        from ..utils.hf_model import has_hf_weights, iter_hf_weights
+        mcfg = get_config(model_path)
+        assert mcfg.num_experts > 0, f"expert_model_parallel_size={self.ep_size} needs a mixture-of-experts model"
+        assert self.world_size % self.ep_size == 0, f"world size {self.world_size} not divisible by ep {self.ep_size}"
+        ep_group, edp_group = self._make_groups(self.ep_size)
+        self.pg = edp_group
+        cap = int(_get(self.config, "max_token_len_per_gpu", 16384))
+        ctx = EPContext(ep_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size,
+                        max_tokens=(cap + 127) // 128 * 128, top_k=mcfg.num_experts_per_tok)
+        model = MoEModel(mcfg, device=self.device, dtype=dtype, ep=ctx)
+        from ..models.params import FlatParams
+        ref = FlatParams(mcfg, "cpu", dtype)                 # full model on the host, cut down to this rank's experts
+        if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+        else:
+            ref.init_random(seed=seed)
+        model.load_full_state(ref.views)
+        model.recompute = str(_get(self.config, "recompute", "selective"))
+        return model
+
     def _build(self, model_path, dtype, seed):
+        if self.ep_size > 1:
+            return self._build_expert_parallel(model_path, dtype, seed)
         if self.tp_size == 1:
             return super()._build(model_path, dtype, seed)
         if self.model_kind.value_head:

@@ -111,8 +111,13 @@ class PolicyEngine:
         self.state = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._host_state: dict | None = None
         self.fused = None
+        mp = getattr(model, "tp", None) or getattr(model, "ep", None)
+        ep = getattr(model, "ep", None)
+        self.micro_group = ep.group if (ep is not None and ep.world > 1) else None      # ranks that must run equal micro-batch counts
         if fused_zero1 is None:
-            fused_zero1 = self.world > 1 and self.device.type == "cuda" and n % (self.world * 128) == 0 and \
+            # the fused step computes the clipping norm over the data-parallel group only; a model-parallel
+            # group adds terms to the norm, so those runs take the NCCL path with the corrected norm
+            fused_zero1 = (mp is None or mp.world == 1) and self.world > 1 and self.device.type == "cuda" and n % (self.world * 128) == 0 and \
                 dist.get_backend(process_group) == "nccl"
         if fused_zero1:
             self._enable_fused_zero1()
@@ -176,7 +181,7 @@ class PolicyEngine:
     def forward(self, data: DataProto, temperature: float | None = None, want_entropy: bool = True) -> DataProto:
         """Returns a DataProto with ``log_probs`` (and ``entropy``) [B,T] for the rows of ``data``."""
         temp = temperature if temperature is not None else data.meta_info.get("temperature", self.temperature)
-        mbs, idx = prepare_dynamic_batch(data, self.max_tokens, dp_group=None)
+        mbs, idx = prepare_dynamic_batch(data, self.max_tokens, dp_group=self.micro_group, strict_equal=self.micro_group is not None)
         lps, ents = [], []
         for mb in mbs:
             pk = _Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device)
@@ -201,7 +206,8 @@ class PolicyEngine:
         ent_coef = float(args.get("entropy_coef", 0.0) or 0.0)
         kl_coef = float(args.get("kl_coef", 0.0) or 0.0)
         self.model.params.alloc_grads()
-        mbs, _ = prepare_dynamic_batch(data, self.max_tokens, dp_group=None)
+        # expert-parallel ranks hold different data but exchange tokens layer by layer: equal micro-batch counts
+        mbs, _ = prepare_dynamic_batch(data, self.max_tokens, dp_group=self.micro_group, strict_equal=self.micro_group is not None)
         metrics: dict[str, list] = {}
         for mb in mbs:
             mb = mb.to(self.device)
@@ -344,10 +350,10 @@ class PolicyEngine:
         return {"grad_norm": st[1], "lr": lr, "skipped": st[3]}
 
     def _tensor_parallel_norm(self, grad_shard: torch.Tensor, lo: int) -> None:
-        """With a tensor-parallel model the squared norm is the sum over the TP ranks of their sharded
+        """With a tensor- or expert-parallel model the squared norm is the sum over the TP ranks of their sharded
         parameters plus the replicated parameters ONCE: sum_r S_r - (W - 1) * rep, where S_r is rank r's
         full-buffer value and rep the replicated part (equal on every rank)."""
-        tp = getattr(self.model, "tp", None)
+        tp = getattr(self.model, "tp", None) or getattr(self.model, "ep", None)     # model-parallel group of either kind
         if tp is None or tp.world == 1:
             return
         rep = torch.zeros(1, dtype=torch.float32, device=self.device)

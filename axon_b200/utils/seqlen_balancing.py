@@ -101,31 +101,44 @@ def _select_rows(batch, idx):
 
 
 def rearrange_micro_batches(batch, max_token_len, dp_group=None, num_batches_divided_by=None,
-                            same_micro_num_in_dp=True, min_num_micro_batch=None, use_dynamic_bsz_balance=True):
+                            same_micro_num_in_dp=True, min_num_micro_batch=None, use_dynamic_bsz_balance=True,
+                            strict_equal=False):
     """Split ``batch`` (needs ``attention_mask`` [B,S]) into micro-batches whose total real tokens never
-    exceed ``max_token_len``. Returns (micro_batches, index_lists)."""
+    exceed ``max_token_len``. Returns (micro_batches, index_lists). With ``dp_group`` the count is raised to
+    the group's maximum (ONE collective per call, so ranks cannot fall out of step); ``strict_equal``
+    additionally refuses a rank that has fewer rows than that count (groups whose ranks exchange
+    activations inside the model need exactly equal counts)."""
     lens = batch["attention_mask"].sum(1).to(torch.long).cpu()
     B = lens.numel()
     assert int(lens.max()) <= max_token_len, f"a sequence of {int(lens.max())} tokens exceeds the cap {max_token_len}"
     total = int(lens.sum())
+    cost = calculate_workload(lens).tolist() if use_dynamic_bsz_balance else lens.tolist()
+
+    def split(n):
+        parts = get_seqlen_balanced_partitions(cost, n, equal_size=False)
+        return parts, max(int(lens[torch.tensor(p)].sum()) for p in parts)
+
     n = max(1, min(B, ceildiv(total, max_token_len)))
     if min_num_micro_batch is not None:
-        n = max(n, min_num_micro_batch)
-    while True:
-        n = min(n, B)
-        if dp_group is not None and same_micro_num_in_dp and torch.distributed.is_initialized():
-            t = torch.tensor([n], device="cuda" if torch.distributed.get_backend(dp_group) == "nccl" else "cpu")
-            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=dp_group)
-            n = int(t.item())
-        if num_batches_divided_by is not None:
-            n = roundup_divisible(n, num_batches_divided_by)
-        n = min(n, B)
-        cost = calculate_workload(lens).tolist() if use_dynamic_bsz_balance else lens.tolist()
-        parts = get_seqlen_balanced_partitions(cost, n, equal_size=False)
-        worst = max(int(lens[torch.tensor(p)].sum()) for p in parts)
-        if worst <= max_token_len or n >= B:
-            break
+        n = min(B, max(n, min_num_micro_batch))
+    if num_batches_divided_by is not None:
+        n = min(B, roundup_divisible(n, num_batches_divided_by))
+    parts, worst = split(n)
+    while worst > max_token_len and n < B:
         n += 1
+        parts, worst = split(n)
+    if dp_group is not None and same_micro_num_in_dp and torch.distributed.is_initialized():
+        t = torch.tensor([n], device="cuda" if torch.distributed.get_backend(dp_group) == "nccl" else "cpu")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=dp_group)
+        n_all = int(t.item())
+        if num_batches_divided_by is not None:
+            n_all = roundup_divisible(n_all, num_batches_divided_by)
+        if strict_equal:
+            assert B >= n_all, (f"this rank holds {B} rows but its group runs {n_all} micro-batches; give every rank at least "
+                                f"as many rows as micro-batches (raise the token cap or the batch size)")
+        if min(n_all, B) != n:
+            n = min(n_all, B)
+            parts, worst = split(n)
     if use_dynamic_bsz_balance:   # heavier micro-batches first
         parts.sort(key=lambda p: -sum(int(lens[i]) ** 2 for i in p))
     return [_select_rows(batch, p) for p in parts], parts
@@ -139,10 +152,11 @@ def get_reverse_idx(idx_map):
 
 
 def prepare_dynamic_batch(data, max_token_len: int, dp_group=None, num_batches_divided_by=None,
-                          same_micro_num_in_dp=True, min_num_micro_batch=None, use_dynamic_bsz_balance=True):
+                          same_micro_num_in_dp=True, min_num_micro_batch=None, use_dynamic_bsz_balance=True,
+                          strict_equal=False):
     """DataProto -> (list of micro DataProtos, index lists) under the token cap."""
     mbs, idx = rearrange_micro_batches(data.batch, max_token_len, dp_group, num_batches_divided_by,
-                                       same_micro_num_in_dp, min_num_micro_batch, use_dynamic_bsz_balance)
+                                       same_micro_num_in_dp, min_num_micro_batch, use_dynamic_bsz_balance, strict_equal)
     out = []
     for p in idx:
         d = data.select_idxs(torch.tensor(p, dtype=torch.long))

@@ -8,15 +8,15 @@ from axon_b200.core.resource_pool import ResourcePool
 from axon_b200.protocol import DataProto
 
 
-def _cfg(tp):
-    return {"model_path": "tiny-qwen3", "force_cpu": True, "seed": 7, "max_token_len_per_gpu": 512,
+def _cfg(tp, model="tiny-qwen3", ep=1):
+    return {"model_path": model, "force_cpu": True, "seed": 7, "max_token_len_per_gpu": 512,
             "optimizer_args": {"lr": 1e-3, "weight_decay": 0.0, "betas": [0.9, 0.95], "eps": 1e-8}, "grad_clip": 1.0,
-            "megatron": {"tensor_model_parallel_size": tp}, "recompute": "full"}
+            "megatron": {"tensor_model_parallel_size": tp, "expert_model_parallel_size": ep}, "recompute": "full"}
 
 
-def _batch(n_rows=4, T=48):
+def _batch(n_rows=4, T=48, vocab=4096):
     g = torch.Generator().manual_seed(3)
-    ids = torch.randint(0, 4096, (n_rows, T), generator=g)
+    ids = torch.randint(0, vocab, (n_rows, T), generator=g)
     att = torch.ones(n_rows, T, dtype=torch.long)
     att[1, 40:] = 0
     rm = att.clone().float()
@@ -28,7 +28,7 @@ def _batch(n_rows=4, T=48):
     return d
 
 
-def _run(cls_path, cfg, world):
+def _run(cls_path, cfg, world, vocab=4096):
     import importlib
     mod, name = cls_path.rsplit(".", 1)
     cls = getattr(importlib.import_module(mod), name)
@@ -36,7 +36,7 @@ def _run(cls_path, cfg, world):
                           rpc_timeout=300)
     try:
         wg.init_model()
-        data = _batch()
+        data = _batch(vocab=vocab)
         fwd = wg.forward(data)
         data.batch["old_log_probs"] = fwd.batch["log_probs"]
         from axon_b200.driver.driver_utils import process_mini_batch
@@ -60,3 +60,17 @@ def test_tensor_parallel_trainer_matches_data_parallel_trainer(world, tp):
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)                 # log-probs after one optimizer step
     assert (got[3] - got[0]).abs().max() > 1e-4                                      # and the step did move the model
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world,ep", [(2, 2), (4, 2)])
+def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
+    """ep=2 (x edp=1 or 2): every rank trains on its own rows, experts are split over the group."""
+    import numpy as np
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-moe"), 1, vocab=2048)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, "tiny-moe", ep), world, vocab=2048)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
