@@ -1,8 +1,9 @@
 """Trainer side of the disaggregated weight push
 (reference: axon/trainer/mixins/p2p_mixin.py:58-703).
 
-``get_parameter_mapping`` describes what this rank holds (every trainer rank holds the full fused
-parameters, so any rank can serve any sampler shard and the routing table spreads the load).
+``get_parameter_mapping`` describes what this rank holds: the full fused parameters on a data-parallel
+trainer (any rank can serve any sampler shard and the routing table spreads the load), this rank's
+slices on a tensor- or expert-parallel one.
 ``send_trainer_to_sampler_weights`` compiles the routing table into a copy plan once (cached across
 steps) and executes it: on CUDA within a node through the sampler's symmetric-memory buffers with
 the fused peer-store kernel (optionally quantising to fp8 blocks on the way), otherwise as one
@@ -48,7 +49,18 @@ class TrainerP2PMixin:
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def get_parameter_mapping(self):
-        return get_param_metadata(self.model.cfg, rank=self.rank, dtype=self.model.params.dtype)
+        # a tensor- or expert-parallel trainer describes its own slices; the routing table then matches
+        # them against the sampler's slices box by box
+        tp, ep = getattr(self.model, "tp", None), getattr(self.model, "ep", None)
+        inner = getattr(self.model, "inner", self.model)
+        rep = ()
+        if tp is not None and tp.world > 1:
+            from ...utils.p2p.param_mapper import split_kind
+            rep = [n for n in inner.replicated_names() if split_kind(n) != "replicated"]
+        return get_param_metadata(self.model.cfg, rank=self.rank, dtype=self.model.params.dtype,
+                                  tp=tp.world if tp is not None else 1, tp_rank=tp.rank if tp is not None else 0,
+                                  ep=ep.world if ep is not None else 1, ep_rank=ep.rank if ep is not None else 0,
+                                  replicated_names=rep)
 
     def _local_offsets(self) -> dict:
         return {n: o for n, (o, _) in self.model.params.offsets.items()}

@@ -62,12 +62,12 @@ def split_kind(name: str) -> str:
     return "replicated"
 
 
-def shard_rows(cfg: ModelConfig, name: str, tp: int, tp_rank: int, ep: int = 1, ep_rank: int = 0):
+def shard_rows(cfg: ModelConfig, name: str, tp: int, tp_rank: int, ep: int = 1, ep_rank: int = 0, replicated_names=()):
     """The slices of the FULL fused parameter that one rank holds, as a list of
     (row_start, row_end, col_start, col_end) boxes in full-parameter coordinates (experts: dim 0 is the
     expert index and boxes cover whole experts)."""
     shape = param_layout(cfg)[name]
-    kind = split_kind(name)
+    kind = "replicated" if name in replicated_names else split_kind(name)
     D = cfg.head_dim
     if kind == "replicated" or (tp == 1 and kind != "expert"):
         return [(0, shape[0], 0, shape[1] if len(shape) > 1 else 1)]
@@ -98,13 +98,16 @@ def shard_rows(cfg: ModelConfig, name: str, tp: int, tp_rank: int, ep: int = 1, 
 
 
 def get_param_metadata(cfg: ModelConfig, rank: int, tp: int = 1, tp_rank: int = 0, ep: int = 1, ep_rank: int = 0,
-                       dtype=torch.bfloat16) -> RankMapping:
+                       dtype=torch.bfloat16, replicated_names=()) -> RankMapping:
     """One rank's ``RankMapping``: a ``ParameterMetadata`` per fused parameter with its shard shape,
-    split dim and split index (tp rank for dense tensors, ep rank for expert tensors)."""
+    split dim and split index (tp rank for dense tensors, ep rank for expert tensors).
+    ``replicated_names``: parameters this rank holds in full although their kind could be split
+    (a tensor-parallel trainer that keeps the embedding and the head whole)."""
     out = []
+    replicated_names = set(replicated_names)
     for name, full in param_layout(cfg).items():
-        kind = split_kind(name)
-        boxes = shard_rows(cfg, name, tp, tp_rank, ep, ep_rank)
+        kind = "replicated" if name in replicated_names else split_kind(name)
+        boxes = shard_rows(cfg, name, tp, tp_rank, ep, ep_rank, replicated_names)
         if kind == "expert":
             shape = (boxes[0][1] - boxes[0][0], *full[1:])
             out.append(ParameterMetadata(name, name, shape, tuple(full), dtype, split_dim=0, split_idx=ep_rank,

@@ -144,3 +144,35 @@ def test_routing_errors_and_name_mapping():
     assert convert_hf_to_vllm_param_name("model.layers.0.mlp.up_proj.weight") == ("model.layers.0.mlp.gate_up_proj.weight", "up")
     assert convert_hf_to_vllm_param_name("model.layers.0.mlp.experts.7.down_proj.weight") == ("model.layers.0.mlp.experts.w2_weight", "w2:7")
     assert convert_hf_to_vllm_param_name("model.norm.weight") == ("model.norm.weight", None)
+
+
+def test_tensor_parallel_trainer_with_whole_embedding_feeds_vocab_split_sampler():
+    """A TP=2 trainer that keeps the embedding and the head whole (as the tensor-parallel model does)
+    pushes to a TP=2 sampler that splits them over the vocabulary: built from the model's own layout."""
+    from axon_b200.models.tp_dense import slice_full_param, tp_param_layout
+    cfg = cfg_dense()
+    full = full_tensors(cfg, 5)
+    rep = [n for n in param_layout(cfg) if n.endswith("embed_tokens.weight") or n.endswith("lm_head.weight")]
+    a_maps, a_flats, a_offs = [], {}, {}
+    for r in range(2):
+        a_maps.append(get_param_metadata(cfg, r, 2, r, replicated_names=rep))
+        lay = tp_param_layout(cfg, 2, r, False)
+        chunks, off, o = [], 0, {}
+        for name in lay:
+            sh = slice_full_param(cfg, name, full[name], 2, r).reshape(-1)
+            assert tuple(slice_full_param(cfg, name, full[name], 2, r).shape) == tuple(lay[name])
+            o[name], off = off, off + sh.numel()
+            chunks.append(sh)
+        a_flats[r], a_offs[r] = torch.cat(chunks), o
+        for pm in a_maps[-1].params:
+            assert tuple(pm.param_shape) == tuple(lay[pm.param_name]), pm.param_name
+    s_maps, s_exp, s_offs = build_side(cfg, full, [(t, 2, t, 1, 0) for t in range(2)])
+    table = RoutingTable(a_maps, s_maps)
+    dst = [torch.full_like(s_exp[r], float("nan")) for r in sorted(s_exp)]
+    for r in range(2):
+        execute_plan(compile_plan(table, r, a_offs[r], s_offs), a_flats[r], dst)
+    for r in range(2):
+        for name in param_layout(cfg):
+            n = local_shard(cfg, full, name, 2, r, 1, 0).numel()
+            o = s_offs[r][name]
+            assert torch.equal(dst[r][o:o + n], s_exp[r][o:o + n]), (r, name)
