@@ -37,8 +37,46 @@ FIXED_CONFIG = False        # batch-invariant mode: one tile width, no K split, 
 USE_CLUSTER_DECODE = True   # cluster split-K kernel (partials reduced through distributed shared memory)
 
 
+USE_STREAM_DECODE = True    # weight-streaming kernel (run-time token width, last-arriver split-K reduction)
+_STREAM_PLANS: dict = {}
+_STREAM_COUNTERS: dict = {}
+_STREAM_TUNE_VERSION = 0
+
+
+def stream_tune(force_splits=0, max_bn=0, smem_budget_kb=0, reduce_kb=0, min_kblocks=0, target_ctas=0) -> None:
+    """Experiment hook: change the planning knobs of the weight-streaming kernel (0 keeps a knob)."""
+    global _STREAM_TUNE_VERSION
+    C.lib().axb_gemm_stream_tune(int(force_splits), int(max_bn), int(smem_budget_kb), int(reduce_kb), int(min_kblocks), int(target_ctas))
+    _STREAM_TUNE_VERSION += 1
+
+
+def _native_gemm_stream(x, w, out, M, N, K):
+    lib = C.lib()
+    key = (M, N, K, _STREAM_TUNE_VERSION)
+    plan = _STREAM_PLANS.get(key)
+    if plan is None:
+        wsf, nc, sp, bn = ctypes.c_longlong(0), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+        rc = lib.axb_gemm_stream_workspace(M, N, K, ctypes.byref(wsf), ctypes.byref(nc), ctypes.byref(sp), ctypes.byref(bn))
+        C.launched(rc, "gemm_stream_workspace", 0)
+        plan = _STREAM_PLANS[key] = (wsf.value, nc.value, sp.value, bn.value)
+    ws_floats, n_counters, splits, _ = plan
+    ws = cnt = None
+    if splits > 1:
+        ws = C.workspace(x.device, ws_floats * 4, "gemm_stream")
+        cnt = _STREAM_COUNTERS.get(x.device.index)
+        if cnt is None or cnt.numel() < n_counters:
+            cnt = _STREAM_COUNTERS[x.device.index] = torch.zeros(max(4096, 2 * n_counters), dtype=torch.int32, device=x.device)
+    rc = lib.axb_gemm_stream(C.ptr(x), C.ptr(w), C.ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),
+                             ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(out.stride(0)),
+                             int(out.dtype == torch.float32), C.ptr(ws), C.ptr(cnt), C.ptr(C.status(x.device)), C.stream())
+    C.launched(rc, "gemm_stream", 1)
+    return out
+
+
 def _native_gemm_smallm(x, w, out, M, N, K):
     lib = C.lib()
+    if USE_STREAM_DECODE and N % 4 == 0 and out.stride(0) % 4 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0:
+        return _native_gemm_stream(x, w, out, M, N, K)
     if USE_CLUSTER_DECODE and lib.axb_gemm_decode_cluster_size(M, N, K) >= 2:
         rc = lib.axb_gemm_decode_cluster(C.ptr(x), C.ptr(w), C.ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),
                                          ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(out.stride(0)),

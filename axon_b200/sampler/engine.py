@@ -34,6 +34,7 @@ class _Seq:
     length: int = 0            # tokens currently in the KV cache
     last_token: int = 0
     done: bool = False
+    leader: object = None      # during admission: the sequence whose prompt pages and prefill this one reuses
 
 
 class GenerationEngine:
@@ -61,6 +62,7 @@ class GenerationEngine:
         # CUDA-graph decode: one captured graph per batch-size bucket (re-captured after every wake_up,
         # because the KV pool moves). Disabled on CPU.
         self.use_cuda_graph = self.device.type == "cuda"
+        self.share_prompts = True          # n samples of one prompt share its KV pages and its prefill
         self._graphs: dict[int, dict] = {}
         self.max_pages_per_seq = (self.cfg.max_position_embeddings + PAGE - 1) // PAGE
 
@@ -131,21 +133,34 @@ class GenerationEngine:
         self.finished[s.rid] = s.out
 
     def _admit(self) -> list[_Seq]:
-        """Pick waiting sequences that fit the page pool and the token budget."""
+        """Pick waiting sequences that fit the page pool and the token budget. Fresh sequences with the
+        same prompt as an earlier one of the batch (n samples per prompt) become its followers: they
+        share the prompt's full pages and are not prefilled again."""
         batch, tokens = [], 0
+        leaders: dict[tuple, _Seq] = {}
         while self.waiting and len(self.running) + len(batch) < self.max_num_seqs:
             s = self.waiting[0]
             n = len(s.prompt) + len(s.out.token_ids)  # a preempted sequence re-prefills its output too
             need = (n + 1 + PAGE - 1) // PAGE
+            key = tuple(s.prompt) if (self.share_prompts and not s.out.token_ids) else None
+            lead = leaders.get(key) if key is not None else None
+            shared = (len(s.prompt) // PAGE) if lead is not None else 0
             # keep one page of head-room per running sequence so decode can always advance
-            if need > self.cache.num_free() - len(self.running) - len(batch):
+            if need - shared > self.cache.num_free() - len(self.running) - len(batch):
                 break
-            if batch and tokens + n > self.max_num_batched_tokens:
+            if lead is None and batch and tokens + n > self.max_num_batched_tokens:
                 break
             self.waiting.popleft()
-            s.pages = self.cache.alloc(need)
+            if lead is not None:
+                s.pages = self.cache.share(lead.pages[:shared]) + self.cache.alloc(need - shared)
+                s.leader = lead
+            else:
+                s.pages = self.cache.alloc(need)
+                s.leader = None
+                tokens += n
+                if key is not None:
+                    leaders[key] = s
             batch.append(s)
-            tokens += n
         return batch
 
     def _block_table(self, seqs) -> torch.Tensor:
@@ -178,7 +193,8 @@ class GenerationEngine:
         # the one host sync of a step: finish detection needs the ids
         self._record(seqs, toks.cpu().tolist(), lps.cpu().tolist())
 
-    def _prefill(self, seqs) -> None:
+    def _prefill(self, all_seqs) -> None:
+        seqs = [s for s in all_seqs if getattr(s, "leader", None) is None]     # followers reuse their leader's prefill
         toks = [torch.tensor(s.prompt + s.out.token_ids, dtype=torch.int32) for s in seqs]
         batch = PackedBatch.from_sequences(toks, self.device)
         lens = [int(t.numel()) for t in toks]
@@ -189,8 +205,24 @@ class GenerationEngine:
         for s, n in zip(seqs, lens):
             s.length = n
         self.stats["prefill_tokens"] += sum(lens)
-        self._sample_and_record(seqs, logits)
-        self.running.extend(s for s in seqs if not s.done)
+        if len(seqs) != len(all_seqs):
+            row = {id(s): i for i, s in enumerate(seqs)}
+            src, dst, rows = [], [], []
+            for s in all_seqs:
+                lead = s.leader if s.leader is not None else s
+                rows.append(row[id(lead)])
+                if s.leader is not None:
+                    s.length = lead.length
+                    full = len(s.prompt) // PAGE
+                    if len(s.prompt) % PAGE:          # the partly filled last prompt page is private: copy it
+                        src.append(lead.pages[full])
+                        dst.append(s.pages[full])
+                    s.leader = None
+            self.cache.copy_pages(src, dst)
+            self.stats["shared_prompt_seqs"] = self.stats.get("shared_prompt_seqs", 0) + len(all_seqs) - len(seqs)
+            logits = logits[torch.tensor(rows, dtype=torch.long, device=logits.device)]
+        self._sample_and_record(all_seqs, logits)
+        self.running.extend(s for s in all_seqs if not s.done)
 
     # ------------------------------------------------------------------ CUDA-graph decode
     def set_max_model_len(self, n: int) -> None:

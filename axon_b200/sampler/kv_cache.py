@@ -1,5 +1,6 @@
-"""Paged KV cache: per-layer ``[num_pages, Hkv, 128, D]`` K and V pools, a host-side free list,
-and per-sequence block tables. Page = 128 tokens (one TMA tile of the decode kernel)."""
+"""Paged KV cache: per-layer ``[num_pages, Hkv, 128, D]`` K and V pools, a host-side free list with
+reference counts (sequences sampled from the same prompt share the prompt's full pages), and
+per-sequence block tables. Page = 128 tokens (one TMA tile of the decode kernel)."""
 from __future__ import annotations
 
 import torch
@@ -18,6 +19,7 @@ class PagedKVCache:
         self.k = [torch.zeros(shape, dtype=dtype, device=self.device) for _ in range(cfg.num_hidden_layers)]
         self.v = [torch.zeros(shape, dtype=dtype, device=self.device) for _ in range(cfg.num_hidden_layers)]
         self.free = list(range(self.num_pages - 1, -1, -1))
+        self.ref = [0] * self.num_pages
         self._arange = torch.arange(4096, dtype=torch.int32, device=self.device)
 
     @staticmethod
@@ -36,10 +38,32 @@ class PagedKVCache:
         if n > len(self.free):
             raise MemoryError(f"KV cache exhausted: want {n} pages, {len(self.free)} free")
         out = [self.free.pop() for _ in range(n)]
+        for p in out:
+            self.ref[p] = 1
         return out
 
+    def share(self, pages: list[int]) -> list[int]:
+        """Another owner for pages that are already full (read-only from now on)."""
+        for p in pages:
+            assert self.ref[p] > 0, f"page {p} is not allocated"
+            self.ref[p] += 1
+        return list(pages)
+
     def release(self, pages: list[int]) -> None:
-        self.free.extend(pages)
+        for p in pages:
+            self.ref[p] -= 1
+            if self.ref[p] == 0:
+                self.free.append(p)
+
+    def copy_pages(self, src: list[int], dst: list[int]) -> None:
+        """Copy whole pages (every layer, K and V): the partly filled last prompt page of a shared prompt."""
+        if not src:
+            return
+        si = torch.tensor(src, dtype=torch.long, device=self.device)
+        di = torch.tensor(dst, dtype=torch.long, device=self.device)
+        for k, v in zip(self.k, self.v):
+            k[di] = k[si]
+            v[di] = v[si]
 
     def drop(self) -> None:
         """Release the device memory (sleep); the cache must be rebuilt before the next use."""

@@ -85,22 +85,47 @@ def test_gemm_decode_cluster_matches_reference_and_split_kernel(M, N, K):
     ref = a.float() @ b.float().t()
     cs = lib.axb_gemm_decode_cluster_size(M, N, K)
     assert 0 <= cs <= 8
-    G.USE_CLUSTER_DECODE = True
+    G.USE_CLUSTER_DECODE, G.USE_STREAM_DECODE = True, False
     try:
         out = G.gemm_nt(a, b)
         out32 = G.gemm_nt(a, b, out_dtype=torch.float32)
         again = G.gemm_nt(a, b)
-    finally:
-        G.USE_CLUSTER_DECODE = True
-    _check(out, ref, K)
-    _check(out32, ref, K)
-    assert torch.equal(out, again)
-    G.USE_CLUSTER_DECODE = False
-    try:
+        _check(out, ref, K)
+        _check(out32, ref, K)
+        assert torch.equal(out, again)
+        G.USE_CLUSTER_DECODE = False
         old32 = G.gemm_nt(a, b, out_dtype=torch.float32)
     finally:
-        G.USE_CLUSTER_DECODE = True
+        G.USE_CLUSTER_DECODE, G.USE_STREAM_DECODE = True, True
     torch.testing.assert_close(out32, old32, rtol=1e-4, atol=1e-3 * (K ** 0.5) / 16)
+    C.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (5, 1024, 512), (17, 1024, 4096), (48, 6144, 4096), (64, 4096, 4096),
+                                   (100, 4096, 12288), (129, 6144, 4096), (160, 24576, 4096), (256, 6144, 4096),
+                                   (200, 2048 + 40, 1024), (256, 1000, 576), (33, 151936, 1024)])
+def test_gemm_stream_matches_reference(M, N, K):
+    """Weight-streaming decode kernel: against fp32 PyTorch for bf16 and fp32 outputs, bit-identical
+    from run to run (the split-K sum order is fixed although the reducing CTA is not), under several
+    forced plans (no split, many splits, one 256-wide token tile), and its arrival counters are back at
+    zero after every launch."""
+    a, b = _rand(M, K), _rand(N, K)
+    ref = a.float() @ b.float().t()
+    assert G.USE_STREAM_DECODE
+    try:
+        for knobs in (dict(), dict(force_splits=1), dict(force_splits=3), dict(force_splits=7, max_bn=256), dict(max_bn=64, smem_budget_kb=60)):
+            G.stream_tune(force_splits=0, max_bn=128, smem_budget_kb=108, reduce_kb=256, min_kblocks=8)
+            G.stream_tune(**knobs)
+            out = G.gemm_nt(a, b)
+            out32 = G.gemm_nt(a, b, out_dtype=torch.float32)
+            _check(out, ref, K)
+            _check(out32, ref, K)
+            assert torch.equal(out, G.gemm_nt(a, b)), knobs
+            for cnt in G._STREAM_COUNTERS.values():
+                assert int(cnt.abs().sum()) == 0
+    finally:
+        G.stream_tune(force_splits=0, max_bn=128, smem_budget_kb=108, reduce_kb=256, min_kblocks=8)
     C.check_status()
 
 

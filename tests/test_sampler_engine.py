@@ -80,3 +80,43 @@ def test_preemption_eos_and_pause_cpu():
     eng2.finished.clear()
     out = eng2.generate([prompts[0]], sp)[0]
     assert out.token_ids == outs[0].token_ids
+
+
+def _shared_prompt_run(device, dtype, share):
+    torch.manual_seed(0)
+    cfg = tiny_qwen3() if device == "cpu" else tiny_gpu()
+    model = _make(cfg, device, dtype)
+    eng = GenerationEngine(model, num_pages=40, max_num_seqs=16)
+    eng.share_prompts = share
+    g = torch.Generator().manual_seed(5)
+    base = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (256, 150, 7)]   # full pages only / partial tail / no full page
+    prompts = [p for p in base for _ in range(4)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.9, max_tokens=24, ignore_eos=True))
+    assert eng.cache.num_free() == 40 and all(r == 0 for r in eng.cache.ref)
+    return eng, [(o.token_ids, o.logprobs) for o in outs]
+
+
+def _check_shared(device, dtype, tol, exact=True):
+    eng_a, a = _shared_prompt_run(device, dtype, True)
+    eng_b, b = _shared_prompt_run(device, dtype, False)
+    assert eng_a.stats.get("shared_prompt_seqs", 0) == 9 and eng_b.stats.get("shared_prompt_seqs", 0) == 0
+    assert eng_a.stats["prefill_tokens"] == 256 + 150 + 7 and eng_b.stats["prefill_tokens"] == 4 * (256 + 150 + 7)
+    same = 0
+    for (ta, la), (tb, lb) in zip(a, b):
+        if exact:
+            assert ta == tb
+            assert max(abs(x - y) for x, y in zip(la, lb)) < tol
+        same += int(ta == tb)
+    # bf16 on the GPU: a different prefill batch may pick a different GEMM split, so a sampled token can flip
+    assert same >= (len(a) if exact else len(a) - 3), same
+    # samples of one prompt differ from each other (independent random streams)
+    assert len({tuple(t) for t, _ in a[:4]}) > 1
+
+
+def test_samples_of_one_prompt_share_its_pages_cpu():
+    _check_shared("cpu", torch.float32, 1e-5)
+
+
+@pytest.mark.gpu
+def test_samples_of_one_prompt_share_its_pages_gpu():
+    _check_shared("cuda", torch.bfloat16, 1e-5, exact=False)
