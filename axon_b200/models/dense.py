@@ -60,17 +60,39 @@ class DenseModel:
         self.recompute = "selective"          # activation recomputation in backward: full | selective | none
 
     # ------------------------------------------------------------------ helpers
+    # ``weights`` is what the forward pass reads and ``_wgrad`` where weight gradients go; both are the
+    # trainable ``params`` here. A model with frozen base weights (adapters) overrides them.
+    @property
+    def weights(self) -> FlatParams:
+        return self.params
+
+    def _wgrad(self, name: str):
+        return self.params.grads[name]
+
     def _p(self, l: int, name: str) -> torch.Tensor:
-        return self.params[f"model.layers.{l}.{name}"]
+        return self.weights[f"model.layers.{l}.{name}"]
 
     def _g(self, l: int, name: str) -> torch.Tensor:
-        return self.params.grads[f"model.layers.{l}.{name}"]
+        return self._wgrad(f"model.layers.{l}.{name}")
 
     def head_weight(self) -> torch.Tensor:
-        return self.params["model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight"]
+        return self.weights["model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight"]
 
     def head_grad(self) -> torch.Tensor:
-        return self.params.grads["model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight"]
+        return self._wgrad("model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight")
+
+    def _lin(self, l: int, name: str, x: torch.Tensor) -> torch.Tensor:
+        """y = x W^T for the layer's linear ``name`` (adapter models add their low-rank path here)."""
+        return G.gemm_nt(x, self._p(l, name))
+
+    def _lin_bwd(self, l: int, name: str, dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """Input gradient of ``_lin``; accumulates the weight gradient."""
+        dx = G.gemm_nn(dy, self._p(l, name))
+        G.gemm_tn(dy, x, out=self._g(l, name), accumulate=True)
+        return dx
+
+    def _embed_bwd(self, batch: "PackedBatch", dx: torch.Tensor) -> None:
+        A.embedding_bwd(batch.input_ids, dx, self._wgrad("model.embed_tokens.weight"))
 
     def _tables(self, max_pos: int):
         return R.rope_tables(max(max_pos, 8), self.cfg.head_dim, self.cfg.rope_theta, self.device)
@@ -91,13 +113,13 @@ class DenseModel:
         qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
         kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
         h, rstd1, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
-        qkv = G.gemm_nt(h, self._p(l, "self_attn.qkv_proj.weight"))
+        qkv = self._lin(l, "self_attn.qkv_proj.weight", h)
         qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
                                   c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
         want = self._KEEP[self.recompute] if keep else ()
         o, lse = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                              need_lse="lse" in want)
-        ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
+        ao = self._lin(l, "self_attn.o_proj.weight", o)
         h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
         mo, mlp_saved = self.mlp_fwd(l, h2, batch, want)
         local = dict(xin=xin, qkv=qkv, o=o, lse=lse, x1=x1, **mlp_saved)
@@ -106,9 +128,9 @@ class DenseModel:
     # ---- MLP hooks (dense SwiGLU here; the mixture-of-experts model overrides the three of them)
     def mlp_fwd(self, l: int, h2, batch: PackedBatch, want=()):
         """Returns (mlp output, tensors to keep for backward)."""
-        gu = G.gemm_nt(h2, self._p(l, "mlp.gate_up_proj.weight"))
+        gu = self._lin(l, "mlp.gate_up_proj.weight", h2)
         a = A.swiglu_fwd(gu)
-        mo = G.gemm_nt(a, self._p(l, "mlp.down_proj.weight"))
+        mo = self._lin(l, "mlp.down_proj.weight", a)
         return mo, ({"gu": gu} if "gu" in want else {})
 
     def mlp_infer(self, l: int, h2):
@@ -117,17 +139,15 @@ class DenseModel:
 
     def mlp_rebuild(self, l: int, k: dict, batch: PackedBatch) -> None:
         if "gu" not in k:
-            k["gu"] = G.gemm_nt(k["h2"], self._p(l, "mlp.gate_up_proj.weight"))
+            k["gu"] = self._lin(l, "mlp.gate_up_proj.weight", k["h2"])
         k["a"] = A.swiglu_fwd(k["gu"])
 
     def mlp_bwd(self, l: int, k: dict, dx_out):
         """Grad wrt the MLP input h2; accumulates the MLP weight gradients."""
-        da = G.gemm_nn(dx_out, self._p(l, "mlp.down_proj.weight"))
-        G.gemm_tn(dx_out, k["a"], out=self._g(l, "mlp.down_proj.weight"), accumulate=True)
+        da = self._lin_bwd(l, "mlp.down_proj.weight", dx_out, k["a"])
         dgu = A.swiglu_bwd(da, k["gu"])
         del da
-        dh2 = G.gemm_nn(dgu, self._p(l, "mlp.gate_up_proj.weight"))
-        G.gemm_tn(dgu, k["h2"], out=self._g(l, "mlp.gate_up_proj.weight"), accumulate=True)
+        dh2 = self._lin_bwd(l, "mlp.gate_up_proj.weight", dgu, k["h2"])
         return dh2
 
     def _rebuild(self, l: int, saved: dict, batch: PackedBatch, tables) -> dict:
@@ -138,14 +158,14 @@ class DenseModel:
         k = dict(saved)
         k["h"], k["rstd1"], _ = N.rmsnorm_fwd(k["xin"], self._p(l, "input_layernorm.weight"), c.rms_norm_eps)
         if "qkv" not in k:
-            k["qkv"] = G.gemm_nt(k["h"], self._p(l, "self_attn.qkv_proj.weight"))
+            k["qkv"] = self._lin(l, "self_attn.qkv_proj.weight", k["h"])
         k["qkv_r"] = R.qknorm_rope_fwd(k["qkv"], batch.position_ids, tables[0], tables[1], c.num_attention_heads,
                                        c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
         if "o" not in k:
             k["o"], k["lse"] = AT.attn_fwd(k["qkv_r"], batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads,
                                            c.head_dim, need_lse=True)
         if "x1" not in k:
-            ao = G.gemm_nt(k["o"], self._p(l, "self_attn.o_proj.weight"))
+            ao = self._lin(l, "self_attn.o_proj.weight", k["o"])
             k["h2"], k["rstd2"], k["x1"] = N.rmsnorm_fwd(k["xin"], self._p(l, "post_attention_layernorm.weight"),
                                                          c.rms_norm_eps, delta=ao)
         else:
@@ -166,8 +186,7 @@ class DenseModel:
                             self._g(l, "post_attention_layernorm.weight"), dres=dx_out)
         del dh2
         # attention
-        do = G.gemm_nn(dx1, self._p(l, "self_attn.o_proj.weight"))
-        G.gemm_tn(dx1, k["o"], out=self._g(l, "self_attn.o_proj.weight"), accumulate=True)
+        do = self._lin_bwd(l, "self_attn.o_proj.weight", dx1, k["o"])
         dqkv_r = AT.attn_bwd(do, k["qkv_r"], k["o"], k["lse"], batch.cu_seqlens, c.num_attention_heads,
                              c.num_key_value_heads, c.head_dim)
         del do
@@ -176,8 +195,7 @@ class DenseModel:
                                  self._g(l, "self_attn.q_norm.weight") if c.qk_norm else None,
                                  self._g(l, "self_attn.k_norm.weight") if c.qk_norm else None, c.rms_norm_eps)
         del dqkv_r
-        dh = G.gemm_nn(dqkv, self._p(l, "self_attn.qkv_proj.weight"))
-        G.gemm_tn(dqkv, k["h"], out=self._g(l, "self_attn.qkv_proj.weight"), accumulate=True)
+        dh = self._lin_bwd(l, "self_attn.qkv_proj.weight", dqkv, k["h"])
         del dqkv
         dx = N.rmsnorm_bwd(dh, k["xin"], self._p(l, "input_layernorm.weight"), k["rstd1"],
                            self._g(l, "input_layernorm.weight"), dres=dx1)
@@ -188,14 +206,14 @@ class DenseModel:
         """Embedding + all layers + final norm. Returns (hf, state) with state holding what backward needs."""
         c = self.cfg
         tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
-        x = A.embedding_fwd(batch.input_ids, self.params["model.embed_tokens.weight"])
+        x = A.embedding_fwd(batch.input_ids, self.weights["model.embed_tokens.weight"])
         delta = None
         layer_inputs = []
         for l in range(c.num_hidden_layers):
             x, delta, saved = self.layer_fwd(l, x, delta, batch, tables, keep=save_for_backward)
             if save_for_backward:
                 layer_inputs.append(saved)
-        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], c.rms_norm_eps, delta=delta)
         state = dict(batch=batch, tables=tables, layer_inputs=layer_inputs, xf=xf, hf=hf, rstd_f=rstd_f) \
             if save_for_backward else None
         return hf, state
@@ -203,15 +221,15 @@ class DenseModel:
     def _trunk_bwd(self, s: dict, dhf: torch.Tensor) -> None:
         c = self.cfg
         batch, tables = s["batch"], s["tables"]
-        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"],
-                           self.params.grads["model.norm.weight"])
+        dx = N.rmsnorm_bwd(dhf, s["xf"], self.weights["model.norm.weight"], s["rstd_f"],
+                           self._wgrad("model.norm.weight"))
         del dhf
         inputs = s["layer_inputs"]
         for l in reversed(range(c.num_hidden_layers)):
             saved = inputs.pop()
             dx = self.layer_bwd(l, saved, dx, batch, tables)
             del saved
-        A.embedding_bwd(batch.input_ids, dx, self.params.grads["model.embed_tokens.weight"])
+        self._embed_bwd(batch, dx)
 
     def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
         """Scalar value per packed position from the value head (fp32 [T]); needs ``value_head`` in the config."""
@@ -280,26 +298,26 @@ class _DenseInference:
         from ..ops import paged as P
         c = self.cfg
         tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
-        x = A.embedding_fwd(batch.input_ids, self.params["model.embed_tokens.weight"])
+        x = A.embedding_fwd(batch.input_ids, self.weights["model.embed_tokens.weight"])
         delta = None
         for l in range(c.num_hidden_layers):
             qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
             kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
             h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
-            qkv = G.gemm_nt(h, self._p(l, "self_attn.qkv_proj.weight"))
+            qkv = self._lin(l, "self_attn.qkv_proj.weight", h)
             qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
                                       c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
             P.kv_write(qkv_r, cache.k[l], cache.v[l], tok_seq, tok_pos, block_table, c.num_attention_heads,
                        c.num_key_value_heads, c.head_dim)
             o, _ = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                                need_lse=False)
-            ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
+            ao = self._lin(l, "self_attn.o_proj.weight", o)
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
             delta = self.mlp_infer(l, h2)
             x = x1
         xl = x[last_index]
         dl = delta[last_index]
-        hf, _, _ = N.rmsnorm_fwd(xl, self.params["model.norm.weight"], c.rms_norm_eps, delta=dl)
+        hf, _, _ = N.rmsnorm_fwd(xl, self.weights["model.norm.weight"], c.rms_norm_eps, delta=dl)
         return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)
 
     def decode(self, tokens, positions, cache, block_table, seq_lens):
@@ -309,25 +327,25 @@ class _DenseInference:
         c = self.cfg
         B = tokens.numel()
         tables = self._tables(c.max_position_embeddings)
-        x = A.embedding_fwd(tokens, self.params["model.embed_tokens.weight"])
+        x = A.embedding_fwd(tokens, self.weights["model.embed_tokens.weight"])
         delta = None
         slots = cache.arange(B)
         for l in range(c.num_hidden_layers):
             qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
             kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
             h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
-            qkv = G.gemm_nt(h, self._p(l, "self_attn.qkv_proj.weight"))
+            qkv = self._lin(l, "self_attn.qkv_proj.weight", h)
             qkv_r = R.qknorm_rope_fwd(qkv, positions, tables[0], tables[1], c.num_attention_heads,
                                       c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
             P.kv_write(qkv_r, cache.k[l], cache.v[l], slots, positions, block_table, c.num_attention_heads,
                        c.num_key_value_heads, c.head_dim)
             o = P.paged_decode(qkv_r, cache.k[l], cache.v[l], block_table, seq_lens, c.num_attention_heads,
                                c.num_key_value_heads, c.head_dim)
-            ao = G.gemm_nt(o, self._p(l, "self_attn.o_proj.weight"))
+            ao = self._lin(l, "self_attn.o_proj.weight", o)
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
             delta = self.mlp_infer(l, h2)
             x = x1
-        hf, _, _ = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        hf, _, _ = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], c.rms_norm_eps, delta=delta)
         return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)
 
 

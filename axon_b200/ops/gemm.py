@@ -40,13 +40,22 @@ USE_CLUSTER_DECODE = True   # cluster split-K kernel (partials reduced through d
 USE_STREAM_DECODE = True    # weight-streaming kernel (run-time token width, last-arriver split-K reduction)
 _STREAM_PLANS: dict = {}
 _STREAM_COUNTERS: dict = {}
+_STREAM_ACC: dict = {}
 _STREAM_TUNE_VERSION = 0
 
 
-def stream_tune(force_splits=0, max_bn=0, smem_budget_kb=0, reduce_kb=0, min_kblocks=0, target_ctas=0) -> None:
-    """Experiment hook: change the planning knobs of the weight-streaming kernel (0 keeps a knob)."""
+_STREAM_KNOBS = {"force_splits": 0, "max_bn": 1, "ring_kb_one": 2, "ring_kb_two": 3, "two_per_sm_tiles": 4, "x_depth": 5,
+                 "min_kblocks": 6, "pdl": 7, "accumulate": 8}
+STREAM_DEFAULTS = dict(force_splits=0, max_bn=128, ring_kb_one=208, ring_kb_two=104, two_per_sm_tiles=1, x_depth=0,
+                       min_kblocks=8, pdl=1, accumulate=1)
+
+
+def stream_tune(**knobs) -> None:
+    """Experiment hook: set planning knobs of the weight-streaming kernel (names of ``STREAM_DEFAULTS``;
+    ``accumulate``: 1 = split-K partials added by L2 reductions, 0 = summed in split order, bit-reproducible)."""
     global _STREAM_TUNE_VERSION
-    C.lib().axb_gemm_stream_tune(int(force_splits), int(max_bn), int(smem_budget_kb), int(reduce_kb), int(min_kblocks), int(target_ctas))
+    for k, v in knobs.items():
+        C.lib().axb_gemm_stream_knob(_STREAM_KNOBS[k], int(v))
     _STREAM_TUNE_VERSION += 1
 
 
@@ -55,14 +64,19 @@ def _native_gemm_stream(x, w, out, M, N, K):
     key = (M, N, K, _STREAM_TUNE_VERSION)
     plan = _STREAM_PLANS.get(key)
     if plan is None:
-        wsf, nc, sp, bn = ctypes.c_longlong(0), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
-        rc = lib.axb_gemm_stream_workspace(M, N, K, ctypes.byref(wsf), ctypes.byref(nc), ctypes.byref(sp), ctypes.byref(bn))
+        wsf, nc, sp, bn, zr = ctypes.c_longlong(0), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+        rc = lib.axb_gemm_stream_workspace(M, N, K, ctypes.byref(wsf), ctypes.byref(nc), ctypes.byref(sp), ctypes.byref(bn), ctypes.byref(zr))
         C.launched(rc, "gemm_stream_workspace", 0)
-        plan = _STREAM_PLANS[key] = (wsf.value, nc.value, sp.value, bn.value)
-    ws_floats, n_counters, splits, _ = plan
+        plan = _STREAM_PLANS[key] = (wsf.value, nc.value, sp.value, bn.value, zr.value)
+    ws_floats, n_counters, splits, _, zeroed = plan
     ws = cnt = None
     if splits > 1:
-        ws = C.workspace(x.device, ws_floats * 4, "gemm_stream")
+        if zeroed:      # accumulation tiles: zero once, every launch leaves them zero
+            ws = _STREAM_ACC.get(x.device.index)
+            if ws is None or ws.numel() < ws_floats:
+                ws = _STREAM_ACC[x.device.index] = torch.zeros(max(1 << 22, 2 * ws_floats), dtype=torch.float32, device=x.device)
+        else:
+            ws = C.workspace(x.device, ws_floats * 4, "gemm_stream")
         cnt = _STREAM_COUNTERS.get(x.device.index)
         if cnt is None or cnt.numel() < n_counters:
             cnt = _STREAM_COUNTERS[x.device.index] = torch.zeros(max(4096, 2 * n_counters), dtype=torch.int32, device=x.device)

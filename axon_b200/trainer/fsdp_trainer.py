@@ -172,6 +172,20 @@ class TrainerWorker(Worker, DistProfilerExtension):
         mcfg = get_config(model_path)
         if self.model_kind.value_head:
             mcfg.extra = {**mcfg.extra, "value_head": True}
+        lora = _get(self.config, "lora", None)
+        if lora is not None and int(_get(lora, "rank", 0) or 0) > 0:
+            # adapters: the base stays frozen in the model, `model.params` (what the optimizer, its
+            # shards and the checkpoints see) holds only the low-rank matrices
+            from ..models.lora import LoRAConfig, LoRADenseModel
+            assert mcfg.num_experts == 0 and not self.model_kind.value_head, "LoRA is available on dense causal-LM models"
+            model = LoRADenseModel(mcfg, LoRAConfig.from_dict(lora), device=self.device, dtype=dtype)
+            model.recompute = str(_get(self.config, "recompute", "selective"))
+            if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+                from ..utils.hf_model import iter_hf_weights
+                model.base.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+            else:
+                model.base.init_random(seed=seed)
+            return model
         model = build_model_for(mcfg, device=self.device, dtype=dtype)
         model.recompute = str(_get(self.config, "recompute", "selective"))
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
@@ -266,6 +280,12 @@ class TrainerWorker(Worker, DistProfilerExtension):
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def save_state(self, path: str, global_step: int = 0, max_ckpt_to_keep=None, save_mode: str = "sharded",
                    async_save: bool = False):
+        if hasattr(self.model, "save_adapter"):
+            # adapter run: the sharded files hold adapters + optimizer state; the exportable artefact is
+            # the PEFT-layout adapter directory (the frozen base is the model the run started from)
+            save_mode = "sharded"
+            if self.rank == 0:
+                self.model.save_adapter(os.path.join(path, "lora_adapter"))
         self.state_manager.save_state(path, global_step=global_step, max_ckpt_to_keep=max_ckpt_to_keep,
                                       save_mode=save_mode, async_save=async_save)
         if self._is_offload_optimizer:

@@ -308,8 +308,9 @@ class PolicyEngine:
         shard, gather the updated bf16 parameters. Skips the update when the norm is not finite."""
         p = self.model.params
         assert p.grad_flat is not None, "no gradients accumulated"
-        if hasattr(self.model, "sync_replicated_grads"):
-            self.model.sync_replicated_grads()
+        for hook in ("sync_replicated_grads", "finalize_grads"):      # model-parallel sums, adapter masks
+            if hasattr(self.model, hook):
+                getattr(self.model, hook)()
         if self.master is None:
             self.load_optimizer()
             if self.master is None:

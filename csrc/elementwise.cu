@@ -46,6 +46,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ xsum,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int H, float eps) {
   __shared__ float red[NORM_THREADS / 32];
+  grid_launch_dependents();   // a GEMM launched as a programmatic dependent may start streaming its weights now
   const long long row = blockIdx.x;
   const int nv = H / 8;
   const uint4* xv = reinterpret_cast<const uint4*>(x + row * H);
@@ -313,6 +314,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat
 // gu is [T][2F] (gate | up); a[T][F] = silu(gate) * up.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ a,
                                   long long T, int F) {
+  grid_launch_dependents();   // see rmsnorm_fwd_kernel
   const int fv = F / 8;
   const long long n = T * fv;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;

@@ -61,6 +61,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens,
                     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                     int Hq, int Hkv, int nsplit, float scale_log2, int* status) {
+  grid_launch_dependents();   // the output projection (a programmatic dependent) may start streaming its weights
   const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
   const int rep = Hq / Hkv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -275,6 +276,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 // out[b][h][:] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 __global__ void paged_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                    __nv_bfloat16* __restrict__ out, int nsplit) {
+  grid_launch_dependents();
   const long long bh = blockIdx.x;
   const int d = threadIdx.x;
   float M = -1e30f;
