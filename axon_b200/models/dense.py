@@ -91,6 +91,16 @@ class DenseModel:
         G.gemm_tn(dy, x, out=self._g(l, name), accumulate=True)
         return dx
 
+    def _attn_fwd(self, qkv_r: torch.Tensor, batch: "PackedBatch", need_lse: bool):
+        """Causal attention over the packed sequences: qkv_r [T, (Hq + 2 Hkv) D] (rotated) -> (o [T, Hq D], lse).
+        Sequence-parallel models override this pair with the head <-> token exchange around the kernel."""
+        c = self.cfg
+        return AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim, need_lse=need_lse)
+
+    def _attn_bwd(self, do, qkv_r, o, lse, batch: "PackedBatch"):
+        c = self.cfg
+        return AT.attn_bwd(do, qkv_r, o, lse, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+
     def _embed_bwd(self, batch: "PackedBatch", dx: torch.Tensor) -> None:
         A.embedding_bwd(batch.input_ids, dx, self._wgrad("model.embed_tokens.weight"))
 
@@ -117,8 +127,7 @@ class DenseModel:
         qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
                                   c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
         want = self._KEEP[self.recompute] if keep else ()
-        o, lse = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-                             need_lse="lse" in want)
+        o, lse = self._attn_fwd(qkv_r, batch, need_lse="lse" in want)
         ao = self._lin(l, "self_attn.o_proj.weight", o)
         h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
         mo, mlp_saved = self.mlp_fwd(l, h2, batch, want)
@@ -162,8 +171,7 @@ class DenseModel:
         k["qkv_r"] = R.qknorm_rope_fwd(k["qkv"], batch.position_ids, tables[0], tables[1], c.num_attention_heads,
                                        c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
         if "o" not in k:
-            k["o"], k["lse"] = AT.attn_fwd(k["qkv_r"], batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads,
-                                           c.head_dim, need_lse=True)
+            k["o"], k["lse"] = self._attn_fwd(k["qkv_r"], batch, need_lse=True)
         if "x1" not in k:
             ao = self._lin(l, "self_attn.o_proj.weight", k["o"])
             k["h2"], k["rstd2"], k["x1"] = N.rmsnorm_fwd(k["xin"], self._p(l, "post_attention_layernorm.weight"),
@@ -187,8 +195,7 @@ class DenseModel:
         del dh2
         # attention
         do = self._lin_bwd(l, "self_attn.o_proj.weight", dx1, k["o"])
-        dqkv_r = AT.attn_bwd(do, k["qkv_r"], k["o"], k["lse"], batch.cu_seqlens, c.num_attention_heads,
-                             c.num_key_value_heads, c.head_dim)
+        dqkv_r = self._attn_bwd(do, k["qkv_r"], k["o"], k["lse"], batch)
         del do
         dqkv = R.qknorm_rope_bwd(dqkv_r, k["qkv"], batch.position_ids, tables[0], tables[1], c.num_attention_heads,
                                  c.num_key_value_heads, c.head_dim, qw, kw,

@@ -37,6 +37,7 @@ FIXED_CONFIG = False        # batch-invariant mode: one tile width, no K split, 
 USE_CLUSTER_DECODE = True   # cluster split-K kernel (partials reduced through distributed shared memory)
 
 
+STREAM_MAX_M = 128
 USE_STREAM_DECODE = True    # weight-streaming kernel (run-time token width, last-arriver split-K reduction)
 _STREAM_PLANS: dict = {}
 _STREAM_COUNTERS: dict = {}
@@ -89,7 +90,10 @@ def _native_gemm_stream(x, w, out, M, N, K):
 
 def _native_gemm_smallm(x, w, out, M, N, K):
     lib = C.lib()
-    if USE_STREAM_DECODE and N % 4 == 0 and out.stride(0) % 4 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0:
+    # up to 128 tokens (one token tile) the weight-streaming kernel wins; above, the two-tile plan re-reads W
+    # and the cluster / split-K kernels below measured faster inside the decode graph
+    if USE_STREAM_DECODE and M <= STREAM_MAX_M and N % 4 == 0 and out.stride(0) % 4 == 0 and x.stride(0) % 8 == 0 \
+            and w.stride(0) % 8 == 0:
         return _native_gemm_stream(x, w, out, M, N, K)
     if USE_CLUSTER_DECODE and lib.axb_gemm_decode_cluster_size(M, N, K) >= 2:
         rc = lib.axb_gemm_decode_cluster(C.ptr(x), C.ptr(w), C.ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),

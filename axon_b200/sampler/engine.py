@@ -64,6 +64,9 @@ class GenerationEngine:
         self.use_cuda_graph = self.device.type == "cuda"
         self.share_prompts = True          # n samples of one prompt share its KV pages and its prefill
         self._graphs: dict[int, dict] = {}
+        # batch-size buckets of the captured graphs: the decode GEMM's token width is a run-time value, so
+        # finer buckets than powers of two pay off as the batch drains
+        self.graph_buckets = (8, 16, 24, 32, 48, 64, 80, 96, 112, 128, 160, 192, 224, 256)
         self.max_pages_per_seq = (self.cfg.max_position_embeddings + PAGE - 1) // PAGE
 
     # ------------------------------------------------------------------ request API
@@ -266,9 +269,9 @@ class GenerationEngine:
 
     def _decode_graph(self, seqs) -> tuple[list, list]:
         B = len(seqs)
-        bucket = 8
-        while bucket < B:
-            bucket *= 2
+        bucket = next((b for b in self.graph_buckets if b >= B), None)
+        if bucket is None:
+            bucket = (B + 63) // 64 * 64
         g = self._graphs.get(bucket)
         if g is None:
             g = self._graphs[bucket] = self._capture(bucket)

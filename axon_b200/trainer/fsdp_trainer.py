@@ -156,7 +156,7 @@ class TrainerWorker(Worker, DistProfilerExtension):
                            warmup_steps=warm, total_steps=int(total), min_lr_ratio=float(_get(sched, "min_lr_ratio", 0.0) or 0.0),
                            schedule=str(_get(sched, "type", "constant")))
         self.engine = PolicyEngine(self.model, ocfg, process_group=self.pg,
-                                   max_token_len_per_gpu=int(_get(cfg, "max_token_len_per_gpu", 16384)),
+                                   max_token_len_per_gpu=int(_get(cfg, "max_token_len_per_gpu", 16384)) * self.ulysses_sequence_parallel_size,
                                    temperature=1.0)
         self.flops_counter = FlopsCounter(self.model.cfg, dtype)
         self.state_manager = FSDPStateManager(self.model, self.engine, processing_class=self.tokenizer, rank=self.rank,
@@ -186,6 +186,29 @@ class TrainerWorker(Worker, DistProfilerExtension):
             else:
                 model.base.init_random(seed=seed)
             return model
+        sp = self.ulysses_sequence_parallel_size
+        if sp > 1:
+            # Ulysses: consecutive ranks form a sequence-parallel group (same rows, T / sp tokens each); the
+            # optimizer keeps sharding over ALL ranks, so its reduce-scatter also completes the partial
+            # weight gradients of the group
+            from ..models.ulysses import UlyssesDenseModel, UlyssesModelAdapter
+            from ..parallel.ulysses import UlyssesContext
+            assert mcfg.num_experts == 0 and not self.model_kind.value_head, "sequence parallelism is available on dense causal-LM models"
+            sp_group = None
+            for i in range(self.world_size // sp):
+                ranks = list(range(i * sp, (i + 1) * sp))
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    sp_group = g
+            cap = int(_get(self.config, "max_token_len_per_gpu", 16384))       # per-rank token cap; the group packs sp times that
+            ctx = UlyssesContext(sp_group, self.device, max_rows_per_rank=(cap + 127) // 128 * 128 + 128, max_width=mcfg.qkv_size)
+            inner = UlyssesDenseModel(mcfg, ctx, device=self.device, dtype=dtype)
+            inner.recompute = str(_get(self.config, "recompute", "selective"))
+            if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+                load_hf_weights(inner, model_path)
+            else:
+                inner.params.init_random(seed=seed)
+            return UlyssesModelAdapter(inner)
         model = build_model_for(mcfg, device=self.device, dtype=dtype)
         model.recompute = str(_get(self.config, "recompute", "selective"))
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
