@@ -58,6 +58,7 @@ class DenseModel:
         self.params = params if params is not None else FlatParams(cfg, self.device, dtype)
         self._saved: dict | None = None
         self.recompute = "selective"          # activation recomputation in backward: full | selective | none
+        self.offloader = None                 # an ActivationOffloader: kept activations wait in pinned host memory
 
     # ------------------------------------------------------------------ helpers
     # ``weights`` is what the forward pass reads and ``_wgrad`` where weight gradients go; both are the
@@ -219,7 +220,8 @@ class DenseModel:
         for l in range(c.num_hidden_layers):
             x, delta, saved = self.layer_fwd(l, x, delta, batch, tables, keep=save_for_backward)
             if save_for_backward:
-                layer_inputs.append(saved)
+                layer_inputs.append(saved if self.offloader is None else self.offloader.stash(l, saved))
+            del saved
         hf, rstd_f, xf = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], c.rms_norm_eps, delta=delta)
         state = dict(batch=batch, tables=tables, layer_inputs=layer_inputs, xf=xf, hf=hf, rstd_f=rstd_f) \
             if save_for_backward else None
@@ -234,8 +236,12 @@ class DenseModel:
         inputs = s["layer_inputs"]
         for l in reversed(range(c.num_hidden_layers)):
             saved = inputs.pop()
+            if self.offloader is not None:
+                saved = self.offloader.fetch(saved)          # also starts bringing layer l - 1 back
             dx = self.layer_bwd(l, saved, dx, batch, tables)
             del saved
+        if self.offloader is not None:
+            self.offloader.end_step()
         self._embed_bwd(batch, dx)
 
     def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
@@ -327,8 +333,9 @@ class _DenseInference:
         hf, _, _ = N.rmsnorm_fwd(xl, self.weights["model.norm.weight"], c.rms_norm_eps, delta=dl)
         return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)
 
-    def decode(self, tokens, positions, cache, block_table, seq_lens):
+    def decode(self, tokens, positions, cache, block_table, seq_lens, shared=None):
         """tokens/positions: int32 [B] (the token to feed and its position); seq_lens = positions + 1.
+        ``shared``: prefix-sharing description of the batch (see ``ops.paged.paged_decode_shared``).
         Returns fp32 logits [B, V]."""
         from ..ops import paged as P
         c = self.cfg
@@ -346,8 +353,12 @@ class _DenseInference:
                                       c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
             P.kv_write(qkv_r, cache.k[l], cache.v[l], slots, positions, block_table, c.num_attention_heads,
                        c.num_key_value_heads, c.head_dim)
-            o = P.paged_decode(qkv_r, cache.k[l], cache.v[l], block_table, seq_lens, c.num_attention_heads,
-                               c.num_key_value_heads, c.head_dim)
+            if shared is None:
+                o = P.paged_decode(qkv_r, cache.k[l], cache.v[l], block_table, seq_lens, c.num_attention_heads,
+                                   c.num_key_value_heads, c.head_dim)
+            else:
+                o = P.paged_decode_shared(qkv_r, cache.k[l], cache.v[l], block_table, seq_lens, shared,
+                                          c.num_attention_heads, c.num_key_value_heads, c.head_dim)
             ao = self._lin(l, "self_attn.o_proj.weight", o)
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
             delta = self.mlp_infer(l, h2)

@@ -67,6 +67,34 @@ def paged_decode(qkv_r, kcache, vcache, block_table, seq_lens, Hq, Hkv, D, scale
     return out
 
 
+def paged_decode_shared(qkv_r, kcache, vcache, block_table, seq_lens, shared: dict, Hq, Hkv, D, scale=None):
+    """``paged_decode`` for a batch in which groups of consecutive sequences share their first pages (the n
+    samples of one prompt): the shared pages are attended to once per group, every sequence's private
+    pages once per sequence, and the partial results are merged. ``shared`` holds int32 device tensors:
+    ``seq_first`` (arange), ``seq_one`` (1 per row), ``seq_page0`` / ``seq_keys`` (first private page and the
+    keys from there on), ``grp_first`` / ``grp_size`` / ``grp_zero`` / ``grp_keys`` (first member, member count
+    - 0 for unused entries -, zeros, shared keys). Same result as ``paged_decode`` with ``seq_lens``."""
+    if not C.use_native(qkv_r):
+        return paged_decode(qkv_r, kcache, vcache, block_table, seq_lens, Hq, Hkv, D, scale)
+    B = qkv_r.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    lib = C.lib()
+    max_pages = block_table.shape[1]
+    n_groups = shared["grp_first"].numel()
+    ns = lib.axb_paged_decode_splits(B, Hkv, max_pages)
+    nsp = lib.axb_paged_decode_splits(n_groups, Hkv, int(shared.get("max_shared_pages", 8)))
+    scratch = C.workspace(qkv_r.device, B * Hq * (ns + nsp) * (D + 2) * 4, "paged")
+    out = torch.empty(B, Hq * D, dtype=qkv_r.dtype, device=qkv_r.device)
+    rc = lib.axb_paged_decode_shared(C.ptr(qkv_r), ctypes.c_longlong(qkv_r.stride(0)), C.ptr(kcache), C.ptr(vcache), kcache.shape[0],
+                                     C.ptr(block_table), max_pages, C.ptr(shared["seq_first"]), C.ptr(shared["seq_one"]),
+                                     C.ptr(shared["seq_page0"]), C.ptr(shared["seq_keys"]), C.ptr(shared["grp_first"]),
+                                     C.ptr(shared["grp_size"]), C.ptr(shared["grp_zero"]), C.ptr(shared["grp_keys"]), n_groups,
+                                     C.ptr(out), B, Hq, Hkv, D, ctypes.c_float(scale), ns, nsp, C.ptr(scratch),
+                                     C.ptr(C.status(qkv_r.device)), C.stream())
+    C.launched(rc, "paged_decode_shared", 3)
+    return out
+
+
 def _ref_process(logits, temperature, top_k, top_p):
     """Processed log-probs (after temperature / top-k / top-p), fp32 [B,V]; rows with T<=0 get argmax one-hot."""
     B, V = logits.shape

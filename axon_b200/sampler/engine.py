@@ -35,6 +35,8 @@ class _Seq:
     last_token: int = 0
     done: bool = False
     leader: object = None      # during admission: the sequence whose prompt pages and prefill this one reuses
+    share_key: int = -1        # rid of the sequence whose prompt pages this one shares (its own rid for that sequence)
+    shared_pages: int = 0      # number of leading pages shared with the group
 
 
 class GenerationEngine:
@@ -63,6 +65,7 @@ class GenerationEngine:
         # because the KV pool moves). Disabled on CPU.
         self.use_cuda_graph = self.device.type == "cuda"
         self.share_prompts = True          # n samples of one prompt share its KV pages and its prefill
+        self.cascade_attention = True      # ... and decode attends to the shared pages once per group
         self._graphs: dict[int, dict] = {}
         # batch-size buckets of the captured graphs: the decode GEMM's token width is a run-time value, so
         # finer buckets than powers of two pay off as the batch drains
@@ -157,9 +160,12 @@ class GenerationEngine:
             if lead is not None:
                 s.pages = self.cache.share(lead.pages[:shared]) + self.cache.alloc(need - shared)
                 s.leader = lead
+                s.share_key, s.shared_pages = lead.rid, shared
+                lead.share_key, lead.shared_pages = lead.rid, shared
             else:
                 s.pages = self.cache.alloc(need)
                 s.leader = None
+                s.share_key, s.shared_pages = -1, 0
                 tokens += n
                 if key is not None:
                     leaders[key] = s
@@ -233,7 +239,7 @@ class GenerationEngine:
         self.max_pages_per_seq = (n + PAGE - 1) // PAGE + 1
         self._graphs.clear()
 
-    def _capture(self, bucket: int) -> dict:
+    def _capture(self, bucket: int, cascade: bool = False) -> dict:
         from ..ops import paged as P
         dev = self.device
         g = dict(tokens=torch.zeros(bucket, dtype=torch.int32, device=dev),
@@ -244,9 +250,17 @@ class GenerationEngine:
                  top_k=torch.zeros(bucket, dtype=torch.int32, device=dev),
                  top_p=torch.ones(bucket, dtype=torch.float32, device=dev),
                  ctr=torch.zeros(bucket, dtype=torch.int32, device=dev))
+        shared = None
+        if cascade:      # prefix-sharing description: one suffix item per row, up to bucket // 2 group items
+            ng = max(1, bucket // 2)
+            zi = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)      # noqa: E731
+            g.update(seq_page0=zi(bucket), seq_keys=zi(bucket), grp_first=zi(ng), grp_size=zi(ng), grp_keys=zi(ng))
+            shared = dict(seq_first=torch.arange(bucket, dtype=torch.int32, device=dev), seq_one=torch.ones(bucket, dtype=torch.int32, device=dev),
+                          seq_page0=g["seq_page0"], seq_keys=g["seq_keys"], grp_first=g["grp_first"], grp_size=g["grp_size"],
+                          grp_zero=zi(ng), grp_keys=g["grp_keys"], max_shared_pages=self.max_pages_per_seq)
 
         def run():
-            logits = self.model.decode(g["tokens"], g["pos"], self.cache, g["bt"], g["lens"])
+            logits = self.model.decode(g["tokens"], g["pos"], self.cache, g["bt"], g["lens"], shared=shared)
             return P.sample(logits, g["temp"], g["top_k"], g["top_p"], seed=self.seed, counters=g["ctr"])
 
         side = torch.cuda.Stream(device=dev)
@@ -263,21 +277,53 @@ class GenerationEngine:
             g["out_tokens"], g["out_lps"] = run()
         g["launches"] = C.LAUNCH_COUNT - n0      # kernels each replay launches
         g["graph"] = graph
-        g["host"] = {k: torch.empty(g[k].shape, dtype=g[k].dtype, pin_memory=True)
-                     for k in ("tokens", "pos", "lens", "bt", "temp", "top_k", "top_p", "ctr")}
+        keys = ("tokens", "pos", "lens", "bt", "temp", "top_k", "top_p", "ctr") + \
+            (("seq_page0", "seq_keys", "grp_first", "grp_size", "grp_keys") if cascade else ())
+        g["host"] = {k: torch.empty(g[k].shape, dtype=g[k].dtype, pin_memory=True) for k in keys}
         return g
+
+    def _share_groups(self, seqs) -> list[tuple[int, int, int]]:
+        """(first row, members, shared pages) of every run of >= 2 consecutive sequences that share prompt
+        pages, cut into items of at most 32 / (query heads per kv head) members."""
+        gmax = max(1, 32 // max(1, self.cfg.num_attention_heads // self.cfg.num_key_value_heads))
+        out, i, n = [], 0, len(seqs)
+        while i < n:
+            s = seqs[i]
+            j = i + 1
+            if s.shared_pages > 0:
+                while j < n and seqs[j].share_key == s.share_key and seqs[j].shared_pages == s.shared_pages:
+                    j += 1
+            if j - i >= 2:
+                for a in range(i, j, gmax):
+                    if min(j, a + gmax) - a >= 2:
+                        out.append((a, min(j, a + gmax) - a, s.shared_pages))
+            i = j
+        return out
 
     def _decode_graph(self, seqs) -> tuple[list, list]:
         B = len(seqs)
         bucket = next((b for b in self.graph_buckets if b >= B), None)
         if bucket is None:
             bucket = (B + 63) // 64 * 64
-        g = self._graphs.get(bucket)
+        groups = self._share_groups(seqs) if (self.share_prompts and self.cascade_attention) else []
+        cascade = bool(groups)
+        g = self._graphs.get((bucket, cascade))
         if g is None:
-            g = self._graphs[bucket] = self._capture(bucket)
+            g = self._graphs[(bucket, cascade)] = self._capture(bucket, cascade)
         h = g["host"]
         h["tokens"].zero_(); h["pos"].zero_(); h["lens"].zero_(); h["bt"].fill_(-1)
         h["temp"].fill_(1.0); h["top_k"].zero_(); h["top_p"].fill_(1.0); h["ctr"].zero_()
+        if cascade:
+            for k in ("seq_page0", "seq_keys", "grp_first", "grp_size", "grp_keys"):
+                h[k].zero_()
+            p0, ky = h["seq_page0"].numpy(), h["seq_keys"].numpy()
+            for i, s in enumerate(seqs):
+                ky[i] = s.length + 1
+            gf, gs, gk = h["grp_first"].numpy(), h["grp_size"].numpy(), h["grp_keys"].numpy()
+            for n, (a, m, sh) in enumerate(groups):
+                gf[n], gs[n], gk[n] = a, m, sh * PAGE
+                p0[a:a + m] = sh
+                ky[a:a + m] -= sh * PAGE
         tok, pos, lens, bt = h["tokens"].numpy(), h["pos"].numpy(), h["lens"].numpy(), h["bt"].numpy()
         temp, tk, tp, ctr = h["temp"].numpy(), h["top_k"].numpy(), h["top_p"].numpy(), h["ctr"].numpy()
         for i, s in enumerate(seqs):
@@ -339,6 +385,7 @@ class GenerationEngine:
         s = self.running.pop()
         self.cache.release(s.pages)
         s.pages, s.length = [], 0
+        s.share_key, s.shared_pages = -1, 0
         self.waiting.appendleft(s)
         self.stats["preempted"] += 1
 

@@ -158,12 +158,19 @@ class TrainerWorker(Worker, DistProfilerExtension):
         self.engine = PolicyEngine(self.model, ocfg, process_group=self.pg,
                                    max_token_len_per_gpu=int(_get(cfg, "max_token_len_per_gpu", 16384)) * self.ulysses_sequence_parallel_size,
                                    temperature=1.0)
+        if bool(_get(cfg, "fsdp.enable_activation_offload", False)) and not self._forward_only:
+            from ..utils.activation_offload import ActivationOffloader
+            target = getattr(self.model, "inner", self.model)
+            target.offloader = ActivationOffloader(self.device)
         self.flops_counter = FlopsCounter(self.model.cfg, dtype)
-        self.state_manager = FSDPStateManager(self.model, self.engine, processing_class=self.tokenizer, rank=self.rank,
-                                              world_size=self.world_size, process_group=self.pg)
+        self.state_manager = self._make_state_manager()
         if self._is_offload_param:
             self.offload_model(include_model=True, include_optimizer=False)
         return {"num_params": int(self.model.params.numel), "device": str(self.device), "dtype": str(dtype)}
+
+    def _make_state_manager(self):
+        return FSDPStateManager(self.model, self.engine, processing_class=self.tokenizer, rank=self.rank,
+                                world_size=self.world_size, process_group=self.pg)
 
     def _build(self, model_path, dtype, seed):
         from ..models.config import get_config

@@ -67,6 +67,15 @@ class TrainerWorker(_Base):
                 dp_group = g
         return tp_group, dp_group
 
+    def _make_state_manager(self):
+        mp = max(self.tp_size, self.ep_size)
+        if mp == 1:
+            return super()._make_state_manager()
+        from ..utils.state.megatron_state_manager import MegatronStateManager
+        return MegatronStateManager(self.model, self.engine, mp_group=getattr(self, "_mp_group", None), tp=self.tp_size, ep=self.ep_size,
+                                    dp_rank=self.rank // mp, processing_class=self.tokenizer, rank=self.rank,
+                                    world_size=self.world_size, process_group=self.pg)
+
     def _build_expert_parallel(self, model_path, dtype, seed):
         import os
         from ..models.config import get_config
@@ -78,6 +87,7 @@ class TrainerWorker(_Base):
         assert self.world_size % self.ep_size == 0, f"world size {self.world_size} not divisible by ep {self.ep_size}"
         ep_group, edp_group = self._make_groups(self.ep_size)
         self.pg = edp_group
+        self._mp_group = ep_group
         cap = int(_get(self.config, "max_token_len_per_gpu", 16384))
         ctx = EPContext(ep_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size,
                         max_tokens=(cap + 127) // 128 * 128, top_k=mcfg.num_experts_per_tok)
@@ -105,6 +115,7 @@ class TrainerWorker(_Base):
         mcfg = get_config(model_path)
         tp_group, dp_group = self._make_groups()
         self.pg = dp_group                          # the optimizer shards over the data-parallel group
+        self._mp_group = tp_group
         rows = int(_get(self.config, "max_token_len_per_gpu", 16384))
         rows = (rows // self.tp_size + 127) // 128 * 128 + 128
         width = max(mcfg.qkv_size, 2 * mcfg.intermediate_size, mcfg.hidden_size) // 1

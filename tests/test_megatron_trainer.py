@@ -28,7 +28,7 @@ def _batch(n_rows=4, T=48, vocab=4096):
     return d
 
 
-def _run(cls_path, cfg, world, vocab=4096):
+def _run(cls_path, cfg, world, vocab=4096, save_dir=None):
     import importlib
     mod, name = cls_path.rsplit(".", 1)
     cls = getattr(importlib.import_module(mod), name)
@@ -44,6 +44,9 @@ def _run(cls_path, cfg, world, vocab=4096):
         out1 = wg.forward_backward(data, loss_fn="ppo", loss_fn_args={"clip_ratio": 0.2})
         opt1 = wg.optim_step(step_lr=True)
         fwd2 = wg.forward(data)
+        if save_dir is not None:
+            wg.save_state(save_dir, global_step=1, save_mode="both")
+            wg.wait_for_save()
         return fwd.batch["log_probs"], out1.meta_info["metrics"], opt1.meta_info["metrics"], fwd2.batch["log_probs"]
     finally:
         wg.shutdown()
@@ -74,3 +77,29 @@ def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
     assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("kind", ["tp", "ep"])
+def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
+    """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
+    run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
+    import json
+    import os
+    from axon_b200.models.config import get_config
+    from axon_b200.models.dense import PackedBatch
+    from axon_b200.models.moe import build_model_for
+    from axon_b200.utils.hf_model import load_hf_weights
+    preset, vocab = ("tiny-qwen3", 4096) if kind == "tp" else ("tiny-moe", 2048)
+    cfg = _cfg(2 if kind == "tp" else 1, preset, 2 if kind == "ep" else 1)
+    d = str(tmp_path / "ck")
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, 2, vocab=vocab, save_dir=d)
+    assert json.load(open(os.path.join(d, "model_parallel_config.json")))["world_size"] == 2
+    assert os.path.exists(os.path.join(d, "model_world_size_2_rank_1.pt")) and os.path.exists(os.path.join(d, "optim_world_size_2_rank_0.pt"))
+    m = build_model_for(get_config(preset), device="cpu", dtype=torch.float32)
+    load_hf_weights(m, os.path.join(d, "huggingface"))
+    data = _batch(vocab=vocab)
+    for row in range(2):
+        n = int(data.batch["attention_mask"][row].sum())
+        lp, _ = m.forward(PackedBatch.from_sequences([data.batch["input_ids"][row, :n].to(torch.int32)], "cpu"))
+        torch.testing.assert_close(lp[: n - 1], got[3][row, 1:n].float(), rtol=2e-3, atol=2e-3)

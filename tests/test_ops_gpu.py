@@ -244,3 +244,56 @@ def test_sampling_distribution_and_logprobs():
         top = ref_lp[b].argmax()
         pr = ref_lp[b, top].exp().item()
         assert abs(counts[b, top].item() / n_draws - pr) < 4 * (pr * (1 - pr) / n_draws) ** 0.5 + 0.02
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (8, 1), (4, 4)])
+def test_paged_decode_shared_prefix_matches_plain_decode(Hq, Hkv):
+    """Decode attention over a batch with shared prompt pages (one prefix item per group + a suffix item per
+    sequence + merge) against the fp32 reference and the plain kernel; padded rows give zeros."""
+    from axon_b200.ops import paged as P
+    torch.manual_seed(11)
+    D = 128
+    rep = Hq // Hkv
+    gmax = 32 // rep
+    # (members, shared pages, private lengths)
+    groups = [(min(8, gmax), 3, [5, 130, 128, 1, 300, 77, 256, 129]), (1, 0, [200]), (min(3, gmax), 1, [1, 64, 129]), (1, 0, [128])]
+    rows, items = [], []
+    page = 0
+    for members, shared, priv in groups:
+        shared_pages = list(range(page, page + shared)); page += shared
+        first = len(rows)
+        for m in range(members):
+            n_priv = (priv[m] + 127) // 128
+            rows.append((shared_pages + list(range(page, page + n_priv)), shared * 128 + priv[m], shared))
+            page += n_priv
+        if members >= 2:
+            items.append((first, members, shared))
+    B, Bpad = len(rows), len(rows) + 3                 # three padded rows, as in a graph bucket
+    num_pages = page + 2
+    max_pages = max(len(r[0]) for r in rows) + 1
+    bt = torch.full((Bpad, max_pages), -1, dtype=torch.int32)
+    sl = torch.zeros(Bpad, dtype=torch.int32)
+    for b, (pg, n, _) in enumerate(rows):
+        bt[b, :len(pg)] = torch.tensor(pg, dtype=torch.int32)
+        sl[b] = n
+    kc, vc = bf(num_pages, Hkv, 128, D, scale=0.7), bf(num_pages, Hkv, 128, D, scale=0.7)
+    q = bf(Bpad, (Hq + 2 * Hkv) * D, scale=0.7)
+    ng = max(1, Bpad // 2)
+    z = lambda n: torch.zeros(n, dtype=torch.int32)     # noqa: E731
+    sh = dict(seq_first=torch.arange(Bpad, dtype=torch.int32), seq_one=torch.ones(Bpad, dtype=torch.int32), seq_page0=z(Bpad),
+              seq_keys=sl.clone(), grp_first=z(ng), grp_size=z(ng), grp_zero=z(ng), grp_keys=z(ng))
+    for n, (a, m, s) in enumerate(items):
+        sh["grp_first"][n], sh["grp_size"][n], sh["grp_keys"][n] = a, m, s * 128
+        sh["seq_page0"][a:a + m] = s
+        sh["seq_keys"][a:a + m] -= s * 128
+    ref = P.paged_decode(q, kc, vc, bt, sl, Hq, Hkv, D)
+    qg, kg, vg = q.cuda(), kc.cuda(), vc.cuda()
+    plain = P.paged_decode(qg, kg, vg, bt.cuda(), sl.cuda(), Hq, Hkv, D)
+    shg = {k: v.cuda() for k, v in sh.items()}
+    shg["max_shared_pages"] = 4
+    got = P.paged_decode_shared(qg, kg, vg, bt.cuda(), sl.cuda(), shg, Hq, Hkv, D)
+    C.check_status()
+    close(got[:B], ref[:B], 2e-2)
+    close(got[:B], plain[:B], 2e-2)
+    assert float(got[B:].abs().max()) == 0.0
