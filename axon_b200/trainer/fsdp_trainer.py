@@ -169,6 +169,7 @@ class TrainerWorker(Worker, DistProfilerExtension):
         return {"num_params": int(self.model.params.numel), "device": str(self.device), "dtype": str(dtype)}
 
     def _make_state_manager(self):
+        from ..utils.state import FSDPStateManager
         return FSDPStateManager(self.model, self.engine, processing_class=self.tokenizer, rank=self.rank,
                                 world_size=self.world_size, process_group=self.pg)
 
