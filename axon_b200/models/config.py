@@ -139,7 +139,12 @@ def tiny_moe_gpu() -> ModelConfig:
 
 
 PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen3-30b-a3b": qwen3_30b_a3b,
-           "tiny-qwen3": tiny_qwen3, "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
+           "tiny-qwen3": tiny_qwen3, "tiny-qwen3-untied": lambda: _untied(tiny_qwen3()), "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
+
+
+def _untied(cfg: ModelConfig) -> ModelConfig:
+    cfg.tie_word_embeddings = False
+    return cfg
 
 
 def get_config(name_or_path: str) -> ModelConfig:

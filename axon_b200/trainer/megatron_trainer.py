@@ -14,8 +14,11 @@ reach their experts through peer memory (``parallel/ep.py``). Non-expert gradien
 expert-parallel group and then reduced with the expert gradients over the strided "expert data
 parallel" group, which is also the group the optimizer state is sharded over.
 
-Pipeline and context parallel sizes other than 1, and tensor x expert parallelism together, are
-refused with an explicit error until their schedules land here.
+Pipeline parallelism (``pipeline_model_parallel_size``, alone): stage groups of consecutive ranks,
+``models/pp_dense.py`` (send / recv between stages, micro-batches one after another).
+
+A context-parallel size other than 1, and combinations of two model-parallel dimensions, are refused
+with an explicit error until their schedules land here.
 """
 from __future__ import annotations
 
@@ -33,7 +36,11 @@ class TrainerWorker(_Base):
         if self.ep_size > 1 and self.tp_size > 1:
             raise NotImplementedError("tensor and expert parallelism together are not available in this trainer yet; "
                                       "use one of megatron.tensor_model_parallel_size / expert_model_parallel_size")
-        for key, label in (("pipeline_model_parallel_size", "pipeline"), ("context_parallel_size", "context")):
+        self.pp_size = int(_get(m, "pipeline_model_parallel_size", 1) or 1)
+        if self.pp_size > 1 and (self.tp_size > 1 or self.ep_size > 1):
+            raise NotImplementedError("pipeline parallelism together with tensor / expert parallelism is not available in this "
+                                      "trainer yet; use one model-parallel dimension")
+        for key, label in (("context_parallel_size", "context"),):
             if int(_get(m, key, 1) or 1) != 1:
                 raise NotImplementedError(f"{label} parallelism > 1 is not available in this trainer yet "
                                           f"(megatron.{key}={_get(m, key)}); use tensor and data parallelism")
@@ -44,8 +51,9 @@ class TrainerWorker(_Base):
     def _register_dispatch_collect_info(self, mesh_name: str, dp_rank: int, is_collect: bool) -> None:
         if mesh_name == "trainer" and getattr(self, "_pending_dispatch", False):
             self._pending_dispatch = False
-            assert self.world_size % self.tp_size == 0, f"world size {self.world_size} not divisible by tp {self.tp_size}"
-            return super()._register_dispatch_collect_info(mesh_name, self.rank // self.tp_size, self.rank % self.tp_size == 0)
+            mp = max(self.tp_size, self.pp_size)          # ranks of one tensor- / pipeline-parallel group see the same rows
+            assert self.world_size % mp == 0, f"world size {self.world_size} not divisible by the model-parallel size {mp}"
+            return super()._register_dispatch_collect_info(mesh_name, self.rank // mp, self.rank % mp == 0)
         return super()._register_dispatch_collect_info(mesh_name, dp_rank, is_collect)
 
     def _make_groups(self, tp: int | None = None):
@@ -67,13 +75,34 @@ class TrainerWorker(_Base):
                 dp_group = g
         return tp_group, dp_group
 
+    def _build_pipeline_parallel(self, model_path, dtype, seed):
+        import os
+        from ..models.config import get_config
+        from ..models.params import FlatParams
+        from ..models.pp_dense import PipelineContext, PPDenseModel
+        from ..utils.hf_model import has_hf_weights, iter_hf_weights
+        mcfg = get_config(model_path)
+        assert self.world_size % self.pp_size == 0, f"world size {self.world_size} not divisible by pp {self.pp_size}"
+        assert not self.model_kind.value_head, "value-head models are not pipeline-parallel yet; run the critic with pp=1"
+        pp_group, dp_group = self._make_groups(self.pp_size)
+        self.pg, self._mp_group = dp_group, pp_group
+        model = PPDenseModel(mcfg, PipelineContext(pp_group, self.device), device=self.device, dtype=dtype)
+        ref = FlatParams(mcfg, "cpu", dtype)                 # full model on the host, cut down to this stage
+        if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+        else:
+            ref.init_random(seed=seed)
+        model.load_full_state(ref.views)
+        model.recompute = str(_get(self.config, "recompute", "selective"))
+        return model
+
     def _make_state_manager(self):
-        mp = max(self.tp_size, self.ep_size)
+        mp = max(self.tp_size, self.ep_size, self.pp_size)
         if mp == 1:
             return super()._make_state_manager()
         from ..utils.state.megatron_state_manager import MegatronStateManager
         return MegatronStateManager(self.model, self.engine, mp_group=getattr(self, "_mp_group", None), tp=self.tp_size, ep=self.ep_size,
-                                    dp_rank=self.rank // mp, processing_class=self.tokenizer, rank=self.rank,
+                                    pp=self.pp_size, dp_rank=self.rank // mp, processing_class=self.tokenizer, rank=self.rank,
                                     world_size=self.world_size, process_group=self.pg)
 
     def _build_expert_parallel(self, model_path, dtype, seed):
@@ -103,6 +132,8 @@ class TrainerWorker(_Base):
         return model
 
     def _build(self, model_path, dtype, seed):
+        if self.pp_size > 1:
+            return self._build_pipeline_parallel(model_path, dtype, seed)
         if self.ep_size > 1:
             return self._build_expert_parallel(model_path, dtype, seed)
         if self.tp_size == 1:

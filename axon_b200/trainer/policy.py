@@ -111,7 +111,7 @@ class PolicyEngine:
         self.state = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._host_state: dict | None = None
         self.fused = None
-        mp = getattr(model, "tp", None) or getattr(model, "ep", None)
+        mp = getattr(model, "tp", None) or getattr(model, "ep", None) or getattr(model, "pp", None)
         ep = getattr(model, "ep", None)
         self.micro_group = ep.group if (ep is not None and ep.world > 1) else None      # ranks that must run equal micro-batch counts
         if fused_zero1 is None:
@@ -351,10 +351,10 @@ class PolicyEngine:
         return {"grad_norm": st[1], "lr": lr, "skipped": st[3]}
 
     def _tensor_parallel_norm(self, grad_shard: torch.Tensor, lo: int) -> None:
-        """With a tensor- or expert-parallel model the squared norm is the sum over the TP ranks of their sharded
+        """With a tensor-, expert- or pipeline-parallel model the squared norm is the sum over the TP ranks of their sharded
         parameters plus the replicated parameters ONCE: sum_r S_r - (W - 1) * rep, where S_r is rank r's
         full-buffer value and rep the replicated part (equal on every rank)."""
-        tp = getattr(self.model, "tp", None) or getattr(self.model, "ep", None)     # model-parallel group of either kind
+        tp = getattr(self.model, "tp", None) or getattr(self.model, "ep", None) or getattr(self.model, "pp", None)   # model-parallel group of any kind
         if tp is None or tp.world == 1:
             return
         rep = torch.zeros(1, dtype=torch.float32, device=self.device)

@@ -53,9 +53,9 @@ def gather_full_params(model, group, tp: int = 1, tp_rank: int = 0, ep: int = 1,
 
 
 class MegatronStateManager(FSDPStateManager):
-    def __init__(self, model, optimizer, mp_group=None, tp: int = 1, ep: int = 1, dp_rank: int = 0, **kw):
+    def __init__(self, model, optimizer, mp_group=None, tp: int = 1, ep: int = 1, pp: int = 1, dp_rank: int = 0, **kw):
         super().__init__(model, optimizer, **kw)
-        self.mp_group, self.tp, self.ep, self.dp_rank = mp_group, tp, ep, dp_rank
+        self.mp_group, self.tp, self.ep, self.pp, self.dp_rank = mp_group, tp, ep, pp, dp_rank
 
     def _mp_rank(self) -> int:
         return dist.get_rank(self.mp_group) if self.mp_group is not None else 0
@@ -69,12 +69,18 @@ class MegatronStateManager(FSDPStateManager):
         super().save_state(local_path, global_step, max_ckpt_to_keep, "sharded", async_save)
         if self.rank == 0:
             with open(os.path.join(local_path, "model_parallel_config.json"), "w") as f:
-                json.dump({"tensor_model_parallel_size": self.tp, "expert_model_parallel_size": self.ep, "world_size": self.world_size}, f, indent=1)
+                json.dump({"tensor_model_parallel_size": self.tp, "expert_model_parallel_size": self.ep,
+                           "pipeline_model_parallel_size": self.pp, "world_size": self.world_size}, f, indent=1)
         if want_hf and self.dp_rank == 0:
             inner = getattr(self.model, "inner", self.model)
             rep = inner.replicated_names() if hasattr(inner, "replicated_names") else ()
             r = self._mp_rank()
-            full = gather_full_params(inner, self.mp_group, self.tp, r if self.tp > 1 else 0, self.ep, r if self.ep > 1 else 0, rep)
+            if self.pp > 1:            # stages hold disjoint parameters: collect them by name
+                stages = [None] * self.pp
+                dist.all_gather_object(stages, {n: v.detach().cpu() for n, v in inner.params.views.items()}, group=self.mp_group)
+                full = {n: v for d in stages for n, v in d.items()}
+            else:
+                full = gather_full_params(inner, self.mp_group, self.tp, r if self.tp > 1 else 0, self.ep, r if self.ep > 1 else 0, rep)
             if r == 0:
                 from ...models.params import FlatParams
                 from ..hf_model import save_hf_model
@@ -88,7 +94,8 @@ class MegatronStateManager(FSDPStateManager):
         if local_path and os.path.exists(cfg_file):
             with open(cfg_file) as f:
                 c = json.load(f)
-            assert (c["tensor_model_parallel_size"], c["expert_model_parallel_size"], c["world_size"]) == (self.tp, self.ep, self.world_size), \
-                f"checkpoint was written with layout {c}, this run has tp={self.tp} ep={self.ep} world={self.world_size}; " \
+            assert (c["tensor_model_parallel_size"], c["expert_model_parallel_size"], c.get("pipeline_model_parallel_size", 1),
+                    c["world_size"]) == (self.tp, self.ep, self.pp, self.world_size), \
+                f"checkpoint was written with layout {c}, this run has tp={self.tp} ep={self.ep} pp={self.pp} world={self.world_size}; " \
                 f"load its huggingface/ export instead"
         return super().load_state(local_path, "sharded")

@@ -8,10 +8,10 @@ from axon_b200.core.resource_pool import ResourcePool
 from axon_b200.protocol import DataProto
 
 
-def _cfg(tp, model="tiny-qwen3", ep=1):
+def _cfg(tp, model="tiny-qwen3", ep=1, pp=1):
     return {"model_path": model, "force_cpu": True, "seed": 7, "max_token_len_per_gpu": 512,
             "optimizer_args": {"lr": 1e-3, "weight_decay": 0.0, "betas": [0.9, 0.95], "eps": 1e-8}, "grad_clip": 1.0,
-            "megatron": {"tensor_model_parallel_size": tp, "expert_model_parallel_size": ep}, "recompute": "full"}
+            "megatron": {"tensor_model_parallel_size": tp, "expert_model_parallel_size": ep, "pipeline_model_parallel_size": pp}, "recompute": "full"}
 
 
 def _batch(n_rows=4, T=48, vocab=4096):
@@ -80,7 +80,7 @@ def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["tp", "ep"])
+@pytest.mark.parametrize("kind", ["tp", "ep", "pp"])
 def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
     run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
@@ -90,8 +90,8 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     from axon_b200.models.dense import PackedBatch
     from axon_b200.models.moe import build_model_for
     from axon_b200.utils.hf_model import load_hf_weights
-    preset, vocab = ("tiny-qwen3", 4096) if kind == "tp" else ("tiny-moe", 2048)
-    cfg = _cfg(2 if kind == "tp" else 1, preset, 2 if kind == "ep" else 1)
+    preset, vocab = ("tiny-moe", 2048) if kind == "ep" else ("tiny-qwen3-untied", 4096)
+    cfg = _cfg(2 if kind == "tp" else 1, preset, 2 if kind == "ep" else 1, 2 if kind == "pp" else 1)
     d = str(tmp_path / "ck")
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, 2, vocab=vocab, save_dir=d)
     assert json.load(open(os.path.join(d, "model_parallel_config.json")))["world_size"] == 2
@@ -103,3 +103,17 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
         n = int(data.batch["attention_mask"][row].sum())
         lp, _ = m.forward(PackedBatch.from_sequences([data.batch["input_ids"][row, :n].to(torch.int32)], "cpu"))
         torch.testing.assert_close(lp[: n - 1], got[3][row, 1:n].float(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world,pp", [(2, 2), (4, 2)])
+def test_pipeline_parallel_trainer_matches_data_parallel_trainer(world, pp):
+    """Two pipeline stages (x dp=1 or 2): same log-probs, gradient norm and update as the single-process trainer."""
+    import numpy as np
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied"), 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied", pp=pp), world)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
