@@ -82,7 +82,8 @@ def paged_decode_shared(qkv_r, kcache, vcache, block_table, seq_lens, shared: di
     max_pages = block_table.shape[1]
     n_groups = shared["grp_first"].numel()
     ns = lib.axb_paged_decode_splits(B, Hkv, max_pages)
-    nsp = lib.axb_paged_decode_splits(n_groups, Hkv, int(shared.get("max_shared_pages", 8)))
+    # splits of the prefix items: sized for the usual group count (8 samples per prompt), not for the array length
+    nsp = lib.axb_paged_decode_splits(int(shared.get("typical_groups", max(1, B // 8))), Hkv, int(shared.get("max_shared_pages", 8)))
     scratch = C.workspace(qkv_r.device, B * Hq * (ns + nsp) * (D + 2) * 4, "paged")
     out = torch.empty(B, Hq * D, dtype=qkv_r.dtype, device=qkv_r.device)
     rc = lib.axb_paged_decode_shared(C.ptr(qkv_r), ctypes.c_longlong(qkv_r.stride(0)), C.ptr(kcache), C.ptr(vcache), kcache.shape[0],

@@ -100,6 +100,50 @@ def case_paged_decode(small):
     return (lambda: P.paged_decode(q, kc, vc, bt, lens, Hq, Hkv, D)), dict(flops=4.0 * B * ctx * Hq * D, bytes=4.0 * B * ctx * Hkv * D, shape=[B, ctx])
 
 
+def _grpo_decode_batch(small):
+    """B sequences = groups of 8 samples sharing a 1024-token prompt (8 pages), each with a private tail."""
+    B, shared, tail, Hq, Hkv, D = (64, 8, 300, 32, 8, 128) if small else (256, 8, 500, 32, 8, 128)
+    tail_pages = (tail + 127) // 128
+    n_groups = B // 8
+    n_pages = n_groups * shared + B * tail_pages
+    kc, vc = bf(n_pages, Hkv, 128, D, scale=0.3), bf(n_pages, Hkv, 128, D, scale=0.3)
+    perm = torch.randperm(n_pages).to(torch.int32)
+    bt = torch.full((B, shared + tail_pages + 1), -1, dtype=torch.int32)
+    for b in range(B):
+        g = b // 8
+        bt[b, :shared] = perm[g * shared:(g + 1) * shared]
+        o = n_groups * shared + b * tail_pages
+        bt[b, shared:shared + tail_pages] = perm[o:o + tail_pages]
+    lens = torch.full((B,), shared * 128 + tail, dtype=torch.int32, device="cuda")
+    q = bf(B, (Hq + 2 * Hkv) * D, scale=0.3)
+    return B, shared, tail, Hq, Hkv, D, kc, vc, bt.cuda(), lens, q
+
+
+def case_paged_decode_grpo_plain(small):
+    """The plain decode kernel on a GRPO-shaped batch (every sample streams the shared prompt pages itself)."""
+    from ...ops import paged as P
+    B, shared, tail, Hq, Hkv, D, kc, vc, bt, lens, q = _grpo_decode_batch(small)
+    ctx = shared * 128 + tail
+    return (lambda: P.paged_decode(q, kc, vc, bt, lens, Hq, Hkv, D)), dict(flops=4.0 * B * ctx * Hq * D, bytes=4.0 * B * ctx * Hkv * D, shape=[B, ctx])
+
+
+def case_paged_decode_grpo_shared(small):
+    """Shared-prefix decode attention on the same batch: prompt pages once per group of 8, tails per sequence."""
+    from ...ops import paged as P
+    B, shared, tail, Hq, Hkv, D, kc, vc, bt, lens, q = _grpo_decode_batch(small)
+    ng = B // 2
+    zi = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")      # noqa: E731
+    sh = dict(seq_first=torch.arange(B, dtype=torch.int32, device="cuda"), seq_one=torch.ones(B, dtype=torch.int32, device="cuda"),
+              seq_page0=torch.full((B,), shared, dtype=torch.int32, device="cuda"), seq_keys=torch.full((B,), tail, dtype=torch.int32, device="cuda"),
+              grp_first=zi(ng), grp_size=zi(ng), grp_zero=zi(ng), grp_keys=zi(ng), max_shared_pages=shared)
+    sh["grp_first"][: B // 8] = torch.arange(0, B, 8, dtype=torch.int32, device="cuda")
+    sh["grp_size"][: B // 8] = 8
+    sh["grp_keys"][: B // 8] = shared * 128
+    ctx = shared * 128 + tail
+    unique = (B // 8) * shared * 128 + B * tail          # keys that have to be read at least once
+    return (lambda: P.paged_decode_shared(q, kc, vc, bt, lens, sh, Hq, Hkv, D)), dict(flops=4.0 * B * ctx * Hq * D, bytes=4.0 * unique * Hkv * D, shape=[B, ctx])
+
+
 def case_lmhead_fwd(small):
     from ...ops import lm_head as L
     T, H, V = (1024, 4096, 151936) if small else (8192, 4096, 151936)
@@ -179,7 +223,8 @@ def case_moe_grouped(small):
 
 
 CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode,
-         "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode,
+         "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode, "paged_decode_grpo_plain": case_paged_decode_grpo_plain,
+         "paged_decode_grpo_shared": case_paged_decode_grpo_shared,
          "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "gemm_ag": case_gemm_ag,
          "gemm_rs": case_gemm_rs, "moe_grouped": case_moe_grouped}
 
