@@ -66,6 +66,7 @@ class GenerationEngine:
         self.use_cuda_graph = self.device.type == "cuda"
         self.share_prompts = True          # n samples of one prompt share its KV pages and its prefill
         self.cascade_attention = True      # ... and decode attends to the shared pages once per group
+        self.cascade_min_batch = 48
         self._graphs: dict[int, dict] = {}
         # batch-size buckets of the captured graphs: the decode GEMM's token width is a run-time value, so
         # finer buckets than powers of two pay off as the batch drains
@@ -305,7 +306,8 @@ class GenerationEngine:
         bucket = next((b for b in self.graph_buckets if b >= B), None)
         if bucket is None:
             bucket = (B + 63) // 64 * 64
-        groups = self._share_groups(seqs) if (self.share_prompts and self.cascade_attention) else []
+        # below this batch size the extra prefix / merge launches cost more than the shared pages save
+        groups = self._share_groups(seqs) if (self.share_prompts and self.cascade_attention and B >= self.cascade_min_batch) else []
         cascade = bool(groups)
         g = self._graphs.get((bucket, cascade))
         if g is None:

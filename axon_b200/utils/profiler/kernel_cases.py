@@ -62,6 +62,48 @@ def case_gemm_decode(small):
     return run, dict(flops=2.0 * M * N * K, bytes=2.0 * (M * K + N * K + M * N), shape=[M, N, K])
 
 
+def case_gemm_stream(small):
+    """Weight-streaming decode GEMM (64 tokens x 6144 features x K 4096), weights rotated so that they come from HBM."""
+    from ...ops import gemm as G
+    M, N, K = 64, 6144, 4096
+    a = bf(M, K)
+    ws = [bf(N, K) for _ in range(3 if small else 8)]
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    st = {"i": 0}
+
+    def run():
+        st["i"] = (st["i"] + 1) % len(ws)
+        G.gemm_nt(a, ws[st["i"]], out=out)
+    return run, dict(flops=2.0 * M * N * K, bytes=2.0 * (M * K + N * K + M * N), shape=[M, N, K])
+
+
+def case_gemm_decode_chain(small):
+    """The four projections of a Qwen3-8B layer at decode batch 64, 8 layers' worth of distinct weights (3 GB, so L2
+    is cold for weights by construction), replayed as one CUDA graph: the per-launch figure is per LAYER
+    (qkv + o + gate_up + down = 385 MB of weights); launch gaps and dependent-launch overlap are included."""
+    from ...ops import gemm as G
+    L, M = (2, 64) if small else (8, 64)
+    shapes = [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)]
+    Ws = [[bf(n, k, scale=0.02) for (n, k) in shapes] for _ in range(L)]
+    xs = [bf(M, k) for (_, k) in shapes]
+    outs = [torch.empty(M, n, device="cuda", dtype=torch.bfloat16) for (n, _) in shapes]
+
+    def body():
+        for l in range(L):
+            for i in range(4):
+                G.gemm_nt(xs[i], Ws[l][i], out=outs[i])
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        body()
+        body()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    byts = sum(2.0 * n * k for n, k in shapes)
+    return (lambda: graph.replay()), dict(flops=2.0 * M * sum(n * k for n, k in shapes) * L, bytes=byts * L, shape=[M, L, "layers"])
+
+
 def _qkv(lens, Hq, Hkv, D=128):
     T = sum(lens)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
@@ -222,7 +264,8 @@ def case_moe_grouped(small):
                                                      shape=[T * k, 2 * F, H, E])
 
 
-CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode,
+CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode, "gemm_stream": case_gemm_stream,
+         "gemm_decode_chain": case_gemm_decode_chain,
          "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode, "paged_decode_grpo_plain": case_paged_decode_grpo_plain,
          "paged_decode_grpo_shared": case_paged_decode_grpo_shared,
          "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "gemm_ag": case_gemm_ag,

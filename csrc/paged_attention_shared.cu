@@ -12,9 +12,9 @@
 // merge kernel of the plain path combines a sequence's suffix splits and its prefix slot. A sequence
 // without a shared prefix gets neutral prefix slots from its suffix item.
 //
-// Tile pipeline: 3-stage TMA ring of 64 KB K|V page tiles; the S product of the next block runs under the
-// soft-max of the current one (S double-buffered in TMEM, P in shared memory); thread t owns key t for the
-// soft-max and output dimension t in the epilogue; the running maximum is raised lazily. Waits are bounded.
+// Same tile pipeline as paged_decode_kernel (3-stage TMA ring of 64 KB K|V page tiles, tcgen05 products,
+// thread t owns key t for the softmax and output dimension t in the epilogue; the running maximum is raised
+// lazily); waits are bounded.
 #include "ptx.cuh"
 #include "host_utils.h"
 
@@ -34,8 +34,7 @@ template <int NCOL>
 struct PsCfg {
   static constexpr int NPAD = NCOL <= 16 ? 16 : 32;                 // MMA N
   static constexpr int QBYTES = 2 * NPAD * 128;                      // [2 K-chunks][NPAD rows][64] bf16
-  static constexpr int TMEM_COLS = NPAD == 16 ? 64 : 128;            // S0 | S1 | O^T
-  static constexpr int SMEM = PS_STAGES * 2 * PS_TILE + 3 * QBYTES + 2 * 4 * NCOL * 4 + 256 + 1024;
+  static constexpr int SMEM = PS_STAGES * 2 * PS_TILE + 2 * QBYTES + 2 * 4 * NCOL * 4 + 256 + 1024;
 };
 
 // items: first[w] (batch index of the item's first sequence), size[w] (sequences, 0 = inactive), page0[w]
@@ -94,21 +93,19 @@ paged_decode_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
   uint8_t* sKV = smem;                                  // [stage][K 32K | V 32K]
   uint8_t* sQ = smem + PS_STAGES * 2 * PS_TILE;         // [2 chunks][NPAD rows][64] bf16
   uint8_t* sP = sQ + Cfg::QBYTES;
-  float* red = reinterpret_cast<float*>(sP + 2 * Cfg::QBYTES);   // [2][4 warps][NCOL]; sP is double-buffered
+  float* red = reinterpret_cast<float*>(sP + Cfg::QBYTES);   // [2][4 warps][NCOL]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(red) + 2 * 4 * NCOL * 4);
   uint64_t* full = bars;                                // [PS_STAGES]
-  uint64_t* bar_s = bars + PS_STAGES;                   // an S product is complete
-  uint64_t* bar_pv = bars + PS_STAGES + 1;              // a P*V product is complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PS_STAGES + 2);
+  uint64_t* bar_mma = bars + PS_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PS_STAGES + 1);
 
   if (tid == 0) {
     for (int s = 0; s < PS_STAGES; ++s) mbar_init(&full[s], 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_pv, 1);
+    mbar_init(bar_mma, 1);
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_alloc(tmem_slot, 2 * NPAD);
     tmem_relinquish();
   }
   // Q^T operand: row c = (sequence c / rep of the item, head c % rep of the kv group), zero padded to NPAD rows
@@ -123,8 +120,8 @@ paged_decode_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);   // + (i & 1) * NPAD: the S buffer of block i
-  const uint32_t tO = tS + 2 * NPAD;
+  const uint32_t tS = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t tO = tS + NPAD;
   constexpr uint32_t idesc_s = umma_idesc(128, NPAD, 0, 0);
   constexpr uint32_t idesc_o = umma_idesc(128, NPAD, 1, 0);
   const int* bt = block_table + (long long)b0 * max_pages + page0;
@@ -151,42 +148,37 @@ paged_decode_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
     l_thr[c] = 0.f;
   }
   bool ok = true;
-  // The S product of block i+1 is issued as soon as that of block i is complete, so it runs under the
-  // soft-max of block i; P*V of block i follows once its probabilities are in shared memory. S is double
-  // buffered in TMEM, P in shared memory. The running maximum is raised only when a block exceeds it by
-  // more than 2^8 (probabilities stay below 256, exact after the final normalisation), so the accumulator
-  // is rescaled on few blocks.
-  auto issue_s = [&](int i) {   // thread 0: S^T(i) = K(i) Q^T into S buffer i & 1
-    const int s = i % PS_STAGES;
-    if (!mbar_wait(&full[s], (i / PS_STAGES) & 1)) {
-      report_error(status, AXB_ERR_WAIT_FULL);
-      ok = false;
-      return;
-    }
-    tc_fence_after();
-    const uint32_t kaddr = smem_u32(sKV + s * 2 * PS_TILE), qaddr = smem_u32(sQ);
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      umma_f16_ss(tmem_base + (i & 1) * NPAD, umma_smem_desc(kaddr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                  umma_smem_desc(qaddr + (ks >> 2) * (NPAD * 128) + (ks & 3) * 32, 16, 1024), idesc_s, ks != 0);
-    }
-    tc_commit(bar_s);
-  };
-  if (tid == 0) issue_s(0);
-  __syncwarp();
+  uint32_t ph = 0;  // bar_mma completes once per block (after S) and once after the last P*V
   for (int i = 0; i < nb; ++i) {
-    if (ok && !mbar_wait(bar_s, i & 1)) {
+    const int s = i % PS_STAGES;
+    const uint32_t kaddr = smem_u32(sKV + s * 2 * PS_TILE);
+    if (tid == 0 && ok) {
+      if (!mbar_wait(&full[s], (i / PS_STAGES) & 1)) {
+        report_error(status, AXB_ERR_WAIT_FULL);
+        ok = false;
+      }
+      tc_fence_after();
+      const uint32_t qaddr = smem_u32(sQ);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        umma_f16_ss(tmem_base, umma_smem_desc(kaddr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                    umma_smem_desc(qaddr + (ks >> 2) * (NPAD * 128) + (ks & 3) * 32, 16, 1024), idesc_s, ks != 0);
+      }
+      tc_commit(bar_mma);  // also covers the P*V product of the previous block
+    }
+    __syncwarp();
+    if (ok && !mbar_wait(bar_mma, ph)) {
       report_error(status, AXB_ERR_WAIT_TMEM_FULL);
       ok = false;
     }
+    ph ^= 1;
     tc_fence_after();
-    if (tid == 0 && ok && i + 1 < nb) issue_s(i + 1);
-    __syncwarp();
+    // the stage of block i-1 is free now: prefetch block i + STAGES - 1 into it
+    if (tid == 0 && ok && i + PS_STAGES - 1 < nb) issue_load(i + PS_STAGES - 1);
 
     uint32_t sv[NPAD];
-    const uint32_t tSi = tS + (i & 1) * NPAD;
-    tmem_ld_32x16(tSi, sv);
-    if (NPAD == 32) tmem_ld_32x16(tSi + 16, sv + 16);
+    tmem_ld_32x16(tS, sv);
+    if (NPAD == 32) tmem_ld_32x16(tS + 16, sv + 16);
     tmem_ld_wait();
     const int kpos = (blk_begin + i) * PS_PAGE + tid;
     const bool valid = kpos < n_keys;
@@ -200,11 +192,12 @@ paged_decode_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
     __syncthreads();
     float alpha[NCOL];
     bool changed = false;
-    uint8_t* sPi = sP + (i & 1) * Cfg::QBYTES;
 #pragma unroll
     for (int c = 0; c < NCOL; ++c) {
       const float* r = red + (i & 1) * 4 * NCOL + c;
       const float bm = fmaxf(fmaxf(r[0], r[NCOL]), fmaxf(r[2 * NCOL], r[3 * NCOL]));
+      // the running maximum is raised only when a block exceeds it by more than 2^8: probabilities stay below
+      // 256 (exact after the final normalisation) and the accumulator is rescaled on few blocks
       const bool raise = bm > m_run[c] + 8.f;
       const float mn = raise ? bm : m_run[c];
       alpha[c] = raise ? exp2f(m_run[c] - mn) : 1.f;
@@ -213,17 +206,8 @@ paged_decode_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
       const float p = exp2f(sc[c] - mn);
       l_thr[c] = l_thr[c] * alpha[c] + p;
       if (c < ncols)
-        *reinterpret_cast<__nv_bfloat16*>(sPi + (tid >> 6) * (NPAD * 128) + ps_sw128(c, tid & 63)) = __float2bfloat16(p);
+        *reinterpret_cast<__nv_bfloat16*>(sP + (tid >> 6) * (NPAD * 128) + ps_sw128(c, tid & 63)) = __float2bfloat16(p);
     }
-    if (i > 0) {
-      // P*V of block i-1 is complete: the accumulator is stable and that block's stage is free
-      if (ok && !mbar_wait(bar_pv, (i - 1) & 1)) {
-        report_error(status, AXB_ERR_WAIT_TMEM_FULL);
-        ok = false;
-      }
-      tc_fence_after();
-    }
-    if (tid == 0 && ok && i + 2 < nb) issue_load(i + 2);
     if (i > 0 && changed) {  // uniform across the CTA: m_run is identical in every thread
       uint32_t o[NPAD];
       tmem_ld_32x16(tO, o);
@@ -246,18 +230,18 @@ paged_decode_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
     __syncthreads();
     if (tid == 0 && ok) {
       tc_fence_after();
-      const uint32_t vaddr = smem_u32(sKV + (i % PS_STAGES) * 2 * PS_TILE) + PS_TILE, paddr = smem_u32(sPi);
+      const uint32_t vaddr = kaddr + PS_TILE, paddr = smem_u32(sP);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        umma_f16_ss(tmem_base + 2 * NPAD, umma_smem_desc(vaddr + ks * 2048, 16384, 1024),
+        umma_f16_ss(tmem_base + NPAD, umma_smem_desc(vaddr + ks * 2048, 16384, 1024),
                     umma_smem_desc(paddr + (ks >> 2) * (NPAD * 128) + (ks & 3) * 32, 16, 1024), idesc_o,
                     (i | ks) != 0);
       }
-      tc_commit(bar_pv);
+      if (i == nb - 1) tc_commit(bar_mma);
     }
     __syncwarp();
   }
-  if (ok && !mbar_wait(bar_pv, (nb - 1) & 1)) {
+  if (ok && !mbar_wait(bar_mma, ph)) {
     report_error(status, AXB_ERR_WAIT_TMEM_FULL);
     ok = false;
   }
@@ -296,7 +280,7 @@ paged_decode_items_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    tmem_dealloc(tmem_base, 2 * NPAD);
   }
 }
 
