@@ -65,7 +65,11 @@ class GenerationEngine:
         # because the KV pool moves). Disabled on CPU.
         self.use_cuda_graph = self.device.type == "cuda"
         self.share_prompts = True          # n samples of one prompt share its KV pages and its prefill
-        self.cascade_attention = True      # ... and decode attends to the shared pages once per group
+        # Decode attention over the shared pages once per group (csrc/paged_attention_shared.cu). Off by default: with
+        # one CTA per SM the per-CTA start-up of the extra prefix / suffix items costs as much as the shared tiles
+        # save once responses are a few pages long (measured end to end); the kernel pays off for long shared
+        # prefixes with short tails and is kept selectable.
+        self.cascade_attention = False
         self.cascade_min_batch = 48
         self._graphs: dict[int, dict] = {}
         # batch-size buckets of the captured graphs: the decode GEMM's token width is a run-time value, so

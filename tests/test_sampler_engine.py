@@ -82,12 +82,13 @@ def test_preemption_eos_and_pause_cpu():
     assert out.token_ids == outs[0].token_ids
 
 
-def _shared_prompt_run(device, dtype, share):
+def _shared_prompt_run(device, dtype, share, cascade=False):
     torch.manual_seed(0)
     cfg = tiny_qwen3() if device == "cpu" else tiny_gpu()
     model = _make(cfg, device, dtype)
     eng = GenerationEngine(model, num_pages=40, max_num_seqs=16)
     eng.share_prompts = share
+    eng.cascade_attention, eng.cascade_min_batch = cascade, 1
     g = torch.Generator().manual_seed(5)
     base = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (256, 150, 7)]   # full pages only / partial tail / no full page
     prompts = [p for p in base for _ in range(4)]
@@ -120,3 +121,14 @@ def test_samples_of_one_prompt_share_its_pages_cpu():
 @pytest.mark.gpu
 def test_samples_of_one_prompt_share_its_pages_gpu():
     _check_shared("cuda", torch.bfloat16, 1e-5, exact=False)
+
+
+@pytest.mark.gpu
+def test_shared_prefix_attention_in_the_decode_graph_gpu():
+    """Decode graphs with the shared-prefix attention kernel give the same samples as the plain kernel."""
+    _, a = _shared_prompt_run("cuda", torch.bfloat16, True, cascade=True)
+    _, b = _shared_prompt_run("cuda", torch.bfloat16, True, cascade=False)
+    same = sum(int(ta == tb) for (ta, _), (tb, _) in zip(a, b))
+    assert same >= len(a) - 3, same
+    first = max(abs(la[0] - lb[0]) for (_, la), (_, lb) in zip(a, b))
+    assert first < 0.05, first
