@@ -188,9 +188,14 @@ class PolicyEngine:
         cur = torch.cuda.current_stream(self.device)
         dst = {k: torch.empty(v.shape, dtype=v.dtype, device=self.device) for k, v in self._host_state.items()}   # allocated on the compute stream
         self._load_stream.wait_stream(cur)
+        # 32 MiB pieces: the host-to-device copy engine is shared with the per-micro-batch input copies of the
+        # compute stream, which would otherwise queue behind one multi-gigabyte transfer
+        piece = (32 << 20) // 4
         with torch.cuda.stream(self._load_stream):
             for k, v in self._host_state.items():
-                dst[k].copy_(v, non_blocking=True)
+                d, h = dst[k].view(-1), v.view(-1)
+                for a in range(0, h.numel(), piece):
+                    d[a:a + piece].copy_(h[a:a + piece], non_blocking=True)
                 dst[k].record_stream(self._load_stream)
         self._load_event = torch.cuda.Event()
         self._load_event.record(self._load_stream)
