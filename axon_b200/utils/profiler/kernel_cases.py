@@ -104,6 +104,27 @@ def case_gemm_decode_chain(small):
     return (lambda: graph.replay()), dict(flops=2.0 * M * sum(n * k for n, k in shapes) * L, bytes=byts * L, shape=[M, L, "layers"])
 
 
+def case_train_microbatch(small):
+    """One training micro-batch (forward + backward) of the dense model: Qwen3-8B on 8192 packed tokens (``--small``:
+    the tiny GPU preset on 1024 tokens), random weights, activations kept (recompute "none")."""
+    from ...models.config import get_config
+    from ...models.dense import DenseModel, PackedBatch
+    cfg = get_config("tiny-gpu" if small else "qwen3-8b")
+    model = DenseModel(cfg, device="cuda")
+    model.params.init_random(seed=0)
+    model.recompute = "none"
+    model.params.alloc_grads()
+    g = torch.Generator().manual_seed(0)
+    lens = (320, 256, 288, 160) if small else (2560, 2048, 2304, 1280)
+    batch = PackedBatch.from_sequences([torch.randint(0, cfg.vocab_size, (n,), generator=g, dtype=torch.int32) for n in lens], "cuda")
+    T = batch.input_ids.numel()
+
+    def run():
+        lp, _ = model.forward(batch, 1.0, save_for_backward=True)
+        model.backward(torch.ones_like(lp) / T, None)
+    return run, dict(flops=model.flops_per_token(max(lens)) * T, bytes=0.0, shape=[T, cfg.num_hidden_layers, "layers"])
+
+
 def _qkv(lens, Hq, Hkv, D=128):
     T = sum(lens)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
@@ -265,11 +286,14 @@ def case_moe_grouped(small):
 
 
 CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode, "gemm_stream": case_gemm_stream,
-         "gemm_decode_chain": case_gemm_decode_chain,
+         "gemm_decode_chain": case_gemm_decode_chain, "train_microbatch": case_train_microbatch,
          "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode, "paged_decode_grpo_plain": case_paged_decode_grpo_plain,
          "paged_decode_grpo_shared": case_paged_decode_grpo_shared,
          "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "gemm_ag": case_gemm_ag,
          "gemm_rs": case_gemm_rs, "moe_grouped": case_moe_grouped}
+
+
+_NOT_IN_ALL = {"train_microbatch"}      # whole-model cases (tens of GB): run by name
 
 
 def main() -> None:
@@ -282,7 +306,7 @@ def main() -> None:
     from ...ops import _common as C
     gbs, tfl, src = _peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    for name in (sorted(CASES) if args.case == "all" else [args.case]):
+    for name in ([n for n in sorted(CASES) if n not in _NOT_IN_ALL] if args.case == "all" else [args.case]):
         fn, info = CASES[name](args.small)
         for _ in range(args.warmup):
             fn()
