@@ -166,7 +166,7 @@ class ColocatedRLRunner:
 
     def _enter_training(self) -> None:
         self.engine.sleep()
-        self.policy.load_optimizer(overlap=True)       # arrives under the old-log-prob forward; optim_step waits for it
+        self.policy.load_optimizer()
         if self.cfg.recompute == "auto" and self.device.type == "cuda":
             # keep as many activations as the memory left after parameters, gradients and optimizer
             # state allows (per token and layer: selective 2(3H + qkv) bytes, none adds 4F bytes)
@@ -208,7 +208,7 @@ class ColocatedRLRunner:
         t2 = time.perf_counter()
         self._enter_training()
         if self.device.type == "cuda":
-            torch.cuda.current_stream(self.device).synchronize()      # not the side stream that loads the optimizer state
+            torch.cuda.synchronize(self.device)
         t2a = time.perf_counter()
         if rewards is None:
             rewards = np.array([self.reward_fn(p, o) for p, o in zip(prompts, outs)], dtype=np.float32) \

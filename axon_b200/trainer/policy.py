@@ -110,8 +110,6 @@ class PolicyEngine:
         self.sched_step = 0                   # learning-rate schedule position (advances once per RL step)
         self.state = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._host_state: dict | None = None
-        self._load_stream = None
-        self._load_event = None
         self.fused = None
         mp = getattr(model, "tp", None) or getattr(model, "ep", None) or getattr(model, "pp", None)
         ep = getattr(model, "ep", None)
@@ -163,7 +161,6 @@ class PolicyEngine:
         """Move master / moments to pinned host memory (frees HBM for the KV pool during rollout)."""
         if self.master is None or self.device.type != "cuda":
             return
-        self.wait_optimizer()
         if self._host_state is None:
             self._host_state = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
                                 for k, v in (("master", self.master), ("m", self.exp_avg), ("v", self.exp_avg_sq))}
@@ -172,40 +169,12 @@ class PolicyEngine:
         torch.cuda.current_stream().synchronize()
         self.master = self.exp_avg = self.exp_avg_sq = None
 
-    def load_optimizer(self, overlap: bool = False) -> None:
-        """Bring master / moments back from pinned host memory. With ``overlap`` the copies run on a side
-        stream, so forward-only work queued next (old log-probs) proceeds while they arrive; everything that
-        touches the optimizer state calls ``wait_optimizer`` first."""
+    def load_optimizer(self) -> None:
         if self.master is not None or self._host_state is None:
             return
-        if not overlap or self.device.type != "cuda":
-            self.master = self._host_state["master"].to(self.device, non_blocking=True)
-            self.exp_avg = self._host_state["m"].to(self.device, non_blocking=True)
-            self.exp_avg_sq = self._host_state["v"].to(self.device, non_blocking=True)
-            return
-        if self._load_stream is None:
-            self._load_stream = torch.cuda.Stream(device=self.device)
-        cur = torch.cuda.current_stream(self.device)
-        dst = {k: torch.empty(v.shape, dtype=v.dtype, device=self.device) for k, v in self._host_state.items()}   # allocated on the compute stream
-        self._load_stream.wait_stream(cur)
-        # 32 MiB pieces: the host-to-device copy engine is shared with the per-micro-batch input copies of the
-        # compute stream, which would otherwise queue behind one multi-gigabyte transfer
-        piece = (32 << 20) // 4
-        with torch.cuda.stream(self._load_stream):
-            for k, v in self._host_state.items():
-                d, h = dst[k].view(-1), v.view(-1)
-                for a in range(0, h.numel(), piece):
-                    d[a:a + piece].copy_(h[a:a + piece], non_blocking=True)
-                dst[k].record_stream(self._load_stream)
-        self._load_event = torch.cuda.Event()
-        self._load_event.record(self._load_stream)
-        self.master, self.exp_avg, self.exp_avg_sq = dst["master"], dst["m"], dst["v"]
-
-    def wait_optimizer(self) -> None:
-        """Order the compute stream after an overlapped ``load_optimizer``."""
-        if self._load_event is not None:
-            torch.cuda.current_stream(self.device).wait_event(self._load_event)
-            self._load_event = None
+        self.master = self._host_state["master"].to(self.device, non_blocking=True)
+        self.exp_avg = self._host_state["m"].to(self.device, non_blocking=True)
+        self.exp_avg_sq = self._host_state["v"].to(self.device, non_blocking=True)
 
     # ------------------------------------------------------------------ forward only
     @torch.no_grad()
@@ -346,7 +315,6 @@ class PolicyEngine:
             self.load_optimizer()
             if self.master is None:
                 self.init_optimizer()
-        self.wait_optimizer()
         lo, hi = self.shard
         if self.fused is not None:
             self.opt_step += 1

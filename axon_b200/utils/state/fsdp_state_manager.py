@@ -78,7 +78,6 @@ class FSDPStateManager(BaseStateManager):
         eng, params = self.optimizer, self.model.params
         lo, hi = eng.shard
         eng.load_optimizer()          # state may be parked on the host during rollout
-        eng.wait_optimizer()
         pin = bool(async_save) and torch.cuda.is_available()
         files: dict[str, dict] = {}
         if sharded:
