@@ -318,10 +318,15 @@ class _DenseInference:
             kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
             h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
             qkv = self._lin(l, "self_attn.qkv_proj.weight", h)
-            qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
-                                      c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
-            P.kv_write(qkv_r, cache.k[l], cache.v[l], tok_seq, tok_pos, block_table, c.num_attention_heads,
-                       c.num_key_value_heads, c.head_dim)
+            if tok_pos is batch.position_ids:      # the usual case: cache positions are the RoPE positions - one launch
+                qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
+                                          c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps,
+                                          kv_cache=(cache.k[l], cache.v[l], tok_seq, block_table))
+            else:
+                qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
+                                          c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
+                P.kv_write(qkv_r, cache.k[l], cache.v[l], tok_seq, tok_pos, block_table, c.num_attention_heads,
+                           c.num_key_value_heads, c.head_dim)
             o, _ = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                                need_lse=False)
             ao = self._lin(l, "self_attn.o_proj.weight", o)
@@ -350,9 +355,8 @@ class _DenseInference:
             h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
             qkv = self._lin(l, "self_attn.qkv_proj.weight", h)
             qkv_r = R.qknorm_rope_fwd(qkv, positions, tables[0], tables[1], c.num_attention_heads,
-                                      c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
-            P.kv_write(qkv_r, cache.k[l], cache.v[l], slots, positions, block_table, c.num_attention_heads,
-                       c.num_key_value_heads, c.head_dim)
+                                      c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps,
+                                      kv_cache=(cache.k[l], cache.v[l], slots, block_table))
             if shared is None:
                 o = P.paged_decode(qkv_r, cache.k[l], cache.v[l], block_table, seq_lens, c.num_attention_heads,
                                    c.num_key_value_heads, c.head_dim)

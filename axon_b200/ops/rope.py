@@ -42,8 +42,16 @@ def _rot_t(g, cos, sin):  # transpose (inverse) rotation applied to grads
     return torch.cat([g1 * c + g2 * s, g2 * c - g1 * s], -1)
 
 
-def qknorm_rope_fwd(qkv, pos, cos_t, sin_t, Hq, Hkv, D, qw=None, kw=None, eps=1e-6):
+def qknorm_rope_fwd(qkv, pos, cos_t, sin_t, Hq, Hkv, D, qw=None, kw=None, eps=1e-6, kv_cache=None):
+    """QK-norm + RoPE of packed qkv rows. ``kv_cache = (kcache, vcache, tok_seq, block_table)``: the rotated K rows
+    and the V rows are also written to their pages of the paged KV cache (token t at position ``pos[t]`` of block
+    table row ``tok_seq[t]``) in the same launch."""
     T = qkv.shape[0]
+    if kv_cache is not None and not C.use_native(qkv):
+        from .paged import kv_write
+        out = qknorm_rope_fwd(qkv, pos, cos_t, sin_t, Hq, Hkv, D, qw, kw, eps)
+        kv_write(out, kv_cache[0], kv_cache[1], kv_cache[2], pos, kv_cache[3], Hq, Hkv, D)
+        return out
     if not C.use_native(qkv):
         x = qkv.view(T, Hq + 2 * Hkv, D).float()
         cos, sin = cos_t[pos.long()], sin_t[pos.long()]
@@ -56,6 +64,13 @@ def qknorm_rope_fwd(qkv, pos, cos_t, sin_t, Hq, Hkv, D, qw=None, kw=None, eps=1e
         outs.append(x[:, Hq + Hkv:])
         return torch.cat(outs, 1).to(qkv.dtype).view_as(qkv)
     out = torch.empty_like(qkv)
+    if kv_cache is not None:
+        kc, vc, tok_seq, bt = kv_cache
+        rc = C.lib().axb_qknorm_rope_fwd_kv(C.ptr(qkv), C.ptr(out), C.ptr(qw), C.ptr(kw), C.ptr(pos), C.ptr(cos_t), C.ptr(sin_t),
+                                            ctypes.c_longlong(T), Hq, Hkv, D, ctypes.c_float(eps), C.ptr(kc), C.ptr(vc), C.ptr(tok_seq),
+                                            C.ptr(bt), bt.shape[1], kc.shape[0], kc.shape[2], C.stream())
+        C.launched(rc, "qknorm_rope_fwd_kv")
+        return out
     rc = C.lib().axb_qknorm_rope_fwd(C.ptr(qkv), C.ptr(out), C.ptr(qw), C.ptr(kw), C.ptr(pos), C.ptr(cos_t),
                                      C.ptr(sin_t), ctypes.c_longlong(T), Hq, Hkv, D, ctypes.c_float(eps),
                                      C.stream())

@@ -173,14 +173,24 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, float*
 // Rotary pairs element i with i + D/2 (rotate-half convention); lanes l and l^16 are partners.
 // Heads [0,Hq) are queries, [Hq,Hq+Hkv) keys (both optionally RMS-normalised with their own
 // weight, then rotated), [Hq+Hkv, Hq+2Hkv) values (copied).
+// Optional second destination of the K / V rows: the paged KV cache ([num_pages][Hkv][page][D]).
+struct QkvCacheDst {
+  __nv_bfloat16* kcache;
+  __nv_bfloat16* vcache;
+  const int* tok_seq;        // block-table row of every token
+  const int* block_table;
+  int max_pages, num_pages, page;
+};
+
 template <int EPL>
 __global__ void __launch_bounds__(256)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out,
                        const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
                        const int* __restrict__ pos, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, long long n_items, int Hq, int Hkv,
-                       float eps) {
+                       float eps, QkvCacheDst cache) {
   constexpr int D = EPL * 32;
+  grid_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int HT = Hq + 2 * Hkv;
   for (long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); item < n_items;
@@ -221,13 +231,29 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __r
         f[k] = lane < 16 ? f[k] * c - other * s : f[k] * c + other * s;
       }
     }
+    // sampler paths: the rotated K row and the V row also go straight to their page of the KV cache
+    __nv_bfloat16* cdst = nullptr;
+    if (cache.kcache != nullptr && h >= Hq) {
+      const int seq = cache.tok_seq[t], p = pos[t];
+      if (seq >= 0 && p >= 0) {
+        const int page = cache.block_table[(long long)seq * cache.max_pages + p / cache.page];
+        if (page >= 0 && page < cache.num_pages) {
+          const int is_v = h >= Hq + Hkv;
+          const int hk = h - Hq - is_v * Hkv;
+          cdst = (is_v ? cache.vcache : cache.kcache) + (((long long)page * Hkv + hk) * cache.page + (p % cache.page)) * D + lane * EPL;
+        }
+      }
+    }
     if (EPL == 4) {
       uint2 o;
       o.x = pack_bf16x2(f[0], f[1]);
       o.y = pack_bf16x2(f[EPL - 2], f[EPL - 1]);
       *reinterpret_cast<uint2*>(dst) = o;
+      if (cdst != nullptr) *reinterpret_cast<uint2*>(cdst) = o;
     } else {
-      *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(f[0], f[1]);
+      const uint32_t o = pack_bf16x2(f[0], f[1]);
+      *reinterpret_cast<uint32_t*>(dst) = o;
+      if (cdst != nullptr) *reinterpret_cast<uint32_t*>(cdst) = o;
     }
   }
 }
@@ -438,21 +464,38 @@ extern "C" int axb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   return check_launch();
 }
 
-extern "C" int axb_qknorm_rope_fwd(const void* qkv, void* out, const void* qw, const void* kw,
-                                   const int* pos, const float* cos_t, const float* sin_t,
-                                   long long T, int Hq, int Hkv, int D, float eps, void* stream) {
+static int launch_qknorm_rope_fwd(const void* qkv, void* out, const void* qw, const void* kw, const int* pos,
+                                  const float* cos_t, const float* sin_t, long long T, int Hq, int Hkv, int D,
+                                  float eps, QkvCacheDst cache, void* stream) {
   if ((D != 128 && D != 64) || T <= 0) return AXB_LAUNCH_BAD_ARG;
   const long long n = T * (Hq + 2 * Hkv);
   const int grid = grid_for(n, 8, 16);
   if (D == 128)
     qknorm_rope_fwd_kernel<4><<<grid, 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, (const __nv_bfloat16*)qw,
-        (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps);
+        (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps, cache);
   else
     qknorm_rope_fwd_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, (const __nv_bfloat16*)qw,
-        (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps);
+        (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps, cache);
   return check_launch();
+}
+
+extern "C" int axb_qknorm_rope_fwd(const void* qkv, void* out, const void* qw, const void* kw,
+                                   const int* pos, const float* cos_t, const float* sin_t,
+                                   long long T, int Hq, int Hkv, int D, float eps, void* stream) {
+  return launch_qknorm_rope_fwd(qkv, out, qw, kw, pos, cos_t, sin_t, T, Hq, Hkv, D, eps, QkvCacheDst{}, stream);
+}
+
+// Same, and the rotated K rows / the V rows of token t are also written to page
+// block_table[tok_seq[t]][pos[t] / page] of the KV cache (one launch instead of two on the sampler paths).
+extern "C" int axb_qknorm_rope_fwd_kv(const void* qkv, void* out, const void* qw, const void* kw, const int* pos,
+                                      const float* cos_t, const float* sin_t, long long T, int Hq, int Hkv, int D,
+                                      float eps, void* kcache, void* vcache, const int* tok_seq,
+                                      const int* block_table, int max_pages, int num_pages, int page, void* stream) {
+  if (kcache == nullptr || vcache == nullptr || tok_seq == nullptr || block_table == nullptr || page <= 0) return AXB_LAUNCH_BAD_ARG;
+  QkvCacheDst c{(__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, tok_seq, block_table, max_pages, num_pages, page};
+  return launch_qknorm_rope_fwd(qkv, out, qw, kw, pos, cos_t, sin_t, T, Hq, Hkv, D, eps, c, stream);
 }
 
 extern "C" int axb_qknorm_rope_bwd_partials(long long T, int Hq, int Hkv) {

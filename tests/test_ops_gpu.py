@@ -297,3 +297,28 @@ def test_paged_decode_shared_prefix_matches_plain_decode(Hq, Hkv):
     close(got[:B], ref[:B], 2e-2)
     close(got[:B], plain[:B], 2e-2)
     assert float(got[B:].abs().max()) == 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (128, 4, 4)])
+def test_qknorm_rope_with_fused_kv_cache_write(D, Hq, Hkv):
+    """One launch = QK-norm + RoPE and the K / V rows in their cache pages: against the two separate ops."""
+    from axon_b200.ops import paged as P
+    from axon_b200.ops import rope as R
+    torch.manual_seed(5)
+    T, page, max_pages, num_pages = 37, 128, 4, 16
+    qkv = bf(T, (Hq + 2 * Hkv) * D).cuda()
+    pos = torch.randperm(max_pages * page)[:T].to(torch.int32).cuda()      # distinct slots: no two tokens race for one
+    tok_seq = torch.randint(0, 3, (T,), dtype=torch.int32).cuda()
+    bt = torch.randperm(num_pages)[: 3 * max_pages].view(3, max_pages).to(torch.int32).cuda()
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(max_pages * page).float()[:, None] * inv[None, :]
+    cos_t, sin_t = ang.cos().cuda(), ang.sin().cuda()
+    qw, kw = (bf(D) * 0.1 + 1).cuda(), (bf(D) * 0.1 + 1).cuda()
+    k1, v1 = torch.zeros(num_pages, Hkv, page, D, dtype=torch.bfloat16, device="cuda"), torch.zeros(num_pages, Hkv, page, D, dtype=torch.bfloat16, device="cuda")
+    k2, v2 = torch.zeros_like(k1), torch.zeros_like(v1)
+    ref = R.qknorm_rope_fwd(qkv, pos, cos_t, sin_t, Hq, Hkv, D, qw, kw)
+    P.kv_write(ref, k1, v1, tok_seq, pos, bt, Hq, Hkv, D)
+    got = R.qknorm_rope_fwd(qkv, pos, cos_t, sin_t, Hq, Hkv, D, qw, kw, kv_cache=(k2, v2, tok_seq, bt))
+    assert torch.equal(got, ref) and torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert float(k2.abs().sum()) > 0
