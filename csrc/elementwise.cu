@@ -46,6 +46,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ xsum,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int H, float eps) {
   __shared__ float red[NORM_THREADS / 32];
+  grid_dependency_wait();     // launched as a programmatic dependent: the producer of x / delta has completed from here on
   grid_launch_dependents();   // a GEMM launched as a programmatic dependent may start streaming its weights now
   const long long row = blockIdx.x;
   const int nv = H / 8;
@@ -190,6 +191,7 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __r
                        const float* __restrict__ sin_t, long long n_items, int Hq, int Hkv,
                        float eps, QkvCacheDst cache) {
   constexpr int D = EPL * 32;
+  grid_dependency_wait();
   grid_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int HT = Hq + 2 * Hkv;
@@ -340,6 +342,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat
 // gu is [T][2F] (gate | up); a[T][F] = silu(gate) * up.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ a,
                                   long long T, int F) {
+  grid_dependency_wait();
   grid_launch_dependents();   // see rmsnorm_fwd_kernel
   const int fv = F / 8;
   const long long n = T * fv;
@@ -431,10 +434,10 @@ extern "C" int axb_rmsnorm_fwd(const void* x, const void* delta, const void* w, 
                                float* rstd, long long T, int H, float eps, void* stream) {
   if (H % 8 != 0 || T <= 0) return AXB_LAUNCH_BAD_ARG;
   if (delta != nullptr && xsum == nullptr) return AXB_LAUNCH_BAD_ARG;
-  rmsnorm_fwd_kernel<<<(unsigned)T, NORM_THREADS, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w,
-      (__nv_bfloat16*)xsum, (__nv_bfloat16*)y, rstd, H, eps);
-  return check_launch();
+  const int rc = launch_dependent(rmsnorm_fwd_kernel, dim3((unsigned)T), dim3(NORM_THREADS), 0, (cudaStream_t)stream,
+                                  (const __nv_bfloat16*)x, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)w,
+                                  (__nv_bfloat16*)xsum, (__nv_bfloat16*)y, rstd, H, eps);
+  return rc ? rc : check_launch();
 }
 
 // Number of row-partials rmsnorm_bwd writes; scratch must hold that many rows of H floats.
@@ -470,15 +473,14 @@ static int launch_qknorm_rope_fwd(const void* qkv, void* out, const void* qw, co
   if ((D != 128 && D != 64) || T <= 0) return AXB_LAUNCH_BAD_ARG;
   const long long n = T * (Hq + 2 * Hkv);
   const int grid = grid_for(n, 8, 16);
+  int rc;
   if (D == 128)
-    qknorm_rope_fwd_kernel<4><<<grid, 256, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, (const __nv_bfloat16*)qw,
-        (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps, cache);
+    rc = launch_dependent(qknorm_rope_fwd_kernel<4>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv,
+                          (__nv_bfloat16*)out, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps, cache);
   else
-    qknorm_rope_fwd_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, (const __nv_bfloat16*)qw,
-        (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps, cache);
-  return check_launch();
+    rc = launch_dependent(qknorm_rope_fwd_kernel<2>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv,
+                          (__nv_bfloat16*)out, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, pos, cos_t, sin_t, n, Hq, Hkv, eps, cache);
+  return rc ? rc : check_launch();
 }
 
 extern "C" int axb_qknorm_rope_fwd(const void* qkv, void* out, const void* qw, const void* kw,
@@ -536,9 +538,9 @@ extern "C" int axb_qknorm_rope_bwd(const void* dout, const void* qkv, void* dqkv
 
 extern "C" int axb_swiglu_fwd(const void* gu, void* a, long long T, int F, void* stream) {
   if (F % 8 != 0 || T <= 0) return AXB_LAUNCH_BAD_ARG;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, T, F);
-  return check_launch();
+  const int rc = launch_dependent(swiglu_fwd_kernel, dim3(grid_for(T * (F / 8), 256)), dim3(256), 0, (cudaStream_t)stream,
+                                  (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, T, F);
+  return rc ? rc : check_launch();
 }
 extern "C" int axb_swiglu_bwd(const void* da, const void* gu, void* dgu, long long T, int F, void* stream) {
   if (F % 8 != 0 || T <= 0) return AXB_LAUNCH_BAD_ARG;

@@ -91,6 +91,28 @@ inline int sm_count() {
   return n;
 }
 
+// Launch as a programmatic dependent of the previous kernel of the stream: the grid may be scheduled while that
+// kernel drains, so launch latency and CTA ramp-up overlap its tail. The kernel MUST execute griddepcontrol.wait
+// (grid_dependency_wait) before its first global memory access; only kernels written that way are launched here.
+template <typename... KArgs, typename... Args>
+inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) != cudaSuccess) {
+    cudaGetLastError();
+    return -4;   // AXB_LAUNCH_CUDA_ERROR
+  }
+  return 0;
+}
+
 inline int check_launch() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

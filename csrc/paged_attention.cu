@@ -61,6 +61,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens,
                     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                     int Hq, int Hkv, int nsplit, float scale_log2, int* status) {
+  grid_dependency_wait();
   grid_launch_dependents();   // the output projection (a programmatic dependent) may start streaming its weights
   const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
   const int rep = Hq / Hkv;
@@ -276,6 +277,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 // out[b][h][:] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 __global__ void paged_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                    __nv_bfloat16* __restrict__ out, int nsplit) {
+  grid_dependency_wait();
   grid_launch_dependents();
   const long long bh = blockIdx.x;
   const int d = threadIdx.x;
@@ -344,11 +346,12 @@ extern "C" int axb_paged_decode(const void* q, long long q_row_stride, const voi
   float* part_o = reinterpret_cast<float*>(scratch);
   float* part_ml = part_o ? part_o + (long long)B * Hq * nsplit * PA_D : nullptr;
   if (nsplit > 1 && scratch == nullptr) return AXB_LAUNCH_BAD_ARG;
-  paged_decode_kernel<<<dim3(Hkv, B, nsplit), 128, PA_SMEM, s>>>(
-      tmK, tmV, (const __nv_bfloat16*)q, q_row_stride, block_table, max_pages, seq_lens, (__nv_bfloat16*)out,
-      part_o, part_ml, Hq, Hkv, nsplit, softmax_scale * 1.4426950408889634f, status);
-  rc = check_launch();
+  rc = launch_dependent(paged_decode_kernel, dim3(Hkv, B, nsplit), dim3(128), PA_SMEM, s, tmK, tmV, (const __nv_bfloat16*)q,
+                        q_row_stride, block_table, max_pages, seq_lens, (__nv_bfloat16*)out, part_o, part_ml, Hq, Hkv, nsplit,
+                        softmax_scale * 1.4426950408889634f, status);
+  if (!rc) rc = check_launch();
   if (rc || nsplit == 1) return rc;
-  paged_merge_kernel<<<B * Hq, PA_D, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, nsplit);
-  return check_launch();
+  rc = launch_dependent(paged_merge_kernel, dim3(B * Hq), dim3(PA_D), 0, s, (const float*)part_o, (const float*)part_ml,
+                        (__nv_bfloat16*)out, nsplit);
+  return rc ? rc : check_launch();
 }
