@@ -24,6 +24,7 @@ class ModelConfig:
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1e6
     qk_norm: bool = True
+    attention_bias: bool = False      # bias on the q / k / v projections (Qwen2 / Qwen2.5 family)
     tie_word_embeddings: bool = False
     max_position_embeddings: int = 40960
     eos_token_id: int = 151645
@@ -52,6 +53,8 @@ class ModelConfig:
         per_layer = self.qkv_size * H + H * self.q_size + 2 * H
         if self.qk_norm:
             per_layer += 2 * self.head_dim
+        if self.attention_bias:
+            per_layer += self.qkv_size
         if self.num_experts > 0:
             per_layer += self.num_experts * H + self.num_experts * 3 * H * self.moe_intermediate_size
         else:
@@ -63,7 +66,7 @@ class ModelConfig:
         d = asdict(self)
         d.pop("extra")
         d.update(self.extra)
-        d["architectures"] = [{"qwen3": "Qwen3ForCausalLM", "llama": "LlamaForCausalLM",
+        d["architectures"] = [{"qwen3": "Qwen3ForCausalLM", "llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM",
                                "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "Qwen3ForCausalLM")]
         return d
 
@@ -76,6 +79,8 @@ class ModelConfig:
         mt = d.get("model_type", "qwen3")
         if "qk_norm" not in kw:
             kw["qk_norm"] = mt.startswith("qwen3")
+        if "attention_bias" not in d and mt == "qwen2":      # Qwen2 checkpoints carry q/k/v biases without a config flag
+            kw["attention_bias"] = True
         if isinstance(kw.get("eos_token_id"), list):
             kw["eos_token_id"] = kw["eos_token_id"][0]
         if kw.get("pad_token_id") is None:
@@ -100,6 +105,12 @@ def llama3_8b() -> ModelConfig:
                        num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
                        rms_norm_eps=1e-5, rope_theta=5e5, qk_norm=False, max_position_embeddings=131072,
                        eos_token_id=128009, pad_token_id=128009)
+
+
+def qwen2_5_7b() -> ModelConfig:
+    return ModelConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584, num_hidden_layers=28, num_attention_heads=28,
+                       num_key_value_heads=4, head_dim=128, intermediate_size=18944, qk_norm=False, attention_bias=True,
+                       max_position_embeddings=32768)
 
 
 def qwen3_30b_a3b() -> ModelConfig:
@@ -138,8 +149,15 @@ def tiny_moe_gpu() -> ModelConfig:
                        num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
 
 
-PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen3-30b-a3b": qwen3_30b_a3b,
+PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen2.5-7b": qwen2_5_7b,
+           "tiny-qwen2": lambda: _with(tiny_qwen3(), model_type="qwen2", qk_norm=False, attention_bias=True), "qwen3-30b-a3b": qwen3_30b_a3b,
            "tiny-qwen3": tiny_qwen3, "tiny-qwen3-untied": lambda: _untied(tiny_qwen3()), "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
+
+
+def _with(cfg: ModelConfig, **kw) -> ModelConfig:
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    return cfg
 
 
 def _untied(cfg: ModelConfig) -> ModelConfig:

@@ -83,14 +83,29 @@ class DenseModel:
         return self._wgrad("model.embed_tokens.weight" if self.cfg.tie_word_embeddings else "lm_head.weight")
 
     def _lin(self, l: int, name: str, x: torch.Tensor) -> torch.Tensor:
-        """y = x W^T for the layer's linear ``name`` (adapter models add their low-rank path here)."""
-        return G.gemm_nt(x, self._p(l, name))
+        """y = x W^T (+ bias) for the layer's linear ``name`` (adapter models add their low-rank path here)."""
+        return self._bias_fwd(l, name, G.gemm_nt(x, self._p(l, name)))
 
     def _lin_bwd(self, l: int, name: str, dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
-        """Input gradient of ``_lin``; accumulates the weight gradient."""
+        """Input gradient of ``_lin``; accumulates the weight (and bias) gradient."""
         dx = G.gemm_nn(dy, self._p(l, name))
         G.gemm_tn(dy, x, out=self._g(l, name), accumulate=True)
+        self._bias_bwd(l, name, dy)
         return dx
+
+    def _has_bias(self, name: str) -> bool:
+        return self.cfg.attention_bias and name == "self_attn.qkv_proj.weight"
+
+    def _bias_fwd(self, l: int, name: str, y: torch.Tensor) -> torch.Tensor:
+        if self._has_bias(name):
+            y += self._p(l, name[:-len("weight")] + "bias")
+        return y
+
+    def _bias_bwd(self, l: int, name: str, dy: torch.Tensor) -> None:
+        if self._has_bias(name):
+            g = self._g(l, name[:-len("weight")] + "bias")
+            if g is not None:                       # frozen-base models hand out no matrix / bias gradients
+                g += dy.float().sum(0)
 
     def _attn_fwd(self, qkv_r: torch.Tensor, batch: "PackedBatch", need_lse: bool):
         """Causal attention over the packed sequences: qkv_r [T, (Hq + 2 Hkv) D] (rotated) -> (o [T, Hq D], lse).

@@ -128,7 +128,7 @@ class LoRADenseModel(DenseModel):
         """Gradients of frozen tensors: small vectors (norm weights) go to a scratch sink that nobody
         reads, matrices are not computed at all."""
         w = self.base[name]
-        if w.dim() > 1:
+        if w.dim() > 1 or name.endswith(".bias"):
             return None
         key = tuple(w.shape)
         if key not in self._sinks:
@@ -175,7 +175,7 @@ class LoRADenseModel(DenseModel):
 
     # ------------------------------------------------------------------ linear hooks
     def _lin(self, l: int, name: str, x: torch.Tensor) -> torch.Tensor:
-        y = G.gemm_nt(x, self._p(l, name))
+        y = self._bias_fwd(l, name, G.gemm_nt(x, self._p(l, name)))
         A, B, _ = self._ab(l, name)
         if A is None:
             return y

@@ -26,6 +26,8 @@ def param_layout(cfg: ModelConfig) -> "OrderedDict[str, tuple[int, ...]]":
         p = f"model.layers.{l}."
         lay[p + "input_layernorm.weight"] = (H,)
         lay[p + "self_attn.qkv_proj.weight"] = (cfg.qkv_size, H)
+        if cfg.attention_bias:
+            lay[p + "self_attn.qkv_proj.bias"] = (cfg.qkv_size,)
         if cfg.qk_norm:
             lay[p + "self_attn.q_norm.weight"] = (D,)
             lay[p + "self_attn.k_norm.weight"] = (D,)
@@ -96,7 +98,9 @@ class FlatParams:
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
         for name, v in self.views.items():
-            if v.dim() == 1:
+            if v.dim() == 1 and name.endswith(".bias"):
+                v.copy_((torch.randn(v.shape, generator=g, device=self.device) * std).to(v.dtype))
+            elif v.dim() == 1:
                 v.fill_(1.0)
             else:
                 # generate in chunks to bound the fp32 temporary
@@ -131,6 +135,10 @@ class FlatParams:
                 base = name[: -len("qkv_proj.weight")]
                 q, k, vv = v.split([cfg.q_size, cfg.kv_size, cfg.kv_size], 0)
                 out[base + "q_proj.weight"], out[base + "k_proj.weight"], out[base + "v_proj.weight"] = q, k, vv
+            elif name.endswith("qkv_proj.bias"):
+                base = name[: -len("qkv_proj.bias")]
+                q, k, vv = v.split([cfg.q_size, cfg.kv_size, cfg.kv_size], 0)
+                out[base + "q_proj.bias"], out[base + "k_proj.bias"], out[base + "v_proj.bias"] = q, k, vv
             elif name.endswith("gate_up_proj.weight"):
                 base = name[: -len("gate_up_proj.weight")]
                 g, u = v.split(cfg.intermediate_size, 0)

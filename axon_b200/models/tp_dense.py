@@ -80,6 +80,7 @@ def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, in
 class TPDenseModel:
     def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False):
         assert cfg.num_experts == 0
+        assert not cfg.attention_bias, "tensor-parallel layout of q/k/v biases is not built yet (Qwen2 family: use data / sequence / pipeline parallelism)"
         assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype

@@ -32,7 +32,10 @@ def autograd_reference(cfg: ModelConfig, sd: dict, seqs, temperature, g_lp, g_en
         for l in range(cfg.num_hidden_layers):
             p = f"model.layers.{l}."
             h = rms(x, P[p + "input_layernorm.weight"])
-            qkv = (h @ P[p + "self_attn.qkv_proj.weight"].t()).view(L, Hq + 2 * Hkv, D)
+            qkv = h @ P[p + "self_attn.qkv_proj.weight"].t()
+            if cfg.attention_bias:
+                qkv = qkv + P[p + "self_attn.qkv_proj.bias"]
+            qkv = qkv.view(L, Hq + 2 * Hkv, D)
             q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:]
             if cfg.qk_norm:
                 q = rms(q, P[p + "self_attn.q_norm.weight"])
@@ -81,8 +84,10 @@ def _run(cfg, device, dtype, seqs, temperature=0.9):
     return model, lp.cpu(), ent.cpu(), lp_r, ent_r, grads_r
 
 
-def test_dense_model_cpu_matches_autograd():
-    cfg = tiny_qwen3()
+@pytest.mark.parametrize("preset", ["tiny-qwen3", "tiny-qwen2"])
+def test_dense_model_cpu_matches_autograd(preset):
+    from axon_b200.models.config import get_config
+    cfg = get_config(preset)
     seqs = [torch.randint(0, cfg.vocab_size, (n,)) for n in (17, 5, 33)]
     model, lp, ent, lp_r, ent_r, grads_r = _run(cfg, "cpu", torch.float32, seqs)
     assert torch.allclose(lp.double(), lp_r, atol=1e-4), (lp.double() - lp_r).abs().max()
@@ -108,3 +113,24 @@ def test_dense_model_gpu_matches_autograd():
         g = g.double().cpu()
         rel = (g - ref).norm() / (ref.norm() + 1e-12)
         assert rel < 0.08, (name, rel.item())
+
+
+def test_qwen2_family_bias_round_trips_through_hf_names(tmp_path):
+    """Qwen2-style checkpoints: q/k/v biases fuse into one vector and split back under their HF names."""
+    from axon_b200.models.config import ModelConfig, get_config
+    from axon_b200.utils.hf_model import load_hf_weights, save_hf_model
+    cfg = get_config("tiny-qwen2")
+    assert cfg.attention_bias and not cfg.qk_norm
+    m = DenseModel(cfg, device="cpu", dtype=torch.float32)
+    m.params.init_random(std=0.05, seed=2)
+    sd = m.params.to_hf_state_dict()
+    b = "model.layers.0.self_attn."
+    assert tuple(sd[b + "k_proj.bias"].shape) == (cfg.kv_size,) and b + "qkv_proj.bias" not in sd
+    save_hf_model(m, str(tmp_path / "hf"), cfg=cfg)
+    cfg2 = ModelConfig.from_pretrained(str(tmp_path / "hf"))
+    assert cfg2.attention_bias and cfg2.model_type == "qwen2"
+    m2 = DenseModel(cfg2, device="cpu", dtype=torch.float32)
+    load_hf_weights(m2, str(tmp_path / "hf"))
+    torch.testing.assert_close(m2.params.flat, m.params.flat, rtol=0, atol=4e-3)      # bf16 on disk
+    # a config.json without the flag (as Qwen2 ships it) still turns the biases on
+    assert ModelConfig.from_hf_dict({"model_type": "qwen2", "hidden_size": 256, "num_attention_heads": 4}).attention_bias
