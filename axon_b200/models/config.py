@@ -67,7 +67,7 @@ class ModelConfig:
         d.pop("extra")
         d.update(self.extra)
         d["architectures"] = [{"qwen3": "Qwen3ForCausalLM", "llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM",
-                               "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "Qwen3ForCausalLM")]
+                               "mistral": "MistralForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "Qwen3ForCausalLM")]
         return d
 
     @classmethod
@@ -79,6 +79,12 @@ class ModelConfig:
         mt = d.get("model_type", "qwen3")
         if "qk_norm" not in kw:
             kw["qk_norm"] = mt.startswith("qwen3")
+        supported = ("qwen3", "qwen3_moe", "qwen2", "llama", "mistral")
+        if mt not in supported:
+            raise NotImplementedError(f"model_type '{mt}' is not among the decoder families built here {supported}")
+        if mt == "mistral" and d.get("sliding_window") and d.get("sliding_window") < d.get("max_position_embeddings", 0):
+            kw.setdefault("max_position_embeddings", d["sliding_window"])
+            kw["max_position_embeddings"] = min(kw["max_position_embeddings"], d["sliding_window"])      # full attention inside the window only
         if "attention_bias" not in d and mt == "qwen2":      # Qwen2 checkpoints carry q/k/v biases without a config flag
             kw["attention_bias"] = True
         if isinstance(kw.get("eos_token_id"), list):
