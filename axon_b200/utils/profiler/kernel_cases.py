@@ -251,6 +251,25 @@ def case_gemm_ag(small):
     return run, dict(flops=2.0 * T * N * K, bytes=2.0 * (T * K + N * K + T * N), shape=[T, N, K])
 
 
+def case_gemm_gather_w(small):
+    """Weight all-gather -> GEMM (sharded parameters) with both weight shards on this GPU: same kernel and TMA
+    traffic pattern as across NVLink."""
+    import ctypes
+    from ...ops import _common as C
+    T, F, K, W = (2048, 6144, 4096, 2) if small else (8192, 6144, 4096, 2)
+    shards = [bf(F // W, K) for _ in range(W)]
+    x = bf(T, K)
+    out = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
+    ptrs = (ctypes.c_ulonglong * W)(*[t.data_ptr() for t in shards])
+    lib = C.lib()
+
+    def run():
+        rc = lib.axb_gemm_gather_weights(ptrs, W, 0, C.ptr(x), C.ptr(out), F // W, T, K, ctypes.c_longlong(K), ctypes.c_longlong(K),
+                                         ctypes.c_longlong(F), 0, C.ptr(C.status(x.device)), C.stream())
+        C.launched(rc, "gemm_gather_weights")
+    return run, dict(flops=2.0 * T * F * K, bytes=2.0 * (T * K + F * K + T * F), shape=[T, F, K])
+
+
 def case_gemm_rs(small):
     """GEMM -> reduce-scatter (scatter part) with both staging areas on this GPU."""
     import ctypes
@@ -289,7 +308,7 @@ CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_dec
          "gemm_decode_chain": case_gemm_decode_chain, "train_microbatch": case_train_microbatch,
          "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode, "paged_decode_grpo_plain": case_paged_decode_grpo_plain,
          "paged_decode_grpo_shared": case_paged_decode_grpo_shared,
-         "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "gemm_ag": case_gemm_ag,
+         "lmhead_fwd": case_lmhead_fwd, "rmsnorm": case_rmsnorm, "adamw": case_adamw, "gemm_ag": case_gemm_ag, "gemm_gather_w": case_gemm_gather_w,
          "gemm_rs": case_gemm_rs, "moe_grouped": case_moe_grouped}
 
 

@@ -251,6 +251,39 @@ extern "C" int axb_gemm_allgather_a(const unsigned long long* x_ptrs, int world,
 #undef AXB_AG
 }
 
+// Weight all-gather fused into the consuming GEMM (ZeRO-3 / FSDP style parameter sharding):
+//   Y[T][F] = X[T][K] * concat_r(W_r)^T,  W_r = rank r's row shard [F / world][K] in peer-visible memory.
+// The weights ride on the 128-row side of the MMA (each weight tile is fetched by TMA through the tensor map
+// of the rank that owns it, own shard first), the tokens on the N side, and the epilogue stores transposed,
+// so no gathered copy of W is ever materialised. feats_per_rank must be a multiple of 128.
+extern "C" int axb_gemm_gather_weights(const unsigned long long* w_ptrs, int world, int rank, const void* X, void* Y,
+                                       int feats_per_rank, int T, int K, long long ldw, long long ldx, long long ldy,
+                                       int out_fp32, int* status, void* stream) {
+  using namespace axb;
+  if (world < 1 || world > PeerGatherTiles::MAX_RANKS || rank < 0 || rank >= world || feats_per_rank <= 0 ||
+      feats_per_rank % GEMM_BM != 0 || T <= 0 || (ldx & 7) || (ldw & 7))
+    return AXB_LAUNCH_BAD_ARG;
+  PeerGatherTiles::Params tp;
+  for (int r = 0; r < PeerGatherTiles::MAX_RANKS; ++r) {
+    const void* base = reinterpret_cast<const void*>(w_ptrs[r < world ? r : rank]);
+    int rc = make_tmap_2d(&tp.maps[r], base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, feats_per_rank, ldw * 2, GEMM_BK,
+                          GEMM_BM, true);
+    if (rc != AXB_LAUNCH_OK) return rc;
+  }
+  tp.world = world;
+  tp.rank = rank;
+  tp.blocks_per_rank = feats_per_rank / GEMM_BM;
+  const int F = world * feats_per_rank;
+  TransposedEpi::Params ep{Y, ldy, out_fp32 ? 1 : 0, nullptr};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const void* own = reinterpret_cast<const void*>(w_ptrs[rank]);
+  if (T % 256 == 0 || T > 2048)
+    return launch_gemm_inst<256, false, false, TransposedEpi, PeerGatherTiles>(own, X, F, T, K, ldw, ldx, ep, status, s, 0, 1, tp,
+                                                                                feats_per_rank, -1);
+  return launch_gemm_inst<128, false, false, TransposedEpi, PeerGatherTiles>(own, X, F, T, K, ldw, ldx, ep, status, s, 0, 1, tp,
+                                                                              feats_per_rank, -1);
+}
+
 // GEMM -> reduce-scatter, part 1: partial[T][N] = X[T][K] * op(W); the epilogue stores every tile into the
 // staging slot [rank][local row][N] of the rank that owns the rows (staging_ptrs[r], bf16, row pitch ld).
 extern "C" int axb_gemm_scatter(const void* X, const void* W, const unsigned long long* staging_ptrs, int world, int rank,
