@@ -207,7 +207,9 @@ class ColocatedRLRunner:
                                              max_tokens=cap, ignore_eos=response_caps is not None))
         self._enter_rollout()
         t1 = time.perf_counter()
+        pre0 = self.engine.stats.get("preempted", 0)
         outs = self.engine.generate(prompts, params)
+        self.phase_detail["preempted"] = self.engine.stats.get("preempted", 0) - pre0      # sequences pushed back for lack of KV pages
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         t2 = time.perf_counter()
