@@ -154,11 +154,11 @@ sample_kernel(const float* __restrict__ logits, long long ldl, int V, const floa
     thr_key = max(thr_key, pk);
   }
 
-  // inverse-CDF over the kept set in index order; thread t owns a contiguous segment
-  const int per = (V + SMP_THREADS - 1) / SMP_THREADS;
-  const int i0 = threadIdx.x * per, i1 = min(V, i0 + per);
+  // Inverse CDF over the kept set. Any fixed order of the kept elements samples the same distribution; the
+  // order used is (thread, then index): thread t owns elements t, t + 1024, t + 2048, ..., so that every pass
+  // over the logits is coalesced (a contiguous segment per thread would touch 32 cache lines per warp load).
   float ssum = 0.f;
-  for (int i = i0; i < i1; ++i) {
+  for (int i = threadIdx.x; i < V; i += SMP_THREADS) {
     const float z = row[i] * inv_t;
     if (f2key(z) >= thr_key) ssum += __expf(z - m);
   }
@@ -167,15 +167,23 @@ sample_kernel(const float* __restrict__ logits, long long ldl, int V, const floa
   if (threadIdx.x == 0) {
     const float u = uniform01(seed, (uint32_t)b, counters ? (uint32_t)counters[b] : 0u);
     float target = u * total, cum = 0.f;
-    int t = 0;
-    for (; t < SMP_THREADS - 1; ++t) {
-      if (cum + seg[t] > target) break;
+    int t = 0, last_ne = 0;
+    bool found = false;
+    for (; t < SMP_THREADS; ++t) {
+      if (seg[t] > 0.f) last_ne = t;
+      if (cum + seg[t] > target) {
+        found = true;
+        break;
+      }
       cum += seg[t];
     }
-    // walk the chosen segment
+    if (!found) {            // rounding pushed the target to the very end: the last thread that kept anything
+      t = last_ne;
+      cum -= seg[t];
+    }
+    // walk the chosen thread's elements
     int choice = -1, last_kept = -1;
-    const int j0 = t * per, j1 = min(V, j0 + per);
-    for (int i = j0; i < j1; ++i) {
+    for (int i = t; i < V; i += SMP_THREADS) {
       const float z = row[i] * inv_t;
       if (f2key(z) < thr_key) continue;
       last_kept = i;
