@@ -119,6 +119,7 @@ class ColocatedRLRunner:
         self.global_step = 0
         self.timing: dict[str, float] = {}
         self.phase_detail: dict = {}
+        self._kv_peak_pages: int | None = None      # peak KV occupancy seen in earlier rollouts (pages)
         if self.device.type == "cuda":
             # Make step 1 look like every later step: the optimizer state exists from the start, and if
             # rollouts will need its memory the pinned host buffers it moves to are allocated now
@@ -136,12 +137,19 @@ class ColocatedRLRunner:
         if self.cfg.offload_optimizer is not None:
             return bool(self.cfg.offload_optimizer)
         need, want_pages = self._kv_need()
+        if self._kv_peak_pages is not None:
+            # observed: the most pages any rollout so far held at once, with a quarter on top and a page per sequence
+            want_pages = min(want_pages, int(self._kv_peak_pages * 1.25) + self.cfg.max_num_seqs)
+            grads = 0 if self.model.params.grad_flat is None or getattr(self.model.params, "grads_persistent", False) \
+                else self.model.params.grad_flat.numel() * 4
+            return (self._free_bytes() + grads) * self.cfg.kv_memory_fraction < want_pages * need
         grads = 0 if self.model.params.grad_flat is None or getattr(self.model.params, "grads_persistent", False) \
             else self.model.params.grad_flat.numel() * 4
-        # Sequences finish at different times and samples of a prompt share its pages, so the pool never holds the
-        # worst case (Qwen3-8B GRPO, 256 x (1024 + up to 4096): peak ~0.2 of it); if it ever runs short the engine
-        # preempts and re-prefills. Moving 48 GB of optimizer state over PCIe twice per step is only worth it when
-        # even that share does not fit beside it.
+        # No rollout seen yet: size for a share of the worst case. Sequences finish at different times and samples of
+        # a prompt share its pages, so the pool never holds the worst case; once a rollout has been observed its
+        # peak occupancy decides (above). If the pool ever runs short the engine preempts and re-prefills. Moving
+        # the optimizer state (12 bytes per parameter) over PCIe twice per step is only worth it when the expected
+        # demand does not fit beside it.
         return (self._free_bytes() + grads) * self.cfg.kv_memory_fraction < want_pages * need * self.cfg.kv_expected_fill
 
     # ------------------------------------------------------------------ memory phases
@@ -210,6 +218,12 @@ class ColocatedRLRunner:
         pre0 = self.engine.stats.get("preempted", 0)
         outs = self.engine.generate(prompts, params)
         self.phase_detail["preempted"] = self.engine.stats.get("preempted", 0) - pre0      # sequences pushed back for lack of KV pages
+        peak = self.engine.cache.num_pages - self.engine.cache.min_free
+        self.phase_detail["kv_peak_pages"] = peak
+        if self.phase_detail["preempted"] == 0:
+            self._kv_peak_pages = max(peak, self._kv_peak_pages or 0)
+        else:                                    # the pool was too small: the true demand is unknown, size for the rule of thumb again
+            self._kv_peak_pages = None
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
         t2 = time.perf_counter()

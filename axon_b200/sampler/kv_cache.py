@@ -20,6 +20,7 @@ class PagedKVCache:
         self.v = [torch.zeros(shape, dtype=dtype, device=self.device) for _ in range(cfg.num_hidden_layers)]
         self.free = list(range(self.num_pages - 1, -1, -1))
         self.ref = [0] * self.num_pages
+        self.min_free = self.num_pages          # low-water mark of the free list (peak occupancy = num_pages - min_free)
         self._arange = torch.arange(4096, dtype=torch.int32, device=self.device)
 
     @staticmethod
@@ -40,6 +41,7 @@ class PagedKVCache:
         out = [self.free.pop() for _ in range(n)]
         for p in out:
             self.ref[p] = 1
+        self.min_free = min(self.min_free, len(self.free))
         return out
 
     def share(self, pages: list[int]) -> list[int]:

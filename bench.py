@@ -226,7 +226,7 @@ def main() -> None:
             "phase_seconds_per_step": {k: v / args.steps for k, v in phase.items()},
             "last_step": {k: last.get(k) for k in ("loss", "grad_norm", "sampler_probs_diff_mean", "entropy")},
             "peak_mem_gib": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
-            "runner": {k: runner.phase_detail.get(k) for k in ("kv_pages", "offloaded", "recompute", "preempted")},
+            "runner": {k: runner.phase_detail.get(k) for k in ("kv_pages", "kv_peak_pages", "offloaded", "recompute", "preempted")},
         }
         print(json.dumps(out))
     if world > 1:
