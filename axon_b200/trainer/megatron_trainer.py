@@ -40,18 +40,21 @@ class TrainerWorker(_Base):
         if self.pp_size > 1 and (self.tp_size > 1 or self.ep_size > 1):
             raise NotImplementedError("pipeline parallelism together with tensor / expert parallelism is not available in this "
                                       "trainer yet; use one model-parallel dimension")
-        for key, label in (("context_parallel_size", "context"),):
-            if int(_get(m, key, 1) or 1) != 1:
-                raise NotImplementedError(f"{label} parallelism > 1 is not available in this trainer yet "
-                                          f"(megatron.{key}={_get(m, key)}); use tensor and data parallelism")
+        self.cp_size = int(_get(m, "context_parallel_size", 1) or 1)
+        if self.cp_size > 1 and (self.tp_size > 1 or self.ep_size > 1 or self.pp_size > 1):
+            raise NotImplementedError("context parallelism together with tensor / expert / pipeline parallelism is not available "
+                                      "in this trainer yet; use one model-parallel dimension")
         self._pending_dispatch = True
         super().__init__(config, model=model, name=name, **kwargs)
+        if self.cp_size > 1:
+            assert self.ulysses_sequence_parallel_size == 1, "choose one of Ulysses and context parallelism"
+            self.ulysses_sequence_parallel_size = self.cp_size      # the token caps count per group, as with Ulysses
 
     # the base class registers dp_rank = rank // sp; with TP the data shard is rank // tp
     def _register_dispatch_collect_info(self, mesh_name: str, dp_rank: int, is_collect: bool) -> None:
         if mesh_name == "trainer" and getattr(self, "_pending_dispatch", False):
             self._pending_dispatch = False
-            mp = max(self.tp_size, self.pp_size)          # ranks of one tensor- / pipeline-parallel group see the same rows
+            mp = max(self.tp_size, self.pp_size, self.cp_size)          # ranks of one tensor- / pipeline- / context-parallel group see the same rows
             assert self.world_size % mp == 0, f"world size {self.world_size} not divisible by the model-parallel size {mp}"
             return super()._register_dispatch_collect_info(mesh_name, self.rank // mp, self.rank % mp == 0)
         return super()._register_dispatch_collect_info(mesh_name, dp_rank, is_collect)
@@ -131,7 +134,38 @@ class TrainerWorker(_Base):
         model.recompute = str(_get(self.config, "recompute", "selective"))
         return model
 
+    def _build_context_parallel(self, model_path, dtype, seed):
+        """Consecutive ranks form a context-parallel group (same rows, two zigzag chunks of every sequence
+        each); the optimizer keeps sharding over ALL ranks, so its reduce-scatter also completes the
+        partial weight gradients of the group."""
+        from ..models.config import get_config
+        from ..models.cp import CPDenseModel, CPModelAdapter
+        from ..parallel.cp import ContextParallel
+        from ..utils.hf_model import has_hf_weights, load_hf_weights
+        import os
+        mcfg = get_config(model_path)
+        assert mcfg.num_experts == 0 and not self.model_kind.value_head, "context parallelism is available on dense causal-LM models"
+        assert self.world_size % self.cp_size == 0, f"world size {self.world_size} not divisible by cp {self.cp_size}"
+        cp_group = None
+        for i in range(self.world_size // self.cp_size):
+            ranks = list(range(i * self.cp_size, (i + 1) * self.cp_size))
+            g = dist.new_group(ranks)
+            if self.rank in ranks:
+                cp_group = g
+        cap = int(_get(self.config, "max_token_len_per_gpu", 16384))       # per-rank token cap; the group packs cp times that
+        # per-sequence padding adds at most 2 cp - 1 tokens per sequence; leave room for a few hundred sequences
+        ctx = ContextParallel(cp_group, self.device, max_local_tokens=(cap + 127) // 128 * 128 + 1024, kv_width=2 * mcfg.kv_size)
+        inner = CPDenseModel(mcfg, ctx, device=self.device, dtype=dtype)
+        inner.recompute = str(_get(self.config, "recompute", "selective"))
+        if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+            load_hf_weights(inner, model_path)
+        else:
+            inner.params.init_random(seed=seed)
+        return CPModelAdapter(inner)
+
     def _build(self, model_path, dtype, seed):
+        if self.cp_size > 1:
+            return self._build_context_parallel(model_path, dtype, seed)
         if self.pp_size > 1:
             return self._build_pipeline_parallel(model_path, dtype, seed)
         if self.ep_size > 1:

@@ -84,6 +84,20 @@ def compile_plan(table: RoutingTable, actor_rank: int, actor_offsets: dict, samp
                         d["dst_scale_off"] = sampler_scale_offsets[s_rank][s.param_name] + (local_row0 // 128) * sc_cols + (c0 - sc0) // 128
                         d["scale_cols"] = sc_cols
                     rows.append(d)
+    return plan_from_descs(rows, elem_bytes)
+
+
+def copy_desc(src_off: int, dst_off: int, rows: int, cols: int, src_stride: int, dst_stride: int, dst_rank: int):
+    """One bf16 slice copy: ``rows x cols`` elements from ``src_off`` (row stride ``src_stride``) of the
+    sender's buffer to ``dst_off`` of rank ``dst_rank``'s buffer. Offsets and strides are multiples of
+    8 elements (16-byte vectors)."""
+    d = np.zeros((), dtype=DESC_DTYPE)
+    d["src_off"], d["dst_off"], d["rows"], d["cols"] = src_off, dst_off, rows, cols
+    d["src_stride"], d["dst_stride"], d["dst_rank"] = src_stride, dst_stride, dst_rank
+    return d
+
+
+def plan_from_descs(rows: list, elem_bytes: int = 2) -> SyncPlan:
     descs = np.array(rows, dtype=DESC_DTYPE) if rows else np.zeros(0, dtype=DESC_DTYPE)
     per = descs["rows"].astype(np.int64) * ((descs["cols"].astype(np.int64) + 7) // 8)
     prefix = np.concatenate([[0], np.cumsum(per)[:-1]]).astype(np.int64) if len(descs) else np.zeros(0, np.int64)
