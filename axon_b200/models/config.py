@@ -157,7 +157,8 @@ def tiny_moe_gpu() -> ModelConfig:
 
 PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen2.5-7b": qwen2_5_7b,
            "tiny-qwen2": lambda: _with(tiny_qwen3(), model_type="qwen2", qk_norm=False, attention_bias=True), "qwen3-30b-a3b": qwen3_30b_a3b,
-           "tiny-qwen3": tiny_qwen3, "tiny-qwen3-untied": lambda: _untied(tiny_qwen3()), "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
+           "tiny-qwen3": tiny_qwen3, "tiny-qwen3-untied": lambda: _untied(tiny_qwen3()),
+           "tiny-qwen3-untied-5l": lambda: _with(_untied(tiny_qwen3()), num_hidden_layers=5), "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
 
 
 def _with(cfg: ModelConfig, **kw) -> ModelConfig:

@@ -183,9 +183,12 @@ class PolicyEngine:
         temp = temperature if temperature is not None else data.meta_info.get("temperature", self.temperature)
         mbs, idx = prepare_dynamic_batch(data, self.max_tokens, dp_group=self.micro_group, strict_equal=self.micro_group is not None)
         lps, ents = [], []
-        for mb in mbs:
-            pk = _Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device)
-            lp, ent = self.model.forward(pk.batch, temp)
+        packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device) for mb in mbs]
+        if hasattr(self.model, "forward_many"):      # pipeline stages: micro-batches stream through the stages
+            results = self.model.forward_many([pk.batch for pk in packs], temp)
+        else:
+            results = (self.model.forward(pk.batch, temp) for pk in packs)
+        for pk, (lp, ent) in zip(packs, results):
             lps.append(pk.to_padded(lp))
             ents.append(pk.to_padded(ent))
         order = torch.tensor([i for p in idx for i in p], dtype=torch.long, device=self.device)
@@ -209,10 +212,9 @@ class PolicyEngine:
         # expert-parallel ranks hold different data but exchange tokens layer by layer: equal micro-batch counts
         mbs, _ = prepare_dynamic_batch(data, self.max_tokens, dp_group=self.micro_group, strict_equal=self.micro_group is not None)
         metrics: dict[str, list] = {}
-        for mb in mbs:
-            mb = mb.to(self.device)
-            pk = _Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device)
-            lp_packed, ent_packed = self.model.forward(pk.batch, temp, save_for_backward=True)
+
+        def loss_step(mb, pk, lp_packed, ent_packed):
+            """Loss of one micro-batch from its packed log-probs / entropies: returns their gradients."""
             lp_leaf = lp_packed.detach().requires_grad_(True)
             ent_leaf = ent_packed.detach().requires_grad_(ent_coef != 0.0)
             mb.batch["log_probs"] = pk.to_padded(lp_leaf)
@@ -237,13 +239,25 @@ class PolicyEngine:
                 total = total + kl_coef * kl_loss
                 m["kl_loss"] = kl_loss.detach().item()
             total.backward()
-            self.model.backward(lp_leaf.grad, ent_leaf.grad if ent_coef != 0.0 else None)
             m["loss"] = total.detach().item()
             with torch.no_grad():
                 rm = mb.batch["response_mask"]
                 m["entropy"] = ((mb.batch["entropy"].detach() * rm).sum() / rm.sum().clamp_min(1)).item()
             for k, v in m.items():
                 metrics.setdefault(k, []).append(v)
+            return lp_leaf.grad, ent_leaf.grad if ent_coef != 0.0 else None
+
+        mbs = [mb.to(self.device) for mb in mbs]
+        packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device) for mb in mbs]
+        if hasattr(self.model, "train_many"):
+            # pipeline stages: the model orders forwards and backwards of the micro-batches (1F1B) and calls
+            # the loss on the last stage only; its metrics are then handed to the other stages
+            self.model.train_many([pk.batch for pk in packs], temp, lambda i, lp, ent: loss_step(mbs[i], packs[i], lp, ent))
+            return self.model.share_from_last(metrics)
+        for mb, pk in zip(mbs, packs):
+            lp_packed, ent_packed = self.model.forward(pk.batch, temp, save_for_backward=True)
+            g_lp, g_ent = loss_step(mb, pk, lp_packed, ent_packed)
+            self.model.backward(g_lp, g_ent)
         return metrics
 
     # ------------------------------------------------------------------ value head (critic / reward model)

@@ -117,3 +117,22 @@ def test_pipeline_parallel_trainer_matches_data_parallel_trainer(world, pp):
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
     assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world,pp,cap", [(2, 2, 64), (3, 3, 64), (3, 3, 128)])
+def test_pipeline_schedule_over_several_micro_batches(world, pp, cap):
+    """A token cap of 64 makes every row its own micro-batch (4 micro-batches: more than stages), 128
+    gives 2 (fewer than 3 stages): the one-forward-one-backward schedule and the streamed forward match
+    the single-process trainer."""
+    import numpy as np
+    name = "tiny-qwen3-untied-5l"        # 5 layers over 3 stages: uneven stages too
+    ref_cfg, got_cfg = _cfg(1, name), _cfg(1, name, pp=pp)
+    ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = cap
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, world)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(np.mean(got[1]["actor/loss"]), np.mean(ref[1]["actor/loss"]), rtol=1e-3, atol=1e-5)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
