@@ -34,6 +34,7 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    num_nextn_predict_layers: int = 0     # multi-token-prediction modules after the decoder (DeepSeek-V3 style, depth 1)
     extra: dict = field(default_factory=dict)
 
     @property
@@ -158,6 +159,7 @@ def tiny_moe_gpu() -> ModelConfig:
 PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen2.5-7b": qwen2_5_7b,
            "tiny-qwen2": lambda: _with(tiny_qwen3(), model_type="qwen2", qk_norm=False, attention_bias=True), "qwen3-30b-a3b": qwen3_30b_a3b,
            "tiny-qwen3": tiny_qwen3, "tiny-qwen3-untied": lambda: _untied(tiny_qwen3()),
+           "tiny-qwen3-mtp": lambda: _with(tiny_qwen3(), num_nextn_predict_layers=1),
            "tiny-qwen3-untied-5l": lambda: _with(_untied(tiny_qwen3()), num_hidden_layers=5), "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
 
 

@@ -59,6 +59,8 @@ class DenseModel:
         self._saved: dict | None = None
         self.recompute = "selective"          # activation recomputation in backward: full | selective | none
         self.offloader = None                 # an ActivationOffloader: kept activations wait in pinned host memory
+        self.mtp_scale = 0.0                  # weight of sum_t(-logprob) of the multi-token-prediction module in backward (0 = module idle)
+        self.mtp_last = None
 
     # ------------------------------------------------------------------ helpers
     # ``weights`` is what the forward pass reads and ``_wgrad`` where weight gradients go; both are the
@@ -242,11 +244,13 @@ class DenseModel:
             if save_for_backward else None
         return hf, state
 
-    def _trunk_bwd(self, s: dict, dhf: torch.Tensor) -> None:
+    def _trunk_bwd(self, s: dict, dhf: torch.Tensor, extra_dx: torch.Tensor | None = None) -> None:
+        """``extra_dx``: a further gradient with respect to the stream before the final norm (the
+        multi-token-prediction module reads it)."""
         c = self.cfg
         batch, tables = s["batch"], s["tables"]
         dx = N.rmsnorm_bwd(dhf, s["xf"], self.weights["model.norm.weight"], s["rstd_f"],
-                           self._wgrad("model.norm.weight"))
+                           self._wgrad("model.norm.weight"), dres=extra_dx)
         del dhf
         inputs = s["layer_inputs"]
         for l in reversed(range(c.num_hidden_layers)):
@@ -286,6 +290,9 @@ class DenseModel:
         lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), batch.labels, temperature)
         if save_for_backward:
             state.update(kind="lm", lse=lse, ent=ent, temperature=temperature)
+            if self.cfg.num_nextn_predict_layers > 0 and self.mtp_scale:
+                from .mtp import mtp_fwd
+                self.mtp_last = mtp_fwd(self, state)         # (sum of negative log-probs, positions) of this micro-batch
             self._saved = state
         return lp, ent
 
@@ -299,7 +306,11 @@ class DenseModel:
         g_ent = None if g_entropy is None else g_entropy.float().contiguous()
         dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["batch"].labels, s["lse"], s["ent"], g_lp, g_ent,
                             s["temperature"], dweight=self.head_grad())
-        self._trunk_bwd(s, dhf)
+        extra = None
+        if "mtp" in s:
+            from .mtp import mtp_bwd
+            extra = mtp_bwd(self, s, float(self.mtp_scale))
+        self._trunk_bwd(s, dhf, extra)
 
     # ------------------------------------------------------------------ analytic FLOPs (for MFU)
     def flops_per_token(self, seqlen: int) -> float:

@@ -22,8 +22,13 @@ def param_layout(cfg: ModelConfig) -> "OrderedDict[str, tuple[int, ...]]":
     H, D = cfg.hidden_size, cfg.head_dim
     lay: OrderedDict[str, tuple[int, ...]] = OrderedDict()
     lay["model.embed_tokens.weight"] = (cfg.vocab_size, H)
-    for l in range(cfg.num_hidden_layers):
+    for l in range(cfg.num_hidden_layers + cfg.num_nextn_predict_layers):
         p = f"model.layers.{l}."
+        if l >= cfg.num_hidden_layers:          # multi-token-prediction module: input norms + projection, then a decoder layer
+            lay[p + "enorm.weight"] = (H,)
+            lay[p + "hnorm.weight"] = (H,)
+            lay[p + "eh_proj.weight"] = (H, 2 * H)
+            lay[p + "shared_head.norm.weight"] = (H,)
         lay[p + "input_layernorm.weight"] = (H,)
         lay[p + "self_attn.qkv_proj.weight"] = (cfg.qkv_size, H)
         if cfg.attention_bias:

@@ -82,6 +82,7 @@ class TPDenseModel:
         assert cfg.num_experts == 0
         assert not cfg.attention_bias, "tensor-parallel layout of q/k/v biases is not built yet (Qwen2 family: use data / sequence / pipeline parallelism)"
         assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
+        assert cfg.num_nextn_predict_layers == 0, "the multi-token-prediction module is trained by the data-parallel trainer only"
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
         self.shard_head = bool(vocab_parallel_head) and not cfg.tie_word_embeddings and tp.world > 1

@@ -158,6 +158,10 @@ class TrainerWorker(Worker, DistProfilerExtension):
         self.engine = PolicyEngine(self.model, ocfg, process_group=self.pg,
                                    max_token_len_per_gpu=int(_get(cfg, "max_token_len_per_gpu", 16384)) * self.ulysses_sequence_parallel_size,
                                    temperature=1.0)
+        # multi-token prediction: on when the model has such a module and the factor is set (the reference
+        # switches it with AXON_ENABLE_MTP and takes megatron's mtp_loss_scaling_factor)
+        if os.environ.get("AXON_ENABLE_MTP", "1") not in ("0", "false", "False"):
+            self.engine.mtp_loss_coef = float(_get(cfg, "mtp_loss_scaling_factor", _get(cfg, "megatron.mtp_loss_scaling_factor", 0.0)) or 0.0)
         if bool(_get(cfg, "fsdp.enable_activation_offload", False)) and not self._forward_only:
             from ..utils.activation_offload import ActivationOffloader
             target = getattr(self.model, "inner", self.model)

@@ -98,6 +98,7 @@ class PolicyEngine:
         self.world = dist.get_world_size(process_group) if (process_group is not None or dist.is_initialized()) else 1
         self.rank = dist.get_rank(process_group) if self.world > 1 else 0
         self.max_tokens = max_token_len_per_gpu
+        self.mtp_loss_coef = 0.0      # weight of the multi-token-prediction loss (models with such a module)
         self.temperature = temperature
         self.device = model.device
         n = model.params.numel
@@ -248,6 +249,13 @@ class PolicyEngine:
             return lp_leaf.grad, ent_leaf.grad if ent_coef != 0.0 else None
 
         mbs = [mb.to(self.device) for mb in mbs]
+        mtp = self.mtp_loss_coef > 0 and getattr(self.model.cfg, "num_nextn_predict_layers", 0) > 0 and hasattr(self.model, "mtp_scale")
+        if mtp:
+            # token-mean over the whole mini-batch (all ranks, all micro-batches): a sequence of n tokens has n - 2 targets
+            cnt = sum((mb.batch["attention_mask"].sum(1) - 2).clamp_min(0).sum() for mb in mbs).float().reshape(1)
+            if self.world > 1:
+                dist.all_reduce(cnt, group=self.pg)
+            self.model.mtp_scale = self.mtp_loss_coef / max(float(cnt), 1.0)
         packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device) for mb in mbs]
         if hasattr(self.model, "train_many"):
             # pipeline stages: the model orders forwards and backwards of the micro-batches (1F1B) and calls
@@ -257,7 +265,12 @@ class PolicyEngine:
         for mb, pk in zip(mbs, packs):
             lp_packed, ent_packed = self.model.forward(pk.batch, temp, save_for_backward=True)
             g_lp, g_ent = loss_step(mb, pk, lp_packed, ent_packed)
+            if mtp and self.model.mtp_last is not None:
+                nll, n = self.model.mtp_last
+                metrics.setdefault("mtp_loss", []).append(float(nll) / max(float(n), 1.0))
             self.model.backward(g_lp, g_ent)
+        if mtp:
+            self.model.mtp_scale = 0.0
         return metrics
 
     # ------------------------------------------------------------------ value head (critic / reward model)
