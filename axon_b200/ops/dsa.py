@@ -11,7 +11,8 @@ gathered latent rows: 512 value dims + 64 rotary dims, all heads share one key r
 
 Native paths. The indexer forward is one tcgen05 GEMM ``[S * heads, D] x [Skv, D]^T`` whose epilogue applies the
 ReLU and the head weight and sums the 32 accumulator rows of a query across the lanes of a warp
-(``csrc/gemm.cu``: ``IndexerEpi``), so the per-head scores never leave the SM. The rest has PyTorch
+(``csrc/gemm.cu``: ``IndexerEpi``), so the per-head scores never leave the SM; its backward at the selected keys is
+``csrc/dsa.cu`` (one block per query, warp per key, transposing butterfly for the 32 head dot products). The rest has PyTorch
 implementations here (fp32, chunked over queries so the gathered rows stay small), which are also the oracles.
 """
 from __future__ import annotations
@@ -49,7 +50,8 @@ def indexer_logits(q, k, w, ks, ke) -> torch.Tensor:
     wf = w.float().contiguous()
     ld = (Skv + 3) // 4 * 4
     out = (torch.zeros if Hi > 32 else torch.empty)(S, ld, dtype=torch.float32, device=q.device)
-    rc = C.lib().axb_indexer_fwd(C.ptr(q2), C.ptr(k), C.ptr(wf), C.ptr(ks.int().contiguous()), C.ptr(ke.int().contiguous()),
+    ks_i, ke_i = ks.int().contiguous(), ke.int().contiguous()          # named: they must outlive the launch call
+    rc = C.lib().axb_indexer_fwd(C.ptr(q2), C.ptr(k), C.ptr(wf), C.ptr(ks_i), C.ptr(ke_i),
                                  C.ptr(out), S, Hi, Skv, D, ctypes.c_longlong(q2.stride(0)), ctypes.c_longlong(k.stride(0)),
                                  ctypes.c_longlong(ld), C.ptr(C.status(q.device)), C.stream())
     C.launched(rc, "indexer_fwd")
@@ -85,6 +87,24 @@ def indexer_bwd_ref(g: torch.Tensor, idx: torch.Tensor, q: torch.Tensor, k: torc
         coef = (sc > 0).float() * gj * w[sl].float().unsqueeze(-1)  # [s, Hi, topk]
         dq[sl] = torch.einsum("shj,sjd->shd", coef, ksel)
         dk.index_add_(0, ixc.reshape(-1), torch.einsum("shj,shd->sjd", coef, q[sl].float()).reshape(-1, D))
+    return dq, dk, dw
+
+
+def indexer_bwd(g: torch.Tensor, idx: torch.Tensor, q: torch.Tensor, k: torch.Tensor, w: torch.Tensor):
+    """(dq, dk, dw) in fp32; native kernel for bf16 inputs with head dim 128 and 32 / 64 heads."""
+    S, Hi, D = q.shape
+    if not C.use_native(q) or Hi % 32 != 0 or Hi > 64 or D != 128 or q.dtype != torch.bfloat16:
+        return indexer_bwd_ref(g, idx, q, k, w)
+    q2, kc = q.reshape(S * Hi, D), k.contiguous()
+    assert q2.stride(1) == 1 and k.dtype == torch.bfloat16
+    gf, ix, wf = g.float().contiguous(), idx.int().contiguous(), w.float().contiguous()
+    dq = torch.empty(S, Hi, D, dtype=torch.float32, device=q.device)
+    dk = torch.zeros(k.shape[0], D, dtype=torch.float32, device=q.device)
+    dw = torch.empty(S, Hi, dtype=torch.float32, device=q.device)
+    rc = C.lib().axb_indexer_bwd(C.ptr(gf), C.ptr(ix), C.ptr(q2), C.ptr(kc), C.ptr(wf), C.ptr(dq), C.ptr(dk), C.ptr(dw),
+                                 S, Hi, ix.shape[1], k.shape[0], D, ctypes.c_longlong(q2.stride(0)),
+                                 ctypes.c_longlong(kc.stride(0)), C.stream())
+    C.launched(rc, "indexer_bwd")
     return dq, dk, dw
 
 
@@ -138,7 +158,7 @@ def sparse_mla_bwd_ref(do: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, out:
 class _SparseMLA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, kv, idx, scale, d_v):
-        out, lse = sparse_mla_fwd_ref(q, kv, idx, scale, d_v)
+        out, lse = sparse_mla_fwd(q, kv, idx, scale, d_v)
         ctx.save_for_backward(q, kv, idx, out, lse)
         ctx.scale, ctx.d_v = scale, d_v
         return out, lse
@@ -146,7 +166,7 @@ class _SparseMLA(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, _dlse):
         q, kv, idx, out, lse = ctx.saved_tensors
-        dq, dkv = sparse_mla_bwd_ref(do, q, kv, out, lse, idx, ctx.scale, ctx.d_v)
+        dq, dkv = sparse_mla_bwd(do, q, kv, out, lse, idx, ctx.scale, ctx.d_v)
         return dq, dkv.to(kv.dtype), None, None, None
 
 
@@ -170,9 +190,98 @@ class _IndexerLogitsAt(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         q, k, w, idx = ctx.saved_tensors
-        dq, dk, dw = indexer_bwd_ref(g, idx, q, k, w)
+        dq, dk, dw = indexer_bwd(g, idx, q, k, w)
         return dq.to(q.dtype), dk.to(k.dtype), dw.to(w.dtype), None
 
 
 def indexer_logits_at(q, k, w, idx):
     return _IndexerLogitsAt.apply(q, k, w, idx)
+
+
+# ---------------------------------------------------------------------- sparse latent attention on the tensor cores
+# Dense-masked formulation: per chunk of queries, scores against ALL keys run as one tcgen05 GEMM
+# ([queries x heads, Dk] x [Skv, Dk]^T - every head of a query shares the key rows, so the product is a plain
+# matrix product), keys outside a query's selection are masked, and P @ V is a second GEMM. This spends
+# Skv / topk times the FLOPs of a gathering kernel but runs them at GEMM speed without materialising
+# gathered rows; it is the CUDA path for contexts up to a few times ``topk``. A gathering tcgen05 kernel
+# (selected rows copied into swizzled shared memory, value dims split over a CTA pair because a
+# 128 x 512 fp32 accumulator fills tensor memory) is not built.
+_SCORE_BYTES = 256 << 20
+
+
+def _allowed(idx: torch.Tensor, skv_pad: int) -> torch.Tensor:
+    m = torch.zeros(idx.shape[0], skv_pad + 1, dtype=torch.bool, device=idx.device)
+    m.scatter_(1, torch.where(idx >= 0, idx, torch.full_like(idx, skv_pad)).long(), True)
+    return m[:, :skv_pad]
+
+
+def _pad_rows(kv: torch.Tensor, mult: int = 64) -> torch.Tensor:
+    n = kv.shape[0]
+    pad = (-n) % mult
+    return kv.contiguous() if pad == 0 else torch.cat([kv, kv.new_zeros(pad, kv.shape[1])])
+
+
+def _probs(qc, kvp, allowed, scale, H, lse=None):
+    """bf16 probabilities [s * H, Skv_pad] (and lse [s, H]) of one query chunk."""
+    from . import gemm as G
+    s = qc.shape[0]
+    sc = G.gemm_nt(qc.reshape(s * H, -1), kvp, out_dtype=torch.float32).view(s, H, -1)
+    sc.mul_(scale).masked_fill_(~allowed[:, None, :], NEG_INF)
+    if lse is None:
+        lse = torch.logsumexp(sc, -1)
+    p = torch.exp_(sc.sub_(lse.masked_fill(lse == NEG_INF, 0.0).unsqueeze(-1)))
+    return p.view(s * H, -1), lse
+
+
+def sparse_mla_fwd_tc(q, kv, idx, scale: float, d_v: int = 512):
+    from . import gemm as G
+    S, H, Dk = q.shape
+    kvp = _pad_rows(kv)
+    step = max(1, _SCORE_BYTES // (H * kvp.shape[0] * 4))
+    out = torch.empty(S, H, d_v, dtype=q.dtype, device=q.device)
+    lse = torch.empty(S, H, dtype=torch.float32, device=q.device)
+    v = kvp[:, :d_v]
+    for s0 in range(0, S, step):
+        sl = slice(s0, min(S, s0 + step))
+        p, l = _probs(q[sl].contiguous(), kvp, _allowed(idx[sl], kvp.shape[0]), scale, H)
+        out[sl] = G.gemm_nn(p.to(torch.bfloat16), v).view(-1, H, d_v)
+        lse[sl] = l
+    return out, lse
+
+
+def sparse_mla_bwd_tc(do, q, kv, out, lse, idx, scale: float, d_v: int = 512):
+    from . import gemm as G
+    S, H, Dk = q.shape
+    kvp = _pad_rows(kv)
+    n = kvp.shape[0]
+    step = max(1, _SCORE_BYTES // (H * n * 4))
+    dq = torch.empty_like(q)
+    dkv = torch.zeros(n, Dk, dtype=torch.float32, device=q.device)
+    dv = torch.zeros(n, d_v, dtype=torch.float32, device=q.device)
+    vk = kvp[:, :d_v].contiguous()                                   # [Skv, d_v]: K-major operand of dP = dO V^T
+    for s0 in range(0, S, step):
+        sl = slice(s0, min(S, s0 + step))
+        qc, doc = q[sl].contiguous(), do[sl].contiguous().to(q.dtype)
+        s = qc.shape[0]
+        p, _ = _probs(qc, kvp, _allowed(idx[sl], n), scale, H, lse=lse[sl])
+        dp = G.gemm_nt(doc.view(s * H, d_v), vk, out_dtype=torch.float32)
+        delta = (doc.float() * out[sl].float()).sum(-1).view(s * H, 1)
+        ds = (p * (dp - delta) * scale).to(torch.bfloat16)
+        pb = p.to(torch.bfloat16)
+        dq[sl] = G.gemm_nn(ds, kvp).view(s, H, Dk)
+        G.gemm_tn(ds, qc.view(s * H, Dk), out=dkv, accumulate=True)
+        G.gemm_tn(pb, doc.view(s * H, d_v), out=dv, accumulate=True)
+    dkv[:, :d_v] += dv
+    return dq, dkv[: kv.shape[0]]
+
+
+def sparse_mla_fwd(q, kv, idx, scale: float, d_v: int = 512):
+    if C.use_native(q) and q.dtype == torch.bfloat16 and q.shape[2] % 8 == 0 and d_v % 8 == 0:
+        return sparse_mla_fwd_tc(q, kv, idx, scale, d_v)
+    return sparse_mla_fwd_ref(q, kv, idx, scale, d_v)
+
+
+def sparse_mla_bwd(do, q, kv, out, lse, idx, scale: float, d_v: int = 512):
+    if C.use_native(q) and q.dtype == torch.bfloat16 and q.shape[2] % 8 == 0 and d_v % 8 == 0:
+        return sparse_mla_bwd_tc(do, q, kv, out, lse, idx, scale, d_v)
+    return sparse_mla_bwd_ref(do, q, kv, out, lse, idx, scale, d_v)

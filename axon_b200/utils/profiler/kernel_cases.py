@@ -291,6 +291,48 @@ def case_gemm_rs(small):
     return run, dict(flops=2.0 * T * N * K, bytes=2.0 * (T * K + N * K + T * N), shape=[T, N, K])
 
 
+def case_indexer_fwd(small):
+    """Lightning indexer logits: 32 heads x 128 dims, S queries against Skv keys (one GEMM with the head sum
+    in the epilogue). Bytes: q, k once, fp32 logits written once."""
+    from ...ops import dsa
+    S, Skv, Hi, D = (1024, 4096, 32, 128) if small else (4096, 8192, 32, 128)
+    q, k = bf(S, Hi, D, scale=0.3), bf(Skv, D, scale=0.3)
+    w = torch.randn(S, Hi, device="cuda")
+    ks = torch.zeros(S, dtype=torch.int32, device="cuda")
+    ke = torch.full((S,), Skv, dtype=torch.int32, device="cuda")
+
+    def run():
+        dsa.indexer_logits(q, k, w, ks, ke)
+    return run, dict(flops=2.0 * S * Hi * Skv * D, bytes=2.0 * (S * Hi * D + Skv * D) + 4.0 * S * Skv, shape=[S, Hi, Skv, D])
+
+
+def case_indexer_bwd(small):
+    """Lightning indexer backward at 2048 selected keys per query (one block per query, warp per key)."""
+    from ...ops import dsa
+    S, Skv, Hi, D, topk = (512, 4096, 32, 128, 2048) if small else (2048, 8192, 32, 128, 2048)
+    q, k = bf(S, Hi, D, scale=0.3), bf(Skv, D, scale=0.3)
+    w = torch.randn(S, Hi, device="cuda")
+    idx = torch.stack([torch.randperm(Skv, device="cuda")[:topk] for _ in range(S)]).int()
+    g = torch.randn(S, topk, device="cuda")
+
+    def run():
+        dsa.indexer_bwd(g, idx, q, k, w)
+    return run, dict(flops=6.0 * S * topk * Hi * D, bytes=2.0 * S * topk * D + 4.0 * S * topk * D, shape=[S, Hi, topk, D])
+
+
+def case_sparse_mla_fwd(small):
+    """Sparse latent attention forward, dense-masked on the GEMM kernels: 64 heads, 576-dim rows, top-2048 of Skv
+    keys. FLOPs counted for the selected keys only (what a gathering kernel would spend)."""
+    from ...ops import dsa
+    S, Skv, H, Dk, d_v, topk = (512, 4096, 64, 576, 512, 2048) if small else (2048, 8192, 64, 576, 512, 2048)
+    q, kv = bf(S, H, Dk, scale=0.2), bf(Skv, Dk, scale=0.2)
+    idx = torch.stack([torch.randperm(Skv, device="cuda")[:topk] for _ in range(S)]).int()
+
+    def run():
+        dsa.sparse_mla_fwd(q, kv, idx, Dk ** -0.5, d_v)
+    return run, dict(flops=2.0 * S * H * topk * (Dk + d_v), bytes=2.0 * (S * H * (Dk + d_v) + Skv * Dk), shape=[S, H, Skv, topk])
+
+
 def case_moe_grouped(small):
     from ...ops import moe as M
     T, E, k, H, F = (2048, 128, 8, 2048, 768) if small else (8192, 128, 8, 2048, 768)
@@ -304,7 +346,7 @@ def case_moe_grouped(small):
                                                      shape=[T * k, 2 * F, H, E])
 
 
-CASES = {"gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode, "gemm_stream": case_gemm_stream,
+CASES = {"indexer_fwd": case_indexer_fwd, "indexer_bwd": case_indexer_bwd, "sparse_mla_fwd": case_sparse_mla_fwd, "gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode, "gemm_stream": case_gemm_stream,
          "gemm_decode_chain": case_gemm_decode_chain, "train_microbatch": case_train_microbatch,
          "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode, "paged_decode_grpo_plain": case_paged_decode_grpo_plain,
          "paged_decode_grpo_shared": case_paged_decode_grpo_shared,

@@ -363,3 +363,72 @@ extern "C" int axb_rs_reduce(const void* staging, const void* residual, void* ou
       static_cast<__nv_bfloat16*>(out), world, rows, N, ld, ldo);
   return check_launch();
 }
+
+// ------------------------------------------------------------------------- lightning indexer
+// logits[s][j] = sum_h w[s][h] * relu(q[s][h] . k[j]) inside the window [ks[s], ke[s]), -inf outside.
+// The product runs as one GEMM with rows (s, h) and columns j. A warp of the epilogue holds 32 consecutive
+// rows = 32 heads of ONE query (heads is a multiple of 32), so ReLU, head weight and the sum over heads happen
+// on the accumulator: a transposing butterfly leaves lane l with the head-sum of column l, and the warp
+// writes 32 consecutive logits. With more than 32 heads the partial sums of a query's warps are added
+// with atomics into a zeroed buffer (two addends commute, so 64 heads stay bit-reproducible).
+namespace axb {
+struct IndexerEpi {
+  struct Params {
+    float* logits;     // [S][ld]
+    long long ld;
+    const float* w;    // [S * heads]
+    const int* ks;
+    const int* ke;
+    int heads;
+  };
+  const Params& p;
+  const GemmShape& sh;
+  int row;
+  __device__ IndexerEpi(const Params& p_, int, int, int row_, const GemmShape& sh_, int) : p(p_), sh(sh_), row(row_) {}
+  __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
+    if (col0 >= sh.N) return;                       // uniform over the warp
+    const int lane = threadIdx.x & 31;
+    const float wv = row < sh.M ? p.w[row] : 0.0f;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(__uint_as_float(acc[j]), 0.0f) * wv;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < off; ++i) {
+        const float send = upper ? v[i] : v[i + off];
+        const float keep = upper ? v[i + off] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+    const int row0 = row - lane;                    // first row of the warp: head 0 of a 32-head group
+    if (row0 >= sh.M) return;
+    const int s = row0 / p.heads;
+    const int col = col0 + lane;
+    if (col >= sh.N) return;
+    const float out = (col >= p.ks[s] && col < p.ke[s]) ? v[0] : -INFINITY;
+    float* dst = p.logits + (long long)s * p.ld + col;
+    if (p.heads == 32) *dst = out;
+    else atomicAdd(dst, out);
+  }
+  __device__ __forceinline__ void finish() {}
+};
+}  // namespace axb
+
+// q: bf16 [S * heads][ldq] (row = (s, h)), k: bf16 [Skv][ldk], w: fp32 [S * heads], logits: fp32 [S][ld]
+// (zeroed by the caller when heads > 32). heads % 32 == 0, D % 64 == 0.
+extern "C" int axb_indexer_fwd(const void* q, const void* k, const float* w, const int* ks, const int* ke, float* logits,
+                               int S, int heads, int Skv, int D, long long ldq, long long ldk, long long ld, int* status,
+                               void* stream) {
+  using namespace axb;
+  if (S <= 0 || Skv <= 0 || heads <= 0 || heads % 32 != 0 || D <= 0 || D % GEMM_BK != 0 || (ldq & 7) || (ldk & 7))
+    return AXB_LAUNCH_BAD_ARG;
+  IndexerEpi::Params ep{logits, ld, w, ks, ke, heads};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long M = (long long)S * heads;
+  if (M > 0x7fffffffLL) return AXB_LAUNCH_BAD_ARG;
+  if (Skv % 256 == 0 || Skv > 2048)
+    return launch_gemm_inst<256, false, false, IndexerEpi>(q, k, (int)M, Skv, D, ldq, ldk, ep, status, st, 0);
+  return launch_gemm_inst<128, false, false, IndexerEpi>(q, k, (int)M, Skv, D, ldq, ldk, ep, status, st, 0);
+}

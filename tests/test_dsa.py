@@ -75,3 +75,89 @@ def test_sparse_mla_matches_dense_masked_attention():
     o2, _ = dsa.sparse_mla(qb, kvb, idx, scale, d_v)
     (o2 * do).sum().backward()
     torch.testing.assert_close(kvb.grad, kva.grad, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Hi,S,Skv", [(32, 200, 1000), (64, 96, 4096), (32, 1024, 2304)])
+def test_native_indexer_matches_reference(Hi, S, Skv):
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(Hi + S)
+    D = 128
+    q = (torch.randn(S, Hi, D, generator=g) * 0.5).to(dev).to(torch.bfloat16)
+    k = (torch.randn(Skv, D, generator=g) * 0.5).to(dev).to(torch.bfloat16)
+    w = torch.randn(S, Hi, generator=g).to(dev)
+    ks = torch.randint(0, 50, (S,), generator=g).to(dev)
+    ke = (ks + torch.randint(1, Skv, (S,), generator=g).to(dev)).clamp_max(Skv)
+    got = dsa.indexer_logits(q, k, w, ks, ke)
+    ref = dsa.indexer_logits_ref(q, k, w, ks, ke)
+    from axon_b200.ops import _common as C
+    C.check_status()
+    assert torch.equal(torch.isinf(got), torch.isinf(ref))
+    fin = ~torch.isinf(ref)
+    err = (got[fin] - ref[fin]).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref[fin].abs().max().item()), err
+    again = dsa.indexer_logits(q, k, w, ks, ke)
+    assert torch.equal(again, got)                      # reproducible, also with two warps per query
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Hi", [32, 64])
+def test_native_indexer_backward_matches_reference(Hi):
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(Hi)
+    S, Skv, D, topk = 150, 700, 128, 96
+    q = (torch.randn(S, Hi, D, generator=g) * 0.5).to(dev).to(torch.bfloat16)
+    k = (torch.randn(Skv, D, generator=g) * 0.5).to(dev).to(torch.bfloat16)
+    w = torch.randn(S, Hi, generator=g).to(dev)
+    ks = torch.zeros(S, dtype=torch.int64, device=dev)
+    ke = torch.randint(40, Skv, (S,), generator=g).to(dev)
+    idx = dsa.indexer_topk(dsa.indexer_logits(q, k, w, ks, ke), topk)
+    assert (idx < 0).any() and (idx >= 0).any()
+    gl = torch.randn(S, topk, generator=g).to(dev) * (idx >= 0)
+    dq, dk, dw = dsa.indexer_bwd(gl, idx, q, k, w)
+    rq, rk, rw = dsa.indexer_bwd_ref(gl, idx, q, k, w)
+    from axon_b200.ops import _common as C
+    C.check_status()
+    for a, b in ((dq, rq), (dk, rk), (dw, rw)):
+        assert (a - b).abs().max().item() < 1e-3 * max(1.0, b.abs().max().item())
+
+
+def test_dense_masked_tensor_core_formulation_matches_gathering_one():
+    """Runs the GEMM formulation through the CPU fall-backs of the GEMM ops (probabilities pass through bf16)."""
+    q, k, w, ks, ke, qm, kv = _inputs(S=40, Skv=70, H=4, Dk=24)
+    idx = dsa.indexer_topk(dsa.indexer_logits(q, k, w, ks, ke), 12)
+    idx[5] = -1
+    out_r, lse_r = dsa.sparse_mla_fwd_ref(qm, kv, idx, 0.3, 16)
+    out, lse = dsa.sparse_mla_fwd_tc(qm, kv, idx, 0.3, 16)
+    torch.testing.assert_close(lse, lse_r, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(out, out_r, rtol=2e-2, atol=2e-2)
+    do = torch.randn(out.shape, generator=torch.Generator().manual_seed(4))
+    dq_r, dkv_r = dsa.sparse_mla_bwd_ref(do, qm, kv, out_r, lse_r, idx, 0.3, 16)
+    dq, dkv = dsa.sparse_mla_bwd_tc(do, qm, kv, out_r, lse_r, idx, 0.3, 16)
+    assert (dq - dq_r).abs().max() < 3e-2 * max(1.0, float(dq_r.abs().max()))
+    assert (dkv - dkv_r).abs().max() < 3e-2 * max(1.0, float(dkv_r.abs().max()))
+
+
+@pytest.mark.gpu
+def test_sparse_mla_on_gpu_matches_reference():
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(7)
+    S, Skv, H, Dk, d_v, topk = 300, 1000, 16, 576, 512, 128
+    q = (torch.randn(S, H, Dk, generator=g) * 0.3).to(dev).to(torch.bfloat16)
+    kv = (torch.randn(Skv, Dk, generator=g) * 0.3).to(dev).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(Skv, generator=g)[:topk] for _ in range(S)]).int().to(dev)
+    idx[:, -5:] = -1
+    idx[7] = -1
+    scale = Dk ** -0.5
+    out, lse = dsa.sparse_mla_fwd(q, kv, idx, scale, d_v)
+    out_r, lse_r = dsa.sparse_mla_fwd_ref(q, kv, idx, scale, d_v)
+    from axon_b200.ops import _common as C
+    C.check_status()
+    torch.testing.assert_close(lse, lse_r, rtol=2e-3, atol=2e-3)
+    assert (out.float() - out_r.float()).abs().max() < 2e-2
+    do = (torch.randn(S, H, d_v, generator=g) * 0.3).to(dev).to(torch.bfloat16)
+    dq, dkv = dsa.sparse_mla_bwd(do, q, kv, out, lse, idx, scale, d_v)
+    dq_r, dkv_r = dsa.sparse_mla_bwd_ref(do, q, kv, out_r, lse_r, idx, scale, d_v)
+    C.check_status()
+    assert (dq.float() - dq_r.float()).abs().max() < 3e-2 * max(1.0, float(dq_r.float().abs().max()))
+    assert (dkv - dkv_r).abs().max() < 3e-2 * max(1.0, float(dkv_r.abs().max()))
