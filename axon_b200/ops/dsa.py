@@ -9,9 +9,9 @@ gathered latent rows: 512 value dims + 64 rotary dims, all heads share one key r
     idx[s]       = top-k of logits[s]
     out[s, h]    = softmax_j in idx[s] (scale * q_mla[s, h] . kv[j]) @ kv[j, :512]
 
-Native paths. The indexer forward is one tcgen05 GEMM ``[S * heads, D] x [Skv, D]^T`` whose epilogue applies the
-ReLU and the head weight and sums the 32 accumulator rows of a query across the lanes of a warp
-(``csrc/gemm.cu``: ``IndexerEpi``), so the per-head scores never leave the SM; its backward at the selected keys is
+Native paths. The indexer forward is one tcgen05 GEMM ``[Skv, D] x [S * heads, D]^T`` (keys on the 128-row side)
+whose epilogue applies the ReLU and the head weight and sums the 32 heads a thread holds in its accumulator
+registers (``csrc/gemm.cu``: ``IndexerEpi``), so the per-head scores never leave the SM; its backward at the selected keys is
 ``csrc/dsa.cu`` (one block per query, warp per key, transposing butterfly for the 32 head dot products). The rest has PyTorch
 implementations here (fp32, chunked over queries so the gathered rows stay small), which are also the oracles.
 """
@@ -42,14 +42,14 @@ def indexer_logits_ref(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, ks: to
 
 def indexer_logits(q, k, w, ks, ke) -> torch.Tensor:
     S, Hi, D = q.shape
-    if not C.use_native(q) or Hi % 32 != 0 or D % 64 != 0:
+    if not C.use_native(q) or Hi not in (32, 64, 128, 256) or D % 64 != 0:
         return indexer_logits_ref(q, k, w, ks, ke)
     Skv = k.shape[0]
     q2 = q.reshape(S * Hi, D)
     assert q2.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q2.stride(1) == 1 and k.stride(1) == 1
     wf = w.float().contiguous()
     ld = (Skv + 3) // 4 * 4
-    out = (torch.zeros if Hi > 32 else torch.empty)(S, ld, dtype=torch.float32, device=q.device)
+    out = torch.empty(S, ld, dtype=torch.float32, device=q.device)
     ks_i, ke_i = ks.int().contiguous(), ke.int().contiguous()          # named: they must outlive the launch call
     rc = C.lib().axb_indexer_fwd(C.ptr(q2), C.ptr(k), C.ptr(wf), C.ptr(ks_i), C.ptr(ke_i),
                                  C.ptr(out), S, Hi, Skv, D, ctypes.c_longlong(q2.stride(0)), ctypes.c_longlong(k.stride(0)),
@@ -222,15 +222,39 @@ def _pad_rows(kv: torch.Tensor, mult: int = 64) -> torch.Tensor:
 
 
 def _probs(qc, kvp, allowed, scale, H, lse=None):
-    """bf16 probabilities [s * H, Skv_pad] (and lse [s, H]) of one query chunk."""
+    """bf16-valued probabilities [s * H, Skv_pad] (and lse [s, H]) of one query chunk. On CUDA the mask, the
+    scale, the log-sum-exp and the exponent are one kernel over the fp32 scores (``axb_masked_softmax``)."""
     from . import gemm as G
     s = qc.shape[0]
-    sc = G.gemm_nt(qc.reshape(s * H, -1), kvp, out_dtype=torch.float32).view(s, H, -1)
+    sc = G.gemm_nt(qc.reshape(s * H, -1), kvp, out_dtype=torch.float32)
+    n = sc.shape[1]
+    if C.use_native(sc):
+        p = torch.empty(s * H, n, dtype=torch.bfloat16, device=sc.device)
+        ok = allowed.to(torch.uint8).contiguous()
+        lse_in = None if lse is None else lse.reshape(-1).float().contiguous()
+        lse_out = torch.empty(s * H, dtype=torch.float32, device=sc.device) if lse is None else None
+        rc = C.lib().axb_masked_softmax(C.ptr(sc), C.ptr(ok), C.ptr(p), C.ptr(lse_out), C.ptr(lse_in), ctypes.c_longlong(s * H), H, n,
+                                        ctypes.c_longlong(sc.stride(0)), ctypes.c_longlong(n), ctypes.c_float(scale), C.stream())
+        C.launched(rc, "masked_softmax")
+        return p, (lse if lse is not None else lse_out.view(s, H))
+    sc = sc.view(s, H, -1)
     sc.mul_(scale).masked_fill_(~allowed[:, None, :], NEG_INF)
     if lse is None:
         lse = torch.logsumexp(sc, -1)
     p = torch.exp_(sc.sub_(lse.masked_fill(lse == NEG_INF, 0.0).unsqueeze(-1)))
     return p.view(s * H, -1), lse
+
+
+def _dscores(p, dp, delta, scale):
+    """bf16 ``p * (dp - delta) * scale``."""
+    if C.use_native(p) and p.dtype == torch.bfloat16:
+        ds = torch.empty_like(p)
+        d = delta.reshape(-1).float().contiguous()
+        rc = C.lib().axb_softmax_bwd(C.ptr(p), C.ptr(dp), C.ptr(d), C.ptr(ds), ctypes.c_longlong(p.shape[0]), p.shape[1],
+                                     ctypes.c_longlong(p.stride(0)), ctypes.c_longlong(dp.stride(0)), ctypes.c_float(scale), C.stream())
+        C.launched(rc, "softmax_bwd")
+        return ds
+    return (p.float() * (dp - delta) * scale).to(torch.bfloat16)
 
 
 def sparse_mla_fwd_tc(q, kv, idx, scale: float, d_v: int = 512):
@@ -266,8 +290,8 @@ def sparse_mla_bwd_tc(do, q, kv, out, lse, idx, scale: float, d_v: int = 512):
         p, _ = _probs(qc, kvp, _allowed(idx[sl], n), scale, H, lse=lse[sl])
         dp = G.gemm_nt(doc.view(s * H, d_v), vk, out_dtype=torch.float32)
         delta = (doc.float() * out[sl].float()).sum(-1).view(s * H, 1)
-        ds = (p * (dp - delta) * scale).to(torch.bfloat16)
         pb = p.to(torch.bfloat16)
+        ds = _dscores(pb if p.is_cuda else p, dp, delta, scale)
         dq[sl] = G.gemm_nn(ds, kvp).view(s, H, Dk)
         G.gemm_tn(ds, qc.view(s * H, Dk), out=dkv, accumulate=True)
         G.gemm_tn(pb, doc.view(s * H, d_v), out=dv, accumulate=True)

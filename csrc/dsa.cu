@@ -110,6 +110,68 @@ indexer_bwd_kernel(const float* __restrict__ g, const int* __restrict__ idx, con
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Row softmax over the selected keys for the dense-masked form of sparse latent attention.
+// scores: fp32 [rows][ld] (raw q.k of one query chunk, rows = (query, head)); allowed: bytes [queries][n]
+// (1 = the query selected this key). Writes p = exp(scale * score - lse) as bf16 (0 where not selected) and,
+// unless ``lse_in`` is given (backward: reuse the forward's), the row's log-sum-exp. One block per row, two
+// passes over the row (the second one hits L2); a row without any selected key gives zeros and lse = -inf.
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    const float u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, u) : v + u;
+  }
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  v = red[0];
+  for (int i = 1; i < nw; ++i) v = is_max ? fmaxf(v, red[i]) : v + red[i];
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+masked_softmax_kernel(const float* __restrict__ scores, const unsigned char* __restrict__ allowed,
+                      __nv_bfloat16* __restrict__ p, float* __restrict__ lse_out, const float* __restrict__ lse_in,
+                      int heads, int n, long long ld, long long ldp, float scale) {
+  __shared__ float red[8];
+  const long long r = blockIdx.x;
+  const float* row = scores + r * ld;
+  const unsigned char* ok = allowed + (r / heads) * (long long)n;
+  __nv_bfloat16* out = p + r * ldp;
+  float lse;
+  if (lse_in != nullptr) {
+    lse = lse_in[r];
+  } else {
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j < n; j += blockDim.x)
+      if (ok[j]) m = fmaxf(m, row[j] * scale);
+    m = block_reduce(m, true, red);
+    float sum = 0.0f;
+    if (m > -INFINITY)
+      for (int j = threadIdx.x; j < n; j += blockDim.x)
+        if (ok[j]) sum += __expf(row[j] * scale - m);
+    sum = block_reduce(sum, false, red);
+    lse = (m > -INFINITY) ? m + __logf(sum) : -INFINITY;
+    if (threadIdx.x == 0) lse_out[r] = lse;
+  }
+  const float base = (lse > -INFINITY) ? lse : 0.0f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x)
+    out[j] = __float2bfloat16(ok[j] ? __expf(row[j] * scale - base) : 0.0f);
+}
+
+// ds = p * (dp - delta[row]) * scale as bf16 (p is already 0 outside the selection).
+__global__ void __launch_bounds__(256)
+softmax_bwd_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ dp, const float* __restrict__ delta,
+                   __nv_bfloat16* __restrict__ ds, int n, long long ldp, long long lddp, float scale) {
+  const long long r = blockIdx.x;
+  const float d = delta[r];
+  for (int j = threadIdx.x; j < n; j += blockDim.x)
+    ds[r * ldp + j] = __float2bfloat16(__bfloat162float(p[r * ldp + j]) * (dp[r * lddp + j] - d) * scale);
+}
+
 }  // namespace
 
 // g: fp32 [S][topk], idx: int32 [S][topk] (-1 = none), q: bf16 rows (s, h) with pitch ldq, k: bf16 [Skv][ldk],
@@ -131,5 +193,25 @@ extern "C" int axb_indexer_bwd(const float* g, const int* idx, const void* q, co
   indexer_bwd_kernel<<<S, IDX_WARPS * 32, smem, static_cast<cudaStream_t>(stream)>>>(
       g, idx, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), w, dq, dk, dw, heads, topk, Skv,
       ldq, ldk);
+  return check_launch();
+}
+
+extern "C" int axb_masked_softmax(const float* scores, const void* allowed, void* p, float* lse_out, const float* lse_in,
+                                  long long rows, int heads, int n, long long ld, long long ldp, float scale, void* stream) {
+  using namespace axb;
+  if (rows <= 0 || rows > 0x7fffffffLL || heads <= 0 || n <= 0 || (lse_out == nullptr && lse_in == nullptr))
+    return AXB_LAUNCH_BAD_ARG;
+  masked_softmax_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      scores, static_cast<const unsigned char*>(allowed), static_cast<__nv_bfloat16*>(p), lse_out, lse_in, heads, n, ld, ldp,
+      scale);
+  return check_launch();
+}
+
+extern "C" int axb_softmax_bwd(const void* p, const float* dp, const float* delta, void* ds, long long rows, int n,
+                               long long ldp, long long lddp, float scale, void* stream) {
+  using namespace axb;
+  if (rows <= 0 || rows > 0x7fffffffLL || n <= 0) return AXB_LAUNCH_BAD_ARG;
+  softmax_bwd_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(p), dp, delta, static_cast<__nv_bfloat16*>(ds), n, ldp, lddp, scale);
   return check_launch();
 }

@@ -366,11 +366,12 @@ extern "C" int axb_rs_reduce(const void* staging, const void* residual, void* ou
 
 // ------------------------------------------------------------------------- lightning indexer
 // logits[s][j] = sum_h w[s][h] * relu(q[s][h] . k[j]) inside the window [ks[s], ke[s]), -inf outside.
-// The product runs as one GEMM with rows (s, h) and columns j. A warp of the epilogue holds 32 consecutive
-// rows = 32 heads of ONE query (heads is a multiple of 32), so ReLU, head weight and the sum over heads happen
-// on the accumulator: a transposing butterfly leaves lane l with the head-sum of column l, and the warp
-// writes 32 consecutive logits. With more than 32 heads the partial sums of a query's warps are added
-// with atomics into a zeroed buffer (two addends commute, so 64 heads stay bit-reproducible).
+// The product runs as one GEMM with the KEYS on the 128-row side and the (query, head) pairs as columns, so an
+// epilogue thread (one accumulator row = one key) holds 32 consecutive heads of one query in its registers:
+// ReLU, head weight and the sum over heads are 32 fused multiply-adds on the accumulator, no shuffles, and
+// the 32 lanes of a warp then write 32 consecutive logits of that query. With 64 / 128 / 256 heads the
+// partial sums of consecutive 32-column chunks are carried in a register (a tile is 128 / 256 columns wide,
+// so a query never straddles tiles); the result is bit-reproducible.
 namespace axb {
 struct IndexerEpi {
   struct Params {
@@ -383,52 +384,63 @@ struct IndexerEpi {
   };
   const Params& p;
   const GemmShape& sh;
-  int row;
-  __device__ IndexerEpi(const Params& p_, int, int, int row_, const GemmShape& sh_, int) : p(p_), sh(sh_), row(row_) {}
+  int row;             // key index
+  float carry;
+  // head weights and window of the NEXT chunk, loaded one chunk ahead: the epilogue visits a tile's chunks one
+  // after another with a tensor-memory load in between, so a load issued here has that long to arrive
+  float4 wn[8];
+  int ks_n, ke_n;
+  __device__ __forceinline__ void prefetch(int col0) {
+    if (col0 >= sh.N) return;
+    const float4* wv = reinterpret_cast<const float4*>(p.w + col0);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wn[j] = wv[j];
+    const int s = col0 / p.heads;
+    ks_n = p.ks[s];
+    ke_n = p.ke[s];
+  }
+  __device__ IndexerEpi(const Params& p_, int, int n_blk, int row_, const GemmShape& sh_, int)
+      : p(p_), sh(sh_), row(row_), carry(0.0f), ks_n(0), ke_n(0) {
+    prefetch(n_blk * tile_cols());
+  }
+  __device__ __forceinline__ int tile_cols() const { return (p.heads == 256 || sh.N >= 256) ? 256 : 128; }
   __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
-    if (col0 >= sh.N) return;                       // uniform over the warp
-    const int lane = threadIdx.x & 31;
-    const float wv = row < sh.M ? p.w[row] : 0.0f;
-    float v[32];
+    if (col0 >= sh.N) return;                       // columns = (s, h); N = S * heads is a multiple of 32
+    float sum = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = fmaxf(__uint_as_float(acc[j]), 0.0f) * wv;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-      const bool upper = (lane & off) != 0;
-#pragma unroll
-      for (int i = 0; i < off; ++i) {
-        const float send = upper ? v[i] : v[i + off];
-        const float keep = upper ? v[i + off] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-      }
+    for (int j = 0; j < 8; ++j) {
+      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 0]), 0.0f), wn[j].x, sum);
+      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 1]), 0.0f), wn[j].y, sum);
+      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 2]), 0.0f), wn[j].z, sum);
+      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 3]), 0.0f), wn[j].w, sum);
     }
-    const int row0 = row - lane;                    // first row of the warp: head 0 of a 32-head group
-    if (row0 >= sh.M) return;
-    const int s = row0 / p.heads;
-    const int col = col0 + lane;
-    if (col >= sh.N) return;
-    const float out = (col >= p.ks[s] && col < p.ke[s]) ? v[0] : -INFINITY;
-    float* dst = p.logits + (long long)s * p.ld + col;
-    if (p.heads == 32) *dst = out;
-    else atomicAdd(dst, out);
+    const int lo = ks_n, hi = ke_n;
+    const int s = col0 / p.heads;
+    const int h0 = col0 - s * p.heads;
+    if (((col0 + 32) & (tile_cols() - 1)) != 0) prefetch(col0 + 32);      // not past the end of this tile
+    sum += (h0 == 0) ? 0.0f : carry;
+    carry = sum;
+    if (h0 + 32 < p.heads || row >= sh.M) return;
+    p.logits[(long long)s * p.ld + row] = (row >= lo && row < hi) ? sum : -INFINITY;
   }
   __device__ __forceinline__ void finish() {}
 };
 }  // namespace axb
 
-// q: bf16 [S * heads][ldq] (row = (s, h)), k: bf16 [Skv][ldk], w: fp32 [S * heads], logits: fp32 [S][ld]
-// (zeroed by the caller when heads > 32). heads % 32 == 0, D % 64 == 0.
+// q: bf16 [S * heads][ldq] (row = (s, h)), k: bf16 [Skv][ldk], w: fp32 [S * heads] (16-byte aligned),
+// logits: fp32 [S][ld] (every element written). heads in {32, 64, 128, 256}, D % 64 == 0.
 extern "C" int axb_indexer_fwd(const void* q, const void* k, const float* w, const int* ks, const int* ke, float* logits,
                                int S, int heads, int Skv, int D, long long ldq, long long ldk, long long ld, int* status,
                                void* stream) {
   using namespace axb;
-  if (S <= 0 || Skv <= 0 || heads <= 0 || heads % 32 != 0 || D <= 0 || D % GEMM_BK != 0 || (ldq & 7) || (ldk & 7))
+  if (S <= 0 || Skv <= 0 || (heads != 32 && heads != 64 && heads != 128 && heads != 256) || D <= 0 || D % GEMM_BK != 0 ||
+      (ldq & 7) || (ldk & 7) || (reinterpret_cast<uintptr_t>(w) & 15))
     return AXB_LAUNCH_BAD_ARG;
   IndexerEpi::Params ep{logits, ld, w, ks, ke, heads};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long M = (long long)S * heads;
-  if (M > 0x7fffffffLL) return AXB_LAUNCH_BAD_ARG;
-  if (Skv % 256 == 0 || Skv > 2048)
-    return launch_gemm_inst<256, false, false, IndexerEpi>(q, k, (int)M, Skv, D, ldq, ldk, ep, status, st, 0);
-  return launch_gemm_inst<128, false, false, IndexerEpi>(q, k, (int)M, Skv, D, ldq, ldk, ep, status, st, 0);
+  const long long N = (long long)S * heads;
+  if (N > 0x7fffffffLL) return AXB_LAUNCH_BAD_ARG;
+  if (heads == 256 || N >= 256)       // a tile must hold whole queries: 256 columns unless the whole problem is narrower
+    return launch_gemm_inst<256, false, false, IndexerEpi>(k, q, Skv, (int)N, D, ldk, ldq, ep, status, st, 0);
+  return launch_gemm_inst<128, false, false, IndexerEpi>(k, q, Skv, (int)N, D, ldk, ldq, ep, status, st, 0);
 }
