@@ -406,16 +406,17 @@ struct IndexerEpi {
   __device__ __forceinline__ int tile_cols() const { return (p.heads == 256 || sh.N >= 256) ? 256 : 128; }
   __device__ __forceinline__ void chunk(int col0, const uint32_t (&acc)[32]) {
     if (col0 >= sh.N) return;                       // columns = (s, h); N = S * heads is a multiple of 32
-    float sum = 0.0f;
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;      // four chains: the adds of one chain wait on each other
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 0]), 0.0f), wn[j].x, sum);
-      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 1]), 0.0f), wn[j].y, sum);
-      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 2]), 0.0f), wn[j].z, sum);
-      sum = fmaf(fmaxf(__uint_as_float(acc[4 * j + 3]), 0.0f), wn[j].w, sum);
+      s0 = fmaf(fmaxf(__uint_as_float(acc[4 * j + 0]), 0.0f), wn[j].x, s0);
+      s1 = fmaf(fmaxf(__uint_as_float(acc[4 * j + 1]), 0.0f), wn[j].y, s1);
+      s2 = fmaf(fmaxf(__uint_as_float(acc[4 * j + 2]), 0.0f), wn[j].z, s2);
+      s3 = fmaf(fmaxf(__uint_as_float(acc[4 * j + 3]), 0.0f), wn[j].w, s3);
     }
+    float sum = (s0 + s1) + (s2 + s3);
     const int lo = ks_n, hi = ke_n;
-    const int s = col0 / p.heads;
+    const int s = col0 >> (31 - __clz(p.heads));           // heads is a power of two
     const int h0 = col0 - s * p.heads;
     if (((col0 + 32) & (tile_cols() - 1)) != 0) prefetch(col0 + 32);      // not past the end of this tile
     sum += (h0 == 0) ? 0.0f : carry;
