@@ -52,13 +52,15 @@ def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = 
             continue
         boxes = shard_rows(cfg, name, tp, tp_rank)
         rows = sum(b[1] - b[0] for b in boxes)
-        out[name] = (rows, boxes[0][3] - boxes[0][2])
+        out[name] = (rows, boxes[0][3] - boxes[0][2]) if len(full) > 1 else (rows,)
     return out
 
 
 def slice_full_param(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, tp_rank: int, shard_head: bool = False) -> torch.Tensor:
     if _replicated(name, shard_head) or tp == 1:
         return full
+    if full.dim() == 1:
+        return torch.cat([full[a:b] for a, b, _, _ in shard_rows(cfg, name, tp, tp_rank)], 0)
     return torch.cat([full[a:b, c:d] for a, b, c, d in shard_rows(cfg, name, tp, tp_rank)], 0)
 
 
@@ -80,7 +82,6 @@ def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, in
 class TPDenseModel:
     def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False):
         assert cfg.num_experts == 0
-        assert not cfg.attention_bias, "tensor-parallel layout of q/k/v biases is not built yet (Qwen2 family: use data / sequence / pipeline parallelism)"
         assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
         assert cfg.num_nextn_predict_layers == 0, "the multi-token-prediction module is trained by the data-parallel trainer only"
         self.cfg, self.tp = cfg, tp
@@ -158,6 +159,8 @@ class TPDenseModel:
         c, tp = self.cfg, self.tp
         h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
         qkv = tp.allgather_gemm(h, self._p(l, "self_attn.qkv_proj.weight"))
+        if c.attention_bias:
+            qkv += self._p(l, "self_attn.qkv_proj.bias")          # this rank's heads: the bias splits like the rows
         _, o, _ = self._attn(l, qkv, batch, tables, need_lse=False)
         ao = tp.gemm_reduce_scatter(o, self._p(l, "self_attn.o_proj.weight"))
         h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
@@ -174,6 +177,8 @@ class TPDenseModel:
         h, rstd1, _ = N.rmsnorm_fwd(xin, self._p(l, "input_layernorm.weight"), c.rms_norm_eps)
         h_full = tp.all_gather_rows(h)
         qkv = G.gemm_nt(h_full, self._p(l, "self_attn.qkv_proj.weight"))
+        if c.attention_bias:
+            qkv += self._p(l, "self_attn.qkv_proj.bias")
         qkv_r, o, lse = self._attn(l, qkv, batch, tables, need_lse=True)
         ao = tp.gemm_reduce_scatter(o, self._p(l, "self_attn.o_proj.weight"))
         h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
@@ -200,6 +205,8 @@ class TPDenseModel:
                                  self._g(l, "self_attn.q_norm.weight") if c.qk_norm else None,
                                  self._g(l, "self_attn.k_norm.weight") if c.qk_norm else None, c.rms_norm_eps)
         G.gemm_tn(dqkv, h_full, out=self._g(l, "self_attn.qkv_proj.weight"), accumulate=True)
+        if c.attention_bias:
+            self._g(l, "self_attn.qkv_proj.bias").add_(dqkv.float().sum(0))      # all rows, own columns: complete on this rank
         dh = tp.gemm_reduce_scatter(dqkv, self._p(l, "self_attn.qkv_proj.weight"), w_is_kn=True)
         return N.rmsnorm_bwd(dh, xin, self._p(l, "input_layernorm.weight"), rstd1, self._g(l, "input_layernorm.weight"), dres=dx1)
 

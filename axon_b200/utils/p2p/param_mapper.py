@@ -49,8 +49,8 @@ def convert_hf_to_vllm_param_name(name: str) -> tuple[str, str | None]:
 
 # split kind of every fused parameter of the in-house layout
 def split_kind(name: str) -> str:
-    if name.endswith("qkv_proj.weight"):
-        return "qkv"
+    if name.endswith("qkv_proj.weight") or name.endswith("qkv_proj.bias"):
+        return "qkv"                       # the bias vector splits like the rows of its matrix
     if name.endswith("gate_up_proj.weight"):
         return "gate_up"
     if name.endswith("o_proj.weight") or name.endswith("down_proj.weight"):
@@ -77,7 +77,7 @@ def shard_rows(cfg: ModelConfig, name: str, tp: int, tp_rank: int, ep: int = 1, 
         rep = cfg.num_attention_heads // g
         g0, g1 = tp_rank * g // tp, (tp_rank + 1) * g // tp
         qo, ko, vo = 0, cfg.q_size, cfg.q_size + cfg.kv_size
-        H = shape[1]
+        H = shape[1] if len(shape) > 1 else 1
         return [(qo + g0 * rep * D, qo + g1 * rep * D, 0, H), (ko + g0 * D, ko + g1 * D, 0, H),
                 (vo + g0 * D, vo + g1 * D, 0, H)]
     if kind == "gate_up":

@@ -80,7 +80,7 @@ def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["tp", "ep", "pp"])
+@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp"])
 def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
     run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
@@ -90,8 +90,8 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     from axon_b200.models.dense import PackedBatch
     from axon_b200.models.moe import build_model_for
     from axon_b200.utils.hf_model import load_hf_weights
-    preset, vocab = ("tiny-moe", 2048) if kind == "ep" else ("tiny-qwen3-untied", 4096)
-    cfg = _cfg(2 if kind == "tp" else 1, preset, 2 if kind == "ep" else 1, 2 if kind == "pp" else 1)
+    preset, vocab = ("tiny-moe", 2048) if kind == "ep" else (("tiny-qwen2" if kind == "tp-bias" else "tiny-qwen3-untied"), 4096)
+    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind == "ep" else 1, 2 if kind == "pp" else 1)
     d = str(tmp_path / "ck")
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, 2, vocab=vocab, save_dir=d)
     assert json.load(open(os.path.join(d, "model_parallel_config.json")))["world_size"] == 2
@@ -133,6 +133,18 @@ def test_pipeline_schedule_over_several_micro_batches(world, pp, cap):
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, world)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(np.mean(got[1]["actor/loss"]), np.mean(ref[1]["actor/loss"]), rtol=1e-3, atol=1e-5)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.timeout(900)
+def test_tensor_parallel_trainer_with_qkv_bias_matches_data_parallel_trainer():
+    """Qwen2-style q/k/v biases split with the heads of their rank; random biases make them matter."""
+    import numpy as np
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen2"), 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, "tiny-qwen2"), 2)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
