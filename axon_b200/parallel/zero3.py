@@ -1,0 +1,93 @@
+"""Parameter sharding (ZeRO-3 / FSDP style) over a data-parallel group.
+
+The reference's FSDP trainer shards every parameter over the ranks, all-gathers a layer's parameters before
+its forward / backward and reduce-scatters its gradients (``FSDP(...)`` / ``apply_fsdp2``,
+axon/trainer/fsdp_trainer.py:362-422). Here the big matrices of every layer are cut by rows (output features)
+into one shard per rank; all shards live at the same offset of one symmetric-memory buffer per rank, so
+
+* forward: ``y = x @ concat_r(W_r)^T`` is ONE kernel whose weight tiles come by TMA straight from the rank
+  that owns them (``axb_gemm_gather_weights``) - the gathered weight never exists and the NVLink transfer
+  overlaps the tensor-core work tile by tile;
+* backward: dgrad multiplies by an all-gathered copy (freed right after), wgrad makes the full-size fp32
+  gradient of the micro-batch and reduce-scatters it into the rank's gradient shard;
+* optimizer: every rank updates its own shards; embeddings, norms and the head stay replicated and their
+  gradients are all-reduced once per step.
+
+Ranks see different data and meet in these collectives layer by layer, so they run equal numbers of
+micro-batches. On CPU / gloo the same logic runs on all-gather + matmul (tests).
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import torch
+import torch.distributed as dist
+
+from .symm import PeerBarrier
+
+SHARDED_SUFFIXES = ("self_attn.qkv_proj.weight", "self_attn.o_proj.weight", "mlp.gate_up_proj.weight", "mlp.down_proj.weight")
+
+
+def is_sharded(name: str) -> bool:
+    return name.startswith("model.layers.") and name.endswith(SHARDED_SUFFIXES)
+
+
+def zero3_layout(cfg, world: int, row_multiple: int = 1) -> "OrderedDict[str, tuple[int, ...]]":
+    from ..models.params import param_layout
+    out: OrderedDict[str, tuple[int, ...]] = OrderedDict()
+    for name, shape in param_layout(cfg).items():
+        if is_sharded(name):
+            assert shape[0] % (world * row_multiple) == 0, \
+                f"{name}: {shape[0]} rows do not split into {world} shards of a multiple of {row_multiple} rows"
+            out[name] = (shape[0] // world, shape[1])
+        else:
+            out[name] = tuple(shape)
+    return out
+
+
+class ShardContext:
+    def __init__(self, group, device, fused: bool | None = None):
+        live = dist.is_initialized() and group is not None
+        self.group = group
+        self.world = dist.get_world_size(group) if live else 1
+        self.rank = dist.get_rank(group) if live else 0
+        self.device = torch.device(device)
+        if fused is None:
+            fused = self.world > 1 and self.device.type == "cuda" and dist.get_backend(group) == "nccl"
+        self.fused = bool(fused)
+        if self.fused:
+            assert self.world <= 8
+            self.barrier = PeerBarrier(group, self.device)
+            self._sync = torch.zeros(1, device=self.device)
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def all_gather_rows(self, shard: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return shard
+        full = torch.empty(self.world * shard.shape[0], *shard.shape[1:], dtype=shard.dtype, device=shard.device)
+        dist.all_gather(list(full.chunk(self.world)), shard.contiguous(), group=self.group)
+        return full
+
+    def reduce_scatter_rows(self, full: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks of ``full`` [F, K]; this rank's rows [F / W, K] are returned."""
+        if self.world == 1:
+            return full
+        per = full.shape[0] // self.world
+        if dist.get_backend(self.group) == "gloo":
+            dist.all_reduce(full, group=self.group)
+            return full[self.rank * per:(self.rank + 1) * per]
+        out = torch.empty(per, *full.shape[1:], dtype=full.dtype, device=full.device)
+        dist.reduce_scatter_tensor(out, full.contiguous(), group=self.group)
+        return out
+
+    def publish(self) -> None:
+        """After the local shards changed: every rank has finished writing before any peer reads again."""
+        if self.fused:
+            dist.all_reduce(self._sync, group=self.group)       # line the streams up before the bounded device barrier
+            self.barrier()
+        elif self.world > 1:
+            dist.barrier(self.group)

@@ -174,6 +174,10 @@ class TrainerWorker(Worker, DistProfilerExtension):
 
     def _make_state_manager(self):
         from ..utils.state import FSDPStateManager
+        if getattr(self.model, "shard", None) is not None:      # parameter shards: per-rank files + gathered HF export
+            from ..utils.state.megatron_state_manager import MegatronStateManager
+            return MegatronStateManager(self.model, self.engine, mp_group=self._mp_group, dp_rank=0, processing_class=self.tokenizer,
+                                        rank=self.rank, world_size=self.world_size, process_group=self.pg)
         return FSDPStateManager(self.model, self.engine, processing_class=self.tokenizer, rank=self.rank,
                                 world_size=self.world_size, process_group=self.pg)
 
@@ -197,6 +201,32 @@ class TrainerWorker(Worker, DistProfilerExtension):
                 model.base.load_hf_state_dict(dict(iter_hf_weights(model_path)))
             else:
                 model.base.init_random(seed=seed)
+            return model
+        if bool(_get(self.config, "fsdp.param_sharding", False)) and self.world_size > 1:
+            # ZeRO-3 / FSDP-style parameter shards over all ranks: the optimizer works on this rank's shards only
+            # (a group of its own), replicated parameters are summed by the model's hook
+            from ..models.zero3_dense import Zero3DenseModel
+            from ..parallel.zero3 import ShardContext
+            assert mcfg.num_experts == 0 and not self.model_kind.value_head and self.ulysses_sequence_parallel_size == 1, \
+                "parameter sharding is available on dense causal-LM models without sequence parallelism"
+            own = None
+            for r in range(self.world_size):
+                g = dist.new_group([r])
+                if r == self.rank:
+                    own = g
+            world_group = self.pg
+            self.pg = own
+            self._mp_group = world_group
+            model = Zero3DenseModel(mcfg, ShardContext(world_group, self.device), device=self.device, dtype=dtype)
+            model.recompute = str(_get(self.config, "recompute", "selective"))
+            if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+                from ..models.params import FlatParams
+                from ..utils.hf_model import iter_hf_weights
+                ref = FlatParams(mcfg, "cpu", dtype)
+                ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+                model.load_full_state(ref.views)
+            else:
+                model.init_random(seed=seed)
             return model
         sp = self.ulysses_sequence_parallel_size
         if sp > 1:

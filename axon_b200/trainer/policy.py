@@ -112,8 +112,8 @@ class PolicyEngine:
         self.state = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._host_state: dict | None = None
         self.fused = None
-        mp = getattr(model, "tp", None) or getattr(model, "ep", None) or getattr(model, "pp", None)
-        ep = getattr(model, "ep", None)
+        mp = self._model_parallel()
+        ep = getattr(model, "ep", None) or getattr(model, "shard", None)      # ranks with different data that meet in collectives layer by layer
         self.micro_group = ep.group if (ep is not None and ep.world > 1) else None      # ranks that must run equal micro-batch counts
         if fused_zero1 is None:
             # the fused step computes the clipping norm over the data-parallel group only; a model-parallel
@@ -122,6 +122,14 @@ class PolicyEngine:
                 dist.get_backend(process_group) == "nccl"
         if fused_zero1:
             self._enable_fused_zero1()
+
+    def _model_parallel(self):
+        """The context of the model's parallel group of any kind (tensor, expert, pipeline, parameter shards)."""
+        for attr in ("tp", "ep", "pp", "shard"):
+            ctx = getattr(self.model, attr, None)
+            if ctx is not None:
+                return ctx
+        return None
 
     def _enable_fused_zero1(self) -> None:
         """Move the parameters and the main-gradient buffer into symmetric memory and route the
@@ -373,6 +381,8 @@ class PolicyEngine:
                        self.cfg.beta2, self.cfg.eps, self.cfg.weight_decay, self.opt_step, self.state)
         if self.world > 1:
             self._all_gather_params()
+        if hasattr(self.model, "after_optim_step"):      # sharded parameters: tell the peers the new values are in place
+            self.model.after_optim_step()
         p.zero_grads()
         st = self.state.tolist()
         return {"grad_norm": st[1], "lr": lr, "skipped": st[3]}
@@ -381,7 +391,7 @@ class PolicyEngine:
         """With a tensor-, expert- or pipeline-parallel model the squared norm is the sum over the TP ranks of their sharded
         parameters plus the replicated parameters ONCE: sum_r S_r - (W - 1) * rep, where S_r is rank r's
         full-buffer value and rep the replicated part (equal on every rank)."""
-        tp = getattr(self.model, "tp", None) or getattr(self.model, "ep", None) or getattr(self.model, "pp", None)   # model-parallel group of any kind
+        tp = self._model_parallel()
         if tp is None or tp.world == 1:
             return
         rep = torch.zeros(1, dtype=torch.float32, device=self.device)

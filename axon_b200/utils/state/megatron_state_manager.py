@@ -70,12 +70,15 @@ class MegatronStateManager(FSDPStateManager):
         if self.rank == 0:
             with open(os.path.join(local_path, "model_parallel_config.json"), "w") as f:
                 json.dump({"tensor_model_parallel_size": self.tp, "expert_model_parallel_size": self.ep,
-                           "pipeline_model_parallel_size": self.pp, "world_size": self.world_size}, f, indent=1)
+                           "pipeline_model_parallel_size": self.pp, "world_size": self.world_size,
+                           "param_shards": getattr(getattr(self.model, "shard", None), "world", 1)}, f, indent=1)
         if want_hf and self.dp_rank == 0:
             inner = getattr(self.model, "inner", self.model)
             rep = inner.replicated_names() if hasattr(inner, "replicated_names") else ()
             r = self._mp_rank()
-            if self.pp > 1:            # stages hold disjoint parameters: collect them by name
+            if hasattr(inner, "gather_full"):      # the model knows how its shards make up the full tensors
+                full = inner.gather_full()
+            elif self.pp > 1:          # stages hold disjoint parameters: collect them by name
                 stages = [None] * self.pp
                 dist.all_gather_object(stages, {n: v.detach().cpu() for n, v in inner.params.views.items()}, group=self.mp_group)
                 full = {n: v for d in stages for n, v in d.items()}
