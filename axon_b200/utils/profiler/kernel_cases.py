@@ -333,6 +333,87 @@ def case_sparse_mla_fwd(small):
     return run, dict(flops=2.0 * S * H * topk * (Dk + d_v), bytes=2.0 * (S * H * (Dk + d_v) + Skv * Dk), shape=[S, H, Skv, topk])
 
 
+def case_zero1_reduce(small):
+    """Gradient reduce of the fused ZeRO-1 step with both "ranks" on this GPU: this rank's shard of every rank's fp32
+    gradient buffer is read once and summed (plus the sum of squares for the clipping norm)."""
+    import ctypes
+    from ...ops import _common as C
+    W = 2
+    n = (16 << 20) if small else (128 << 20)                  # elements of this rank's shard
+    grads = [torch.randn(W * n, device="cuda") for _ in range(W)]
+    ptrs = (ctypes.c_ulonglong * W)(*[g.data_ptr() for g in grads])
+    lib = C.lib()
+    reduced = torch.empty(n, device="cuda")
+    partials = torch.zeros(lib.axb_zero1_partials(), device="cuda")
+
+    def run():
+        rc = lib.axb_zero1_reduce(ptrs, 0, W, ctypes.c_longlong(0), ctypes.c_longlong(n), C.ptr(reduced), C.ptr(partials), C.stream())
+        C.launched(rc, "zero1_reduce")
+    return run, dict(flops=float(W * n), bytes=4.0 * n * (W + 1), shape=[W, n])
+
+
+def case_zero1_adamw_bcast(small):
+    """AdamW on this rank's shard whose epilogue stores the new bf16 values into every rank's parameter buffer
+    (both "ranks" on this GPU): fp32 master / m / v read and written, gradient read, W bf16 copies written."""
+    import ctypes
+    from ...ops import _common as C
+    W = 2
+    n = (16 << 20) if small else (128 << 20)
+    master, g, m, v = (torch.randn(n, device="cuda") * 0.01 for _ in range(4))
+    v = v.abs()
+    params = [torch.empty(W * n, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    ptrs = (ctypes.c_ulonglong * W)(*[t.data_ptr() for t in params])
+    state = torch.tensor([1.0, 1.0, 1.0, 0.0], device="cuda")       # [sumsq, norm, clip coefficient, skip]
+    lib = C.lib()
+    f = ctypes.c_float
+
+    def run():
+        rc = lib.axb_zero1_adamw_bcast(C.ptr(master), C.ptr(g), C.ptr(m), C.ptr(v), ptrs, W, ctypes.c_longlong(0), ctypes.c_longlong(n),
+                                       f(1e-5), f(0.9), f(0.95), f(1e-8), f(0.01), f(0.1), f(0.05), C.ptr(state), C.stream())
+        C.launched(rc, "zero1_adamw_bcast")
+    return run, dict(flops=12.0 * n, bytes=n * (4.0 * 7 + 2.0 * W), shape=[W, n])
+
+
+def _sync_plan(small, quant):
+    from ...utils.p2p.plan import copy_desc, plan_from_descs
+    R, Cc, L, W = (4096, 4096, 8, 2) if small else (4096, 4096, 48, 2)          # L matrices, split by rows over W destinations
+    src = bf(L * R * Cc, scale=0.05)
+    rows = []
+    per = R // W
+    for l in range(L):
+        for d in range(W):
+            desc = copy_desc((l * R + d * per) * Cc, l * per * Cc, per, Cc, Cc, Cc, d)
+            if quant:
+                desc["quant"], desc["scale_cols"] = 1, Cc // 128
+                desc["dst_scale_off"] = l * (per // 128) * (Cc // 128)
+            rows.append(desc)
+    return src, plan_from_descs(rows), L * per * Cc, L * (per // 128) * (Cc // 128), W, L * R * Cc
+
+
+def case_p2p_copy_plan(small):
+    """Weight-sync plan kernel, bf16 copies: one launch moves every routed slice (row shards of L matrices to two
+    destinations, both on this GPU)."""
+    from ...utils.p2p.plan import execute_plan
+    src, plan, dst_n, _, W, total = _sync_plan(small, False)
+    dst = [torch.empty(dst_n, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+
+    def run():
+        execute_plan(plan, src, dst)
+    return run, dict(flops=0.0, bytes=4.0 * total, shape=[total])
+
+
+def case_p2p_quant_plan(small):
+    """Weight-sync plan kernel with the bf16 -> fp8 (128 x 128 block scales) quantisation fused into the copy."""
+    from ...utils.p2p.plan import execute_plan
+    src, plan, dst_n, sc_n, W, total = _sync_plan(small, True)
+    dst = [torch.empty(dst_n, device="cuda", dtype=torch.uint8) for _ in range(W)]
+    scales = [torch.empty(sc_n, device="cuda") for _ in range(W)]
+
+    def run():
+        execute_plan(plan, src, dst, scale_flats=scales)
+    return run, dict(flops=0.0, bytes=3.0 * total, shape=[total])
+
+
 def case_moe_grouped(small):
     from ...ops import moe as M
     T, E, k, H, F = (2048, 128, 8, 2048, 768) if small else (8192, 128, 8, 2048, 768)
@@ -346,7 +427,7 @@ def case_moe_grouped(small):
                                                      shape=[T * k, 2 * F, H, E])
 
 
-CASES = {"indexer_fwd": case_indexer_fwd, "indexer_bwd": case_indexer_bwd, "sparse_mla_fwd": case_sparse_mla_fwd, "gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode, "gemm_stream": case_gemm_stream,
+CASES = {"zero1_reduce": case_zero1_reduce, "zero1_adamw_bcast": case_zero1_adamw_bcast, "p2p_copy_plan": case_p2p_copy_plan, "p2p_quant_plan": case_p2p_quant_plan, "indexer_fwd": case_indexer_fwd, "indexer_bwd": case_indexer_bwd, "sparse_mla_fwd": case_sparse_mla_fwd, "gemm_train": case_gemm_train, "gemm_wgrad": case_gemm_wgrad, "gemm_decode": case_gemm_decode, "gemm_stream": case_gemm_stream,
          "gemm_decode_chain": case_gemm_decode_chain, "train_microbatch": case_train_microbatch,
          "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd, "paged_decode": case_paged_decode, "paged_decode_grpo_plain": case_paged_decode_grpo_plain,
          "paged_decode_grpo_shared": case_paged_decode_grpo_shared,

@@ -110,20 +110,33 @@ zero1_adamw_bcast_kernel(float* __restrict__ master, const float* __restrict__ g
   const long long n8 = n / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
        i += (long long)gridDim.x * blockDim.x) {
+    // 8 consecutive elements per thread as two 16-byte vectors per array (the shard arrays start on
+    // allocation boundaries): scalar loads at a 32-byte stride would use an eighth of every sector
     float p[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const long long j = i * 8 + k;
-      const float g = grad[j] * coef;
-      const float mi = beta1 * m[j] + (1.f - beta1) * g;
-      const float vi = beta2 * v[j] + (1.f - beta2) * g * g;
-      m[j] = mi;
-      v[j] = vi;
-      float w = master[j];
-      w -= lr * wd * w;
-      w -= lr * (mi * inv_bc1) / (sqrtf(vi) * inv_sqrt_bc2 + eps);
-      master[j] = w;
-      p[k] = w;
+    for (int h = 0; h < 2; ++h) {
+      const float4 g4 = reinterpret_cast<const float4*>(grad)[i * 2 + h];
+      float4 m4 = reinterpret_cast<const float4*>(m)[i * 2 + h];
+      float4 v4 = reinterpret_cast<const float4*>(v)[i * 2 + h];
+      float4 w4 = reinterpret_cast<const float4*>(master)[i * 2 + h];
+      auto upd = [&](float g, float& mi, float& vi, float& w) {
+        g *= coef;
+        mi = beta1 * mi + (1.f - beta1) * g;
+        vi = beta2 * vi + (1.f - beta2) * g * g;
+        w -= lr * wd * w;
+        w -= lr * (mi * inv_bc1) / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+      };
+      upd(g4.x, m4.x, v4.x, w4.x);
+      upd(g4.y, m4.y, v4.y, w4.y);
+      upd(g4.z, m4.z, v4.z, w4.z);
+      upd(g4.w, m4.w, v4.w, w4.w);
+      reinterpret_cast<float4*>(m)[i * 2 + h] = m4;
+      reinterpret_cast<float4*>(v)[i * 2 + h] = v4;
+      reinterpret_cast<float4*>(master)[i * 2 + h] = w4;
+      p[4 * h + 0] = w4.x;
+      p[4 * h + 1] = w4.y;
+      p[4 * h + 2] = w4.z;
+      p[4 * h + 3] = w4.w;
     }
     uint4 o;
     o.x = pack_bf16x2(p[0], p[1]);
@@ -338,6 +351,9 @@ extern "C" int axb_zero1_adamw_bcast(float* master, const float* grad, float* m,
   PeerPtrs p;
   if (int rc = fill_ptrs(p, param_ptrs, world)) return rc;
   if (n <= 0 || (lo & 7) != 0) return AXB_LAUNCH_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m) |
+       reinterpret_cast<uintptr_t>(v)) & 15)
+    return AXB_LAUNCH_BAD_ARG;      // the kernel moves 16-byte vectors
   zero1_adamw_bcast_kernel<<<sm_count() * 4, 256, 0, (cudaStream_t)stream>>>(master, grad, m, v, p, world, lo, n, lr,
                                                                             beta1, beta2, eps, wd, bc1, bc2, state);
   return check_launch();
