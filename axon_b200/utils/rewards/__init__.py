@@ -172,6 +172,13 @@ def code_reward_fn(task_info: dict, action: str, config: RewardConfig | None = N
     tests = task_info.get("tests", task_info.get("ground_truth", []))
     if not tests:
         return RewardOutput(cfg.unk_error_reward, False, {"error": "no tests"})
+    source = task_info.get("data_source", "")
+    if source:
+        # dataset formats of the reference (taco / apps / code_contests, primeintellect, livecodebench / codeforces,
+        # leetcode, kodcode, humanevalplus); unknown sources raise, as there
+        from .code_graders import grade
+        good, details = grade(source, tests, code, timeout=cfg.code_timeout, entry_point=task_info.get("entry_point"))
+        return RewardOutput(cfg.correct_reward if good else cfg.incorrect_reward, good, details)
     passed = 0
     for t in tests:
         if "assert" in t:
