@@ -33,3 +33,35 @@ def test_process_image_and_video():
     frames = [Image.new("RGB", (120, 90), (i * 20, 0, 0)) for i in range(7)]
     vid = process_video({"type": "video", "video": frames}, nframes=4)
     assert len(vid) == 4 and len({f.size for f in vid}) == 1 and vid[0].size[0] % 28 == 0
+
+
+def test_precision_names_device_helpers_and_padding_round_trip(capsys):
+    import logging
+
+    import torch
+
+    from axon_b200 import globals as G
+    from axon_b200.trainer.algos.constants import VALID_BATCH_REDUCE, VALID_TOKEN_REDUCE
+    from axon_b200.utils.logger import DecoratorLoggerBase, LocalLogger, concat_dict_to_str, print_with_rank
+    from axon_b200.utils.torch.attention import pad_input, unpad_input
+    from axon_b200.utils.torch.device import get_device_name, get_nccl_backend, get_torch_device
+    from axon_b200.utils.torch.dtypes import PrecisionType
+    assert PrecisionType.to_dtype("bf16") is torch.bfloat16 and PrecisionType.to_dtype(16) is torch.float16
+    assert PrecisionType.to_dtype(torch.float32) is torch.float32 and PrecisionType.to_str(torch.bfloat16) == "bf16"
+    assert PrecisionType.is_bf16("bfloat16") and not PrecisionType.is_fp16("bf16") and PrecisionType.supported_type("mixed")
+    assert get_device_name() in ("cuda", "cpu") and get_nccl_backend() in ("nccl", "gloo") and hasattr(get_torch_device(), "synchronize")
+    assert "token-mean" in VALID_BATCH_REDUCE and "mean-norm" in VALID_TOKEN_REDUCE and G.THOUGHT_DELIMITER_END == "</think>"
+    x = torch.arange(2 * 5 * 3, dtype=torch.float32).view(2, 5, 3)
+    mask = torch.tensor([[1, 1, 1, 0, 0], [1, 1, 1, 1, 1]])
+    packed, idx, cu, longest, lens = unpad_input(x, mask)
+    assert packed.shape == (8, 3) and cu.tolist() == [0, 3, 8] and longest == 5 and lens.tolist() == [3, 5]
+    back = pad_input(packed, idx, 2, 5)
+    assert torch.equal(back, x * mask[..., None])
+    assert concat_dict_to_str({"a": 1, "b": "text", "c": 0.5}, 3) == "step:3 - a:1 - c:0.5"
+    LocalLogger().log({"loss": 1.5}, step=2)
+    DecoratorLoggerBase("actor", rank=1).logging_function("hidden")          # rank 1 stays quiet
+    DecoratorLoggerBase("actor", rank=0).logging_function("shown")
+    print_with_rank("hello", rank=3)
+    out = capsys.readouterr().out
+    assert "step:2 - loss:1.5" in out and "actor shown" in out and "hidden" not in out and "[Rank 3] hello" in out
+    DecoratorLoggerBase("x", logger=logging.getLogger("t"), level=logging.INFO).logging_function("via logging")
