@@ -74,6 +74,21 @@ def test_plan_equals_gather_then_slice_dense(a_tp, a_dp, s_tp, s_dp):
             n = local_shard(cfg, full, name, *[x for x in s_ranks if x[0] == r][0][1:]).numel()
             o = s_offs[r][name]
             assert torch.equal(dst[r][o:o + n], s_expected[r][o:o + n]), (r, name)
+    # the offline checker agrees: every sampler element written exactly once, nothing outside the shards
+    from axon_b200.utils.p2p.verify_plan import verify_plans
+    plans = {rank: compile_plan(table, rank, a_offs[rank], s_offs) for rank, *_ in a_ranks}
+    spans = {r: [(s_offs[r][n], local_shard(cfg, full, n, *[x for x in s_ranks if x[0] == r][0][1:]).numel()) for n in param_layout(cfg)]
+             for r in dst}
+    rep = verify_plans(plans, spans)
+    assert rep["ok"], rep
+    if len(plans) > 1 or len(next(iter(plans.values())).descs) > 1:
+        broken = dict(plans)
+        first = next(iter(broken))
+        import copy
+        bad = copy.deepcopy(broken[first])
+        bad.descs = bad.descs[:-1]                 # drop one slice: something must be reported missing
+        broken[first] = bad
+        assert not verify_plans(broken, spans)["ok"]
     # every destination byte is sent exactly once and the senders share the load
     total = sum(sum(local_shard(cfg, full, n, *x[1:]).numel() for n in param_layout(cfg)) for x in s_ranks) * 2
     assert sum(sent.values()) == total
