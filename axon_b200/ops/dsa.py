@@ -309,3 +309,26 @@ def sparse_mla_bwd(do, q, kv, out, lse, idx, scale: float, d_v: int = 512):
     if C.use_native(q) and q.dtype == torch.bfloat16 and q.shape[2] % 8 == 0 and d_v % 8 == 0:
         return sparse_mla_bwd_tc(do, q, kv, out, lse, idx, scale, d_v)
     return sparse_mla_bwd_ref(do, q, kv, out, lse, idx, scale, d_v)
+
+
+# ---------------------------------------------------------------------- the two stages together
+def causal_windows(cu_seqlens: torch.Tensor, total: int):
+    """Per packed position t of sequence b: keys [start of b, t] -> (ks, ke) int32 [T]."""
+    cu = cu_seqlens.long()
+    pos = torch.arange(total, device=cu.device)
+    seq = torch.searchsorted(cu[1:].contiguous(), pos, right=True)
+    return cu[seq].int(), (pos + 1).int()
+
+
+def dsa_attention(q: torch.Tensor, kv: torch.Tensor, q_idx: torch.Tensor, k_idx: torch.Tensor, w_idx: torch.Tensor,
+                  cu_seqlens: torch.Tensor, topk: int, scale: float, d_v: int = 512):
+    """Sparse attention layer of the GLM-5 / DeepSeek-V3.2 family over a packed batch (reference: the attention
+    of axon/models/mbridge/glm5.py built on glm5_ops): the indexer scores the causal window of every query, the
+    ``topk`` best keys are selected (no gradient through the selection) and latent attention runs over them.
+    q [T, H, Dk], kv [T, Dk], q_idx [T, Hi, Di], k_idx [T, Di], w_idx [T, Hi] -> (out [T, H, d_v], idx [T, topk]).
+    With ``topk`` >= the longest sequence this is plain causal attention."""
+    ks, ke = causal_windows(cu_seqlens, q.shape[0])
+    with torch.no_grad():
+        idx = indexer_topk(indexer_logits(q_idx, k_idx, w_idx, ks, ke), topk)
+    out, _ = sparse_mla(q, kv, idx, scale, d_v)
+    return out, idx

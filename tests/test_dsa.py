@@ -161,3 +161,26 @@ def test_sparse_mla_on_gpu_matches_reference():
     C.check_status()
     assert (dq.float() - dq_r.float()).abs().max() < 3e-2 * max(1.0, float(dq_r.float().abs().max()))
     assert (dkv - dkv_r).abs().max() < 3e-2 * max(1.0, float(dkv_r.abs().max()))
+
+
+def test_dsa_layer_equals_causal_attention_when_topk_covers_the_sequence():
+    g = torch.Generator().manual_seed(9)
+    cu = torch.tensor([0, 11, 11, 30], dtype=torch.int32)          # an empty sequence in the middle
+    T, H, Dk, d_v, Hi, Di = 30, 3, 24, 16, 4, 8
+    q, kv = torch.randn(T, H, Dk, generator=g).requires_grad_(True), torch.randn(T, Dk, generator=g).requires_grad_(True)
+    q_idx, k_idx, w_idx = torch.randn(T, Hi, Di, generator=g), torch.randn(T, Di, generator=g), torch.randn(T, Hi, generator=g)
+    out, idx = dsa.dsa_attention(q, kv, q_idx, k_idx, w_idx, cu, topk=32, scale=0.25, d_v=d_v)
+    ref = torch.zeros(T, H, d_v)
+    for a, b in ((0, 11), (11, 30)):
+        sc = torch.einsum("shd,jd->shj", q[a:b], kv[a:b]) * 0.25
+        sc = sc.masked_fill(torch.ones(b - a, b - a, dtype=torch.bool).triu(1)[:, None, :], float("-inf"))
+        ref[a:b] = torch.einsum("shj,jd->shd", sc.softmax(-1), kv[a:b, :d_v])
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+    for t in range(T):                                             # selections stay inside the causal window
+        sel = idx[t][idx[t] >= 0]
+        lo = 0 if t < 11 else 11
+        assert sel.numel() == t - lo + 1 and int(sel.min()) >= lo and int(sel.max()) <= t
+    out.sum().backward()
+    assert q.grad is not None and float(kv.grad.abs().sum()) > 0
+    few, idx2 = dsa.dsa_attention(q.detach(), kv.detach(), q_idx, k_idx, w_idx, cu, topk=4, scale=0.25, d_v=d_v)
+    assert idx2.shape == (T, 4) and not torch.allclose(few, ref)
