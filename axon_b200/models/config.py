@@ -34,6 +34,9 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    partial_rotary_factor: float = 1.0    # share of the head dims that rotate (GLM-4: 0.5)
+    rope_interleaved: bool = False        # checkpoint pairs rotary dims (2i, 2i+1) instead of (i, i + half): GLM family
+    sandwich_norm: bool = False           # extra RMSNorm on the attention and MLP outputs before the residual add (GLM-4)
     num_nextn_predict_layers: int = 0     # multi-token-prediction modules after the decoder (DeepSeek-V3 style, depth 1)
     extra: dict = field(default_factory=dict)
 
@@ -44,6 +47,10 @@ class ModelConfig:
     @property
     def kv_size(self) -> int:
         return self.num_key_value_heads * self.head_dim
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor) // 2 * 2
 
     @property
     def qkv_size(self) -> int:
@@ -68,7 +75,7 @@ class ModelConfig:
         d.pop("extra")
         d.update(self.extra)
         d["architectures"] = [{"qwen3": "Qwen3ForCausalLM", "llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM",
-                               "mistral": "MistralForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "Qwen3ForCausalLM")]
+                               "mistral": "MistralForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM", "glm4": "Glm4ForCausalLM"}.get(self.model_type, "Qwen3ForCausalLM")]
         return d
 
     @classmethod
@@ -80,7 +87,11 @@ class ModelConfig:
         mt = d.get("model_type", "qwen3")
         if "qk_norm" not in kw:
             kw["qk_norm"] = mt.startswith("qwen3")
-        supported = ("qwen3", "qwen3_moe", "qwen2", "llama", "mistral")
+        if mt == "glm4":                      # GLM-4 dense: half of each head rotates (interleaved pairs), sandwich norms, q/k/v bias
+            kw.setdefault("partial_rotary_factor", 0.5)
+            kw["rope_interleaved"], kw["sandwich_norm"], kw["qk_norm"] = True, True, False
+            kw.setdefault("attention_bias", True)
+        supported = ("qwen3", "qwen3_moe", "qwen2", "llama", "mistral", "glm4")
         if mt not in supported:
             raise NotImplementedError(f"model_type '{mt}' is not among the decoder families built here {supported}")
         if mt == "mistral" and d.get("sliding_window") and d.get("sliding_window") < d.get("max_position_embeddings", 0):
@@ -159,6 +170,8 @@ def tiny_moe_gpu() -> ModelConfig:
 PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen2.5-7b": qwen2_5_7b,
            "tiny-qwen2": lambda: _with(tiny_qwen3(), model_type="qwen2", qk_norm=False, attention_bias=True), "qwen3-30b-a3b": qwen3_30b_a3b,
            "tiny-qwen3": tiny_qwen3, "tiny-qwen3-untied": lambda: _untied(tiny_qwen3()),
+           "tiny-glm4": lambda: _with(tiny_qwen3(), model_type="glm4", qk_norm=False, attention_bias=True, partial_rotary_factor=0.5,
+                                    rope_interleaved=True, sandwich_norm=True, tie_word_embeddings=False),
            "tiny-qwen3-mtp": lambda: _with(tiny_qwen3(), num_nextn_predict_layers=1),
            "tiny-qwen3-untied-5l": lambda: _with(_untied(tiny_qwen3()), num_hidden_layers=5), "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}
 

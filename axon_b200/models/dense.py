@@ -123,7 +123,7 @@ class DenseModel:
         A.embedding_bwd(batch.input_ids, dx, self._wgrad("model.embed_tokens.weight"))
 
     def _tables(self, max_pos: int):
-        return R.rope_tables(max(max_pos, 8), self.cfg.head_dim, self.cfg.rope_theta, self.device)
+        return R.rope_tables(max(max_pos, 8), self.cfg.head_dim, self.cfg.rope_theta, self.device, self.cfg.rotary_dim)
 
     # ------------------------------------------------------------------ one layer
     # What the forward pass keeps per layer for backward, by ``self.recompute``:
@@ -146,11 +146,18 @@ class DenseModel:
                                   c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
         want = self._KEEP[self.recompute] if keep else ()
         o, lse = self._attn_fwd(qkv_r, batch, need_lse="lse" in want)
-        ao = self._lin(l, "self_attn.o_proj.weight", o)
+        ao = self._post_norm(l, "post_self_attn_layernorm.weight", self._lin(l, "self_attn.o_proj.weight", o))
         h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
         mo, mlp_saved = self.mlp_fwd(l, h2, batch, want)
+        mo = self._post_norm(l, "post_mlp_layernorm.weight", mo)
         local = dict(xin=xin, qkv=qkv, o=o, lse=lse, x1=x1, **mlp_saved)
         return x1, mo, ({k: local[k] for k in local if k in want or k in mlp_saved} if keep else xin)
+
+    def _post_norm(self, l: int, name: str, y: torch.Tensor) -> torch.Tensor:
+        """Sandwich-norm families (GLM-4) normalise a sub-layer's output before it joins the residual stream."""
+        if not self.cfg.sandwich_norm:
+            return y
+        return N.rmsnorm_fwd(y, self._p(l, name), self.cfg.rms_norm_eps)[0]
 
     # ---- MLP hooks (dense SwiGLU here; the mixture-of-experts model overrides the three of them)
     def mlp_fwd(self, l: int, h2, batch: PackedBatch, want=()):
@@ -190,13 +197,20 @@ class DenseModel:
                                        c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
         if "o" not in k:
             k["o"], k["lse"] = self._attn_fwd(k["qkv_r"], batch, need_lse=True)
+        if c.sandwich_norm:       # backward of the output norms needs their inputs: the o-projection is re-run in every mode
+            k["ao_raw"] = self._lin(l, "self_attn.o_proj.weight", k["o"])
+            ao, k["rstd_a"], _ = N.rmsnorm_fwd(k["ao_raw"], self._p(l, "post_self_attn_layernorm.weight"), c.rms_norm_eps)
         if "x1" not in k:
-            ao = self._lin(l, "self_attn.o_proj.weight", k["o"])
+            if not c.sandwich_norm:
+                ao = self._lin(l, "self_attn.o_proj.weight", k["o"])
             k["h2"], k["rstd2"], k["x1"] = N.rmsnorm_fwd(k["xin"], self._p(l, "post_attention_layernorm.weight"),
                                                          c.rms_norm_eps, delta=ao)
         else:
             k["h2"], k["rstd2"], _ = N.rmsnorm_fwd(k["x1"], self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps)
         self.mlp_rebuild(l, k, batch)
+        if c.sandwich_norm:       # ... and so is the down projection
+            k["mo_raw"] = self._lin(l, "mlp.down_proj.weight", k["a"])
+            k["rstd_m"] = N.rmsnorm_fwd(k["mo_raw"], self._p(l, "post_mlp_layernorm.weight"), c.rms_norm_eps)[1]
         return k
 
     def layer_bwd(self, l: int, saved, dx_out, batch: PackedBatch, tables):
@@ -207,12 +221,20 @@ class DenseModel:
         k = self._rebuild(l, saved, batch, tables)
         qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
         kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
-        dh2 = self.mlp_bwd(l, k, dx_out)
+        d_mo = dx_out
+        if c.sandwich_norm:
+            d_mo = N.rmsnorm_bwd(dx_out, k["mo_raw"], self._p(l, "post_mlp_layernorm.weight"), k["rstd_m"],
+                                 self._g(l, "post_mlp_layernorm.weight"))
+        dh2 = self.mlp_bwd(l, k, d_mo)
         dx1 = N.rmsnorm_bwd(dh2, k["x1"], self._p(l, "post_attention_layernorm.weight"), k["rstd2"],
                             self._g(l, "post_attention_layernorm.weight"), dres=dx_out)
-        del dh2
+        del dh2, d_mo
         # attention
-        do = self._lin_bwd(l, "self_attn.o_proj.weight", dx1, k["o"])
+        d_ao = dx1
+        if c.sandwich_norm:
+            d_ao = N.rmsnorm_bwd(dx1, k["ao_raw"], self._p(l, "post_self_attn_layernorm.weight"), k["rstd_a"],
+                                 self._g(l, "post_self_attn_layernorm.weight"))
+        do = self._lin_bwd(l, "self_attn.o_proj.weight", d_ao, k["o"])
         dqkv_r = self._attn_bwd(do, k["qkv_r"], k["o"], k["lse"], batch)
         del do
         dqkv = R.qknorm_rope_bwd(dqkv_r, k["qkv"], batch.position_ids, tables[0], tables[1], c.num_attention_heads,
@@ -355,9 +377,9 @@ class _DenseInference:
                            c.num_key_value_heads, c.head_dim)
             o, _ = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                                need_lse=False)
-            ao = self._lin(l, "self_attn.o_proj.weight", o)
+            ao = self._post_norm(l, "post_self_attn_layernorm.weight", self._lin(l, "self_attn.o_proj.weight", o))
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
-            delta = self.mlp_infer(l, h2)
+            delta = self._post_norm(l, "post_mlp_layernorm.weight", self.mlp_infer(l, h2))
             x = x1
         xl = x[last_index]
         dl = delta[last_index]
@@ -389,9 +411,9 @@ class _DenseInference:
             else:
                 o = P.paged_decode_shared(qkv_r, cache.k[l], cache.v[l], block_table, seq_lens, shared,
                                           c.num_attention_heads, c.num_key_value_heads, c.head_dim)
-            ao = self._lin(l, "self_attn.o_proj.weight", o)
+            ao = self._post_norm(l, "post_self_attn_layernorm.weight", self._lin(l, "self_attn.o_proj.weight", o))
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
-            delta = self.mlp_infer(l, h2)
+            delta = self._post_norm(l, "post_mlp_layernorm.weight", self.mlp_infer(l, h2))
             x = x1
         hf, _, _ = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], c.rms_norm_eps, delta=delta)
         return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)

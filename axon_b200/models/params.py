@@ -38,6 +38,9 @@ def param_layout(cfg: ModelConfig) -> "OrderedDict[str, tuple[int, ...]]":
             lay[p + "self_attn.k_norm.weight"] = (D,)
         lay[p + "self_attn.o_proj.weight"] = (H, cfg.q_size)
         lay[p + "post_attention_layernorm.weight"] = (H,)
+        if cfg.sandwich_norm:
+            lay[p + "post_self_attn_layernorm.weight"] = (H,)
+            lay[p + "post_mlp_layernorm.weight"] = (H,)
         if cfg.num_experts > 0:
             F = cfg.moe_intermediate_size
             lay[p + "mlp.gate.weight"] = (cfg.num_experts, H)
@@ -59,6 +62,30 @@ def _numel(shape) -> int:
     for s in shape:
         n *= s
     return n
+
+
+def rope_row_perm(cfg: ModelConfig) -> "torch.Tensor | None":
+    """Per-head permutation of the q / k output rows between a checkpoint's rotary layout and the layout the
+    kernels rotate (pairs (i, i + D/2), rotating pairs first): ``ours[i] = checkpoint[perm[i]]``. None when the
+    checkpoint already has that layout (full rotary, half-split pairs)."""
+    D, r = cfg.head_dim, cfg.rotary_dim
+    if r == D and not cfg.rope_interleaved:
+        return None
+    half, rh, ph = D // 2, r // 2, (D - r) // 2
+    perm = torch.empty(D, dtype=torch.long)
+    for p in range(rh):
+        a, b = (2 * p, 2 * p + 1) if cfg.rope_interleaved else (p, rh + p)
+        perm[p], perm[half + p] = a, b
+    for j in range(ph):                      # dims that do not rotate: any fixed pairing works, q and k share it
+        perm[rh + j], perm[half + rh + j] = r + j, r + ph + j
+    return perm
+
+
+def _permute_heads(t: torch.Tensor, perm: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """Rows of ``t`` ([heads * D, ...]) re-ordered inside every head."""
+    heads = t.shape[0] // head_dim
+    idx = (torch.arange(heads)[:, None] * head_dim + perm[None, :]).reshape(-1).to(t.device)
+    return t[idx]
 
 
 class FlatParams:
@@ -132,18 +159,24 @@ class FlatParams:
             self.grad_flat.zero_()
 
     # ------------------------------------------------------------------ HF name mapping
-    def to_hf_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
+    def to_hf_state_dict(self, export: bool = True) -> "OrderedDict[str, torch.Tensor]":
+        """HF-named tensors. With ``export`` they have the checkpoint's values (q / k rows of partial- or
+        interleaved-rotary families are re-ordered copies); without it they are views of the buffers in this
+        framework's row order, which ``load_hf_state_dict`` fills and then re-orders in place."""
         cfg = self.cfg
+        perm = rope_row_perm(cfg)
+        inv = None if perm is None else torch.argsort(perm)
         out: OrderedDict[str, torch.Tensor] = OrderedDict()
         for name, v in self.views.items():
-            if name.endswith("qkv_proj.weight"):
-                base = name[: -len("qkv_proj.weight")]
+            if name.endswith("qkv_proj.weight") or name.endswith("qkv_proj.bias"):
+                kind = name.rsplit(".", 1)[1]
+                base = name[: -len("qkv_proj." + kind)]
                 q, k, vv = v.split([cfg.q_size, cfg.kv_size, cfg.kv_size], 0)
-                out[base + "q_proj.weight"], out[base + "k_proj.weight"], out[base + "v_proj.weight"] = q, k, vv
-            elif name.endswith("qkv_proj.bias"):
-                base = name[: -len("qkv_proj.bias")]
-                q, k, vv = v.split([cfg.q_size, cfg.kv_size, cfg.kv_size], 0)
-                out[base + "q_proj.bias"], out[base + "k_proj.bias"], out[base + "v_proj.bias"] = q, k, vv
+                if export and inv is not None:          # back to the checkpoint's rotary layout (copies, not views)
+                    q, k = _permute_heads(q, inv, cfg.head_dim), _permute_heads(k, inv, cfg.head_dim)
+                out[base + "q_proj." + kind], out[base + "k_proj." + kind], out[base + "v_proj." + kind] = q, k, vv
+            elif name.endswith("gate_up_proj.weight") and cfg.model_type == "glm4":
+                out[name] = v                           # GLM-4 checkpoints keep gate and up fused
             elif name.endswith("gate_up_proj.weight"):
                 base = name[: -len("gate_up_proj.weight")]
                 g, u = v.split(cfg.intermediate_size, 0)
@@ -165,7 +198,8 @@ class FlatParams:
     def load_hf_state_dict(self, sd: dict, strict: bool = True) -> list[str]:
         """Copy HF-named tensors into the fused views. Returns the list of missing HF names."""
         missing = []
-        for hf_name, dst in self.to_hf_state_dict().items():
+        perm = rope_row_perm(self.cfg)
+        for hf_name, dst in self.to_hf_state_dict(export=False).items():
             src = sd.get(hf_name)
             if src is None:
                 if hf_name == "lm_head.weight" and "model.embed_tokens.weight" in sd:
@@ -173,7 +207,10 @@ class FlatParams:
                 else:
                     missing.append(hf_name)
                     continue
-            dst.copy_(src.to(dst.dtype))
+            src = src.to(dst.dtype)
+            if perm is not None and hf_name.rsplit(".", 2)[-2] in ("q_proj", "k_proj"):
+                src = _permute_heads(src, perm, self.cfg.head_dim)       # checkpoint rotary layout -> kernel layout
+            dst.copy_(src)
         if strict and missing:
             raise KeyError(f"missing tensors in checkpoint: {missing[:5]} ... ({len(missing)} total)")
         return missing

@@ -222,7 +222,7 @@ class TPDenseModel:
         T = batch.input_ids.numel()
         assert T % (128 * self.tp.world) == 0, "pad the batch with pad_packed_batch(batch, 128 * tp)"
         sl = self.local_slice(T)
-        tables = R.rope_tables(max(int(batch.max_seqlen) or c.max_position_embeddings, 8), c.head_dim, c.rope_theta, self.device)
+        tables = R.rope_tables(max(int(batch.max_seqlen) or c.max_position_embeddings, 8), c.head_dim, c.rope_theta, self.device, c.rotary_dim)
         x = A.embedding_fwd(batch.input_ids[sl].contiguous(), self.params["model.embed_tokens.weight"])
         delta, inputs = None, []
         for l in range(c.num_hidden_layers):

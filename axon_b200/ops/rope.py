@@ -15,13 +15,17 @@ from . import _common as C
 _TABLES: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
-def rope_tables(max_pos: int, dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
-    """fp32 cos/sin tables [max_pos, dim/2] (cached per device)."""
-    key = (str(device), dim, float(theta))
+def rope_tables(max_pos: int, dim: int, theta: float, device, rotary_dim: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables [max_pos, dim/2] (cached per device). With ``rotary_dim < dim`` (partial rotary
+    embeddings) only the first ``rotary_dim / 2`` pairs turn, with frequencies over ``rotary_dim``; the other
+    pairs get angle 0 (cos 1, sin 0), so the kernels that rotate every pair (i, i + dim/2) leave them as they are."""
+    rd = dim if rotary_dim is None else int(rotary_dim)
+    key = (str(device), dim, float(theta), rd)
     tab = _TABLES.get(key)
     if tab is None or tab[0].shape[0] < max_pos:
         n = max(max_pos, 1024)
-        inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+        inv = torch.zeros(dim // 2, dtype=torch.float64)
+        inv[: rd // 2] = 1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float64) / rd))
         ang = torch.arange(n, dtype=torch.float64)[:, None] * inv[None, :]
         tab = (ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous())
         _TABLES[key] = tab

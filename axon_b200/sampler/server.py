@@ -206,8 +206,13 @@ class SamplerServer:
                 dst = views.get(name)
                 if dst is None:
                     if hf_views is None:
-                        hf_views = self.engine.model.params.to_hf_state_dict()
+                        hf_views = self.engine.model.params.to_hf_state_dict(export=False)       # views, in this framework's row order
                     dst = hf_views.get(name)
+                    if dst is not None and name.rsplit(".", 2)[-2] in ("q_proj", "k_proj"):
+                        from ..models.params import _permute_heads, rope_row_perm
+                        perm = rope_row_perm(self.engine.model.cfg)
+                        if perm is not None:          # checkpoint rotary layout -> kernel layout
+                            t = _permute_heads(t, perm, self.engine.model.cfg.head_dim)
                 if dst is None:
                     raise KeyError(f"unknown parameter '{name}'")
                 dst.copy_(t.to(dst.dtype))
