@@ -93,3 +93,36 @@ def test_backward_matches_hf_autograd(tmp_path, recompute):
             assert err < 2e-3 * max(1.0, b.abs().max().item()), (name, err)
             checked += 1
     assert checked > 20
+
+
+@pytest.mark.gpu
+def test_gpu_kernels_match_the_cpu_model():
+    """Same GLM-4-style model (head dim 128) in bf16 on the native kernels and in fp32 on CPU."""
+    from axon_b200.models.config import tiny_gpu
+    from axon_b200.ops import _common as C
+    cfg = tiny_gpu()
+    cfg.model_type, cfg.qk_norm, cfg.attention_bias = "glm4", False, True
+    cfg.partial_rotary_factor, cfg.rope_interleaved, cfg.sandwich_norm = 0.5, True, True
+    ref = DenseModel(cfg, device="cpu", dtype=torch.float32)
+    ref.params.init_random(std=0.05, seed=1)
+    for v in ref.params.views.values():
+        if v.dim() == 1:
+            v.copy_(1 + 0.1 * torch.randn(v.shape))
+    gpu = DenseModel(cfg, device="cuda", dtype=torch.bfloat16)
+    gpu.params.flat.copy_(ref.params.flat.to(torch.bfloat16))
+    ref.params.flat.copy_(gpu.params.flat.float().cpu())            # both start from the bf16-rounded values
+    seqs = [torch.randint(0, cfg.vocab_size, (n,)) for n in (150, 260, 31)]
+    g = torch.randn(sum(s.numel() for s in seqs))
+    out = {}
+    for name, m, dev in (("ref", ref, "cpu"), ("gpu", gpu, "cuda")):
+        b = PackedBatch.from_sequences(seqs, dev)
+        m.params.alloc_grads()
+        m.params.zero_grads()
+        lp, ent = m.forward(b, 1.0, save_for_backward=True)
+        m.backward((g * (b.labels.cpu() >= 0)).to(dev), None)
+        out[name] = (lp.float().cpu(), {k: v.float().cpu() for k, v in m.params.grads.items()})
+    C.check_status()
+    assert (out["gpu"][0] - out["ref"][0]).abs().max() < 0.15 and (out["gpu"][0] - out["ref"][0]).abs().mean() < 0.02
+    for name, gr in out["ref"][1].items():
+        rel = (out["gpu"][1][name] - gr).norm() / (gr.norm() + 1e-12)
+        assert rel < 0.08, (name, float(rel))
