@@ -83,6 +83,7 @@ class TPDenseModel:
     def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False):
         assert cfg.num_experts == 0
         assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
+        assert not cfg.sandwich_norm, "sandwich-norm families (GLM-4) run under data / sequence / context / pipeline parallelism; the tensor-parallel layer code does not carry the extra norms yet"
         assert cfg.num_nextn_predict_layers == 0, "the multi-token-prediction module is trained by the data-parallel trainer only"
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
