@@ -164,7 +164,15 @@ class VocabParallelHead:
         tp.barrier()
         lib = C.lib()
         scratch = C.workspace(tp.device, lib.axb_lmhead_scratch_bytes(ctypes.c_longlong(T), self.vl), "lmhead")
-        rc = lib.axb_lmhead_vp_stats(self._hbuf.ptr_array(), tp.world, tp.rank, C.ptr(w_shard), C.ptr(lab_loc), rows, self.vl, H,
+        # Every vocabulary tile of the stats GEMM streams all hidden rows, and peer memory is not cached on the
+        # reading side: handing the kernel the peers' buffers would move the remote rows over NVLink once per tile
+        # (hundreds of times for a 76 k-column shard). The peers' rows are therefore copied once into local memory
+        # and the kernel's per-rank pointers point into that copy.
+        h_all = torch.empty(tp.world, rows, H, dtype=torch.bfloat16, device=tp.device)
+        for r in range(tp.world):
+            h_all[r].copy_(h_local if r == tp.rank else self._hbuf.peer_tensor(r, rows * H).view(rows, H))
+        h_ptrs = (ctypes.c_ulonglong * tp.world)(*[h_all[r].data_ptr() for r in range(tp.world)])
+        rc = lib.axb_lmhead_vp_stats(h_ptrs, tp.world, tp.rank, C.ptr(w_shard), C.ptr(lab_loc), rows, self.vl, H,
                                      ctypes.c_longlong(H), ctypes.c_longlong(w_shard.stride(0)), ctypes.c_float(temperature),
                                      C.ptr(scratch), self._stats.ptr_array(), C.ptr(C.status(tp.device)), C.stream())
         C.launched(rc, "lmhead_vp_stats", 2)
