@@ -13,6 +13,11 @@ tensor-core work tile by tile (``axb_gemm_gather_weights``, ``csrc/gemm.cu``; ti
 ``dgrad`` is the same gather on the K side and ``wgrad`` produces full-size gradients that the ZeRO reduce
 shards again; both still use the plain kernels on an all-gathered copy here (the forward path is the fused
 one). On CPU / gloo the op all-gathers and multiplies (host-side logic and tests).
+
+Cost across NVLink: the kernel fetches a remote weight tile once per 256-token tile of ``x`` (peer memory is not
+cached on the reading side), so its link traffic is (remote share of the weight) x (token tiles). It pays for
+one to four token tiles (small batches, where a separate gather is pure latency); for long micro-batches the
+training model (``models/zero3_dense.py``) gathers the shard once instead.
 """
 from __future__ import annotations
 
