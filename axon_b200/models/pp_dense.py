@@ -2,7 +2,7 @@
 schedules of ``megatron_forward_backward``, axon/utils/megatron/ - send / recv over NCCL p2p).
 
 The layers are cut into ``P`` contiguous stages; stage 0 also owns the embedding, the last stage the final
-norm and the vocabulary head (tied embeddings would need the embedding on both ends and are refused).
+norm and the vocabulary head (with tied embeddings both ends hold the table and sum its gradient before the optimizer).
 Each stage holds only its own parameters, optimizer shards and activations. One micro-batch runs as
 
     forward :  recv (x, delta) <- prev   ->  local layers  ->  send (x, delta) -> next      last: head -> logprob / entropy
@@ -46,7 +46,7 @@ def stage_layout(cfg: ModelConfig, stages: int, stage: int):
             if any(name.startswith(p) for p in keep):
                 out[name] = shape
         elif name == "model.embed_tokens.weight":
-            if stage == 0:
+            if stage == 0 or (cfg.tie_word_embeddings and stage == stages - 1):      # tied: the last stage's head reads it too
                 out[name] = shape
         elif stage == stages - 1:          # final norm, head, value head
             out[name] = shape
@@ -54,9 +54,12 @@ def stage_layout(cfg: ModelConfig, stages: int, stage: int):
 
 
 class PipelineContext:
-    def __init__(self, group, device):
+    def __init__(self, group, device, ends_group=None):
+        """``ends_group``: the first and the last stage of this pipeline (they share the tied embedding); with two
+        stages that is the pipeline group itself."""
         live = dist.is_initialized() and group is not None
         self.group, self.device = group, torch.device(device)
+        self.ends_group = ends_group
         self.world = dist.get_world_size(group) if live else 1
         self.rank = dist.get_rank(group) if live else 0
         self.ranks = dist.get_process_group_ranks(group) if live else [0]
@@ -105,7 +108,8 @@ class PipelineContext:
 class PPDenseModel(DenseModel):
     def __init__(self, cfg: ModelConfig, pp: PipelineContext, device="cuda", dtype=torch.bfloat16):
         assert cfg.num_experts == 0, "pipeline stages are built for dense models"
-        assert not cfg.tie_word_embeddings or pp.world == 1, "tied embeddings cannot be split over pipeline stages"
+        if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
+            assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
         assert pp.world <= cfg.num_hidden_layers
         self.pp = pp
         self.stage, self.stages = pp.rank, pp.world
@@ -129,6 +133,24 @@ class PPDenseModel(DenseModel):
         return []
 
     def replicated_ranges(self):
+        return []
+
+    # Tied embeddings: the table lives on the first stage (lookup) and on the last (output head). Both copies start
+    # equal, their gradients are summed over the two stages before the optimizer, so they stay equal.
+    def _shares_embedding(self) -> bool:
+        return self.cfg.tie_word_embeddings and self.stages > 1 and (self.first or self.last)
+
+    def sync_replicated_grads(self) -> None:
+        if self._shares_embedding() and self.params.grad_flat is not None:
+            group = self.pp.ends_group if self.stages > 2 else self.pp.group
+            dist.all_reduce(self.params.grads["model.embed_tokens.weight"], group=group)
+
+    def duplicate_ranges(self) -> list[tuple[int, int]]:
+        """Ranges of the flat gradient that another stage holds as well (counted once in the global norm):
+        reported by the last stage only."""
+        if self._shares_embedding() and self.last:
+            o, n = self.params.offsets["model.embed_tokens.weight"]
+            return [(o, o + n)]
         return []
 
     # ------------------------------------------------------------------ the pieces of one micro-batch

@@ -89,7 +89,14 @@ class TrainerWorker(_Base):
         assert not self.model_kind.value_head, "value-head models are not pipeline-parallel yet; run the critic with pp=1"
         pp_group, dp_group = self._make_groups(self.pp_size)
         self.pg, self._mp_group = dp_group, pp_group
-        model = PPDenseModel(mcfg, PipelineContext(pp_group, self.device), device=self.device, dtype=dtype)
+        ends_group = None
+        if mcfg.tie_word_embeddings and self.pp_size > 2:      # first and last stage of every pipeline share the embedding
+            for i in range(self.world_size // self.pp_size):
+                ranks = [i * self.pp_size, (i + 1) * self.pp_size - 1]
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    ends_group = g
+        model = PPDenseModel(mcfg, PipelineContext(pp_group, self.device, ends_group), device=self.device, dtype=dtype)
         ref = FlatParams(mcfg, "cpu", dtype)                 # full model on the host, cut down to this stage
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
             ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))

@@ -404,6 +404,16 @@ class PolicyEngine:
         tot = self.state[:1].clone()
         tp.all_reduce_(tot)
         self.state[:1] = tot - (tp.world - 1) * rep
+        if hasattr(self.model, "duplicate_ranges"):       # parameters held by some ranks of the group only (tied embedding on pipeline ends)
+            dup = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for a, b in self.model.duplicate_ranges():
+                a2, b2 = max(a, lo) - lo, min(b, lo + grad_shard.numel()) - lo
+                if b2 > a2:
+                    dup += grad_shard[a2:b2].float().pow(2).sum()
+            if self.world > 1:
+                dist.all_reduce(dup, group=self.pg)
+            tp.all_reduce_(dup)
+            self.state[:1] -= dup
 
     def _padded_flat(self, t: torch.Tensor) -> torch.Tensor:
         need = self.shard_size * self.world

@@ -148,3 +148,20 @@ def test_tensor_parallel_trainer_with_qkv_bias_matches_data_parallel_trainer():
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world,pp,model,cap", [(2, 2, "tiny-qwen3", 512), (3, 3, "tiny-qwen3-5l", 64)])
+def test_pipeline_stages_share_a_tied_embedding(world, pp, model, cap):
+    """Tied embeddings: the first and the last stage both hold the table, sum its gradient, and stay equal; log-probs,
+    gradient norm (the table counted once) and the update match the single-process trainer."""
+    import numpy as np
+    ref_cfg, got_cfg = _cfg(1, model), _cfg(1, model, pp=pp)
+    ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = cap
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, world)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
