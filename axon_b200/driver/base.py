@@ -105,6 +105,9 @@ class PPODriverBase(ABC):
             sub = cfg_get(cfg, f"{role}.lr_scheduler")
             if isinstance(sub, dict) and not sub.get("total_steps"):
                 sub["total_steps"] = self.total_training_steps
+            args = cfg_get(cfg, f"{role}.lr_scheduler_args")
+            if isinstance(args, dict) and int(args.get("total_training_steps") or -1) <= 0:
+                args["total_training_steps"] = self.total_training_steps
 
     def _prepare_batch(self, batch_dict: dict, global_steps: int) -> DataProto:
         return convert_batch_dict_to_dataproto(batch_dict, global_steps=global_steps, n_samples=int(cfg_get(self.config, "decoding.n", 1)),

@@ -122,8 +122,14 @@ def _ref_process(logits, temperature, top_k, top_p):
     return out
 
 
-def sample(logits, temperature=None, top_k=None, top_p=None, seed: int = 0, counters=None):
-    """Returns (tokens int32 [B], logprobs fp32 [B]) with log-probs under the processed distribution."""
+def sample(logits, temperature=None, top_k=None, top_p=None, seed: int = 0, counters=None,
+           logprobs_mode: str = "processed"):
+    """Returns (tokens int32 [B], logprobs fp32 [B]). ``logprobs_mode``: ``"processed"`` reports the log-prob
+    under the processed distribution (after temperature / top-k / top-p, renormalised over the kept set - the
+    reference's vLLM fork, install/vllm/axon.patch:635-680); ``"full"`` reports the temperature-scaled
+    log-softmax over the whole vocabulary, which is what the trainer's ``old_log_probs`` hold, so that
+    importance-sampling corrections stay unbiased when top-k / top-p truncate the draw."""
+    assert logprobs_mode in ("processed", "full")
     B, V = logits.shape
     if not C.use_native(logits):
         lp = _ref_process(logits, temperature, top_k, top_p)
@@ -135,12 +141,14 @@ def sample(logits, temperature=None, top_k=None, top_p=None, seed: int = 0, coun
             else:
                 g = torch.Generator().manual_seed((seed * 1000003 + b * 7919 + (int(counters[b]) if counters is not None else 0)) % (2 ** 63))
                 toks[b] = int(torch.multinomial(lp[b].exp(), 1, generator=g))
+        if logprobs_mode == "full":
+            lp = _ref_process(logits, temperature, None, None)
         return toks, lp.gather(1, toks.long()[:, None])[:, 0]
     toks = torch.empty(B, dtype=torch.int32, device=logits.device)
     lps = torch.empty(B, dtype=torch.float32, device=logits.device)
-    rc = C.lib().axb_sample(C.ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V, C.ptr(temperature),
-                            C.ptr(top_k), C.ptr(top_p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), C.ptr(counters),
-                            C.ptr(toks), C.ptr(lps), C.stream())
+    rc = C.lib().axb_sample_ex(C.ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V, C.ptr(temperature),
+                               C.ptr(top_k), C.ptr(top_p), ctypes.c_ulonglong(seed & (2 ** 64 - 1)), C.ptr(counters),
+                               C.ptr(toks), C.ptr(lps), 1 if logprobs_mode == "full" else 0, C.stream())
     C.launched(rc, "sample")
     return toks, lps
 

@@ -3,7 +3,7 @@ peer memory written and read directly by the dispatch / combine kernels (``csrc/
 half). The expert computation on the owner is the grouped tcgen05 GEMM pair of the single-GPU path.
 
 Replaces the reference's token dispatchers (NCCL ``all_to_all_single`` or DeepEP under Megatron-Core's
-MoE layer; SURVEY collective inventory "Megatron EP token dispatcher"): no all-to-all collective, no
+MoE layer: axon/config/sampler/sampler.yaml all2all_backend, megatron's moe_token_dispatcher_type): no all-to-all collective, no
 permute / unpermute staging copies, the layout is derived from one W x E count matrix that every rank
 reads in place. Three device barriers per layer and direction order the phases.
 

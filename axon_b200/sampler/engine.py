@@ -65,6 +65,10 @@ class GenerationEngine:
         # because the KV pool moves). Disabled on CPU.
         self.use_cuda_graph = self.device.type == "cuda"
         self.share_prompts = True          # n samples of one prompt share its KV pages and its prefill
+        # "processed": log-prob under the distribution actually drawn from (after top-k / top-p, the reference
+        # fork's convention); "full": temperature-scaled log-softmax over the whole vocabulary (what the trainer
+        # recomputes), which keeps importance-sampling corrections unbiased under truncation.
+        self.logprobs_mode = "processed"
         # Decode attention over the shared pages once per group (csrc/paged_attention_shared.cu). Off by default: with
         # one CTA per SM the per-CTA start-up of the extra prefix / suffix items costs as much as the shared tiles
         # save once responses are a few pages long (measured end to end); the kernel pays off for long shared
@@ -203,7 +207,7 @@ class GenerationEngine:
                 seen[i, torch.tensor(s.prompt + s.out.token_ids, dtype=torch.long).clamp(0, V - 1)] = 1
             P.repetition_penalty_(logits, seen.to(self.device), torch.tensor(pens, dtype=torch.float32).to(self.device))
         t, k, p, ctr = self._sampling_tensors(seqs)
-        toks, lps = P.sample(logits, t, k, p, seed=self.seed, counters=ctr)
+        toks, lps = P.sample(logits, t, k, p, seed=self.seed, counters=ctr, logprobs_mode=self.logprobs_mode)
         # the one host sync of a step: finish detection needs the ids
         self._record(seqs, toks.cpu().tolist(), lps.cpu().tolist())
 
@@ -266,7 +270,8 @@ class GenerationEngine:
 
         def run():
             logits = self.model.decode(g["tokens"], g["pos"], self.cache, g["bt"], g["lens"], shared=shared)
-            return P.sample(logits, g["temp"], g["top_k"], g["top_p"], seed=self.seed, counters=g["ctr"])
+            return P.sample(logits, g["temp"], g["top_k"], g["top_p"], seed=self.seed, counters=g["ctr"],
+                            logprobs_mode=self.logprobs_mode)
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))

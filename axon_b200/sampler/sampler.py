@@ -97,6 +97,7 @@ class SamplerWorker(Worker, DistProfilerExtension):
                                        kv_memory_bytes=kv_bytes, seed=int(_get(cfg, "seed", 42)) + self.rank)
         if _get(scfg, "enforce_eager", False):
             self.engine.use_cuda_graph = False
+        self.engine.logprobs_mode = str(_get(scfg, "logprobs_mode", "processed"))
         max_len = _get(scfg, "max_model_len", None)
         if max_len:
             self.engine.set_max_model_len(int(max_len))

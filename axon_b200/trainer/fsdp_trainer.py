@@ -144,17 +144,14 @@ class TrainerWorker(Worker, DistProfilerExtension):
         except Exception:
             self.tokenizer = None
         betas = _get(cfg, "optimizer_args.betas", [0.9, 0.95])
-        sched = _get(cfg, "lr_scheduler", {}) or {}
-        total = _get(sched, "total_steps", 0) or 0
-        warm = int(_get(sched, "warmup_steps", 0) or 0)
-        if not warm and _get(sched, "warmup_ratio", 0.0) and total:
-            warm = int(float(_get(sched, "warmup_ratio")) * total)
-        ocfg = OptimConfig(lr=float(_get(cfg, "optimizer_args.lr", 1e-6)), weight_decay=float(_get(cfg, "optimizer_args.weight_decay", 0.1)),
-                           beta1=float(betas[0]), beta2=float(betas[1]), eps=float(_get(cfg, "optimizer_args.eps", 1e-8)),
+        from .policy import schedule_from_config
+        sched = schedule_from_config(_get(cfg, "lr_scheduler", None), _get(cfg, "lr_scheduler_args", None),
+                                     float(_get(cfg, "optimizer_args.lr", 1e-6)))
+        extra = dict(_get(cfg, "optimizer_args.override_optimizer_args", {}) or {})
+        ocfg = OptimConfig(lr=float(_get(cfg, "optimizer_args.lr", 1e-6)), weight_decay=float(extra.get("weight_decay", _get(cfg, "optimizer_args.weight_decay", 0.1))),
+                           beta1=float(betas[0]), beta2=float(betas[1]), eps=float(extra.get("eps", _get(cfg, "optimizer_args.eps", 1e-8))),
                            grad_clip=float(_get(cfg, "grad_clip", 1.0) or 0.0),
-                           grad_norm_threshold=float(_get(cfg, "fsdp.grad_norm_threshold", 0.0) or 0.0),
-                           warmup_steps=warm, total_steps=int(total), min_lr_ratio=float(_get(sched, "min_lr_ratio", 0.0) or 0.0),
-                           schedule=str(_get(sched, "type", "constant")))
+                           grad_norm_threshold=float(_get(cfg, "fsdp.grad_norm_threshold", 0.0) or 0.0), **sched)
         self.engine = PolicyEngine(self.model, ocfg, process_group=self.pg,
                                    max_token_len_per_gpu=int(_get(cfg, "max_token_len_per_gpu", 16384)) * self.ulysses_sequence_parallel_size,
                                    temperature=1.0)

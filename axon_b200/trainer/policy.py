@@ -40,19 +40,71 @@ class OptimConfig:
     grad_clip: float = 1.0
     grad_norm_threshold: float = 0.0      # > 0: skip the step when the norm exceeds it
     warmup_steps: int = 0
-    total_steps: int = 0                  # > 0 enables cosine decay to min_lr_ratio * lr
+    total_steps: int = 0                  # > 0 enables decay to the floor (cosine / wsd)
     min_lr_ratio: float = 0.0
-    schedule: str = "constant"            # constant | cosine
+    schedule: str = "constant"            # constant | cosine | wsd
+    min_lr: float = 0.0                   # absolute floor; the larger of min_lr and min_lr_ratio * lr applies
+    warmup_init: float = 0.0              # learning rate the warm-up starts from
+    num_cycles: float = 0.5               # cosine: half waves over the decay span
+    decay_steps: int = 0                  # > 0: the decay ends here instead of at total_steps
+    wsd_decay_steps: int = 0              # wsd: length of the final decay (the stable phase fills the rest)
+    wsd_decay_style: str = "exponential"  # wsd: exponential | linear | cosine
 
 
 def lr_at(cfg: OptimConfig, step: int) -> float:
-    """Learning rate for 1-based optimizer step ``step`` (linear warm-up, then constant or cosine)."""
+    """Learning rate for 1-based optimizer step ``step``: linear warm-up from ``warmup_init``, then constant,
+    cosine decay, or warm-up / stable / decay (``wsd``: constant until the last ``wsd_decay_steps`` steps, which
+    fall to the floor with the chosen shape). Schedules of the reference: axon/utils/scheduler_utils.py:27-140
+    and the megatron scheduler arguments of axon/config/trainer/trainer.yaml:36-57."""
+    floor = max(cfg.min_lr, cfg.min_lr_ratio * cfg.lr)
     if cfg.warmup_steps > 0 and step <= cfg.warmup_steps:
-        return cfg.lr * step / cfg.warmup_steps
-    if cfg.schedule == "cosine" and cfg.total_steps > cfg.warmup_steps:
-        p = min(1.0, (step - cfg.warmup_steps) / (cfg.total_steps - cfg.warmup_steps))
-        return cfg.lr * (cfg.min_lr_ratio + (1 - cfg.min_lr_ratio) * 0.5 * (1 + math.cos(math.pi * p)))
+        return cfg.warmup_init + (cfg.lr - cfg.warmup_init) * step / cfg.warmup_steps
+    end = cfg.decay_steps if cfg.decay_steps > 0 else cfg.total_steps
+    if cfg.schedule == "cosine" and end > cfg.warmup_steps:
+        p = min(1.0, (step - cfg.warmup_steps) / (end - cfg.warmup_steps))
+        return floor + (cfg.lr - floor) * 0.5 * (1 + math.cos(math.pi * 2 * cfg.num_cycles * p))
+    if cfg.schedule == "wsd" and end > cfg.warmup_steps and cfg.wsd_decay_steps > 0:
+        start = max(cfg.warmup_steps, end - cfg.wsd_decay_steps)
+        if step <= start:
+            return cfg.lr
+        p = min(1.0, (step - start) / max(1, end - start))
+        if cfg.wsd_decay_style == "linear":
+            f = 1.0 - p
+        elif cfg.wsd_decay_style == "cosine":
+            f = 0.5 * (1 + math.cos(math.pi * p))
+        else:                                   # exponential: 2^-p scaled to reach zero at p = 1
+            f = (0.5 ** p - 0.5) * 2.0
+        return floor + (cfg.lr - floor) * f
     return cfg.lr
+
+
+def schedule_from_config(lr_scheduler, lr_scheduler_args, lr: float, fallback_total: int = 0) -> dict:
+    """OptimConfig fields from a role's ``lr_scheduler`` / ``lr_scheduler_args`` blocks. ``lr_scheduler`` is the
+    schedule's name (the reference's form) or a mapping ``{type, warmup_steps, warmup_ratio, min_lr_ratio,
+    total_steps}``."""
+    def g(d, k, default=None):
+        if d is None:
+            return default
+        v = d.get(k, default) if isinstance(d, dict) else getattr(d, k, default)
+        return default if v is None else v
+    if isinstance(lr_scheduler, str) or lr_scheduler is None:
+        a = lr_scheduler_args or {}
+        total = int(g(a, "total_training_steps", -1))
+        total = total if total > 0 else int(fallback_total or 0)
+        warm = int(g(a, "lr_warmup_steps", -1))
+        if warm < 0:
+            warm = int(float(g(a, "lr_warmup_steps_ratio", 0.0)) * total) if total > 0 else 0
+        return dict(schedule=str(lr_scheduler or "constant"), warmup_steps=warm, total_steps=total,
+                    min_lr_ratio=float(g(a, "min_lr_ratio", 0.0)), min_lr=float(g(a, "min_lr", 0.0)),
+                    warmup_init=float(g(a, "lr_warmup_init", 0.0)), num_cycles=float(g(a, "num_cycles", 0.5)),
+                    decay_steps=int(g(a, "lr_decay_steps", 0)), wsd_decay_steps=int(g(a, "lr_wsd_decay_steps", 0)),
+                    wsd_decay_style=str(g(a, "lr_wsd_decay_style", "exponential")))
+    total = int(g(lr_scheduler, "total_steps", 0) or fallback_total or 0)
+    warm = int(g(lr_scheduler, "warmup_steps", 0))
+    if not warm and g(lr_scheduler, "warmup_ratio", 0.0) and total:
+        warm = int(float(g(lr_scheduler, "warmup_ratio")) * total)
+    return dict(schedule=str(g(lr_scheduler, "type", "constant")), warmup_steps=warm, total_steps=total,
+                min_lr_ratio=float(g(lr_scheduler, "min_lr_ratio", 0.0)))
 
 
 class _Packing:

@@ -20,7 +20,8 @@ from typing import Any, Iterable
 import yaml
 
 _MISSING = object()
-_INTERP = re.compile(r"\$\{([^${}]+)\}")
+# one level of braces / brackets may appear inside (the literal defaults "{}" and "[]" of oc.select)
+_INTERP = re.compile(r"\$\{((?:[^${}]|\{\})+)\}")
 
 
 class ConfigError(ValueError):

@@ -630,6 +630,17 @@ extern "C" int axb_rmsnorm_bwd_static(const void* dy, const void* x, const void*
              T, H, need, AXB_RMSNORM_BWD_STATIC_MAX_FLOATS);
     return AXB_LAUNCH_TOO_LARGE;
   }
+  // The workspace address is looked up for the CURRENT device; a stream that lives on another device
+  // would run the kernel there with this device's address, so such a call is refused.
+  if (stream != nullptr) {
+    int cur = -1, sdev = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cudaStreamGetDevice((cudaStream_t)stream, &sdev) == cudaSuccess &&
+        sdev != cur) {
+      snprintf(g_static_err, sizeof(g_static_err),
+               "rmsnorm_bwd_static: the stream belongs to device %d but device %d is current", sdev, cur);
+      return AXB_LAUNCH_BAD_ARG;
+    }
+  }
   float* scratch = nullptr;
   int rc = static_scratch(&scratch);
   if (rc) return rc;

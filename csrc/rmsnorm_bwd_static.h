@@ -11,13 +11,19 @@
 // The workspace is a fixed array in the library's device image, AXB_RMSNORM_BWD_STATIC_MAX_FLOATS
 // floats (9.25 MiB) per device. It holds the per-block partial sums of the weight gradient:
 // axb_rmsnorm_bwd_partials(T) rows of H floats. A call whose partials do not fit (rows * H above the
-// maximum) is refused with AXB_LAUNCH_TOO_LARGE and launches nothing; the maximum covers hidden
-// sizes up to 4096 at any token count, and larger hidden sizes while T < MAX_FLOATS / H.
+// maximum) is refused with AXB_LAUNCH_TOO_LARGE and launches nothing. The row count is
+// min(T, 4 x the SM count of the device this process first used), i.e. at most 592 on a 148-SM B200:
+// there the maximum covers hidden sizes up to 4096 at any token count, and larger hidden sizes while
+// T < MAX_FLOATS / H. On a part with more SMs the row cap is higher, so hidden 4096 is refused once
+// T exceeds MAX_FLOATS / 4096 = 592 rows; the limit itself never changes.
 // axb_rmsnorm_bwd_static_error() gives the text for the last refusal on the calling thread.
 //
 // Set-up: the first call on each device (with that device current) looks up the array's address
 // with cudaGetSymbolAddress and keeps it; the library calls no allocating routine, then or later.
 // Make that first call, or axb_rmsnorm_bwd_static_setup(), before any stream capture begins.
+// Several host threads may make the first call on a device at once: each stores the same address,
+// so the unsynchronised write is harmless. The stream passed in must belong to the current device
+// (a null stream always does); a stream of another device is refused with AXB_LAUNCH_BAD_ARG.
 // Nothing in the workspace has to start at zero: each call writes every partial it later reads.
 //
 // One workspace per device means that two calls on the same device whose kernels can overlap

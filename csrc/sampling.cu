@@ -3,9 +3,13 @@
 // One CTA per sequence row of fp32 logits [B][V]:
 //   z = logits / temperature  ->  optional top-k (count radix-select on sortable float keys)
 //   -> optional top-p (mass radix-select over the kept set) -> renormalise -> inverse-CDF sample
-//   -> logprob of the chosen token UNDER THE PROCESSED DISTRIBUTION (after temperature / top-k /
-//   top-p), which is what the trainer's temperature-scaled log-softmax is compared with
-//   (reference: vLLM fork patch install/vllm/axon.patch:635-680).
+//   -> logprob of the chosen token. Two conventions, chosen per launch:
+//     processed (default): under the PROCESSED distribution (after temperature / top-k / top-p,
+//       renormalised over the kept set), as the reference's vLLM fork reports it
+//       (install/vllm/axon.patch:635-680);
+//     full vocabulary: temperature-scaled log-softmax over ALL tokens, the quantity the trainer's
+//       old_log_probs hold; with top-k / top-p active this is the one importance-sampling
+//       corrections should be fed, since the truncated mass only shapes the draw.
 // temperature == 0 selects arg-max and reports the unscaled log-softmax of that token.
 #include "ptx.cuh"
 #include "host_utils.h"
@@ -96,7 +100,8 @@ __device__ uint32_t radix_select(const float* __restrict__ row, int V, float inv
 __global__ void __launch_bounds__(SMP_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ldl, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, unsigned long long seed,
-              const int* __restrict__ counters, int* __restrict__ tokens, float* __restrict__ logprobs) {
+              const int* __restrict__ counters, int* __restrict__ tokens, float* __restrict__ logprobs,
+              int full_vocab_logprob) {
   __shared__ float red[32];
   __shared__ float hist[256];
   __shared__ float seg[SMP_THREADS];
@@ -164,6 +169,12 @@ sample_kernel(const float* __restrict__ logits, long long ldl, int V, const floa
   }
   seg[threadIdx.x] = ssum;
   const float total = block_reduce_sum(ssum, red);  // includes the barriers that publish seg[]
+  float norm = total;                               // denominator of the reported log-prob
+  if (full_vocab_logprob && thr_key != 0u) {
+    float fs = 0.f;
+    for (int i = threadIdx.x; i < V; i += SMP_THREADS) fs += __expf(row[i] * inv_t - m);
+    norm = block_reduce_sum(fs, red);
+  }
   if (threadIdx.x == 0) {
     const float u = uniform01(seed, (uint32_t)b, counters ? (uint32_t)counters[b] : 0u);
     float target = u * total, cum = 0.f;
@@ -196,7 +207,7 @@ sample_kernel(const float* __restrict__ logits, long long ldl, int V, const floa
     if (choice < 0) choice = last_kept >= 0 ? last_kept : 0;
     sh_choice = choice;
     tokens[b] = choice;
-    logprobs[b] = row[choice] * inv_t - m - logf(total);
+    logprobs[b] = row[choice] * inv_t - m - logf(norm);
   }
 }
 
@@ -221,13 +232,21 @@ using namespace axb;
 
 // temperature/top_k/top_p: per-row device arrays (null = 1.0 / off / 1.0). counters: per-row int
 // mixed into the RNG stream (e.g. the decode step), may be null.
+// full_vocab_logprob: 0 = log-prob under the processed (truncated, renormalised) distribution, 1 = under the
+// temperature-scaled softmax over the whole vocabulary.
+extern "C" int axb_sample_ex(const float* logits, long long ldl, int B, int V, const float* temperature,
+                             const int* top_k, const float* top_p, unsigned long long seed, const int* counters,
+                             int* tokens, float* logprobs, int full_vocab_logprob, void* stream) {
+  if (B <= 0 || V <= 0) return AXB_LAUNCH_BAD_ARG;
+  sample_kernel<<<B, SMP_THREADS, 0, (cudaStream_t)stream>>>(logits, ldl, V, temperature, top_k, top_p, seed,
+                                                            counters, tokens, logprobs, full_vocab_logprob);
+  return check_launch();
+}
+
 extern "C" int axb_sample(const float* logits, long long ldl, int B, int V, const float* temperature,
                           const int* top_k, const float* top_p, unsigned long long seed, const int* counters,
                           int* tokens, float* logprobs, void* stream) {
-  if (B <= 0 || V <= 0) return AXB_LAUNCH_BAD_ARG;
-  sample_kernel<<<B, SMP_THREADS, 0, (cudaStream_t)stream>>>(logits, ldl, V, temperature, top_k, top_p, seed,
-                                                            counters, tokens, logprobs);
-  return check_launch();
+  return axb_sample_ex(logits, ldl, B, V, temperature, top_k, top_p, seed, counters, tokens, logprobs, 0, stream);
 }
 
 extern "C" int axb_repetition_penalty(float* logits, long long ldl, int B, int V, const unsigned char* seen,

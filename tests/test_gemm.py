@@ -6,7 +6,7 @@ from axon_b200.ops import gemm as G
 from axon_b200.ops import _common as C
 
 SHAPES = [(128, 256, 64), (256, 512, 256), (304, 200, 136), (1024, 4096, 4096), (72, 24, 72),
-          (4096, 1024, 512), (136, 136, 8)]
+          (4096, 1024, 512), (136, 136, 8), (200, 264, 16), (128, 128, 24), (392, 136, 40)]
 
 
 def _rand(*shape):
@@ -14,9 +14,15 @@ def _rand(*shape):
 
 
 def _check(out, ref, K):
-    tol = 2e-2 * (K ** 0.5) * 0.25 + 1e-2
+    """bf16 outputs: half an ulp of the result's magnitude (inputs ~N(0, 0.25), so |ref| ~ 0.25 sqrt(K)) plus slack.
+    fp32 outputs carry only the accumulation-order error of exact bf16 products: 1e-3 of the result's scale."""
+    scale = 0.25 * (K ** 0.5)
     err = (out.float() - ref).abs().max().item()
-    assert err < tol, f"max err {err} tol {tol}"
+    if out.dtype == torch.float32:
+        tol = 1e-3 * max(scale, ref.abs().max().item()) + 1e-5
+    else:
+        tol = 2e-2 * scale + 1e-2
+    assert err < tol, f"max err {err} tol {tol} dtype {out.dtype}"
 
 
 @pytest.mark.gpu

@@ -247,6 +247,31 @@ def test_sampling_distribution_and_logprobs():
 
 
 @pytest.mark.gpu
+def test_sampling_full_vocabulary_logprob_mode():
+    """With top-p / top-k active, ``logprobs_mode="full"`` returns the temperature-scaled log-softmax over the
+    whole vocabulary for the token drawn from the truncated set."""
+    from axon_b200.ops import paged as P
+    torch.manual_seed(9)
+    B, V = 4, 3000
+    logits = (torch.randn(B, V) * 2).cuda()
+    temp = torch.tensor([1.0, 0.8, 1.2, 1.0]).cuda()
+    top_k = torch.tensor([0, 40, 0, 10], dtype=torch.int32).cuda()
+    top_p = torch.tensor([0.5, 1.0, 0.7, 0.9]).cuda()
+    kept = P._ref_process(logits.cpu(), temp.cpu(), top_k.cpu(), top_p.cpu())
+    full = torch.log_softmax(logits.cpu().float() / temp.cpu()[:, None], -1)
+    for it in range(20):
+        ctr = torch.full((B,), it, dtype=torch.int32, device="cuda")
+        toks, lps = P.sample(logits, temp, top_k, top_p, seed=5, counters=ctr, logprobs_mode="full")
+        toks2, lps2 = P.sample(logits, temp, top_k, top_p, seed=5, counters=ctr)
+        assert torch.equal(toks, toks2)                          # the draw does not depend on the reporting mode
+        t = toks.cpu().long()
+        assert torch.isfinite(kept.gather(1, t[:, None])).all()
+        assert (lps.cpu() - full.gather(1, t[:, None])[:, 0]).abs().max() < 2e-3
+        assert (lps2.cpu() - kept.gather(1, t[:, None])[:, 0]).abs().max() < 2e-3
+        assert (lps <= lps2 + 1e-5).all()                        # truncation can only raise the reported probability
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (8, 1), (4, 4)])
 def test_paged_decode_shared_prefix_matches_plain_decode(Hq, Hkv):
     """Decode attention over a batch with shared prompt pages (one prefix item per group + a suffix item per

@@ -94,3 +94,22 @@ def test_policy_engine_gpu_step():
     assert e.master is None
     e.load_optimizer()
     assert e.master is not None and e.master.is_cuda
+
+
+def test_lr_schedules_and_both_config_forms():
+    """Warm-up from a start value, cosine to the larger of the two floors, warm-up / stable / decay, and the two
+    accepted spellings of the schedule block."""
+    from axon_b200.trainer.policy import OptimConfig, lr_at, schedule_from_config
+    c = OptimConfig(lr=1.0, warmup_steps=4, warmup_init=0.2, total_steps=24, schedule="cosine", min_lr_ratio=0.1, min_lr=0.05)
+    assert abs(lr_at(c, 2) - 0.6) < 1e-9 and abs(lr_at(c, 4) - 1.0) < 1e-9
+    assert abs(lr_at(c, 14) - (0.1 + 0.9 * 0.5)) < 1e-9 and abs(lr_at(c, 24) - 0.1) < 1e-9 and abs(lr_at(c, 99) - 0.1) < 1e-9
+    w = OptimConfig(lr=1.0, warmup_steps=2, total_steps=20, schedule="wsd", wsd_decay_steps=10, wsd_decay_style="linear")
+    assert lr_at(w, 10) == 1.0 and abs(lr_at(w, 15) - 0.5) < 1e-9 and abs(lr_at(w, 20)) < 1e-9
+    e = OptimConfig(lr=1.0, total_steps=10, schedule="wsd", wsd_decay_steps=10, wsd_decay_style="exponential")
+    assert lr_at(e, 0) == 1.0 and 0 < lr_at(e, 5) < 0.5 and abs(lr_at(e, 10)) < 1e-9
+    a = schedule_from_config("cosine", {"total_training_steps": 100, "lr_warmup_steps": -1, "lr_warmup_steps_ratio": 0.1,
+                                        "min_lr_ratio": 0.2, "num_cycles": 0.5}, 1e-5)
+    assert a["schedule"] == "cosine" and a["warmup_steps"] == 10 and a["total_steps"] == 100 and a["min_lr_ratio"] == 0.2
+    b = schedule_from_config({"type": "cosine", "warmup_ratio": 0.1, "total_steps": 100, "min_lr_ratio": 0.2}, None, 1e-5)
+    assert (b["schedule"], b["warmup_steps"], b["total_steps"]) == ("cosine", 10, 100)
+    assert schedule_from_config("constant", {"total_training_steps": -1}, 1e-5, fallback_total=7)["total_steps"] == 7

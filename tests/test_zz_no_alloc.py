@@ -41,11 +41,19 @@ def _reference(x, dy, dres, w, rstd):
 
 
 def _call_static(lib, x, dy, dres, w, rstd, dw, accumulate):
+    """The raw call, bracketed by a check that it took no device memory: neither through PyTorch's allocator
+    (``memory_allocated`` / ``memory_reserved``) nor behind its back (free bytes reported by the driver)."""
     T, H = x.shape
     dx = torch.empty_like(x)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    before = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
     rc = lib.axb_rmsnorm_bwd_static(_p(dy), _p(x), _p(w), _p(rstd), _p(dres), _p(dx), _p(dw), int(accumulate),
                                     ctypes.c_longlong(T), int(H), stream)
+    torch.cuda.synchronize()
+    after = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+    assert after[1:] == before[1:], (before, after)
+    assert after[0] >= before[0], (before, after)          # other processes may free memory meanwhile, this call takes none
     return rc, dx
 
 
