@@ -117,6 +117,7 @@ class AsyncPPO(PPODriverBase):
                         self.sampler_wg.pause_all(str(cfg_get(self.config, "sampler_pausing_strategy", "continue")))
                         self._broadcast_weights()
                         self.sampler_wg.continue_all()
+                    metrics.update(self.weight_sync_metrics())
                 shards = self.actor_wg.get_batch_metrics_and_clear(timing)
                 metrics.update(reduce_data_metrics([s["data"] for s in shards]))
                 metrics.update(reduce_timing_metrics([s["timing"] for s in shards]))

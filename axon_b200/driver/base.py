@@ -215,9 +215,23 @@ class PPODriverBase(ABC):
         """Trainer -> sampler weight push: receivers are posted first (non-blocking), then the senders
         run. The routing table travels once; workers keep their compiled plans."""
         self._nonblocking(self.sampler_wg, "receive_trainer_to_sampler_weights", routing_table=self.routing_table)
-        self.actor_wg.send_trainer_to_sampler_weights(routing_table=self.routing_table)
+        sent = self.actor_wg.send_trainer_to_sampler_weights(routing_table=self.routing_table)
         self._join_nonblocking()
         self.routing_table = None
+        # what the last push did, per trainer rank: bytes, seconds, transport ("peer-store kernel" | "messages")
+        self.last_weight_sync = sent if isinstance(sent, list) else [sent]
+
+    def weight_sync_metrics(self) -> dict:
+        """Scalars of the last trainer -> sampler push for the step log."""
+        recs = [r for r in (getattr(self, "last_weight_sync", None) or []) if isinstance(r, dict)]
+        if not recs:
+            return {}
+        out = {"sync/bytes": float(sum(r.get("bytes", 0) for r in recs)),
+               "sync/seconds_max": float(max(r.get("seconds", 0.0) for r in recs)),
+               "sync/peer_store_kernel": float(all(r.get("transport") == "peer-store kernel" for r in recs))}
+        if all("kernel_ms" in r for r in recs):
+            out["sync/kernel_ms_max"] = float(max(r["kernel_ms"] for r in recs))
+        return out
 
     def _collect_world_sizes(self) -> list[int]:
         sizes = [wg.world_size for wg, on in ((self.critic_wg, self.use_critic), (self.ref_policy_wg, self.use_ref),

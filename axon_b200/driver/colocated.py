@@ -91,7 +91,12 @@ def attach_valid_counts(mini: DataProto, process_group=None) -> None:
     tok = rm.sum().float()
     rows = (rm.sum(-1) > 0).sum().float()
     cnt = torch.stack([tok, rows])
-    if process_group is not None or (dist.is_initialized() and dist.get_world_size() > 1):
+    # an explicit group decides (a group of one rank needs no reduction); without one the default group is used
+    if process_group is not None:
+        reduce = dist.get_world_size(process_group) > 1
+    else:
+        reduce = dist.is_initialized() and dist.get_world_size() > 1
+    if reduce:
         dev = "cuda" if dist.get_backend(process_group) == "nccl" else "cpu"
         c = cnt.to(dev)
         dist.all_reduce(c, group=process_group)
@@ -112,8 +117,11 @@ class ColocatedRLRunner:
         self.policy = PolicyEngine(model, cfg.optim, process_group, cfg.max_token_len_per_gpu, cfg.temperature)
         self.engine: GenerationEngine | None = None
         self.reward_fn = reward_fn
+        # without an explicit group the runner is data parallel over the default group (if one exists)
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        if process_group is None and dist.is_initialized():
+            self.pg = dist.group.WORLD
         self.rng = np.random.default_rng(seed + 7919 * self.rank)
         self.seed = seed
         self.global_step = 0
@@ -178,7 +186,8 @@ class ColocatedRLRunner:
         self.phase_detail = dict(offload=tb - ta, kv_alloc=time.perf_counter() - tb, kv_pages=pages, offloaded=bool(off))
 
     def _enter_training(self) -> None:
-        self.engine.sleep()
+        if self.engine is not None:          # trainer-only ranks of a disaggregated run have no engine
+            self.engine.sleep()
         self.policy.load_optimizer()
         if self.cfg.recompute == "auto" and self.device.type == "cuda":
             # keep as many activations as the memory left after parameters, gradients and optimizer
@@ -230,6 +239,23 @@ class ColocatedRLRunner:
         self._enter_training()
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
+        t2x = time.perf_counter()
+        out = self.train_on_samples(prompts, outs, rewards, groups)
+        self.timing["prepare_and_old_logprob"] += t2x - t2
+        self.timing.update(setup=t1 - t0, rollout=t2 - t1, total=time.perf_counter() - t0, enter_training=t2x - t2,
+                           offload=self.phase_detail.get("offload", 0.0), kv_alloc=self.phase_detail.get("kv_alloc", 0.0))
+        out.update({f"time/{k}": v for k, v in self.timing.items()})
+        return out
+
+    def train_on_samples(self, prompts: list[list[int]], outs, rewards, groups: list[str]) -> dict:
+        """The training half of a step on finished rollouts: rewards -> batch in the reference schema -> advantages ->
+        old log-probs -> mini-batches of forward_backward + optim_step. ``outs[i]`` belongs to ``prompts[i]``; rows
+        with equal ``groups[i]`` form one advantage group. Used by ``step`` and, on trainer-only ranks of a
+        disaggregated run, directly."""
+        c = self.cfg
+        t2 = time.perf_counter()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
         t2a = time.perf_counter()
         if rewards is None:
             rewards = np.array([self.reward_fn(p, o) for p, o in zip(prompts, outs)], dtype=np.float32) \
@@ -254,7 +280,7 @@ class ColocatedRLRunner:
             for s in range(0, len(data), rows_per_mini):
                 mini = data.slice(s, s + rows_per_mini)
                 mini.meta_info = data.meta_info
-                attach_valid_counts(mini, self.pg if self.world > 1 else None)
+                attach_valid_counts(mini, self.pg)
                 m = self.policy.forward_backward(mini, c.loss, c.loss_args)
                 opt = self.policy.optim_step()
                 for k, v in m.items():
@@ -266,11 +292,10 @@ class ColocatedRLRunner:
         self.global_step += 1
         n_tok = int(data.batch["attention_mask"].sum())
         n_resp = int(rm.sum())
-        self.timing = dict(setup=t1 - t0, rollout=t2 - t1, prepare_and_old_logprob=t3 - t2, train=t4 - t3, total=t4 - t0,
-                           enter_training=t2a - t2, build_batch=t2b - t2a, old_logprob=t3 - t2b,
-                           offload=self.phase_detail.get("offload", 0.0), kv_alloc=self.phase_detail.get("kv_alloc", 0.0))
+        self.timing = dict(prepare_and_old_logprob=t3 - t2, train=t4 - t3, total=t4 - t2,
+                           enter_training=t2a - t2, build_batch=t2b - t2a, old_logprob=t3 - t2b)
         self.phase_detail["recompute"] = self.model.recompute
         return {"loss": float(np.sum(metrics.get("loss", [0.0]))), "grad_norm": opt.get("grad_norm", 0.0),
                 "tokens": n_tok, "response_tokens": n_resp, "sequences": len(data),
                 "reward_mean": float(np.mean(rewards)), "sampler_probs_diff_mean": float(gap),
-                "entropy": float(np.mean(metrics.get("entropy", [0.0]))), **{f"time/{k}": v for k, v in self.timing.items()}}
+                "entropy": float(np.mean(metrics.get("entropy", [0.0])))}

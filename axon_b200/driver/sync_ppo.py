@@ -87,6 +87,7 @@ class SyncPPO(PPODriverBase):
                         asyncio.run(self.sampling_client.pause_all(cfg_get(self.config, "sampler_pausing_strategy", "continue")))
                         self._broadcast_weights()
                         asyncio.run(self.sampling_client.continue_all())
+                    metrics.update(self.weight_sync_metrics())
                 self._finish_step(batch, metrics, timing)
         finally:
             stop.set()

@@ -220,6 +220,7 @@ class TPDenseModel:
         """``batch`` is the full packed batch, its length a multiple of 128 * W (``pad_packed_batch``).
         Returns (log-prob, entropy) of THIS rank's tokens [T/W]."""
         c = self.cfg
+        self.tp.begin_pass()
         T = batch.input_ids.numel()
         assert T % (128 * self.tp.world) == 0, "pad the batch with pad_packed_batch(batch, 128 * tp)"
         sl = self.local_slice(T)
@@ -250,6 +251,7 @@ class TPDenseModel:
         assert s is not None
         self._saved = None
         c = self.cfg
+        self.tp.begin_pass()
         self.params.alloc_grads()
         g_lp = None if g_logprob is None else g_logprob.float().contiguous()
         g_ent = None if g_entropy is None else g_entropy.float().contiguous()

@@ -44,10 +44,13 @@ class TPContext:
         self._ag = self._st = None
         self._side = None
         self.fused_max_cols = 512      # wider outputs take the chunked path of ``allgather_gemm``
-        self._turn = 0
+        self._ag_turn = self._rs_turn = 0      # one counter per buffer kind, so that consecutive calls of a kind alternate
+        self._aligned = False
         if self.fused:
             assert max_rows_per_rank % 128 == 0 and max_rows_per_rank > 0 and max_width > 0
-            # two rotating sets so that a buffer is never rewritten while a slower peer may still read it
+            # Two sets per kind, used in turn: a rank that runs ahead into the next all-gather -> GEMM writes the
+            # OTHER activation buffer while a slower peer may still read the previous one; the device barrier of
+            # the call after that orders the reuse. Likewise for the reduce-scatter staging slots.
             self._ag = [SymmetricBuffer(max_rows_per_rank * max_width, torch.bfloat16, group, self.device) for _ in range(2)]
             self._st = [SymmetricBuffer(self.world * max_rows_per_rank * max_width, torch.bfloat16, group, self.device)
                         for _ in range(2)]
@@ -84,10 +87,20 @@ class TPContext:
         return t
 
     # ------------------------------------------------------------------ fused paths
-    def _align_streams(self) -> None:
-        # device barriers wait a bounded ~2 s; a stream-ordered NCCL all-reduce of one element first
-        # removes host-side skew between the ranks (plumbing, not data)
+    def begin_pass(self) -> None:
+        """Call at the start of a forward or backward pass (every rank of the group does, in the same order). The
+        first fused collective after it lines the ranks' streams up with one stream-ordered NCCL all-reduce of one
+        element: the device barriers wait a bounded ~2 s, and ranks can enter a pass seconds apart (uneven data
+        loading, a checkpoint write). Inside a pass every layer's barriers keep the ranks within microseconds of
+        each other, so the later collectives of the pass skip the all-reduce (one NCCL launch per pass instead of
+        one per collective)."""
+        self._aligned = False
+
+    def _align_streams(self, force: bool = False) -> None:
+        if self._aligned and not force:
+            return
         dist.all_reduce(self._sync, group=self.group)
+        self._aligned = True
 
     def allgather_gemm(self, x_local: torch.Tensor, w: torch.Tensor, w_is_kn: bool = False, out_dtype=None) -> torch.Tensor:
         """x_local [T/W, K] (this rank's rows) -> concat(x)[T, K] @ (w [N, K]^T, or w [K, N] when ``w_is_kn``)."""
@@ -98,8 +111,8 @@ class TPContext:
         rows, K = x_local.shape
         N = w.shape[1] if w_is_kn else w.shape[0]
         assert rows % 128 == 0 and rows * K <= self.rows * self.width, "activation shard exceeds the TP workspace"
-        buf = self._ag[self._turn & 1]
-        self._turn += 1
+        buf = self._ag[self._ag_turn & 1]
+        self._ag_turn += 1
         buf.tensor[: rows * K].view(rows, K).copy_(x_local)
         self._align_streams()
         self.barrier()                                           # every rank's shard is in place
@@ -150,8 +163,8 @@ class TPContext:
         N = w.shape[1] if w_is_kn else w.shape[0]
         rows = T // self.world
         assert T % self.world == 0 and rows * N <= self.rows * self.width and N % 8 == 0
-        st = self._st[self._turn & 1]
-        self._turn += 1
+        st = self._st[self._rs_turn & 1]
+        self._rs_turn += 1
         rc = C.lib().axb_gemm_scatter(C.ptr(x), C.ptr(w), st.ptr_array(), self.world, self.rank, T, N, K,
                                       ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(N),
                                       int(w_is_kn), C.ptr(C.status(self.device)), C.stream())

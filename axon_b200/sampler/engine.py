@@ -37,6 +37,7 @@ class _Seq:
     leader: object = None      # during admission: the sequence whose prompt pages and prefill this one reuses
     share_key: int = -1        # rid of the sequence whose prompt pages this one shares (its own rid for that sequence)
     shared_pages: int = 0      # number of leading pages shared with the group
+    route_chunks: list = field(default_factory=list)    # routed-experts capture: int16 [n, layers, top-k] pieces in token order
 
 
 class GenerationEngine:
@@ -69,6 +70,11 @@ class GenerationEngine:
         # fork's convention); "full": temperature-scaled log-softmax over the whole vocabulary (what the trainer
         # recomputes), which keeps importance-sampling corrections unbiased under truncation.
         self.logprobs_mode = "processed"
+        # Routed-experts capture (sparse models): every token's chosen experts per layer are recorded and returned as
+        # ``TokenOutput.moe_routermap`` int16 [prompt + output tokens, moe layers, top-k]; the row of the last sampled
+        # token, which never went through the model, is -1 (reference: the vLLM fork's routed_experts output,
+        # install/vllm/axon.patch:586-748, consumed at axon/engine/engine.py:1157-1175). The trainer replays it.
+        self.capture_routing = False
         # Decode attention over the shared pages once per group (csrc/paged_attention_shared.cu). Off by default: with
         # one CTA per SM the per-CTA start-up of the extra prefix / suffix items costs as much as the shared tiles
         # save once responses are a few pages long (measured end to end); the kernel pays off for long shared
@@ -142,6 +148,8 @@ class GenerationEngine:
         s.done = True
         s.out.finish_reason = reason
         s.out.stop_reason = stop
+        if self.capture_routing:
+            s.out.moe_routermap = self._routermap(s)
         if self.cache is not None:
             self.cache.release(s.pages)
         s.pages = []
@@ -219,7 +227,16 @@ class GenerationEngine:
         tok_seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(lens)]).to(self.device)
         last = (torch.tensor(lens).cumsum(0) - 1).to(self.device)
         bt = self._block_table(seqs)
+        if self.capture_routing:
+            self.model.last_routing = None
         logits = self.model.prefill(batch, self.cache, tok_seq, batch.position_ids, bt, last)
+        if self.capture_routing:
+            rt = self._take_routing()
+            if rt is not None:
+                rt_h, off = rt.cpu().numpy(), 0
+                for s, n in zip(seqs, lens):
+                    s.route_chunks = [rt_h[off:off + n]]       # a re-prefill after preemption covers prompt + output so far
+                    off += n
         for s, n in zip(seqs, lens):
             s.length = n
         self.stats["prefill_tokens"] += sum(lens)
@@ -231,6 +248,8 @@ class GenerationEngine:
                 rows.append(row[id(lead)])
                 if s.leader is not None:
                     s.length = lead.length
+                    if self.capture_routing and getattr(lead, "route_chunks", None):
+                        s.route_chunks = [lead.route_chunks[0]]     # same prompt, same routing
                     full = len(s.prompt) // PAGE
                     if len(s.prompt) % PAGE:          # the partly filled last prompt page is private: copy it
                         src.append(lead.pages[full])
@@ -269,7 +288,11 @@ class GenerationEngine:
                           grp_zero=zi(ng), grp_keys=g["grp_keys"], max_shared_pages=self.max_pages_per_seq)
 
         def run():
+            if self.capture_routing:
+                self.model.last_routing = None
             logits = self.model.decode(g["tokens"], g["pos"], self.cache, g["bt"], g["lens"], shared=shared)
+            if self.capture_routing:
+                g["routing"] = self._take_routing()      # a graph output: same memory on every replay
             return P.sample(logits, g["temp"], g["top_k"], g["top_p"], seed=self.seed, counters=g["ctr"],
                             logprobs_mode=self.logprobs_mode)
 
@@ -347,7 +370,36 @@ class GenerationEngine:
         g["graph"].replay()
         from ..ops import _common as C
         C.LAUNCH_COUNT += g["launches"]
+        if self.capture_routing and g.get("routing") is not None:
+            rt_h = g["routing"][:B].cpu().numpy()
+            for i, s in enumerate(seqs):
+                s.route_chunks.append(rt_h[i:i + 1].copy())
         return g["out_tokens"][:B].cpu().tolist(), g["out_lps"][:B].cpu().tolist()
+
+    def enable_routing_capture(self, on: bool = True) -> None:
+        if on and getattr(self.cfg, "num_experts", 0) <= 0:
+            raise ValueError("routed-experts capture needs a sparse (mixture-of-experts) model")
+        self.capture_routing = bool(on)
+        self.model.capture_routing = bool(on)
+        self._graphs.clear()                     # decode graphs are captured with or without the routing output
+
+    def _take_routing(self) -> torch.Tensor | None:
+        """The expert ids of the model call that just ran: int16 [tokens, moe layers, top-k] (still on the device)."""
+        rt = getattr(self.model, "last_routing", None)
+        self.model.last_routing = None
+        if not rt:
+            return None
+        return torch.stack([r.to(torch.int16) for r in rt], dim=1)
+
+    def _routermap(self, s) -> "np.ndarray | None":
+        chunks = getattr(s, "route_chunks", None)
+        if not chunks:
+            return None
+        rm = np.concatenate(chunks, axis=0)
+        n = len(s.prompt) + len(s.out.token_ids)
+        out = np.full((n,) + rm.shape[1:], -1, dtype=np.int16)
+        out[: min(n, rm.shape[0])] = rm[:n]
+        return out
 
     def _record(self, seqs, toks_h, lps_h) -> None:
         eos = self.cfg.eos_token_id
@@ -383,7 +435,15 @@ class GenerationEngine:
         tokens = torch.tensor([s.last_token for s in seqs], dtype=torch.int32).to(self.device)
         pos = torch.tensor([s.length for s in seqs], dtype=torch.int32).to(self.device)
         bt = self._block_table(seqs)
+        if self.capture_routing:
+            self.model.last_routing = None
         logits = self.model.decode(tokens, pos, self.cache, bt, pos + 1)
+        if self.capture_routing:
+            rt = self._take_routing()
+            if rt is not None:
+                rt_h = rt.cpu().numpy()
+                for i, s in enumerate(seqs):
+                    s.route_chunks.append(rt_h[i:i + 1].copy())
         for s in seqs:
             s.length += 1
         self.stats["decode_tokens"] += len(seqs)

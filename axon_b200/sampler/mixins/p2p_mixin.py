@@ -2,12 +2,17 @@
 (reference: axon/sampler/mixins/p2p_mixin.py:60-757).
 
 The sampler publishes what each of its ranks needs (``get_parameter_mapping``: per fused parameter
-the tensor-/expert-parallel shard this rank owns), posts its receives and copies arriving slices
-into its parameter shards. With tensor parallel size 1 the shard layout equals the engine's flat
-parameter buffer, so received bytes land directly in the live weights.
+the tensor-/expert-parallel shard this rank owns). With tensor parallel size 1 the shard layout equals
+the engine's flat parameter buffer, so pushed bytes land directly in the live weights.
+
+On CUDA within one node the sampler moves its parameters into an IPC-exportable allocation at connect
+time and hands the handle to the trainers; a push is then the trainers' plan kernel storing into that
+buffer, and this side only waits for the bridge all-reduce that follows the stores. Elsewhere it posts
+one receive per sending trainer and unpacks the messages.
 """
 from __future__ import annotations
 
+import socket
 import time
 
 import numpy as np
@@ -31,15 +36,38 @@ class SamplerP2PMixin:
     bridge_pg = None
     _recv_plans = None
     _recv_stage: dict | None = None
+    _peer_path = False
+    _ipc_buffer = None
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def connect_sampler_to_trainer(self, master_addr: str, master_port: int, world_size: int, rank_offset: int):
+        from ...trainer.mixins.p2p_mixin import exchange_peer_info, peer_store_path_possible
         self._n_trainers = rank_offset
         self.bridge_pg = init_trainer_sampler_process_group(master_addr, master_port, rank_offset + self.rank, world_size,
                                                             backend="nccl" if self.device.type == "cuda" else "gloo")
-        t = torch.zeros(1, device=self.device)
-        dist.all_reduce(t, group=self.bridge_pg)
+        self._bridge_token = torch.zeros(1, device=self.device)
+        dist.all_reduce(self._bridge_token, group=self.bridge_pg)
+        mine = {"role": "sampler", "rank": self.rank, "host": socket.gethostname(), "cuda": self.device.type == "cuda",
+                "tp": self.tp, "handle": None, "offsets": None}
+        if self.device.type == "cuda" and self.tp == 1 and not getattr(self, "shares_trainer_weights", False):
+            mine["handle"], mine["offsets"] = self._export_parameters()
+        infos = exchange_peer_info(self.bridge_pg, mine)
+        self._peer_path = peer_store_path_possible(infos)
         return self.bridge_pg.rank()
+
+    def _export_parameters(self):
+        """Move the live parameters into an allocation other processes can map; returns (handle, offsets)."""
+        from ...parallel.ipc import IpcBuffer
+        p = self.model.params
+        if self._ipc_buffer is None:
+            buf = IpcBuffer(p.flat.numel(), p.flat.dtype, self.device)
+            buf.tensor.copy_(p.flat)
+            torch.cuda.current_stream().synchronize()
+            p.rebind(buf.tensor)
+            self._ipc_buffer = buf
+            if getattr(self, "engine", None) is not None:
+                self.engine._graphs.clear()                  # captured decode graphs hold the old addresses
+        return self._ipc_buffer.handle(), {n: o for n, (o, _) in p.offsets.items()}
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def get_parameter_mapping(self):
@@ -62,6 +90,14 @@ class SamplerP2PMixin:
             self._recv_plans = None
         assert getattr(self, "routing_table", None) is not None, "no routing table: the first push must carry it"
         t0 = time.monotonic()
+        if self._peer_path:
+            # the trainers' kernels store into this rank's live buffer; generation must not read it meanwhile
+            with self.server._ctl_lock, torch.cuda.device(self.device):
+                torch.cuda.current_stream().synchronize()
+                dist.all_reduce(self._bridge_token, group=self.bridge_pg)     # completes after every trainer's stores
+                torch.cuda.current_stream().synchronize()
+            return {"bytes": self.model.params.numel * self.model.params.flat.element_size(), "seconds": time.monotonic() - t0,
+                    "transport": "peer-store kernel"}
         if self._recv_plans is None:
             mine = next(m for m in self.routing_table.sampler_rank_mapping if m.rank == self.rank).params
             my_off = self._shard_offsets(mine)
@@ -73,7 +109,7 @@ class SamplerP2PMixin:
             got = recv_plans(self._recv_plans, self.model.params.flat, self.bridge_pg, self._recv_stage)
         if _cfg(self.scfg, "offload_p2p_buffer", False):
             self._recv_stage = {}
-        return {"bytes": got, "seconds": time.monotonic() - t0}
+        return {"bytes": got, "seconds": time.monotonic() - t0, "transport": "messages"}
 
     @staticmethod
     def _print_p2p_mismatch(actor_map, sampler_map) -> str:
@@ -81,7 +117,7 @@ class SamplerP2PMixin:
         s = {p.param_name: p.full_param_shape for m in sampler_map for p in m.params}
         lines = [f"only on trainer: {n}" for n in sorted(set(a) - set(s))] + [f"only on sampler: {n}" for n in sorted(set(s) - set(a))]
         lines += [f"shape differs: {n}: {a[n]} vs {s[n]}" for n in sorted(set(a) & set(s)) if tuple(a[n]) != tuple(s[n])]
-        return "\\n".join(lines)
+        return "\n".join(lines)
 
 
 class _Zero(dict):

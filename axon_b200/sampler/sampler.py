@@ -98,6 +98,8 @@ class SamplerWorker(Worker, DistProfilerExtension):
         if _get(scfg, "enforce_eager", False):
             self.engine.use_cuda_graph = False
         self.engine.logprobs_mode = str(_get(scfg, "logprobs_mode", "processed"))
+        if _get(cfg, "moe_replay", False) and getattr(self.model.cfg, "num_experts", 0) > 0:
+            self.engine.enable_routing_capture(True)      # outputs carry the routed experts for the trainer to replay
         max_len = _get(scfg, "max_model_len", None)
         if max_len:
             self.engine.set_max_model_len(int(max_len))

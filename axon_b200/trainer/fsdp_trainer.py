@@ -154,7 +154,7 @@ class TrainerWorker(Worker, DistProfilerExtension):
                            grad_norm_threshold=float(_get(cfg, "fsdp.grad_norm_threshold", 0.0) or 0.0), **sched)
         self.engine = PolicyEngine(self.model, ocfg, process_group=self.pg,
                                    max_token_len_per_gpu=int(_get(cfg, "max_token_len_per_gpu", 16384)) * self.ulysses_sequence_parallel_size,
-                                   temperature=1.0)
+                                   temperature=1.0, shard_size=int(_get(cfg, "fsdp.fsdp_size", -1) or -1))
         # multi-token prediction: on when the model has such a module and the factor is set (the reference
         # switches it with AXON_ENABLE_MTP and takes megatron's mtp_loss_scaling_factor)
         if os.environ.get("AXON_ENABLE_MTP", "1") not in ("0", "false", "False"):

@@ -143,20 +143,43 @@ class _Packing:
 
 class PolicyEngine:
     def __init__(self, model: DenseModel, optim: OptimConfig | None = None, process_group=None,
-                 max_token_len_per_gpu: int = 8192, temperature: float = 1.0, fused_zero1: bool | None = None):
+                 max_token_len_per_gpu: int = 8192, temperature: float = 1.0, fused_zero1: bool | None = None,
+                 shard_size: int = -1):
+        """``shard_size``: number of ranks the optimizer state (and the reduced gradient) is sharded over.
+        -1 or the group size: every data-parallel rank holds 1 / world of it. A divisor S of the group size gives
+        hybrid sharding (the reference's ``fsdp.fsdp_size``, axon/utils/fsdp/utils.py:550-573): consecutive ranks
+        form shard groups of S, ranks with the same place in their groups are replicas; gradients are
+        reduce-scattered inside a shard group and all-reduced across replicas, parameters are gathered inside
+        the shard group only, so the wide collectives stay within S ranks."""
         self.model = model
         self.cfg = optim or OptimConfig()
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if (process_group is not None or dist.is_initialized()) else 1
         self.rank = dist.get_rank(process_group) if self.world > 1 else 0
+        self.opt_group, self.rep_group = process_group, None
+        self.opt_world, self.opt_rank = self.world, self.rank
+        if shard_size is not None and 0 < int(shard_size) < self.world:
+            S = int(shard_size)
+            assert self.world % S == 0, f"shard size {S} must divide the data-parallel size {self.world}"
+            ranks = dist.get_process_group_ranks(process_group if process_group is not None else dist.group.WORLD)
+            for g in range(self.world // S):                      # every rank creates every group, in the same order
+                grp = dist.new_group([ranks[g * S + i] for i in range(S)])
+                if g == self.rank // S:
+                    self.opt_group = grp
+            for i in range(S):
+                grp = dist.new_group([ranks[g * S + i] for g in range(self.world // S)])
+                if i == self.rank % S:
+                    self.rep_group = grp
+            self.opt_world, self.opt_rank = S, self.rank % S
+            fused_zero1 = False                                   # the peer-memory step reduces over one flat group
         self.max_tokens = max_token_len_per_gpu
         self.mtp_loss_coef = 0.0      # weight of the multi-token-prediction loss (models with such a module)
         self.temperature = temperature
         self.device = model.device
         n = model.params.numel
-        per = (n + self.world - 1) // self.world
+        per = (n + self.opt_world - 1) // self.opt_world
         per = (per + 127) // 128 * 128
-        self.shard = (min(n, self.rank * per), min(n, (self.rank + 1) * per))
+        self.shard = (min(n, self.opt_rank * per), min(n, (self.opt_rank + 1) * per))
         self.shard_size = per
         self.master = self.exp_avg = self.exp_avg_sq = None
         self.opt_step = 0                     # optimizer updates so far (Adam bias correction)
@@ -421,8 +444,8 @@ class PolicyEngine:
         if hasattr(self.model, "sync_replicated_grads") and self.world == 1:
             pass        # single data-parallel rank: replicated gradients were summed before the reduce below
         OPT.sumsq(grad_shard, self.state)
-        if self.world > 1:
-            dist.all_reduce(self.state[:1], group=self.pg)
+        if self.opt_world > 1:
+            dist.all_reduce(self.state[:1], group=self.opt_group)
         self._tensor_parallel_norm(grad_shard, lo)
         OPT.clip_coef(self.state, self.cfg.grad_clip, self.cfg.grad_norm_threshold)
         self.opt_step += 1
@@ -451,8 +474,8 @@ class PolicyEngine:
             a2, b2 = max(a, lo) - lo, min(b, lo + grad_shard.numel()) - lo
             if b2 > a2:
                 rep += grad_shard[a2:b2].float().pow(2).sum()
-        if self.world > 1:
-            dist.all_reduce(rep, group=self.pg)
+        if self.opt_world > 1:
+            dist.all_reduce(rep, group=self.opt_group)
         tot = self.state[:1].clone()
         tp.all_reduce_(tot)
         self.state[:1] = tot - (tp.world - 1) * rep
@@ -462,13 +485,13 @@ class PolicyEngine:
                 a2, b2 = max(a, lo) - lo, min(b, lo + grad_shard.numel()) - lo
                 if b2 > a2:
                     dup += grad_shard[a2:b2].float().pow(2).sum()
-            if self.world > 1:
-                dist.all_reduce(dup, group=self.pg)
+            if self.opt_world > 1:
+                dist.all_reduce(dup, group=self.opt_group)
             tp.all_reduce_(dup)
             self.state[:1] -= dup
 
     def _padded_flat(self, t: torch.Tensor) -> torch.Tensor:
-        need = self.shard_size * self.world
+        need = self.shard_size * self.opt_world
         if t.numel() == need:
             return t
         out = torch.zeros(need, dtype=t.dtype, device=t.device)
@@ -478,27 +501,33 @@ class PolicyEngine:
     def _reduce_scatter_grads(self) -> torch.Tensor:
         g = self._padded_flat(self.model.params.grad_flat)
         out = torch.empty(self.shard_size, dtype=g.dtype, device=g.device)
-        if dist.get_backend(self.pg) == "gloo":
-            dist.all_reduce(g, group=self.pg)
-            out.copy_(g[self.rank * self.shard_size:(self.rank + 1) * self.shard_size])
+        if self.opt_world == 1:
+            out.copy_(g[: self.shard_size])
+        elif dist.get_backend(self.pg) == "gloo":
+            dist.all_reduce(g, group=self.opt_group)
+            out.copy_(g[self.opt_rank * self.shard_size:(self.opt_rank + 1) * self.shard_size])
         else:
-            dist.reduce_scatter_tensor(out, g, group=self.pg)
+            dist.reduce_scatter_tensor(out, g, group=self.opt_group)
+        if self.rep_group is not None:                  # hybrid sharding: sum the shard over the replicas
+            dist.all_reduce(out, group=self.rep_group)
         lo, hi = self.shard
         return out[: hi - lo]
 
     def _all_gather_params(self) -> None:
         p = self.model.params
         lo, hi = self.shard
-        if self.shard_size * self.world == p.flat.numel() and dist.get_backend(self.pg) != "gloo":
-            dist.all_gather_into_tensor(p.flat, p.flat[lo:hi], group=self.pg)   # in place
+        if self.opt_world == 1:
+            return
+        if self.shard_size * self.opt_world == p.flat.numel() and dist.get_backend(self.pg) != "gloo":
+            dist.all_gather_into_tensor(p.flat, p.flat[lo:hi], group=self.opt_group)   # in place
             return
         mine = torch.zeros(self.shard_size, dtype=p.flat.dtype, device=p.flat.device)
         mine[: hi - lo] = p.flat[lo:hi]
-        full = torch.empty(self.shard_size * self.world, dtype=p.flat.dtype, device=p.flat.device)
+        full = torch.empty(self.shard_size * self.opt_world, dtype=p.flat.dtype, device=p.flat.device)
         if dist.get_backend(self.pg) == "gloo":
-            parts = [torch.empty_like(mine) for _ in range(self.world)]
-            dist.all_gather(parts, mine, group=self.pg)
+            parts = [torch.empty_like(mine) for _ in range(self.opt_world)]
+            dist.all_gather(parts, mine, group=self.opt_group)
             full = torch.cat(parts)
         else:
-            dist.all_gather_into_tensor(full, mine, group=self.pg)
+            dist.all_gather_into_tensor(full, mine, group=self.opt_group)
         p.flat.copy_(full[: p.flat.numel()])

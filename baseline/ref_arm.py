@@ -104,6 +104,7 @@ def _run(args, t_start, ClockSampler, plan_steps, synthetic_inputs, metric) -> N
     os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")      # the worker lives in this process, as in the reference
     os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
     os.environ.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
+    os.environ.setdefault("VLLM_LOGGING_STREAM", "ext://sys.stderr")       # stdout carries the result lines only
     for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0"), ("MASTER_ADDR", "127.0.0.1")):
         os.environ.setdefault(k, v)
     if "MASTER_PORT" not in os.environ:

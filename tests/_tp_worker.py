@@ -60,35 +60,6 @@ def main(out_path: str, device_kind: str) -> None:
     ss = m.grad_sumsq().reshape(1).to(dev)
     dist.all_reduce(ss)
     res["norm_rel"] = abs(float(ss.sqrt()) - float(full.params.grad_flat.double().norm())) / float(full.params.grad_flat.double().norm())
-    if os.environ.get("AXON_TP_TIMING") == "1":
-        # optional: the fused collective GEMMs across real NVLink at training shapes against the same products
-        # on whole operands (8192 tokens in total, Qwen3-8B qkv and o projections)
-        from axon_b200.ops import gemm as G
-        Tt, H, Nq = 8192, 4096, 6144
-        big = TPContext(dist.group.WORLD, dev, max_rows_per_rank=Tt // world, max_width=Nq)
-        x_loc = torch.randn(Tt // world, H, device=dev).to(torch.bfloat16)
-        x_all = torch.randn(Tt, H, device=dev).to(torch.bfloat16)
-        w_col = (torch.randn(Nq // world, H, device=dev) * 0.02).to(torch.bfloat16)       # column-parallel shard
-        a_all = torch.randn(Tt, H // world, device=dev).to(torch.bfloat16)
-        w_row = (torch.randn(H, H // world, device=dev) * 0.02).to(torch.bfloat16)        # row-parallel shard
-
-        def timed(fn):
-            ts = []
-            for _ in range(6):
-                dist.barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                fn()
-                e1.record()
-                torch.cuda.synchronize()
-                ts.append(e0.elapsed_time(e1))
-            t = torch.tensor(sorted(ts[2:])[1], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t)
-        res["ms_allgather_gemm_fused"] = timed(lambda: big.allgather_gemm(x_loc, w_col))
-        res["ms_gemm_whole_rows"] = timed(lambda: G.gemm_nt(x_all, w_col))
-        res["ms_gemm_reduce_scatter_fused"] = timed(lambda: big.gemm_reduce_scatter(a_all, w_row))
-        res["ms_gemm_partial_only"] = timed(lambda: G.gemm_nt(a_all, w_row))
     out = [None] * world
     dist.all_gather_object(out, res)
     if rank == 0:

@@ -55,36 +55,6 @@ def main(out_path: str) -> None:
         num += float((g - ref).double().pow(2).sum())
         den += float(ref.double().pow(2).sum())
     res.update(lp_err=lp_err, ent_err=ent_err, grad_rel=(num / max(den, 1e-30)) ** 0.5)
-    if os.environ.get("AXON_Z3_TIMING") == "1":
-        # optional: cost of sharding at Qwen3-8B layer shapes (4 layers, 8192 packed tokens, forward + backward)
-        from axon_b200.models.config import qwen3_8b
-        big = qwen3_8b()
-        big.num_hidden_layers = 4
-        seqs = [torch.randint(0, big.vocab_size, (2048,)) for _ in range(4)]
-        batch = PackedBatch.from_sequences(seqs, dev)
-        glp = torch.ones(batch.input_ids.numel(), device=dev)
-        del full, m
-        torch.cuda.empty_cache()
-        for label, build in (("whole", lambda: DenseModel(big, device=dev)), ("sharded", lambda: Zero3DenseModel(big, ctx, device=dev))):
-            mod = build()
-            (mod.params.init_random if label == "whole" else mod.init_random)(std=0.02, seed=3)
-            mod.recompute = "selective"
-            mod.params.alloc_grads()
-            ts = []
-            for it in range(5):
-                dist.barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                mod.forward(batch, 1.0, save_for_backward=True)
-                mod.backward(glp, None)
-                e1.record()
-                torch.cuda.synchronize()
-                ts.append(e0.elapsed_time(e1))
-            t = torch.tensor(sorted(ts[2:])[1], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            res[f"ms_fwd_bwd_{label}"] = float(t)
-            del mod
-            torch.cuda.empty_cache()
     C.check_status()
     res["status_ok"] = True
     out = [None] * world

@@ -132,3 +132,52 @@ def test_shared_prefix_attention_in_the_decode_graph_gpu():
     assert same >= len(a) - 3, same
     first = max(abs(la[0] - lb[0]) for (_, la), (_, lb) in zip(a, b))
     assert first < 0.05, first
+
+
+def _routing_capture_roundtrip(device, dtype, tol):
+    """The sampler records every token's routed experts; a teacher-forced trainer forward that REPLAYS the record
+    reproduces the sampler's log-probs, and (deterministic CPU arithmetic) recomputes the very same experts."""
+    from axon_b200.models.config import get_config
+    from axon_b200.models.moe import MoEModel
+    cfg = get_config("tiny-moe" if device == "cpu" else "tiny-moe-gpu")
+    torch.manual_seed(1)
+    model = MoEModel(cfg, device=device, dtype=dtype)
+    model.params.init_random(std=0.08, seed=4)
+    eng = GenerationEngine(model, num_pages=32, max_num_seqs=8)
+    eng.enable_routing_capture(True)
+    p_shared = torch.randint(2, cfg.vocab_size, (140,)).tolist()
+    prompts = [p_shared, p_shared, torch.randint(2, cfg.vocab_size, (9,)).tolist()]       # two samples share a prompt
+    outs = eng.generate(prompts, SamplingParams(temperature=0.9, max_tokens=12, ignore_eos=True))
+    L, k, E = cfg.num_hidden_layers, cfg.num_experts_per_tok, cfg.num_experts
+    for p, o in zip(prompts, outs):
+        rm = o.moe_routermap
+        n = len(p) + len(o.token_ids)
+        assert rm.shape == (n, L, k) and str(rm.dtype) == "int16"
+        assert (rm[-1] == -1).all() and (rm[:-1] >= 0).all() and (rm[:-1] < E).all()
+        seq = torch.tensor(p + o.token_ids)
+        batch = PackedBatch.from_sequences([seq], model.device)
+        batch.routermap = torch.from_numpy(rm.astype("int64")).to(model.device)          # -1 rows fall back to computed routing
+        lp, _ = model.forward(batch, 0.9)
+        ref = lp[len(p) - 1: len(p) - 1 + len(o.token_ids)].float().cpu()
+        assert (torch.tensor(o.logprobs) - ref).abs().max().item() < tol
+        if device == "cpu":
+            model.capture_routing, model.last_routing = True, None
+            plain = PackedBatch.from_sequences([seq], model.device)
+            model.forward(plain, 0.9)
+            again = torch.stack(model.last_routing, 1)[: n - 1].sort(-1).values
+            model.last_routing = None
+            assert torch.equal(again, torch.from_numpy(rm[: n - 1].astype("int64")).sort(-1).values)
+    assert (outs[0].moe_routermap[: len(p_shared)] == outs[1].moe_routermap[: len(p_shared)]).all()
+    eng.enable_routing_capture(False)
+    assert eng.generate([prompts[2]], SamplingParams(max_tokens=3, ignore_eos=True))[0].moe_routermap is None
+
+
+def test_routed_experts_capture_and_replay_cpu():
+    _routing_capture_roundtrip("cpu", torch.float32, 1e-4)
+
+
+@pytest.mark.gpu
+def test_routed_experts_capture_and_replay_gpu():
+    _routing_capture_roundtrip("cuda", torch.bfloat16, 0.15)
+    from axon_b200.ops import _common as C
+    C.check_status()

@@ -72,3 +72,18 @@ def test_fused_weight_gather_model_on_two_gpus(tmp_path):
     for x in json.loads(out.read_text()):
         assert x["fused"] and x["status_ok"], x
         assert x["lp_err"] < 0.2 and x["ent_err"] < 0.15 and x["grad_rel"] < 0.08, x
+
+
+@pytest.mark.timeout(900)
+def test_hybrid_sharding_matches_single_process():
+    """``fsdp.fsdp_size = 2`` on four ranks: optimizer shards inside groups of two, replicas across the groups. Log-probs,
+    gradient norm and the parameters after the step equal the single-process run."""
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen3"), 1)
+    c = _cfg(1, "tiny-qwen3")
+    c["fsdp"] = {"fsdp_size": 2}
+    got = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", c, 4)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
