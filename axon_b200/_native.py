@@ -7,6 +7,11 @@ the PyTorch C++ ABI and a source file rebuilds in seconds.
 ``build()`` cross-compiles every ``csrc/*.cu`` for ``sm_100a`` only (no GPU needed) and links
 one shared object next to this file. ``lib()`` loads it; on a machine with a GPU a missing
 library is an error, never a silent fallback.
+
+A second flavour, ``axon_b200/_C_debug.so``, is the same sources compiled with ``-DAXB_DEBUG``: kernels that
+take indices from data (token ids, page tables, replayed expert ids, sync-plan ranks) record the first index
+that falls outside its buffer (``csrc/debug.cuh``) in addition to skipping it. ``AXON_NATIVE_DEBUG=1`` makes
+``lib()`` load that flavour; ``ops._common.check_status`` then also reports such records.
 """
 from __future__ import annotations
 
@@ -23,6 +28,8 @@ _ROOT = _PKG.parent
 _CSRC = _ROOT / "csrc"
 _BUILD = _ROOT / "build"
 _SO = _PKG / "_C.so"
+_SO_DEBUG = _PKG / "_C_debug.so"
+_BUILD_DEBUG = _ROOT / "build" / "debug"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -50,17 +57,39 @@ def _digest(paths) -> str:
     return h.hexdigest()
 
 
-def needs_build() -> bool:
-    stamp = _BUILD / "stamp.txt"
-    if not _SO.exists() or not stamp.exists():
+def debug_requested() -> bool:
+    return os.environ.get("AXON_NATIVE_DEBUG", "0") not in ("", "0", "false", "False")
+
+
+def needs_build(debug: bool = False) -> bool:
+    so, bdir = (_SO_DEBUG, _BUILD_DEBUG) if debug else (_SO, _BUILD)
+    stamp = bdir / "stamp.txt"
+    if not so.exists() or not stamp.exists():
         return True
     deps = list(_CSRC.glob("*.cu")) + list(_CSRC.glob("*.cuh")) + list(_CSRC.glob("*.h"))
     return stamp.read_text().strip() != _digest(deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile csrc/*.cu for sm_100a and link axon_b200/_C.so. Returns the library path."""
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, debug: bool = False) -> Path:
+    """Compile csrc/*.cu for sm_100a and link axon_b200/_C.so (``debug``: _C_debug.so with -DAXB_DEBUG).
+    Returns the library path."""
+    global _SO, _BUILD
+    if debug:
+        # same code path with the debug names and the extra define
+        saved = (_SO, _BUILD, list(NVCC_FLAGS))
+        _SO, _BUILD = _SO_DEBUG, _BUILD_DEBUG
+        NVCC_FLAGS.append("-DAXB_DEBUG")
+        try:
+            _BUILD.parent.mkdir(exist_ok=True)
+            return _build_impl(force, verbose, debug=True)
+        finally:
+            _SO, _BUILD = saved[0], saved[1]
+            NVCC_FLAGS[:] = saved[2]
+    return _build_impl(force, verbose, debug=False)
+
+
+def _build_impl(force: bool, verbose: bool, debug: bool) -> Path:
+    if not force and not needs_build(debug):
         return _SO
     _BUILD.mkdir(exist_ok=True)
     nvcc = _nvcc()
@@ -104,13 +133,15 @@ def lib() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not _SO.exists():
+    debug = debug_requested()
+    so = _SO_DEBUG if debug else _SO
+    if not so.exists():
         try:
-            build()
+            build(debug=debug)
         except Exception as e:  # noqa: BLE001
             raise RuntimeError(
                 "axon_b200 native library is missing and could not be built; run "
                 "`python -c 'import __graft_entry__ as g; g.build()'`"
             ) from e
-    _lib = ctypes.CDLL(str(_SO))
+    _lib = ctypes.CDLL(str(so))
     return _lib

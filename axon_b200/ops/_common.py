@@ -66,6 +66,12 @@ def launched(rc: int, name: str, n: int = 1) -> None:
 
 def check_status(device: torch.device | None = None) -> None:
     """Synchronise and raise if any kernel on the device recorded an error (bounded wait ran out)."""
+    if _native.debug_requested():
+        rec = (ctypes.c_int * 4)()
+        src = ctypes.create_string_buffer(256)
+        if lib().axb_debug_status(rec, src, 256) != 0:
+            raise NativeKernelError(f"debug build: index check failed at {src.value.decode()}:{rec[1]} "
+                                    f"(value {rec[2]}, limit {rec[3]})")
     devs = [device.index] if device is not None and device.index is not None else list(_STATUS)
     for idx in devs:
         buf = _STATUS.get(idx)

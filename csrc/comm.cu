@@ -15,6 +15,7 @@
 // status word instead of spinning forever.
 #include "ptx.cuh"
 #include "host_utils.h"
+#include "debug.cuh"
 #include <cuda_fp8.h>
 
 namespace axb {
@@ -200,6 +201,8 @@ p2p_copy_plan_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, PeerPt
   for (long long w = w0 + threadIdx.x; w < w1; w += blockDim.x) {
     while (d + 1 < n_desc && work_prefix[d + 1] <= w) ++d;
     const CopyDesc& c = descs[d];
+    AXB_DEBUG_CHECK(c.dst_rank >= 0 && c.dst_rank < MAX_RANKS && dst.p[c.dst_rank] != nullptr, c.dst_rank, d);
+    if (c.dst_rank < 0 || c.dst_rank >= MAX_RANKS || dst.p[c.dst_rank] == nullptr) continue;
     const long long local = w - work_prefix[d];
     const int vec_per_row = (c.cols + 7) / 8;
     const int r = (int)(local / vec_per_row);

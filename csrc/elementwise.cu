@@ -4,6 +4,7 @@
 // size must be a multiple of 8.
 #include "ptx.cuh"
 #include "host_utils.h"
+#include "debug.cuh"
 
 namespace axb {
 
@@ -389,6 +390,7 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfl
   const int nv = H / 8;
   for (long long t = blockIdx.x; t < T; t += gridDim.x) {
     int id = ids[t];
+    AXB_DEBUG_CHECK(id >= 0 && id < V, id, V);
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);
     const uint4* src = reinterpret_cast<const uint4*>(table + (long long)id * H);
     uint4* dst = reinterpret_cast<uint4*>(out + t * H);
@@ -400,6 +402,7 @@ __global__ void embedding_bwd_kernel(const int* __restrict__ ids, const __nv_bfl
                                      float* __restrict__ dtable, long long T, int H, int V) {
   for (long long t = blockIdx.x; t < T; t += gridDim.x) {
     const int id = ids[t];
+    AXB_DEBUG_CHECK(id >= 0 && id < V, id, V);
     if (id < 0 || id >= V) continue;
     for (int i = threadIdx.x; i < H; i += blockDim.x)
       atomicAdd(dtable + (long long)id * H + i, __bfloat162float(dy[t * H + i]));

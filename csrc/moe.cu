@@ -12,6 +12,7 @@
 //             the expert OUTPUT (after the second projection), as the sampler does
 //   combine_bwd  dy_sorted[row] = w * dout[token];  dw[token][j] = <dout[token], y_sorted[row]>
 #include "host_utils.h"
+#include "debug.cuh"
 #include "ptx.cuh"
 
 namespace axb {
@@ -54,6 +55,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const int* __
   float wsum = 0.f;
   for (int j = 0; j < k; ++j) {
     int forced = replay != nullptr ? replay[t * k + j] : -1;
+    AXB_DEBUG_CHECK(forced < E, forced, E);          // a replayed expert id outside the model: ignored, recorded in debug builds
     if (forced >= E) forced = -1;
     float best = -1.f;
     int best_e = 0x7fffffff;

@@ -16,6 +16,7 @@
 // Blackwell (axon/sampler/vllm/server.py:355-377,474-478).
 #include "ptx.cuh"
 #include "host_utils.h"
+#include "debug.cuh"
 
 namespace axb {
 
@@ -46,7 +47,10 @@ __global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bflo
     const int is_v = r / Hkv, hk = r - is_v * Hkv;
     const int seq = tok_seq[t], pos = tok_pos[t];
     if (seq < 0 || pos < 0) continue;
+    AXB_DEBUG_CHECK(pos / PA_PAGE < max_pages, pos, max_pages);
+    if (pos / PA_PAGE >= max_pages) continue;
     const int page = block_table[(long long)seq * max_pages + pos / PA_PAGE];
+    AXB_DEBUG_CHECK(page >= 0 && page < num_pages, page, num_pages);
     if (page < 0 || page >= num_pages) continue;
     const __nv_bfloat16* src = qkv + t * (long long)(Hq + 2 * Hkv) * PA_D + (long long)(Hq + is_v * Hkv + hk) * PA_D;
     __nv_bfloat16* dst = (is_v ? vcache : kcache) +
