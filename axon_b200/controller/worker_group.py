@@ -177,8 +177,22 @@ def _worker_main(conn, factory: ClassWithInitArgs, env: dict, max_concurrency: i
     send_lock = threading.Lock()
     pool = ThreadPoolExecutor(max_workers=max(1, max_concurrency), thread_name_prefix="rpc-exec")
 
+    def bind_device():
+        """The current CUDA device is a per-thread setting: the worker chose its GPU on the main thread, every pool
+        thread has to choose it again or its allocations and collectives land on GPU 0."""
+        dev = getattr(obj, "device", None)
+        if dev is None:
+            for role in getattr(obj, "role_objects", {}).values():
+                dev = getattr(role, "device", None)
+                if dev is not None:
+                    break
+        if dev is not None and getattr(dev, "type", None) == "cuda":
+            import torch
+            torch.cuda.set_device(dev)
+
     def execute(call_id, name, args, kwargs):
         try:
+            bind_device()
             res = getattr(obj, name)(*args, **kwargs)
             if hasattr(res, "__await__"):
                 import asyncio

@@ -71,6 +71,8 @@ class ModelConfig:
         return L * per_layer + emb + H
 
     def to_hf_dict(self) -> dict:
+        if "hf_config" in self.extra:            # families described by their own HF config (models/families.py)
+            return dict(self.extra["hf_config"])
         d = asdict(self)
         d.pop("extra")
         d.update(self.extra)
@@ -80,6 +82,9 @@ class ModelConfig:
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        from .families import FAMILY_TYPES, family_config
+        if d.get("model_type") in FAMILY_TYPES:
+            return family_config(d)
         known = {f for f in cls.__dataclass_fields__ if f != "extra"}
         kw = {k: v for k, v in d.items() if k in known}
         if "head_dim" not in kw and "hidden_size" in d and "num_attention_heads" in d:
@@ -186,6 +191,36 @@ def _with(cfg: ModelConfig, **kw) -> ModelConfig:
 def _untied(cfg: ModelConfig) -> ModelConfig:
     cfg.tie_word_embeddings = False
     return cfg
+
+
+def _tiny_family(kind: str) -> ModelConfig:
+    """Small random-init members of the families of ``models/families.py`` (tests, dry runs)."""
+    from .families import family_config
+    base = dict(vocab_size=4096, hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                intermediate_size=256, rms_norm_eps=1e-6, max_position_embeddings=4096, tie_word_embeddings=False, eos_token_id=1,
+                pad_token_id=0, rope_parameters={"rope_type": "default", "rope_theta": 10000.0})
+    extra = {
+        "deepseek_v3": dict(model_type="deepseek_v3", num_key_value_heads=4, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=32,
+                            qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1,
+                            first_k_dense_replace=1, moe_intermediate_size=64, n_shared_experts=1, routed_scaling_factor=2.5,
+                            norm_topk_prob=True, rope_interleave=True),
+        "gpt_oss": dict(model_type="gpt_oss", num_local_experts=4, num_experts_per_tok=2, intermediate_size=64, sliding_window=64,
+                        attention_bias=True),
+        "gemma3": dict(model_type="gemma3_text", sliding_window=64, query_pre_attn_scalar=32, tie_word_embeddings=True, num_hidden_layers=6,
+                       rope_parameters={"full_attention": {"rope_type": "default", "rope_theta": 1000000.0},
+                                        "sliding_attention": {"rope_type": "default", "rope_theta": 10000.0}}),
+        "qwen3_next": dict(model_type="qwen3_next", partial_rotary_factor=0.25, linear_num_value_heads=4, linear_num_key_heads=2,
+                           linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4, num_experts=4, num_experts_per_tok=2,
+                           moe_intermediate_size=64, shared_expert_intermediate_size=64, decoder_sparse_step=1, norm_topk_prob=True),
+        "glm4_moe": dict(model_type="glm4_moe", partial_rotary_factor=0.5, use_qk_norm=True, attention_bias=True, n_routed_experts=8,
+                         num_experts_per_tok=2, n_group=1, topk_group=1, first_k_dense_replace=1, moe_intermediate_size=64, n_shared_experts=1,
+                         routed_scaling_factor=1.0, norm_topk_prob=True),
+    }[kind]
+    return family_config({**base, **extra})
+
+
+for _k in ("deepseek_v3", "gpt_oss", "gemma3", "qwen3_next", "glm4_moe"):
+    PRESETS["tiny-" + _k.replace("_", "-")] = (lambda k=_k: _tiny_family(k))
 
 
 def get_config(name_or_path: str) -> ModelConfig:

@@ -1,0 +1,1062 @@
+"""Decoder families beyond the in-house dense / sparse Qwen-style models: DeepSeek-V3 (latent attention,
+sigmoid group-limited routing, shared experts), GPT-OSS (attention sinks, alternating sliding windows, clamped
+SwiGLU experts with biases), Gemma-2/3 (GeGLU, (1 + w) norms, sandwich norms, soft-capping, sliding windows),
+GLM-4.5 / GLM-4.6 sparse models, and Qwen3-Next / Qwen3.5 (gated delta-rule linear attention mixed with gated
+full attention). These are the families the reference reaches through its HF patches, Megatron model specs and
+weight bridges (axon/models/mcore/models/{gemma4,gpt_oss,qwen3_next,qwen3_5,glm5}.py,
+axon/models/mbridge/{deepseek_v3,gpt_oss,glm4_moe_lite,qwen3_next,qwen3_5}.py,
+axon/monkey_patches/transformers/).
+
+Design: one ``FamilyModel`` class holds the parameters in the same flat buffer (``FlatParams``) as every other
+model here, under the checkpoint's own tensor names, and exposes the interface the policy engine and the
+generation engine expect (``forward`` / ``backward`` over packed batches, ``prefill`` / ``decode`` over the
+paged KV cache). The layer mathematics is written once per family as PyTorch functions over that buffer and
+differentiated by autograd (per-layer recomputation with ``recompute = "full"``); dense projections run on the
+tcgen05 GEMM on CUDA through ``NativeLinear``. The families share nothing hot with the flagship benchmark path:
+they trade the hand-scheduled backward of ``DenseModel`` for breadth, and every one of them is checked
+against the HF implementation of the same architecture on CPU (tests/test_families.py).
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+
+import torch
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from .config import ModelConfig
+from .params import FlatParams
+
+FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text")
+
+
+# ------------------------------------------------------------------------------------------ small pieces
+class NativeLinear(torch.autograd.Function):
+    """y = x W^T on the tcgen05 GEMM (CUDA bf16 operands with 8-element aligned sizes); dgrad and wgrad likewise."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from ..ops import gemm as G
+        ctx.save_for_backward(x, w)
+        return G.gemm_nt(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import gemm as G
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        return G.gemm_nn(dy, w), G.gemm_tn(dy, x, out_dtype=w.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+    """x [..., K] @ w[N, K]^T (+ b)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
+        lead = x.shape[:-1]
+        y = NativeLinear.apply(x.reshape(-1, x.shape[-1]).contiguous(), w).view(*lead, w.shape[0])
+    else:
+        y = F.linear(x, w)
+    return y if b is None else y + b
+
+
+def rms_norm(x, w, eps: float, plus_one: bool = False):
+    """RMSNorm in fp32; ``plus_one``: the stored weight is an offset from 1 (Gemma, Qwen3-Next)."""
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    if w is not None:
+        y = y * ((1.0 + w.float()) if plus_one else w.float())
+    return y.to(x.dtype)
+
+
+def rotate_half(x):
+    a, b = x.chunk(2, dim=-1)
+    return torch.cat((-b, a), dim=-1)
+
+
+def apply_rope(x, cos, sin, interleaved: bool = False):
+    """x [T, heads, D]; cos / sin [T, R] with R <= D: the first R dims turn (half-split pairs), the rest pass.
+    ``interleaved``: the checkpoint pairs dims (2i, 2i + 1); they are regrouped to half-split order first."""
+    R = cos.shape[-1]
+    xr, xp = x[..., :R], x[..., R:]
+    if interleaved:
+        xr = xr.reshape(*xr.shape[:-1], R // 2, 2).transpose(-1, -2).reshape(*xr.shape[:-1], R)
+    c, s = cos[:, None, :].to(x.dtype), sin[:, None, :].to(x.dtype)
+    out = xr * c + rotate_half(xr) * s
+    return torch.cat([out, xp], dim=-1) if xp.shape[-1] else out
+
+
+def yarn_mscale(scale: float = 1.0, mscale: float = 1.0) -> float:
+    return 1.0 if scale <= 1 else 0.1 * mscale * math.log(scale) + 1.0
+
+
+def rope_frequencies(rope: dict, dim: int, max_pos_default: int) -> tuple[torch.Tensor, float]:
+    """(inverse frequencies [dim / 2], factor applied to cos / sin) for the rope types ``default``, ``linear`` and
+    ``yarn`` (the blend of interpolated and extrapolated frequencies with its attention temperature)."""
+    theta = float(rope.get("rope_theta", 10000.0))
+    kind = rope.get("rope_type", rope.get("type", "default")) or "default"
+    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+    if kind == "default":
+        return inv.float(), 1.0
+    factor = float(rope.get("factor", 1.0))
+    if kind == "linear":
+        return (inv / factor).float(), 1.0
+    if kind == "yarn":
+        orig = float(rope.get("original_max_position_embeddings") or max_pos_default)
+        beta_fast, beta_slow = float(rope.get("beta_fast") or 32), float(rope.get("beta_slow") or 1)
+        ms, ms_all = rope.get("mscale"), rope.get("mscale_all_dim")
+        att = rope.get("attention_factor")
+        if att is None:
+            att = yarn_mscale(factor, ms) / yarn_mscale(factor, ms_all) if (ms and ms_all) else yarn_mscale(factor)
+
+        def corr_dim(rot):
+            return dim * math.log(orig / (rot * 2 * math.pi)) / (2 * math.log(theta))
+        low, high = corr_dim(beta_fast), corr_dim(beta_slow)
+        if rope.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(dim // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+        extrap_weight = 1.0 - ramp
+        inv_y = (inv / factor) * (1 - extrap_weight) + inv * extrap_weight
+        return inv_y.float(), float(att)
+    raise NotImplementedError(f"rope type '{kind}'")
+
+
+def attention_packed(q, k, v, cu, scale: float, window: int | None = None, sinks: torch.Tensor | None = None,
+                     softcap: float | None = None):
+    """Causal attention over packed sequences. q [T, Hq, Dk], k [T, Hkv, Dk], v [T, Hkv, Dv]; ``cu`` = sequence
+    boundaries (python ints). ``window``: a key is visible while ``q_pos - k_pos < window``. ``sinks`` [Hq]: one
+    extra logit per head that takes probability mass and contributes nothing. ``softcap``: logits pass through
+    ``cap * tanh(x / cap)``. Returns [T, Hq, Dv]."""
+    Hq, Hkv = q.shape[1], k.shape[1]
+    rep = Hq // Hkv
+    outs = []
+    plain = sinks is None and softcap is None
+    for a, b in zip(cu[:-1], cu[1:]):
+        n = b - a
+        if n == 0:
+            continue
+        qs, ks, vs = q[a:b].transpose(0, 1), k[a:b].transpose(0, 1), v[a:b].transpose(0, 1)      # [H, n, D]
+        if plain and window is None:
+            o = F.scaled_dot_product_attention(qs[None], ks[None], vs[None], is_causal=True, scale=scale, enable_gqa=rep > 1)[0]
+            outs.append(o.transpose(0, 1))
+            continue
+        idx = torch.arange(n, device=q.device)
+        ok = idx[None, :] <= idx[:, None]
+        if window is not None:
+            ok = ok & (idx[:, None] - idx[None, :] < window)
+        if plain:
+            o = F.scaled_dot_product_attention(qs[None], ks[None], vs[None], attn_mask=ok[None, None], scale=scale, enable_gqa=rep > 1)[0]
+            outs.append(o.transpose(0, 1))
+            continue
+        if rep > 1:
+            ks, vs = ks.repeat_interleave(rep, dim=0), vs.repeat_interleave(rep, dim=0)
+        s = torch.matmul(qs, ks.transpose(1, 2)).float() * scale
+        if softcap is not None:
+            s = torch.tanh(s / softcap) * softcap
+        s = s.masked_fill(~ok[None], float("-inf"))
+        if sinks is not None:
+            s = torch.cat([s, sinks.float()[:, None, None].expand(Hq, n, 1)], dim=-1)
+            p = torch.softmax(s, dim=-1)[..., :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
+        outs.append(torch.matmul(p.to(vs.dtype), vs).transpose(0, 1))
+    return torch.cat(outs, dim=0)
+
+
+def attention_cached(q, kc, vc, lens, scale, window=None, sinks=None, softcap=None):
+    """One query token per sequence against that sequence's cached keys. q [B, Hq, Dk]; kc / vc: lists of
+    [n_b, Hkv, D] tensors (the first ``lens[b]`` positions, the query's own key included)."""
+    outs = []
+    Hq = q.shape[1]
+    for b in range(q.shape[0]):
+        k, v = kc[b], vc[b]
+        n = k.shape[0]
+        lo = max(0, n - window) if window is not None else 0
+        k, v = k[lo:], v[lo:]
+        rep = Hq // k.shape[1]
+        ks, vs = k.transpose(0, 1), v.transpose(0, 1)
+        if rep > 1:
+            ks, vs = ks.repeat_interleave(rep, dim=0), vs.repeat_interleave(rep, dim=0)
+        s = torch.matmul(q[b][:, None, :], ks.transpose(1, 2)).float() * scale        # [Hq, 1, n]
+        if softcap is not None:
+            s = torch.tanh(s / softcap) * softcap
+        if sinks is not None:
+            s = torch.cat([s, sinks.float()[:, None, None]], dim=-1)
+            p = torch.softmax(s, dim=-1)[..., :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
+        outs.append(torch.matmul(p.to(vs.dtype), vs)[:, 0])
+    return torch.stack(outs)
+
+
+def experts_forward(x, idx, wts, apply_expert, n_experts: int):
+    """Token-choice expert mixture: row t goes through experts ``idx[t, :]`` with weights ``wts[t, :]``.
+    ``apply_expert(e, rows)`` -> rows' outputs. Experts are visited in order (deterministic accumulation)."""
+    out = torch.zeros_like(x)
+    flat = idx.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=n_experts).tolist()
+    tok = (order // idx.shape[1])
+    w_sorted = wts.reshape(-1)[order]
+    pos = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        rows = tok[pos:pos + c]
+        y = apply_expert(e, x[rows]) * w_sorted[pos:pos + c, None].to(x.dtype)
+        out = out.index_add(0, rows, y.to(out.dtype))
+        pos += c
+    return out
+
+
+def gated_delta_rule(q, k, v, g, beta, state=None):
+    """Gated delta rule, one sequence: q, k [n, H, Dk] (already L2-normalised), v [n, H, Dv], g [n, H] (log decay),
+    beta [n, H]. S <- S * exp(g) ; S <- S + k (beta (v - S^T k))^T ; o = S^T q / sqrt(Dk). Returns (o [n, H, Dv],
+    final state [H, Dk, Dv]). Recurrent form in fp32 (the oracle of the chunked kernels)."""
+    n, H, Dk = k.shape
+    Dv = v.shape[-1]
+    qf, kf, vf = q.float() / math.sqrt(Dk), k.float(), v.float()
+    S = torch.zeros(H, Dk, Dv, dtype=torch.float32, device=q.device) if state is None else state.float()
+    outs = []
+    for t in range(n):
+        S = S * g[t].float().exp()[:, None, None]
+        mem = torch.einsum("hkv,hk->hv", S, kf[t])
+        delta = (vf[t] - mem) * beta[t].float()[:, None]
+        S = S + kf[t][:, :, None] * delta[:, None, :]
+        outs.append(torch.einsum("hkv,hk->hv", S, qf[t]))
+    return torch.stack(outs).to(v.dtype), S
+
+
+def l2norm(x, eps: float = 1e-6):
+    return x * torch.rsqrt(x.float().pow(2).sum(-1, keepdim=True) + eps).to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------ parameters
+class FamilyParams(FlatParams):
+    """Flat parameter buffer under the checkpoint's tensor names, with the HF import / export the rest of the framework
+    calls (``load_hf_state_dict`` / ``to_hf_state_dict`` / ``init_random``)."""
+
+    def __init__(self, cfg, device, dtype, layout, spec):
+        super().__init__(cfg, device, dtype, layout=layout)
+        self.spec = spec
+
+    def init_random(self, std: float = 0.02, seed: int = 0) -> None:
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        for name, v in self.views.items():
+            kind = self.spec.init_kind(name)
+            if kind == "ones":
+                v.fill_(1.0)
+            elif kind == "zeros":
+                v.zero_()
+            elif kind == "a_log":
+                v.copy_(torch.log(torch.empty(v.shape).uniform_(1.0, 16.0, generator=g)).to(v.dtype))
+            else:
+                v.copy_((torch.randn(v.shape, generator=g) * std).to(v.dtype))
+
+    def load_hf_state_dict(self, sd: dict, strict: bool = True) -> list[str]:
+        """Copies tensors by name. Checkpoints that store every expert separately
+        (``mlp.experts.<e>.{gate,up,down}_proj.weight``) are stacked into the ``[E, ...]`` tensors used here."""
+        sd = dict(sd)
+        missing = []
+        for name in self.layout:
+            t = sd.get(name)
+            if t is None and name.endswith(("mlp.experts.gate_up_proj", "mlp.experts.down_proj")):
+                base = name[: name.rindex(".experts.") + len(".experts.")]
+                E = self.layout[name][0]
+                if f"{base}0.down_proj.weight" in sd:
+                    if name.endswith("gate_up_proj"):
+                        t = torch.stack([torch.cat([sd[f"{base}{e}.gate_proj.weight"], sd[f"{base}{e}.up_proj.weight"]], 0) for e in range(E)])
+                    else:
+                        t = torch.stack([sd[f"{base}{e}.down_proj.weight"] for e in range(E)])
+            if t is None:
+                missing.append(name)
+                continue
+            self.views[name].copy_(t.to(self.views[name].dtype).reshape(self.views[name].shape))
+        if strict and missing:
+            raise KeyError(f"checkpoint lacks {missing[:5]} ... ({len(missing)} tensors)")
+        return missing
+
+    def to_hf_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
+        return OrderedDict((n, self.views[n]) for n in self.layout)
+
+
+# ------------------------------------------------------------------------------------------ the model
+class FamilyModel:
+    """A decoder of one of ``FAMILY_TYPES`` built from its HF config dictionary ``hf``."""
+
+    def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, hf: dict | None = None):
+        self.cfg = cfg
+        self.hf = dict(hf if hf is not None else cfg.extra.get("hf_config", {}))
+        self.kind = self.hf.get("model_type", cfg.model_type)
+        assert self.kind in FAMILY_TYPES, f"'{self.kind}' is not one of {FAMILY_TYPES}"
+        self.device, self.dtype = torch.device(device), dtype
+        self.spec = _SPECS[self.kind](self.hf)
+        self.layout = self.spec.layout()
+        self.params = FamilyParams(cfg, self.device, dtype, self.layout, self.spec)
+        self.buffers: dict[str, torch.Tensor] = self.spec.buffers(self.device)      # non-trainable tensors of the checkpoint
+        self.recompute = "full"
+        self._saved = None
+        self._rope_cache: dict = {}
+        self.recurrent_state: dict = {}       # sampler: per-sequence state of linear-attention layers, keyed by the first page
+        # linear-attention state is per sequence and keyed by its first cache page: samples of one prompt must not share pages
+        self.has_recurrent_state = any(t == "linear_attention" for t in getattr(self.spec, "types", []))
+
+    # ---- parameters
+    def init_random(self, std: float = 0.02, seed: int = 0) -> None:
+        self.params.init_random(std, seed)
+
+    def load_state_dict(self, sd: dict, strict: bool = True) -> None:
+        """Tensors by checkpoint name (the HF names of the family); buffers of the checkpoint are taken along."""
+        self.params.load_hf_state_dict(sd, strict=strict)
+        for n in list(self.buffers):
+            if n in sd:
+                self.buffers[n] = sd[n].to(self.device)
+
+    def state_dict(self) -> "OrderedDict[str, torch.Tensor]":
+        out = OrderedDict((n, self.params[n]) for n in self.layout)
+        out.update(self.buffers)
+        return out
+
+    # ---- rope tables
+    def _rope(self, which: str, positions: torch.Tensor):
+        key = which
+        if key not in self._rope_cache:
+            self._rope_cache[key] = self.spec.rope(which)
+        inv, att = self._rope_cache[key]
+        ang = positions.to(torch.float32)[:, None] * inv.to(positions.device)[None, :]
+        emb = torch.cat([ang, ang], dim=-1)
+        return emb.cos() * att, emb.sin() * att
+
+    # ---- training interface (DenseModel's)
+    def _leaves(self, grad: bool) -> dict:
+        if not grad:
+            return dict(self.params.views)
+        return {n: v.detach().requires_grad_(self.spec.trainable(n)) for n, v in self.params.views.items()}
+
+    def hidden_states(self, W: dict, input_ids, position_ids, cu: list[int], ckpt: bool):
+        x = self.spec.embed(W, input_ids)
+        ctx = {"positions": position_ids, "cu": cu, "model": self}
+        for l in range(self.cfg.num_hidden_layers):
+            fn = lambda h, l=l: self.spec.layer(W, l, h, ctx)      # noqa: E731
+            x = checkpoint(fn, x, use_reentrant=False) if ckpt else fn(x)
+        return self.spec.final_norm(W, x)
+
+    def logprob_entropy(self, W: dict, h, labels, temperature: float, ckpt: bool, chunk: int = 2048):
+        """Per-token log-prob of ``labels`` and entropy from hidden states, vocabulary in fp32, token chunks recomputed
+        in backward so that no [T, V] tensor outlives its chunk."""
+        head = self.spec.head_weight(W)
+        cap = self.spec.final_softcap
+
+        def piece(hc, lc):
+            z = F.linear(hc, head).float()
+            if cap:
+                z = torch.tanh(z / cap) * cap
+            z = z / temperature
+            lse = torch.logsumexp(z, dim=-1)
+            p = torch.softmax(z, dim=-1)
+            ent = lse - (p * z).sum(-1)
+            lp = z.gather(1, lc.clamp_min(0)[:, None].long())[:, 0] - lse
+            return torch.where(lc >= 0, lp, torch.zeros_like(lp)), ent
+        lps, ents = [], []
+        for s in range(0, h.shape[0], chunk):
+            hc, lc = h[s:s + chunk], labels[s:s + chunk]
+            a, b = checkpoint(piece, hc, lc, use_reentrant=False) if (ckpt and torch.is_grad_enabled()) else piece(hc, lc)
+            lps.append(a)
+            ents.append(b)
+        return torch.cat(lps), torch.cat(ents)
+
+    def forward(self, batch, temperature: float = 1.0, save_for_backward: bool = False):
+        cu = batch.cu_seqlens.tolist()
+        with torch.set_grad_enabled(save_for_backward):
+            W = self._leaves(save_for_backward)
+            ck = save_for_backward and self.recompute == "full"
+            h = self.hidden_states(W, batch.input_ids.long(), batch.position_ids, cu, ck)
+            lp, ent = self.logprob_entropy(W, h, batch.labels, temperature, ck)
+        if save_for_backward:
+            self._saved = (W, lp, ent)
+        return lp.detach(), ent.detach()
+
+    def backward(self, g_logprob, g_entropy=None) -> None:
+        assert self._saved is not None, "forward(save_for_backward=True) must come first"
+        W, lp, ent = self._saved
+        self._saved = None
+        self.params.alloc_grads()
+        outs, grads = [lp], [g_logprob.to(lp.dtype)]
+        if g_entropy is not None:
+            outs.append(ent)
+            grads.append(g_entropy.to(ent.dtype))
+        torch.autograd.backward(outs, grads)
+        for n, leaf in W.items():
+            if leaf.grad is not None:
+                self.params.grads[n].add_(leaf.grad.float())
+
+    def logits(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None) -> torch.Tensor:
+        """fp32 logits [T, V] of one sequence (tests, evaluation)."""
+        T = input_ids.numel()
+        pos = position_ids if position_ids is not None else torch.arange(T, device=input_ids.device)
+        with torch.no_grad():
+            W = self._leaves(False)
+            h = self.hidden_states(W, input_ids.long(), pos, [0, T], False)
+            z = F.linear(h, self.spec.head_weight(W)).float()
+            if self.spec.final_softcap:
+                z = torch.tanh(z / self.spec.final_softcap) * self.spec.final_softcap
+        return z
+
+    # ---- sampler interface
+    @torch.no_grad()
+    def prefill(self, batch, cache, tok_seq, tok_pos, block_table, last_index):
+        W = self._leaves(False)
+        cu = batch.cu_seqlens.tolist()
+        x = self.spec.embed(W, batch.input_ids.long())
+        ctx = {"positions": batch.position_ids, "cu": cu, "model": self, "cache": cache, "tok_seq": tok_seq.long(),
+               "tok_pos": tok_pos.long(), "block_table": block_table, "mode": "prefill"}
+        for l in range(self.cfg.num_hidden_layers):
+            x = self.spec.layer(W, l, x, ctx)
+        h = self.spec.final_norm(W, x[last_index])
+        z = F.linear(h, self.spec.head_weight(W)).float()
+        return torch.tanh(z / self.spec.final_softcap) * self.spec.final_softcap if self.spec.final_softcap else z
+
+    @torch.no_grad()
+    def decode(self, tokens, positions, cache, block_table, seq_lens, shared=None):
+        W = self._leaves(False)
+        B = tokens.numel()
+        x = self.spec.embed(W, tokens.long())
+        ctx = {"positions": positions, "cu": list(range(B + 1)), "model": self, "cache": cache,
+               "tok_seq": torch.arange(B, device=tokens.device), "tok_pos": positions.long(), "block_table": block_table,
+               "mode": "decode", "seq_lens": seq_lens}
+        for l in range(self.cfg.num_hidden_layers):
+            x = self.spec.layer(W, l, x, ctx)
+        h = self.spec.final_norm(W, x)
+        z = F.linear(h, self.spec.head_weight(W)).float()
+        return torch.tanh(z / self.spec.final_softcap) * self.spec.final_softcap if self.spec.final_softcap else z
+
+    def flops_per_token(self, seqlen: int) -> float:
+        return 6.0 * self.params.numel
+
+
+# ------------------------------------------------------------------------------------------ KV cache helpers
+PAGE = 128
+
+
+def cache_write(cache, l: int, k, v, ctx) -> None:
+    """Store k [T, Hkv, Dk] / v [T, Hkv, Dv] of the packed tokens at (row ``tok_seq``, position ``tok_pos``) of the
+    paged pool; narrower heads than the pool's ``head_dim`` are zero-padded."""
+    bt, seq, pos = ctx["block_table"], ctx["tok_seq"], ctx["tok_pos"]
+    page = bt[seq, pos // PAGE].long()
+    slot = pos % PAGE
+    D = cache.k[l].shape[-1]
+    cache.k[l][page, :, slot, : k.shape[-1]] = k.to(cache.k[l].dtype)
+    cache.v[l][page, :, slot, : v.shape[-1]] = v.to(cache.v[l].dtype)
+    del D
+
+
+def cache_read(cache, l: int, ctx, dk: int, dv: int):
+    """Per sequence of a decode batch: (keys [n, Hkv, dk], values [n, Hkv, dv]) for the first ``seq_lens[b]`` positions."""
+    bt, lens = ctx["block_table"], ctx["seq_lens"].tolist()
+    ks, vs = [], []
+    for b, n in enumerate(lens):
+        pages = bt[b, : (n + PAGE - 1) // PAGE].long()
+        k = cache.k[l][pages].permute(0, 2, 1, 3).reshape(-1, cache.k[l].shape[1], cache.k[l].shape[3])[:n, :, :dk]
+        v = cache.v[l][pages].permute(0, 2, 1, 3).reshape(-1, cache.v[l].shape[1], cache.v[l].shape[3])[:n, :, :dv]
+        ks.append(k)
+        vs.append(v)
+    return ks, vs
+
+
+def attend(q, k, v, ctx, l: int, scale: float, window=None, sinks=None, softcap=None):
+    """Attention of a layer in whichever mode the context is in: packed training / prefill (writing the cache in
+    prefill) or single-token decode against the cache."""
+    mode = ctx.get("mode")
+    if mode is not None:
+        cache_write(ctx["cache"], l, k, v, ctx)
+    if mode == "decode":
+        ks, vs = cache_read(ctx["cache"], l, ctx, k.shape[-1], v.shape[-1])
+        return attention_cached(q, ks, vs, ctx["seq_lens"], scale, window, sinks, softcap)
+    return attention_packed(q, k, v, ctx["cu"], scale, window, sinks, softcap)
+
+
+# ------------------------------------------------------------------------------------------ family specs
+class _Spec:
+    """What a family defines: parameter layout, initialisation kinds, rope, embedding, one layer, final norm, head."""
+    final_softcap: float | None = None
+
+    def __init__(self, hf: dict):
+        self.hf = hf
+        self.H = hf["hidden_size"]
+        self.L = hf["num_hidden_layers"]
+        self.V = hf["vocab_size"]
+        self.eps = hf.get("rms_norm_eps", 1e-6)
+        self.tied = bool(hf.get("tie_word_embeddings", False))
+        rp = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
+        self.rope_params = dict(rp)
+        self.rope_params.setdefault("rope_theta", hf.get("rope_theta", 10000.0))
+
+    # layout helpers
+    def base_layout(self) -> "OrderedDict[str, tuple]":
+        lay = OrderedDict()
+        lay["model.embed_tokens.weight"] = (self.V, self.H)
+        for l in range(self.L):
+            for n, s in self.layer_layout(l).items():
+                lay[f"model.layers.{l}.{n}"] = s
+        lay["model.norm.weight"] = (self.H,)
+        if not self.tied:
+            lay["lm_head.weight"] = (self.V, self.H)
+        return lay
+
+    def layout(self):
+        return self.base_layout()
+
+    def buffers(self, device) -> dict:
+        return {}
+
+    def aliases(self, sd: dict) -> dict:
+        return {}
+
+    def trainable(self, name: str) -> bool:
+        return True
+
+    def init_kind(self, name: str) -> str:
+        if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+            return "ones"
+        if name.endswith(".bias") or name.endswith("_bias"):
+            return "zeros"
+        return "normal"
+
+    def embed(self, W, ids):
+        return W["model.embed_tokens.weight"][ids]
+
+    def final_norm(self, W, x):
+        return rms_norm(x, W["model.norm.weight"], self.eps)
+
+    def head_weight(self, W):
+        return W["model.embed_tokens.weight"] if self.tied else W["lm_head.weight"]
+
+    def rope(self, which: str):
+        raise NotImplementedError
+
+    def P(self, W, l: int, name: str):
+        return W[f"model.layers.{l}.{name}"]
+
+    def swiglu(self, W, l, prefix, x):
+        g = linear(x, self.P(W, l, f"{prefix}.gate_proj.weight"))
+        u = linear(x, self.P(W, l, f"{prefix}.up_proj.weight"))
+        return linear(F.silu(g) * u, self.P(W, l, f"{prefix}.down_proj.weight"))
+
+
+class _DeepseekV3(_Spec):
+    """DeepSeek-V3 / GLM-4.x "lite": multi-head latent attention + sigmoid routing over expert groups with a
+    correction bias, shared experts, the first layers dense."""
+
+    mla = True
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        self.nh = hf["num_attention_heads"]
+        self.q_lora, self.kv_lora = hf.get("q_lora_rank"), hf["kv_lora_rank"]
+        self.d_nope, self.d_rope, self.d_v = hf["qk_nope_head_dim"], hf["qk_rope_head_dim"], hf["v_head_dim"]
+        self.d_qk = self.d_nope + self.d_rope
+        self.E, self.k = hf["n_routed_experts"], hf["num_experts_per_tok"]
+        self.n_group, self.topk_group = hf.get("n_group", 1), hf.get("topk_group", 1)
+        self.first_dense = hf.get("first_k_dense_replace", 0)
+        self.Fm, self.F = hf["moe_intermediate_size"], hf["intermediate_size"]
+        self.n_shared = hf.get("n_shared_experts", 0) or 0
+        self.route_scale = hf.get("routed_scaling_factor", 1.0)
+        self.norm_topk = hf.get("norm_topk_prob", True)
+        self.interleave = bool(hf.get("rope_interleave", True))
+        self.bias = bool(hf.get("attention_bias", False))
+        self.scale = self.d_qk ** -0.5
+        if self.rope_params.get("rope_type", "default") == "yarn" and self.rope_params.get("mscale_all_dim"):
+            m = yarn_mscale(self.rope_params["factor"], self.rope_params["mscale_all_dim"])
+            self.scale *= m * m
+
+    def is_moe(self, l):
+        return l >= self.first_dense
+
+    def layer_layout(self, l):
+        H, nh = self.H, self.nh
+        lay = OrderedDict()
+        lay["input_layernorm.weight"] = (H,)
+        if self.q_lora:
+            lay["self_attn.q_a_proj.weight"] = (self.q_lora, H)
+            lay["self_attn.q_a_layernorm.weight"] = (self.q_lora,)
+            lay["self_attn.q_b_proj.weight"] = (nh * self.d_qk, self.q_lora)
+        else:
+            lay["self_attn.q_proj.weight"] = (nh * self.d_qk, H)
+        lay["self_attn.kv_a_proj_with_mqa.weight"] = (self.kv_lora + self.d_rope, H)
+        lay["self_attn.kv_a_layernorm.weight"] = (self.kv_lora,)
+        lay["self_attn.kv_b_proj.weight"] = (nh * (self.d_nope + self.d_v), self.kv_lora)
+        lay["self_attn.o_proj.weight"] = (H, nh * self.d_v)
+        lay["post_attention_layernorm.weight"] = (H,)
+        lay.update(self.mlp_layout(l))
+        return lay
+
+    def mlp_layout(self, l):
+        H = self.H
+        lay = OrderedDict()
+        if self.is_moe(l):
+            lay["mlp.gate.weight"] = (self.E, H)
+            lay["mlp.gate.e_score_correction_bias"] = (self.E,)
+            lay["mlp.experts.gate_up_proj"] = (self.E, 2 * self.Fm, H)
+            lay["mlp.experts.down_proj"] = (self.E, H, self.Fm)
+            if self.n_shared:
+                for n, s in (("gate_proj", (self.Fm * self.n_shared, H)), ("up_proj", (self.Fm * self.n_shared, H)),
+                             ("down_proj", (H, self.Fm * self.n_shared))):
+                    lay[f"mlp.shared_experts.{n}.weight"] = s
+        else:
+            for n, s in (("gate_proj", (self.F, H)), ("up_proj", (self.F, H)), ("down_proj", (H, self.F))):
+                lay[f"mlp.{n}.weight"] = s
+        return lay
+
+    def trainable(self, name):
+        return not name.endswith("e_score_correction_bias")      # updated by the load-balancing rule, not by gradients
+
+    def init_kind(self, name):
+        return "zeros" if name.endswith("e_score_correction_bias") else super().init_kind(name)
+
+    def rope(self, which):
+        return rope_frequencies(self.rope_params, self.d_rope, self.hf.get("max_position_embeddings", 4096))
+
+    def attention(self, W, l, h, ctx):
+        T = h.shape[0]
+        nh = self.nh
+        if self.q_lora:
+            qa = rms_norm(linear(h, self.P(W, l, "self_attn.q_a_proj.weight")), self.P(W, l, "self_attn.q_a_layernorm.weight"), self.eps)
+            q = linear(qa, self.P(W, l, "self_attn.q_b_proj.weight"))
+        else:
+            q = linear(h, self.P(W, l, "self_attn.q_proj.weight"))
+        q = q.view(T, nh, self.d_qk)
+        ckv = linear(h, self.P(W, l, "self_attn.kv_a_proj_with_mqa.weight"))
+        c, k_rot = ckv[:, : self.kv_lora], ckv[:, self.kv_lora:]
+        kv = linear(rms_norm(c, self.P(W, l, "self_attn.kv_a_layernorm.weight"), self.eps), self.P(W, l, "self_attn.kv_b_proj.weight"))
+        kv = kv.view(T, nh, self.d_nope + self.d_v)
+        k_nope, v = kv[..., : self.d_nope], kv[..., self.d_nope:]
+        cos, sin = ctx["model"]._rope("main", ctx["positions"])
+        q_rot = apply_rope(q[..., self.d_nope:], cos, sin, self.interleave)
+        k_rot = apply_rope(k_rot[:, None, :], cos, sin, self.interleave).expand(T, nh, self.d_rope)
+        qf = torch.cat([q[..., : self.d_nope], q_rot], dim=-1)
+        kf = torch.cat([k_nope, k_rot], dim=-1)
+        o = attend(qf, kf, v, ctx, l, self.scale)
+        return linear(o.reshape(T, nh * self.d_v), self.P(W, l, "self_attn.o_proj.weight"))
+
+    def route(self, W, l, h):
+        scores = F.linear(h.float(), self.P(W, l, "mlp.gate.weight").float()).sigmoid()
+        choice = scores + self.P(W, l, "mlp.gate.e_score_correction_bias").float()
+        if self.n_group > 1:
+            grp = choice.view(-1, self.n_group, self.E // self.n_group).topk(2, dim=-1)[0].sum(-1)
+            keep = torch.zeros_like(grp).scatter_(1, grp.topk(self.topk_group, dim=-1)[1], 1.0)
+            mask = keep[:, :, None].expand(-1, self.n_group, self.E // self.n_group).reshape(-1, self.E)
+            choice = choice.masked_fill(mask == 0, 0.0)
+        idx = choice.topk(self.k, dim=-1)[1]
+        w = scores.gather(1, idx)
+        if self.norm_topk:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        return idx, w * self.route_scale
+
+    def moe(self, W, l, h):
+        idx, w = self.route(W, l, h)
+        gu, dn = self.P(W, l, "mlp.experts.gate_up_proj"), self.P(W, l, "mlp.experts.down_proj")
+
+        def expert(e, rows):
+            g, u = F.linear(rows, gu[e]).chunk(2, dim=-1)
+            return F.linear(F.silu(g) * u, dn[e])
+        out = experts_forward(h, idx, w, expert, self.E)
+        if self.n_shared:
+            out = out + self.swiglu(W, l, "mlp.shared_experts", h)
+        return out
+
+    def layer(self, W, l, x, ctx):
+        x = x + self.attention(W, l, rms_norm(x, self.P(W, l, "input_layernorm.weight"), self.eps), ctx)
+        h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps)
+        return x + (self.moe(W, l, h) if self.is_moe(l) else self.swiglu(W, l, "mlp", h))
+
+
+class _Glm4Moe(_DeepseekV3):
+    """GLM-4.5 / 4.6: grouped-query attention (half of each head rotates, optional per-head q/k norm, q/k/v bias)
+    with the DeepSeek-style routed + shared experts."""
+    mla = False
+
+    def __init__(self, hf):
+        _Spec.__init__(self, hf)
+        self.nh, self.nkv = hf["num_attention_heads"], hf["num_key_value_heads"]
+        self.D = hf.get("head_dim") or self.H // self.nh
+        self.rot = int(self.D * hf.get("partial_rotary_factor", 0.5))
+        self.qk_norm = bool(hf.get("use_qk_norm", False))
+        self.bias = bool(hf.get("attention_bias", False))
+        self.E, self.k = hf["n_routed_experts"], hf["num_experts_per_tok"]
+        self.n_group, self.topk_group = hf.get("n_group", 1), hf.get("topk_group", 1)
+        self.first_dense = hf.get("first_k_dense_replace", 0)
+        self.Fm, self.F = hf["moe_intermediate_size"], hf["intermediate_size"]
+        self.n_shared = hf.get("n_shared_experts", 0) or 0
+        self.route_scale = hf.get("routed_scaling_factor", 1.0)
+        self.norm_topk = hf.get("norm_topk_prob", True)
+        self.scale = self.D ** -0.5
+
+    def layer_layout(self, l):
+        H = self.H
+        lay = OrderedDict()
+        lay["input_layernorm.weight"] = (H,)
+        for n, rows in (("q_proj", self.nh * self.D), ("k_proj", self.nkv * self.D), ("v_proj", self.nkv * self.D)):
+            lay[f"self_attn.{n}.weight"] = (rows, H)
+            if self.bias:
+                lay[f"self_attn.{n}.bias"] = (rows,)
+        lay["self_attn.o_proj.weight"] = (H, self.nh * self.D)
+        if self.qk_norm:
+            lay["self_attn.q_norm.weight"] = (self.D,)
+            lay["self_attn.k_norm.weight"] = (self.D,)
+        lay["post_attention_layernorm.weight"] = (H,)
+        lay.update(self.mlp_layout(l))
+        return lay
+
+    def rope(self, which):
+        return rope_frequencies(self.rope_params, self.rot, self.hf.get("max_position_embeddings", 4096))
+
+    def attention(self, W, l, h, ctx):
+        T = h.shape[0]
+        b = (lambda n: self.P(W, l, f"self_attn.{n}.bias")) if self.bias else (lambda n: None)
+        q = linear(h, self.P(W, l, "self_attn.q_proj.weight"), b("q_proj")).view(T, self.nh, self.D)
+        k = linear(h, self.P(W, l, "self_attn.k_proj.weight"), b("k_proj")).view(T, self.nkv, self.D)
+        v = linear(h, self.P(W, l, "self_attn.v_proj.weight"), b("v_proj")).view(T, self.nkv, self.D)
+        if self.qk_norm:
+            q = rms_norm(q, self.P(W, l, "self_attn.q_norm.weight"), self.eps)
+            k = rms_norm(k, self.P(W, l, "self_attn.k_norm.weight"), self.eps)
+        cos, sin = ctx["model"]._rope("main", ctx["positions"])
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        o = attend(q, k, v, ctx, l, self.scale)
+        return linear(o.reshape(T, self.nh * self.D), self.P(W, l, "self_attn.o_proj.weight"))
+
+
+class _GptOss(_Spec):
+    """GPT-OSS: every layer sparse; attention with a learned sink logit per head, sliding-window layers alternate
+    with full-attention layers, biases on every projection; experts use a clamped SwiGLU with interleaved gate / up
+    columns and the router softmaxes over the chosen experts only."""
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        self.nh, self.nkv = hf["num_attention_heads"], hf["num_key_value_heads"]
+        self.D = hf.get("head_dim") or self.H // self.nh
+        self.E, self.k, self.F = hf["num_local_experts"], hf["num_experts_per_tok"], hf["intermediate_size"]
+        self.window = hf.get("sliding_window", 128)
+        self.types = hf.get("layer_types") or ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(self.L)]
+        self.alpha, self.limit = 1.702, float(hf.get("swiglu_limit", 7.0))
+        self.scale = self.D ** -0.5
+
+    def layer_layout(self, l):
+        H = self.H
+        lay = OrderedDict()
+        lay["input_layernorm.weight"] = (H,)
+        for n, rows in (("q_proj", self.nh * self.D), ("k_proj", self.nkv * self.D), ("v_proj", self.nkv * self.D)):
+            lay[f"self_attn.{n}.weight"] = (rows, H)
+            lay[f"self_attn.{n}.bias"] = (rows,)
+        lay["self_attn.o_proj.weight"] = (H, self.nh * self.D)
+        lay["self_attn.o_proj.bias"] = (H,)
+        lay["self_attn.sinks"] = (self.nh,)
+        lay["post_attention_layernorm.weight"] = (H,)
+        lay["mlp.router.weight"] = (self.E, H)
+        lay["mlp.router.bias"] = (self.E,)
+        lay["mlp.experts.gate_up_proj"] = (self.E, H, 2 * self.F)
+        lay["mlp.experts.gate_up_proj_bias"] = (self.E, 2 * self.F)
+        lay["mlp.experts.down_proj"] = (self.E, self.F, H)
+        lay["mlp.experts.down_proj_bias"] = (self.E, H)
+        return lay
+
+    def rope(self, which):
+        return rope_frequencies(self.rope_params, self.D, self.hf.get("max_position_embeddings", 4096))
+
+    def layer(self, W, l, x, ctx):
+        T = x.shape[0]
+        h = rms_norm(x, self.P(W, l, "input_layernorm.weight"), self.eps)
+        q = linear(h, self.P(W, l, "self_attn.q_proj.weight"), self.P(W, l, "self_attn.q_proj.bias")).view(T, self.nh, self.D)
+        k = linear(h, self.P(W, l, "self_attn.k_proj.weight"), self.P(W, l, "self_attn.k_proj.bias")).view(T, self.nkv, self.D)
+        v = linear(h, self.P(W, l, "self_attn.v_proj.weight"), self.P(W, l, "self_attn.v_proj.bias")).view(T, self.nkv, self.D)
+        cos, sin = ctx["model"]._rope("main", ctx["positions"])
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        win = self.window if self.types[l] == "sliding_attention" else None
+        o = attend(q, k, v, ctx, l, self.scale, window=win, sinks=self.P(W, l, "self_attn.sinks"))
+        x = x + linear(o.reshape(T, self.nh * self.D), self.P(W, l, "self_attn.o_proj.weight"), self.P(W, l, "self_attn.o_proj.bias"))
+        h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps)
+        logits = F.linear(h, self.P(W, l, "mlp.router.weight"), self.P(W, l, "mlp.router.bias"))
+        top, idx = logits.topk(self.k, dim=-1)
+        w = torch.softmax(top, dim=-1, dtype=top.dtype)
+        gu, gub = self.P(W, l, "mlp.experts.gate_up_proj"), self.P(W, l, "mlp.experts.gate_up_proj_bias")
+        dn, dnb = self.P(W, l, "mlp.experts.down_proj"), self.P(W, l, "mlp.experts.down_proj_bias")
+
+        def expert(e, rows):
+            y = rows @ gu[e] + gub[e]
+            g, u = y[..., ::2].clamp(max=self.limit), y[..., 1::2].clamp(-self.limit, self.limit)
+            return ((u + 1) * (g * torch.sigmoid(g * self.alpha))) @ dn[e] + dnb[e]
+        return x + experts_forward(h, idx, w, expert, self.E)
+
+    def init_kind(self, name):
+        return "zeros" if name.endswith("sinks") else super().init_kind(name)
+
+
+class _Gemma(_Spec):
+    """Gemma-2 / Gemma-3 text: embeddings scaled by sqrt(hidden), (1 + w) RMSNorm before AND after attention and
+    MLP, GeGLU, query scale from ``query_pre_attn_scalar``, sliding-window layers by pattern, optional soft-capping
+    of attention logits and of the final logits, per-head q/k norm and a separate local rope base (Gemma-3)."""
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        self.nh, self.nkv = hf["num_attention_heads"], hf["num_key_value_heads"]
+        self.D = hf.get("head_dim") or self.H // self.nh
+        self.F = hf["intermediate_size"]
+        self.tied = bool(hf.get("tie_word_embeddings", True))
+        self.window = hf.get("sliding_window")
+        self.gemma3 = hf.get("model_type") == "gemma3_text"
+        pat = hf.get("sliding_window_pattern", 6 if self.gemma3 else 2)
+        self.types = hf.get("layer_types") or [
+            "full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(self.L)]
+        self.scale = float(hf.get("query_pre_attn_scalar", self.D)) ** -0.5
+        self.attn_cap = hf.get("attn_logit_softcapping")
+        self.final_softcap = hf.get("final_logit_softcapping")
+        self.local_theta = hf.get("rope_local_base_freq", 10000.0)
+        rp = hf.get("rope_parameters") or {}
+        if "full_attention" in rp:                        # per-layer-type rope parameters
+            self.rope_params = dict(rp["full_attention"])
+            self.local_rope = dict(rp.get("sliding_attention", {"rope_type": "default", "rope_theta": self.local_theta}))
+        else:
+            self.local_rope = {"rope_type": "default", "rope_theta": self.local_theta if self.gemma3 else self.rope_params["rope_theta"]}
+
+    def layer_layout(self, l):
+        H = self.H
+        lay = OrderedDict()
+        lay["input_layernorm.weight"] = (H,)
+        lay["self_attn.q_proj.weight"] = (self.nh * self.D, H)
+        lay["self_attn.k_proj.weight"] = (self.nkv * self.D, H)
+        lay["self_attn.v_proj.weight"] = (self.nkv * self.D, H)
+        lay["self_attn.o_proj.weight"] = (H, self.nh * self.D)
+        if self.gemma3:
+            lay["self_attn.q_norm.weight"] = (self.D,)
+            lay["self_attn.k_norm.weight"] = (self.D,)
+        lay["post_attention_layernorm.weight"] = (H,)
+        lay["pre_feedforward_layernorm.weight"] = (H,)
+        lay["post_feedforward_layernorm.weight"] = (H,)
+        for n, s in (("gate_proj", (self.F, H)), ("up_proj", (self.F, H)), ("down_proj", (H, self.F))):
+            lay[f"mlp.{n}.weight"] = s
+        return lay
+
+    def init_kind(self, name):       # (1 + w) norms start at w = 0
+        return "zeros" if name.endswith("norm.weight") else "normal"
+
+    def rope(self, which):
+        rp = self.local_rope if which == "local" else self.rope_params
+        return rope_frequencies(rp, self.D, self.hf.get("max_position_embeddings", 8192))
+
+    def embed(self, W, ids):
+        e = W["model.embed_tokens.weight"][ids]
+        return e * torch.tensor(self.H ** 0.5, dtype=e.dtype)
+
+    def final_norm(self, W, x):
+        return rms_norm(x, W["model.norm.weight"], self.eps, plus_one=True)
+
+    def layer(self, W, l, x, ctx):
+        T = x.shape[0]
+        n1 = lambda t, name: rms_norm(t, self.P(W, l, name), self.eps, plus_one=True)      # noqa: E731
+        h = n1(x, "input_layernorm.weight")
+        q = linear(h, self.P(W, l, "self_attn.q_proj.weight")).view(T, self.nh, self.D)
+        k = linear(h, self.P(W, l, "self_attn.k_proj.weight")).view(T, self.nkv, self.D)
+        v = linear(h, self.P(W, l, "self_attn.v_proj.weight")).view(T, self.nkv, self.D)
+        if self.gemma3:
+            q, k = n1(q, "self_attn.q_norm.weight"), n1(k, "self_attn.k_norm.weight")
+        sliding = self.types[l] == "sliding_attention"
+        cos, sin = ctx["model"]._rope("local" if sliding else "main", ctx["positions"])
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        o = attend(q, k, v, ctx, l, self.scale, window=self.window if sliding else None, softcap=self.attn_cap)
+        x = x + n1(linear(o.reshape(T, self.nh * self.D), self.P(W, l, "self_attn.o_proj.weight")), "post_attention_layernorm.weight")
+        h = n1(x, "pre_feedforward_layernorm.weight")
+        g = linear(h, self.P(W, l, "mlp.gate_proj.weight"))
+        u = linear(h, self.P(W, l, "mlp.up_proj.weight"))
+        m = linear(F.gelu(g, approximate="tanh") * u, self.P(W, l, "mlp.down_proj.weight"))
+        return x + n1(m, "post_feedforward_layernorm.weight")
+
+
+class _Qwen3Next(_Spec):
+    """Qwen3-Next / Qwen3.5: three of four layers mix tokens with a gated delta-rule linear attention (short causal
+    convolution over q | k | v, L2-normalised keys and queries, per-head decay and write strength, gated RMSNorm on
+    the output); every fourth layer is full attention with a sigmoid output gate, (1 + w) norms and a quarter of each
+    head rotated. MLPs are sparse with one always-on shared expert behind its own sigmoid gate."""
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        self.nh, self.nkv = hf["num_attention_heads"], hf["num_key_value_heads"]
+        self.D = hf.get("head_dim") or self.H // self.nh
+        self.rot = int(self.D * (hf.get("partial_rotary_factor") or self.rope_params.get("partial_rotary_factor", 0.25)))
+        self.types = hf.get("layer_types") or [
+            "full_attention" if (i + 1) % hf.get("full_attention_interval", 4) == 0 else "linear_attention" for i in range(self.L)]
+        self.nv, self.nk = hf["linear_num_value_heads"], hf["linear_num_key_heads"]
+        self.dk, self.dv = hf["linear_key_head_dim"], hf["linear_value_head_dim"]
+        self.conv_k = hf.get("linear_conv_kernel_dim", 4)
+        self.E, self.k = hf.get("num_experts", 0), hf.get("num_experts_per_tok", 0)
+        self.Fm, self.F = hf.get("moe_intermediate_size", 0), hf.get("intermediate_size", 0)
+        self.Fs = hf.get("shared_expert_intermediate_size", 0)
+        self.sparse_step = hf.get("decoder_sparse_step", 1)
+        self.mlp_only = set(hf.get("mlp_only_layers", []) or [])
+        self.norm_topk = hf.get("norm_topk_prob", True)
+        self.scale = self.D ** -0.5
+
+    def is_moe(self, l):
+        return l not in self.mlp_only and self.E > 0 and (l + 1) % self.sparse_step == 0
+
+    def layer_layout(self, l):
+        H = self.H
+        lay = OrderedDict()
+        lay["input_layernorm.weight"] = (H,)
+        if self.types[l] == "linear_attention":
+            kd, vd = self.nk * self.dk, self.nv * self.dv
+            lay["linear_attn.in_proj_qkvz.weight"] = (2 * kd + 2 * vd, H)
+            lay["linear_attn.in_proj_ba.weight"] = (2 * self.nv, H)
+            lay["linear_attn.conv1d.weight"] = (2 * kd + vd, 1, self.conv_k)
+            lay["linear_attn.dt_bias"] = (self.nv,)
+            lay["linear_attn.A_log"] = (self.nv,)
+            lay["linear_attn.norm.weight"] = (self.dv,)
+            lay["linear_attn.out_proj.weight"] = (H, vd)
+        else:
+            lay["self_attn.q_proj.weight"] = (2 * self.nh * self.D, H)
+            lay["self_attn.k_proj.weight"] = (self.nkv * self.D, H)
+            lay["self_attn.v_proj.weight"] = (self.nkv * self.D, H)
+            lay["self_attn.o_proj.weight"] = (H, self.nh * self.D)
+            lay["self_attn.q_norm.weight"] = (self.D,)
+            lay["self_attn.k_norm.weight"] = (self.D,)
+        lay["post_attention_layernorm.weight"] = (H,)
+        if self.is_moe(l):
+            lay["mlp.gate.weight"] = (self.E, H)
+            lay["mlp.experts.gate_up_proj"] = (self.E, 2 * self.Fm, H)
+            lay["mlp.experts.down_proj"] = (self.E, H, self.Fm)
+            for n, s in (("gate_proj", (self.Fs, H)), ("up_proj", (self.Fs, H)), ("down_proj", (H, self.Fs))):
+                lay[f"mlp.shared_expert.{n}.weight"] = s
+            lay["mlp.shared_expert_gate.weight"] = (1, H)
+        else:
+            for n, s in (("gate_proj", (self.F, H)), ("up_proj", (self.F, H)), ("down_proj", (H, self.F))):
+                lay[f"mlp.{n}.weight"] = s
+        return lay
+
+    def init_kind(self, name):
+        if name.endswith("linear_attn.norm.weight") or name.endswith("dt_bias"):
+            return "ones"
+        if name.endswith("A_log"):
+            return "a_log"
+        if name.endswith("norm.weight"):
+            return "zeros"                       # (1 + w) norms
+        return "normal"
+
+    def rope(self, which):
+        return rope_frequencies(self.rope_params, self.rot, self.hf.get("max_position_embeddings", 4096))
+
+    def final_norm(self, W, x):
+        return rms_norm(x, W["model.norm.weight"], self.eps, plus_one=True)
+
+    def full_attention(self, W, l, h, ctx):
+        T = h.shape[0]
+        qg = linear(h, self.P(W, l, "self_attn.q_proj.weight")).view(T, self.nh, 2 * self.D)
+        q, gate = qg[..., : self.D], qg[..., self.D:].reshape(T, self.nh * self.D)
+        k = linear(h, self.P(W, l, "self_attn.k_proj.weight")).view(T, self.nkv, self.D)
+        v = linear(h, self.P(W, l, "self_attn.v_proj.weight")).view(T, self.nkv, self.D)
+        q = rms_norm(q, self.P(W, l, "self_attn.q_norm.weight"), self.eps, plus_one=True)
+        k = rms_norm(k, self.P(W, l, "self_attn.k_norm.weight"), self.eps, plus_one=True)
+        cos, sin = ctx["model"]._rope("main", ctx["positions"])
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        o = attend(q, k, v, ctx, l, self.scale).reshape(T, self.nh * self.D)
+        return linear(o * torch.sigmoid(gate), self.P(W, l, "self_attn.o_proj.weight"))
+
+    def linear_attention(self, W, l, h, ctx):
+        T = h.shape[0]
+        nk, nv, dk, dv = self.nk, self.nv, self.dk, self.dv
+        r = nv // nk
+        qkvz = linear(h, self.P(W, l, "linear_attn.in_proj_qkvz.weight")).view(T, nk, 2 * dk + 2 * r * dv)
+        ba = linear(h, self.P(W, l, "linear_attn.in_proj_ba.weight")).view(T, nk, 2 * r)
+        q, k, v, z = torch.split(qkvz, [dk, dk, r * dv, r * dv], dim=-1)
+        b, a = ba[..., :r].reshape(T, nv), ba[..., r:].reshape(T, nv)
+        v, z = v.reshape(T, nv, dv), z.reshape(T, nv, dv)
+        mixed = torch.cat([q.reshape(T, nk * dk), k.reshape(T, nk * dk), v.reshape(T, nv * dv)], dim=-1)      # [T, C]
+        wconv = self.P(W, l, "linear_attn.conv1d.weight")[:, 0, :]                                            # [C, K]
+        K = self.conv_k
+        mode, model = ctx.get("mode"), ctx["model"]
+        beta = torch.sigmoid(b)
+        g = -self.P(W, l, "linear_attn.A_log").float().exp() * F.softplus(a.float() + self.P(W, l, "linear_attn.dt_bias").float())
+        outs = []
+        cu = ctx["cu"]
+        for s_i, (s0, s1) in enumerate(zip(cu[:-1], cu[1:])):
+            if s1 == s0:
+                continue
+            key = None
+            prev_conv = prev_state = None
+            if mode is not None:
+                key = (l, int(ctx["block_table"][int(ctx["tok_seq"][s0])][0]))
+                if mode == "decode":
+                    prev_conv, prev_state = model.recurrent_state[key]
+            seg = mixed[s0:s1]
+            hist = prev_conv if prev_conv is not None else torch.zeros(K - 1, seg.shape[1], dtype=seg.dtype, device=seg.device)
+            padded = torch.cat([hist, seg], dim=0)                                                              # [n + K - 1, C]
+            win = padded.unfold(0, K, 1)                                                                        # [n, C, K]
+            conv = F.silu((win * wconv[None].to(win.dtype)).sum(-1))
+            n = s1 - s0
+            qs, ks, vs = torch.split(conv, [nk * dk, nk * dk, nv * dv], dim=-1)
+            qs, ks = l2norm(qs.reshape(n, nk, dk)), l2norm(ks.reshape(n, nk, dk))
+            if r > 1:
+                qs, ks = qs.repeat_interleave(r, dim=1), ks.repeat_interleave(r, dim=1)
+            o, S = gated_delta_rule(qs, ks, vs.reshape(n, nv, dv), g[s0:s1], beta[s0:s1], prev_state)
+            if key is not None:
+                model.recurrent_state[key] = (padded[-(K - 1):].clone(), S)
+            outs.append(o)
+        o = torch.cat(outs, dim=0)                                                                               # [T, nv, dv]
+        of = o.float()
+        of = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + self.eps)
+        o = (self.P(W, l, "linear_attn.norm.weight") * of.to(h.dtype)) * F.silu(z.float()).to(h.dtype)
+        return linear(o.reshape(T, nv * dv), self.P(W, l, "linear_attn.out_proj.weight"))
+
+    def moe(self, W, l, h):
+        probs = torch.softmax(F.linear(h, self.P(W, l, "mlp.gate.weight")), dim=-1, dtype=torch.float)
+        w, idx = probs.topk(self.k, dim=-1)
+        if self.norm_topk:
+            w = w / w.sum(-1, keepdim=True)
+        gu, dn = self.P(W, l, "mlp.experts.gate_up_proj"), self.P(W, l, "mlp.experts.down_proj")
+
+        def expert(e, rows):
+            g, u = F.linear(rows, gu[e]).chunk(2, dim=-1)
+            return F.linear(F.silu(g) * u, dn[e])
+        out = experts_forward(h, idx, w.to(h.dtype), expert, self.E)
+        shared = self.swiglu(W, l, "mlp.shared_expert", h)
+        return out + torch.sigmoid(F.linear(h, self.P(W, l, "mlp.shared_expert_gate.weight"))) * shared
+
+    def layer(self, W, l, x, ctx):
+        h = rms_norm(x, self.P(W, l, "input_layernorm.weight"), self.eps, plus_one=True)
+        mix = self.linear_attention if self.types[l] == "linear_attention" else self.full_attention
+        x = x + mix(W, l, h, ctx)
+        h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps, plus_one=True)
+        return x + (self.moe(W, l, h) if self.is_moe(l) else self.swiglu(W, l, "mlp", h))
+
+
+_SPECS = {"deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
+          "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen3Next}
+
+
+# ------------------------------------------------------------------------------------------ construction
+def family_config(hf: dict) -> ModelConfig:
+    """The ``ModelConfig`` view of a family's HF config: the fields the engines read (cache geometry, vocabulary,
+    special tokens); everything else stays in ``extra['hf_config']`` for the family's spec."""
+    mt = hf["model_type"]
+    nh = hf["num_attention_heads"]
+    if mt in ("deepseek_v3", "glm4_moe_lite"):
+        # the paged cache holds expanded keys (nope + rope) and values per head
+        nkv, hd = nh, max(hf["qk_nope_head_dim"] + hf["qk_rope_head_dim"], hf["v_head_dim"])
+    else:
+        nkv = hf.get("num_key_value_heads", nh)
+        hd = hf.get("head_dim") or hf["hidden_size"] // nh
+    eos = hf.get("eos_token_id", 1)
+    eos = eos[0] if isinstance(eos, list) else eos
+    cfg = ModelConfig(model_type=mt, vocab_size=hf["vocab_size"], hidden_size=hf["hidden_size"],
+                      num_hidden_layers=hf["num_hidden_layers"], num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd,
+                      intermediate_size=hf.get("intermediate_size", 0), rms_norm_eps=hf.get("rms_norm_eps", 1e-6),
+                      tie_word_embeddings=bool(hf.get("tie_word_embeddings", mt.startswith("gemma"))),
+                      max_position_embeddings=hf.get("max_position_embeddings", 4096), eos_token_id=eos if eos is not None else 1,
+                      pad_token_id=hf.get("pad_token_id") if hf.get("pad_token_id") is not None else 0,
+                      num_experts=hf.get("n_routed_experts") or hf.get("num_local_experts") or hf.get("num_experts") or 0,
+                      num_experts_per_tok=hf.get("num_experts_per_tok", 0) or 0, moe_intermediate_size=hf.get("moe_intermediate_size", 0) or 0)
+    cfg.extra["hf_config"] = dict(hf)
+    return cfg
+
+
+def build_family_model(hf: dict, device="cuda", dtype=torch.bfloat16) -> FamilyModel:
+    return FamilyModel(family_config(hf), device=device, dtype=dtype, hf=hf)

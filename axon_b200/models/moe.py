@@ -186,5 +186,8 @@ class MoEModel(DenseModel):
 
 
 def build_model_for(cfg: ModelConfig, device="cuda", dtype=torch.bfloat16):
-    """Dense or sparse model class by configuration."""
+    """Dense or sparse in-house model, or one of the families of ``models/families.py``, by configuration."""
+    from .families import FAMILY_TYPES, FamilyModel
+    if cfg.model_type in FAMILY_TYPES:
+        return FamilyModel(cfg, device=device, dtype=dtype)
     return (MoEModel if cfg.num_experts > 0 else DenseModel)(cfg, device=device, dtype=dtype)

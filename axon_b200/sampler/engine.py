@@ -65,7 +65,8 @@ class GenerationEngine:
         # CUDA-graph decode: one captured graph per batch-size bucket (re-captured after every wake_up,
         # because the KV pool moves). Disabled on CPU.
         self.use_cuda_graph = self.device.type == "cuda"
-        self.share_prompts = True          # n samples of one prompt share its KV pages and its prefill
+        # n samples of one prompt share its KV pages and its prefill (not for models that keep per-sequence recurrent state)
+        self.share_prompts = not getattr(model, "has_recurrent_state", False)
         # "processed": log-prob under the distribution actually drawn from (after top-k / top-p, the reference
         # fork's convention); "full": temperature-scaled log-softmax over the whole vocabulary (what the trainer
         # recomputes), which keeps importance-sampling corrections unbiased under truncation.

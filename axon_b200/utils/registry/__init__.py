@@ -2,6 +2,8 @@
 rewards (reference: axon/utils/registry/, ``ClassRegistry`` and ``FunctionRegistry``)."""
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from enum import Enum
 from typing import Any, Callable, Generic, TypeVar
@@ -54,6 +56,17 @@ class FunctionRegistry(Generic[T]):
         return _key(name) in self._entries
 
 
+def _same_definition(a, b) -> bool:
+    """Two class objects made from the same source (a recipe file imported once as a package module and once by
+    path): re-registering such a class under its name is not a conflict."""
+    import inspect
+    try:
+        return a.__qualname__ == b.__qualname__ and inspect.getsourcefile(a) is not None and \
+            os.path.realpath(inspect.getsourcefile(a)) == os.path.realpath(inspect.getsourcefile(b))
+    except (TypeError, OSError):
+        return False
+
+
 class ClassRegistry(Generic[T]):
     """Maps names to classes; ``register`` works as ``@reg.register("name")`` or ``reg.register("name", cls)``."""
 
@@ -68,7 +81,8 @@ class ClassRegistry(Generic[T]):
         def deco(c):
             if self.base is not None and not (isinstance(c, type) and issubclass(c, self.base)):
                 raise TypeError(f"{c} is not a subclass of {self.base.__name__}")
-            if key in self._classes and self._classes[key] is not c and not override:
+            old = self._classes.get(key)
+            if old is not None and old is not c and not override and not _same_definition(old, c):
                 raise ValueError(f"{self.name} '{key}' is already registered")
             self._classes[key] = c
             return c
