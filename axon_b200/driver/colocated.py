@@ -225,7 +225,10 @@ class ColocatedRLRunner:
         self._enter_rollout()
         t1 = time.perf_counter()
         pre0 = self.engine.stats.get("preempted", 0)
+        host0, steps0 = self.engine.stats.get("decode_host_prep_s", 0.0), self.engine.stats.get("decode_steps", 0)
         outs = self.engine.generate(prompts, params)
+        self.phase_detail["decode_host_prep_s"] = self.engine.stats.get("decode_host_prep_s", 0.0) - host0
+        self.phase_detail["decode_steps"] = self.engine.stats.get("decode_steps", 0) - steps0
         self.phase_detail["preempted"] = self.engine.stats.get("preempted", 0) - pre0      # sequences pushed back for lack of KV pages
         peak = self.engine.cache.num_pages - self.engine.cache.min_free
         self.phase_detail["kv_peak_pages"] = peak

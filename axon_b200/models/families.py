@@ -28,7 +28,8 @@ from torch.utils.checkpoint import checkpoint
 from .config import ModelConfig
 from .params import FlatParams
 
-FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text")
+FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text",
+                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text")
 
 
 # ------------------------------------------------------------------------------------------ small pieces
@@ -124,21 +125,22 @@ def rope_frequencies(rope: dict, dim: int, max_pos_default: int) -> tuple[torch.
 
 
 def attention_packed(q, k, v, cu, scale: float, window: int | None = None, sinks: torch.Tensor | None = None,
-                     softcap: float | None = None):
+                     softcap: float | None = None, allowed: list | None = None):
     """Causal attention over packed sequences. q [T, Hq, Dk], k [T, Hkv, Dk], v [T, Hkv, Dv]; ``cu`` = sequence
     boundaries (python ints). ``window``: a key is visible while ``q_pos - k_pos < window``. ``sinks`` [Hq]: one
     extra logit per head that takes probability mass and contributes nothing. ``softcap``: logits pass through
-    ``cap * tanh(x / cap)``. Returns [T, Hq, Dv]."""
+    ``cap * tanh(x / cap)``. ``allowed``: per sequence a bool [n, n] matrix of keys each query may see (sparse
+    attention by selected indices), applied on top of causality. Returns [T, Hq, Dv]."""
     Hq, Hkv = q.shape[1], k.shape[1]
     rep = Hq // Hkv
     outs = []
     plain = sinks is None and softcap is None
-    for a, b in zip(cu[:-1], cu[1:]):
+    for si, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
         n = b - a
         if n == 0:
             continue
         qs, ks, vs = q[a:b].transpose(0, 1), k[a:b].transpose(0, 1), v[a:b].transpose(0, 1)      # [H, n, D]
-        if plain and window is None:
+        if plain and window is None and allowed is None:
             o = F.scaled_dot_product_attention(qs[None], ks[None], vs[None], is_causal=True, scale=scale, enable_gqa=rep > 1)[0]
             outs.append(o.transpose(0, 1))
             continue
@@ -146,6 +148,8 @@ def attention_packed(q, k, v, cu, scale: float, window: int | None = None, sinks
         ok = idx[None, :] <= idx[:, None]
         if window is not None:
             ok = ok & (idx[:, None] - idx[None, :] < window)
+        if allowed is not None:
+            ok = ok & allowed[si]
         if plain:
             o = F.scaled_dot_product_attention(qs[None], ks[None], vs[None], attn_mask=ok[None, None], scale=scale, enable_gqa=rep > 1)[0]
             outs.append(o.transpose(0, 1))
@@ -165,7 +169,7 @@ def attention_packed(q, k, v, cu, scale: float, window: int | None = None, sinks
     return torch.cat(outs, dim=0)
 
 
-def attention_cached(q, kc, vc, lens, scale, window=None, sinks=None, softcap=None):
+def attention_cached(q, kc, vc, lens, scale, window=None, sinks=None, softcap=None, select=None):
     """One query token per sequence against that sequence's cached keys. q [B, Hq, Dk]; kc / vc: lists of
     [n_b, Hkv, D] tensors (the first ``lens[b]`` positions, the query's own key included)."""
     outs = []
@@ -175,6 +179,8 @@ def attention_cached(q, kc, vc, lens, scale, window=None, sinks=None, softcap=No
         n = k.shape[0]
         lo = max(0, n - window) if window is not None else 0
         k, v = k[lo:], v[lo:]
+        if select is not None:                       # sparse attention: only the chosen cache positions
+            k, v = k[select[b]], v[select[b]]
         rep = Hq // k.shape[1]
         ks, vs = k.transpose(0, 1), v.transpose(0, 1)
         if rep > 1:
@@ -301,7 +307,7 @@ class FamilyModel:
         self._rope_cache: dict = {}
         self.recurrent_state: dict = {}       # sampler: per-sequence state of linear-attention layers, keyed by the first page
         # linear-attention state is per sequence and keyed by its first cache page: samples of one prompt must not share pages
-        self.has_recurrent_state = any(t == "linear_attention" for t in getattr(self.spec, "types", []))
+        self.has_recurrent_state = any(t == "linear_attention" for t in getattr(self.spec, "types", [])) or self.kind == "glm_moe_dsa"
 
     # ---- parameters
     def init_random(self, std: float = 0.02, seed: int = 0) -> None:
@@ -446,35 +452,36 @@ def cache_write(cache, l: int, k, v, ctx) -> None:
     bt, seq, pos = ctx["block_table"], ctx["tok_seq"], ctx["tok_pos"]
     page = bt[seq, pos // PAGE].long()
     slot = pos % PAGE
-    D = cache.k[l].shape[-1]
-    cache.k[l][page, :, slot, : k.shape[-1]] = k.to(cache.k[l].dtype)
-    cache.v[l][page, :, slot, : v.shape[-1]] = v.to(cache.v[l].dtype)
-    del D
+    cache.k[l][page, : k.shape[1], slot, : k.shape[-1]] = k.to(cache.k[l].dtype)
+    cache.v[l][page, : v.shape[1], slot, : v.shape[-1]] = v.to(cache.v[l].dtype)
 
 
-def cache_read(cache, l: int, ctx, dk: int, dv: int):
-    """Per sequence of a decode batch: (keys [n, Hkv, dk], values [n, Hkv, dv]) for the first ``seq_lens[b]`` positions."""
+def cache_read(cache, l: int, ctx, dk: int, dv: int, heads: int | None = None):
+    """Per sequence of a decode batch: (keys [n, heads, dk], values [n, heads, dv]) for the first ``seq_lens[b]`` positions."""
     bt, lens = ctx["block_table"], ctx["seq_lens"].tolist()
     ks, vs = [], []
+    hk = heads if heads is not None else cache.k[l].shape[1]
     for b, n in enumerate(lens):
         pages = bt[b, : (n + PAGE - 1) // PAGE].long()
-        k = cache.k[l][pages].permute(0, 2, 1, 3).reshape(-1, cache.k[l].shape[1], cache.k[l].shape[3])[:n, :, :dk]
-        v = cache.v[l][pages].permute(0, 2, 1, 3).reshape(-1, cache.v[l].shape[1], cache.v[l].shape[3])[:n, :, :dv]
+        k = cache.k[l][pages].permute(0, 2, 1, 3).reshape(-1, cache.k[l].shape[1], cache.k[l].shape[3])[:n, :hk, :dk]
+        v = cache.v[l][pages].permute(0, 2, 1, 3).reshape(-1, cache.v[l].shape[1], cache.v[l].shape[3])[:n, :hk, :dv]
         ks.append(k)
         vs.append(v)
     return ks, vs
 
 
-def attend(q, k, v, ctx, l: int, scale: float, window=None, sinks=None, softcap=None):
+def attend(q, k, v, ctx, l: int, scale: float, window=None, sinks=None, softcap=None, allowed=None, select=None,
+           write: bool = True):
     """Attention of a layer in whichever mode the context is in: packed training / prefill (writing the cache in
-    prefill) or single-token decode against the cache."""
+    prefill) or single-token decode against the cache. ``write = False``: the layer reuses keys / values that layer
+    ``l`` has already stored (layers that share another layer's keys and values)."""
     mode = ctx.get("mode")
-    if mode is not None:
+    if mode is not None and write:
         cache_write(ctx["cache"], l, k, v, ctx)
     if mode == "decode":
-        ks, vs = cache_read(ctx["cache"], l, ctx, k.shape[-1], v.shape[-1])
-        return attention_cached(q, ks, vs, ctx["seq_lens"], scale, window, sinks, softcap)
-    return attention_packed(q, k, v, ctx["cu"], scale, window, sinks, softcap)
+        ks, vs = cache_read(ctx["cache"], l, ctx, k.shape[-1], v.shape[-1], k.shape[1])
+        return attention_cached(q, ks, vs, ctx["seq_lens"], scale, window, sinks, softcap, select)
+    return attention_packed(q, k, v, ctx["cu"], scale, window, sinks, softcap, allowed)
 
 
 # ------------------------------------------------------------------------------------------ family specs
@@ -637,8 +644,13 @@ class _DeepseekV3(_Spec):
         k_rot = apply_rope(k_rot[:, None, :], cos, sin, self.interleave).expand(T, nh, self.d_rope)
         qf = torch.cat([q[..., : self.d_nope], q_rot], dim=-1)
         kf = torch.cat([k_nope, k_rot], dim=-1)
-        o = attend(qf, kf, v, ctx, l, self.scale)
+        sparse = self.select_keys(W, l, h, qa if self.q_lora else None, cos, sin, ctx)
+        o = attend(qf, kf, v, ctx, l, self.scale, **sparse)
         return linear(o.reshape(T, nh * self.d_v), self.P(W, l, "self_attn.o_proj.weight"))
+
+    def select_keys(self, W, l, h, q_resid, cos, sin, ctx) -> dict:
+        """Hook for sparse attention: keyword arguments for ``attend`` (none: every causal key is visible)."""
+        return {}
 
     def route(self, W, l, h):
         scores = F.linear(h.float(), self.P(W, l, "mlp.gate.weight").float()).sigmoid()
@@ -670,6 +682,74 @@ class _DeepseekV3(_Spec):
         x = x + self.attention(W, l, rms_norm(x, self.P(W, l, "input_layernorm.weight"), self.eps), ctx)
         h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps)
         return x + (self.moe(W, l, h) if self.is_moe(l) else self.swiglu(W, l, "mlp", h))
+
+
+class _GlmMoeDsa(_DeepseekV3):
+    """GLM-5 (DeepSeek-V3.2 style sparse attention): latent attention in which every query attends only to the
+    ``index_topk`` keys a light indexer ranks highest. The indexer has its own query heads (from the compressed query),
+    one shared key per token (LayerNorm, partly rotated) and per-head weights:
+    ``score[s, t] = sum_h w[s, h] * relu(q[s, h] . k[t]) * d^-1/2 * H^-1/2``; its choice is not differentiated."""
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        self.ih, self.idim, self.topk = hf["index_n_heads"], hf["index_head_dim"], hf["index_topk"]
+        self.interleave = bool(hf.get("rope_interleave", False))
+
+    def layer_layout(self, l):
+        lay = super().layer_layout(l)
+        out = OrderedDict()
+        for n, shp in lay.items():
+            out[n] = shp
+            if n == "self_attn.o_proj.weight":
+                out["self_attn.indexer.wq_b.weight"] = (self.ih * self.idim, self.q_lora)
+                out["self_attn.indexer.wk.weight"] = (self.idim, self.H)
+                out["self_attn.indexer.k_norm.weight"] = (self.idim,)
+                out["self_attn.indexer.k_norm.bias"] = (self.idim,)
+                out["self_attn.indexer.weights_proj.weight"] = (self.ih, self.H)
+        return out
+
+    def trainable(self, name):
+        return super().trainable(name) and ".indexer." not in name       # the selection carries no gradient
+
+    def init_kind(self, name):
+        return "ones" if name.endswith("indexer.k_norm.weight") else super().init_kind(name)
+
+    @torch.no_grad()
+    def select_keys(self, W, l, h, q_resid, cos, sin, ctx):
+        T = h.shape[0]
+        r = self.d_rope
+        q = F.linear(q_resid, self.P(W, l, "self_attn.indexer.wq_b.weight")).view(T, self.ih, self.idim)
+        q = torch.cat([apply_rope(q[..., :r], cos, sin), q[..., r:]], dim=-1)
+        k = F.layer_norm(F.linear(h, self.P(W, l, "self_attn.indexer.wk.weight")), (self.idim,),
+                         self.P(W, l, "self_attn.indexer.k_norm.weight"), self.P(W, l, "self_attn.indexer.k_norm.bias"), 1e-6)
+        k = torch.cat([apply_rope(k[:, None, :r], cos, sin)[:, 0], k[:, r:]], dim=-1)
+        w = F.linear(h, self.P(W, l, "self_attn.indexer.weights_proj.weight")).float() * (self.ih ** -0.5)
+        mode, model, cu = ctx.get("mode"), ctx["model"], ctx["cu"]
+        allowed, select = [], []
+        for s0, s1 in zip(cu[:-1], cu[1:]):
+            if s1 == s0:
+                continue
+            keys = k[s0:s1]
+            if mode is not None:
+                key = ("index", l, int(ctx["block_table"][int(ctx["tok_seq"][s0])][0]))
+                if mode == "decode":
+                    keys = torch.cat([model.recurrent_state[key], keys], dim=0)
+                model.recurrent_state[key] = keys
+            sc = torch.relu(torch.einsum("shd,td->sht", q[s0:s1].float(), keys.float()) * (self.idim ** -0.5))
+            score = torch.einsum("sht,sh->st", sc, w[s0:s1])
+            n_q, n_k = score.shape
+            if mode != "decode":
+                causal = torch.arange(n_k, device=h.device)[None, :] <= torch.arange(n_q, device=h.device)[:, None]
+                score = score.masked_fill(~causal, float("-inf"))
+            # exact ties (keys whose every head was cut to zero by the ReLU) go to the later position, so that a decode step
+            # and the full forward choose the same set whatever order the library's top-k visits equal values in
+            score = score.double() + torch.arange(n_k, device=h.device, dtype=torch.float64)[None, :] * 1e-15
+            top = score.topk(min(self.topk, n_k), dim=-1).indices
+            if mode == "decode":
+                select.append(top[0])
+            else:
+                allowed.append(torch.zeros(n_q, n_k, dtype=torch.bool, device=h.device).scatter_(1, top, True))
+        return {"select": select} if mode == "decode" else {"allowed": allowed}
 
 
 class _Glm4Moe(_DeepseekV3):
@@ -872,6 +952,162 @@ class _Gemma(_Spec):
         return x + n1(m, "post_feedforward_layernorm.weight")
 
 
+class _Gemma4(_Spec):
+    """Gemma-4 text: sliding-window layers with the local head size alternate with global layers that use a wider
+    head, their own number of KV heads, keys doubling as values (``attention_k_eq_v``) and a rope that turns only a
+    share of each head; queries and keys are RMS-normalised per head (weighted), values without weight, and the
+    softmax scale is 1. The last ``num_kv_shared_layers`` layers compute no keys / values of their own: each reuses
+    those of the last earlier layer of its type. Optional extras: a small per-layer token embedding mixed into every
+    layer through a gate, a sparse expert block in parallel with the dense MLP, a learned scalar per layer, and
+    soft-capped final logits."""
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        g = hf.get
+        self.nh, self.nkv = hf["num_attention_heads"], hf["num_key_value_heads"]
+        self.D, self.Dg = hf["head_dim"], g("global_head_dim") or hf["head_dim"]
+        self.k_eq_v = bool(g("attention_k_eq_v", False))
+        self.nkv_g = g("num_global_key_value_heads") or self.nkv
+        self.F = hf["intermediate_size"]
+        self.tied = bool(g("tie_word_embeddings", True))
+        self.window = g("sliding_window")
+        self.types = hf["layer_types"]
+        self.n_shared_kv = g("num_kv_shared_layers", 0) or 0
+        self.first_shared = self.L - self.n_shared_kv
+        self.double_wide = bool(g("use_double_wide_mlp", False))
+        self.Hp = g("hidden_size_per_layer_input", 0) or 0
+        self.Vp = g("vocab_size_per_layer_input") or self.V
+        self.moe_on = bool(g("enable_moe_block", False))
+        self.E, self.k, self.Fm = g("num_experts", 0) or 0, g("top_k_experts", 0) or 0, g("moe_intermediate_size", 0) or 0
+        self.final_softcap = g("final_logit_softcapping")
+        self.rope_by_type = hf["rope_parameters"]
+
+    def shared(self, l):
+        return self.n_shared_kv > 0 and l >= self.first_shared
+
+    def kv_source(self, l):
+        prev = self.types[: self.first_shared]
+        return len(prev) - 1 - prev[::-1].index(self.types[l])
+
+    def dims(self, l):
+        full = self.types[l] != "sliding_attention"
+        D = self.Dg if full else self.D
+        alt = self.k_eq_v and full
+        return D, (self.nkv_g if alt else self.nkv), alt
+
+    def layout(self):
+        lay = self.base_layout()
+        if self.Hp:
+            lay["model.embed_tokens_per_layer.weight"] = (self.Vp, self.L * self.Hp)
+            lay["model.per_layer_model_projection.weight"] = (self.L * self.Hp, self.H)
+            lay["model.per_layer_projection_norm.weight"] = (self.Hp,)
+        return lay
+
+    def buffers(self, device):
+        return {f"model.layers.{l}.layer_scalar": torch.ones(1, device=device) for l in range(self.L)}
+
+    def layer_layout(self, l):
+        H = self.H
+        D, nkv, alt = self.dims(l)
+        lay = OrderedDict()
+        lay["self_attn.q_norm.weight"] = (D,)
+        lay["self_attn.k_norm.weight"] = (D,)
+        lay["self_attn.k_proj.weight"] = (nkv * D, H)
+        lay["self_attn.q_proj.weight"] = (self.nh * D, H)
+        if not alt:
+            lay["self_attn.v_proj.weight"] = (nkv * D, H)
+        lay["self_attn.o_proj.weight"] = (H, self.nh * D)
+        Fl = self.F * (2 if (self.double_wide and self.shared(l)) else 1)
+        for n, shp in (("gate_proj", (Fl, H)), ("up_proj", (Fl, H)), ("down_proj", (H, Fl))):
+            lay[f"mlp.{n}.weight"] = shp
+        for n in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+            lay[f"{n}.weight"] = (H,)
+        if self.Hp:
+            lay["per_layer_input_gate.weight"] = (self.Hp, H)
+            lay["per_layer_projection.weight"] = (H, self.Hp)
+            lay["post_per_layer_input_norm.weight"] = (H,)
+        if self.moe_on:
+            lay["router.proj.weight"] = (self.E, H)
+            lay["router.scale"] = (H,)
+            lay["router.per_expert_scale"] = (self.E,)
+            lay["experts.gate_up_proj"] = (self.E, 2 * self.Fm, H)
+            lay["experts.down_proj"] = (self.E, H, self.Fm)
+            for n in ("post_feedforward_layernorm_1", "post_feedforward_layernorm_2", "pre_feedforward_layernorm_2"):
+                lay[f"{n}.weight"] = (H,)
+        return lay
+
+    def init_kind(self, name):
+        if name.endswith(("router.scale", "router.per_expert_scale")):
+            return "ones"
+        return super().init_kind(name)
+
+    def rope(self, which):
+        rp = dict(self.rope_by_type[which])
+        if rp.get("rope_type", "default") == "proportional":
+            hd = self.Dg
+            angles = int(rp.get("partial_rotary_factor", 1.0) * hd // 2)
+            inv = 1.0 / (float(rp["rope_theta"]) ** (torch.arange(0, 2 * angles, 2, dtype=torch.float64) / hd))
+            inv = torch.cat([inv, torch.zeros(hd // 2 - angles, dtype=torch.float64)]) / float(rp.get("factor", 1.0))
+            return inv.float(), 1.0
+        return rope_frequencies(rp, self.Dg if which == "full_attention" else self.D, self.hf.get("max_position_embeddings", 8192))
+
+    def embed(self, W, ids):
+        e = W["model.embed_tokens.weight"][ids]
+        x = e * torch.tensor(self.H ** 0.5, dtype=e.dtype)
+        self._per_layer = None
+        if self.Hp:
+            T = ids.shape[0]
+            pe = W["model.embed_tokens_per_layer.weight"][ids] * torch.tensor(self.Hp ** 0.5, dtype=e.dtype)
+            proj = linear(x, W["model.per_layer_model_projection.weight"]) * (self.H ** -0.5)
+            proj = rms_norm(proj.view(T, self.L, self.Hp), W["model.per_layer_projection_norm.weight"], self.eps)
+            self._per_layer = (proj + pe.view(T, self.L, self.Hp)) * (2.0 ** -0.5)
+        self._kv = {}
+        return x
+
+    def layer(self, W, l, x, ctx):
+        T = x.shape[0]
+        D, nkv, alt = self.dims(l)
+        N = lambda t, name: rms_norm(t, self.P(W, l, name), self.eps)      # noqa: E731
+        sliding = self.types[l] == "sliding_attention"
+        h = N(x, "input_layernorm.weight")
+        cos, sin = ctx["model"]._rope(self.types[l], ctx["positions"])
+        q = apply_rope(N(linear(h, self.P(W, l, "self_attn.q_proj.weight")).view(T, self.nh, D), "self_attn.q_norm.weight"), cos, sin)
+        if self.shared(l):
+            src = self.kv_source(l)
+            k, v = self._kv[src]
+            o = attend(q, k, v, ctx, src, 1.0, window=self.window if sliding else None, write=False)
+        else:
+            kr = linear(h, self.P(W, l, "self_attn.k_proj.weight")).view(T, nkv, D)
+            vr = kr if alt else linear(h, self.P(W, l, "self_attn.v_proj.weight")).view(T, nkv, D)
+            k = apply_rope(N(kr, "self_attn.k_norm.weight"), cos, sin)
+            v = rms_norm(vr, None, self.eps)
+            self._kv[l] = (k, v)
+            o = attend(q, k, v, ctx, l, 1.0, window=self.window if sliding else None)
+        x = x + N(linear(o.reshape(T, self.nh * D), self.P(W, l, "self_attn.o_proj.weight")), "post_attention_layernorm.weight")
+        res = x
+        h = N(x, "pre_feedforward_layernorm.weight")
+        g = linear(h, self.P(W, l, "mlp.gate_proj.weight"))
+        m = linear(F.gelu(g, approximate="tanh") * linear(h, self.P(W, l, "mlp.up_proj.weight")), self.P(W, l, "mlp.down_proj.weight"))
+        if self.moe_on:
+            m1 = N(m, "post_feedforward_layernorm_1.weight")
+            r = rms_norm(res, None, self.eps) * self.P(W, l, "router.scale") * (self.H ** -0.5)
+            probs = torch.softmax(F.linear(r, self.P(W, l, "router.proj.weight")), dim=-1)
+            wts, idx = probs.topk(self.k, dim=-1)
+            wts = wts / wts.sum(-1, keepdim=True) * self.P(W, l, "router.per_expert_scale")[idx]
+            gu, dn = self.P(W, l, "experts.gate_up_proj"), self.P(W, l, "experts.down_proj")
+
+            def expert(e, rows):
+                a, b = F.linear(rows, gu[e]).chunk(2, dim=-1)
+                return F.linear(F.gelu(a, approximate="tanh") * b, dn[e])
+            m2 = experts_forward(N(res, "pre_feedforward_layernorm_2.weight"), idx, wts, expert, self.E)
+            m = m1 + N(m2, "post_feedforward_layernorm_2.weight")
+        x = res + N(m, "post_feedforward_layernorm.weight")
+        if self.Hp:
+            gate = F.gelu(linear(x, self.P(W, l, "per_layer_input_gate.weight")), approximate="tanh") * self._per_layer[:, l]
+            x = x + N(linear(gate, self.P(W, l, "per_layer_projection.weight")), "post_per_layer_input_norm.weight")
+        return x * ctx["model"].buffers[f"model.layers.{l}.layer_scalar"].to(x.dtype)
+
+
 class _Qwen3Next(_Spec):
     """Qwen3-Next / Qwen3.5: three of four layers mix tokens with a gated delta-rule linear attention (short causal
     convolution over q | k | v, L2-normalised keys and queries, per-head decay and write strength, gated RMSNorm on
@@ -960,7 +1196,8 @@ class _Qwen3Next(_Spec):
         o = attend(q, k, v, ctx, l, self.scale).reshape(T, self.nh * self.D)
         return linear(o * torch.sigmoid(gate), self.P(W, l, "self_attn.o_proj.weight"))
 
-    def linear_attention(self, W, l, h, ctx):
+    def project_linear(self, W, l, h):
+        """(q | k | v rows [T, C], z [T, nv, dv], b [T, nv], a [T, nv]) from the fused, key-head-grouped projections."""
         T = h.shape[0]
         nk, nv, dk, dv = self.nk, self.nv, self.dk, self.dv
         r = nv // nk
@@ -968,8 +1205,14 @@ class _Qwen3Next(_Spec):
         ba = linear(h, self.P(W, l, "linear_attn.in_proj_ba.weight")).view(T, nk, 2 * r)
         q, k, v, z = torch.split(qkvz, [dk, dk, r * dv, r * dv], dim=-1)
         b, a = ba[..., :r].reshape(T, nv), ba[..., r:].reshape(T, nv)
-        v, z = v.reshape(T, nv, dv), z.reshape(T, nv, dv)
-        mixed = torch.cat([q.reshape(T, nk * dk), k.reshape(T, nk * dk), v.reshape(T, nv * dv)], dim=-1)      # [T, C]
+        mixed = torch.cat([q.reshape(T, nk * dk), k.reshape(T, nk * dk), v.reshape(T, nv * dv)], dim=-1)
+        return mixed, z.reshape(T, nv, dv), b, a
+
+    def linear_attention(self, W, l, h, ctx):
+        T = h.shape[0]
+        nk, nv, dk, dv = self.nk, self.nv, self.dk, self.dv
+        r = nv // nk
+        mixed, z, b, a = self.project_linear(W, l, h)                                                         # mixed [T, C]
         wconv = self.P(W, l, "linear_attn.conv1d.weight")[:, 0, :]                                            # [C, K]
         K = self.conv_k
         mode, model = ctx.get("mode"), ctx["model"]
@@ -1028,8 +1271,35 @@ class _Qwen3Next(_Spec):
         return x + (self.moe(W, l, h) if self.is_moe(l) else self.swiglu(W, l, "mlp", h))
 
 
-_SPECS = {"deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
-          "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen3Next}
+class _Qwen35(_Qwen3Next):
+    """Qwen3.5 text models: the Qwen3-Next layer with separate, ungrouped q|k|v, z, b and a projections."""
+
+    def layer_layout(self, l):
+        lay = super().layer_layout(l)
+        if self.types[l] != "linear_attention":
+            return lay
+        kd, vd = self.nk * self.dk, self.nv * self.dv
+        out = OrderedDict()
+        for n, shp in lay.items():
+            if n == "linear_attn.in_proj_qkvz.weight":
+                out["linear_attn.in_proj_qkv.weight"] = (2 * kd + vd, self.H)
+                out["linear_attn.in_proj_z.weight"] = (vd, self.H)
+            elif n == "linear_attn.in_proj_ba.weight":
+                out["linear_attn.in_proj_b.weight"] = (self.nv, self.H)
+                out["linear_attn.in_proj_a.weight"] = (self.nv, self.H)
+            else:
+                out[n] = shp
+        return out
+
+    def project_linear(self, W, l, h):
+        T = h.shape[0]
+        mixed = linear(h, self.P(W, l, "linear_attn.in_proj_qkv.weight"))
+        z = linear(h, self.P(W, l, "linear_attn.in_proj_z.weight")).view(T, self.nv, self.dv)
+        return mixed, z, F.linear(h, self.P(W, l, "linear_attn.in_proj_b.weight")), F.linear(h, self.P(W, l, "linear_attn.in_proj_a.weight"))
+
+
+_SPECS = {"deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
+          "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen35, "qwen3_5_moe_text": _Qwen35}
 
 
 # ------------------------------------------------------------------------------------------ construction
@@ -1038,9 +1308,12 @@ def family_config(hf: dict) -> ModelConfig:
     special tokens); everything else stays in ``extra['hf_config']`` for the family's spec."""
     mt = hf["model_type"]
     nh = hf["num_attention_heads"]
-    if mt in ("deepseek_v3", "glm4_moe_lite"):
+    if mt in ("deepseek_v3", "glm4_moe_lite", "glm_moe_dsa"):
         # the paged cache holds expanded keys (nope + rope) and values per head
         nkv, hd = nh, max(hf["qk_nope_head_dim"] + hf["qk_rope_head_dim"], hf["v_head_dim"])
+    elif mt == "gemma4_text":            # the pool is sized for the wider of the two layer kinds
+        nkv = max(hf.get("num_key_value_heads", nh), hf.get("num_global_key_value_heads") or 0)
+        hd = max(hf["head_dim"], hf.get("global_head_dim") or 0)
     else:
         nkv = hf.get("num_key_value_heads", nh)
         hd = hf.get("head_dim") or hf["hidden_size"] // nh

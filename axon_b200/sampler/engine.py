@@ -13,6 +13,7 @@ trainer, so sampler and trainer log-probs agree by construction.
 from __future__ import annotations
 
 import itertools
+import time
 from collections import deque
 from dataclasses import dataclass, field
 
@@ -335,6 +336,7 @@ class GenerationEngine:
         return out
 
     def _decode_graph(self, seqs) -> tuple[list, list]:
+        t_host0 = time.perf_counter()
         B = len(seqs)
         bucket = next((b for b in self.graph_buckets if b >= B), None)
         if bucket is None:
@@ -371,6 +373,9 @@ class GenerationEngine:
         g["graph"].replay()
         from ..ops import _common as C
         C.LAUNCH_COUNT += g["launches"]
+        # the device is idle while the host fills the step's inputs (the previous step ended with a sync): that time is
+        # what overlapping the scheduler with the device would win back
+        self.stats["decode_host_prep_s"] = self.stats.get("decode_host_prep_s", 0.0) + (time.perf_counter() - t_host0)
         if self.capture_routing and g.get("routing") is not None:
             rt_h = g["routing"][:B].cpu().numpy()
             for i, s in enumerate(seqs):

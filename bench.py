@@ -296,7 +296,8 @@ def main() -> None:
                 "phase_seconds_per_step": {kk: v / k for kk, v in phase.items()},
                 "last_step": {kk: last.get(kk) for kk in ("loss", "grad_norm", "sampler_probs_diff_mean", "entropy")},
                 "peak_mem_gib": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
-                "runner": {kk: runner.phase_detail.get(kk) for kk in ("kv_pages", "kv_peak_pages", "offloaded", "recompute", "preempted")},
+                "runner": {kk: runner.phase_detail.get(kk) for kk in ("kv_pages", "kv_peak_pages", "offloaded", "recompute", "preempted", "decode_steps",
+                                                                            "decode_host_prep_s")},
                 "multi_gpu_checks": checks,
                 "wall_s_since_start": time.time() - T_PROCESS_START,
             }

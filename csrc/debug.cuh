@@ -29,7 +29,7 @@ static int read_and_clear(int* out4) {
 
 namespace {
 struct Registrar {
-  Registrar() { register_reader(&read_and_clear, __FILE__); }
+  Registrar() { register_reader(&read_and_clear, __BASE_FILE__); }   // the unit being compiled, not this header
 };
 static Registrar registrar;
 }  // namespace

@@ -52,6 +52,37 @@ HF = {
                        norm_topk_prob=True, rms_norm_eps=1e-6, max_position_embeddings=256, tie_word_embeddings=False,
                        rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25},
                        layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"]),
+    "qwen3_5_text": dict(model_type="qwen3_5_text", vocab_size=160, hidden_size=64, num_hidden_layers=4, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=16, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8,
+                         linear_value_head_dim=8, linear_conv_kernel_dim=4, intermediate_size=96, rms_norm_eps=1e-6,
+                         max_position_embeddings=256, tie_word_embeddings=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25,
+                                          "mrope_section": [1, 1, 0], "mrope_interleaved": True},
+                         layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"]),
+    "gemma4_text": dict(model_type="gemma4_text", vocab_size=160, hidden_size=64, num_hidden_layers=6, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=16, global_head_dim=32, intermediate_size=96, sliding_window=8,
+                        hidden_size_per_layer_input=8, vocab_size_per_layer_input=160, num_kv_shared_layers=2, attention_k_eq_v=True,
+                        num_global_key_value_heads=1, enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32,
+                        max_position_embeddings=256, use_double_wide_mlp=True, final_logit_softcapping=12.0, rms_norm_eps=1e-6,
+                        tie_word_embeddings=True,
+                        layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention", "sliding_attention",
+                                     "full_attention"],
+                        rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                                         "full_attention": {"rope_type": "proportional", "partial_rotary_factor": 0.25,
+                                                            "rope_theta": 1000000.0}}),
+    "glm_moe_dsa": dict(model_type="glm_moe_dsa", vocab_size=160, hidden_size=64, num_hidden_layers=3, num_attention_heads=4,
+                        num_key_value_heads=4, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                        n_routed_experts=8, num_experts_per_tok=2, n_group=1, topk_group=1, first_k_dense_replace=1,
+                        moe_intermediate_size=32, intermediate_size=96, n_shared_experts=1, routed_scaling_factor=1.5,
+                        norm_topk_prob=True, rms_norm_eps=1e-5, max_position_embeddings=256, index_n_heads=8, index_head_dim=16,
+                        index_topk=6, rope_parameters={"rope_type": "default", "rope_theta": 10000.0}, tie_word_embeddings=False,
+                        mlp_layer_types=["dense", "sparse", "sparse"]),
+    "glm4_moe_lite": dict(model_type="glm4_moe_lite", vocab_size=160, hidden_size=64, num_hidden_layers=3, num_attention_heads=4,
+                          num_key_value_heads=4, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                          n_routed_experts=8, num_experts_per_tok=2, n_group=1, topk_group=1, first_k_dense_replace=1,
+                          moe_intermediate_size=32, intermediate_size=96, n_shared_experts=1, routed_scaling_factor=1.8,
+                          norm_topk_prob=True, rms_norm_eps=1e-5, max_position_embeddings=256,
+                          rope_parameters={"rope_type": "default", "rope_theta": 10000.0}, tie_word_embeddings=False),
 }
 
 
@@ -69,11 +100,13 @@ def _hf_model(name):
             if p.dim() >= 2 or n.endswith(("bias", "sinks", "dt_bias", "A_log")):
                 p.copy_(torch.randn(p.shape, generator=g) * (0.08 if p.dim() >= 2 else 0.3))
             else:
-                p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=g) if "norm" in n and mt not in ("gemma2", "gemma3_text", "qwen3_next")
+                p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=g) if "norm" in n and mt not in ("gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text")
                         else 0.1 * torch.randn(p.shape, generator=g))
         for n, b in model.named_buffers():
             if n.endswith("e_score_correction_bias"):
                 b.copy_(0.1 * torch.randn(b.shape, generator=g))
+            if n.endswith("layer_scalar"):
+                b.copy_(1.0 + 0.2 * torch.randn(b.shape, generator=g))
         if "A_log" in dict(model.named_parameters()).keys().__str__():
             for n, p in model.named_parameters():
                 if n.endswith("A_log"):
@@ -102,7 +135,7 @@ def test_logits_match_transformers(name):
     assert (got - ref).abs().max() < 2e-4 * max(1.0, ref.abs().max().item()), (got - ref).abs().max()
 
 
-@pytest.mark.parametrize("name", ["deepseek_v3", "gpt_oss", "gemma2", "qwen3_next", "glm4_moe"])
+@pytest.mark.parametrize("name", ["deepseek_v3", "gpt_oss", "gemma2", "qwen3_next", "glm4_moe", "gemma4_text"])
 def test_gradients_match_transformers(name):
     from axon_b200.models.dense import PackedBatch
     try:
@@ -140,7 +173,7 @@ def test_gradients_match_transformers(name):
         assert checked >= 10
 
 
-@pytest.mark.parametrize("name", ["deepseek_v3", "gpt_oss", "gemma3_text", "qwen3_next"])
+@pytest.mark.parametrize("name", ["deepseek_v3", "gpt_oss", "gemma3_text", "qwen3_next", "glm_moe_dsa", "gemma4_text"])
 def test_sampler_path_matches_full_forward(name):
     """Prefill a prompt into the paged cache, decode three tokens one at a time: every step's logits equal the logits
     of the full forward over the tokens so far."""
