@@ -49,6 +49,29 @@ class PackedBatch:
         return PackedBatch(ids.to(device), pos.to(device), cu.to(device), labels.to(device), max(lens))
 
 
+def _cached_prefill_plan(batch: "PackedBatch", past_lens, block_table, tok_seq, device) -> dict:
+    """Index tensors for attention over [cached prefix | new tokens] of every sequence: where the new rows and the
+    prefix rows sit in the packed full-length row set, and which (page, slot) of the cache each prefix row comes from."""
+    import numpy as np
+    cu = batch.cu_seqlens.tolist()
+    rows_of = tok_seq[torch.tensor(cu[:-1], dtype=torch.long, device=tok_seq.device)].tolist() if len(cu) > 1 else []
+    bt = block_table.cpu().numpy()
+    new_rows, pre_rows, pre_page, pre_slot, cu_full = [], [], [], [], [0]
+    off = 0
+    for i, past in enumerate(int(p) for p in past_lens):
+        n_new = cu[i + 1] - cu[i]
+        pre_rows.append(np.arange(off, off + past))
+        pos = np.arange(past)
+        pre_page.append(bt[rows_of[i], pos // 128])
+        pre_slot.append(pos % 128)
+        new_rows.append(np.arange(off + past, off + past + n_new))
+        off += past + n_new
+        cu_full.append(off)
+    t = lambda a, dt=torch.long: torch.from_numpy(np.concatenate(a).astype(np.int64)).to(device=device, dtype=dt)      # noqa: E731
+    return dict(T_full=off, new_rows=t(new_rows), pre_rows=t(pre_rows), pre_page=t(pre_page), pre_slot=t(pre_slot),
+                cu_full=torch.tensor(cu_full, dtype=torch.int32, device=device))
+
+
 class DenseModel:
     def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params: FlatParams | None = None):
         assert cfg.num_experts == 0 or type(self) is not DenseModel, "use MoEModel for sparse configs"
@@ -352,13 +375,27 @@ class _DenseInference:
     """Mixed into DenseModel: prefill over packed prompts and single-token decode against a paged
     KV cache. Both write rotated K / V into the cache and return fp32 logits for sampling."""
 
-    def prefill(self, batch: PackedBatch, cache, tok_seq, tok_pos, block_table, last_index):
-        """batch: packed prompts (whole sequences, no cached prefix). tok_seq/tok_pos: per packed token
-        cache row and position. last_index: int64 [B] packed index of each prompt's last token.
-        Returns fp32 logits [B, V] of the next token."""
+    supports_cached_prefill = True
+
+    def prefill(self, batch: PackedBatch, cache, tok_seq, tok_pos, block_table, last_index, past_lens=None):
+        """batch: packed NEW tokens of every sequence (``position_ids`` are their positions in the sequence).
+        tok_seq/tok_pos: per packed token cache row and position. last_index: int64 [B'] packed indices whose
+        next-token logits are wanted. ``past_lens`` (python ints, one per sequence): tokens of the sequence whose keys
+        and values are already in its cache pages (a prefix shared with an earlier request, or earlier chunks of a long
+        prompt). Returns fp32 logits [B', V].
+
+        With a cached prefix the new tokens' linear layers run on the new tokens only; for attention the prefix keys
+        and values are gathered from the pages into a packed [prefix | new] row set and the packed causal kernel runs
+        over it (its outputs at the new rows are kept). That reads every cached key once per layer, as a decode step
+        would, and needs no attention kernel with separate query and key lengths."""
         from ..ops import paged as P
         c = self.cfg
-        tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        plan = None
+        if past_lens is not None and any(int(p) > 0 for p in past_lens):
+            plan = _cached_prefill_plan(batch, past_lens, block_table, tok_seq, self.device)
+        max_pos = int(batch.position_ids.max().item()) + 1 if plan is not None else (int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
+        tables = self._tables(max_pos)
         x = A.embedding_fwd(batch.input_ids, self.weights["model.embed_tokens.weight"])
         delta = None
         for l in range(c.num_hidden_layers):
@@ -367,16 +404,21 @@ class _DenseInference:
             h, _, xin = N.rmsnorm_fwd(x, self._p(l, "input_layernorm.weight"), c.rms_norm_eps, delta=delta)
             qkv = self._lin(l, "self_attn.qkv_proj.weight", h)
             if tok_pos is batch.position_ids:      # the usual case: cache positions are the RoPE positions - one launch
-                qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
-                                          c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps,
+                qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], Hq, Hkv, D, qw, kw, c.rms_norm_eps,
                                           kv_cache=(cache.k[l], cache.v[l], tok_seq, block_table))
             else:
-                qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], c.num_attention_heads,
-                                          c.num_key_value_heads, c.head_dim, qw, kw, c.rms_norm_eps)
-                P.kv_write(qkv_r, cache.k[l], cache.v[l], tok_seq, tok_pos, block_table, c.num_attention_heads,
-                           c.num_key_value_heads, c.head_dim)
-            o, _ = AT.attn_fwd(qkv_r, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-                               need_lse=False)
+                qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], Hq, Hkv, D, qw, kw, c.rms_norm_eps)
+                P.kv_write(qkv_r, cache.k[l], cache.v[l], tok_seq, tok_pos, block_table, Hq, Hkv, D)
+            if plan is None:
+                o, _ = AT.attn_fwd(qkv_r, batch.cu_seqlens, Hq, Hkv, D, need_lse=False)
+            else:
+                full = torch.zeros(plan["T_full"], (Hq + 2 * Hkv) * D, dtype=qkv_r.dtype, device=qkv_r.device)
+                full[plan["new_rows"]] = qkv_r
+                kv = full.view(plan["T_full"], Hq + 2 * Hkv, D)
+                kv[plan["pre_rows"], Hq:Hq + Hkv] = cache.k[l][plan["pre_page"], :, plan["pre_slot"]]
+                kv[plan["pre_rows"], Hq + Hkv:] = cache.v[l][plan["pre_page"], :, plan["pre_slot"]]
+                o_full, _ = AT.attn_fwd(full, plan["cu_full"], Hq, Hkv, D, need_lse=False)
+                o = o_full[plan["new_rows"]].contiguous()
             ao = self._post_norm(l, "post_self_attn_layernorm.weight", self._lin(l, "self_attn.o_proj.weight", o))
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
             delta = self._post_norm(l, "post_mlp_layernorm.weight", self.mlp_infer(l, h2))
@@ -420,4 +462,5 @@ class _DenseInference:
 
 
 DenseModel.prefill = _DenseInference.prefill
+DenseModel.supports_cached_prefill = True
 DenseModel.decode = _DenseInference.decode

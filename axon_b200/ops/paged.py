@@ -8,12 +8,57 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
 from . import _common as C
 
 PAGE = 128
+# Decode attention kernels: "classic" launches one CTA per (sequence or group, kv head, key split); "persistent" runs
+# one CTA per SM that pulls those work units from a counter and keeps its tile pipeline running across them
+# (csrc/paged_attention_persist.cu). Same arguments, same results.
+DECODE_IMPL = os.environ.get("AXON_PAGED_DECODE", "classic")
+_PLAIN_ITEMS: dict = {}
+
+
+def _plain_items(B: int, device) -> dict:
+    """Item arrays that describe a batch without shared prefixes: one item per sequence over all of its pages."""
+    key = (B, str(device))
+    it = _PLAIN_ITEMS.get(key)
+    if it is None:
+        z = torch.zeros(B, dtype=torch.int32, device=device)
+        it = _PLAIN_ITEMS[key] = dict(seq_first=torch.arange(B, dtype=torch.int32, device=device),
+                                      seq_one=torch.ones(B, dtype=torch.int32, device=device), seq_page0=z, zero=z)
+    return it
+
+
+def _decode_persistent(qkv_r, kcache, vcache, block_table, seq_lens, shared, Hq, Hkv, D, scale):
+    lib = C.lib()
+    B = qkv_r.shape[0]
+    max_pages = block_table.shape[1]
+    ns = lib.axb_paged_decode_splits(B, Hkv, max_pages)
+    if shared is None:
+        it = _plain_items(B, qkv_r.device)
+        first, one, page0, keys = it["seq_first"], it["seq_one"], it["seq_page0"], seq_lens
+        gf = gs = gz = gk = it["zero"]
+        n_groups, nsp = 0, 1
+    else:
+        first, one, page0, keys = shared["seq_first"], shared["seq_one"], shared["seq_page0"], shared["seq_keys"]
+        gf, gs, gz, gk = shared["grp_first"], shared["grp_size"], shared["grp_zero"], shared["grp_keys"]
+        n_groups = gf.numel()
+        nsp = lib.axb_paged_decode_splits(int(shared.get("typical_groups", max(1, B // 8))), Hkv, int(shared.get("max_shared_pages", 8)))
+    nslots = ns if n_groups == 0 else ns + nsp
+    scratch = C.workspace(qkv_r.device, B * Hq * nslots * (D + 2) * 4, "paged")
+    counters = C.workspace(qkv_r.device, 64, "paged_counters")
+    out = torch.empty(B, Hq * D, dtype=qkv_r.dtype, device=qkv_r.device)
+    rc = lib.axb_paged_decode_shared_persist(C.ptr(qkv_r), ctypes.c_longlong(qkv_r.stride(0)), C.ptr(kcache), C.ptr(vcache),
+                                             kcache.shape[0], C.ptr(block_table), max_pages, C.ptr(first), C.ptr(one), C.ptr(page0),
+                                             C.ptr(keys), C.ptr(gf), C.ptr(gs), C.ptr(gz), C.ptr(gk), n_groups, C.ptr(out), B, Hq, Hkv,
+                                             D, ctypes.c_float(scale), ns, nsp, C.ptr(scratch), C.ptr(counters),
+                                             C.ptr(C.status(qkv_r.device)), C.stream())
+    C.launched(rc, "paged_decode_persist", 1 if (n_groups == 0 and ns == 1) else (2 if n_groups == 0 else 3))
+    return out
 
 
 def kv_write(qkv_r, kcache, vcache, tok_seq, tok_pos, block_table, Hq, Hkv, D):
@@ -54,6 +99,8 @@ def paged_decode(qkv_r, kcache, vcache, block_table, seq_lens, Hq, Hkv, D, scale
             s = torch.einsum("hd,hnd->hn", q[b], k) * scale
             out[b] = torch.einsum("hn,hnd->hd", s.softmax(-1), v)
         return out.reshape(B, Hq * D).to(qkv_r.dtype)
+    if DECODE_IMPL == "persistent":
+        return _decode_persistent(qkv_r, kcache, vcache, block_table, seq_lens, None, Hq, Hkv, D, scale)
     lib = C.lib()
     max_pages = block_table.shape[1]
     ns = lib.axb_paged_decode_splits(B, Hkv, max_pages)
@@ -78,6 +125,8 @@ def paged_decode_shared(qkv_r, kcache, vcache, block_table, seq_lens, shared: di
         return paged_decode(qkv_r, kcache, vcache, block_table, seq_lens, Hq, Hkv, D, scale)
     B = qkv_r.shape[0]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if DECODE_IMPL == "persistent":
+        return _decode_persistent(qkv_r, kcache, vcache, block_table, seq_lens, shared, Hq, Hkv, D, scale)
     lib = C.lib()
     max_pages = block_table.shape[1]
     n_groups = shared["grp_first"].numel()

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import itertools
 import time
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -38,6 +38,8 @@ class _Seq:
     leader: object = None      # during admission: the sequence whose prompt pages and prefill this one reuses
     share_key: int = -1        # rid of the sequence whose prompt pages this one shares (its own rid for that sequence)
     shared_pages: int = 0      # number of leading pages shared with the group
+    cached: int = 0            # leading tokens whose keys / values are already in the pages (prefix cache hit, earlier chunks)
+    chunk_end: int = 0         # the prefill call in progress covers tokens [cached, chunk_end)
     route_chunks: list = field(default_factory=list)    # routed-experts capture: int16 [n, layers, top-k] pieces in token order
 
 
@@ -77,6 +79,17 @@ class GenerationEngine:
         # token, which never went through the model, is -1 (reference: the vLLM fork's routed_experts output,
         # install/vllm/axon.patch:586-748, consumed at axon/engine/engine.py:1157-1175). The trainer replays it.
         self.capture_routing = False
+        # Prefix caching across requests: full pages of finished or prefilled sequences stay in the pool under a hash of
+        # the tokens they hold (chained page by page); a new request whose prompt starts with the same tokens shares
+        # those pages and prefills only the rest. The cache holds one reference per page and gives pages back, least
+        # recently used first, when the pool runs short. Chunked prefill: a prompt longer than ``max_num_batched_tokens``
+        # is prefilled in pieces, later pieces attending to the cached keys of the earlier ones.
+        self.enable_prefix_caching = False
+        self.enable_chunked_prefill = True
+        self._cached_ok = bool(getattr(model, "supports_cached_prefill", False))
+        self._prefix_pages: "OrderedDict[int, int]" = OrderedDict()      # chain hash -> page
+        self._page_hash: dict[int, int] = {}
+        self.prefilling: list[_Seq] = []       # sequences whose prompt is partly prefilled (chunked)
         # Decode attention over the shared pages once per group (csrc/paged_attention_shared.cu). Off by default: with
         # one CTA per SM the per-CTA start-up of the extra prefix / suffix items costs as much as the shared tiles
         # save once responses are a few pages long (measured end to end); the kernel pays off for long shared
@@ -98,7 +111,7 @@ class GenerationEngine:
         return rid
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self.prefilling)
 
     def generate(self, prompts, params) -> list[TokenOutput]:
         """Blocking helper: run all prompts to completion; ``params`` is one SamplingParams or a list."""
@@ -132,6 +145,10 @@ class GenerationEngine:
         for s in self.running:
             self._finish(s, "abort")
         self.running = []
+        for s in self.prefilling:
+            self._finish(s, "abort")
+        self.prefilling = []
+        self.reset_prefix_cache()
         if self.cache is not None:
             self.cache.drop()
         self.cache = None
@@ -152,16 +169,78 @@ class GenerationEngine:
         s.out.stop_reason = stop
         if self.capture_routing:
             s.out.moe_routermap = self._routermap(s)
+        if self.enable_prefix_caching and self.cache is not None and s.pages and s.length > 0:
+            # the keys / values of the first ``length`` tokens are in the pages: later turns that extend this text reuse them
+            self._register_prefix(s.prompt + s.out.token_ids, s.pages, s.length)
         if self.cache is not None:
             self.cache.release(s.pages)
         s.pages = []
         self.finished[s.rid] = s.out
 
+    # ------------------------------------------------------------------ prefix cache
+    @staticmethod
+    def _chain(tokens: list, n_pages: int) -> list[int]:
+        keys, h = [], 0
+        for k in range(n_pages):
+            h = hash((h, tuple(tokens[k * PAGE:(k + 1) * PAGE])))
+            keys.append(h)
+        return keys
+
+    def reset_prefix_cache(self) -> None:
+        """Forget every cached prefix (the weights changed, or the pool is being dropped)."""
+        if self.cache is not None and self.cache.k:
+            self.cache.release(list(self._prefix_pages.values()))
+        self._prefix_pages.clear()
+        self._page_hash.clear()
+
+    def _lookup_prefix(self, tokens: list) -> list[int]:
+        """Pages holding the longest cached prefix of ``tokens`` that leaves at least one token to compute."""
+        pages = []
+        for key in self._chain(tokens, (len(tokens) - 1) // PAGE):
+            pg = self._prefix_pages.get(key)
+            if pg is None:
+                break
+            self._prefix_pages.move_to_end(key)
+            pages.append(pg)
+        return pages
+
+    def _register_prefix(self, tokens: list, pages: list[int], n_tokens: int) -> None:
+        """Keep the full pages among the first ``n_tokens`` tokens of a sequence findable for later requests."""
+        if not self.enable_prefix_caching or not self._cached_ok:
+            return
+        for k, key in enumerate(self._chain(tokens, n_tokens // PAGE)):
+            if key in self._prefix_pages:
+                self._prefix_pages.move_to_end(key)
+                continue
+            if pages[k] in self._page_hash:
+                continue
+            self.cache.share([pages[k]])
+            self._prefix_pages[key] = pages[k]
+            self._page_hash[pages[k]] = key
+
+    def _evict_prefixes(self, need: int) -> None:
+        """Give back cached pages nobody else holds, oldest first, until ``need`` pages are free."""
+        for key in list(self._prefix_pages):
+            if self.cache.num_free() >= need:
+                break
+            pg = self._prefix_pages[key]
+            if self.cache.ref[pg] == 1:
+                del self._prefix_pages[key]
+                del self._page_hash[pg]
+                self.cache.release([pg])
+
     def _admit(self) -> list[_Seq]:
         """Pick waiting sequences that fit the page pool and the token budget. Fresh sequences with the
         same prompt as an earlier one of the batch (n samples per prompt) become its followers: they
-        share the prompt's full pages and are not prefilled again."""
+        share the prompt's full pages and are not prefilled again. With prefix caching a fresh sequence also
+        shares the pages of the longest cached prefix of its prompt. A prompt longer than the token budget is
+        admitted alone and prefilled in chunks over several steps."""
         batch, tokens = [], 0
+        budget = self.max_num_batched_tokens
+        if self.prefilling:                      # the next chunk of a partly prefilled prompt goes first, on its own
+            s = self.prefilling.pop(0)
+            s.chunk_end = min(len(s.prompt) + len(s.out.token_ids), s.cached + budget)
+            return [s]
         leaders: dict[tuple, _Seq] = {}
         while self.waiting and len(self.running) + len(batch) < self.max_num_seqs:
             s = self.waiting[0]
@@ -169,11 +248,21 @@ class GenerationEngine:
             need = (n + 1 + PAGE - 1) // PAGE
             key = tuple(s.prompt) if (self.share_prompts and not s.out.token_ids) else None
             lead = leaders.get(key) if key is not None else None
-            shared = (len(s.prompt) // PAGE) if lead is not None else 0
+            held: list[int] = []
+            if lead is None and self.enable_prefix_caching and self._cached_ok and not s.out.token_ids:
+                held = self.cache.share(self._lookup_prefix(s.prompt))       # hold the hit before anything is evicted
+            shared = (len(s.prompt) // PAGE) if lead is not None else len(held)
             # keep one page of head-room per running sequence so decode can always advance
-            if need - shared > self.cache.num_free() - len(self.running) - len(batch):
+            reserve = len(self.running) + len(batch)
+            if need - shared > self.cache.num_free() - reserve and self._prefix_pages:
+                self._evict_prefixes(need - shared + reserve)
+            if need - shared > self.cache.num_free() - reserve:
+                self.cache.release(held)
                 break
-            if lead is None and batch and tokens + n > self.max_num_batched_tokens:
+            fresh = n - shared * PAGE if lead is None else 0
+            chunked = lead is None and fresh > budget and self.enable_chunked_prefill and self._cached_ok
+            if lead is None and batch and (tokens + fresh > budget or chunked):
+                self.cache.release(held)
                 break
             self.waiting.popleft()
             if lead is not None:
@@ -182,13 +271,19 @@ class GenerationEngine:
                 s.share_key, s.shared_pages = lead.rid, shared
                 lead.share_key, lead.shared_pages = lead.rid, shared
             else:
-                s.pages = self.cache.alloc(need)
+                s.pages = held + self.cache.alloc(need - shared)
                 s.leader = None
                 s.share_key, s.shared_pages = -1, 0
-                tokens += n
-                if key is not None:
+                s.cached = shared * PAGE
+                s.chunk_end = s.cached + budget if chunked else n
+                if held:
+                    self.stats["prefix_cache_hit_tokens"] = self.stats.get("prefix_cache_hit_tokens", 0) + s.cached
+                tokens += s.chunk_end - s.cached
+                if key is not None and not chunked:
                     leaders[key] = s
             batch.append(s)
+            if chunked:
+                break
         return batch
 
     def _block_table(self, seqs) -> torch.Tensor:
@@ -223,25 +318,52 @@ class GenerationEngine:
 
     def _prefill(self, all_seqs) -> None:
         seqs = [s for s in all_seqs if getattr(s, "leader", None) is None]     # followers reuse their leader's prefill
-        toks = [torch.tensor(s.prompt + s.out.token_ids, dtype=torch.int32) for s in seqs]
+        full = [s.prompt + s.out.token_ids for s in seqs]
+        for s, f in zip(seqs, full):
+            if s.chunk_end <= s.cached:                # sequences admitted before these fields existed, or re-admitted
+                s.cached, s.chunk_end = 0, len(f)
+        past = [s.cached for s in seqs]
+        toks = [torch.tensor(f[s.cached:s.chunk_end], dtype=torch.int32) for s, f in zip(seqs, full)]
         batch = PackedBatch.from_sequences(toks, self.device)
         lens = [int(t.numel()) for t in toks]
+        if any(past):
+            batch.position_ids = batch.position_ids + torch.cat(
+                [torch.full((n,), p, dtype=torch.int32) for n, p in zip(lens, past)]).to(self.device)
+            batch.max_seqlen = max(p + n for p, n in zip(past, lens))
         tok_seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(lens)]).to(self.device)
-        last = (torch.tensor(lens).cumsum(0) - 1).to(self.device)
+        ends = torch.tensor(lens).cumsum(0) - 1
+        complete = [s.chunk_end >= len(f) for s, f in zip(seqs, full)]
+        last = ends[torch.tensor(complete)].to(self.device) if any(complete) else ends[:1].to(self.device)
         bt = self._block_table(seqs)
         if self.capture_routing:
             self.model.last_routing = None
-        logits = self.model.prefill(batch, self.cache, tok_seq, batch.position_ids, bt, last)
+        if any(past):
+            logits = self.model.prefill(batch, self.cache, tok_seq, batch.position_ids, bt, last, past_lens=past)
+        else:
+            logits = self.model.prefill(batch, self.cache, tok_seq, batch.position_ids, bt, last)
         if self.capture_routing:
             rt = self._take_routing()
             if rt is not None:
                 rt_h, off = rt.cpu().numpy(), 0
                 for s, n in zip(seqs, lens):
-                    s.route_chunks = [rt_h[off:off + n]]       # a re-prefill after preemption covers prompt + output so far
+                    # a re-prefill after preemption covers prompt + output so far; later chunks of a long prompt follow on
+                    s.route_chunks = (s.route_chunks if s.cached > 0 else []) + [rt_h[off:off + n]]
                     off += n
-        for s, n in zip(seqs, lens):
-            s.length = n
         self.stats["prefill_tokens"] += sum(lens)
+        pending = []
+        for s, f, done in zip(seqs, full, complete):
+            if done:
+                s.length = len(f)
+                self._register_prefix(f, s.pages, len(f))
+            else:
+                s.cached = s.chunk_end
+                pending.append(s)
+        if pending:                                   # chunked prompts continue in the next step; nothing is sampled for them
+            self.prefilling.extend(pending)
+            all_seqs = [s for s in all_seqs if s not in pending]
+            seqs = [s for s in seqs if s not in pending]
+            if not all_seqs:
+                return
         if len(seqs) != len(all_seqs):
             row = {id(s): i for i, s in enumerate(seqs)}
             src, dst, rows = [], [], []
@@ -251,11 +373,11 @@ class GenerationEngine:
                 if s.leader is not None:
                     s.length = lead.length
                     if self.capture_routing and getattr(lead, "route_chunks", None):
-                        s.route_chunks = [lead.route_chunks[0]]     # same prompt, same routing
-                    full = len(s.prompt) // PAGE
+                        s.route_chunks = [np.concatenate(lead.route_chunks, axis=0)]     # same prompt, same routing
+                    full_pages = len(s.prompt) // PAGE
                     if len(s.prompt) % PAGE:          # the partly filled last prompt page is private: copy it
-                        src.append(lead.pages[full])
-                        dst.append(s.pages[full])
+                        src.append(lead.pages[full_pages])
+                        dst.append(s.pages[full_pages])
                     s.leader = None
             self.cache.copy_pages(src, dst)
             self.stats["shared_prompt_seqs"] = self.stats.get("shared_prompt_seqs", 0) + len(all_seqs) - len(seqs)
@@ -480,5 +602,5 @@ class GenerationEngine:
                 return
         if self.running:
             self._decode()
-        elif self.waiting and not self.paused:
+        elif (self.waiting or self.prefilling) and not self.paused:
             raise MemoryError("a waiting request does not fit the KV pool even when it is empty")

@@ -90,6 +90,9 @@ class SamplerP2PMixin:
             self._recv_plans = None
         assert getattr(self, "routing_table", None) is not None, "no routing table: the first push must carry it"
         t0 = time.monotonic()
+        if getattr(self, "engine", None) is not None and hasattr(self.engine, "reset_prefix_cache"):
+            with self.server._ctl_lock:
+                self.engine.reset_prefix_cache()     # cached keys / values belong to the weights being replaced
         if self._peer_path:
             # the trainers' kernels store into this rank's live buffer; generation must not read it meanwhile
             with self.server._ctl_lock, torch.cuda.device(self.device):

@@ -98,6 +98,8 @@ class SamplerWorker(Worker, DistProfilerExtension):
         if _get(scfg, "enforce_eager", False):
             self.engine.use_cuda_graph = False
         self.engine.logprobs_mode = str(_get(scfg, "logprobs_mode", "processed"))
+        self.engine.enable_prefix_caching = bool(_get(scfg, "enable_prefix_caching", False))
+        self.engine.enable_chunked_prefill = bool(_get(scfg, "enable_chunked_prefill", True))
         if _get(cfg, "moe_replay", False) and getattr(self.model.cfg, "num_experts", 0) > 0:
             self.engine.enable_routing_capture(True)      # outputs carry the routed experts for the trainer to replay
         max_len = _get(scfg, "max_model_len", None)
@@ -157,6 +159,7 @@ class SamplerWorker(Worker, DistProfilerExtension):
     def update_weights(self, named_tensors=None):
         """Hybrid deployment: nothing to move (shared buffer) — only cached state that depends on the
         old weights is dropped. Otherwise copy the given (name, tensor) pairs in."""
+        self.engine.reset_prefix_cache()              # cached keys / values were computed with the old weights
         if self.shares_trainer_weights or named_tensors is None:
             return 0
         return self.server.update_weights(named_tensors)

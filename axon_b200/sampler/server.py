@@ -200,6 +200,7 @@ class SamplerServer:
         """Copy (name, tensor) pairs into the engine's parameter views while generation is held."""
         n = 0
         with self._ctl_lock:
+            self.engine.reset_prefix_cache()
             views = self.engine.model.params.views
             hf_views = None
             for name, t in named_tensors:

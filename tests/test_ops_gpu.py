@@ -246,6 +246,54 @@ def test_sampling_distribution_and_logprobs():
         assert abs(counts[b, top].item() / n_draws - pr) < 4 * (pr * (1 - pr) / n_draws) ** 0.5 + 0.02
 
 
+@pytest.fixture
+def persistent_decode():
+    """Run the paged decode wrappers on the persistent kernels for the duration of a test."""
+    from axon_b200.ops import paged as P
+    old, P.DECODE_IMPL = P.DECODE_IMPL, "persistent"
+    yield
+    P.DECODE_IMPL = old
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("lens,Hq,Hkv", [([1, 127, 128, 129, 700, 3000], 8, 2), ([5] * 40 + [2000] * 3 + [130] * 200, 32, 8),
+                                          ([4096, 17], 4, 4)])
+def test_persistent_paged_decode_matches_reference(persistent_decode, lens, Hq, Hkv):
+    """One CTA per SM pulling (sequence, head, split) units from a counter: same numbers as the fp32 reference and as the
+    one-CTA-per-unit kernel, on batches whose sequences differ in length by three orders of magnitude; twice in a row
+    (the work counter is reset by every launch)."""
+    from axon_b200.ops import paged as P
+    torch.manual_seed(13)
+    D, B = 128, len(lens)
+    max_pages = max((n + 127) // 128 for n in lens) + 1
+    num_pages = sum((n + 127) // 128 for n in lens) + 3
+    perm = torch.randperm(num_pages)
+    bt = torch.full((B, max_pages), -1, dtype=torch.int32)
+    nxt = 0
+    for b, n in enumerate(lens):
+        for i in range((n + 127) // 128):
+            bt[b, i] = perm[nxt]
+            nxt += 1
+    kc, vc = bf(num_pages, Hkv, 128, D, scale=0.7), bf(num_pages, Hkv, 128, D, scale=0.7)
+    q = bf(B, (Hq + 2 * Hkv) * D, scale=0.7)
+    sl = torch.tensor(lens, dtype=torch.int32)
+    P.DECODE_IMPL = "classic"
+    ref = P.paged_decode(q, kc, vc, bt, sl, Hq, Hkv, D)
+    classic = P.paged_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), sl.cuda(), Hq, Hkv, D)
+    P.DECODE_IMPL = "persistent"
+    for _ in range(2):
+        got = P.paged_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), sl.cuda(), Hq, Hkv, D)
+        C.check_status()
+        close(got, ref, 2e-2)
+        close(got, classic, 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (8, 1), (4, 4)])
+def test_persistent_shared_prefix_decode(persistent_decode, Hq, Hkv):
+    test_paged_decode_shared_prefix_matches_plain_decode(Hq, Hkv)
+
+
 @pytest.mark.gpu
 def test_sampling_full_vocabulary_logprob_mode():
     """With top-p / top-k active, ``logprobs_mode="full"`` returns the temperature-scaled log-softmax over the

@@ -181,3 +181,65 @@ def test_routed_experts_capture_and_replay_gpu():
     _routing_capture_roundtrip("cuda", torch.bfloat16, 0.15)
     from axon_b200.ops import _common as C
     C.check_status()
+
+
+def _same_generation(want, got, tol, exact):
+    for a, b in zip(want, got):
+        if exact:
+            assert a.token_ids == b.token_ids
+            assert (torch.tensor(a.logprobs) - torch.tensor(b.logprobs)).abs().max().item() < tol
+        else:           # bf16: another prefill shape may round a near-tie the other way; the first step must still agree
+            assert abs(a.logprobs[0] - b.logprobs[0]) < tol
+    assert sum(int(a.token_ids == b.token_ids) for a, b in zip(want, got)) >= (len(want) if exact else len(want) - 1)
+
+
+def _prefix_and_chunk_run(device, dtype, tol, exact=True):
+    """A second turn that extends an earlier request's text reuses its pages; a prompt longer than the token budget is
+    prefilled in chunks. Both give the tokens and log-probs of the plain engine (greedy sampling)."""
+    cfg = tiny_qwen3() if device == "cpu" else tiny_gpu()
+    model = _make(cfg, device, dtype)
+    g = torch.Generator().manual_seed(5)
+    first = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (300, 140)]
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+
+    cached = GenerationEngine(model, num_pages=40, max_num_seqs=8)
+    cached.enable_prefix_caching = True
+    turn1 = cached.generate(first, sp)
+    second = [p + o.token_ids + torch.randint(2, cfg.vocab_size, (37,), generator=g).tolist() for p, o in zip(first, turn1)]
+    plain = GenerationEngine(model, num_pages=40, max_num_seqs=8)
+    _same_generation(plain.generate(first, sp), turn1, tol, exact)
+    want = plain.generate(second, sp)
+    held = 40 - cached.cache.num_free()
+    assert held == (300 + 24 - 1) // 128 + (140 + 24 - 1) // 128            # full pages of the finished turns stay cached
+    got = cached.generate(second, sp)
+    assert cached.stats["prefix_cache_hit_tokens"] == 2 * 128 + 1 * 128
+    _same_generation(want, got, tol, exact)
+    # a weight update (sleep / wake-up, or an explicit reset) drops every cached page
+    cached.reset_prefix_cache()
+    assert cached.cache.num_free() == 40
+
+    # eviction: a small pool keeps serving by dropping the least recently used cached pages
+    small = GenerationEngine(model, num_pages=6, max_num_seqs=2)
+    small.enable_prefix_caching = True
+    for p in first + second:
+        out = small.generate([p], sp)[0]
+        assert len(out.token_ids) == 24
+    small.reset_prefix_cache()
+    assert small.cache.num_free() == 6
+
+    chunked = GenerationEngine(model, num_pages=40, max_num_seqs=8, max_num_batched_tokens=128)
+    got = chunked.generate(second, sp)
+    assert chunked.stats["prefill_tokens"] == sum(len(p) for p in second)
+    _same_generation(want, got, tol, exact)
+    assert chunked.cache.num_free() == 40
+
+
+def test_prefix_caching_and_chunked_prefill_cpu():
+    _prefix_and_chunk_run("cpu", torch.float32, 1e-4)
+
+
+@pytest.mark.gpu
+def test_prefix_caching_and_chunked_prefill_gpu():
+    _prefix_and_chunk_run("cuda", torch.bfloat16, 0.12, exact=False)
+    from axon_b200.ops import _common as C
+    C.check_status()
