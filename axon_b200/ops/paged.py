@@ -15,10 +15,10 @@ import torch
 from . import _common as C
 
 PAGE = 128
-# Decode attention kernels: "classic" launches one CTA per (sequence or group, kv head, key split); "persistent" runs
-# one CTA per SM that pulls those work units from a counter and keeps its tile pipeline running across them
-# (csrc/paged_attention_persist.cu). Same arguments, same results.
-DECODE_IMPL = os.environ.get("AXON_PAGED_DECODE", "classic")
+# Decode attention kernels: "persistent" (default) runs one warp-specialised CTA per SM that pulls (sequence or group,
+# kv head, key split) work units from a counter and keeps its TMA tile ring running across them
+# (csrc/paged_attention_persist.cu); "classic" launches one CTA per unit. Same arguments, same results.
+DECODE_IMPL = os.environ.get("AXON_PAGED_DECODE", "persistent")
 _PLAIN_ITEMS: dict = {}
 
 

@@ -133,6 +133,11 @@ class FSDPStateManager(BaseStateManager):
         if local_path is None:
             return
         self.wait()
+        if os.path.exists(os.path.join(local_path, "dist_ckpt", "metadata.json")) and not os.path.exists(os.path.join(local_path, self._name("optim"))):
+            # written by a model-parallel run in the layout-independent array store: every rank reads whole tensors
+            from .megatron_state_manager import MegatronStateManager
+            return MegatronStateManager(self.model, self.optimizer, dp_rank=self.rank, rank=self.rank, world_size=self.world_size,
+                                        process_group=self.pg).load_state(local_path)
         mode = StateSaveMode(save_mode) if save_mode else StateSaveMode.SHARDED
         eng, params = self.optimizer, self.model.params
         lo, hi = eng.shard

@@ -2,9 +2,13 @@
 axon/utils/state/megatron_state_manager.py:177-473 - sharded state through megatron's dist_checkpointing,
 HF export through the bridge's ``save_weights``).
 
-Sharded files: every rank writes its slice of ITS OWN flat parameter buffer and its optimizer shard
-(``model_world_size_W_rank_R.pt`` ... as the data-parallel manager does), plus ``model_parallel_config.json``
-naming the (tp, ep) layout the files were written under; resuming needs the same layout.
+Sharded state goes to ``<path>/dist_ckpt/`` in the layout-independent array store of ``dist_checkpoint.py``:
+every parameter is one array in full-model coordinates to which each tensor- / expert- / pipeline-parallel rank
+contributes its boxes, so the parameters load under ANY other (tp, ep, pp, dp) layout; the fp32 master weights
+and Adam moments are flat per model-parallel rank and load under any data-parallel size of the same
+model-parallel layout (under another one the masters are rebuilt from the parameters and the moments start at
+zero, with a warning). ``model_parallel_config.json`` names the layout the checkpoint was written under.
+Checkpoints in the older per-rank layout (``model_world_size_W_rank_R.pt``) are still read.
 
 HF export: tensor- and expert-parallel shards are gathered over the model-parallel group and re-assembled
 with the same row / column boxes the weight-sync planner uses (``utils/p2p/param_mapper.shard_rows``), then
@@ -15,12 +19,15 @@ from __future__ import annotations
 
 import json
 import os
+import warnings
 
 import torch
 import torch.distributed as dist
 
 from ..p2p.param_mapper import shard_rows
-from .fsdp_state_manager import FSDPStateManager
+from .dist_checkpoint import AsyncSaveRequest, ShardedObject, ShardedTensor, load_sharded, read_metadata, save_sharded
+from .fsdp_state_manager import FSDPStateManager, _barrier
+from .utils import delete_oldest_checkpoints
 
 
 def gather_full_params(model, group, tp: int = 1, tp_rank: int = 0, ep: int = 1, ep_rank: int = 0, replicated_names=()):
@@ -56,22 +63,94 @@ class MegatronStateManager(FSDPStateManager):
     def __init__(self, model, optimizer, mp_group=None, tp: int = 1, ep: int = 1, pp: int = 1, dp_rank: int = 0, **kw):
         super().__init__(model, optimizer, **kw)
         self.mp_group, self.tp, self.ep, self.pp, self.dp_rank = mp_group, tp, ep, pp, dp_rank
+        self._request: AsyncSaveRequest | None = None
 
     def _mp_rank(self) -> int:
         return dist.get_rank(self.mp_group) if self.mp_group is not None else 0
+
+    def wait(self) -> None:
+        super().wait()
+        if self._request is not None:
+            req, self._request = self._request, None
+            req.finalize()
+
+    # ------------------------------------------------------------------ sharded arrays
+    def _inner(self):
+        return getattr(self.model, "inner", self.model)
+
+    def _layout_tag(self) -> str:
+        return f"tp{self.tp}_ep{self.ep}_pp{self.pp}_mp{self._mp_rank()}"
+
+    def _param_entries(self) -> dict:
+        """key -> ShardedTensor for the parameters this rank holds, in full-model coordinates."""
+        from ...models.params import param_layout
+        inner = self._inner()
+        cfg = inner.cfg
+        full = param_layout(cfg)
+        rep = set(inner.replicated_names()) if hasattr(inner, "replicated_names") else set()
+        r = self._mp_rank()
+        out = {}
+        for name, mine in inner.params.views.items():
+            shape = full[name]
+            g2 = (int(shape[0]), int(torch.Size(shape[1:]).numel()) if len(shape) > 1 else 1)
+            zshard = getattr(self.model, "shard", None)
+            if self.pp > 1 or tuple(mine.shape) == tuple(shape):          # whole tensor on this rank (a stage's own, or replicated)
+                boxes = [((0, 0), g2)]
+                writer = self.dp_rank == 0 and (self.pp > 1 or (r == 0 and (zshard is None or zshard.rank == 0)))
+            elif zshard is not None and self.tp == 1 and self.ep == 1:    # row shards of the parameter-sharded data-parallel model
+                boxes = [((zshard.rank * int(mine.shape[0]), 0), (int(mine.shape[0]), g2[1]))]
+                writer = True
+            else:
+                rows = shard_rows(cfg, name, self.tp, r if self.tp > 1 else 0, self.ep, r if self.ep > 1 else 0, rep)
+                boxes = [((r0, c0), (r1 - r0, c1 - c0)) for (r0, r1, c0, c1) in rows]
+                writer = self.dp_rank == 0
+            out["model/" + name] = ShardedTensor("model/" + name, mine.detach(), g2, boxes, 0 if writer else 1)
+        return out
+
+    def _optim_entries(self) -> dict:
+        eng = self.optimizer
+        lo, hi = eng.shard
+        n = int(self.model.params.flat.numel())
+        tag = self._layout_tag()
+        out = {}
+        for part in ("master", "exp_avg", "exp_avg_sq"):
+            t = getattr(eng, part)
+            if t is not None:
+                key = f"optimizer/{tag}/{part}"
+                out[key] = ShardedTensor.slice_1d(key, t, n, lo)
+        return out
 
     def save_state(self, local_path: str, global_step: int = 0, max_ckpt_to_keep: int | None = None,
                    save_mode: str | None = None, async_save: bool | None = None):
         if local_path is None:
             return
+        self.wait()
         want_hf = save_mode in ("hf", "both")
-        # the sharded part (and rotation, async writing) is the data-parallel manager's; HF export is done here
-        super().save_state(local_path, global_step, max_ckpt_to_keep, "sharded", async_save)
+        os.makedirs(local_path, exist_ok=True)
+        _barrier(None)
+        eng = self.optimizer
+        eng.load_optimizer()
+        state = {}
+        state.update(self._param_entries())
+        state.update(self._optim_entries())
+        state["extra/common"] = ShardedObject("extra/common", {"opt_step": eng.opt_step, "sched_step": getattr(eng, "sched_step", eng.opt_step),
+                                                               "global_step": global_step}, replica_id=self.rank)
+        state[f"extra/rng_rank{self.rank}"] = ShardedObject(f"extra/rng_rank{self.rank}", self.get_rng_state())
+        # manifests and barriers span ALL ranks of the job (the optimizer's group is one data-parallel replica set only)
+        req = save_sharded(state, os.path.join(local_path, "dist_ckpt"), group=None, async_save=bool(async_save))
         if self.rank == 0:
             with open(os.path.join(local_path, "model_parallel_config.json"), "w") as f:
                 json.dump({"tensor_model_parallel_size": self.tp, "expert_model_parallel_size": self.ep,
-                           "pipeline_model_parallel_size": self.pp, "world_size": self.world_size,
+                           "pipeline_model_parallel_size": self.pp, "world_size": self.world_size, "layout": "dist_ckpt",
                            "param_shards": getattr(getattr(self.model, "shard", None), "world", 1)}, f, indent=1)
+            hf_dir = os.path.join(local_path, "huggingface")
+            os.makedirs(hf_dir, exist_ok=True)
+            if not want_hf:
+                self._inner().cfg.save_pretrained(hf_dir)
+        if async_save:
+            self._request = req            # finalized by wait(): before the next save, a load, or shutdown
+        elif max_ckpt_to_keep and max_ckpt_to_keep > 0 and self.rank == 0:
+            delete_oldest_checkpoints(os.path.dirname(os.path.dirname(os.path.abspath(local_path))), max_ckpt_to_keep)
         if want_hf and self.dp_rank == 0:
             inner = getattr(self.model, "inner", self.model)
             rep = inner.replicated_names() if hasattr(inner, "replicated_names") else ()
@@ -93,6 +172,41 @@ class MegatronStateManager(FSDPStateManager):
                 save_hf_model(host, os.path.join(local_path, "huggingface"), cfg=inner.cfg, tokenizer=self.processing_class)
 
     def load_state(self, local_path: str, save_mode: str | None = None):
+        if local_path is None:
+            return
+        self.wait()
+        dist_dir = os.path.join(local_path, "dist_ckpt")
+        if not os.path.exists(os.path.join(dist_dir, "metadata.json")):
+            return self._load_per_rank_files(local_path)
+        meta = read_metadata(dist_dir)
+        eng = self.optimizer
+        eng.load_optimizer()
+        template = dict(self._param_entries())
+        optim = self._optim_entries()
+        same_mp = all(k in meta["tensors"] and tuple(meta["tensors"][k]["global_shape"]) == tuple(v.global_shape) for k, v in optim.items())
+        if same_mp:
+            template.update(optim)
+        template["extra/common"] = ShardedObject("extra/common", None)
+        rng_key = f"extra/rng_rank{self.rank}"
+        if rng_key in meta["objects"]:
+            template[rng_key] = ShardedObject(rng_key, None)
+        objs = load_sharded(template, dist_dir, group=None)
+        if not same_mp:
+            warnings.warn(f"{local_path}: optimizer state was written under another model-parallel layout than {self._layout_tag()}; "
+                          "master weights are rebuilt from the parameters and the Adam moments start at zero", stacklevel=2)
+            lo, hi = eng.shard
+            eng.master.copy_(self.model.params.flat[lo:hi].float())
+            eng.exp_avg.zero_()
+            eng.exp_avg_sq.zero_()
+        common = objs.get("extra/common") or {}
+        eng.opt_step = int(common.get("opt_step", eng.opt_step))
+        if hasattr(eng, "sched_step"):
+            eng.sched_step = int(common.get("sched_step", eng.opt_step))
+        if rng_key in objs:
+            self.load_rng_state(objs[rng_key])
+        _barrier(None)
+
+    def _load_per_rank_files(self, local_path: str):
         cfg_file = os.path.join(local_path or "", "model_parallel_config.json")
         if local_path and os.path.exists(cfg_file):
             with open(cfg_file) as f:

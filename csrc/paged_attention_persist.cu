@@ -1,20 +1,32 @@
-// Persistent form of the item-based paged decode attention (paged_attention_shared.cu).
+// Persistent, warp-specialised form of the item-based paged decode attention (paged_attention_shared.cu).
 //
-// The item kernels launch one CTA per (item, kv head, key split). With short items - the private tail of a
-// sample after its shared prompt is a handful of pages - every CTA spends as long on start-up (TMEM allocation,
-// barrier initialisation, the query load's global-memory latency, filling an empty TMA pipeline) as on its keys,
-// which is why attention over shared prompt pages read 2.4x fewer bytes but ran only 7 % faster.
+// The item kernels launch one CTA per (item, kv head, key split) and run every step of a key block - tile wait,
+// S product, softmax, P*V product, next loads - one after the other on the same 128 threads. Counters of that
+// kernel show ~4000 cycles per 64 KB block with most issue slots lost at CTA-wide barriers, i.e. ~0.7 of the HBM
+// rate, and with short items (the private tail of a sample after its shared prompt) the per-CTA start-up costs as
+// much as the keys themselves.
 //
-// Here ONE CTA per SM lives for the whole launch and pulls work units (item, kv head, split) from an atomic
-// counter. TMEM is allocated once and the barriers are initialised once; the K|V tile ring keeps running
-// ACROSS units (while the last tiles of a unit are being consumed, the first tiles of the next unit are already
-// in flight), and the next unit's query rows are fetched with cp.async while the current unit computes. The tile
-// mathematics is that of the item kernel: S^T = K_tile Q^T and O^T += V_tile^T P^T on tcgen05 with N = query
-// columns, thread t owns key t for the softmax and output dimension t in the epilogue, lazily raised running
-// maximum, un-normalised partial results per (sequence, head, slot) merged by paged_merge_slots_kernel.
+// Here ONE CTA per SM lives for the whole launch, pulls work units (item, kv head, split) from an atomic counter
+// and splits the work over three roles that only meet at mbarriers:
 //
-// Every wait is bounded; a wait that runs out records a status code, drains the loads still in flight (bounded),
-// frees TMEM and returns.
+//   producer warp   fetches unit ids, loads each unit's query rows and its K / V tiles by TMA into a ring of six
+//                   32 KB slots (K0 V0 K1 V1 ...), running ahead of the consumers by up to six tiles - across unit
+//                   boundaries, so the pipeline never drains between units;
+//   MMA warp        one thread issues S^T = K_tile Q^T (tcgen05, N = query columns) for block g+1 BEFORE the
+//                   O^T += V_tile^T P^T product of block g, so the tensor core always has the next scores ready
+//                   when the softmax threads finish a block; tcgen05.commit releases the tile slots;
+//   softmax threads 128 threads, thread t owns key t of the block and output dimension t in the epilogue. The
+//                   running maximum is raised lazily: a block first checks with one OR-reducing barrier whether
+//                   any score exceeds the running maximum by more than 2^8; only then (the first block of a unit
+//                   and rare later ones) are exact column maxima exchanged and the accumulator rescaled.
+//
+// TMEM holds two S accumulators (alternating by block) and two O accumulators (alternating by unit), shared
+// memory two query buffers (by unit) and two P buffers (by block), so that no role waits for another one's
+// previous step. Results are un-normalised partials per (sequence, head, slot) merged by pp_merge_slots_kernel,
+// or the normalised bf16 output directly when there is one slot.
+//
+// Every wait is bounded; a wait that runs out records a status code and raises an abort flag that all roles
+// poll; the producer then waits (bounded) for its loads in flight, TMEM is freed and the kernel returns.
 #include "ptx.cuh"
 #include "host_utils.h"
 
@@ -22,26 +34,43 @@ namespace axb {
 
 constexpr int PP_D = 128;
 constexpr int PP_PAGE = 128;
-constexpr int PP_TILE = PP_PAGE * PP_D * 2;  // 32 KB
-constexpr int PP_STAGES = 3;
-constexpr int PP_RING = 16;                  // unit ids fetched ahead of the compute cursor
+constexpr int PP_TILE = PP_PAGE * PP_D * 2;  // 32 KB: the K (or V) rows of one page and kv head
+constexpr int PP_SLOTS = 6;                  // tile slots: K and V tiles of successive blocks alternate
+constexpr int PP_RING = 16;                  // unit ids published ahead of the slowest consumer
+constexpr int PP_THREADS = 192;              // 4 softmax warps + producer warp + MMA warp
 
 __device__ __forceinline__ uint32_t pp_sw128(int row, int col_elem) {
   const int unit = (col_elem >> 3) ^ (row & 7);
   return row * 128 + unit * 16 + (col_elem & 7) * 2;
 }
-
-__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// barrier 1 over the 128 softmax threads
+__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ bool softmax_bar_or(bool p) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.red.or.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"((uint32_t)p)
+      : "memory");
+  return r != 0;
+}
 
 template <int NCOL>
 struct PpCfg {
   static constexpr int NPAD = NCOL <= 16 ? 16 : 32;                 // MMA N
   static constexpr int QBYTES = 2 * NPAD * 128;                      // [2 K-chunks][NPAD rows][64] bf16
-  static constexpr int SMEM = PP_STAGES * 2 * PP_TILE + 3 * QBYTES + 2 * 4 * NCOL * 4 + 512 + 1024;
+  static constexpr int TCOLS = 4 * NPAD;                             // S0 | S1 | O0 | O1
+  static constexpr int SMEM = PP_SLOTS * PP_TILE + 4 * QBYTES + 2 * 4 * NCOL * 4 + 1024 + 1024;
 };
 
 struct PpUnit {        // one (item, kv head, split)
@@ -69,11 +98,12 @@ __device__ __forceinline__ PpUnit pp_decode(int u, const int* item_first, const 
 }
 
 // items as in paged_decode_items_kernel; total = n_items * Hkv * nsplit work units. work_counter must be 0 at launch.
+// tmQ: the query rows as a 3-D tensor [sequence][head][128] with box (64, rep, sequences per item).
 // out != nullptr (only with nslots == 1 and single-sequence items): write the normalised bf16 result directly.
 template <int NCOL>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(PP_THREADS, 1)
 paged_decode_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                            const __nv_bfloat16* __restrict__ q, long long q_row_stride,
+                            const __grid_constant__ CUtensorMap tmQ, int q_box_bytes,
                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ item_first,
                             const int* __restrict__ item_size, const int* __restrict__ item_page0,
                             const int* __restrict__ item_keys, int n_items, int slot0, int neutral_from, int neutral_n,
@@ -90,356 +120,415 @@ paged_decode_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sKV = smem;                                   // [stage][K 32K | V 32K]
-  uint8_t* sQ = smem + PP_STAGES * 2 * PP_TILE;          // two query buffers, used in turn by successive units
-  uint8_t* sP = sQ + 2 * Cfg::QBYTES;
-  float* red = reinterpret_cast<float*>(sP + Cfg::QBYTES);    // [2][4 warps][NCOL]
+  uint8_t* sT = smem;                                    // [slot] 32 KB tiles; tile 2g = K of block g, 2g+1 = V of block g
+  uint8_t* sQ = smem + PP_SLOTS * PP_TILE;               // two query buffers, by unit
+  uint8_t* sP = sQ + 2 * Cfg::QBYTES;                    // two probability buffers, by block
+  float* red = reinterpret_cast<float*>(sP + 2 * Cfg::QBYTES);   // [4 warps][NCOL] column maxima, then [4][NCOL] row sums
   uint8_t* tail = reinterpret_cast<uint8_t*>(red) + 2 * 4 * NCOL * 4;
-  uint64_t* full = reinterpret_cast<uint64_t*>(tail);    // [PP_STAGES]
-  uint64_t* bar_mma = full + PP_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_mma + 1);
-  int* ring = reinterpret_cast<int*>(tmem_slot + 2);     // [PP_RING] unit ids in processing order, -1 = no more work
+  uint64_t* full = reinterpret_cast<uint64_t*>(tail);    // [PP_SLOTS] tile landed
+  uint64_t* empty = full + PP_SLOTS;                     // [PP_SLOTS] the product that read the tile has completed
+  uint64_t* q_full = empty + PP_SLOTS;                   // [2] query rows landed
+  uint64_t* q_empty = q_full + 2;                        // [2] the unit's last S product has completed
+  uint64_t* bar_s = q_empty + 2;                         // [2] S of a block has completed
+  uint64_t* p_ready = bar_s + 2;                         // [2] 128 arrivals: P written (and O rescaled) for a block
+  uint64_t* bar_pv = p_ready + 2;                        // [2] P*V of an even / odd block has completed
+  uint64_t* o_free = bar_pv + 2;                         // [2] 128 arrivals: the unit's accumulator has been read
+  uint64_t* ring_full = o_free + 2;                      // [PP_RING] unit id published
+  uint64_t* ring_empty = ring_full + PP_RING;            // [PP_RING] 128 arrivals: the softmax threads are done with the unit
+  int* ring = reinterpret_cast<int*>(ring_empty + PP_RING);   // [PP_RING] unit ids in processing order, -1 = no more work
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring + PP_RING);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (tid == 0) {
-    for (int s = 0; s < PP_STAGES; ++s) mbar_init(&full[s], 1);
-    mbar_init(bar_mma, 1);
+    for (int s = 0; s < PP_SLOTS; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int k = 0; k < 2; ++k) {
+      mbar_init(&q_full[k], 1);
+      mbar_init(&q_empty[k], 1);
+      mbar_init(&bar_s[k], 1);
+      mbar_init(&p_ready[k], 128);
+      mbar_init(&o_free[k], 128);
+      mbar_init(&bar_pv[k], 1);
+    }
+    for (int k = 0; k < PP_RING; ++k) {
+      mbar_init(&ring_full[k], 1);
+      mbar_init(&ring_empty[k], 128);
+    }
+    *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, 2 * NPAD);
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, Cfg::TCOLS);
     tmem_relinquish();
   }
+  // query and probability buffers start as zeros: rows beyond a unit's columns must not hold NaN patterns
+  for (int i = tid; i < 4 * Cfg::QBYTES / 16; i += PP_THREADS) reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0, 0, 0, 0);
+  fence_async_shared();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-  const uint32_t tO = tS + NPAD;
-  constexpr uint32_t idesc_s = umma_idesc(128, NPAD, 0, 0);
-  constexpr uint32_t idesc_o = umma_idesc(128, NPAD, 1, 0);
 
-  // ---- thread 0: unit fetching and the load cursor (these variables are meaningful in thread 0 only)
-  int rw = 0;                    // units fetched into the ring so far
-  int rl = 0;                    // ring index of the unit the load cursor is in
-  int lblk = 0, l_nb = 0, l_hk = 0;
-  const int* l_bt = block_table;
-  bool l_open = false;           // the load cursor has a unit with blocks left
-  bool l_end = false;            // the load cursor has seen the end marker
-  long long g_issue = 0;         // K|V blocks whose loads were issued (all units of this CTA)
-  long long g_done = 0;          // blocks whose stage may be overwritten (their P*V product has completed)
+  auto give_up = [&](int code) {
+    report_error(status, code);
+    *abort_flag = 1;
+  };
 
-  // Unit ids come from an atomic counter. The atomic's round trip to L2 is hidden by splitting the fetch: the request
-  // is made at the start of a unit and its result is first touched (written into the ring) one unit later.
-  unsigned int pend = 0;
-  bool has_pend = false;
-  auto fetch_begin = [&]() {     // thread 0
-    pend = atomicAdd(work_counter, 1u);
-    has_pend = true;
-  };
-  auto fetch_commit = [&]() {    // thread 0
-    ring[rw % PP_RING] = pend < (unsigned int)total ? (int)pend : -1;
-    ++rw;
-    has_pend = false;
-  };
-  auto fetch_unit = [&]() {      // thread 0: request and use at once (start-up, or the load cursor ran out of known units)
-    if (!has_pend) fetch_begin();
-    fetch_commit();
-  };
-  auto advance_loads = [&](int rr) {   // thread 0: issue loads while a stage is free; rr = compute cursor's ring index
-    while (!l_end && g_issue < g_done + PP_STAGES) {
-      if (!l_open) {
-        if (rl >= rw) {
-          if (rw - rr >= PP_RING - 1) break;     // ring full: wait for the compute cursor
-          fetch_unit();
+  if (warp == 4) {
+    // ================================================================== producer: unit ids, query rows, K / V tiles
+    long long t = 0;           // tiles issued
+    int nq = 0;                // units with blocks so far (selects the query buffer)
+    bool ok = true;
+    for (int n = 0; ok; ++n) {
+      int u = -1;
+      if (lane == 0) {
+        if (n >= PP_RING && !mbar_wait(&ring_empty[n % PP_RING], (uint32_t)(((n / PP_RING) - 1) & 1))) {
+          give_up(AXB_ERR_WAIT_EMPTY);
+          ok = false;
         }
-        const int u = ring[rl % PP_RING];
-        if (u < 0) {
-          l_end = true;
-          break;
+        if (ok) {
+          const unsigned int v = atomicAdd(work_counter, 1u);
+          u = v < (unsigned int)total ? (int)v : -1;
         }
-        const PpUnit x = pp_decode(u, item_first, item_size, item_page0, item_keys, Hkv, nsplit, rep, NCOL);
-        if (x.nb <= 0) {
-          ++rl;
-          continue;
-        }
-        l_bt = block_table + (long long)x.b0 * max_pages + x.page0 + x.blk_begin;
-        l_nb = x.nb;
-        l_hk = x.hk;
-        lblk = 0;
-        l_open = true;
+        ring[n % PP_RING] = u;
+        mbar_arrive(&ring_full[n % PP_RING]);       // release: the id is visible to whoever passes the barrier
       }
-      const int s = (int)(g_issue % PP_STAGES);
-      const int page = l_bt[lblk];
-      const int row0 = (page * Hkv + l_hk) * PP_PAGE;
-      uint8_t* k = sKV + s * 2 * PP_TILE;
-      mbar_expect_tx(&full[s], 2 * PP_TILE);
-      tma_load_2d(k, &tmK, &full[s], 0, row0);
-      tma_load_2d(k + 16384, &tmK, &full[s], 64, row0);
-      tma_load_2d(k + PP_TILE, &tmV, &full[s], 0, row0);
-      tma_load_2d(k + PP_TILE + 16384, &tmV, &full[s], 64, row0);
-      ++g_issue;
-      if (++lblk >= l_nb) {
-        l_open = false;
-        ++rl;
-      }
-    }
-  };
-  // query rows of a unit -> sQ[buf] with cp.async (16-byte pieces keep the 128-byte swizzle's granularity)
-  auto fetch_q = [&](const PpUnit& x, int buf) {
-    const uint32_t base = smem_u32(sQ + buf * Cfg::QBYTES);
-    for (int i = tid; i < x.ncols * 16; i += 128) {
-      const int c = i >> 4, piece = i & 15;            // column (sequence, head) and 16-byte piece of its 128 dims
-      const __nv_bfloat16* src = q + (long long)(x.b0 + c / rep) * q_row_stride + (long long)(x.hk * rep + c % rep) * PP_D + piece * 8;
-      cp_async_16(base + (piece >> 3) * (NPAD * 128) + pp_sw128(c, (piece & 7) * 8), src);
-    }
-    cp_async_commit();
-  };
-
-  // zero both query buffers once: rows beyond a unit's columns must not hold NaN patterns
-  for (int i = tid; i < 2 * Cfg::QBYTES / 16; i += 128) reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) {
-    fetch_unit();
-    fetch_unit();
-  }
-  __syncthreads();
-
-  bool ok = true;
-  uint32_t ph = 0;          // bar_mma: one completion per block (after S) and one after a unit's last P*V
-  long long g = 0;          // blocks consumed so far by this CTA (selects stage and parity)
-  int rr = 0;               // compute cursor: ring index of the current unit
-  int u_cur = ring[0];
-  PpUnit cur;
-  cur.nb = -1;
-  if (u_cur >= 0) cur = pp_decode(u_cur, item_first, item_size, item_page0, item_keys, Hkv, nsplit, rep, NCOL);
-  int qbuf = 0;             // query buffer the current unit reads
-  int q_unit = -1;          // ring index of the unit whose query rows were last requested (into qbuf, or qbuf ^ 1 if it is rr + 1)
-
-  while (u_cur >= 0) {
-    // next unit id (thread 0 keeps the ring one ahead), and its query rows into the other buffer
-    if (tid == 0) {
-      if (has_pend) fetch_commit();
-      while (rw < rr + 2) fetch_unit();
-      if (rw - rr < PP_RING - 1) fetch_begin();          // the unit after next: asked for now, looked at one unit from now
-      advance_loads(rr);
-    }
-    __syncthreads();
-    const int u_next = ring[(rr + 1) % PP_RING];
-    PpUnit nxt;
-    nxt.nb = -1;
-    if (u_next >= 0) nxt = pp_decode(u_next, item_first, item_size, item_page0, item_keys, Hkv, nsplit, rep, NCOL);
-
-    if (cur.nb >= 0) {
-      const int ncols = cur.ncols;
-      // slots this item never fills for its sequences: no shared prefix -> neutral prefix slots
-      if (neutral_n > 0 && cur.page0 == 0 && cur.sp == 0) {
-        for (int i = tid; i < ncols * neutral_n; i += 128) {
-          const int c = i / neutral_n, sl = i % neutral_n;
-          const long long idx = ((long long)(cur.b0 + c / rep) * Hq + cur.hk * rep + c % rep) * nslots + neutral_from + sl;
-          part_ml[idx * 2] = -1e30f;
-          part_ml[idx * 2 + 1] = 0.f;
+      u = __shfl_sync(0xffffffffu, u, 0);
+      ok = __shfl_sync(0xffffffffu, (int)(ok && *abort_flag == 0), 0) != 0;      // lane 0 decides for the warp
+      if (u < 0 || !ok) break;
+      const PpUnit x = pp_decode(u, item_first, item_size, item_page0, item_keys, Hkv, nsplit, rep, NCOL);
+      if (x.nb <= 0) continue;
+      if (lane == 0) {
+        const int qb = nq & 1;
+        if (nq >= 2 && !mbar_wait(&q_empty[qb], (uint32_t)(((nq >> 1) - 1) & 1))) {
+          give_up(AXB_ERR_WAIT_EMPTY);
+          ok = false;
+        } else {
+          mbar_expect_tx(&q_full[qb], 2 * q_box_bytes);
+          tma_load_3d(sQ + qb * Cfg::QBYTES, &tmQ, &q_full[qb], 0, x.hk * rep, x.b0);
+          tma_load_3d(sQ + qb * Cfg::QBYTES + NPAD * 128, &tmQ, &q_full[qb], 64, x.hk * rep, x.b0);
         }
       }
-      if (cur.nb == 0) {
-        if (out != nullptr) {                      // a row without keys (padding of a batch bucket): zeros
-          for (int c = 0; c < ncols; ++c)
-            out[((long long)(cur.b0 + c / rep) * Hq + cur.hk * rep + c % rep) * PP_D + tid] = __float2bfloat16(0.f);
-        } else if (tid < ncols) {
-          const long long idx = ((long long)(cur.b0 + tid / rep) * Hq + cur.hk * rep + tid % rep) * nslots + slot0 + cur.sp;
-          part_ml[idx * 2] = -1e30f;
-          part_ml[idx * 2 + 1] = 0.f;
-        }
-      } else if (ok) {
-        // the unit's query rows were requested while the previous unit computed; if that unit did no work (or this is
-        // the first one) they are requested now
-        if (q_unit != rr) {
-          fetch_q(cur, qbuf);
-          q_unit = rr;
-        }
-        cp_async_wait_all();
-        fence_async_shared();
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
-        if (nxt.nb > 0) {
-          fetch_q(nxt, qbuf ^ 1);
-          q_unit = rr + 1;
-        }
-        const uint32_t qaddr = smem_u32(sQ + qbuf * Cfg::QBYTES);
-
-        float m_run[NCOL], l_thr[NCOL];
-#pragma unroll
-        for (int c = 0; c < NCOL; ++c) {
-          m_run[c] = -1e30f;
-          l_thr[c] = 0.f;
-        }
-        const int nb = cur.nb;
-        for (int i = 0; i < nb; ++i, ++g) {
-          const int s = (int)(g % PP_STAGES);
-          const uint32_t kaddr = smem_u32(sKV + s * 2 * PP_TILE);
-          if (tid == 0 && ok) {
-            if (!mbar_wait(&full[s], (uint32_t)((g / PP_STAGES) & 1))) {
-              report_error(status, AXB_ERR_WAIT_FULL);
-              ok = false;
-            }
-            tc_fence_after();
-            if (ok) {
-#pragma unroll
-              for (int ks = 0; ks < 8; ++ks) {
-                umma_f16_ss(tmem_base, umma_smem_desc(kaddr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                            umma_smem_desc(qaddr + (ks >> 2) * (NPAD * 128) + (ks & 3) * 32, 16, 1024), idesc_s, ks != 0);
+      ++nq;
+      const int* bt = block_table + (long long)x.b0 * max_pages + x.page0 + x.blk_begin;
+      for (int blk0 = 0; blk0 < x.nb && ok; blk0 += 32) {
+        const int mine = blk0 + lane < x.nb ? bt[blk0 + lane] : 0;       // 32 page ids with one coalesced load
+        const int cnt = min(32, x.nb - blk0);
+        for (int j = 0; j < cnt; ++j) {
+          const int page = __shfl_sync(0xffffffffu, mine, j);
+          if (lane == 0 && ok) {
+            const int row0 = (page * Hkv + x.hk) * PP_PAGE;
+            for (int half = 0; half < 2 && ok; ++half, ++t) {
+              const int s = (int)(t % PP_SLOTS);
+              if (t >= PP_SLOTS && !mbar_wait(&empty[s], (uint32_t)(((t / PP_SLOTS) - 1) & 1))) {
+                give_up(AXB_ERR_WAIT_EMPTY);
+                ok = false;
+                break;
               }
-              tc_commit(bar_mma);   // also covers the P*V product of the previous block
+              uint8_t* dst = sT + s * PP_TILE;
+              mbar_expect_tx(&full[s], PP_TILE);
+              tma_load_2d(dst, half == 0 ? &tmK : &tmV, &full[s], 0, row0);
+              tma_load_2d(dst + 16384, half == 0 ? &tmK : &tmV, &full[s], 64, row0);
             }
           }
-          // every thread learns whether thread 0 gave up (uniform control flow from here on)
-          ok = __syncthreads_and(ok ? 1 : 0) != 0;
-          if (!ok) break;
-          if (!mbar_wait(bar_mma, ph)) {
-            report_error(status, AXB_ERR_WAIT_TMEM_FULL);
+        }
+        ok = __shfl_sync(0xffffffffu, (int)(ok && *abort_flag == 0), 0) != 0;
+      }
+    }
+    // after an error loads may still be in flight: wait (bounded) for the latest use of every slot and query buffer
+    if (lane == 0 && *abort_flag != 0) {
+      for (long long b = t > PP_SLOTS ? t - PP_SLOTS : 0; b < t; ++b)
+        mbar_wait(&full[b % PP_SLOTS], (uint32_t)((b / PP_SLOTS) & 1));
+      for (int b = nq > 2 ? nq - 2 : 0; b < nq; ++b) mbar_wait(&q_full[b & 1], (uint32_t)((b >> 1) & 1));
+    }
+  } else if (warp == 5) {
+    // ================================================================== MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc(128, NPAD, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc(128, NPAD, 1, 0);
+      bool ok = true;
+      int n = 0;                 // ring position of the S cursor
+      int nq = 0;                // units with blocks the S cursor has entered
+      long long g = 0;           // blocks whose S product has been issued
+      PpUnit x;
+      x.nb = 0;
+      int i = 0;                 // S cursor: next block of x
+      bool more = true;
+      // the block whose P*V product is still to be issued (always the one before the S cursor)
+      bool pend = false, pend_first = false;
+      long long pend_g = 0;
+      int pend_ob = 0, pend_nq = 0;
+      auto issue_pv = [&]() {
+        const int s = (int)((2 * pend_g + 1) % PP_SLOTS);
+        if (!mbar_wait(&p_ready[pend_g & 1], (uint32_t)((pend_g >> 1) & 1)) ||
+            !mbar_wait(&full[s], (uint32_t)(((2 * pend_g + 1) / PP_SLOTS) & 1)) ||
+            (pend_first && pend_nq >= 2 && !mbar_wait(&o_free[pend_ob], (uint32_t)(((pend_nq >> 1) - 1) & 1)))) {
+          give_up(AXB_ERR_WAIT_TMEM_EMPTY);
+          ok = false;
+          return;
+        }
+        tc_fence_after();
+        const uint32_t vaddr = smem_u32(sT + s * PP_TILE), paddr = smem_u32(sP + (pend_g & 1) * Cfg::QBYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          umma_f16_ss(tmem_base + (2 + pend_ob) * NPAD, umma_smem_desc(vaddr + ks * 2048, 16384, 1024),
+                      umma_smem_desc(paddr + (ks >> 2) * (NPAD * 128) + (ks & 3) * 32, 16, 1024), idesc_o,
+                      (!pend_first || ks != 0) ? 1u : 0u);
+        }
+        tc_commit(&empty[s]);
+        tc_commit(&bar_pv[pend_g & 1]);
+      };
+      while (ok && more) {
+        // ---- move the S cursor to the next block (entering the next unit with blocks if need be)
+        while (i >= x.nb) {
+          // Never block on an unpublished unit with a product still owed: the producer may be waiting for the softmax
+          // threads to finish the unit that needs it (a run of sixteen units without blocks closes that cycle).
+          if (pend && !mbar_try_wait(&ring_full[n % PP_RING], (uint32_t)((n / PP_RING) & 1))) {
+            issue_pv();
+            pend = false;
+            if (!ok) break;
+          }
+          if (!mbar_wait(&ring_full[n % PP_RING], (uint32_t)((n / PP_RING) & 1))) {
+            give_up(AXB_ERR_WAIT_FULL);
             ok = false;
+            break;
           }
-          ph ^= 1;
-          tc_fence_after();
-          // the stage of the previous block is free now: keep the ring full, across the unit boundary if need be
-          if (tid == 0 && ok) {
-            g_done = g;
-            advance_loads(rr);
+          const int u = ring[n % PP_RING];
+          ++n;
+          if (u < 0) {
+            more = false;
+            break;
           }
-
-          uint32_t sv[NPAD];
-          tmem_ld_32x16(tS, sv);
-          if (NPAD == 32) tmem_ld_32x16(tS + 16, sv + 16);
-          tmem_ld_wait();
-          const int kpos = (cur.blk_begin + i) * PP_PAGE + tid;
-          const bool valid = kpos < cur.n_keys;
-          float sc[NCOL];
-#pragma unroll
-          for (int c = 0; c < NCOL; ++c) {
-            sc[c] = (valid && c < ncols) ? __uint_as_float(sv[c]) * scale_log2 : -INFINITY;
-            const float wm = warp_max_redux(sc[c]);
-            if (lane == 0) red[((i & 1) * 4 + warp) * NCOL + c] = wm;
-          }
-          ok = __syncthreads_and(ok ? 1 : 0) != 0;
-          if (!ok) break;
-          float alpha[NCOL];
-          bool changed = false;
-#pragma unroll
-          for (int c = 0; c < NCOL; ++c) {
-            const float* r = red + (i & 1) * 4 * NCOL + c;
-            const float bm = fmaxf(fmaxf(r[0], r[NCOL]), fmaxf(r[2 * NCOL], r[3 * NCOL]));
-            // the running maximum is raised only when a block exceeds it by more than 2^8: probabilities stay below
-            // 256 (exact after the final normalisation) and the accumulator is rescaled on few blocks
-            const bool raise = bm > m_run[c] + 8.f;
-            const float mn = raise ? bm : m_run[c];
-            alpha[c] = raise ? exp2f(m_run[c] - mn) : 1.f;
-            changed |= raise;
-            m_run[c] = mn;
-            const float p = exp2f(sc[c] - mn);
-            l_thr[c] = l_thr[c] * alpha[c] + p;
-            if (c < ncols)
-              *reinterpret_cast<__nv_bfloat16*>(sP + (tid >> 6) * (NPAD * 128) + pp_sw128(c, tid & 63)) = __float2bfloat16(p);
-          }
-          if (i > 0 && changed) {  // uniform across the CTA: m_run is identical in every thread
-            uint32_t o[NPAD];
-            tmem_ld_32x16(tO, o);
-            if (NPAD == 32) tmem_ld_32x16(tO + 16, o + 16);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < NCOL; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c]);
-#pragma unroll
-            for (int g8 = 0; g8 < NCOL / 8; ++g8) {
-              asm volatile(
-                  "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                  ::"r"(tO + g8 * 8), "r"(o[g8 * 8]), "r"(o[g8 * 8 + 1]), "r"(o[g8 * 8 + 2]), "r"(o[g8 * 8 + 3]),
-                  "r"(o[g8 * 8 + 4]), "r"(o[g8 * 8 + 5]), "r"(o[g8 * 8 + 6]), "r"(o[g8 * 8 + 7])
-                  : "memory");
+          x = pp_decode(u, item_first, item_size, item_page0, item_keys, Hkv, nsplit, rep, NCOL);
+          i = 0;
+          if (x.nb > 0) {
+            if (!mbar_wait(&q_full[nq & 1], (uint32_t)((nq >> 1) & 1))) {
+              give_up(AXB_ERR_WAIT_FULL);
+              ok = false;
+              break;
             }
-            tmem_st_wait();
+            ++nq;
           }
-          fence_async_shared();
-          tc_fence_before();
-          __syncthreads();
-          if (tid == 0) {
+        }
+        if (!ok || !more || *abort_flag != 0) break;
+        // ---- S of block g: its accumulator was read by the softmax two blocks back, whose P this thread has waited for
+        {
+          const int s = (int)((2 * g) % PP_SLOTS);
+          if (!mbar_wait(&full[s], (uint32_t)(((2 * g) / PP_SLOTS) & 1))) {
+            give_up(AXB_ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int qb = (nq - 1) & 1;
+          const uint32_t kaddr = smem_u32(sT + s * PP_TILE), qaddr = smem_u32(sQ + qb * Cfg::QBYTES);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            umma_f16_ss(tmem_base + (uint32_t)(g & 1) * NPAD, umma_smem_desc(kaddr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                        umma_smem_desc(qaddr + (ks >> 2) * (NPAD * 128) + (ks & 3) * 32, 16, 1024), idesc_s, ks != 0);
+          }
+          tc_commit(&bar_s[g & 1]);
+          tc_commit(&empty[s]);
+          if (i == x.nb - 1) tc_commit(&q_empty[qb]);
+        }
+        // ---- P*V of the block before it
+        if (pend) issue_pv();
+        pend = true;
+        pend_g = g;
+        pend_first = i == 0;
+        pend_nq = nq - 1;
+        pend_ob = (nq - 1) & 1;
+        ++g;
+        ++i;
+      }
+      if (ok && pend && *abort_flag == 0) issue_pv();
+    }
+  } else {
+    // ================================================================== softmax and epilogue (128 threads; thread = key / dim)
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    // `fail` is this thread's own finding (a wait ran out); the threads only leave their loops together, on `quit`,
+    // which is always the result of an OR-reducing barrier
+    bool fail = false, quit = false;
+    int nq = 0;
+    long long g = 0;
+    // this thread's byte offset inside a P buffer for column 0; column c adds c * 128 and flips the 16-byte unit by c & 7
+    const int pcol = tid & 63;
+    uint8_t* const pbase = sP + (tid >> 6) * (NPAD * 128);
+    for (int n = 0; !quit; ++n) {
+      if (!mbar_wait(&ring_full[n % PP_RING], (uint32_t)((n / PP_RING) & 1))) {
+        give_up(AXB_ERR_WAIT_FULL);
+        fail = true;
+      }
+      if (softmax_bar_or(fail)) break;
+      const int u = ring[n % PP_RING];
+      if (u < 0) break;
+      const PpUnit cur = pp_decode(u, item_first, item_size, item_page0, item_keys, Hkv, nsplit, rep, NCOL);
+      if (cur.nb >= 0) {
+        const int ncols = cur.ncols;
+        // slots this item never fills for its sequences: no shared prefix -> neutral prefix slots
+        if (neutral_n > 0 && cur.page0 == 0 && cur.sp == 0) {
+          for (int k = tid; k < ncols * neutral_n; k += 128) {
+            const int c = k / neutral_n, sl = k % neutral_n;
+            const long long idx = ((long long)(cur.b0 + c / rep) * Hq + cur.hk * rep + c % rep) * nslots + neutral_from + sl;
+            part_ml[idx * 2] = -1e30f;
+            part_ml[idx * 2 + 1] = 0.f;
+          }
+        }
+        if (cur.nb == 0) {
+          if (out != nullptr) {                      // a row without keys (padding of a batch bucket): zeros
+            for (int c = 0; c < ncols; ++c)
+              out[((long long)(cur.b0 + c / rep) * Hq + cur.hk * rep + c % rep) * PP_D + tid] = __float2bfloat16(0.f);
+          } else if (tid < ncols) {
+            const long long idx = ((long long)(cur.b0 + tid / rep) * Hq + cur.hk * rep + tid % rep) * nslots + slot0 + cur.sp;
+            part_ml[idx * 2] = -1e30f;
+            part_ml[idx * 2 + 1] = 0.f;
+          }
+        } else {
+          const uint32_t tO = lane_base + (2 + (nq & 1)) * NPAD;
+          float m_run[NCOL], l_thr[NCOL];
+#pragma unroll
+          for (int c = 0; c < NCOL; ++c) {
+            m_run[c] = -1e30f;
+            l_thr[c] = 0.f;
+          }
+          const int nb = cur.nb;
+          for (int i = 0; i < nb; ++i, ++g) {
+            if (!mbar_wait(&bar_s[g & 1], (uint32_t)((g >> 1) & 1))) {
+              give_up(AXB_ERR_WAIT_TMEM_FULL);
+              fail = true;
+            }
             tc_fence_after();
-            const uint32_t vaddr = kaddr + PP_TILE, paddr = smem_u32(sP);
+            uint32_t sv[NPAD];
+            const uint32_t tSg = lane_base + (uint32_t)(g & 1) * NPAD;
+            tmem_ld_32x16(tSg, sv);
+            if (NPAD == 32) tmem_ld_32x16(tSg + 16, sv + 16);
+            tmem_ld_wait();
+            const bool valid = (cur.blk_begin + i) * PP_PAGE + tid < cur.n_keys;
+            float sc[NCOL];
+            bool over = false;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              umma_f16_ss(tmem_base + NPAD, umma_smem_desc(vaddr + ks * 2048, 16384, 1024),
-                          umma_smem_desc(paddr + (ks >> 2) * (NPAD * 128) + (ks & 3) * 32, 16, 1024), idesc_o,
-                          (i | ks) != 0);
+            for (int c = 0; c < NCOL; ++c) {
+              sc[c] = (valid && c < ncols) ? __uint_as_float(sv[c]) * scale_log2 : -INFINITY;
+              over |= sc[c] > m_run[c] + 8.f;
             }
-            if (i == nb - 1) tc_commit(bar_mma);
+            // one barrier tells every thread whether any score of the block is more than 2^8 above its column's running
+            // maximum, and whether anyone gave up (uniform control flow from here on)
+            const bool slow = softmax_bar_or(over || fail || *abort_flag != 0);
+            if (slow) {
+              quit = softmax_bar_or(fail || *abort_flag != 0);
+              if (quit) break;
+              // exact column maxima over the 128 keys; raise the running maximum where the block exceeds it by > 2^8
+#pragma unroll
+              for (int c = 0; c < NCOL; ++c) {
+                const float wm = warp_max_redux(sc[c]);
+                if (lane == 0) red[warp * NCOL + c] = wm;
+              }
+              softmax_bar_sync();
+              bool changed = false;
+              float alpha[NCOL];
+#pragma unroll
+              for (int c = 0; c < NCOL; ++c) {
+                const float bm = fmaxf(fmaxf(red[c], red[NCOL + c]), fmaxf(red[2 * NCOL + c], red[3 * NCOL + c]));
+                const bool raise = bm > m_run[c] + 8.f;
+                const float mn = raise ? bm : m_run[c];
+                alpha[c] = raise ? ex2_approx(m_run[c] - mn) : 1.f;
+                changed |= raise;
+                m_run[c] = mn;
+                l_thr[c] *= alpha[c];
+              }
+              if (i > 0 && changed) {  // uniform: m_run is identical in every thread
+                // the accumulator holds the products up to the previous block: wait for that one, then rescale
+                if (!mbar_wait(&bar_pv[(g - 1) & 1], (uint32_t)(((g - 1) >> 1) & 1))) {
+                  give_up(AXB_ERR_WAIT_TMEM_FULL);
+                  fail = true;
+                }
+                tc_fence_after();
+                uint32_t o[NPAD];
+                tmem_ld_32x16(tO, o);
+                if (NPAD == 32) tmem_ld_32x16(tO + 16, o + 16);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < NCOL; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c]);
+#pragma unroll
+                for (int g8 = 0; g8 < NCOL / 8; ++g8) {
+                  asm volatile(
+                      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                      ::"r"(tO + g8 * 8), "r"(o[g8 * 8]), "r"(o[g8 * 8 + 1]), "r"(o[g8 * 8 + 2]), "r"(o[g8 * 8 + 3]),
+                      "r"(o[g8 * 8 + 4]), "r"(o[g8 * 8 + 5]), "r"(o[g8 * 8 + 6]), "r"(o[g8 * 8 + 7])
+                      : "memory");
+                }
+                tmem_st_wait();
+              }
+            }
+            // probabilities: the buffer of this parity was read by the product two blocks back, which completed before
+            // this block's S product did (the tensor core runs one CTA's products in issue order)
+            uint8_t* const pb = pbase + (g & 1) * Cfg::QBYTES;
+#pragma unroll
+            for (int c = 0; c < NCOL; ++c) {
+              const float p = ex2_approx(sc[c] - m_run[c]);
+              l_thr[c] += p;
+              if (c < ncols) *reinterpret_cast<__nv_bfloat16*>(pb + pp_sw128(c, pcol)) = __float2bfloat16(p);
+            }
+            fence_async_shared();
+            tc_fence_before();
+            mbar_arrive(&p_ready[g & 1]);
           }
-          __syncwarp();
-        }
-        if (ok) {
-          if (!mbar_wait(bar_mma, ph)) {
-            report_error(status, AXB_ERR_WAIT_TMEM_FULL);
-            ok = false;
+          if (quit) break;
+          // ---- unit epilogue: wait for the last product, then un-normalised partials (or the normalised result)
+          // (one barrier per block parity: the products two blocks back are known to be complete, the one two blocks
+          // ahead cannot have been issued, so the phase parity is unambiguous although most blocks never wait here)
+          if (!mbar_wait(&bar_pv[(g - 1) & 1], (uint32_t)(((g - 1) >> 1) & 1))) {
+            give_up(AXB_ERR_WAIT_TMEM_FULL);
+            fail = true;
           }
-          ph ^= 1;
           tc_fence_after();
-          if (tid == 0) {
-            g_done = g;                 // the unit's last stage is free as well
-            advance_loads(rr);
-          }
-        }
-        ok = __syncthreads_and(ok ? 1 : 0) != 0;
-        if (ok) {
-          // ---- unit epilogue: un-normalised partials. l per column: reduce the per-thread sums over the CTA.
-          float l_tot[NCOL];
+          float* red2 = red + 4 * NCOL;
 #pragma unroll
           for (int c = 0; c < NCOL; ++c) {
             const float ws = warp_sum(l_thr[c]);
-            if (lane == 0) red[warp * NCOL + c] = ws;
+            if (lane == 0) red2[warp * NCOL + c] = ws;
           }
-          __syncthreads();
-#pragma unroll
-          for (int c = 0; c < NCOL; ++c) l_tot[c] = red[c] + red[NCOL + c] + red[2 * NCOL + c] + red[3 * NCOL + c];
+          quit = softmax_bar_or(fail || *abort_flag != 0);       // also orders the row sums above
+          if (quit) break;
           uint32_t o[NPAD];
           tmem_ld_32x16(tO, o);
           if (NPAD == 32) tmem_ld_32x16(tO + 16, o + 16);
           tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(&o_free[nq & 1]);         // the accumulator may be overwritten by the unit after next
 #pragma unroll
           for (int c = 0; c < NCOL; ++c) {
             if (c < ncols) {
+              const float l_tot = red2[c] + red2[NCOL + c] + red2[2 * NCOL + c] + red2[3 * NCOL + c];
               const long long bh = (long long)(cur.b0 + c / rep) * Hq + cur.hk * rep + c % rep;
               if (out != nullptr) {
-                out[bh * PP_D + tid] = __float2bfloat16(l_tot[c] > 0.f ? __uint_as_float(o[c]) / l_tot[c] : 0.f);
+                out[bh * PP_D + tid] = __float2bfloat16(l_tot > 0.f ? __uint_as_float(o[c]) / l_tot : 0.f);
               } else {
                 const long long idx = bh * nslots + slot0 + cur.sp;
                 part_o[idx * PP_D + tid] = __uint_as_float(o[c]);
                 if (tid == 0) {
                   part_ml[idx * 2] = m_run[c];
-                  part_ml[idx * 2 + 1] = l_tot[c];
+                  part_ml[idx * 2 + 1] = l_tot;
                 }
               }
             }
           }
-          tc_fence_before();      // the next unit's first S product overwrites the accumulators read above
-          __syncthreads();
-          tc_fence_after();
-          if (q_unit == rr + 1) qbuf ^= 1;      // the next unit's rows sit in the other buffer
+          ++nq;
         }
       }
+      mbar_arrive(&ring_empty[n % PP_RING]);
     }
-    if (!ok) break;
-    // move on
-    ++rr;
-    u_cur = u_next;
-    cur = nxt;
   }
 
-  // ---- shut down. After an error loads may still be in flight: wait for them (bounded) before the memory goes away.
-  cp_async_wait_all();
-  if (!ok && tid == 0) {
-    for (long long b = g; b < g_issue; ++b) mbar_wait(&full[b % PP_STAGES], (uint32_t)((b / PP_STAGES) & 1));
-  }
+  // ---- shut down: every role has left its loop (on success all loads were consumed; after an error the producer
+  // has waited for the ones in flight)
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 5) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * NPAD);
+    tmem_dealloc(tmem_base, Cfg::TCOLS);
   }
 }
 
@@ -504,6 +593,14 @@ extern "C" int axb_paged_decode_shared_persist(const void* q, long long q_row_st
   rc = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, PP_D, rows, PP_D * 2, 64, PP_PAGE, true);
   if (rc) return rc;
   if ((rc = set_attr<8>()) || (rc = set_attr<32>())) return rc;
+  // query rows as [sequence][head][128]; one box = the rep heads of a kv head for the sequences of one item, 64 dims wide
+  const int rep = Hq / Hkv;
+  const int grp_seqs = 32 / rep < B ? 32 / rep : B;        // a box never exceeds the tensor
+  CUtensorMap tmQ1, tmQg;
+  rc = make_tmap_3d(&tmQ1, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, PP_D, Hq, B, PP_D * 2, q_row_stride * 2, 64, rep, 1, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tmQg, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, PP_D, Hq, B, PP_D * 2, q_row_stride * 2, 64, rep, grp_seqs, true);
+  if (rc) return rc;
   if (cudaMemsetAsync(counters, 0, 2 * sizeof(unsigned int), s) != cudaSuccess) return AXB_LAUNCH_CUDA_ERROR;
   const bool direct = n_groups == 0 && nsplit == 1;          // no prefix items, one split: the result needs no merge
   const int nslots = n_groups == 0 ? nsplit : nsplit + nsplit_p;
@@ -512,8 +609,8 @@ extern "C" int axb_paged_decode_shared_persist(const void* q, long long q_row_st
   const float sl2 = softmax_scale * 1.4426950408889634f;
   // suffix items: one sequence each, slots [0, nsplit); they neutralise the prefix slots of unshared sequences
   const int total_s = B * Hkv * nsplit;
-  paged_decode_persist_kernel<8><<<persist_grid(total_s), 128, PpCfg<8>::SMEM, s>>>(
-      tmK, tmV, (const __nv_bfloat16*)q, q_row_stride, block_table, max_pages, seq_first, seq_one, seq_page0, seq_keys, B,
+  paged_decode_persist_kernel<8><<<persist_grid(total_s), PP_THREADS, PpCfg<8>::SMEM, s>>>(
+      tmK, tmV, tmQ1, 64 * 2 * rep, block_table, max_pages, seq_first, seq_one, seq_page0, seq_keys, B,
       0, nsplit, n_groups == 0 ? 0 : nsplit_p, part_o, part_ml, direct ? (__nv_bfloat16*)out : nullptr, Hq, Hkv, nsplit, nslots,
       sl2, counters, status);
   rc = check_launch();
@@ -521,8 +618,8 @@ extern "C" int axb_paged_decode_shared_persist(const void* q, long long q_row_st
   if (n_groups > 0) {
     // prefix items: one group each, slots [nsplit, nsplit + nsplit_p)
     const int total_p = n_groups * Hkv * nsplit_p;
-    paged_decode_persist_kernel<32><<<persist_grid(total_p), 128, PpCfg<32>::SMEM, s>>>(
-        tmK, tmV, (const __nv_bfloat16*)q, q_row_stride, block_table, max_pages, grp_first, grp_size, grp_zero, grp_keys,
+    paged_decode_persist_kernel<32><<<persist_grid(total_p), PP_THREADS, PpCfg<32>::SMEM, s>>>(
+        tmK, tmV, tmQg, 64 * 2 * rep * grp_seqs, block_table, max_pages, grp_first, grp_size, grp_zero, grp_keys,
         n_groups, nsplit, 0, 0, part_o, part_ml, nullptr, Hq, Hkv, nsplit_p, nslots, sl2, counters + 1, status);
     rc = check_launch();
     if (rc) return rc;

@@ -28,7 +28,7 @@ def _batch(n_rows=4, T=48, vocab=4096):
     return d
 
 
-def _run(cls_path, cfg, world, vocab=4096, save_dir=None):
+def _run(cls_path, cfg, world, vocab=4096, save_dir=None, load_dir=None):
     import importlib
     mod, name = cls_path.rsplit(".", 1)
     cls = getattr(importlib.import_module(mod), name)
@@ -37,6 +37,9 @@ def _run(cls_path, cfg, world, vocab=4096, save_dir=None):
     try:
         wg.init_model()
         data = _batch(vocab=vocab)
+        if load_dir is not None:                   # resume: the forward below runs on the restored parameters
+            wg.load_state(load_dir)
+            return (wg.forward(data).batch["log_probs"],)
         fwd = wg.forward(data)
         data.batch["old_log_probs"] = fwd.batch["log_probs"]
         from axon_b200.driver.driver_utils import process_mini_batch
@@ -95,14 +98,30 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     d = str(tmp_path / "ck")
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, 2, vocab=vocab, save_dir=d)
     assert json.load(open(os.path.join(d, "model_parallel_config.json")))["world_size"] == 2
-    assert os.path.exists(os.path.join(d, "model_world_size_2_rank_1.pt")) and os.path.exists(os.path.join(d, "optim_world_size_2_rank_0.pt"))
+    # the sharded state is one array per parameter in full-model coordinates ...
+    from axon_b200.models.params import FlatParams
+    from axon_b200.utils.state.dist_checkpoint import ShardedTensor, load_sharded, read_metadata
+    dist_dir = os.path.join(d, "dist_ckpt")
+    meta = read_metadata(dist_dir)
+    assert any(k.startswith("optimizer/") for k in meta["tensors"]) and "extra/common" in meta["objects"]
+    host = FlatParams(get_config(preset), "cpu", torch.float32)
+    load_sharded({"model/" + n: ShardedTensor("model/" + n, v, (v.shape[0], v[0].numel() if v.dim() > 1 else 1),
+                                              [((0, 0), (v.shape[0], v[0].numel() if v.dim() > 1 else 1))]) for n, v in host.views.items()}, dist_dir)
     m = build_model_for(get_config(preset), device="cpu", dtype=torch.float32)
     load_hf_weights(m, os.path.join(d, "huggingface"))
+    for n, v in host.views.items():              # ... which an unsharded reader assembles to the exported tensors
+        torch.testing.assert_close(v, m.params.views[n].float(), rtol=0, atol=0, msg=n)
     data = _batch(vocab=vocab)
     for row in range(2):
         n = int(data.batch["attention_mask"][row].sum())
         lp, _ = m.forward(PackedBatch.from_sequences([data.batch["input_ids"][row, :n].to(torch.int32)], "cpu"))
         torch.testing.assert_close(lp[: n - 1], got[3][row, 1:n].float(), rtol=2e-3, atol=2e-3)
+    # resume under the writing layout and - for the tensor-parallel run - under NO model parallelism at all
+    again = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, 2, vocab=vocab, load_dir=d)
+    torch.testing.assert_close(again[0], got[3], rtol=1e-5, atol=1e-5)
+    if kind == "tp":
+        single = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset), 1, vocab=vocab, load_dir=d)
+        torch.testing.assert_close(single[0], got[3], rtol=1e-3, atol=1e-3)
 
 
 @pytest.mark.timeout(900)
