@@ -72,7 +72,8 @@ class ModelConfig:
 
     def to_hf_dict(self) -> dict:
         if "hf_config" in self.extra:            # families described by their own HF config (models/families.py)
-            return dict(self.extra["hf_config"])
+            hf = dict(self.extra["hf_config"])
+            return dict(hf["_nested_config"]) if "_nested_config" in hf else hf
         d = asdict(self)
         d.pop("extra")
         d.update(self.extra)

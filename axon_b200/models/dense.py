@@ -38,6 +38,8 @@ class PackedBatch:
     labels: torch.Tensor         # int32 [T]
     max_seqlen: int = 0
     routermap: torch.Tensor | None = None   # int [T, n_moe_layers, top_k] expert ids chosen by the sampler (-1: none)
+    # vision-language models: pixel_values [patches, patch_dim], image_grid_thw [images, 3], mrope_positions [3, T]
+    multimodal: dict | None = None
 
     @staticmethod
     def from_sequences(seqs: list[torch.Tensor], device) -> "PackedBatch":

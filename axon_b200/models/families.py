@@ -29,7 +29,8 @@ from .config import ModelConfig
 from .params import FlatParams
 
 FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text",
-                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text")
+                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl")
+VISION_LANGUAGE_TYPES = ("qwen2_vl",)
 
 
 # ------------------------------------------------------------------------------------------ small pieces
@@ -285,7 +286,8 @@ class FamilyParams(FlatParams):
         return missing
 
     def to_hf_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
-        return OrderedDict((n, self.views[n]) for n in self.layout)
+        shape_of = getattr(self.spec, "checkpoint_shape", lambda n: None)
+        return OrderedDict((n, self.views[n] if shape_of(n) is None else self.views[n].view(shape_of(n))) for n in self.layout)
 
 
 # ------------------------------------------------------------------------------------------ the model
@@ -294,7 +296,7 @@ class FamilyModel:
 
     def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, hf: dict | None = None):
         self.cfg = cfg
-        self.hf = dict(hf if hf is not None else cfg.extra.get("hf_config", {}))
+        self.hf = dict(cfg.extra.get("hf_config") or hf or {})      # the flattened form (vision-language configs nest the decoder)
         self.kind = self.hf.get("model_type", cfg.model_type)
         assert self.kind in FAMILY_TYPES, f"'{self.kind}' is not one of {FAMILY_TYPES}"
         self.device, self.dtype = torch.device(device), dtype
@@ -341,8 +343,16 @@ class FamilyModel:
             return dict(self.params.views)
         return {n: v.detach().requires_grad_(self.spec.trainable(n)) for n, v in self.params.views.items()}
 
-    def hidden_states(self, W: dict, input_ids, position_ids, cu: list[int], ckpt: bool):
-        x = self.spec.embed(W, input_ids)
+    def hidden_states(self, W: dict, input_ids, position_ids, cu: list[int], ckpt: bool, multimodal: dict | None = None):
+        """``multimodal`` (vision-language families): ``pixel_values`` [patches, patch_dim] and ``image_grid_thw`` [images, 3]
+        of every image of the packed batch in token order, and optionally ``mrope_positions`` [3, T] (else the packed
+        ``position_ids`` serve all three rotary rows, which is exact for text-only sequences)."""
+        if multimodal:
+            x = self.spec.embed(W, input_ids, multimodal)
+            if multimodal.get("mrope_positions") is not None:
+                position_ids = multimodal["mrope_positions"].to(input_ids.device)
+        else:
+            x = self.spec.embed(W, input_ids)
         ctx = {"positions": position_ids, "cu": cu, "model": self}
         for l in range(self.cfg.num_hidden_layers):
             fn = lambda h, l=l: self.spec.layer(W, l, h, ctx)      # noqa: E731
@@ -378,7 +388,7 @@ class FamilyModel:
         with torch.set_grad_enabled(save_for_backward):
             W = self._leaves(save_for_backward)
             ck = save_for_backward and self.recompute == "full"
-            h = self.hidden_states(W, batch.input_ids.long(), batch.position_ids, cu, ck)
+            h = self.hidden_states(W, batch.input_ids.long(), batch.position_ids, cu, ck, getattr(batch, "multimodal", None))
             lp, ent = self.logprob_entropy(W, h, batch.labels, temperature, ck)
         if save_for_backward:
             self._saved = (W, lp, ent)
@@ -398,13 +408,13 @@ class FamilyModel:
             if leaf.grad is not None:
                 self.params.grads[n].add_(leaf.grad.float())
 
-    def logits(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None) -> torch.Tensor:
+    def logits(self, input_ids: torch.Tensor, position_ids: torch.Tensor | None = None, multimodal: dict | None = None) -> torch.Tensor:
         """fp32 logits [T, V] of one sequence (tests, evaluation)."""
         T = input_ids.numel()
         pos = position_ids if position_ids is not None else torch.arange(T, device=input_ids.device)
         with torch.no_grad():
             W = self._leaves(False)
-            h = self.hidden_states(W, input_ids.long(), pos, [0, T], False)
+            h = self.hidden_states(W, input_ids.long(), pos, [0, T], False, multimodal)
             z = F.linear(h, self.spec.head_weight(W)).float()
             if self.spec.final_softcap:
                 z = torch.tanh(z / self.spec.final_softcap) * self.spec.final_softcap
@@ -415,8 +425,10 @@ class FamilyModel:
     def prefill(self, batch, cache, tok_seq, tok_pos, block_table, last_index):
         W = self._leaves(False)
         cu = batch.cu_seqlens.tolist()
-        x = self.spec.embed(W, batch.input_ids.long())
-        ctx = {"positions": batch.position_ids, "cu": cu, "model": self, "cache": cache, "tok_seq": tok_seq.long(),
+        mm = getattr(batch, "multimodal", None)
+        x = self.spec.embed(W, batch.input_ids.long(), mm) if mm else self.spec.embed(W, batch.input_ids.long())
+        rope_pos = mm["mrope_positions"].to(x.device) if mm and mm.get("mrope_positions") is not None else batch.position_ids
+        ctx = {"positions": rope_pos, "cu": cu, "model": self, "cache": cache, "tok_seq": tok_seq.long(),
                "tok_pos": tok_pos.long(), "block_table": block_table, "mode": "prefill"}
         for l in range(self.cfg.num_hidden_layers):
             x = self.spec.layer(W, l, x, ctx)
@@ -1298,7 +1310,166 @@ class _Qwen35(_Qwen3Next):
         return mixed, z, F.linear(h, self.P(W, l, "linear_attn.in_proj_b.weight")), F.linear(h, self.P(W, l, "linear_attn.in_proj_a.weight"))
 
 
-_SPECS = {"deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
+class _Qwen2VL(_Spec):
+    """Qwen2-VL: a Qwen2 decoder (q / k / v biases) whose rotary angles come from three position rows (temporal,
+    height, width: text tokens carry the same number in all three), fed with the embeddings of a vision transformer
+    at the image placeholder tokens. The tower works on flattened patches [N, C * t * p * p] in merge-window order:
+    linear patch embedding (the checkpoint's Conv3d kernel flattened), blocks of LayerNorm - full attention inside
+    each frame with 2-D rotary angles (half of a head's pairs follow the patch row, half the column) - LayerNorm -
+    QuickGELU MLP, then LayerNorm and a two-layer MLP over each window of merge^2 patches.
+    Reference: axon/models/transformers/qwen2_vl.py (packed forward of the HF model), HF modeling_qwen2_vl.py."""
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        self.nh, self.nkv = hf["num_attention_heads"], hf.get("num_key_value_heads", hf["num_attention_heads"])
+        self.D = hf.get("head_dim") or self.H // self.nh
+        self.F = hf["intermediate_size"]
+        self.sections = list(self.rope_params.get("mrope_section") or [self.D // 2, 0, 0])
+        v = dict(hf["vision_config"])
+        self.v = v
+        self.vE, self.vL, self.vH = v["embed_dim"], v["depth"], v["num_heads"]
+        self.vF = int(v["embed_dim"] * v.get("mlp_ratio", 4))
+        self.merge = v.get("spatial_merge_size", 2)
+        self.patch_dim = v.get("in_channels", 3) * v.get("temporal_patch_size", 2) * v["patch_size"] ** 2
+        self.image_token, self.video_token = hf.get("image_token_id"), hf.get("video_token_id")
+
+    def layout(self):
+        lay = OrderedDict()
+        E, m2 = self.vE, self.merge ** 2
+        lay["model.visual.patch_embed.proj.weight"] = (E, self.patch_dim)
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            for n in ("norm1", "norm2"):
+                lay[p + n + ".weight"], lay[p + n + ".bias"] = (E,), (E,)
+            lay[p + "attn.qkv.weight"], lay[p + "attn.qkv.bias"] = (3 * E, E), (3 * E,)
+            lay[p + "attn.proj.weight"], lay[p + "attn.proj.bias"] = (E, E), (E,)
+            lay[p + "mlp.fc1.weight"], lay[p + "mlp.fc1.bias"] = (self.vF, E), (self.vF,)
+            lay[p + "mlp.fc2.weight"], lay[p + "mlp.fc2.bias"] = (E, self.vF), (E,)
+        lay["model.visual.merger.ln_q.weight"], lay["model.visual.merger.ln_q.bias"] = (E,), (E,)
+        lay["model.visual.merger.mlp.0.weight"], lay["model.visual.merger.mlp.0.bias"] = (E * m2, E * m2), (E * m2,)
+        lay["model.visual.merger.mlp.2.weight"], lay["model.visual.merger.mlp.2.bias"] = (self.H, E * m2), (self.H,)
+        lay["model.language_model.embed_tokens.weight"] = (self.V, self.H)
+        for l in range(self.L):
+            p = f"model.language_model.layers.{l}."
+            for n, rows in (("q_proj", self.nh * self.D), ("k_proj", self.nkv * self.D), ("v_proj", self.nkv * self.D)):
+                lay[p + f"self_attn.{n}.weight"], lay[p + f"self_attn.{n}.bias"] = (rows, self.H), (rows,)
+            lay[p + "self_attn.o_proj.weight"] = (self.H, self.nh * self.D)
+            lay[p + "mlp.gate_proj.weight"], lay[p + "mlp.up_proj.weight"] = (self.F, self.H), (self.F, self.H)
+            lay[p + "mlp.down_proj.weight"] = (self.H, self.F)
+            lay[p + "input_layernorm.weight"], lay[p + "post_attention_layernorm.weight"] = (self.H,), (self.H,)
+        lay["model.language_model.norm.weight"] = (self.H,)
+        if not self.tied:
+            lay["lm_head.weight"] = (self.V, self.H)
+        return lay
+
+    def checkpoint_shape(self, name):
+        # the checkpoint stores the patch embedding as a Conv3d kernel [E, C, t, p, p]; it is used flattened here
+        if name == "model.visual.patch_embed.proj.weight":
+            return (self.vE, self.v.get("in_channels", 3), self.v.get("temporal_patch_size", 2), self.v["patch_size"], self.v["patch_size"])
+        return None
+
+    def init_kind(self, name):
+        if ".norm" in name or "ln_q" in name or name.endswith("layernorm.weight"):
+            return "zeros" if name.endswith(".bias") else "ones"
+        return super().init_kind(name)
+
+    def P(self, W, l, name):
+        return W[f"model.language_model.layers.{l}.{name}"]
+
+    def final_norm(self, W, x):
+        return rms_norm(x, W["model.language_model.norm.weight"], self.eps)
+
+    def head_weight(self, W):
+        return W["model.language_model.embed_tokens.weight"] if self.tied else W["lm_head.weight"]
+
+    # ---- vision tower
+    def vision_rotary(self, grid_thw, device):
+        hd = self.vE // self.vH
+        inv = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)))      # hd / 4 frequencies
+        ms, rows = self.merge, []
+        for t, h, w in grid_thw.tolist():
+            hi = torch.arange(h)[:, None].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).reshape(-1)
+            wi = torch.arange(w)[None, :].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).reshape(-1)
+            rows.append(torch.cat([hi[:, None].float() * inv[None], wi[:, None].float() * inv[None]], dim=1).repeat(t, 1))
+        ang = torch.cat(rows).to(device)
+        ang = torch.cat([ang, ang], dim=1)                                                           # [N, hd]
+        return ang.cos(), ang.sin()
+
+    def vision(self, W, patches, grid_thw):
+        """[N, patch_dim] patches of all images -> [N / merge^2, H] embeddings in token order."""
+        E, Hh = self.vE, self.vH
+        hd = E // Hh
+        x = linear(patches.to(W["model.visual.patch_embed.proj.weight"].dtype), W["model.visual.patch_embed.proj.weight"])
+        cos, sin = self.vision_rotary(grid_thw, x.device)
+        segs, a = [], 0
+        for t, h, w in grid_thw.tolist():
+            for _ in range(int(t)):
+                segs.append((a, a + int(h) * int(w)))
+                a += int(h) * int(w)
+        assert a == x.shape[0], f"{x.shape[0]} patches for grids that describe {a}"
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            h1 = F.layer_norm(x, (E,), W[p + "norm1.weight"], W[p + "norm1.bias"], 1e-6)
+            q, k, v = (linear(h1, W[p + "attn.qkv.weight"]) + W[p + "attn.qkv.bias"]).view(-1, 3, Hh, hd).unbind(1)
+            q = (q.float() * cos[:, None] + rotate_half(q.float()) * sin[:, None]).to(x.dtype)
+            k = (k.float() * cos[:, None] + rotate_half(k.float()) * sin[:, None]).to(x.dtype)
+            outs = []
+            for s0, s1 in segs:                                 # full attention inside each frame
+                o = F.scaled_dot_product_attention(q[s0:s1].transpose(0, 1)[None], k[s0:s1].transpose(0, 1)[None],
+                                                   v[s0:s1].transpose(0, 1)[None])
+                outs.append(o[0].transpose(0, 1).reshape(s1 - s0, E))
+            x = x + linear(torch.cat(outs), W[p + "attn.proj.weight"]) + W[p + "attn.proj.bias"]
+            h2 = F.layer_norm(x, (E,), W[p + "norm2.weight"], W[p + "norm2.bias"], 1e-6)
+            m = linear(h2, W[p + "mlp.fc1.weight"]) + W[p + "mlp.fc1.bias"]
+            x = x + linear(m * torch.sigmoid(1.702 * m), W[p + "mlp.fc2.weight"]) + W[p + "mlp.fc2.bias"]
+        x = F.layer_norm(x, (E,), W["model.visual.merger.ln_q.weight"], W["model.visual.merger.ln_q.bias"], 1e-6)
+        x = x.view(-1, E * self.merge ** 2)
+        x = F.gelu(linear(x, W["model.visual.merger.mlp.0.weight"]) + W["model.visual.merger.mlp.0.bias"])
+        return linear(x, W["model.visual.merger.mlp.2.weight"]) + W["model.visual.merger.mlp.2.bias"]
+
+    def embed(self, W, ids, multimodal=None):
+        x = W["model.language_model.embed_tokens.weight"][ids]
+        if multimodal and multimodal.get("pixel_values") is not None and multimodal["pixel_values"].numel():
+            vis = self.vision(W, multimodal["pixel_values"].to(x.device), multimodal["image_grid_thw"]).to(x.dtype)
+            where = torch.zeros_like(ids, dtype=torch.bool)
+            for tok in (self.image_token, self.video_token):
+                if tok is not None:
+                    where |= ids == tok
+            idx = torch.nonzero(where).flatten()
+            assert idx.numel() == vis.shape[0], f"{idx.numel()} placeholder tokens for {vis.shape[0]} vision embeddings"
+            x = x.index_copy(0, idx, vis)
+        return x
+
+    # ---- decoder
+    def rope(self, which):
+        return rope_frequencies({"rope_theta": self.rope_params["rope_theta"]}, self.D, self.hf.get("max_position_embeddings", 32768))
+
+    def rotary(self, ctx):
+        pos = ctx["positions"]
+        if pos.dim() == 1:                                      # text only: the three rows coincide
+            return ctx["model"]._rope("default", pos)
+        key = ("mrope", id(pos))
+        if ctx.get("_mrope_key") != key:
+            from .vision import mrope_tables
+            c, s = mrope_tables(pos, self.D, float(self.rope_params["rope_theta"]), self.sections, device=pos.device)
+            ctx["_mrope"], ctx["_mrope_key"] = (torch.cat([c, c], -1), torch.cat([s, s], -1)), key
+        return ctx["_mrope"]
+
+    def layer(self, W, l, x, ctx):
+        T = x.shape[0]
+        h = rms_norm(x, self.P(W, l, "input_layernorm.weight"), self.eps)
+        cos, sin = self.rotary(ctx)
+        q = (linear(h, self.P(W, l, "self_attn.q_proj.weight")) + self.P(W, l, "self_attn.q_proj.bias")).view(T, self.nh, self.D)
+        k = (linear(h, self.P(W, l, "self_attn.k_proj.weight")) + self.P(W, l, "self_attn.k_proj.bias")).view(T, self.nkv, self.D)
+        v = (linear(h, self.P(W, l, "self_attn.v_proj.weight")) + self.P(W, l, "self_attn.v_proj.bias")).view(T, self.nkv, self.D)
+        o = attend(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, ctx, l, self.D ** -0.5)
+        x = x + linear(o.reshape(T, self.nh * self.D), self.P(W, l, "self_attn.o_proj.weight"))
+        h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps)
+        return x + linear(F.silu(linear(h, self.P(W, l, "mlp.gate_proj.weight"))) * linear(h, self.P(W, l, "mlp.up_proj.weight")),
+                          self.P(W, l, "mlp.down_proj.weight"))
+
+
+_SPECS = {"qwen2_vl": _Qwen2VL, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
           "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen35, "qwen3_5_moe_text": _Qwen35}
 
 
@@ -1307,6 +1478,11 @@ def family_config(hf: dict) -> ModelConfig:
     """The ``ModelConfig`` view of a family's HF config: the fields the engines read (cache geometry, vocabulary,
     special tokens); everything else stays in ``extra['hf_config']`` for the family's spec."""
     mt = hf["model_type"]
+    if mt in VISION_LANGUAGE_TYPES and "text_config" in hf:
+        # vision-language checkpoints nest the decoder's fields: lift them, keep the nested form for export
+        nested = dict(hf)
+        hf = {**{k: v for k, v in hf["text_config"].items() if k != "model_type"}, **{k: v for k, v in hf.items() if k != "text_config"}}
+        hf["_nested_config"] = nested
     nh = hf["num_attention_heads"]
     if mt in ("deepseek_v3", "glm4_moe_lite", "glm_moe_dsa"):
         # the paged cache holds expanded keys (nope + rope) and values per head

@@ -110,12 +110,13 @@ def schedule_from_config(lr_scheduler, lr_scheduler_args, lr: float, fallback_to
 class _Packing:
     """Index maps between the padded [B,T] view and one packed micro-batch."""
 
-    def __init__(self, input_ids: torch.Tensor, attention_mask: torch.Tensor, device):
+    def __init__(self, input_ids: torch.Tensor, attention_mask: torch.Tensor, device, data: DataProto | None = None):
         lens = attention_mask.sum(1).to(torch.long).cpu().numpy()
         B, T = input_ids.shape
         rows = np.repeat(np.arange(B), lens)
         cols = np.concatenate([np.arange(n) for n in lens]) if B else np.zeros(0, dtype=np.int64)
         self.lens = lens
+        self._rows, self._cols = rows, cols
         self.total = int(lens.sum())
         flat = torch.from_numpy(rows * T + cols).to(device)
         ids = input_ids.to(device).reshape(-1)[flat].to(torch.int32)
@@ -134,6 +135,32 @@ class _Packing:
         self.src = torch.from_numpy(np.nonzero(keep)[0]).to(device)
         self.dst = flat[self.src] + 1
         self.shape = (B, T)
+        if data is not None:
+            self.batch.multimodal = self._multimodal(data, device)
+
+    def _multimodal(self, data: DataProto, device) -> dict | None:
+        """Vision inputs of the rows in packed order: every row's ``multi_modal_inputs`` entry (pixel_values,
+        image_grid_thw; videos likewise) concatenated, and the three rotary rows of ``position_ids`` ([B, 3, T], or
+        [B, 4, T] with a leading text row) gathered at the packed tokens."""
+        mm = data.non_tensor_batch.get("multi_modal_inputs") if data.non_tensor_batch else None
+        if mm is None or not any(isinstance(m, dict) and len(m) for m in mm):
+            return None
+        pix, grids = [], []
+        for b, n in enumerate(self.lens):
+            m = mm[b] if isinstance(mm[b], dict) else {}
+            if n == 0:
+                continue
+            for pk, gk in (("pixel_values", "image_grid_thw"), ("pixel_values_videos", "video_grid_thw")):
+                if m.get(pk) is not None and len(m[pk]):
+                    pix.append(torch.as_tensor(m[pk]))
+                    grids.append(torch.as_tensor(m[gk]).reshape(-1, 3))
+        out = {"pixel_values": torch.cat(pix).to(device) if pix else None,
+               "image_grid_thw": torch.cat(grids) if grids else None, "mrope_positions": None}
+        pos = data.batch.get("position_ids") if hasattr(data.batch, "get") else None
+        if pos is not None and pos.dim() == 3:
+            p3 = pos[:, -3:, :]                                  # [B, 3, T]
+            out["mrope_positions"] = p3[torch.from_numpy(self._rows), :, torch.from_numpy(self._cols)].t().contiguous().to(device)
+        return out
 
     def to_padded(self, packed: torch.Tensor) -> torch.Tensor:
         out = torch.zeros(self.shape[0] * self.shape[1], dtype=packed.dtype, device=packed.device)
@@ -267,7 +294,7 @@ class PolicyEngine:
         temp = temperature if temperature is not None else data.meta_info.get("temperature", self.temperature)
         mbs, idx = prepare_dynamic_batch(data, self.max_tokens, dp_group=self.micro_group, strict_equal=self.micro_group is not None)
         lps, ents = [], []
-        packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device) for mb in mbs]
+        packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device, mb) for mb in mbs]
         if hasattr(self.model, "forward_many"):      # pipeline stages: micro-batches stream through the stages
             results = self.model.forward_many([pk.batch for pk in packs], temp)
         else:
@@ -339,7 +366,7 @@ class PolicyEngine:
             if self.world > 1:
                 dist.all_reduce(cnt, group=self.pg)
             self.model.mtp_scale = self.mtp_loss_coef / max(float(cnt), 1.0)
-        packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device) for mb in mbs]
+        packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device, mb) for mb in mbs]
         if hasattr(self.model, "train_many"):
             # pipeline stages: the model orders forwards and backwards of the micro-batches (1F1B) and calls
             # the loss on the last stage only; its metrics are then handed to the other stages

@@ -292,3 +292,133 @@ def test_driver_trains_a_family_model_end_to_end(tmp_path, preset):
         drv.shutdown()
     logs = [json.loads(line) for line in open(tmp_path / "axon-agent_ppo.jsonl")]
     assert [r["step"] for r in logs][:2] == [1, 2] and logs[0]["data"]["batch/sampler_logprobs_diff_mean"] < 1e-4
+
+
+def test_qwen2_vl_matches_transformers_with_an_image():
+    """Vision tower + three-row rotary decoder against HF Qwen2-VL on a prompt with one image and one text-only prompt:
+    logits, the gradient of a log-prob loss through decoder AND tower, and the HF state-dict round trip."""
+    try:
+        from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    except Exception:
+        pytest.skip("transformers has no Qwen2-VL")
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.dense import PackedBatch
+    from axon_b200.models.families import FamilyModel
+    torch.manual_seed(0)
+    cfg = Qwen2VLConfig(text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                         vocab_size=300, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}, max_position_embeddings=512,
+                                         tie_word_embeddings=False),
+                        vision_config=dict(depth=2, embed_dim=32, hidden_size=64, num_heads=2, mlp_ratio=2, in_channels=3, patch_size=4,
+                                           temporal_patch_size=2, spatial_merge_size=2),
+                        image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    ref = Qwen2VLForConditionalGeneration(cfg).float().eval()
+    grid = torch.tensor([[1, 4, 6]])                               # one image: 24 patches -> 6 placeholder tokens
+    pix = torch.randn(24, 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 17, 292] + [290] * 6 + [293, 44, 9, 120, 33, 7]])
+    with torch.no_grad():
+        types = (ids == 290).int()                                 # 1 marks image placeholder tokens
+        want = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+        got_pos = ref.model.get_rope_index(ids, types, image_grid_thw=grid, attention_mask=torch.ones_like(ids))[0][:, 0]      # [3, T]
+    mcfg = ModelConfig.from_hf_dict(cfg.to_dict())
+    assert mcfg.to_hf_dict()["text_config"]["hidden_size"] == 64          # the nested form survives for export
+    m = FamilyModel(mcfg, device="cpu", dtype=torch.float32)
+    m.load_state_dict(ref.state_dict())
+    mm = {"pixel_values": pix, "image_grid_thw": grid, "mrope_positions": got_pos}
+    z = m.logits(ids[0].to(torch.int32), multimodal=mm)
+    assert (z - want).abs().max() < 2e-4, (z - want).abs().max()
+    # our own position builder gives the rows HF computes
+    from axon_b200.models.vision import mrope_position_ids
+
+    class _Proc:
+        image_token_id, video_token_id, vision_start_token_id = 290, 291, 292
+
+        class image_processor:
+            merge_size = 2
+    mine = mrope_position_ids(_Proc, ids, torch.ones_like(ids), image_grid_thw=grid)
+    assert torch.equal(mine.reshape(3, -1).long(), got_pos.long())
+    # text-only: plain positions serve all three rows
+    t_ids = torch.randint(0, 280, (1, 12))
+    with torch.no_grad():
+        want_t = ref(input_ids=t_ids).logits[0].float()
+    assert (m.logits(t_ids[0].to(torch.int32)) - want_t).abs().max() < 2e-4
+    # gradients through decoder and tower
+    batch = PackedBatch.from_sequences([ids[0]], "cpu")
+    batch.multimodal = mm
+    lp, _ = m.forward(batch, 1.0, save_for_backward=True)
+    g = torch.linspace(0.5, 1.5, lp.numel())
+    g[-1] = 0
+    m.backward(g)
+    out = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+    lp_ref = torch.log_softmax(out[:-1], -1).gather(1, ids[0, 1:, None])[:, 0]
+    assert (lp[:-1] - lp_ref.detach()).abs().max() < 2e-4
+    (lp_ref * g[:-1]).sum().backward()
+    sd = dict(ref.named_parameters())
+    for name in ("model.visual.blocks.0.attn.qkv.weight", "model.visual.merger.mlp.2.weight", "model.language_model.layers.1.self_attn.k_proj.bias",
+                 "model.language_model.layers.0.mlp.down_proj.weight", "model.visual.patch_embed.proj.weight"):
+        a, b = m.params.grads[name], sd[name].grad.reshape(m.params.grads[name].shape)
+        assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
+    # round trip in the checkpoint's shapes
+    ref2 = Qwen2VLForConditionalGeneration(cfg).float()
+    ref2.load_state_dict({k: v.clone() for k, v in m.params.to_hf_state_dict().items()})
+    with torch.no_grad():
+        assert torch.equal(ref2(input_ids=t_ids).logits, ref(input_ids=t_ids).logits)
+
+
+def test_policy_engine_trains_a_vision_language_model_on_padded_rows_with_images():
+    """Rows with and without images through ``PolicyEngine``: per-row ``multi_modal_inputs`` and the [B, 4, T] position
+    rows of the driver are packed for the model; log-probs equal the per-sequence forward, and an update moves the
+    vision tower as well as the decoder."""
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.families import FamilyModel
+    from axon_b200.models.vision import mrope_position_ids
+    from axon_b200.protocol import DataProto
+    from axon_b200.trainer.policy import OptimConfig, PolicyEngine
+    hf = {"model_type": "qwen2_vl", "image_token_id": 290, "video_token_id": 291, "vision_start_token_id": 292, "vision_end_token_id": 293,
+          "text_config": dict(model_type="qwen2_vl_text", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                              num_key_value_heads=2, vocab_size=300, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}, rope_theta=10000.0,
+                              max_position_embeddings=512, tie_word_embeddings=False, rms_norm_eps=1e-6),
+          "vision_config": dict(depth=1, embed_dim=32, hidden_size=64, num_heads=2, mlp_ratio=2, in_channels=3, patch_size=4,
+                                temporal_patch_size=2, spatial_merge_size=2)}
+    m = FamilyModel(ModelConfig.from_hf_dict(hf), device="cpu", dtype=torch.float32)
+    m.init_random(0.05, seed=2)
+    g = torch.Generator().manual_seed(1)
+    T = 20
+    rows = [[5, 17, 292] + [290] * 6 + [293, 44, 9, 120, 33, 7], torch.randint(2, 280, (12,), generator=g).tolist(),
+            [292] + [290] * 4 + [293, 8, 9, 10]]
+    grids = [torch.tensor([[1, 4, 6]]), None, torch.tensor([[1, 4, 4]])]
+    pix = [torch.randn(24, 96, generator=g), None, torch.randn(16, 96, generator=g)]
+    ids = torch.zeros(3, T, dtype=torch.long)
+    att = torch.zeros(3, T, dtype=torch.long)
+    for b, r in enumerate(rows):
+        ids[b, :len(r)], att[b, :len(r)] = torch.tensor(r), 1
+
+    class _Proc:
+        image_token_id, video_token_id, vision_start_token_id = 290, 291, 292
+
+        class image_processor:
+            merge_size = 2
+    text = (att.cumsum(1) - 1) * att
+    pos = torch.stack([torch.cat([text[b:b + 1], mrope_position_ids(_Proc, ids[b], att[b], image_grid_thw=grids[b]).reshape(3, T)]) for b in range(3)])
+    mm = np.empty(3, dtype=object)
+    for b in range(3):
+        mm[b] = {} if grids[b] is None else {"pixel_values": pix[b], "image_grid_thw": grids[b]}
+    resp = att.clone().float()
+    resp[:, :2] = 0
+    d = DataProto.from_dict({"input_ids": ids, "attention_mask": att, "position_ids": pos, "response_mask": resp,
+                             "advantages": torch.randn(3, 1, generator=g).expand(3, T) * resp}, {"multi_modal_inputs": mm})
+    d.batch["valid_token_count"] = resp.sum().expand(3).clone()
+    eng = PolicyEngine(m, OptimConfig(lr=5e-3, weight_decay=0.0, grad_clip=1.0), max_token_len_per_gpu=32)     # several micro-batches
+    lp = eng.forward(d).batch["log_probs"]
+    for b, r in enumerate(rows):
+        n = len(r)
+        one = {"pixel_values": pix[b], "image_grid_thw": grids[b], "mrope_positions": pos[b, 1:, :n]} if grids[b] is not None else None
+        z = m.logits(ids[b, :n].to(torch.int32), multimodal=one)
+        want = torch.log_softmax(z[:-1], -1).gather(1, ids[b, 1:n, None])[:, 0]
+        assert (lp[b, 1:n] - want).abs().max() < 1e-4, b
+    d.batch["old_log_probs"] = lp
+    before = {k: m.params[k].clone() for k in ("model.visual.blocks.0.attn.qkv.weight", "model.language_model.layers.1.mlp.up_proj.weight")}
+    eng.forward_backward(copy.deepcopy(d), "ppo", {})
+    st = eng.optim_step()
+    assert np.isfinite(st["grad_norm"]) and st["grad_norm"] > 0
+    for k, v in before.items():
+        assert (m.params[k] - v).abs().max() > 0, k
