@@ -437,11 +437,13 @@ class FamilyModel:
         return torch.tanh(z / self.spec.final_softcap) * self.spec.final_softcap if self.spec.final_softcap else z
 
     @torch.no_grad()
-    def decode(self, tokens, positions, cache, block_table, seq_lens, shared=None):
+    def decode(self, tokens, positions, cache, block_table, seq_lens, shared=None, rope_positions=None):
+        """``rope_positions``: rotary position of every token where it differs from its place in the cache (sequences
+        whose prompt held images: the rotary count resumes after the prompt's largest row)."""
         W = self._leaves(False)
         B = tokens.numel()
         x = self.spec.embed(W, tokens.long())
-        ctx = {"positions": positions, "cu": list(range(B + 1)), "model": self, "cache": cache,
+        ctx = {"positions": positions if rope_positions is None else rope_positions, "cu": list(range(B + 1)), "model": self, "cache": cache,
                "tok_seq": torch.arange(B, device=tokens.device), "tok_pos": positions.long(), "block_table": block_table,
                "mode": "decode", "seq_lens": seq_lens}
         for l in range(self.cfg.num_hidden_layers):
@@ -452,6 +454,20 @@ class FamilyModel:
 
     def flops_per_token(self, seqlen: int) -> float:
         return 6.0 * self.params.numel
+
+    supports_cuda_graph = False         # decode reads sequence lengths on the host (per-sequence gathers from the pages)
+
+    def rotary_rows(self, prompt_ids, image_data: dict) -> torch.Tensor:
+        """Three rotary rows [3, n] of a prompt whose placeholder tokens stand for ``image_data`` (vision-language families)."""
+        assert self.kind in VISION_LANGUAGE_TYPES, f"'{self.kind}' takes no vision inputs"
+        from types import SimpleNamespace
+        from .vision import mrope_position_ids
+        sp = self.spec
+        proc = SimpleNamespace(image_token_id=sp.image_token, video_token_id=sp.video_token,
+                               image_processor=SimpleNamespace(merge_size=sp.merge))
+        ids = torch.as_tensor(list(prompt_ids), dtype=torch.long)
+        g = lambda k: torch.as_tensor(image_data[k]).reshape(-1, 3) if image_data.get(k) is not None else None      # noqa: E731
+        return mrope_position_ids(proc, ids, None, g("image_grid_thw"), g("video_grid_thw"), image_data.get("second_per_grid_ts")).reshape(3, -1)
 
 
 # ------------------------------------------------------------------------------------------ KV cache helpers

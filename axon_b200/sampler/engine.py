@@ -41,6 +41,9 @@ class _Seq:
     cached: int = 0            # leading tokens whose keys / values are already in the pages (prefix cache hit, earlier chunks)
     chunk_end: int = 0         # the prefill call in progress covers tokens [cached, chunk_end)
     route_chunks: list = field(default_factory=list)    # routed-experts capture: int16 [n, layers, top-k] pieces in token order
+    mm: dict | None = None     # vision inputs of the prompt: pixel_values [patches, patch_dim], image_grid_thw [images, 3]
+    mrope: object = None       # rotary rows [3, prompt length] of a prompt with vision inputs
+    rope_delta: int = 0        # rotary position of generated token i = prompt length + i + rope_delta
 
 
 class GenerationEngine:
@@ -67,7 +70,7 @@ class GenerationEngine:
         self.stats = dict(prefill_tokens=0, decode_tokens=0, decode_steps=0, preempted=0)
         # CUDA-graph decode: one captured graph per batch-size bucket (re-captured after every wake_up,
         # because the KV pool moves). Disabled on CPU.
-        self.use_cuda_graph = self.device.type == "cuda"
+        self.use_cuda_graph = self.device.type == "cuda" and getattr(model, "supports_cuda_graph", True)
         # n samples of one prompt share its KV pages and its prefill (not for models that keep per-sequence recurrent state)
         self.share_prompts = not getattr(model, "has_recurrent_state", False)
         # "processed": log-prob under the distribution actually drawn from (after top-k / top-p, the reference
@@ -103,20 +106,30 @@ class GenerationEngine:
         self.max_pages_per_seq = (self.cfg.max_position_embeddings + PAGE - 1) // PAGE
 
     # ------------------------------------------------------------------ request API
-    def add_request(self, prompt_ids, params: SamplingParams) -> int:
+    def add_request(self, prompt_ids, params: SamplingParams, image_data: dict | None = None) -> int:
+        """``image_data`` (vision-language models): the processor's ``pixel_values`` / ``image_grid_thw`` (and the video
+        pair) for the placeholder tokens of ``prompt_ids``; requests that pass the SAME dict object share their prompt
+        pages (n samples of one prompt)."""
         rid = next(self._rid)
         seq = _Seq(rid, list(map(int, prompt_ids)), params)
         seq.out.prompt_len = len(seq.prompt)
+        if image_data:
+            assert hasattr(self.model, "rotary_rows"), "this model takes no vision inputs"
+            seq.mm = image_data
+            seq.mrope = self.model.rotary_rows(seq.prompt, image_data)                   # [3, n]
+            seq.rope_delta = int(seq.mrope.max()) + 1 - len(seq.prompt)
         self.waiting.append(seq)
         return rid
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running or self.prefilling)
 
-    def generate(self, prompts, params) -> list[TokenOutput]:
-        """Blocking helper: run all prompts to completion; ``params`` is one SamplingParams or a list."""
+    def generate(self, prompts, params, image_data=None) -> list[TokenOutput]:
+        """Blocking helper: run all prompts to completion; ``params`` is one SamplingParams or a list, ``image_data``
+        None or one entry (dict or None) per prompt."""
         plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
-        rids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        ilist = image_data if image_data is not None else [None] * len(prompts)
+        rids = [self.add_request(p, sp, im) for p, sp, im in zip(prompts, plist, ilist)]
         while self.has_unfinished():
             self.step()
         return [self.finished.pop(r) for r in rids]
@@ -246,7 +259,7 @@ class GenerationEngine:
             s = self.waiting[0]
             n = len(s.prompt) + len(s.out.token_ids)  # a preempted sequence re-prefills its output too
             need = (n + 1 + PAGE - 1) // PAGE
-            key = tuple(s.prompt) if (self.share_prompts and not s.out.token_ids) else None
+            key = (tuple(s.prompt), id(s.mm)) if (self.share_prompts and not s.out.token_ids) else None
             lead = leaders.get(key) if key is not None else None
             held: list[int] = []
             if lead is None and self.enable_prefix_caching and self._cached_ok and not s.out.token_ids:
@@ -335,6 +348,23 @@ class GenerationEngine:
         complete = [s.chunk_end >= len(f) for s, f in zip(seqs, full)]
         last = ends[torch.tensor(complete)].to(self.device) if any(complete) else ends[:1].to(self.device)
         bt = self._block_table(seqs)
+        if any(s.mm is not None for s in seqs):
+            # vision inputs in packed order, and three rotary rows per token (text-only sequences repeat their positions;
+            # tokens generated before a preemption continue after the prompt's largest rotary position)
+            rows, pix, grids = [], [], []
+            for s, n in zip(seqs, lens):
+                if s.mm is None:
+                    rows.append(torch.arange(n)[None].expand(3, n))
+                    continue
+                extra = torch.arange(n - len(s.prompt))[None].expand(3, -1) + len(s.prompt) + s.rope_delta
+                rows.append(torch.cat([s.mrope, extra], dim=1))
+                for pk, gk in (("pixel_values", "image_grid_thw"), ("pixel_values_videos", "video_grid_thw")):
+                    if s.mm.get(pk) is not None and len(s.mm[pk]):
+                        pix.append(torch.as_tensor(s.mm[pk]))
+                        grids.append(torch.as_tensor(s.mm[gk]).reshape(-1, 3))
+            batch.multimodal = {"pixel_values": torch.cat(pix).to(self.device) if pix else None,
+                                "image_grid_thw": torch.cat(grids) if grids else None,
+                                "mrope_positions": torch.cat(rows, dim=1).to(self.device)}
         if self.capture_routing:
             self.model.last_routing = None
         if any(past):
@@ -565,7 +595,11 @@ class GenerationEngine:
         bt = self._block_table(seqs)
         if self.capture_routing:
             self.model.last_routing = None
-        logits = self.model.decode(tokens, pos, self.cache, bt, pos + 1)
+        if any(s.rope_delta for s in seqs):
+            delta = torch.tensor([s.rope_delta for s in seqs], dtype=torch.int32).to(self.device)
+            logits = self.model.decode(tokens, pos, self.cache, bt, pos + 1, rope_positions=pos + delta)
+        else:
+            logits = self.model.decode(tokens, pos, self.cache, bt, pos + 1)
         if self.capture_routing:
             rt = self._take_routing()
             if rt is not None:

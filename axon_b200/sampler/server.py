@@ -121,10 +121,14 @@ class SamplerServer:
     def _drain_inbox(self) -> None:
         while True:
             try:
-                prompt, params, fut = self._inbox.get_nowait()
+                prompt, params, fut, images = self._inbox.get_nowait()
             except queue.Empty:
                 return
-            rid = self.engine.add_request(prompt, params)
+            try:
+                rid = self.engine.add_request(prompt, params, images) if images else self.engine.add_request(prompt, params)
+            except Exception as e:  # noqa: BLE001 - a bad request (e.g. images for a text model) fails alone
+                fut.set_exception(e)
+                continue
             self._futures[rid] = fut
 
     def _resolve(self) -> None:
@@ -136,18 +140,35 @@ class SamplerServer:
                 fut.set_result(out)
 
     # ------------------------------------------------------------------ requests
-    def submit(self, prompt_ids, params: SamplingParams | dict | None = None) -> Future:
+    def submit(self, prompt_ids, params: SamplingParams | dict | None = None, image_data=None) -> Future:
+        """``image_data``: vision inputs of the prompt for vision-language models - the processor's output
+        (``pixel_values`` + ``image_grid_thw``) or a list of images (PIL, data / file URLs, OpenAI ``image_url`` items)
+        that the server's processor turns into it."""
         if self.error is not None:
             raise RuntimeError(f"sampler server '{self.name}' has failed") from self.error
         if not isinstance(params, SamplingParams):
             params = params_from_dict(params)
         fut: Future = Future()
-        self._inbox.put((list(prompt_ids), params, fut))
+        self._inbox.put((list(prompt_ids), params, fut, self.prepare_images(image_data)))
         self._wake.set()
         return fut
 
-    async def generate(self, prompt_ids, params=None) -> TokenOutput:
-        return await asyncio.wrap_future(self.submit(prompt_ids, params))
+    def prepare_images(self, image_data):
+        if not image_data:
+            return None
+        if isinstance(image_data, dict) and "pixel_values" in image_data:
+            import torch
+            return {k: torch.as_tensor(v) for k, v in image_data.items() if v is not None}
+        proc = getattr(self, "processor", None)
+        ip = getattr(proc, "image_processor", None)
+        if ip is None:
+            raise ValueError("raw images need a processor with an image_processor on the sampler server; send pixel_values + image_grid_thw")
+        from ..utils.openai_client import load_images
+        out = ip(images=load_images(image_data), return_tensors="pt")
+        return {"pixel_values": out["pixel_values"], "image_grid_thw": out["image_grid_thw"]}
+
+    async def generate(self, prompt_ids, params=None, image_data=None) -> TokenOutput:
+        return await asyncio.wrap_future(self.submit(prompt_ids, params, image_data))
 
     def num_pending(self) -> int:
         return len(self._futures) + self._inbox.qsize()
@@ -244,7 +265,11 @@ class SamplerServer:
             if not isinstance(prompt, list) or (prompt and not isinstance(prompt[0], int)):
                 raise HTTPException(400, "prompt must be a list of token ids")
             n = int(body.get("n", 1))
-            outs = await asyncio.gather(*(server.generate(prompt, body) for _ in range(n)))
+            try:
+                images = server.prepare_images(body.get("image_data"))      # one object: the n samples share the prompt's pages
+            except ValueError as e:
+                raise HTTPException(400, str(e))
+            outs = await asyncio.gather(*(server.generate(prompt, body, images) for _ in range(n)))
             choices = []
             for i, o in enumerate(outs):
                 text = server.tokenizer.decode(o.token_ids) if server.tokenizer is not None else ""

@@ -60,16 +60,20 @@ class SamplingClient:
         return self._http[key]
 
     # ------------------------------------------------------------------ sampling
-    async def _one(self, addr, prompt_ids, params: dict) -> dict:
+    async def _one(self, addr, prompt_ids, params: dict, image_data=None) -> dict:
         if isinstance(addr, str):
             body = {"prompt": list(prompt_ids), "logprobs": 1, "return_token_ids": True, **params}
+            if image_data:
+                from ..utils.openai_client import serialize_images_for_http
+                body["image_data"] = ({k: (v.tolist() if hasattr(v, "tolist") else v) for k, v in image_data.items()}
+                                      if isinstance(image_data, dict) else serialize_images_for_http(image_data))
             r = await self._client().post(addr.rstrip("/") + "/v1/completions", json=body)
             r.raise_for_status()
             ch = r.json()["choices"][0]
             return {"token_ids": ch["token_ids"], "logprobs": ch["logprobs"]["token_logprobs"],
                     "token_strs": ch["logprobs"].get("tokens") or [], "finish_reason": ch.get("finish_reason"),
                     "stop_reason": ch.get("stop_reason"), "moe_routermap": decode_routed_experts(ch.get("routed_experts"))}
-        out = await addr.generate(prompt_ids, params)
+        out = await (addr.generate(prompt_ids, params, image_data) if image_data else addr.generate(prompt_ids, params))
         strs = []
         tok = self.tokenizer or getattr(addr, "tokenizer", None)
         if tok is not None:
@@ -92,7 +96,7 @@ class SamplingClient:
                 async with self._sem(idx):
                     self._inflight[idx] += 1
                     try:
-                        r = await self._one(addr, prompt, p)
+                        r = await self._one(addr, prompt, p, image_data)
                     finally:
                         self._inflight[idx] -= 1
                 acc["token_ids"] += r["token_ids"]

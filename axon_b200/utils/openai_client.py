@@ -31,6 +31,28 @@ def serialize_images_for_http(images: list[Any]) -> list[dict]:
     return out
 
 
+def load_images(items: list[Any]) -> list[Any]:
+    """The inverse of ``serialize_images_for_http``: PIL images from PIL images, ``data:`` URLs, file paths / ``file://``
+    URLs and OpenAI ``image_url`` items (remote URLs are refused: a sampler does not fetch from the network)."""
+    import base64
+    import io
+    from PIL import Image
+    out = []
+    for it in items or []:
+        if isinstance(it, dict):
+            it = (it.get("image_url") or {}).get("url") if it.get("type") == "image_url" else it.get("url") or it.get("image")
+        if isinstance(it, str):
+            if it.startswith("data:"):
+                out.append(Image.open(io.BytesIO(base64.b64decode(it.split(",", 1)[1]))).convert("RGB"))
+            elif it.startswith(("http://", "https://")):
+                raise ValueError("remote image URLs are not fetched by the sampler; send a data: URL")
+            else:
+                out.append(Image.open(it[len("file://"):] if it.startswith("file://") else it).convert("RGB"))
+        else:
+            out.append(it)
+    return out
+
+
 def _url(address: str, path: str) -> str:
     base = address if address.startswith("http") else f"http://{address}"
     return base.rstrip("/") + path

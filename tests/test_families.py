@@ -422,3 +422,56 @@ def test_policy_engine_trains_a_vision_language_model_on_padded_rows_with_images
     assert np.isfinite(st["grad_norm"]) and st["grad_norm"] > 0
     for k, v in before.items():
         assert (m.params[k] - v).abs().max() > 0, k
+
+
+def test_sampler_generates_from_a_prompt_with_an_image():
+    """Greedy generation through the paged engine for a prompt with an image (and a text-only neighbour in the same
+    batch): every sampled token's log-prob equals the full forward over prompt + output with the rotary rows continued
+    after the image; two samples of the same request object share the prompt's pages."""
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.families import FamilyModel
+    from axon_b200.sampler.engine import GenerationEngine
+    from axon_b200.sampler.params import SamplingParams
+    hf = {"model_type": "qwen2_vl", "image_token_id": 290, "video_token_id": 291, "vision_start_token_id": 292, "vision_end_token_id": 293,
+          "text_config": dict(model_type="qwen2_vl_text", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                              num_key_value_heads=2, vocab_size=300, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}, rope_theta=10000.0,
+                              max_position_embeddings=512, tie_word_embeddings=False, rms_norm_eps=1e-6, eos_token_id=299),
+          "vision_config": dict(depth=1, embed_dim=32, hidden_size=64, num_heads=2, mlp_ratio=2, in_channels=3, patch_size=4,
+                                temporal_patch_size=2, spatial_merge_size=2)}
+    m = FamilyModel(ModelConfig.from_hf_dict(hf), device="cpu", dtype=torch.float32)
+    m.init_random(0.08, seed=4)
+    g = torch.Generator().manual_seed(2)
+    img = {"pixel_values": torch.randn(24, 96, generator=g), "image_grid_thw": torch.tensor([[1, 4, 6]])}
+    p_img = [5, 17, 292] + [290] * 6 + [293, 44, 9]
+    p_txt = torch.randint(2, 280, (9,), generator=g).tolist()
+    eng = GenerationEngine(m, num_pages=16, max_num_seqs=4)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = eng.generate([p_img, p_txt, p_img], sp, image_data=[img, None, img])
+    assert eng.stats.get("shared_prompt_seqs", 0) == 1 and outs[0].token_ids == outs[2].token_ids
+    assert eng.cache.num_free() == 16
+    # full forward over prompt + output, rotary rows as the engine continues them
+    full = p_img + outs[0].token_ids
+    rows = m.rotary_rows(p_img, img)
+    delta = int(rows.max()) + 1 - len(p_img)
+    assert delta < 0                                              # six placeholders advance the rotary count by less than six
+    pos = torch.cat([rows, (torch.arange(len(outs[0].token_ids)) + len(p_img) + delta)[None].expand(3, -1)], dim=1)
+    z = m.logits(torch.tensor(full, dtype=torch.int32), multimodal={**img, "mrope_positions": pos})
+    lp = torch.log_softmax(z, -1)
+    for i, (tok, got) in enumerate(zip(outs[0].token_ids, outs[0].logprobs)):
+        row = len(p_img) - 1 + i
+        assert int(lp[row].argmax()) == tok
+        assert abs(float(lp[row, tok]) - got) < 1e-4
+    zt = torch.log_softmax(m.logits(torch.tensor(p_txt + outs[1].token_ids, dtype=torch.int32)), -1)
+    for i, (tok, got) in enumerate(zip(outs[1].token_ids, outs[1].logprobs)):
+        assert abs(float(zt[len(p_txt) - 1 + i, tok]) - got) < 1e-4
+    # the same request through the server front end (processor output as plain lists, as the HTTP body carries it)
+    from axon_b200.sampler.server import SamplerServer
+    srv = SamplerServer(eng, name="vl").start()
+    try:
+        fut = srv.submit(p_img, {"temperature": 0.0, "max_tokens": 6, "ignore_eos": True},
+                         image_data={"pixel_values": img["pixel_values"].tolist(), "image_grid_thw": img["image_grid_thw"].tolist()})
+        assert fut.result(timeout=60).token_ids == outs[0].token_ids
+        with pytest.raises(ValueError, match="processor"):
+            srv.submit(p_img, {}, image_data=["data:image/png;base64,AAAA"])
+    finally:
+        srv.stop()
