@@ -224,6 +224,73 @@ p2p_copy_plan_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, PeerPt
 struct QuantTile {
   int desc, block_row, block_col, pad;
 };
+// One 128 x 128 (or ragged edge) tile: bf16 -> e4m3 with one scale = amax / 448, by 256 threads.
+// Full tiles whose rows are 16-byte aligned on both sides stay in registers between the maximum and the cast:
+// thread t holds 8 vectors of 8 elements (rows t / 16 + 16 k), reads each once and stores 8-byte vectors.
+__device__ __forceinline__ void quant_tile_128(const __nv_bfloat16* __restrict__ src, long long src_stride,
+                                               unsigned char* __restrict__ dst, long long dst_stride, int nr, int nc,
+                                               float* red, float* s_scale, float* scale_out) {
+  const bool fast = nr == 128 && nc == 128 && (src_stride & 7) == 0 && (dst_stride & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0;
+  uint4 v[8];
+  float amax = 0.f;
+  if (fast) {
+    const int r = threadIdx.x >> 4, cv = (threadIdx.x & 15) * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = *reinterpret_cast<const uint4*>(src + (long long)(r + 16 * k) * src_stride + cv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < nr * 128; i += blockDim.x) {
+      const int r = i >> 7, cc = i & 127;
+      if (cc < nc) amax = fmaxf(amax, fabsf(__bfloat162float(src[(long long)r * src_stride + cc])));
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = red[0];
+    for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
+    const float scale = (a > 0.f && isfinite(a)) ? a / 448.f : 1.f;
+    *s_scale = scale;
+    *scale_out = scale;
+  }
+  __syncthreads();
+  const float inv = 1.f / *s_scale;
+  if (fast) {
+    const int r = threadIdx.x >> 4, cv = (threadIdx.x & 15) * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+      uint32_t w[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float2 f0 = __bfloat1622float2(h[2 * j]), f1 = __bfloat1622float2(h[2 * j + 1]);
+        const __nv_fp8x4_e4m3 q(make_float4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv));
+        w[j] = *reinterpret_cast<const uint32_t*>(&q);
+      }
+      *reinterpret_cast<uint2*>(dst + (long long)(r + 16 * k) * dst_stride + cv) = make_uint2(w[0], w[1]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < nr * 128; i += blockDim.x) {
+      const int r = i >> 7, cc = i & 127;
+      if (cc < nc) {
+        const __nv_fp8_e4m3 f(__bfloat162float(src[(long long)r * src_stride + cc]) * inv);
+        dst[(long long)r * dst_stride + cc] = *reinterpret_cast<const unsigned char*>(&f);
+      }
+    }
+  }
+  __syncthreads();      // red / s_scale are reused by the caller's next tile
+}
+
 __global__ void __launch_bounds__(256)
 p2p_quant_plan_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, PeerPtrs dst_scales,
                       const CopyDesc* __restrict__ descs, const QuantTile* __restrict__ tiles, int n_tiles) {
@@ -234,35 +301,10 @@ p2p_quant_plan_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, PeerP
     const CopyDesc& c = descs[q.desc];
     const int r0 = q.block_row * 128, c0 = q.block_col * 128;
     const int nr = min(128, c.rows - r0), nc = min(128, c.cols - c0);
-    float amax = 0.f;
-    for (int i = threadIdx.x; i < nr * 16; i += blockDim.x) {   // 16 vectors of 8 per 128-wide row
-      const int r = i >> 4, cv = (i & 15) * 8;
-      const __nv_bfloat16* s = src + c.src_off + (long long)(r0 + r) * c.src_stride + c0 + cv;
-      for (int k = 0; k < 8 && cv + k < nc; ++k) amax = fmaxf(amax, fabsf(__bfloat162float(s[k])));
-    }
-    amax = warp_max(amax);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float a = red[0];
-      for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
-      const float scale = (a > 0.f && isfinite(a)) ? a / 448.f : 1.f;
-      s_scale = scale;
-      reinterpret_cast<float*>(dst_scales.p[c.dst_rank])[c.dst_scale_off + (long long)q.block_row * c.scale_cols + q.block_col] = scale;
-    }
-    __syncthreads();
-    const float inv = 1.f / s_scale;
-    unsigned char* t0 = reinterpret_cast<unsigned char*>(dst.p[c.dst_rank]);
-    for (int i = threadIdx.x; i < nr * 16; i += blockDim.x) {
-      const int r = i >> 4, cv = (i & 15) * 8;
-      const __nv_bfloat16* s = src + c.src_off + (long long)(r0 + r) * c.src_stride + c0 + cv;
-      unsigned char* t = t0 + c.dst_off + (long long)(r0 + r) * c.dst_stride + c0 + cv;
-      for (int k = 0; k < 8 && cv + k < nc; ++k) {
-        const __nv_fp8_e4m3 f(__bfloat162float(s[k]) * inv);
-        t[k] = *reinterpret_cast<const unsigned char*>(&f);
-      }
-    }
-    __syncthreads();
+    quant_tile_128(src + c.src_off + (long long)r0 * c.src_stride + c0, c.src_stride,
+                   reinterpret_cast<unsigned char*>(dst.p[c.dst_rank]) + c.dst_off + (long long)r0 * c.dst_stride + c0, c.dst_stride,
+                   nr, nc, red, &s_scale,
+                   reinterpret_cast<float*>(dst_scales.p[c.dst_rank]) + c.dst_scale_off + (long long)q.block_row * c.scale_cols + q.block_col);
   }
 }
 
@@ -274,30 +316,8 @@ fp8_block_quant_kernel(const __nv_bfloat16* __restrict__ x, unsigned char* __res
   __shared__ float s_scale;
   const int bc = (cols + 127) / 128;
   const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 128;
-  const int nr = min(128, rows - r0), nc = min(128, cols - c0);
-  float amax = 0.f;
-  for (int i = threadIdx.x; i < nr * 128; i += blockDim.x) {
-    const int r = i >> 7, cc = i & 127;
-    if (cc < nc) amax = fmaxf(amax, fabsf(__bfloat162float(x[(long long)(r0 + r) * ldx + c0 + cc])));
-  }
-  amax = warp_max(amax);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float a = red[0];
-    for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
-    s_scale = (a > 0.f && isfinite(a)) ? a / 448.f : 1.f;
-    scales[(long long)blockIdx.y * bc + blockIdx.x] = s_scale;
-  }
-  __syncthreads();
-  const float inv = 1.f / s_scale;
-  for (int i = threadIdx.x; i < nr * 128; i += blockDim.x) {
-    const int r = i >> 7, cc = i & 127;
-    if (cc < nc) {
-      const __nv_fp8_e4m3 f(__bfloat162float(x[(long long)(r0 + r) * ldx + c0 + cc]) * inv);
-      y[(long long)(r0 + r) * ldy + c0 + cc] = *reinterpret_cast<const unsigned char*>(&f);
-    }
-  }
+  quant_tile_128(x + (long long)r0 * ldx + c0, ldx, y + (long long)r0 * ldy + c0, ldy, min(128, rows - r0), min(128, cols - c0), red,
+                 &s_scale, scales + (long long)blockIdx.y * bc + blockIdx.x);
 }
 
 }  // namespace axb
