@@ -188,7 +188,8 @@ def sample(logits, temperature=None, top_k=None, top_p=None, seed: int = 0, coun
             if t <= 0:
                 toks[b] = int(lp[b].argmax())
             else:
-                g = torch.Generator().manual_seed((seed * 1000003 + b * 7919 + (int(counters[b]) if counters is not None else 0)) % (2 ** 63))
+                # with counters the draw depends on (seed, counter) only, not on the row the sequence occupies
+                g = torch.Generator().manual_seed((seed * 1000003 + (int(counters[b]) if counters is not None else b * 7919)) % (2 ** 63))
                 toks[b] = int(torch.multinomial(lp[b].exp(), 1, generator=g))
         if logprobs_mode == "full":
             lp = _ref_process(logits, temperature, None, None)

@@ -97,6 +97,11 @@ class GenerationEngine:
         # one CTA per SM the per-CTA start-up of the extra prefix / suffix items costs as much as the shared tiles
         # save once responses are a few pages long (measured end to end); the kernel pays off for long shared
         # prefixes with short tails and is kept selectable.
+        # Speculative decoding with n-gram drafts (prompt lookup): up to this many tokens that followed the latest earlier
+        # occurrence of the sequence's last tokens are proposed and verified in one pass over [last token | drafts]
+        # against the cached prefix. 0 = off. Needs a model with cached-prefix prefill.
+        self.speculative_ngram = 0
+        self.speculative_ngram_match = 3          # longest suffix tried first; shorter ones down to one token
         self.cascade_attention = False
         self.cascade_min_batch = 48
         self._graphs: dict[int, dict] = {}
@@ -571,7 +576,88 @@ class GenerationEngine:
             elif len(s.out.token_ids) >= sp.max_tokens:
                 self._finish(s, "length")
 
+    # ------------------------------------------------------------------ speculative decoding (n-gram drafts)
+    def _ngram_draft(self, hist: list, budget: int) -> list:
+        """Tokens that followed the most recent earlier occurrence of the history's suffix (longest suffix first)."""
+        n = len(hist)
+        for m in range(min(self.speculative_ngram_match, n - 1), 0, -1):
+            tail = hist[n - m:]
+            for start in range(n - m - 1, -1, -1):
+                if hist[start:start + m] == tail:
+                    return hist[start + m:start + m + budget]
+        return []
+
+    def _speculate(self, seqs) -> set:
+        """Verify n-gram drafts of the sequences that have one; returns the ids of the sequences handled here.
+        Position i of a verified run is sampled with the parameters and the random counter plain decoding would use for
+        that token, so an accepted draft token IS the token plain decoding would have produced; the first sampled token
+        that differs from its draft replaces it and ends the run. Every verified sequence gains at least one token."""
+        from ..ops import paged as P
+        work = []
+        for s in seqs:
+            if s.params.repetition_penalty != 1.0 or s.rope_delta:
+                continue
+            budget = min(self.speculative_ngram, s.params.max_tokens - len(s.out.token_ids) - 1)
+            if budget <= 0:
+                continue
+            d = self._ngram_draft(s.prompt + s.out.token_ids, budget)
+            if not d:
+                continue
+            need = (s.length + 1 + len(d) + PAGE - 1) // PAGE - len(s.pages)
+            if need > 0:
+                if self.cache.num_free() - len(self.running) < need:
+                    continue                      # no room for the draft's keys: this sequence decodes normally
+                s.pages.extend(self.cache.alloc(need))
+            work.append((s, d))
+        if not work:
+            return set()
+        toks = [torch.tensor([s.last_token] + d, dtype=torch.int32) for s, d in work]
+        batch = PackedBatch.from_sequences(toks, self.device)
+        lens = [int(t.numel()) for t in toks]
+        past = [s.length for s, _ in work]
+        batch.position_ids = batch.position_ids + torch.cat([torch.full((n,), p, dtype=torch.int32) for n, p in zip(lens, past)]).to(self.device)
+        batch.max_seqlen = max(p + n for p, n in zip(past, lens))
+        tok_seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(lens)]).to(self.device)
+        rows = torch.arange(sum(lens), device=self.device)
+        logits = self.model.prefill(batch, self.cache, tok_seq, batch.position_ids, self._block_table([s for s, _ in work]), rows,
+                                    past_lens=past)
+        rep = [s for (s, _), n in zip(work, lens) for _ in range(n)]
+        t, k, p, _ = self._sampling_tensors(rep)
+        ctr = torch.tensor([len(s.out.token_ids) + i + 7919 * (s.rid + 1) for (s, _), n in zip(work, lens) for i in range(n)],
+                           dtype=torch.int32).to(self.device)
+        out_t, out_lp = P.sample(logits, t, k, p, seed=self.seed, counters=ctr, logprobs_mode=self.logprobs_mode)
+        out_t, out_lp = out_t.cpu().tolist(), out_lp.cpu().tolist()
+        off = 0
+        for (s, d), n in zip(work, lens):
+            accepted = 0
+            for i in range(n):
+                tok = out_t[off + i]
+                self._record([s], [tok], [out_lp[off + i]])
+                s.length += 1
+                if s.done or i >= len(d) or tok != d[i]:
+                    break
+                accepted += 1
+            off += n
+            self.stats["spec_draft_tokens"] = self.stats.get("spec_draft_tokens", 0) + len(d)
+            self.stats["spec_accepted_tokens"] = self.stats.get("spec_accepted_tokens", 0) + accepted
+            self.stats["decode_tokens"] += accepted + 1
+        self.stats["spec_verify_steps"] = self.stats.get("spec_verify_steps", 0) + 1
+        return {id(s) for s, _ in work}
+
     def _decode(self) -> None:
+        everyone = self.running
+        if self.speculative_ngram > 0 and self._cached_ok and not self.capture_routing:
+            handled = self._speculate(everyone)
+            if handled:
+                rest = [s for s in everyone if id(s) not in handled]
+                self.running = rest                   # the plain path below sees only the sequences without a draft
+                if rest:
+                    self._decode_plain()
+                self.running = [s for s in everyone if not s.done and (id(s) in handled or s in self.running)]
+                return
+        self._decode_plain()
+
+    def _decode_plain(self) -> None:
         seqs = self.running
         # make room for the token about to be written
         for s in seqs:

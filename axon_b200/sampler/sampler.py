@@ -100,6 +100,14 @@ class SamplerWorker(Worker, DistProfilerExtension):
         self.engine.logprobs_mode = str(_get(scfg, "logprobs_mode", "processed"))
         self.engine.enable_prefix_caching = bool(_get(scfg, "enable_prefix_caching", False))
         self.engine.enable_chunked_prefill = bool(_get(scfg, "enable_chunked_prefill", True))
+        spec = _get(scfg, "speculative_config", None) or {}
+        spec = spec.to_dict() if hasattr(spec, "to_dict") else dict(spec)
+        if spec:
+            method = str(spec.get("method", "ngram"))
+            if method != "ngram":
+                raise ValueError(f"speculative_config.method={method!r}: only 'ngram' (prompt lookup) drafts are built")
+            self.engine.speculative_ngram = int(spec.get("num_speculative_tokens", 4))
+            self.engine.speculative_ngram_match = int(spec.get("prompt_lookup_max", 3))
         if _get(cfg, "moe_replay", False) and getattr(self.model.cfg, "num_experts", 0) > 0:
             self.engine.enable_routing_capture(True)      # outputs carry the routed experts for the trainer to replay
         max_len = _get(scfg, "max_model_len", None)

@@ -138,6 +138,10 @@ def parse_args(argv=None):
     ap.add_argument("--mean-response", type=float, default=1500.0)
     ap.add_argument("--micro-batch-tokens", type=int, default=8192)
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--via-driver", action="store_true",
+                    help="diagnostic: the same model through train_agent (driver, worker groups, Engine, programs) and through the "
+                         "single-process runner on fixed-length responses; reports both rates")
+    ap.add_argument("--fixed-response", type=int, default=512, help="--via-driver: response tokens per sample")
     ap.add_argument("--ab-nccl", action="store_true",
                     help="N > 1: after the timed steps run one extra step with the NCCL optimizer path and report its time")
     return ap.parse_args(argv)
@@ -158,6 +162,10 @@ def main() -> None:
     if args.impl == "reference":
         from baseline.ref_arm import run_reference_arm
         run_reference_arm(args, T_PROCESS_START, ClockSampler, plan_steps, synthetic_inputs, METRIC)
+        return
+    if args.via_driver:
+        from axon_b200.driver.via_driver_bench import run_via_driver
+        run_via_driver(args, T_PROCESS_START, ClockSampler)
         return
     if args.topology == "disaggregated":
         from axon_b200.driver.disaggregated_bench import run_disaggregated

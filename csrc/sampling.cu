@@ -176,7 +176,9 @@ sample_kernel(const float* __restrict__ logits, long long ldl, int V, const floa
     norm = block_reduce_sum(fs, red);
   }
   if (threadIdx.x == 0) {
-    const float u = uniform01(seed, (uint32_t)b, counters ? (uint32_t)counters[b] : 0u);
+    // with per-row counters (request id and token index folded in by the caller) the draw does not depend on the row a
+    // sequence happens to occupy in the batch
+    const float u = uniform01(seed, counters ? 0u : (uint32_t)b, counters ? (uint32_t)counters[b] : 0u);
     float target = u * total, cum = 0.f;
     int t = 0, last_ne = 0;
     bool found = false;

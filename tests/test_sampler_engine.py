@@ -243,3 +243,40 @@ def test_prefix_caching_and_chunked_prefill_gpu():
     _prefix_and_chunk_run("cuda", torch.bfloat16, 0.12, exact=False)
     from axon_b200.ops import _common as C
     C.check_status()
+
+
+def _speculative_run(device, dtype, exact):
+    """N-gram speculative decoding returns what plain decoding returns (greedy and sampled), accepts drafts on
+    repetitive text and reports how many."""
+    cfg = tiny_qwen3() if device == "cpu" else tiny_gpu()
+    model = _make(cfg, device, dtype)
+    g = torch.Generator().manual_seed(7)
+    motif = torch.randint(2, cfg.vocab_size, (12,), generator=g).tolist()
+    prompts = [motif * 6, torch.randint(2, cfg.vocab_size, (50,), generator=g).tolist(), (motif[:5] * 9)[:40]]
+    for temp in (0.0, 0.7):
+        sp = SamplingParams(temperature=temp, max_tokens=40, ignore_eos=True)
+        plain = GenerationEngine(model, num_pages=24, max_num_seqs=8, seed=3)
+        want = plain.generate(prompts, sp)
+        spec = GenerationEngine(model, num_pages=24, max_num_seqs=8, seed=3)
+        spec.speculative_ngram = 4
+        got = spec.generate(prompts, sp)
+        assert spec.cache.num_free() == 24
+        assert spec.stats["spec_draft_tokens"] > 0 and spec.stats["spec_verify_steps"] > 0
+        for a, b in zip(want, got):
+            assert len(b.token_ids) == 40 and len(b.logprobs) == 40
+            if exact:
+                assert a.token_ids == b.token_ids, temp
+                assert (torch.tensor(a.logprobs) - torch.tensor(b.logprobs)).abs().max().item() < 1e-4
+        assert 0 <= spec.stats["spec_accepted_tokens"] <= spec.stats["spec_draft_tokens"]
+    return spec
+
+
+def test_ngram_speculative_decoding_matches_plain_decoding_cpu():
+    _speculative_run("cpu", torch.float32, True)
+
+
+@pytest.mark.gpu
+def test_ngram_speculative_decoding_gpu():
+    _speculative_run("cuda", torch.bfloat16, False)
+    from axon_b200.ops import _common as C
+    C.check_status()
