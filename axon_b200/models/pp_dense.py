@@ -37,18 +37,25 @@ def stage_layers(num_layers: int, stages: int, stage: int) -> range:
     return range(lo, lo + base + (1 if stage < rem else 0))
 
 
+def stage_keeps(cfg: ModelConfig, stages: int, stage: int):
+    """Predicate over parameter names: does ``stage`` hold this parameter?"""
+    keep = tuple(f"model.layers.{l}." for l in stage_layers(cfg.num_hidden_layers, stages, stage))
+
+    def holds(name: str) -> bool:
+        if name.startswith("model.layers."):
+            return name.startswith(keep) if keep else False
+        if name == "model.embed_tokens.weight":
+            return stage == 0 or (cfg.tie_word_embeddings and stage == stages - 1)      # tied: the last stage's head reads it too
+        return stage == stages - 1         # final norm, head, value head
+    return holds
+
+
 def stage_layout(cfg: ModelConfig, stages: int, stage: int):
     lay = param_layout(cfg)
-    keep = {f"model.layers.{l}." for l in stage_layers(cfg.num_hidden_layers, stages, stage)}
+    holds = stage_keeps(cfg, stages, stage)
     out = type(lay)()
     for name, shape in lay.items():
-        if name.startswith("model.layers."):
-            if any(name.startswith(p) for p in keep):
-                out[name] = shape
-        elif name == "model.embed_tokens.weight":
-            if stage == 0 or (cfg.tie_word_embeddings and stage == stages - 1):      # tied: the last stage's head reads it too
-                out[name] = shape
-        elif stage == stages - 1:          # final norm, head, value head
+        if holds(name):
             out[name] = shape
     return out
 
@@ -105,17 +112,11 @@ class PipelineContext:
         return t
 
 
-class PPDenseModel(DenseModel):
-    def __init__(self, cfg: ModelConfig, pp: PipelineContext, device="cuda", dtype=torch.bfloat16):
-        assert cfg.num_experts == 0, "pipeline stages are built for dense models"
-        if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
-            assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
-        assert pp.world <= cfg.num_hidden_layers
-        self.pp = pp
-        self.stage, self.stages = pp.rank, pp.world
-        params = FlatParams(cfg, torch.device(device), dtype, layout=stage_layout(cfg, self.stages, self.stage))
-        super().__init__(cfg, device, dtype, params=params)
-        self.layers = stage_layers(cfg.num_hidden_layers, self.stages, self.stage)
+class PipelineSchedule:
+    """The stage-to-stage protocol and the schedules, for any model that provides the pieces of one micro-batch on its
+    stage: ``_layers_fwd(batch, inp, save) -> (x, delta, state)``, ``_head_fwd(x, delta, batch, temperature, state) ->
+    (logprob, entropy)`` over the whole micro-batch (last stage), ``_state_bwd(state, upstream) -> d(stream) | None`` and
+    ``_stream_shape(batch)``; plus ``pp`` (PipelineContext), ``stage``, ``stages``, ``params``, ``device``, ``dtype``."""
 
     @property
     def first(self) -> bool:
@@ -124,81 +125,6 @@ class PPDenseModel(DenseModel):
     @property
     def last(self) -> bool:
         return self.stage == self.stages - 1
-
-    def load_full_state(self, full_views: dict) -> None:
-        for name, dst in self.params.views.items():
-            dst.copy_(full_views[name].to(dst.device).to(dst.dtype))
-
-    def replicated_names(self) -> list[str]:
-        return []
-
-    def replicated_ranges(self):
-        return []
-
-    # Tied embeddings: the table lives on the first stage (lookup) and on the last (output head). Both copies start
-    # equal, their gradients are summed over the two stages before the optimizer, so they stay equal.
-    def _shares_embedding(self) -> bool:
-        return self.cfg.tie_word_embeddings and self.stages > 1 and (self.first or self.last)
-
-    def sync_replicated_grads(self) -> None:
-        if self._shares_embedding() and self.params.grad_flat is not None:
-            group = self.pp.ends_group if self.stages > 2 else self.pp.group
-            dist.all_reduce(self.params.grads["model.embed_tokens.weight"], group=group)
-
-    def duplicate_ranges(self) -> list[tuple[int, int]]:
-        """Ranges of the flat gradient that another stage holds as well (counted once in the global norm):
-        reported by the last stage only."""
-        if self._shares_embedding() and self.last:
-            o, n = self.params.offsets["model.embed_tokens.weight"]
-            return [(o, o + n)]
-        return []
-
-    # ------------------------------------------------------------------ the pieces of one micro-batch
-    def _layers_fwd(self, batch: PackedBatch, inp, save: bool):
-        """``inp`` = (x, delta) from the previous stage, None on the first. Returns (x, delta, state)."""
-        from ..ops import activation as A
-        c = self.cfg
-        tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
-        if self.first:
-            x, delta = A.embedding_fwd(batch.input_ids, self.weights["model.embed_tokens.weight"]), None
-        else:
-            x, delta = inp
-        kept = []
-        for l in self.layers:
-            x, delta, saved = self.layer_fwd(l, x, delta, batch, tables, keep=save)
-            if save:
-                kept.append(saved)
-        return x, delta, dict(batch=batch, tables=tables, layer_inputs=kept)
-
-    def _head_fwd(self, x, delta, batch: PackedBatch, temperature: float, state: dict):
-        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], self.cfg.rms_norm_eps, delta=delta)
-        lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), batch.labels, temperature)
-        state.update(hf=hf, rstd_f=rstd_f, xf=xf, lse=lse, ent=ent, temperature=temperature)
-        return lp, ent
-
-    def _state_bwd(self, s: dict, upstream):
-        """``upstream``: (g_logprob, g_entropy) on the last stage, d(stream) from the next stage otherwise.
-        Returns d(stream) for the previous stage (None on the first, which ends in the embedding)."""
-        batch, tables = s["batch"], s["tables"]
-        if self.last:
-            g_logprob, g_entropy = upstream
-            g_lp = None if g_logprob is None else g_logprob.float().contiguous()
-            g_ent = None if g_entropy is None else g_entropy.float().contiguous()
-            dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), batch.labels, s["lse"], s["ent"], g_lp, g_ent,
-                                s["temperature"], dweight=self.head_grad())
-            dx = N.rmsnorm_bwd(dhf, s["xf"], self.weights["model.norm.weight"], s["rstd_f"], self._wgrad("model.norm.weight"))
-        else:
-            dx = upstream
-        kept = s["layer_inputs"]
-        for l in reversed(self.layers):
-            dx = self.layer_bwd(l, kept.pop(), dx, batch, tables)
-        if self.first:
-            self._embed_bwd(batch, dx)
-            return None
-        return dx
-
-    def _stream_shape(self, batch: PackedBatch):
-        return (batch.input_ids.numel(), self.cfg.hidden_size)
 
     def _recv_fwd(self, batch: PackedBatch):
         if self.first:
@@ -309,6 +235,94 @@ class PPDenseModel(DenseModel):
     def share_from_last(self, obj):
         """Hand a (picklable) result of the last stage to every stage."""
         return self.pp.share_object_from_last(obj)
+
+
+class PPDenseModel(PipelineSchedule, DenseModel):
+    def __init__(self, cfg: ModelConfig, pp: PipelineContext, device="cuda", dtype=torch.bfloat16):
+        assert cfg.num_experts == 0, "pipeline stages are built for dense models"
+        if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
+            assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
+        assert pp.world <= cfg.num_hidden_layers
+        self.pp = pp
+        self.stage, self.stages = pp.rank, pp.world
+        params = FlatParams(cfg, torch.device(device), dtype, layout=stage_layout(cfg, self.stages, self.stage))
+        super().__init__(cfg, device, dtype, params=params)
+        self.layers = stage_layers(cfg.num_hidden_layers, self.stages, self.stage)
+
+    def load_full_state(self, full_views: dict) -> None:
+        for name, dst in self.params.views.items():
+            dst.copy_(full_views[name].to(dst.device).to(dst.dtype))
+
+    def replicated_names(self) -> list[str]:
+        return []
+
+    def replicated_ranges(self):
+        return []
+
+    # Tied embeddings: the table lives on the first stage (lookup) and on the last (output head). Both copies start
+    # equal, their gradients are summed over the two stages before the optimizer, so they stay equal.
+    def _shares_embedding(self) -> bool:
+        return self.cfg.tie_word_embeddings and self.stages > 1 and (self.first or self.last)
+
+    def sync_replicated_grads(self) -> None:
+        if self._shares_embedding() and self.params.grad_flat is not None:
+            group = self.pp.ends_group if self.stages > 2 else self.pp.group
+            dist.all_reduce(self.params.grads["model.embed_tokens.weight"], group=group)
+
+    def duplicate_ranges(self) -> list[tuple[int, int]]:
+        """Ranges of the flat gradient that another stage holds as well (counted once in the global norm):
+        reported by the last stage only."""
+        if self._shares_embedding() and self.last:
+            o, n = self.params.offsets["model.embed_tokens.weight"]
+            return [(o, o + n)]
+        return []
+
+    # ------------------------------------------------------------------ the pieces of one micro-batch
+    def _layers_fwd(self, batch: PackedBatch, inp, save: bool):
+        """``inp`` = (x, delta) from the previous stage, None on the first. Returns (x, delta, state)."""
+        from ..ops import activation as A
+        c = self.cfg
+        tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
+        if self.first:
+            x, delta = A.embedding_fwd(batch.input_ids, self.weights["model.embed_tokens.weight"]), None
+        else:
+            x, delta = inp
+        kept = []
+        for l in self.layers:
+            x, delta, saved = self.layer_fwd(l, x, delta, batch, tables, keep=save)
+            if save:
+                kept.append(saved)
+        return x, delta, dict(batch=batch, tables=tables, layer_inputs=kept)
+
+    def _head_fwd(self, x, delta, batch: PackedBatch, temperature: float, state: dict):
+        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], self.cfg.rms_norm_eps, delta=delta)
+        lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), batch.labels, temperature)
+        state.update(hf=hf, rstd_f=rstd_f, xf=xf, lse=lse, ent=ent, temperature=temperature)
+        return lp, ent
+
+    def _state_bwd(self, s: dict, upstream):
+        """``upstream``: (g_logprob, g_entropy) on the last stage, d(stream) from the next stage otherwise.
+        Returns d(stream) for the previous stage (None on the first, which ends in the embedding)."""
+        batch, tables = s["batch"], s["tables"]
+        if self.last:
+            g_logprob, g_entropy = upstream
+            g_lp = None if g_logprob is None else g_logprob.float().contiguous()
+            g_ent = None if g_entropy is None else g_entropy.float().contiguous()
+            dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), batch.labels, s["lse"], s["ent"], g_lp, g_ent,
+                                s["temperature"], dweight=self.head_grad())
+            dx = N.rmsnorm_bwd(dhf, s["xf"], self.weights["model.norm.weight"], s["rstd_f"], self._wgrad("model.norm.weight"))
+        else:
+            dx = upstream
+        kept = s["layer_inputs"]
+        for l in reversed(self.layers):
+            dx = self.layer_bwd(l, kept.pop(), dx, batch, tables)
+        if self.first:
+            self._embed_bwd(batch, dx)
+            return None
+        return dx
+
+    def _stream_shape(self, batch: PackedBatch):
+        return (batch.input_ids.numel(), self.cfg.hidden_size)
 
     def flops_per_token(self, seqlen: int) -> float:
         return DenseModel.flops_per_token(self, seqlen) / self.stages

@@ -80,7 +80,9 @@ def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, in
 
 
 class TPDenseModel:
-    def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False):
+    def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False,
+                 holds=None):
+        """``holds``: optional predicate over parameter names; only those parameters are allocated (pipeline stages)."""
         assert cfg.num_experts == 0
         assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
         assert not cfg.sandwich_norm, "sandwich-norm families (GLM-4) run under data / sequence / context / pipeline parallelism; the tensor-parallel layer code does not carry the extra norms yet"
@@ -88,7 +90,10 @@ class TPDenseModel:
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
         self.shard_head = bool(vocab_parallel_head) and not cfg.tie_word_embeddings and tp.world > 1
-        self.params = FlatParams(cfg, self.device, dtype, layout=tp_param_layout(cfg, tp.world, tp.rank, self.shard_head))
+        layout = tp_param_layout(cfg, tp.world, tp.rank, self.shard_head)
+        if holds is not None:
+            layout = OrderedDict((n, sh) for n, sh in layout.items() if holds(n))
+        self.params = FlatParams(cfg, self.device, dtype, layout=layout)
         self.vp_head = None
         if self.shard_head:
             from ..parallel.vocab_parallel import VocabParallelHead

@@ -1,0 +1,136 @@
+"""Tensor parallelism INSIDE pipeline stages: ``world = dp x pp x tp`` (reference: the Megatron trainer initialises
+tensor-, pipeline- and data-parallel sizes together, axon/trainer/megatron_trainer.py:164-173; its quick-start recipe
+runs TP 4 x PP 2).
+
+A stage holds the tensor-parallel shards of its own layers (``tp_dense.TPDenseModel`` restricted by
+``pp_dense.stage_keeps``); the residual stream that travels between stages is the sequence-parallel local part
+[T / tp, H], so every tensor-parallel rank talks to the same rank of the neighbouring stage and the point-to-point
+volume per rank drops by tp. The schedules (one micro-batch, streamed forward, one-forward-one-backward) are those of
+``pp_dense.PipelineSchedule``. The last stage's per-token results are gathered over its tensor-parallel group, so the
+loss code sees whole micro-batches, and the incoming gradients are cut back to the local rows.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import activation as A
+from ..ops import lm_head as LM
+from ..ops import norm as N
+from ..ops import rope as R
+from ..parallel.tp import TPContext
+from .config import ModelConfig
+from .dense import DenseModel, PackedBatch
+from .pp_dense import PipelineContext, PipelineSchedule, stage_keeps, stage_layers
+from .tp_dense import TPDenseModel, pad_packed_batch
+
+
+class BlockContext:
+    """The model-parallel block (all tensor-parallel ranks of all stages of one replica) as the policy engine sees it:
+    gradient-norm pieces are summed over ``group``; parameters replicated inside a tensor-parallel group appear
+    ``replication`` times in that sum."""
+
+    def __init__(self, group, world: int, replication: int):
+        self.group, self.world, self.replication = group, world, replication
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+
+class TPPPDenseModel(PipelineSchedule, TPDenseModel):
+    def __init__(self, cfg: ModelConfig, tp: TPContext, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16):
+        assert pp.world <= cfg.num_hidden_layers
+        if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
+            assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
+        self.pp = pp
+        self.stage, self.stages = pp.rank, pp.world
+        TPDenseModel.__init__(self, cfg, tp, device=device, dtype=dtype, vocab_parallel_head=False,
+                              holds=stage_keeps(cfg, self.stages, self.stage))
+        self.layers = stage_layers(cfg.num_hidden_layers, self.stages, self.stage)
+        self.mp_ctx = BlockContext(block_group, tp.world * pp.world, tp.world)
+        self.recompute = "full"
+
+    # ------------------------------------------------------------------ parameters shared between ranks
+    def _shares_embedding(self) -> bool:
+        return self.cfg.tie_word_embeddings and self.stages > 1 and (self.first or self.last)
+
+    def sync_replicated_grads(self) -> None:
+        TPDenseModel.sync_replicated_grads(self)            # norms / embedding / head: partial per tensor-parallel rank
+        if self._shares_embedding() and self.params.grad_flat is not None:
+            group = self.pp.ends_group if self.stages > 2 else self.pp.group
+            dist.all_reduce(self.params.grads["model.embed_tokens.weight"], group=group)
+
+    def replicated_ranges(self) -> list[tuple[int, int]]:
+        keep = set(self.replicated_names())
+        return [(o, o + n) for name, (o, n) in self.params.offsets.items() if name in keep]
+
+    def duplicate_ranges(self) -> list[tuple[int, int]]:
+        # the tied table also lives on the first stage: counted once more by ONE rank of the last stage
+        if self._shares_embedding() and self.last and self.tp.rank == 0:
+            o, n = self.params.offsets["model.embed_tokens.weight"]
+            return [(o, o + n)]
+        return []
+
+    # ------------------------------------------------------------------ the pieces of one micro-batch
+    def _padded_len(self, batch: PackedBatch) -> int:
+        m = 128 * self.tp.world
+        return (batch.input_ids.numel() + m - 1) // m * m
+
+    def _stream_shape(self, batch: PackedBatch):
+        return (self._padded_len(batch) // self.tp.world, self.cfg.hidden_size)
+
+    def _layers_fwd(self, batch: PackedBatch, inp, save: bool):
+        c = self.cfg
+        self.tp.begin_pass()
+        padded, t_real = pad_packed_batch(batch, 128 * self.tp.world)
+        T = padded.input_ids.numel()
+        sl = self.local_slice(T)
+        tables = R.rope_tables(max(int(padded.max_seqlen) or c.max_position_embeddings, 8), c.head_dim, c.rope_theta, self.device, c.rotary_dim)
+        if self.first:
+            x, delta = A.embedding_fwd(padded.input_ids[sl].contiguous(), self.params["model.embed_tokens.weight"]), None
+        else:
+            x, delta = inp
+        inputs = []
+        for l in self.layers:
+            x, delta, xin = self.layer_fwd(l, x, delta, padded, tables)
+            if save:
+                inputs.append(xin)
+        return x, delta, dict(batch=padded, tables=tables, inputs=inputs, sl=sl, T=T, T_real=t_real)
+
+    def _head_fwd(self, x, delta, batch: PackedBatch, temperature: float, state: dict):
+        hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], self.cfg.rms_norm_eps, delta=delta)
+        labels = state["batch"].labels[state["sl"]].contiguous()
+        lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), labels, temperature)
+        state.update(hf=hf, rstd_f=rstd_f, xf=xf, lse=lse, ent=ent, labels=labels, temperature=temperature)
+        n = state["T_real"]
+        return self.tp.all_gather_rows(lp.contiguous())[:n], self.tp.all_gather_rows(ent.contiguous())[:n]
+
+    def _cut(self, g, s):
+        if g is None:
+            return None
+        full = torch.zeros(s["T"], dtype=torch.float32, device=self.device)
+        full[: s["T_real"]] = g.float()
+        return full[s["sl"]].contiguous()
+
+    def _state_bwd(self, s: dict, upstream):
+        self.tp.begin_pass()
+        batch, tables = s["batch"], s["tables"]
+        if self.last:
+            g_lp, g_ent = self._cut(upstream[0], s), self._cut(upstream[1], s)
+            dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
+                                dweight=self.head_grad())
+            dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"])
+        else:
+            dx = upstream
+        kept = s["inputs"]
+        for l in reversed(self.layers):
+            dx = self.layer_bwd(l, kept.pop(), dx, batch, tables)
+        if self.first:
+            A.embedding_bwd(batch.input_ids[s["sl"]].contiguous(), dx, self.params.grads["model.embed_tokens.weight"])
+            return None
+        return dx
+
+    def flops_per_token(self, seqlen: int) -> float:
+        return DenseModel.flops_per_token(self, seqlen) / (self.stages * self.tp.world)

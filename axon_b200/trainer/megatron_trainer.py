@@ -17,8 +17,9 @@ parallel" group, which is also the group the optimizer state is sharded over.
 Pipeline parallelism (``pipeline_model_parallel_size``, alone): stage groups of consecutive ranks,
 ``models/pp_dense.py`` (send / recv between stages, micro-batches one after another).
 
-A context-parallel size other than 1, and combinations of two model-parallel dimensions, are refused
-with an explicit error until their schedules land here.
+Tensor x pipeline (``world = dp x pp x tp``): ``models/tp_pp_dense.py`` - tensor-parallel shards inside pipeline
+stages, the sequence-parallel local stream travels between stages. Other combinations of two model-parallel
+dimensions (with expert or context parallelism) are refused with an explicit error.
 """
 from __future__ import annotations
 
@@ -37,9 +38,9 @@ class TrainerWorker(_Base):
             raise NotImplementedError("tensor and expert parallelism together are not available in this trainer yet; "
                                       "use one of megatron.tensor_model_parallel_size / expert_model_parallel_size")
         self.pp_size = int(_get(m, "pipeline_model_parallel_size", 1) or 1)
-        if self.pp_size > 1 and (self.tp_size > 1 or self.ep_size > 1):
-            raise NotImplementedError("pipeline parallelism together with tensor / expert parallelism is not available in this "
-                                      "trainer yet; use one model-parallel dimension")
+        if self.pp_size > 1 and self.ep_size > 1:
+            raise NotImplementedError("pipeline parallelism together with expert parallelism is not available in this trainer "
+                                      "yet; tensor x pipeline is, or use one of the two")
         self.cp_size = int(_get(m, "context_parallel_size", 1) or 1)
         if self.cp_size > 1 and (self.tp_size > 1 or self.ep_size > 1 or self.pp_size > 1):
             raise NotImplementedError("context parallelism together with tensor / expert / pipeline parallelism is not available "
@@ -54,7 +55,8 @@ class TrainerWorker(_Base):
     def _register_dispatch_collect_info(self, mesh_name: str, dp_rank: int, is_collect: bool) -> None:
         if mesh_name == "trainer" and getattr(self, "_pending_dispatch", False):
             self._pending_dispatch = False
-            mp = max(self.tp_size, self.pp_size, self.cp_size)          # ranks of one tensor- / pipeline- / context-parallel group see the same rows
+            # ranks of one tensor- / pipeline- / context-parallel group (or tensor x pipeline block) see the same rows
+            mp = self.tp_size * self.pp_size if (self.tp_size > 1 and self.pp_size > 1) else max(self.tp_size, self.pp_size, self.cp_size)
             assert self.world_size % mp == 0, f"world size {self.world_size} not divisible by the model-parallel size {mp}"
             return super()._register_dispatch_collect_info(mesh_name, self.rank // mp, self.rank % mp == 0)
         return super()._register_dispatch_collect_info(mesh_name, dp_rank, is_collect)
@@ -107,13 +109,61 @@ class TrainerWorker(_Base):
         return model
 
     def _make_state_manager(self):
-        mp = max(self.tp_size, self.ep_size, self.pp_size)
+        both = self.tp_size > 1 and self.pp_size > 1
+        mp = self.tp_size * self.pp_size if both else max(self.tp_size, self.ep_size, self.pp_size)
         if mp == 1:
             return super()._make_state_manager()
         from ..utils.state.megatron_state_manager import MegatronStateManager
         return MegatronStateManager(self.model, self.engine, mp_group=getattr(self, "_mp_group", None), tp=self.tp_size, ep=self.ep_size,
-                                    pp=self.pp_size, dp_rank=self.rank // mp, processing_class=self.tokenizer, rank=self.rank,
-                                    world_size=self.world_size, process_group=self.pg)
+                                    pp=self.pp_size, dp_rank=self.rank // mp, tp_rank=(self.rank % self.tp_size) if both else None,
+                                    processing_class=self.tokenizer, rank=self.rank, world_size=self.world_size, process_group=self.pg)
+
+    def _build_tensor_pipeline_parallel(self, model_path, dtype, seed):
+        """world = dp x pp x tp: tensor-parallel groups are consecutive ranks, the stages of one replica are tp ranks
+        apart, replicas are pp x tp ranks apart (the order megatron's ``initialize_model_parallel`` uses)."""
+        import os
+        from ..models.config import get_config
+        from ..models.params import FlatParams
+        from ..models.pp_dense import PipelineContext
+        from ..models.tp_pp_dense import TPPPDenseModel
+        from ..parallel.tp import TPContext
+        from ..utils.hf_model import has_hf_weights, iter_hf_weights
+        mcfg = get_config(model_path)
+        tp, pp, world = self.tp_size, self.pp_size, self.world_size
+        block = tp * pp
+        assert world % block == 0, f"world size {world} not divisible by tp x pp = {block}"
+        assert not self.model_kind.value_head, "value-head models are not model-parallel yet; run the critic with tp = pp = 1"
+
+        def make(groups):
+            mine = None
+            for ranks in groups:
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    mine = g
+            return mine
+        n_rep = world // block
+        tp_group = make([list(range(b * block + s * tp, b * block + (s + 1) * tp)) for b in range(n_rep) for s in range(pp)])
+        pp_group = make([[b * block + s * tp + t for s in range(pp)] for b in range(n_rep) for t in range(tp)])
+        dp_group = make([[b * block + j for b in range(n_rep)] for j in range(block)])
+        block_group = make([list(range(b * block, (b + 1) * block)) for b in range(n_rep)])
+        ends_group = None
+        if mcfg.tie_word_embeddings and pp > 2:
+            ends_group = make([[b * block + t, b * block + (pp - 1) * tp + t] for b in range(n_rep) for t in range(tp)])
+        self.pg, self._mp_group = dp_group, block_group
+        rows = int(_get(self.config, "max_token_len_per_gpu", 16384))
+        rows = (rows // tp + 127) // 128 * 128 + 128
+        width = max(mcfg.qkv_size, 2 * mcfg.intermediate_size, mcfg.hidden_size)
+        ctx = TPContext(tp_group, self.device, max_rows_per_rank=rows, max_width=width)
+        model = TPPPDenseModel(mcfg, ctx, PipelineContext(pp_group, self.device, ends_group=ends_group), block_group,
+                               device=self.device, dtype=dtype)
+        ref = FlatParams(mcfg, "cpu", dtype)
+        if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+        else:
+            ref.init_random(seed=seed)
+        model.load_full_state(ref.views)
+        model.recompute = str(_get(self.config, "recompute", "selective"))
+        return model
 
     def _build_expert_parallel(self, model_path, dtype, seed):
         import os
@@ -173,6 +223,8 @@ class TrainerWorker(_Base):
     def _build(self, model_path, dtype, seed):
         if self.cp_size > 1:
             return self._build_context_parallel(model_path, dtype, seed)
+        if self.pp_size > 1 and self.tp_size > 1:
+            return self._build_tensor_pipeline_parallel(model_path, dtype, seed)
         if self.pp_size > 1:
             return self._build_pipeline_parallel(model_path, dtype, seed)
         if self.ep_size > 1:

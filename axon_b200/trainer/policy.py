@@ -227,7 +227,7 @@ class PolicyEngine:
 
     def _model_parallel(self):
         """The context of the model's parallel group of any kind (tensor, expert, pipeline, parameter shards)."""
-        for attr in ("tp", "ep", "pp", "shard"):
+        for attr in ("mp_ctx", "tp", "ep", "pp", "shard"):
             ctx = getattr(self.model, attr, None)
             if ctx is not None:
                 return ctx
@@ -505,7 +505,11 @@ class PolicyEngine:
             dist.all_reduce(rep, group=self.opt_group)
         tot = self.state[:1].clone()
         tp.all_reduce_(tot)
-        self.state[:1] = tot - (tp.world - 1) * rep
+        # every replicated parameter appears R times in the sum over the group (R = the group size, or the tensor-parallel
+        # size when the group also spans pipeline stages, whose replicated parts differ): keep one of the R
+        R = int(getattr(tp, "replication", tp.world))
+        rep_all = tp.all_reduce_(rep.clone())
+        self.state[:1] = tot - rep_all * ((R - 1) / R)
         if hasattr(self.model, "duplicate_ranges"):       # parameters held by some ranks of the group only (tied embedding on pipeline ends)
             dup = torch.zeros(1, dtype=torch.float32, device=self.device)
             for a, b in self.model.duplicate_ranges():

@@ -297,5 +297,6 @@ def load_sharded(template: dict, ckpt_dir: str, group=None, strict: bool = True)
         if src_dtype == torch.bfloat16:
             t = t.view(torch.int16).view(torch.bfloat16)
         dst.copy_(t.view(dst.shape).to(dst.dtype))
-    _barrier(group)
+    if group is not False:               # False: a single rank reads on its own (no collective)
+        _barrier(group)
     return out

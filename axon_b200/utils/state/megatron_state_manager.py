@@ -60,9 +60,13 @@ def gather_full_params(model, group, tp: int = 1, tp_rank: int = 0, ep: int = 1,
 
 
 class MegatronStateManager(FSDPStateManager):
-    def __init__(self, model, optimizer, mp_group=None, tp: int = 1, ep: int = 1, pp: int = 1, dp_rank: int = 0, **kw):
+    def __init__(self, model, optimizer, mp_group=None, tp: int = 1, ep: int = 1, pp: int = 1, dp_rank: int = 0,
+                 tp_rank: int | None = None, **kw):
+        """``tp_rank``: this rank's place in its tensor-parallel group when that differs from its place in ``mp_group``
+        (tensor parallelism inside pipeline stages, where ``mp_group`` is the whole tensor x pipeline block)."""
         super().__init__(model, optimizer, **kw)
         self.mp_group, self.tp, self.ep, self.pp, self.dp_rank = mp_group, tp, ep, pp, dp_rank
+        self.tp_rank = tp_rank
         self._request: AsyncSaveRequest | None = None
 
     def _mp_rank(self) -> int:
@@ -88,15 +92,16 @@ class MegatronStateManager(FSDPStateManager):
         cfg = inner.cfg
         full = param_layout(cfg)
         rep = set(inner.replicated_names()) if hasattr(inner, "replicated_names") else set()
-        r = self._mp_rank()
+        r = self.tp_rank if self.tp_rank is not None else self._mp_rank()
         out = {}
         for name, mine in inner.params.views.items():
             shape = full[name]
             g2 = (int(shape[0]), int(torch.Size(shape[1:]).numel()) if len(shape) > 1 else 1)
             zshard = getattr(self.model, "shard", None)
-            if self.pp > 1 or tuple(mine.shape) == tuple(shape):          # whole tensor on this rank (a stage's own, or replicated)
+            if tuple(mine.shape) == tuple(shape):          # whole tensor on this rank (a stage's own, or replicated in its group)
                 boxes = [((0, 0), g2)]
-                writer = self.dp_rank == 0 and (self.pp > 1 or (r == 0 and (zshard is None or zshard.rank == 0)))
+                one_of_group = (self.pp > 1 and self.tp == 1) or (r == 0 and (zshard is None or zshard.rank == 0))
+                writer = self.dp_rank == 0 and one_of_group
             elif zshard is not None and self.tp == 1 and self.ep == 1:    # row shards of the parameter-sharded data-parallel model
                 boxes = [((zshard.rank * int(mine.shape[0]), 0), (int(mine.shape[0]), g2[1]))]
                 writer = True
@@ -151,6 +156,21 @@ class MegatronStateManager(FSDPStateManager):
             self._request = req            # finalized by wait(): before the next save, a load, or shutdown
         elif max_ckpt_to_keep and max_ckpt_to_keep > 0 and self.rank == 0:
             delete_oldest_checkpoints(os.path.dirname(os.path.dirname(os.path.abspath(local_path))), max_ckpt_to_keep)
+        if want_hf and self.tp > 1 and self.pp > 1:
+            # shards of two kinds: assemble the export from the array store just written (any layout reads back whole)
+            req.finalize()
+            self._request = None
+            if self.rank == 0:
+                from ...models.params import FlatParams
+                from ..hf_model import save_hf_model
+                inner = self._inner()
+                host = FlatParams(inner.cfg, "cpu", inner.params.flat.dtype)
+                load_sharded({"model/" + n: ShardedTensor("model/" + n, v, (int(v.shape[0]), int(v[0].numel()) if v.dim() > 1 else 1),
+                                                          [((0, 0), (int(v.shape[0]), int(v[0].numel()) if v.dim() > 1 else 1))])
+                              for n, v in host.views.items()}, os.path.join(local_path, "dist_ckpt"), group=False)
+                save_hf_model(host, os.path.join(local_path, "huggingface"), cfg=inner.cfg, tokenizer=self.processing_class)
+            _barrier(None)
+            return
         if want_hf and self.dp_rank == 0:
             inner = getattr(self.model, "inner", self.model)
             rep = inner.replicated_names() if hasattr(inner, "replicated_names") else ()

@@ -83,7 +83,7 @@ def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp"])
+@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp"])
 def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
     run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
@@ -94,10 +94,11 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     from axon_b200.models.moe import build_model_for
     from axon_b200.utils.hf_model import load_hf_weights
     preset, vocab = ("tiny-moe", 2048) if kind == "ep" else (("tiny-qwen2" if kind == "tp-bias" else "tiny-qwen3-untied"), 4096)
-    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind == "ep" else 1, 2 if kind == "pp" else 1)
+    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind == "ep" else 1, 2 if kind.endswith("pp") else 1)
+    world = 4 if kind == "tp-pp" else 2
     d = str(tmp_path / "ck")
-    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, 2, vocab=vocab, save_dir=d)
-    assert json.load(open(os.path.join(d, "model_parallel_config.json")))["world_size"] == 2
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, world, vocab=vocab, save_dir=d)
+    assert json.load(open(os.path.join(d, "model_parallel_config.json")))["world_size"] == world
     # the sharded state is one array per parameter in full-model coordinates ...
     from axon_b200.models.params import FlatParams
     from axon_b200.utils.state.dist_checkpoint import ShardedTensor, load_sharded, read_metadata
@@ -117,8 +118,11 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
         lp, _ = m.forward(PackedBatch.from_sequences([data.batch["input_ids"][row, :n].to(torch.int32)], "cpu"))
         torch.testing.assert_close(lp[: n - 1], got[3][row, 1:n].float(), rtol=2e-3, atol=2e-3)
     # resume under the writing layout and - for the tensor-parallel run - under NO model parallelism at all
-    again = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, 2, vocab=vocab, load_dir=d)
+    again = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, world, vocab=vocab, load_dir=d)
     torch.testing.assert_close(again[0], got[3], rtol=1e-5, atol=1e-5)
+    if kind == "tp-pp":          # written by tp 2 x pp 2, resumed by two pipeline stages without tensor parallelism
+        other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, pp=2), 2, vocab=vocab, load_dir=d)
+        torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
     if kind == "tp":
         single = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset), 1, vocab=vocab, load_dir=d)
         torch.testing.assert_close(single[0], got[3], rtol=1e-3, atol=1e-3)
@@ -131,6 +135,20 @@ def test_pipeline_parallel_trainer_matches_data_parallel_trainer(world, pp):
     import numpy as np
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied"), 1)
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied", pp=pp), world)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+def test_tensor_parallel_inside_pipeline_stages_matches_data_parallel_trainer():
+    """world = 4 as pp 2 x tp 2: same log-probs, gradient norm (replicated parameters counted once across the tensor-
+    parallel ranks of EACH stage) and update as the single-process trainer."""
+    import numpy as np
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied"), 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, "tiny-qwen3-untied", pp=2), 4)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
