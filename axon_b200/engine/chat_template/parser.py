@@ -10,6 +10,8 @@ reports placeholder regions for images/videos.
 """
 from __future__ import annotations
 
+import re
+
 import hashlib
 import json
 from dataclasses import dataclass, field
@@ -197,6 +199,8 @@ class ChatTemplateParser:
             return QwenChatTemplateParser(tokenizer, disable_thinking=disable_thinking, **kw)
         if "llama" in name:
             return LlamaChatTemplateParser(tokenizer, **kw)
+        if "gemma-4" in name or "gemma4" in name:
+            return Gemma4ChatTemplateParser(tokenizer, disable_thinking=disable_thinking or True, **kw)
         if "gemma" in name:
             return GemmaChatTemplateParser(tokenizer, **kw)
         if "moonlight" in name or "kimi" in name:
@@ -309,6 +313,115 @@ class GemmaChatTemplateParser(ChatTemplateParser):
         return self.user_token + _text_of(m.get("content", "")) + self.eot_token
 
 
+class Gemma4ChatTemplateParser(ChatTemplateParser):
+    """Gemma-4 (reference: axon/engine/chat_template/parser.py:543-808, the chat template shipped with
+    google/gemma-4-*-it). Turns are ``<|turn>role\ncontent<turn|>\n`` with roles system / user / model. Tool calls
+    and their results live INSIDE the model turn (``<|tool_call>...<tool_call|><|tool_response>...<tool_response|>``):
+    ``tool`` messages are consumed by the assistant message before them, and an assistant message that follows
+    tool results continues the open model turn instead of starting a new one. Thinking: with thinking off (the
+    default for RL) the generation prompt carries an empty thought channel, which is re-inserted before the content
+    of every earlier model turn so that rendered histories stay prefix-cumulative with the token tree; with thinking
+    on, the system turn starts with ``<|think|>``. Text only: media parts are refused."""
+    bos = "<bos>"
+    start_turn, end_turn = "<|turn>", "<turn|>"
+    THINK = "<|think|>"
+    EMPTY_THOUGHT = "<|channel>thought\n<channel|>"
+    _MEDIA = ("image", "input_image", "image_url", "audio", "input_audio", "audio_url", "video", "input_video", "video_url")
+
+    def __init__(self, tokenizer, disable_thinking: bool = True, **kw):
+        super().__init__(tokenizer, **kw)
+        self.bos = getattr(tokenizer, "bos_token", None) or self.bos
+        self.disable_thinking = disable_thinking
+        self.generation_prompt = f"{self.start_turn}model\n" + (self.EMPTY_THOUGHT if disable_thinking else "")
+
+    def _assistant_message_stop_texts(self) -> tuple:
+        return (self.end_turn, *super()._assistant_message_stop_texts())
+
+    def _text(self, content, strip: bool) -> str:
+        if isinstance(content, str):
+            return content.strip() if strip else content
+        out = []
+        for part in content or []:
+            if not isinstance(part, dict):
+                continue
+            if part.get("type") in ("text", "input_text"):
+                t = part.get("text") or ""
+                out.append(t.strip() if strip else t)
+            elif part.get("type") in self._MEDIA:
+                raise ValueError("Gemma4ChatTemplateParser is text-only; use a multimodal parser for media content")
+        return "".join(out)
+
+    def parse(self, messages, add_generation_prompt: bool = False, tools=None, **kwargs) -> str:
+        from ...tools.types import ToolCall
+        msgs = list(messages)
+        out = self.bos
+        thinking = not self.disable_thinking
+        has_system = bool(msgs) and msgs[0].get("role") in ("system", "developer")
+        if thinking or tools or has_system:
+            out += f"{self.start_turn}system\n"
+            if thinking:
+                out += self.THINK + "\n"
+            if has_system:
+                c = msgs[0].get("content", "")
+                out += c.strip() if isinstance(c, str) else "".join((p.get("text") or "").strip() + " " for p in c
+                                                                    if isinstance(p, dict) and p.get("type") in ("text", "input_text"))
+                msgs = msgs[1:]
+            if tools:
+                assert self.tool_parser, "a tool parser is required when tools are given"
+                out += self.tool_parser.get_tool_system_prompt(tools)
+            out += f"{self.end_turn}\n"
+        last_user = max((i for i, m in enumerate(msgs) if m.get("role") == "user"), default=-1)
+        prev_role, tail = None, None               # tail: what the last rendered message ended with (call / response / None)
+        for i, m in enumerate(msgs):
+            role = m.get("role")
+            if role == "tool":                     # rendered by the assistant message in front of it
+                continue
+            if role == "skip":
+                out += m["content"]
+                continue
+            tail = None
+            mapped = "model" if role == "assistant" else role
+            if not (mapped == "model" and prev_role == "assistant"):      # a model message after tool results continues its turn
+                out += f"{self.start_turn}{mapped}\n"
+            calls = m.get("tool_calls")
+            thought = m.get("reasoning") or m.get("reasoning_content")
+            if thought and i > last_user and calls:
+                out += f"<|channel>thought\n{thought}\n<channel|>"
+            answered = False
+            if calls:
+                assert self.tool_parser, f"a tool parser is required to render tool calls: {m}"
+                objs = [ToolCall.from_raw_tool_call(c) for c in calls]
+                out += self.tool_parser.format_tool_calls(objs)
+                tail = "call"
+                for follow in msgs[i + 1:]:
+                    if follow.get("role") != "tool":
+                        break
+                    name = follow.get("name", "unknown")
+                    for c in objs:
+                        if follow.get("tool_call_id") and c.id == follow["tool_call_id"]:
+                            name = c.name
+                    body = follow.get("content", "")
+                    out += self.tool_parser.format_tool_result(content=self._text(body, False) if not isinstance(body, dict) else body, name=name)
+                    answered, tail = True, "response"
+            for r in m.get("tool_responses") or []:
+                assert self.tool_parser
+                out += self.tool_parser.format_tool_result(content=r.get("response"), name=r.get("name", "unknown"))
+                answered, tail = True, "response"
+            text = self._text(m.get("content", ""), strip=mapped != "model")
+            if text:
+                out += (self.EMPTY_THOUGHT if mapped == "model" and self.disable_thinking else "") + text
+            if tail == "call" and not answered:
+                out += "<|tool_response>"          # the call waits for its result: the turn stays open on the opener
+            elif answered and not text.strip():
+                pass                               # turn left open: the next assistant message continues it
+            else:
+                out += f"{self.end_turn}\n"
+            prev_role = role
+        if add_generation_prompt and tail not in ("call", "response") and not (msgs and msgs[-1].get("role") == "skip"):
+            out += self.generation_prompt
+        return out
+
+
 class OpenAIHarmonyChatTemplateParser(ChatTemplateParser):
     """gpt-oss Harmony format: ``<|start|>role<|message|>...<|end|>``; assistant turns carry a channel."""
     eot_token = "<|end|>"
@@ -388,6 +501,91 @@ class GlmChatTemplateParser(ChatTemplateParser):
 
     def _assistant_message_stop_texts(self) -> tuple:
         return ("<|user|>", "<|observation|>", "<|endoftext|>", *super()._assistant_message_stop_texts())
+
+
+class MultiModalChatTemplateParser(ChatTemplateParser):
+    """Base of the vision-language parsers (reference: axon/engine/chat_template/parser.py:1301-1700). Callers pass
+    ``messages`` only. Media travel inline as content parts - ``{"type": "image", "image": x}``, ``{"type": "image_url",
+    "image_url": x | {"url": x}}`` and the same for ``video`` - or, in the legacy form, as ``<image>`` / ``<video>`` marks
+    in the text with the payloads in ``images=`` / ``videos=`` (consumed in order). ``normalize`` brings both to the
+    canonical part list, ``collect_media`` returns the payloads in placeholder order, ``parse`` renders through the
+    processor's (else the tokenizer's) chat template."""
+    LEGACY_MARKS = {"image": "<image>", "video": "<video>"}
+
+    def __init__(self, tokenizer, processor=None, **kw):
+        super().__init__(tokenizer, **kw)
+        self.processor = processor
+
+    @staticmethod
+    def _unwrap(x):
+        return x.get("url", x) if isinstance(x, dict) else x
+
+    def normalize(self, messages, images=None, videos=None, allow_legacy_placeholders: bool = True) -> list:
+        pools = {"image": list(images or []), "video": list(videos or [])}
+        out = []
+        for m in messages:
+            c = m.get("content")
+            parts = []
+            if isinstance(c, str):
+                if allow_legacy_placeholders and any(mark in c for mark in self.LEGACY_MARKS.values()):
+                    rx = re.compile("(" + "|".join(re.escape(v) for v in self.LEGACY_MARKS.values()) + ")")
+                    for piece in rx.split(c):
+                        mod = next((k for k, v in self.LEGACY_MARKS.items() if v == piece), None)
+                        if mod is None:
+                            if piece:
+                                parts.append({"type": "text", "text": piece})
+                        else:
+                            if not pools[mod]:
+                                raise ValueError(f"more {self.LEGACY_MARKS[mod]} marks than {mod}s passed")
+                            parts.append({"type": mod, mod: pools[mod].pop(0)})
+                else:
+                    out.append(dict(m))
+                    continue
+            else:
+                for part in c or []:
+                    if not isinstance(part, dict):
+                        parts.append({"type": "text", "text": str(part)})
+                        continue
+                    t = part.get("type", "text")
+                    if t in ("text", "input_text"):
+                        parts.append({"type": "text", "text": part.get("text") or ""})
+                    elif "image" in t:
+                        parts.append({"type": "image", "image": self._unwrap(part.get("image", part.get("image_url", part.get(t))))})
+                    elif "video" in t:
+                        parts.append({"type": "video", "video": self._unwrap(part.get("video", part.get("video_url", part.get(t))))})
+                    else:
+                        parts.append(dict(part))
+            out.append({**m, "content": parts})
+        left = {k: len(v) for k, v in pools.items() if v}
+        if left:
+            raise ValueError(f"payloads without a placeholder: {left}")
+        return out
+
+    def count_placeholders(self, messages) -> tuple[int, int]:
+        n = {"image": 0, "video": 0}
+        for m in self.normalize(messages, allow_legacy_placeholders=False):
+            for part in m["content"] if isinstance(m.get("content"), list) else []:
+                if part.get("type") in n:
+                    n[part["type"]] += 1
+        return n["image"], n["video"]
+
+    def collect_media(self, messages, images=None, videos=None) -> tuple[list, list]:
+        got = {"image": [], "video": []}
+        for m in self.normalize(messages, images, videos):
+            for part in m["content"] if isinstance(m.get("content"), list) else []:
+                if part.get("type") in got:
+                    got[part["type"]].append(part[part["type"]])
+        return got["image"], got["video"]
+
+    def parse(self, messages, add_generation_prompt: bool = False, tools=None, **kwargs) -> str:
+        norm = self.normalize(messages, kwargs.pop("images", None), kwargs.pop("videos", None),
+                              kwargs.pop("allow_legacy_placeholders", True))
+        owner = self.processor if hasattr(self.processor, "apply_chat_template") else self.tokenizer
+        if not hasattr(owner, "apply_chat_template"):
+            raise NotImplementedError(f"{type(self).__name__} needs a processor or tokenizer with a chat template")
+        if tools:
+            kwargs["tools"] = tools
+        return owner.apply_chat_template(norm, tokenize=False, add_generation_prompt=add_generation_prompt, **kwargs)
 
 
 class QwenVLChatTemplateParser(QwenChatTemplateParser):

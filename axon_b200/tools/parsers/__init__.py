@@ -217,9 +217,9 @@ class HarmonyToolCallParser(ToolCallParser):
         return "".join(self.format_tool_call(c) for c in calls)
 
 
-@register_parser("gemma4")
-class Gemma4ToolCallParser(ToolCallParser):
-    """Gemma: fenced ``tool_code`` blocks holding ``name(arg=value, ...)`` Python-style calls."""
+@register_parser("gemma")
+class GemmaToolCodeParser(ToolCallParser):
+    """Gemma 2 / 3: fenced ``tool_code`` blocks holding ``name(arg=value, ...)`` Python-style calls."""
     _RX = re.compile(r"```tool_code\s*(.*?)\s*```", re.S)
     _CALL = re.compile(r"([\w.]+)\((.*)\)\s*$", re.S)
 
@@ -245,3 +245,182 @@ class Gemma4ToolCallParser(ToolCallParser):
 
     def format_tool_result(self, content, name=""):
         return f"```tool_output\n{content}\n```"
+
+
+_G4_Q = '<|"|>'
+
+
+class _Gemma4Values:
+    """Gemma-4's compact value grammar: ``{key:value,...}``, ``[v,...]``, strings between ``<|"|>`` marks, ``true`` /
+    ``false`` / ``null``, numbers; a bare word that is none of those is a string."""
+
+    def __init__(self, text: str):
+        self.t, self.i = text, 0
+
+    def _ws(self):
+        while self.i < len(self.t) and self.t[self.i].isspace():
+            self.i += 1
+
+    def value(self):
+        self._ws()
+        t = self.t
+        if t.startswith(_G4_Q, self.i):
+            end = t.find(_G4_Q, self.i + len(_G4_Q))
+            end = len(t) if end < 0 else end
+            out = t[self.i + len(_G4_Q):end]
+            self.i = min(len(t), end + len(_G4_Q))
+            return out
+        if self.i < len(t) and t[self.i] == "{":
+            self.i += 1
+            return self.members("}")
+        if self.i < len(t) and t[self.i] == "[":
+            self.i += 1
+            out = []
+            while True:
+                self._ws()
+                if self.i >= len(t) or t[self.i] == "]":
+                    self.i += 1
+                    return out
+                out.append(self.value())
+                self._ws()
+                if self.i < len(t) and t[self.i] == ",":
+                    self.i += 1
+        j = self.i
+        while j < len(t) and t[j] not in ",}]":
+            j += 1
+        word = t[self.i:j].strip()
+        self.i = j
+        if word in ("true", "false"):
+            return word == "true"
+        if word == "null":
+            return None
+        try:
+            return float(word) if any(c in word for c in ".eE") else int(word)
+        except ValueError:
+            return word
+
+    def members(self, close: str | None) -> dict:
+        out = {}
+        t = self.t
+        while True:
+            self._ws()
+            if self.i >= len(t) or (close and t[self.i] == close):
+                self.i += 1
+                return out
+            if t.startswith(_G4_Q, self.i):
+                key = self.value()
+            else:
+                j = t.find(":", self.i)
+                if j < 0:
+                    self.i = len(t)
+                    return out
+                key = t[self.i:j].strip()
+                self.i = j
+            self._ws()
+            if self.i < len(t) and t[self.i] == ":":
+                self.i += 1
+            out[key] = self.value()
+            self._ws()
+            if self.i < len(t) and t[self.i] == ",":
+                self.i += 1
+
+
+def _g4_render(v, quote_keys: bool = False) -> str:
+    if isinstance(v, str):
+        return f"{_G4_Q}{v}{_G4_Q}"
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if v is None:
+        return "null"
+    if isinstance(v, dict):
+        return "{" + ",".join(f"{(_G4_Q + str(k) + _G4_Q) if quote_keys else k}:{_g4_render(v[k], quote_keys)}" for k in sorted(v)) + "}"
+    if isinstance(v, (list, tuple)):
+        return "[" + ",".join(_g4_render(x, quote_keys) for x in v) + "]"
+    return str(v)
+
+
+def _g4_balanced(text: str, start: int) -> int:
+    """Index of the brace that closes the one at ``start`` (string marks respected); -1 if it never closes."""
+    depth, i = 0, start
+    while i < len(text):
+        if text.startswith(_G4_Q, i):
+            j = text.find(_G4_Q, i + len(_G4_Q))
+            if j < 0:
+                return -1
+            i = j + len(_G4_Q)
+            continue
+        if text[i] == "{":
+            depth += 1
+        elif text[i] == "}":
+            depth -= 1
+            if depth == 0:
+                return i
+        i += 1
+    return -1
+
+
+@register_parser("gemma4")
+class Gemma4ToolCallParser(ToolCallParser):
+    """Gemma-4's native tool grammar (reference: axon/tools/parsers/gemma4_parser.py):
+    ``<|tool_call>call:name{arg:<|"|>text<|"|>,n:3}<tool_call|>`` in the model turn, results as
+    ``<|tool_response>response:name{value:...}<tool_response|>``, declarations as ``<|tool>declaration:...<tool|>``."""
+    CALL_START, CALL_END = "<|tool_call>", "<tool_call|>"
+    RESP_START, RESP_END = "<|tool_response>", "<tool_response|>"
+
+    def parse(self, response: str):
+        calls, kept, pos = [], [], 0
+        while True:
+            start = response.find(self.CALL_START, pos)
+            if start < 0:
+                kept.append(response[pos:])
+                break
+            head = start + len(self.CALL_START)
+            brace = response.find("{", head)
+            if not response.startswith("call:", head) or brace < 0:
+                kept.append(response[pos:head])
+                pos = head
+                continue
+            close = _g4_balanced(response, brace)
+            if close < 0:
+                kept.append(response[pos:])
+                break
+            name = response[head + len("call:"):brace].strip()
+            args = _Gemma4Values(response[brace + 1:close]).members(None)
+            end = close + 1
+            for closer in (self.CALL_END, "<turn|>"):
+                if response.startswith(closer, end):
+                    end += len(closer)
+                    break
+            if response.startswith(self.RESP_START, end):          # the template leaves a bare opener after a pending call
+                end += len(self.RESP_START)
+            kept.append(response[pos:start])
+            calls.append(ToolCall(name=name, arguments=args))
+            pos = end
+        return calls, "".join(kept).strip()
+
+    def format_tool_call(self, c: ToolCall) -> str:
+        args = c.arguments if isinstance(c.arguments, dict) else {"raw": c.arguments}
+        return f"{self.CALL_START}call:{c.name}{{" + ",".join(f"{k}:{_g4_render(args[k])}" for k in sorted(args)) + f"}}{self.CALL_END}"
+
+    def format_tool_calls(self, calls):
+        return "".join(self.format_tool_call(c) for c in calls)
+
+    def format_tool_result(self, content, name=""):
+        inner = ",".join(f"{k}:{_g4_render(content[k])}" for k in sorted(content)) if isinstance(content, dict) \
+            else f"value:{_g4_render(content)}"
+        return f"{self.RESP_START}response:{name or 'unknown'}{{{inner}}}{self.RESP_END}"
+
+    def get_tool_system_prompt(self, tools) -> str:
+        out = []
+        for tool in tools:
+            fn = tool.get("function", tool)
+            decl = {"description": fn.get("description", "")}
+            params = fn.get("parameters") or {}
+            if params:
+                props = {k: {kk: (str(vv).upper() if kk == "type" else vv) for kk, vv in v.items()} for k, v in (params.get("properties") or {}).items()}
+                decl["parameters"] = {"properties": props, "required": list(params.get("required") or []),
+                                      "type": str(params.get("type", "object")).upper()}
+            out.append(f"<|tool>declaration:{fn.get('name', '')}{_g4_render(decl)}<tool|>")
+        return "".join(out)
+
+

@@ -222,3 +222,59 @@ def test_http_routes():
     assert eng.program_manager.get_num_completed_programs() == 1
     assert c.post("/generate", json={"session_id": "nope", "messages": []}).status_code == 404
     assert c.post("/tokenize", json={"prompt": "ab"}).json()["count"] == 2
+
+
+def test_gemma4_template_keeps_tool_traffic_inside_the_model_turn():
+    """Gemma-4: ``<|turn>role ... <turn|>`` turns, native call / response grammar inside ONE model turn, the empty thought
+    channel re-inserted before earlier model answers, a pending call leaves the turn open on ``<|tool_response>``."""
+    from axon_b200.engine.chat_template.parser import Gemma4ChatTemplateParser
+    from axon_b200.tools.types import ToolCall
+    tok = ByteTokenizer()
+    tok.name_or_path = "google/gemma-4-31b-it"
+    tp = get_tool_call_parser("gemma4")
+    p = ChatTemplateParser.get_parser(tok, tool_parser=tp)
+    assert isinstance(p, Gemma4ChatTemplateParser)
+    call = {"id": "c1", "function": {"name": "add", "arguments": {"a": 1, "b": 2}}}
+    msgs = [{"role": "system", "content": " Be brief. "}, {"role": "user", "content": " hi "},
+            {"role": "assistant", "content": "", "tool_calls": [call]}, {"role": "tool", "tool_call_id": "c1", "content": "3"},
+            {"role": "assistant", "content": "It is 3."}, {"role": "user", "content": "thanks"}]
+    assert p.parse(msgs, add_generation_prompt=True) == (
+        "<bos><|turn>system\nBe brief.<turn|>\n<|turn>user\nhi<turn|>\n<|turn>model\n"
+        "<|tool_call>call:add{a:1,b:2}<tool_call|><|tool_response>response:add{value:<|\"|>3<|\"|>}<tool_response|>"
+        "<|channel>thought\n<channel|>It is 3.<turn|>\n<|turn>user\nthanks<turn|>\n<|turn>model\n<|channel>thought\n<channel|>")
+    # a call without its result yet: the turn stays open and no generation prompt is added
+    assert p.parse(msgs[:3], add_generation_prompt=True).endswith("<|tool_call>call:add{a:1,b:2}<tool_call|><|tool_response>")
+    # thinking on: marker in the system turn, plain generation prompt; tools are declared in the system turn
+    pt = Gemma4ChatTemplateParser(tok, disable_thinking=False, tool_parser=tp)
+    tools = [{"type": "function", "function": {"name": "add", "description": "sum", "parameters": {"type": "object", "properties": {"a": {"type": "integer"}}, "required": ["a"]}}}]
+    r = pt.parse(msgs[1:2], add_generation_prompt=True, tools=tools)
+    assert r.startswith("<bos><|turn>system\n<|think|>\n<|tool>declaration:add{") and r.endswith("<|turn>model\n")
+    with pytest.raises(ValueError, match="text-only"):
+        p.parse([{"role": "user", "content": [{"type": "image", "image": "x"}]}])
+    # the tool grammar round-trips nested values and strings that contain braces and commas
+    c = ToolCall(name="search", arguments={"query": "weather in {Paris}, today", "k": 3, "opts": {"deep": True, "tags": ["a", "b"]}, "x": None})
+    calls, rest = tp.parse("let me look " + tp.format_tool_call(c) + tp.format_tool_call(ToolCall(name="noop", arguments={})))
+    assert rest == "let me look" and calls[0].arguments == c.arguments and calls[1].name == "noop"
+
+
+def test_multimodal_parser_normalises_inline_and_legacy_media():
+    from axon_b200.engine.chat_template.parser import MultiModalChatTemplateParser
+
+    class _Tok(ByteTokenizer):
+        def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=False, **kw):
+            out = ""
+            for m in messages:
+                body = m["content"] if isinstance(m["content"], str) else "".join(
+                    p.get("text", "") if p["type"] == "text" else f"[{p['type']}]" for p in m["content"])
+                out += f"<{m['role']}>{body}"
+            return out + ("<assistant>" if add_generation_prompt else "")
+    p = MultiModalChatTemplateParser(_Tok())
+    msgs = [{"role": "user", "content": "look <image> and <video> please"},
+            {"role": "user", "content": [{"type": "image_url", "image_url": {"url": "u1"}}, {"type": "text", "text": "x"}]}]
+    assert p.collect_media(msgs, ["I0"], ["V0"]) == (["I0", "u1"], ["V0"])
+    assert p.count_placeholders(msgs[1:]) == (1, 0)
+    assert p.parse(msgs, add_generation_prompt=True, images=["I0"], videos=["V0"]) == "<user>look [image] and [video] please<user>[image]x<assistant>"
+    with pytest.raises(ValueError, match="more <image> marks"):
+        p.normalize(msgs, images=[], videos=["V0"])
+    with pytest.raises(ValueError, match="without a placeholder"):
+        p.normalize(msgs[1:], images=["extra"])
