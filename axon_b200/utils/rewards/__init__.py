@@ -118,11 +118,16 @@ def _as_number(s: str) -> float | None:
 
 
 def math_equal(pred: str, truth: str) -> bool:
+    """Quick string / numeric comparison first, then the full grader (normalisation in the MATH checker's style, tuples /
+    intervals / sets element-wise, symbolic equality with sympy): ``math_grading.grade_answer``."""
     a, b = normalize_math(pred), normalize_math(truth)
     if a == b:
         return True
     x, y = _as_number(a), _as_number(b)
-    return x is not None and y is not None and abs(x - y) <= 1e-6 * max(1.0, abs(y))
+    if x is not None and y is not None:
+        return abs(x - y) <= 1e-6 * max(1.0, abs(y))
+    from .math_grading import grade_answer
+    return grade_answer(pred, truth)
 
 
 @register_reward("math")
@@ -132,7 +137,8 @@ def math_reward_fn(task_info: dict, action: str, config: RewardConfig | None = N
     if truths is None:
         return RewardOutput(cfg.unk_error_reward, False, {"error": "no ground truth"})
     truths = truths if isinstance(truths, (list, tuple)) else [truths]
-    pred = last_boxed(_strip_think(action or ""))
+    from .math_grading import extract_answer
+    pred = extract_answer(_strip_think(action or ""))        # the last boxed expression, else a closing "answer is ..."
     if pred is None:
         return RewardOutput(cfg.format_error_reward, False, {"error": "no boxed answer"})
     for t in truths:

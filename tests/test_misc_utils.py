@@ -65,3 +65,22 @@ def test_precision_names_device_helpers_and_padding_round_trip(capsys):
     out = capsys.readouterr().out
     assert "step:2 - loss:1.5" in out and "actor shown" in out and "hidden" not in out and "[Rank 3] hello" in out
     DecoratorLoggerBase("x", logger=logging.getLogger("t"), level=logging.INFO).logging_function("via logging")
+
+
+def test_math_grading_normalises_and_compares_symbolically():
+    from axon_b200.utils.rewards import RewardConfig, math_reward_fn
+    from axon_b200.utils.rewards.math_grading import extract_answer, grade_answer as g
+    same = [("\\frac12", "1/2"), ("0.5", "\\frac{1}{2}"), ("\\dfrac{3}{4}", "0.75"), ("5 cm", "5"), ("30^\\circ", "30"), ("x = 5", "5"),
+            ("1,234", "1234"), ("\\$12.50", "12.5"), ("2\\sqrt{3}", "\\sqrt{12}"), ("(1, 2)", "(1,2)"), ("\\{1,2,3\\}", "\\{3,2,1\\}"),
+            ("3, 1", "1, 3"), ("x^2+2x+1", "(x+1)^2"), ("\\frac{\\pi}{2}", "pi/2"), ("\\text{seven}", "7"), ("10\\%", "10"),
+            ("2^{10}", "1024"), ("\\sqrt2", "\\sqrt{2}"), ("12 square units", "12"), ("3.0", "3"), ("[0,1)", "[0,1)"), ("\\infty", "oo"),
+            ("\\frac{1}{3}", "0.3333333333")]
+    different = [("(1,2)", "[1,2]"), ("7", "8"), ("\\frac{1}{3}", "0.33"), ("abc", "abd"), ("(1,2)", "(2,1)"), ("x+1", "x+2"), ("", "1")]
+    assert [p for p in same if not g(*p)] == []
+    assert [p for p in different if g(*p)] == []
+    assert extract_answer("so the final answer is 42.") == "42" and extract_answer("x \\boxed{\\frac{1}{2}} y") == "\\frac{1}{2}"
+    cfg = RewardConfig()
+    ok = math_reward_fn({"ground_truth": ["\\frac{\\sqrt{12}}{2}"]}, "<think>hm</think> thus \\boxed{\\sqrt{3}}", cfg)
+    assert ok.is_correct and ok.reward == cfg.correct_reward
+    assert not math_reward_fn({"ground_truth": "4"}, "\\boxed{5}", cfg).is_correct
+    assert math_reward_fn({"ground_truth": "4"}, "no answer here", cfg).reward == cfg.format_error_reward
