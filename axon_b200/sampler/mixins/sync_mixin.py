@@ -4,8 +4,8 @@
 The reference materialises every parameter out of its sharded trainer (all-gathers), renames it and
 loads it into the inference engine. Here the sampler and the trainer of a GPU share one flat
 parameter buffer, so ``sampler_mode`` moves no weight at all: it asks the colocated trainer to
-vacate the device (optimizer state to pinned host memory), re-creates the KV pool in the freed space
-and resumes the server. A sampler that does NOT share the buffer (separate process) falls back to
+make room (gradients freed; optimizer state to pinned host memory only when the KV pool would not fit beside it),
+re-creates the KV pool and resumes the server. A sampler that does NOT share the buffer (separate process) falls back to
 pulling named tensors from its fused trainer peer."""
 from __future__ import annotations
 
@@ -24,7 +24,12 @@ class SyncSamplerMixin:
     def sampler_mode(self):
         peer = self._trainer_peer()
         if peer is not None:
-            peer.rollout_mode()
+            need = None
+            eng = getattr(self, "engine", None)
+            if eng is not None and getattr(eng, "_num_pages", None):
+                from ..kv_cache import PagedKVCache
+                need = int(eng._num_pages) * PagedKVCache.bytes_per_page(eng.cfg, eng.model.params.flat.element_size())
+            peer.rollout_mode(need)
             if not self.shares_trainer_weights:
                 self.server.update_weights(peer.model.params.views.items())
         self.server.wake_up()
