@@ -109,7 +109,7 @@ def build_role_worker_mapping(config, is_async: bool):
     actor_cls = _synthesize("ActorWorker", TrainerWorker, t_mixins)
     sampler_cls = _synthesize("SamplerRoleWorker", SamplerWorker, s_mixins)
     actor_pool, sampler_pool = _build_resource_pools(config, disagg)
-    sampler_cfg = config if is_async else {**{k: config.get(k) for k in ("model_path", "seed", "force_cpu", "global_profiler")},
+    sampler_cfg = config if is_async else {**{k: config.get(k) for k in ("model_path", "seed", "force_cpu", "global_profiler", "max_seq_length", "moe_replay")},
                                             "sampler": config["sampler"]}
     mapping = {
         Role.Actor: RoleWorkerConfig(actor_cls, actor_pool, {"config": config["actor"], "name": "actor"}),

@@ -29,8 +29,8 @@ from .config import ModelConfig
 from .params import FlatParams
 
 FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text",
-                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl")
-VISION_LANGUAGE_TYPES = ("qwen2_vl",)
+                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl")
+VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl")
 
 
 # ------------------------------------------------------------------------------------------ small pieces
@@ -1485,7 +1485,102 @@ class _Qwen2VL(_Spec):
                           self.P(W, l, "mlp.down_proj.weight"))
 
 
-_SPECS = {"qwen2_vl": _Qwen2VL, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
+class _Qwen25VL(_Qwen2VL):
+    """Qwen2.5-VL: the decoder of Qwen2-VL; the vision tower has RMSNorm, a gated SiLU MLP with biases and WINDOWED
+    attention - merge-size units of patches are regrouped window by window (``window_size`` pixels a side), most blocks
+    attend inside a window only, the blocks in ``fullatt_block_indexes`` inside a whole frame; the merged embeddings are
+    put back into raster order at the end. Reference: axon/models/transformers/qwen2_vl.py (shared forward), HF
+    modeling_qwen2_5_vl.py."""
+
+    def __init__(self, hf):
+        v = dict(hf["vision_config"])
+        v.setdefault("embed_dim", v["hidden_size"])
+        hf = {**hf, "vision_config": v}
+        super().__init__(hf)
+        self.vF = int(v["intermediate_size"])
+        self.window = int(v.get("window_size", 112))
+        self.full_blocks = set(v.get("fullatt_block_indexes") or [])
+
+    def layout(self):
+        lay = OrderedDict()
+        E, m2 = self.vE, self.merge ** 2
+        lay["model.visual.patch_embed.proj.weight"] = (E, self.patch_dim)
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            lay[p + "norm1.weight"], lay[p + "norm2.weight"] = (E,), (E,)
+            lay[p + "attn.qkv.weight"], lay[p + "attn.qkv.bias"] = (3 * E, E), (3 * E,)
+            lay[p + "attn.proj.weight"], lay[p + "attn.proj.bias"] = (E, E), (E,)
+            for n, (o, i) in (("gate_proj", (self.vF, E)), ("up_proj", (self.vF, E)), ("down_proj", (E, self.vF))):
+                lay[p + f"mlp.{n}.weight"], lay[p + f"mlp.{n}.bias"] = (o, i), (o,)
+        lay["model.visual.merger.ln_q.weight"] = (E,)
+        lay["model.visual.merger.mlp.0.weight"], lay["model.visual.merger.mlp.0.bias"] = (E * m2, E * m2), (E * m2,)
+        lay["model.visual.merger.mlp.2.weight"], lay["model.visual.merger.mlp.2.bias"] = (self.H, E * m2), (self.H,)
+        text = _Qwen2VL.layout(self)
+        for n, sh in text.items():
+            if not n.startswith("model.visual."):
+                lay[n] = sh
+        return lay
+
+    def window_order(self, grid_thw):
+        """(order of the merge units window by window, segment boundaries in patches of that order)."""
+        ms, unit = self.merge, self.merge ** 2
+        side = self.window // ms // self.v["patch_size"]
+        order, cu, base = [], [0], 0
+        for t, h, w in grid_thw.tolist():
+            gh, gw = h // ms, w // ms
+            idx = torch.arange(t * gh * gw).reshape(t, gh, gw)
+            ph, pw = side - gh % side, side - gw % side
+            nh, nw = (gh + ph) // side, (gw + pw) // side
+            pad = F.pad(idx, (0, pw, 0, ph), value=-1).reshape(t, nh, side, nw, side).permute(0, 1, 3, 2, 4).reshape(t, nh * nw, side, side)
+            counts = (pad >= 0).sum((2, 3)).reshape(-1)
+            flat = pad.reshape(-1)
+            order.append(flat[flat >= 0] + base)
+            for c in counts.tolist():
+                if c:
+                    cu.append(cu[-1] + c * unit)
+            base += t * gh * gw
+        return torch.cat(order), cu
+
+    def vision(self, W, patches, grid_thw):
+        E, Hh, unit = self.vE, self.vH, self.merge ** 2
+        hd = E // Hh
+        x = linear(patches.to(W["model.visual.patch_embed.proj.weight"].dtype), W["model.visual.patch_embed.proj.weight"])
+        cos, sin = self.vision_rotary(grid_thw, x.device)
+        order, cu_win = self.window_order(grid_thw)
+        order = order.to(x.device)
+        N = x.shape[0]
+        regroup = lambda t: t.reshape(N // unit, unit, -1)[order].reshape(N, -1)      # noqa: E731
+        x, cos, sin = regroup(x), regroup(cos), regroup(sin)
+        frames, a = [], 0
+        for t, h, w in grid_thw.tolist():
+            for _ in range(int(t)):
+                frames.append((a, a + int(h) * int(w)))
+                a += int(h) * int(w)
+        assert a == N, f"{N} patches for grids that describe {a}"
+        windows = list(zip(cu_win[:-1], cu_win[1:]))
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            h1 = rms_norm(x, W[p + "norm1.weight"], 1e-6)
+            q, k, v = (linear(h1, W[p + "attn.qkv.weight"]) + W[p + "attn.qkv.bias"]).view(-1, 3, Hh, hd).unbind(1)
+            q = (q.float() * cos[:, None] + rotate_half(q.float()) * sin[:, None]).to(x.dtype)
+            k = (k.float() * cos[:, None] + rotate_half(k.float()) * sin[:, None]).to(x.dtype)
+            outs = []
+            for s0, s1 in (frames if b in self.full_blocks else windows):
+                o = F.scaled_dot_product_attention(q[s0:s1].transpose(0, 1)[None], k[s0:s1].transpose(0, 1)[None],
+                                                   v[s0:s1].transpose(0, 1)[None])
+                outs.append(o[0].transpose(0, 1).reshape(s1 - s0, E))
+            x = x + linear(torch.cat(outs), W[p + "attn.proj.weight"]) + W[p + "attn.proj.bias"]
+            h2 = rms_norm(x, W[p + "norm2.weight"], 1e-6)
+            g = linear(h2, W[p + "mlp.gate_proj.weight"]) + W[p + "mlp.gate_proj.bias"]
+            u = linear(h2, W[p + "mlp.up_proj.weight"]) + W[p + "mlp.up_proj.bias"]
+            x = x + linear(F.silu(g) * u, W[p + "mlp.down_proj.weight"]) + W[p + "mlp.down_proj.bias"]
+        x = rms_norm(x, W["model.visual.merger.ln_q.weight"], 1e-6).view(-1, E * unit)
+        x = F.gelu(linear(x, W["model.visual.merger.mlp.0.weight"]) + W["model.visual.merger.mlp.0.bias"])
+        x = linear(x, W["model.visual.merger.mlp.2.weight"]) + W["model.visual.merger.mlp.2.bias"]
+        return x[torch.argsort(order)]
+
+
+_SPECS = {"qwen2_vl": _Qwen2VL, "qwen2_5_vl": _Qwen25VL, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
           "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen35, "qwen3_5_moe_text": _Qwen35}
 
 

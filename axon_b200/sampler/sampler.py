@@ -91,6 +91,8 @@ class SamplerWorker(Worker, DistProfilerExtension):
             free, total = torch.cuda.mem_get_info()
             util = float(_get(scfg, "gpu_memory_utilization", 0.85))
             kv_bytes = max(1 << 28, int(free - (1.0 - util) * total))
+            if self.shares_trainer_weights:
+                kv_bytes = self._kv_bytes_beside_optimizer(trainer, kv_bytes)
         num_pages = _get(scfg, "num_kv_pages", None)
         self.engine = GenerationEngine(self.model, num_pages=num_pages, max_num_seqs=int(_get(scfg, "max_num_seqs", 256)),
                                        max_num_batched_tokens=int(_get(scfg, "max_num_batched_tokens", 32768)),
@@ -135,6 +137,29 @@ class SamplerWorker(Worker, DistProfilerExtension):
         self._http_thread = threading.Thread(target=self._http_server.run, daemon=True, name="sampler-http")
         self._http_thread.start()
         self.address = f"http://127.0.0.1:{port}"
+
+    def _kv_bytes_beside_optimizer(self, trainer, kv_bytes: int) -> int:
+        """Colocated mode: the trainer's optimizer state (12 bytes per parameter of its shard, allocated at its first
+        step) can stay on the device during rollout if the KV pool leaves room for it. When the pool that remains
+        still covers the expected demand - ``kv_expected_fill`` (0.4) of the worst case of every sequence at full
+        length at once - take the smaller pool; a pool that turns out too small only costs preemptions. Otherwise keep
+        the large pool and let the optimizer state move to the host around every rollout."""
+        from .kv_cache import PagedKVCache
+        cfg, scfg = self.config, self.scfg
+        eng = getattr(trainer, "engine", None)
+        if eng is None or getattr(trainer, "_forward_only", False) or getattr(eng, "master", None) is not None:
+            return kv_bytes                      # no optimizer, or its state is already counted in the free memory
+        opt_bytes = 12 * int(self.model.params.numel) // max(1, int(getattr(eng, "opt_world", 1)))
+        fill = _get(scfg, "kv_expected_fill", 0.4)
+        if fill is None:
+            return kv_bytes
+        seq_len = int(_get(scfg, "max_model_len", None) or _get(cfg, "max_seq_length", 0) or 0)
+        if seq_len <= 0:
+            return kv_bytes
+        per_token = PagedKVCache.bytes_per_page(self.model.cfg, self.model.params.flat.element_size()) / 128
+        want = float(fill) * int(_get(scfg, "max_num_seqs", 256)) * seq_len * per_token
+        fit = kv_bytes - opt_bytes
+        return int(fit) if fit >= max(want, 4 << 30) else kv_bytes
 
     # ------------------------------------------------------------------ direct methods
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)

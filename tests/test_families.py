@@ -475,3 +475,54 @@ def test_sampler_generates_from_a_prompt_with_an_image():
             srv.submit(p_img, {}, image_data=["data:image/png;base64,AAAA"])
     finally:
         srv.stop()
+
+
+def test_qwen2_5_vl_windowed_tower_matches_transformers():
+    """Windowed vision tower (regrouping by windows, full-attention blocks, RMSNorm, gated MLP) + decoder against HF
+    Qwen2.5-VL with two images of different sizes (one larger than a window): logits and tower gradients."""
+    try:
+        from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    except Exception:
+        pytest.skip("transformers has no Qwen2.5-VL")
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.dense import PackedBatch
+    from axon_b200.models.families import FamilyModel
+    torch.manual_seed(0)
+    cfg = Qwen2_5_VLConfig(text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                            vocab_size=300, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}, max_position_embeddings=512,
+                                            tie_word_embeddings=False),
+                           vision_config=dict(depth=4, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+                                              temporal_patch_size=2, spatial_merge_size=2, window_size=16, fullatt_block_indexes=[1, 3]),
+                           image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    ref = Qwen2_5_VLForConditionalGeneration(cfg).float().eval()
+    grid = torch.tensor([[1, 6, 8], [1, 2, 4]])                    # 48 + 8 patches -> 12 + 2 placeholder tokens; windows of 2 x 2 merged units
+    pix = torch.randn(56, 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 292] + [290] * 12 + [293, 44, 292] + [290] * 2 + [293, 9, 120, 33]])
+    types = (ids == 290).int()
+    with torch.no_grad():
+        want = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+        pos = ref.model.get_rope_index(ids, types, image_grid_thw=grid, attention_mask=torch.ones_like(ids))[0][:, 0]
+    m = FamilyModel(ModelConfig.from_hf_dict(cfg.to_dict()), device="cpu", dtype=torch.float32)
+    m.load_state_dict(ref.state_dict())
+    mm = {"pixel_values": pix, "image_grid_thw": grid, "mrope_positions": pos}
+    z = m.logits(ids[0].to(torch.int32), multimodal=mm)
+    assert (z - want).abs().max() < 2e-4, (z - want).abs().max()
+    # height / width rows and every text position agree with HF; for image tokens this build keeps the temporal row at the
+    # image's first position (a still image has one frame), where transformers 5.5 scales that offset by tokens_per_second
+    mine = m.rotary_rows(ids[0].tolist(), {"image_grid_thw": grid}).long()
+    assert torch.equal(mine[1:], pos[1:].long()) and torch.equal(mine[0][types[0] == 0], pos[0][types[0] == 0].long())
+    assert mine[0][types[0] == 1].tolist() == [2] * 12 + [9] * 2
+    batch = PackedBatch.from_sequences([ids[0]], "cpu")
+    batch.multimodal = mm
+    lp, _ = m.forward(batch, 1.0, save_for_backward=True)
+    g = torch.linspace(0.5, 1.5, lp.numel())
+    g[-1] = 0
+    m.backward(g)
+    out = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+    lp_ref = torch.log_softmax(out[:-1], -1).gather(1, ids[0, 1:, None])[:, 0]
+    (lp_ref * g[:-1]).sum().backward()
+    sd = dict(ref.named_parameters())
+    for name in ("model.visual.blocks.0.attn.qkv.weight", "model.visual.blocks.1.mlp.gate_proj.bias", "model.visual.merger.ln_q.weight",
+                 "model.visual.patch_embed.proj.weight"):
+        a, b = m.params.grads[name], sd[name].grad.reshape(m.params.grads[name].shape)
+        assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
