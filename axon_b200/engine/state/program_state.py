@@ -204,11 +204,26 @@ class ProgramState:
         self.last_llm_call_time = time.monotonic()
 
     def get_steps_from_prefix_tree(self) -> list[Step]:
+        """One Step per leaf: the tokens on the path from the root. Runs of nodes with a single child extend the
+        frame's lists in place (a session is mostly one long chain); lists are copied at branch points only, where
+        every sibling but the first zeroes the masks of the shared prefix (it is trained once)."""
         out: list[Step] = []
         # frame: node, ids, strs, logprobs, masks, routermaps, max step idx, multimodal data
         stack = [(self.prefix_tree.root, [], [], [], [], [], -1, None)]
         while stack:
             node, ids, strs, lps, masks, rms, top, mm = stack.pop()
+            while len(node.children) == 1:
+                (child,) = node.children.values()
+                ids.append(child.token_id)
+                strs.append(child.token_str)
+                lps.append(child.logprob)
+                masks.append(max(child.masks))
+                rms.append(child.moe_routermap if _has_entries(child.moe_routermap) else None)
+                if child.step_idx > top:
+                    top = child.step_idx
+                if child.multi_modal_data:
+                    mm = child.multi_modal_data
+                node = child
             if node.is_leaf():
                 if ids:
                     out.append(self._leaf_step(ids, strs, lps, masks, rms, top, mm))

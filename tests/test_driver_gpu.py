@@ -52,6 +52,8 @@ def test_sync_colocated_driver_on_gpu_with_resume(tmp_path):
         a_worker = drv.sampler_wg.workers[0].role_objects["actor"]
         s_worker = drv.sampler_wg.workers[0].role_objects["sampler"]
         assert a_worker.device.type == "cuda" and s_worker.shares_trainer_weights
+        # the small KV pool fits beside the optimizer state, so the mode switch leaves that state on the device
+        assert a_worker.rollout_kept_optimizer is True and a_worker.engine.master is not None
         checksum, sched = a_worker.params_checksum(), a_worker.engine.sched_step
     finally:
         drv.shutdown()
