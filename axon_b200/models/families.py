@@ -224,6 +224,13 @@ def gated_delta_rule(q, k, v, g, beta, state=None):
     final state [H, Dk, Dv]). Recurrent form in fp32 (the oracle of the chunked kernels)."""
     n, H, Dk = k.shape
     Dv = v.shape[-1]
+    if q.is_cuda and q.dtype == torch.bfloat16 and Dk in (64, 128, 256) and n > 0:
+        # the recurrent CUDA kernels (forward and reverse sweep), differentiable through their autograd wrapper
+        from ..ops.gdn import gated_delta_rule as native_rule
+        cu = torch.tensor([0, n], dtype=torch.int32, device=q.device)
+        o, st = native_rule(q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous(), g.float(), beta.float(), cu,
+                            scale=1.0 / math.sqrt(Dk), initial_state=None if state is None else state.float()[None])
+        return o.to(v.dtype), st[0]
     qf, kf, vf = q.float() / math.sqrt(Dk), k.float(), v.float()
     S = torch.zeros(H, Dk, Dv, dtype=torch.float32, device=q.device) if state is None else state.float()
     outs = []
