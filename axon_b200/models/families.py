@@ -29,8 +29,8 @@ from .config import ModelConfig
 from .params import FlatParams
 
 FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text",
-                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl")
-VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl")
+                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl", "qwen3_vl")
+VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl")
 
 
 # ------------------------------------------------------------------------------------------ small pieces
@@ -1474,7 +1474,8 @@ class _Qwen2VL(_Spec):
         key = ("mrope", id(pos))
         if ctx.get("_mrope_key") != key:
             from .vision import mrope_tables
-            c, s = mrope_tables(pos, self.D, float(self.rope_params["rope_theta"]), self.sections, device=pos.device)
+            c, s = mrope_tables(pos, self.D, float(self.rope_params["rope_theta"]), self.sections, device=pos.device,
+                                interleaved=getattr(self, "mrope_interleaved", False))
             ctx["_mrope"], ctx["_mrope_key"] = (torch.cat([c, c], -1), torch.cat([s, s], -1)), key
         return ctx["_mrope"]
 
@@ -1587,7 +1588,157 @@ class _Qwen25VL(_Qwen2VL):
         return x[torch.argsort(order)]
 
 
-_SPECS = {"qwen2_vl": _Qwen2VL, "qwen2_5_vl": _Qwen25VL, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
+class _Qwen3VL(_Qwen2VL):
+    """Qwen3-VL: a Qwen3 decoder (no projection biases, RMSNorm on every query / key head before the rotation) with
+    INTERLEAVED three-row rotary positions; the vision tower adds bilinearly interpolated learned position embeddings
+    to the patches, uses LayerNorm blocks with a tanh-GELU MLP, and besides the final merger taps the outputs of the
+    blocks in ``deepstack_visual_indexes``: each tap is merged (LayerNorm AFTER grouping merge^2 patches) and ADDED to
+    the decoder's hidden states at the image tokens after decoder layer 0, 1, ... ("DeepStack"). Reference: HF
+    modeling_qwen3_vl.py; the reference patches this family in axon/models/transformers/qwen3_vl.py."""
+    mrope_interleaved = True
+
+    def __init__(self, hf):
+        v = dict(hf["vision_config"])
+        v.setdefault("embed_dim", v["hidden_size"])
+        v.setdefault("mlp_ratio", v["intermediate_size"] / v["hidden_size"])
+        hf = {**hf, "vision_config": v}
+        super().__init__(hf)
+        self.vF = int(v["intermediate_size"])
+        self.taps = list(v.get("deepstack_visual_indexes") or [])
+        self.grid_side = int(round(v["num_position_embeddings"] ** 0.5))
+        self._deepstack, self._visual_idx = None, None
+
+    def layout(self):
+        lay = OrderedDict()
+        E, m2 = self.vE, self.merge ** 2
+        lay["model.visual.patch_embed.proj.weight"], lay["model.visual.patch_embed.proj.bias"] = (E, self.patch_dim), (E,)
+        lay["model.visual.pos_embed.weight"] = (self.grid_side ** 2, E)
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            for n in ("norm1", "norm2"):
+                lay[p + n + ".weight"], lay[p + n + ".bias"] = (E,), (E,)
+            lay[p + "attn.qkv.weight"], lay[p + "attn.qkv.bias"] = (3 * E, E), (3 * E,)
+            lay[p + "attn.proj.weight"], lay[p + "attn.proj.bias"] = (E, E), (E,)
+            lay[p + "mlp.linear_fc1.weight"], lay[p + "mlp.linear_fc1.bias"] = (self.vF, E), (self.vF,)
+            lay[p + "mlp.linear_fc2.weight"], lay[p + "mlp.linear_fc2.bias"] = (E, self.vF), (E,)
+        for p, nd in [("model.visual.merger.", E)] + [(f"model.visual.deepstack_merger_list.{i}.", E * m2) for i in range(len(self.taps))]:
+            lay[p + "norm.weight"], lay[p + "norm.bias"] = (nd,), (nd,)
+            lay[p + "linear_fc1.weight"], lay[p + "linear_fc1.bias"] = (E * m2, E * m2), (E * m2,)
+            lay[p + "linear_fc2.weight"], lay[p + "linear_fc2.bias"] = (self.H, E * m2), (self.H,)
+        lay["model.language_model.embed_tokens.weight"] = (self.V, self.H)
+        for l in range(self.L):
+            p = f"model.language_model.layers.{l}."
+            for n, rows in (("q_proj", self.nh * self.D), ("k_proj", self.nkv * self.D), ("v_proj", self.nkv * self.D)):
+                lay[p + f"self_attn.{n}.weight"] = (rows, self.H)
+            lay[p + "self_attn.o_proj.weight"] = (self.H, self.nh * self.D)
+            lay[p + "self_attn.q_norm.weight"], lay[p + "self_attn.k_norm.weight"] = (self.D,), (self.D,)
+            lay[p + "mlp.gate_proj.weight"], lay[p + "mlp.up_proj.weight"] = (self.F, self.H), (self.F, self.H)
+            lay[p + "mlp.down_proj.weight"] = (self.H, self.F)
+            lay[p + "input_layernorm.weight"], lay[p + "post_attention_layernorm.weight"] = (self.H,), (self.H,)
+        lay["model.language_model.norm.weight"] = (self.H,)
+        if not self.tied:
+            lay["lm_head.weight"] = (self.V, self.H)
+        return lay
+
+    def init_kind(self, name):
+        if name.endswith(("q_norm.weight", "k_norm.weight")) or ".norm." in name:
+            return "zeros" if name.endswith(".bias") else "ones"
+        return super().init_kind(name)
+
+    def position_embeddings(self, W, grid_thw):
+        """Learned [side x side] table sampled bilinearly at every patch of every grid, in merge-window order."""
+        table, side, ms = W["model.visual.pos_embed.weight"], self.grid_side, self.merge
+        outs = []
+        for t, h, w in grid_thw.tolist():
+            hs, ws = torch.linspace(0, side - 1, h), torch.linspace(0, side - 1, w)
+            h0, w0 = hs.int(), ws.int()
+            h1, w1 = (h0 + 1).clip(max=side - 1), (w0 + 1).clip(max=side - 1)
+            dh, dw = (hs - h0).to(table.dtype), (ws - w0).to(table.dtype)
+            pe = 0
+            for hi, wi, wt in ((h0, w0, (1 - dh)[:, None] * (1 - dw)[None]), (h0, w1, (1 - dh)[:, None] * dw[None]),
+                               (h1, w0, dh[:, None] * (1 - dw)[None]), (h1, w1, dh[:, None] * dw[None])):
+                idx = (hi.long()[:, None] * side + wi.long()[None]).reshape(-1).to(table.device)
+                pe = pe + table[idx] * wt.reshape(-1, 1).to(table.device)
+            pe = pe.repeat(int(t), 1).view(int(t), h // ms, ms, w // ms, ms, -1).permute(0, 1, 3, 2, 4, 5).reshape(int(t) * h * w, -1)
+            outs.append(pe)
+        return torch.cat(outs)
+
+    def _merge(self, W, p, x, after_grouping: bool):
+        E, m2 = self.vE, self.merge ** 2
+        if after_grouping:
+            x = F.layer_norm(x.view(-1, E * m2), (E * m2,), W[p + "norm.weight"], W[p + "norm.bias"], 1e-6)
+        else:
+            x = F.layer_norm(x, (E,), W[p + "norm.weight"], W[p + "norm.bias"], 1e-6).view(-1, E * m2)
+        x = F.gelu(linear(x, W[p + "linear_fc1.weight"]) + W[p + "linear_fc1.bias"])
+        return linear(x, W[p + "linear_fc2.weight"]) + W[p + "linear_fc2.bias"]
+
+    def vision(self, W, patches, grid_thw):
+        """-> (embeddings for the placeholder tokens [N / merge^2, H], list of DeepStack features of the same shape)."""
+        E, Hh = self.vE, self.vH
+        hd = E // Hh
+        x = linear(patches.to(W["model.visual.patch_embed.proj.weight"].dtype), W["model.visual.patch_embed.proj.weight"]) \
+            + W["model.visual.patch_embed.proj.bias"]
+        x = x + self.position_embeddings(W, grid_thw).to(x.dtype)
+        cos, sin = self.vision_rotary(grid_thw, x.device)
+        segs, a = [], 0
+        for t, h, w in grid_thw.tolist():
+            for _ in range(int(t)):
+                segs.append((a, a + int(h) * int(w)))
+                a += int(h) * int(w)
+        assert a == x.shape[0], f"{x.shape[0]} patches for grids that describe {a}"
+        taps = []
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            h1 = F.layer_norm(x, (E,), W[p + "norm1.weight"], W[p + "norm1.bias"], 1e-6)
+            q, k, v = (linear(h1, W[p + "attn.qkv.weight"]) + W[p + "attn.qkv.bias"]).view(-1, 3, Hh, hd).unbind(1)
+            q = (q.float() * cos[:, None] + rotate_half(q.float()) * sin[:, None]).to(x.dtype)
+            k = (k.float() * cos[:, None] + rotate_half(k.float()) * sin[:, None]).to(x.dtype)
+            outs = []
+            for s0, s1 in segs:
+                o = F.scaled_dot_product_attention(q[s0:s1].transpose(0, 1)[None], k[s0:s1].transpose(0, 1)[None],
+                                                   v[s0:s1].transpose(0, 1)[None])
+                outs.append(o[0].transpose(0, 1).reshape(s1 - s0, E))
+            x = x + linear(torch.cat(outs), W[p + "attn.proj.weight"]) + W[p + "attn.proj.bias"]
+            h2 = F.layer_norm(x, (E,), W[p + "norm2.weight"], W[p + "norm2.bias"], 1e-6)
+            m = F.gelu(linear(h2, W[p + "mlp.linear_fc1.weight"]) + W[p + "mlp.linear_fc1.bias"], approximate="tanh")
+            x = x + linear(m, W[p + "mlp.linear_fc2.weight"]) + W[p + "mlp.linear_fc2.bias"]
+            if b in self.taps:
+                taps.append(self._merge(W, f"model.visual.deepstack_merger_list.{self.taps.index(b)}.", x, after_grouping=True))
+        return self._merge(W, "model.visual.merger.", x, after_grouping=False), taps
+
+    def embed(self, W, ids, multimodal=None):
+        x = W["model.language_model.embed_tokens.weight"][ids]
+        self._deepstack, self._visual_idx = None, None
+        if multimodal and multimodal.get("pixel_values") is not None and multimodal["pixel_values"].numel():
+            vis, taps = self.vision(W, multimodal["pixel_values"].to(x.device), multimodal["image_grid_thw"])
+            where = torch.zeros_like(ids, dtype=torch.bool)
+            for tok in (self.image_token, self.video_token):
+                if tok is not None:
+                    where |= ids == tok
+            idx = torch.nonzero(where).flatten()
+            assert idx.numel() == vis.shape[0], f"{idx.numel()} placeholder tokens for {vis.shape[0]} vision embeddings"
+            x = x.index_copy(0, idx, vis.to(x.dtype))
+            self._deepstack, self._visual_idx = [t.to(x.dtype) for t in taps], idx
+        return x
+
+    def layer(self, W, l, x, ctx):
+        T = x.shape[0]
+        h = rms_norm(x, self.P(W, l, "input_layernorm.weight"), self.eps)
+        cos, sin = self.rotary(ctx)
+        q = rms_norm(linear(h, self.P(W, l, "self_attn.q_proj.weight")).view(T, self.nh, self.D), self.P(W, l, "self_attn.q_norm.weight"), self.eps)
+        k = rms_norm(linear(h, self.P(W, l, "self_attn.k_proj.weight")).view(T, self.nkv, self.D), self.P(W, l, "self_attn.k_norm.weight"), self.eps)
+        v = linear(h, self.P(W, l, "self_attn.v_proj.weight")).view(T, self.nkv, self.D)
+        o = attend(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, ctx, l, self.D ** -0.5)
+        x = x + linear(o.reshape(T, self.nh * self.D), self.P(W, l, "self_attn.o_proj.weight"))
+        h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps)
+        x = x + linear(F.silu(linear(h, self.P(W, l, "mlp.gate_proj.weight"))) * linear(h, self.P(W, l, "mlp.up_proj.weight")),
+                       self.P(W, l, "mlp.down_proj.weight"))
+        if self._deepstack is not None and l < len(self._deepstack):
+            x = x.index_add(0, self._visual_idx, self._deepstack[l])
+        return x
+
+
+_SPECS = {"qwen2_vl": _Qwen2VL, "qwen2_5_vl": _Qwen25VL, "qwen3_vl": _Qwen3VL, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
           "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen35, "qwen3_5_moe_text": _Qwen35}
 
 

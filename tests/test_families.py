@@ -526,3 +526,53 @@ def test_qwen2_5_vl_windowed_tower_matches_transformers():
                  "model.visual.patch_embed.proj.weight"):
         a, b = m.params.grads[name], sd[name].grad.reshape(m.params.grads[name].shape)
         assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
+
+
+def test_qwen3_vl_deepstack_and_interleaved_rotary_match_transformers():
+    """Qwen3-VL: interpolated position table, DeepStack taps added after the first decoder layers, interleaved
+    three-row rotary positions, query / key norms - logits and gradients (tower taps included) against HF."""
+    try:
+        from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+    except Exception:
+        pytest.skip("transformers has no Qwen3-VL")
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.dense import PackedBatch
+    from axon_b200.models.families import FamilyModel
+    torch.manual_seed(0)
+    cfg = Qwen3VLConfig(text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                                         head_dim=16, vocab_size=300, rope_scaling={"rope_type": "default", "mrope_section": [2, 3, 3], "mrope_interleaved": True},
+                                         max_position_embeddings=512, tie_word_embeddings=False),
+                        vision_config=dict(depth=3, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+                                           temporal_patch_size=2, spatial_merge_size=2, num_position_embeddings=64, deepstack_visual_indexes=[0, 1]),
+                        image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    ref = Qwen3VLForConditionalGeneration(cfg).float().eval()
+    grid = torch.tensor([[1, 6, 8], [1, 2, 4]])
+    pix = torch.randn(56, 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 292] + [290] * 12 + [293, 44, 292] + [290] * 2 + [293, 9, 120, 33]])
+    types = (ids == 290).int()
+    with torch.no_grad():
+        want = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+        pos = ref.model.get_rope_index(ids, types, image_grid_thw=grid, attention_mask=torch.ones_like(ids))[0][:, 0]
+    m = FamilyModel(ModelConfig.from_hf_dict(cfg.to_dict()), device="cpu", dtype=torch.float32)
+    m.load_state_dict(ref.state_dict())
+    mm = {"pixel_values": pix, "image_grid_thw": grid, "mrope_positions": pos}
+    z = m.logits(ids[0].to(torch.int32), multimodal=mm)
+    assert (z - want).abs().max() < 2e-4, (z - want).abs().max()
+    assert torch.equal(m.rotary_rows(ids[0].tolist(), {"image_grid_thw": grid}).long(), pos.long())
+    t_ids = torch.randint(0, 280, (1, 12))
+    with torch.no_grad():
+        assert (m.logits(t_ids[0].to(torch.int32)) - ref(input_ids=t_ids).logits[0].float()).abs().max() < 2e-4
+    batch = PackedBatch.from_sequences([ids[0]], "cpu")
+    batch.multimodal = mm
+    lp, _ = m.forward(batch, 1.0, save_for_backward=True)
+    g = torch.linspace(0.5, 1.5, lp.numel())
+    g[-1] = 0
+    m.backward(g)
+    out = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+    lp_ref = torch.log_softmax(out[:-1], -1).gather(1, ids[0, 1:, None])[:, 0]
+    (lp_ref * g[:-1]).sum().backward()
+    sd = dict(ref.named_parameters())
+    for name in ("model.visual.pos_embed.weight", "model.visual.deepstack_merger_list.1.linear_fc2.weight", "model.visual.blocks.0.attn.qkv.weight",
+                 "model.language_model.layers.2.self_attn.k_norm.weight", "model.visual.patch_embed.proj.bias"):
+        a, b = m.params.grads[name], sd[name].grad.reshape(m.params.grads[name].shape)
+        assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
