@@ -109,6 +109,7 @@ class FlatParams:
         self.views = {n: self.flat[o:o + k].view(self.layout[n]) for n, (o, k) in self.offsets.items()}
         self.grad_flat: torch.Tensor | None = None
         self.grads: dict[str, torch.Tensor] = {}
+        self.expert_offset = 0         # global index of the first expert held (a rank that holds a slice of the experts)
 
     def __getitem__(self, name: str) -> torch.Tensor:
         return self.views[name]
@@ -184,13 +185,13 @@ class FlatParams:
             elif name.endswith("experts.w13_weight"):
                 base = name[: -len("w13_weight")]
                 F = cfg.moe_intermediate_size
-                for e in range(cfg.num_experts):
-                    out[f"{base}{e}.gate_proj.weight"] = v[e, :F]
-                    out[f"{base}{e}.up_proj.weight"] = v[e, F:]
+                for e in range(v.shape[0]):
+                    out[f"{base}{e + self.expert_offset}.gate_proj.weight"] = v[e, :F]
+                    out[f"{base}{e + self.expert_offset}.up_proj.weight"] = v[e, F:]
             elif name.endswith("experts.w2_weight"):
                 base = name[: -len("w2_weight")]
-                for e in range(cfg.num_experts):
-                    out[f"{base}{e}.down_proj.weight"] = v[e]
+                for e in range(v.shape[0]):
+                    out[f"{base}{e + self.expert_offset}.down_proj.weight"] = v[e]
             else:
                 out[name] = v
         return out

@@ -99,7 +99,9 @@ def align(ids: torch.Tensor, num_experts: int) -> MoELayout:
     cap = max_rows_for(T, k, num_experts)
     dev = ids.device
     if not C.use_native(ids):
-        flat = ids.reshape(-1).to(torch.long)
+        flat_all = ids.reshape(-1).to(torch.long)
+        held = (flat_all >= 0) & (flat_all < num_experts)       # ids outside [0, E): experts of another rank, no row
+        flat = flat_all[held]
         counts = torch.bincount(flat, minlength=num_experts).to(torch.int32)
         padded = (counts + PAD - 1) // PAD * PAD
         offsets = torch.zeros(num_experts + 1, dtype=torch.int32)
@@ -108,9 +110,11 @@ def align(ids: torch.Tensor, num_experts: int) -> MoELayout:
         rank_in_expert = torch.empty_like(flat)
         starts = torch.cumsum(counts.to(torch.long), 0) - counts.to(torch.long)
         rank_in_expert[order] = torch.arange(flat.numel()) - starts[flat[order]]
-        row_of = (offsets[:-1].to(torch.long)[flat] + rank_in_expert).to(torch.int32)
+        row_of = torch.full((flat_all.numel(),), -1, dtype=torch.int32)
+        rows = (offsets[:-1].to(torch.long)[flat] + rank_in_expert)
+        row_of[held] = rows.to(torch.int32)
         token_of = torch.full((cap,), -1, dtype=torch.int32)
-        token_of[row_of.to(torch.long)] = (torch.arange(flat.numel()) // k).to(torch.int32)
+        token_of[rows] = (torch.arange(flat_all.numel())[held] // k).to(torch.int32)
         tile_expert = torch.full((cap // PAD,), -1, dtype=torch.int32)
         for e in range(num_experts):
             tile_expert[int(offsets[e]) // PAD:int(offsets[e + 1]) // PAD] = e
@@ -161,7 +165,9 @@ def combine(ys: torch.Tensor, w: torch.Tensor, lay: MoELayout) -> torch.Tensor:
     """out[t] = sum_j w[t, j] * ys[row_of[t, j]]  (weights applied after the second projection)."""
     T, k, H = lay.num_tokens, lay.top_k, ys.shape[1]
     if not C.use_native(ys):
-        return (ys[lay.row_of.to(torch.long)].view(T, k, H).float() * w.view(T, k, 1).float()).sum(1).to(ys.dtype)
+        rows = lay.row_of.to(torch.long)
+        picked = ys[rows.clamp(min=0)].view(T, k, H).float() * (rows >= 0).view(T, k, 1)
+        return (picked * w.view(T, k, 1).float()).sum(1).to(ys.dtype)
     out = torch.empty(T, H, dtype=ys.dtype, device=ys.device)
     rc = C.lib().axb_moe_combine(C.ptr(ys), C.ptr(lay.row_of), C.ptr(w.contiguous()), C.ptr(out), ctypes.c_longlong(T), k, H,
                                  C.stream())

@@ -715,6 +715,9 @@ class GenerationEngine:
         self.step_count += 1
         if self.paused and self.pause_strategy == "hold":
             return
+        begin = getattr(self.model, "begin_step", None)
+        if begin is not None:
+            begin()                      # a sharded model lines its group's streams up before the step's collectives
         if not (self.paused and self.pause_strategy in ("drain", "reset")):
             new = self._admit()
             if new:

@@ -72,7 +72,11 @@ class SamplerP2PMixin:
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def get_parameter_mapping(self):
         tp_rank = self.rank % self.tp
-        return get_param_metadata(self.model.cfg, rank=self.rank, tp=self.tp, tp_rank=tp_rank, dtype=self.model.params.dtype)
+        cfg = getattr(self.model, "full_cfg", self.model.cfg)       # a sharded model computes on its local configuration
+        ep = self.tp if getattr(cfg, "num_experts", 0) > 0 else 1   # experts are divided whole over the group
+        whole = ("model.embed_tokens.weight", "lm_head.weight") if self.tp > 1 else ()      # every rank of a group holds these in full
+        return get_param_metadata(cfg, rank=self.rank, tp=self.tp, tp_rank=tp_rank, ep=ep, ep_rank=tp_rank if ep > 1 else 0,
+                                  dtype=self.model.params.dtype, replicated_names=whole)
 
     def _shard_offsets(self, metas) -> dict:
         if self.tp == 1:
@@ -90,9 +94,8 @@ class SamplerP2PMixin:
             self._recv_plans = None
         assert getattr(self, "routing_table", None) is not None, "no routing table: the first push must carry it"
         t0 = time.monotonic()
-        if getattr(self, "engine", None) is not None and hasattr(self.engine, "reset_prefix_cache"):
-            with self.server._ctl_lock:
-                self.engine.reset_prefix_cache()     # cached keys / values belong to the weights being replaced
+        if getattr(self, "server", None) is not None:
+            self.server.reset_prefix_cache()         # cached keys / values belong to the weights being replaced
         if self._peer_path:
             # the trainers' kernels store into this rank's live buffer; generation must not read it meanwhile
             with self.server._ctl_lock, torch.cuda.device(self.device):

@@ -75,9 +75,23 @@ class SamplerWorker(Worker, DistProfilerExtension):
         peers = getattr(self, "_fused_peers", None) or {}
         trainer = next((p for r, p in peers.items() if r != self.name and getattr(p, "model", None) is not None
                         and hasattr(p, "engine") and not getattr(p, "_forward_only", False)), None)
+        lockstep = None
+        self.tp_group = None
+        if self.tp * self.pp > 1:
+            if self.pp > 1:
+                raise NotImplementedError("the sampler shards a model over tensor-parallel groups; pipeline stages are not built")
+            if trainer is not None:
+                raise NotImplementedError("a tensor-parallel sampler owns its weights (disaggregated deployment); "
+                                          "colocated samplers share the trainer's buffer and run one replica per GPU")
+            lockstep = self._make_tp_groups()
         if trainer is not None:
             self.model = trainer.model                  # zero-copy: generation reads the trainer's live parameters
             self.shares_trainer_weights = True
+        elif self.tp > 1:
+            from ..models.tp_infer import Shard, build_sharded_model
+            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            self.model = build_sharded_model(_get(cfg, "model_path"), Shard.create(self.tp_group, self.device), device=self.device,
+                                             dtype=dtype, seed=int(_get(cfg, "seed", 42)), load_weights=True)
         else:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
             self.model = build_model(_get(cfg, "model_path"), device=self.device, dtype=dtype, seed=int(_get(cfg, "seed", 42)),
@@ -94,9 +108,16 @@ class SamplerWorker(Worker, DistProfilerExtension):
             if self.shares_trainer_weights:
                 kv_bytes = self._kv_bytes_beside_optimizer(trainer, kv_bytes)
         num_pages = _get(scfg, "num_kv_pages", None)
+        if lockstep is not None and num_pages is None:
+            # the engines of a group must make the same scheduling decisions: they take the smallest pool any rank can hold
+            from .kv_cache import PagedKVCache
+            fit = (kv_bytes if kv_bytes is not None else 4 << 30) // PagedKVCache.bytes_per_page(self.model.cfg, self.model.params.flat.element_size())
+            agreed = torch.tensor([max(8, int(fit))], dtype=torch.int64)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=lockstep.group)
+            num_pages = int(agreed.item())
         self.engine = GenerationEngine(self.model, num_pages=num_pages, max_num_seqs=int(_get(scfg, "max_num_seqs", 256)),
                                        max_num_batched_tokens=int(_get(scfg, "max_num_batched_tokens", 32768)),
-                                       kv_memory_bytes=kv_bytes, seed=int(_get(cfg, "seed", 42)) + self.rank)
+                                       kv_memory_bytes=kv_bytes, seed=int(_get(cfg, "seed", 42)) + self.dp_rank)
         if _get(scfg, "enforce_eager", False):
             self.engine.use_cuda_graph = False
         self.engine.logprobs_mode = str(_get(scfg, "logprobs_mode", "processed"))
@@ -117,13 +138,29 @@ class SamplerWorker(Worker, DistProfilerExtension):
             self.engine.set_max_model_len(int(max_len))
         mode = SamplerMode.HYBRID if self.shares_trainer_weights else SamplerMode.STANDALONE
         server_cls = SERVER_REGISTRY.get(str(_get(scfg, "name", "native")), SamplerServer)
-        self.server = server_cls(self.engine, tokenizer=self.tokenizer, name=f"{self.name}-{self.rank}", mode=mode).start()
-        if _get(scfg, "serve_http", False):
-            self._start_http()
+        self.server = server_cls(self.engine, tokenizer=self.tokenizer, name=f"{self.name}-{self.rank}", mode=mode,
+                                 lockstep=lockstep).start()
+        if _get(scfg, "serve_http", False) and (lockstep is None or lockstep.leader):
+            self._start_http()                          # a group is reached through its first rank
         if self.shares_trainer_weights and _get(scfg, "offload_sampler", True):
             self.server.sleep()                          # training starts with the KV pool released
         return {"address": self.address, "shares_trainer_weights": self.shares_trainer_weights,
                 "kv_pages": self.engine._num_pages}
+
+    def _make_tp_groups(self):
+        """Process groups of this rank's tensor-parallel group: one for the activations (NCCL on GPUs) and a CPU one
+        for the lockstep control messages. Every rank creates every group, in the same order."""
+        from .server import Lockstep
+        assert dist.is_initialized(), "a tensor-parallel sampler needs the worker group's process group"
+        mine_data = mine_ctl = None
+        for g in range(self.world_size // self.tp):
+            ranks = list(range(g * self.tp, (g + 1) * self.tp))
+            data = dist.new_group(ranks)
+            ctl = dist.new_group(ranks, backend="gloo", timeout=datetime.timedelta(hours=6))
+            if g == self.dp_rank:
+                mine_data, mine_ctl = data, ctl
+        self.tp_group = mine_data
+        return Lockstep(mine_ctl)
 
     def _start_http(self) -> None:
         import socket
@@ -192,7 +229,7 @@ class SamplerWorker(Worker, DistProfilerExtension):
     def update_weights(self, named_tensors=None):
         """Hybrid deployment: nothing to move (shared buffer) — only cached state that depends on the
         old weights is dropped. Otherwise copy the given (name, tensor) pairs in."""
-        self.engine.reset_prefix_cache()              # cached keys / values were computed with the old weights
+        self.server.reset_prefix_cache()              # cached keys / values were computed with the old weights
         if self.shares_trainer_weights or named_tensors is None:
             return 0
         return self.server.update_weights(named_tensors)

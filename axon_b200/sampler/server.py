@@ -61,10 +61,43 @@ def decode_routed_experts(obj):
     return arr.reshape(obj["shape"]).copy()
 
 
+class Lockstep:
+    """Control channel of a tensor-parallel sampler group. The engines of the group must take the same requests and
+    the same control operations in the same order between the same steps (their collectives pair up step by step),
+    so only the group's first rank decides: before every tick that changes anything it sends
+    ``{"new": requests, "ops": control operations, "step": run one engine step}`` to the others, which apply it
+    and wait for the next message. Sampling needs no exchange: the summed activations are bit-identical on every
+    rank, and random draws depend only on (seed, request, position).
+
+    The messages travel over a CPU (gloo) group so that they never queue behind kernels; ``timeout`` is how long a
+    follower waits for the next message, so it bounds how long the group may sit idle only through the leader's
+    keep-alive messages."""
+
+    def __init__(self, group, keepalive: float = 20.0):
+        import torch.distributed as dist
+        self.group, self.keepalive = group, keepalive
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.src = dist.get_global_rank(group, 0)
+        self.leader = self.rank == 0
+
+    def send(self, msg: dict) -> None:
+        import torch.distributed as dist
+        dist.broadcast_object_list([msg], src=self.src, group=self.group)
+
+    def recv(self) -> dict:
+        import torch.distributed as dist
+        box = [None]
+        dist.broadcast_object_list(box, src=self.src, group=self.group)
+        return box[0]
+
+
 @register_server("native")
 class SamplerServer:
-    def __init__(self, engine, tokenizer=None, name: str = "sampler-0", mode: SamplerMode = SamplerMode.HYBRID):
+    def __init__(self, engine, tokenizer=None, name: str = "sampler-0", mode: SamplerMode = SamplerMode.HYBRID,
+                 lockstep: "Lockstep | None" = None):
         self.engine, self.tokenizer, self.name, self.mode = engine, tokenizer, name, mode
+        self.lockstep = lockstep if (lockstep is not None and lockstep.world > 1) else None
+        self._ops: "queue.Queue[tuple]" = queue.Queue()
         self._inbox: "queue.Queue[tuple]" = queue.Queue()
         self._futures: dict[int, Future] = {}
         self._thread: threading.Thread | None = None
@@ -88,7 +121,8 @@ class SamplerServer:
         self._stop.set()
         self._wake.set()
         if self._thread is not None:
-            self._thread.join(timeout=30)
+            follower = self.lockstep is not None and not self.lockstep.leader
+            self._thread.join(timeout=5 if follower else 30)      # a follower ends with the leader's last message
             self._thread = None
 
     def _loop(self) -> None:
@@ -97,9 +131,18 @@ class SamplerServer:
             if eng.device.type == "cuda":
                 import torch
                 torch.cuda.set_device(eng.device)
+            if self.lockstep is not None and not self.lockstep.leader:
+                return self._follow()
+            last_sent = time.monotonic()
             while not self._stop.is_set():
-                self._drain_inbox()
+                new = self._drain_inbox()
+                ops = self._drain_ops()
                 busy = eng.has_unfinished() and eng.cache is not None and not self._paused_hold
+                if self.lockstep is not None and (new or ops or busy or time.monotonic() - last_sent > self.lockstep.keepalive):
+                    self.lockstep.send({"new": new, "ops": [(n, a) for n, a, _ in ops], "step": busy})
+                    last_sent = time.monotonic()
+                for _, _, done in ops:
+                    done.set()
                 if busy:
                     self._idle.clear()
                     with self._ctl_lock:
@@ -110,6 +153,8 @@ class SamplerServer:
                     self._idle.set()
                     self._wake.wait(0.005)
                     self._wake.clear()
+            if self.lockstep is not None:
+                self.lockstep.send({"stop": True})
         except BaseException as e:  # noqa: BLE001
             self.error = e
             for f in self._futures.values():
@@ -117,19 +162,89 @@ class SamplerServer:
                     f.set_exception(e)
             self._futures.clear()
             self._idle.set()
+            while True:                          # nobody may wait forever for an operation this thread will not run
+                try:
+                    self._ops.get_nowait()[2].set()
+                except queue.Empty:
+                    break
 
-    def _drain_inbox(self) -> None:
+    def _follow(self) -> None:
+        """A tensor-parallel follower: apply the leader's messages in order."""
+        eng = self.engine
+        while True:
+            msg = self.lockstep.recv()
+            if msg.get("stop"):
+                return
+            for prompt, params, images in msg.get("new", ()):
+                eng.add_request(prompt, params, images) if images else eng.add_request(prompt, params)
+            for name, args in msg.get("ops", ()):
+                with self._ctl_lock:
+                    self._apply_op(name, args)
+            if msg.get("step"):
+                self._idle.clear()
+                with self._ctl_lock:
+                    eng.step()
+                eng.finished.clear()             # results are delivered by the leader
+            else:
+                self._idle.set()
+
+    def _drain_inbox(self) -> list:
+        """Move queued requests into the engine; returns what a lockstep leader forwards: (prompt, params, images)."""
+        taken = []
         while True:
             try:
                 prompt, params, fut, images = self._inbox.get_nowait()
             except queue.Empty:
-                return
+                return taken
             try:
                 rid = self.engine.add_request(prompt, params, images) if images else self.engine.add_request(prompt, params)
             except Exception as e:  # noqa: BLE001 - a bad request (e.g. images for a text model) fails alone
                 fut.set_exception(e)
                 continue
             self._futures[rid] = fut
+            taken.append((prompt, params, images))
+
+    # Control operations that change engine state. Alone, a server runs them in the caller's thread; in a lockstep
+    # group the leader's loop runs them between two steps and forwards them, so every rank applies them at the same point.
+    def _apply_op(self, name: str, args: tuple) -> None:
+        eng = self.engine
+        if name == "reset":
+            eng.pause("reset")
+            eng.resume()
+        elif name == "sleep":
+            eng.sleep()
+        elif name == "wake":
+            eng.wake_up(*args)
+        elif name == "reset_prefix_cache":
+            eng.reset_prefix_cache()
+        else:
+            raise ValueError(f"unknown control operation '{name}'")
+
+    def _drain_ops(self) -> list:
+        ops = []
+        while True:
+            try:
+                op = self._ops.get_nowait()
+            except queue.Empty:
+                return ops
+            with self._ctl_lock:
+                self._apply_op(op[0], op[1])
+            ops.append(op)
+
+    def _run_op(self, name: str, *args, timeout: float = 120.0) -> None:
+        if self.lockstep is None:
+            with self._ctl_lock:
+                self._apply_op(name, args)
+            return
+        if not self.lockstep.leader:
+            return                               # arrives through the leader's message
+        done = threading.Event()
+        self._ops.put((name, args, done))
+        self._wake.set()
+        if not done.wait(timeout):
+            raise TimeoutError(f"sampler server '{self.name}': control operation '{name}' was not picked up")
+        if self.error is not None:
+            raise RuntimeError(f"sampler server '{self.name}' has failed") from self.error
 
     def _resolve(self) -> None:
         fin = self.engine.finished
@@ -178,7 +293,7 @@ class SamplerServer:
         """drain: wait for in-flight requests to finish (new ones queue). hold: freeze in place.
         continue: do nothing (in-flight requests keep running across the weight update).
         reset: abort in-flight requests; they resolve with finish_reason 'abort' and their partial text."""
-        if strategy == "continue":
+        if strategy == "continue" or self._follower:
             return
         if strategy == "hold":
             self._paused_hold = True
@@ -190,9 +305,7 @@ class SamplerServer:
                 time.sleep(0.005)
             return
         if strategy == "reset":
-            with self._ctl_lock:
-                self.engine.pause("reset")
-                self.engine.resume()
+            self._run_op("reset")
             self._wake.set()
             return
         raise ValueError(f"unknown pause strategy '{strategy}'")
@@ -205,26 +318,40 @@ class SamplerServer:
         self._wake.set()
         self._idle.wait(timeout)
 
+    @property
+    def _follower(self) -> bool:
+        """A follower of a lockstep group: its engine is driven by the leader's messages, so the control calls
+        that reach it directly (the controller addresses every rank) have nothing to do."""
+        return self.lockstep is not None and not self.lockstep.leader
+
     def sleep(self) -> None:
+        if self._follower:
+            return
         self._paused_hold = True
         self._wait_idle(60.0)
-        with self._ctl_lock:
-            self.engine.sleep()
+        self._run_op("sleep")
 
     def wake_up(self, num_pages: int | None = None) -> None:
-        with self._ctl_lock:
-            self.engine.wake_up(num_pages)
+        self._run_op("wake", num_pages)
         self._paused_hold = False
         self._wake.set()
+
+    def reset_prefix_cache(self) -> None:
+        self._run_op("reset_prefix_cache")
 
     def update_weights(self, named_tensors) -> int:
         """Copy (name, tensor) pairs into the engine's parameter views while generation is held."""
         n = 0
+        self.reset_prefix_cache()
         with self._ctl_lock:
-            self.engine.reset_prefix_cache()
             views = self.engine.model.params.views
             hf_views = None
+            localize = getattr(self.engine.model, "localize", None)      # a sharded model keeps its part of every tensor
             for name, t in named_tensors:
+                if localize is not None:
+                    t = localize(name, t)
+                    if t is None:
+                        continue
                 dst = views.get(name)
                 if dst is None:
                     if hf_views is None:

@@ -7,6 +7,8 @@
 //   zero1_adamw_bcast   sharded AdamW on the reduced shard (clip coefficient / skip flag read on the
 //                       device) + all-gather fused as peer STORES of the new bf16 values into every
 //                       rank's parameter buffer
+//   peer_allreduce      one-launch all-reduce of a small bf16 vector (push to every rank's staging slot,
+//                       per-block flags, fixed-order sum); epoch kept on the device, graph-replayable
 //   p2p_copy_plan       trainer -> sampler weight sync: executes a compiled RoutingTable plan (strided
 //                       2-D slice copies between arbitrary ranks) in ONE launch; optional fused
 //                       bf16 -> fp8(e4m3) 128x128 block-scaled quantisation on the way
@@ -320,6 +322,82 @@ fp8_block_quant_kernel(const __nv_bfloat16* __restrict__ x, unsigned char* __res
                  &s_scale, scales + (long long)blockIdx.y * bc + blockIdx.x);
 }
 
+// One-launch all-reduce of a small bf16 vector (a decode step's activations under tensor parallelism).
+// Every rank owns, in symmetric memory, staging [2 turns][world slots][cap] bf16 and flags
+// [2][world][max_blocks] u32. Block b of rank r handles elements [b * chunk, (b + 1) * chunk):
+//   1. stores its chunk of x into slot r of EVERY rank's staging (peer stores over NVLink),
+//   2. fences, then sets flag (turn, r, b) on every rank to the call's epoch,
+//   3. waits (bounded) until its own flags (turn, 0..world-1, b) reached the epoch,
+//   4. sums the world slots of its own staging in rank order (every rank gets the same bits) into out.
+// The epoch lives in device memory (state[0], bumped by the block that finishes last), so the launch has
+// no per-call arguments and can be replayed from a CUDA graph. turn = epoch & 1: a rank that runs one
+// call ahead writes the other half, and it cannot run two ahead because step 3 of the call in between
+// needs this rank's flags. out may alias x. No block waits for another block of the same launch.
+__global__ void __launch_bounds__(256)
+peer_allreduce_kernel(PeerPtrs bufs, int rank, int world, const __nv_bfloat16* x, __nv_bfloat16* out, long long n,
+                      long long chunk, long long cap, long long flag_off_bytes, int max_blocks, unsigned int* state,
+                      int* status) {
+  __shared__ unsigned int s_epoch;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(state) + 1u;
+  __syncthreads();
+  const unsigned int e = s_epoch;
+  const int turn = static_cast<int>(e & 1u);
+  const long long lo = blockIdx.x * chunk, hi = min(n, lo + chunk);
+  for (int d = 1; d <= world; ++d) {
+    const int p = (rank + d) % world;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(bufs.p[p]) + (static_cast<long long>(turn) * world + rank) * cap;
+    for (long long i = lo + tid * 8; i < hi; i += 256 * 8)
+      *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(x + i);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < world) {
+    unsigned int* theirs = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(bufs.p[tid]) + flag_off_bytes) +
+                           (static_cast<long long>(turn) * world + rank) * max_blocks + blockIdx.x;
+    st_release_sys(theirs, e);
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(reinterpret_cast<const char*>(bufs.p[rank]) + flag_off_bytes) +
+                               (static_cast<long long>(turn) * world + tid) * max_blocks + blockIdx.x;
+    const long long t0 = clock64();
+    while (static_cast<int>(ld_acquire_sys(mine) - e) < 0) {
+      if (clock64() - t0 > AXB_PEER_WAIT_CYCLES) {
+        report_error(status, AXB_ERR_WAIT_PEER);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(bufs.p[rank]) + static_cast<long long>(turn) * world * cap;
+  for (long long i = lo + tid * 8; i < hi; i += 256 * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world; ++r) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(base + r * cap + i));      // L2 is where the peers' stores land
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    uint4 o;
+    uint32_t* u = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) u[q] = pack_bf16x2(acc[2 * q], acc[2 * q + 1]);
+    *reinterpret_cast<uint4*>(out + i) = o;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(state + 1, 1u) == gridDim.x - 1) {       // last block out: publish the epoch for the next launch
+      state[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(state) = e;
+    }
+  }
+}
+
 }  // namespace axb
 
 using namespace axb;
@@ -335,6 +413,27 @@ extern "C" int axb_peer_barrier(const unsigned long long* pad_ptrs, int rank, in
   PeerPtrs pads;
   if (int rc = fill_ptrs(pads, pad_ptrs, world)) return rc;
   peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pads, rank, world, epoch, status);
+  return check_launch();
+}
+
+// bufs: base of every rank's symmetric allocation ([2][world][cap] bf16 staging, flags at flag_off_bytes:
+// [2][world][max_blocks] u32, zero before the first call). state: 2 zero-initialised u32 of this rank.
+// n (a multiple of 8, <= cap) bf16 elements of x are summed over the ranks into out (may alias x).
+extern "C" int axb_peer_allreduce(const unsigned long long* buf_ptrs, int rank, int world, const void* x, void* out,
+                                  long long n, long long cap, long long flag_off_bytes, int max_blocks,
+                                  unsigned int* state, int* status, void* stream) {
+  PeerPtrs b;
+  if (int rc = fill_ptrs(b, buf_ptrs, world)) return rc;
+  if (n <= 0 || (n & 7) || n > cap || (cap & 7) || max_blocks < 1 || rank < 0 || rank >= world || (flag_off_bytes & 3) ||
+      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return AXB_LAUNCH_BAD_ARG;
+  long long blocks = (n + 2047) / 2048;
+  if (blocks > max_blocks) blocks = max_blocks;
+  const long long chunk = ((n + blocks - 1) / blocks + 7) & ~7ll;
+  blocks = (n + chunk - 1) / chunk;
+  peer_allreduce_kernel<<<static_cast<int>(blocks), 256, 0, (cudaStream_t)stream>>>(
+      b, rank, world, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n, chunk, cap, flag_off_bytes,
+      max_blocks, state, status);
   return check_launch();
 }
 

@@ -212,6 +212,7 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const i
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < k; ++j) {
       const int r = row_of[t * k + j];
+      if (r < 0) continue;                      // assignment to an expert this rank does not hold
       const float wj = w[t * k + j];
       float v[8];
       unpack8f(reinterpret_cast<const uint4*>(ys + static_cast<long long>(r) * H)[i], v);
@@ -285,7 +286,8 @@ extern "C" int axb_moe_route(const float* logits, const int* replay, int* ids, f
 }
 
 // ids int32 [T*k]. Outputs: counts [E], offsets [E+1], tile_expert [max_tiles], row_of [T*k], token_of
-// [max_tiles*128] (filled with -1 for padding). max_tiles >= (T*k + E*127) / 128.
+// [max_tiles*128] (filled with -1 for padding). max_tiles >= (T*k + E*127) / 128. Ids outside [0, E) (experts held by
+// another rank) get no row: row_of stays -1 and the combine skips them.
 extern "C" int axb_moe_align(const int* ids, long long T, int k, int E, int* counts, int* offsets, int* tile_expert,
                              int max_tiles, int* row_of, int* token_of, void* stream) {
   if (T <= 0 || E <= 0 || E > MOE_MAX_EXPERTS || k <= 0) return AXB_LAUNCH_BAD_ARG;
@@ -294,6 +296,7 @@ extern "C" int axb_moe_align(const int* ids, long long T, int k, int E, int* cou
   cudaStream_t s = (cudaStream_t)stream;
   if (cudaMemsetAsync(token_of, 0xff, sizeof(int) * static_cast<size_t>(max_tiles) * MOE_PAD, s) != cudaSuccess)
     return AXB_LAUNCH_CUDA_ERROR;
+  if (cudaMemsetAsync(row_of, 0xff, sizeof(int) * static_cast<size_t>(T) * k, s) != cudaSuccess) return AXB_LAUNCH_CUDA_ERROR;
   moe_count_kernel<<<E, 256, 0, s>>>(ids, T * k, counts);
   moe_offsets_kernel<<<1, 32, 0, s>>>(counts, E, offsets, tile_expert, max_tiles);
   moe_positions_kernel<<<E, 256, 0, s>>>(ids, T * k, k, offsets, row_of, token_of);

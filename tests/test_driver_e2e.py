@@ -89,3 +89,25 @@ def test_disaggregated_modes_push_weights(tmp_path, mode):
     assert "timing_s/sync_weights" in logs[0]["data"] and "actor/loss" in logs[1]["data"]
     if mode == "async":
         assert "async/staleness_steps" in logs[0]["data"]
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("model", ["dense", "moe"])
+def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
+    """1 trainer + a sampler group of 2 ranks that shard the model: the weight push re-slices every tensor for the
+    group's ranks, the group generates in lockstep behind its first rank, and what it samples has the log-probs the
+    trainer computes for the same tokens."""
+    extra = ["num_gpus_per_node=3", "sampler_trainer_gpu_ratio=2", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
+             "sampler.tensor_model_parallel_size=2"]
+    if model == "moe":          # the group also divides the experts; the routed experts it records are replayed by the trainer
+        extra += ["model_path=tiny-moe", "strategy=megatron", "moe_replay=true"]
+    drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
+    try:
+        assert drv.global_steps == 3
+        assert len(drv.server_addresses) == 1           # the group is reached through its first rank
+    finally:
+        drv.shutdown()
+    logs = _logged_steps(tmp_path)
+    assert [r["step"] for r in logs] == [1, 2]
+    for r in logs:
+        assert abs(r["data"]["batch/sampler_logprobs_diff_max"]) < 0.02 and abs(r["data"]["batch/sampler_logprobs_diff_min"]) < 0.02, r["data"]

@@ -1,0 +1,55 @@
+"""Tensor-parallel sampler group: a model sharded over the group (heads, MLP columns, whole experts) generates what
+the unsharded model generates; the group's servers run in lockstep behind their first rank (requests, sleep / wake,
+weight updates with full tensors, reset). CPU: 2 gloo ranks. GPU: 2 ranks, sums through the peer-memory kernel."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(tmp_path, n, kind, port):
+    out = tmp_path / "tps.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_sampler_worker.py"), str(out), kind]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return json.loads(out.read_text())
+
+
+def _check(res, presets, tol, exact):
+    for x in res:
+        for p in presets:
+            y = x[p]
+            assert y["same_tokens_on_all_ranks"] and y["logprob_err"] < tol, (p, y)
+            if exact:
+                assert y["equals_unsharded"], (p, y)
+            if x["rank"] == 0:
+                assert y["server_first_len"] == [16] * 6 and y["updated"] > 0 and y["after_update_err"] < tol, (p, y)
+                assert y["aborted_reason"] in ("abort", "length") and y["third_equals_second"], (p, y)
+                assert y["server_first_err"] < tol, (p, y)
+            else:
+                assert y["follower_done"] and y["follower_error"] is None, (p, y)
+        assert x["tiny-moe" if exact else "tiny-moe-gpu"]["routed"]
+
+
+@pytest.mark.timeout(900)
+def test_tp2_sampler_group_matches_unsharded_model_cpu(tmp_path):
+    res = _run(tmp_path, 2, "cpu", 29671)
+    _check(res, ("tiny-qwen3", "tiny-moe"), 1e-4, exact=True)
+    assert not res[0]["fused"]
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_tp2_sampler_group_sums_through_peer_memory_gpu(tmp_path):
+    res = _run(tmp_path, 2, "cuda", 29672)
+    _check(res, ("tiny-gpu", "tiny-moe-gpu"), 0.15, exact=False)
+    for x in res:
+        assert x["fused"] and x["reduce_calls"]["fused"] > 0 and x["status"] == 0, x
+        assert x["tiny-gpu"]["graphs"] > 0, x          # the decode graph replays the peer-memory sums
