@@ -12,9 +12,14 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def _trainer_logprobs(model, prompt, out_ids, temperature):
+def _trainer_logprobs(model, prompt, out, temperature):
+    """The unsharded model's log-probs of the sampled tokens; a sparse model replays the experts the sampler recorded
+    (a near-tie in the router may otherwise resolve differently in bf16)."""
     from axon_b200.models.dense import PackedBatch
+    out_ids = out.token_ids
     batch = PackedBatch.from_sequences([torch.tensor(prompt + out_ids)], model.device)
+    if out.moe_routermap is not None:
+        batch.routermap = torch.from_numpy(out.moe_routermap.astype("int64")).to(model.device)
     lp, _ = model.forward(batch, temperature)
     return lp[len(prompt) - 1: len(prompt) - 1 + len(out_ids)].float().cpu()
 
@@ -57,7 +62,7 @@ def main(out_path: str, device_kind: str) -> None:
         outs = eng.generate(prompts, sp)
         worst = 0.0
         for p, o in zip(prompts, outs):
-            ref = _trainer_logprobs(full, p, o.token_ids, 0.8)
+            ref = _trainer_logprobs(full, p, o, 0.8)
             worst = max(worst, (torch.tensor(o.logprobs) - ref).abs().max().item())
         toks = [o.token_ids for o in outs]
         everyone = [None] * world
@@ -70,6 +75,8 @@ def main(out_path: str, device_kind: str) -> None:
             res[key]["equals_unsharded"] = [o.token_ids for o in ref_eng.generate(prompts, sp)] == toks
         # ---------------- servers: requests and control on the first rank only
         eng2 = GenerationEngine(part, num_pages=24, max_num_seqs=8, seed=7)
+        if cfg.num_experts:
+            eng2.enable_routing_capture(True)
         srv = SamplerServer(eng2, name=f"s{rank}", lockstep=Lockstep(ctl)).start()
         greedy = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
         if rank == 0:
@@ -93,12 +100,12 @@ def main(out_path: str, device_kind: str) -> None:
             third = srv.submit(prompts[0], greedy).result(timeout=300)
             worst2 = 0.0
             for p, o in zip(prompts[:3], second):
-                worst2 = max(worst2, (torch.tensor(o.logprobs) - _trainer_logprobs(other, p, o.token_ids, 1.0)).abs().max().item())
+                worst2 = max(worst2, (torch.tensor(o.logprobs) - _trainer_logprobs(other, p, o, 1.0)).abs().max().item())
             res[key].update(server_first_len=[len(o.token_ids) for o in first], updated=n_up, after_update_err=worst2,
                             aborted_reason=aborted.finish_reason, aborted_len=len(aborted.token_ids),
                             third_equals_second=third.token_ids == second[0].token_ids)
             # requests reach the server one by one, so batches differ from a one-shot run: compare against the trainer pass
-            res[key]["server_first_err"] = max((torch.tensor(o.logprobs) - _trainer_logprobs(full, p, o.token_ids, 1.0)).abs().max().item()
+            res[key]["server_first_err"] = max((torch.tensor(o.logprobs) - _trainer_logprobs(full, p, o, 1.0)).abs().max().item()
                                                for p, o in zip(prompts, first))
             srv.stop()
         else:
@@ -110,7 +117,7 @@ def main(out_path: str, device_kind: str) -> None:
     if device_kind == "cuda":
         from axon_b200.ops import _common as C
         torch.cuda.synchronize()
-        res["status"] = int(C.status(dev).item()) if hasattr(C.status(dev), "item") else 0
+        res["status"] = int(C.status(dev).flatten()[0].item())
     allres = [None] * world
     dist.all_gather_object(allres, res, group=side)
     if rank == 0:
