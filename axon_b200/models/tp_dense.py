@@ -44,9 +44,14 @@ def _replicated(name: str, shard_head: bool) -> bool:
     return split_kind(name) in REPLICATED_KINDS
 
 
-def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = False) -> "OrderedDict[str, tuple[int, ...]]":
+def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = False, ep: int = 1) -> "OrderedDict[str, tuple[int, ...]]":
+    """Parameter shapes of one rank, in the full model's parameter order. ``ep``: the stacked expert tensors keep
+    ``num_experts / ep`` whole experts (which ones does not change the shape)."""
     out: OrderedDict[str, tuple[int, ...]] = OrderedDict()
     for name, full in param_layout(cfg).items():
+        if split_kind(name) == "expert":
+            out[name] = (full[0] // ep, *full[1:])
+            continue
         if _replicated(name, shard_head) or tp == 1:
             out[name] = tuple(full)
             continue
@@ -56,7 +61,11 @@ def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = 
     return out
 
 
-def slice_full_param(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, tp_rank: int, shard_head: bool = False) -> torch.Tensor:
+def slice_full_param(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, tp_rank: int, shard_head: bool = False,
+                     ep: int = 1, ep_rank: int = 0) -> torch.Tensor:
+    if split_kind(name) == "expert":
+        n = full.shape[0] // ep
+        return full[ep_rank * n:(ep_rank + 1) * n]
     if _replicated(name, shard_head) or tp == 1:
         return full
     if full.dim() == 1:
@@ -72,25 +81,31 @@ def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, in
         return batch, T
     dev = batch.input_ids.device
     z = lambda n, v, dt: torch.full((n,), v, dtype=dt, device=dev)      # noqa: E731
+    rm = getattr(batch, "routermap", None)
+    if rm is not None:                       # padding rows replay nothing
+        rm = torch.cat([rm, torch.full((pad, *rm.shape[1:]), -1, dtype=rm.dtype, device=rm.device)])
     return PackedBatch(torch.cat([batch.input_ids, z(pad, 0, batch.input_ids.dtype)]),
                        torch.cat([batch.position_ids, torch.arange(pad, dtype=batch.position_ids.dtype, device=dev)]),
                        torch.cat([batch.cu_seqlens, torch.tensor([T + pad], dtype=batch.cu_seqlens.dtype, device=dev)]),
                        torch.cat([batch.labels, z(pad, -100, batch.labels.dtype)]),
-                       max(batch.max_seqlen, pad)), T
+                       max(batch.max_seqlen, pad), routermap=rm), T
 
 
 class TPDenseModel:
+    SPARSE = False           # the sparse subclass (tp_moe.TPMoEModel) replaces the MLP hooks
+    ep_world = 1
+
     def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False,
                  holds=None):
         """``holds``: optional predicate over parameter names; only those parameters are allocated (pipeline stages)."""
-        assert cfg.num_experts == 0
-        assert cfg.num_key_value_heads % tp.world == 0 and cfg.intermediate_size % tp.world == 0
+        assert (cfg.num_experts > 0) == self.SPARSE, "dense configurations use TPDenseModel, sparse ones TPMoEModel"
+        assert cfg.num_key_value_heads % tp.world == 0 and (self.SPARSE or cfg.intermediate_size % tp.world == 0)
         assert not cfg.sandwich_norm, "sandwich-norm families (GLM-4) run under data / sequence / context / pipeline parallelism; the tensor-parallel layer code does not carry the extra norms yet"
         assert cfg.num_nextn_predict_layers == 0, "the multi-token-prediction module is trained by the data-parallel trainer only"
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
         self.shard_head = bool(vocab_parallel_head) and not cfg.tie_word_embeddings and tp.world > 1
-        layout = tp_param_layout(cfg, tp.world, tp.rank, self.shard_head)
+        layout = tp_param_layout(cfg, tp.world, tp.rank, self.shard_head, ep=self.ep_world)
         if holds is not None:
             layout = OrderedDict((n, sh) for n, sh in layout.items() if holds(n))
         self.params = FlatParams(cfg, self.device, dtype, layout=layout)
@@ -104,8 +119,8 @@ class TPDenseModel:
     # ------------------------------------------------------------------ parameters
     def load_full_state(self, full_views: dict) -> None:
         for name, dst in self.params.views.items():
-            dst.copy_(slice_full_param(self.cfg, name, full_views[name].to(dst.device), self.tp.world, self.tp.rank,
-                                       self.shard_head).to(dst.dtype))
+            dst.copy_(slice_full_param(self.cfg, name, full_views[name], self.tp.world, self.tp.rank, self.shard_head,
+                                       ep=self.ep_world, ep_rank=self.tp.rank if self.ep_world > 1 else 0).to(dst.device).to(dst.dtype))
 
     def init_random(self, std: float = 0.02, seed: int = 0) -> None:
         """Same values as ``FlatParams.init_random`` of the unsharded model with this seed."""
@@ -170,10 +185,28 @@ class TPDenseModel:
         _, o, _ = self._attn(l, qkv, batch, tables, need_lse=False)
         ao = tp.gemm_reduce_scatter(o, self._p(l, "self_attn.o_proj.weight"))
         h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
+        return x1, self._mlp_fwd(l, h2, batch), xin
+
+    def _mlp_fwd(self, l, h2, batch):
+        """MLP on this rank's rows h2 [T/W, H] -> [T/W, H]: column-parallel gate / up over all rows, row-parallel down."""
+        tp = self.tp
         gu = tp.allgather_gemm(h2, self._p(l, "mlp.gate_up_proj.weight"))
+        return tp.gemm_reduce_scatter(A.swiglu_fwd(gu), self._p(l, "mlp.down_proj.weight"))
+
+    def _mlp_bwd(self, l, h2, dx_out, batch):
+        """Gradient w.r.t. h2 (local rows) from the gradient of the MLP output (local rows); recomputes the MLP's
+        activations and accumulates its weight gradients."""
+        tp = self.tp
+        h2_full = tp.all_gather_rows(h2)
+        gu = G.gemm_nt(h2_full, self._p(l, "mlp.gate_up_proj.weight"))
         a = A.swiglu_fwd(gu)
-        mo = tp.gemm_reduce_scatter(a, self._p(l, "mlp.down_proj.weight"))
-        return x1, mo, xin
+        dy_full = tp.all_gather_rows(dx_out)                                   # grad of the row-parallel output, all rows
+        da = G.gemm_nn(dy_full, self._p(l, "mlp.down_proj.weight"))
+        G.gemm_tn(dy_full, a, out=self._g(l, "mlp.down_proj.weight"), accumulate=True)
+        dgu = A.swiglu_bwd(da, gu)
+        del da, a, gu
+        G.gemm_tn(dgu, h2_full, out=self._g(l, "mlp.gate_up_proj.weight"), accumulate=True)
+        return tp.gemm_reduce_scatter(dgu, self._p(l, "mlp.gate_up_proj.weight"), w_is_kn=True)
 
     def layer_bwd(self, l, xin, dx_out, batch, tables):
         c, tp = self.cfg, self.tp
@@ -188,18 +221,8 @@ class TPDenseModel:
         qkv_r, o, lse = self._attn(l, qkv, batch, tables, need_lse=True)
         ao = tp.gemm_reduce_scatter(o, self._p(l, "self_attn.o_proj.weight"))
         h2, rstd2, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
-        h2_full = tp.all_gather_rows(h2)
-        gu = G.gemm_nt(h2_full, self._p(l, "mlp.gate_up_proj.weight"))
-        a = A.swiglu_fwd(gu)
         # ---- MLP backward
-        dy_full = tp.all_gather_rows(dx_out)                                   # grad of the row-parallel output, all rows
-        da = G.gemm_nn(dy_full, self._p(l, "mlp.down_proj.weight"))
-        G.gemm_tn(dy_full, a, out=self._g(l, "mlp.down_proj.weight"), accumulate=True)
-        dgu = A.swiglu_bwd(da, gu)
-        del da, a, gu
-        G.gemm_tn(dgu, h2_full, out=self._g(l, "mlp.gate_up_proj.weight"), accumulate=True)
-        dh2 = tp.gemm_reduce_scatter(dgu, self._p(l, "mlp.gate_up_proj.weight"), w_is_kn=True)
-        del dgu, h2_full, dy_full
+        dh2 = self._mlp_bwd(l, h2, dx_out, batch)
         dx1 = N.rmsnorm_bwd(dh2, x1, self._p(l, "post_attention_layernorm.weight"), rstd2,
                             self._g(l, "post_attention_layernorm.weight"), dres=dx_out)
         # ---- attention backward
@@ -309,4 +332,5 @@ class TPModelAdapter:
 
     def flops_per_token(self, seqlen: int) -> float:
         from .dense import DenseModel
-        return DenseModel.flops_per_token(self, seqlen) / self.tp.world
+        from .moe import MoEModel
+        return (MoEModel if self.cfg.num_experts > 0 else DenseModel).flops_per_token(self, seqlen) / self.tp.world

@@ -78,16 +78,7 @@ def local_config(cfg: ModelConfig, world: int) -> ModelConfig:
 
 def local_layout(cfg: ModelConfig, world: int, rank: int):
     """Parameter shapes of one rank, in the full model's parameter order (the order weight-sync plans assume)."""
-    lay = tp_param_layout(cfg, world, rank)
-    full = None
-    for name in lay:
-        if name.endswith("w13_weight") or name.endswith("w2_weight"):
-            if full is None:
-                from .params import param_layout
-                full = param_layout(cfg)
-            shp = full[name]
-            lay[name] = (shp[0] // world, *shp[1:])
-    return lay
+    return tp_param_layout(cfg, world, rank, ep=world if cfg.num_experts > 0 else 1)
 
 
 class _ShardedInference:

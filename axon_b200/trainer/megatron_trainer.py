@@ -34,9 +34,9 @@ class TrainerWorker(_Base):
         m = _get(config, "megatron", {}) or {}
         self.tp_size = int(_get(m, "tensor_model_parallel_size", 1) or 1)
         self.ep_size = int(_get(m, "expert_model_parallel_size", 1) or 1)
-        if self.ep_size > 1 and self.tp_size > 1:
-            raise NotImplementedError("tensor and expert parallelism together are not available in this trainer yet; "
-                                      "use one of megatron.tensor_model_parallel_size / expert_model_parallel_size")
+        if self.ep_size > 1 and self.tp_size > 1 and self.ep_size != self.tp_size:
+            raise NotImplementedError("tensor and expert parallelism together divide the experts over the tensor-parallel group's own "
+                                      f"ranks: set expert_model_parallel_size == tensor_model_parallel_size (got ep={self.ep_size}, tp={self.tp_size})")
         self.pp_size = int(_get(m, "pipeline_model_parallel_size", 1) or 1)
         if self.pp_size > 1 and self.ep_size > 1:
             raise NotImplementedError("pipeline parallelism together with expert parallelism is not available in this trainer "
@@ -191,6 +191,38 @@ class TrainerWorker(_Base):
         model.recompute = str(_get(self.config, "recompute", "selective"))
         return model
 
+    def _build_tensor_expert_parallel(self, model_path, dtype, seed):
+        """tp == ep: consecutive ranks form one group that divides the attention heads (sequence-parallel activations)
+        AND the experts; the ranks of a group see the same rows, groups are data-parallel replicas."""
+        import os
+        from ..models.config import get_config
+        from ..models.params import FlatParams
+        from ..models.tp_dense import TPModelAdapter
+        from ..models.tp_moe import TPMoEModel
+        from ..parallel.ep import EPContext
+        from ..parallel.tp import TPContext
+        from ..utils.hf_model import has_hf_weights, iter_hf_weights
+        if self.model_kind.value_head:
+            raise NotImplementedError("value-head models are not tensor-parallel yet; run the critic with tp=1")
+        mcfg = get_config(model_path)
+        assert mcfg.num_experts > 0, f"expert_model_parallel_size={self.ep_size} needs a mixture-of-experts model"
+        tp_group, dp_group = self._make_groups()
+        self.pg = dp_group
+        self._mp_group = tp_group
+        rows = int(_get(self.config, "max_token_len_per_gpu", 16384))
+        rows = (rows // self.tp_size + 127) // 128 * 128 + 128
+        tp = TPContext(tp_group, self.device, max_rows_per_rank=rows, max_width=max(mcfg.qkv_size, mcfg.hidden_size))
+        ep = EPContext(tp_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, max_tokens=rows,
+                       top_k=mcfg.num_experts_per_tok)
+        inner = TPMoEModel(mcfg, tp, ep, device=self.device, dtype=dtype)
+        ref = FlatParams(mcfg, "cpu", dtype)                 # full model on the host, cut down to this rank's part
+        if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+        else:
+            ref.init_random(seed=seed)
+        inner.load_full_state(ref.views)
+        return TPModelAdapter(inner)
+
     def _build_context_parallel(self, model_path, dtype, seed):
         """Consecutive ranks form a context-parallel group (same rows, two zigzag chunks of every sequence
         each); the optimizer keeps sharding over ALL ranks, so its reduce-scatter also completes the
@@ -227,6 +259,8 @@ class TrainerWorker(_Base):
             return self._build_tensor_pipeline_parallel(model_path, dtype, seed)
         if self.pp_size > 1:
             return self._build_pipeline_parallel(model_path, dtype, seed)
+        if self.ep_size > 1 and self.tp_size > 1:
+            return self._build_tensor_expert_parallel(model_path, dtype, seed)
         if self.ep_size > 1:
             return self._build_expert_parallel(model_path, dtype, seed)
         if self.tp_size == 1:

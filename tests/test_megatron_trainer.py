@@ -83,7 +83,22 @@ def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_and_expert_parallel_over_one_group_matches_data_parallel_trainer(world):
+    """tp = ep = 2 (x dp = 1 or 2): the group divides the attention heads AND the experts; the ranks of a group see the
+    same rows, each routes its own share of the tokens to the experts' owners."""
+    import numpy as np
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-moe"), 1, vocab=2048)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, "tiny-moe", 2), world, vocab=2048)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp", "tp-ep"])
 def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
     run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
@@ -93,8 +108,8 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     from axon_b200.models.dense import PackedBatch
     from axon_b200.models.moe import build_model_for
     from axon_b200.utils.hf_model import load_hf_weights
-    preset, vocab = ("tiny-moe", 2048) if kind == "ep" else (("tiny-qwen2" if kind == "tp-bias" else "tiny-qwen3-untied"), 4096)
-    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind == "ep" else 1, 2 if kind.endswith("pp") else 1)
+    preset, vocab = ("tiny-moe", 2048) if kind.endswith("ep") else (("tiny-qwen2" if kind == "tp-bias" else "tiny-qwen3-untied"), 4096)
+    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind.endswith("ep") else 1, 2 if kind.endswith("pp") else 1)
     world = 4 if kind == "tp-pp" else 2
     d = str(tmp_path / "ck")
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, world, vocab=vocab, save_dir=d)
@@ -122,6 +137,9 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     torch.testing.assert_close(again[0], got[3], rtol=1e-5, atol=1e-5)
     if kind == "tp-pp":          # written by tp 2 x pp 2, resumed by two pipeline stages without tensor parallelism
         other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, pp=2), 2, vocab=vocab, load_dir=d)
+        torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
+    if kind == "tp-ep":         # written by one tp = ep = 2 group, resumed by two expert-parallel ranks without tensor parallelism
+        other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, 2), 2, vocab=vocab, load_dir=d)
         torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
     if kind == "tp":
         single = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset), 1, vocab=vocab, load_dir=d)
