@@ -29,8 +29,8 @@ from .config import ModelConfig
 from .params import FlatParams
 
 FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text",
-                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl", "qwen3_vl")
-VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl")
+                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "glm4v")
+VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "glm4v")
 
 
 # ------------------------------------------------------------------------------------------ small pieces
@@ -1465,7 +1465,8 @@ class _Qwen2VL(_Spec):
 
     # ---- decoder
     def rope(self, which):
-        return rope_frequencies({"rope_theta": self.rope_params["rope_theta"]}, self.D, self.hf.get("max_position_embeddings", 32768))
+        return rope_frequencies({"rope_theta": self.rope_params["rope_theta"]}, getattr(self, "rot_dim", self.D),
+                                self.hf.get("max_position_embeddings", 32768))
 
     def rotary(self, ctx):
         pos = ctx["positions"]
@@ -1474,7 +1475,7 @@ class _Qwen2VL(_Spec):
         key = ("mrope", id(pos))
         if ctx.get("_mrope_key") != key:
             from .vision import mrope_tables
-            c, s = mrope_tables(pos, self.D, float(self.rope_params["rope_theta"]), self.sections, device=pos.device,
+            c, s = mrope_tables(pos, getattr(self, "rot_dim", self.D), float(self.rope_params["rope_theta"]), self.sections, device=pos.device,
                                 interleaved=getattr(self, "mrope_interleaved", False))
             ctx["_mrope"], ctx["_mrope_key"] = (torch.cat([c, c], -1), torch.cat([s, s], -1)), key
         return ctx["_mrope"]
@@ -1738,7 +1739,135 @@ class _Qwen3VL(_Qwen2VL):
         return x
 
 
-_SPECS = {"qwen2_vl": _Qwen2VL, "qwen2_5_vl": _Qwen25VL, "qwen3_vl": _Qwen3VL, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
+class _Glm4V(_Qwen2VL):
+    """GLM-4.1V: a GLM-4 decoder (q / k / v biases, fused gate|up, an extra RMSNorm on the attention and on the MLP
+    output before each residual add, rotary angles from three position rows applied to interleaved pairs of the first
+    ``partial_rotary_factor`` share of a head) fed by a vision tower of RMSNorm blocks with SwiGLU MLPs: patch
+    embedding (with bias) - RMSNorm - a learned position table sampled bicubically at every patch's place in its
+    image - blocks with 2-D rotary attention inside each frame - RMSNorm - a merge x merge strided convolution over
+    each window - a merger (linear, LayerNorm, GELU, SwiGLU). Reference: axon/models/transformers/glm4v.py
+    (packed forward of the HF model), HF modeling_glm4v.py."""
+
+    def __init__(self, hf):
+        v = dict(hf["vision_config"])
+        v.setdefault("embed_dim", v["hidden_size"])
+        hf = {**hf, "vision_config": v}
+        super().__init__(hf)
+        self.rot_dim = int(self.D * float(self.rope_params.get("partial_rotary_factor", hf.get("partial_rotary_factor", 1.0)))) // 2 * 2
+        self.sections = list(self.rope_params.get("mrope_section") or [self.rot_dim // 2, 0, 0])
+        self.vOut, self.vCtx = int(v["out_hidden_size"]), int(v["intermediate_size"])
+        self.v_eps = float(v.get("rms_norm_eps", 1e-5))
+        self.grid_side = int(v["image_size"]) // int(v["patch_size"])
+
+    def layout(self):
+        lay = OrderedDict()
+        E, m, O = self.vE, self.merge, self.vOut
+        lay["model.visual.embeddings.position_embedding.weight"] = (self.grid_side ** 2, E)
+        lay["model.visual.patch_embed.proj.weight"], lay["model.visual.patch_embed.proj.bias"] = (E, self.patch_dim), (E,)
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            lay[p + "norm1.weight"], lay[p + "norm2.weight"] = (E,), (E,)
+            lay[p + "attn.qkv.weight"], lay[p + "attn.proj.weight"] = (3 * E, E), (E, E)
+            lay[p + "mlp.gate_proj.weight"], lay[p + "mlp.up_proj.weight"], lay[p + "mlp.down_proj.weight"] = (O, E), (O, E), (E, O)
+        lay["model.visual.merger.proj.weight"] = (O, O)
+        lay["model.visual.merger.post_projection_norm.weight"], lay["model.visual.merger.post_projection_norm.bias"] = (O,), (O,)
+        lay["model.visual.merger.gate_proj.weight"], lay["model.visual.merger.up_proj.weight"] = (self.vCtx, O), (self.vCtx, O)
+        lay["model.visual.merger.down_proj.weight"] = (O, self.vCtx)
+        lay["model.visual.post_conv_layernorm.weight"] = (E,)
+        lay["model.visual.downsample.weight"], lay["model.visual.downsample.bias"] = (O, E * m * m), (O,)
+        lay["model.visual.post_layernorm.weight"] = (E,)
+        lay["model.language_model.embed_tokens.weight"] = (self.V, self.H)
+        for l in range(self.L):
+            p = f"model.language_model.layers.{l}."
+            for n, rows in (("q_proj", self.nh * self.D), ("k_proj", self.nkv * self.D), ("v_proj", self.nkv * self.D)):
+                lay[p + f"self_attn.{n}.weight"], lay[p + f"self_attn.{n}.bias"] = (rows, self.H), (rows,)
+            lay[p + "self_attn.o_proj.weight"] = (self.H, self.nh * self.D)
+            lay[p + "mlp.gate_up_proj.weight"], lay[p + "mlp.down_proj.weight"] = (2 * self.F, self.H), (self.H, self.F)
+            for n in ("input_layernorm", "post_attention_layernorm", "post_self_attn_layernorm", "post_mlp_layernorm"):
+                lay[p + n + ".weight"] = (self.H,)
+        lay["model.language_model.norm.weight"] = (self.H,)
+        if not self.tied:
+            lay["lm_head.weight"] = (self.V, self.H)
+        return lay
+
+    def checkpoint_shape(self, name):
+        if name == "model.visual.downsample.weight":         # a Conv2d kernel [out, E, merge, merge] in the checkpoint
+            return (self.vOut, self.vE, self.merge, self.merge)
+        return super().checkpoint_shape(name)
+
+    def init_kind(self, name):
+        if "post_projection_norm" in name or name.endswith(("post_conv_layernorm.weight", "post_layernorm.weight")):
+            return "zeros" if name.endswith(".bias") else "ones"
+        return super().init_kind(name)
+
+    def patch_places(self, grid_thw):
+        """(row, column, image height, image width) of every patch, in merge-window order."""
+        ms, hs, ws, th, tw = self.merge, [], [], [], []
+        for t, h, w in grid_thw.tolist():
+            hi = torch.arange(h)[:, None].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).reshape(-1).repeat(t)
+            wi = torch.arange(w)[None, :].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).reshape(-1).repeat(t)
+            hs.append(hi), ws.append(wi), th.append(torch.full_like(hi, h)), tw.append(torch.full_like(wi, w))
+        return torch.cat(hs).float(), torch.cat(ws).float(), torch.cat(th).float(), torch.cat(tw).float()
+
+    def vision(self, W, patches, grid_thw):
+        E, Hh, m = self.vE, self.vH, self.merge
+        hd = E // Hh
+        x = linear(patches.to(W["model.visual.patch_embed.proj.weight"].dtype), W["model.visual.patch_embed.proj.weight"]) \
+            + W["model.visual.patch_embed.proj.bias"]
+        x = rms_norm(x, W["model.visual.post_conv_layernorm.weight"], self.v_eps)
+        # the position table as a [side x side] image, sampled bicubically at each patch's centre
+        hi, wi, th, tw = (t.to(x.device) for t in self.patch_places(grid_thw))
+        table = W["model.visual.embeddings.position_embedding.weight"].float().view(self.grid_side, self.grid_side, E).permute(2, 0, 1)[None]
+        grid = torch.stack(((wi + 0.5) / tw * 2 - 1, (hi + 0.5) / th * 2 - 1), dim=-1)[None, :, None, :]
+        pe = F.grid_sample(table, grid, mode="bicubic", align_corners=False, padding_mode="border")[0, :, :, 0].t()
+        x = x + pe.to(x.dtype)
+        cos, sin = self.vision_rotary(grid_thw, x.device)
+        segs, a = [], 0
+        for t, h, w in grid_thw.tolist():
+            for _ in range(int(t)):
+                segs.append((a, a + int(h) * int(w)))
+                a += int(h) * int(w)
+        assert a == x.shape[0], f"{x.shape[0]} patches for grids that describe {a}"
+        for b in range(self.vL):
+            p = f"model.visual.blocks.{b}."
+            h1 = rms_norm(x, W[p + "norm1.weight"], self.v_eps)
+            q, k, v = linear(h1, W[p + "attn.qkv.weight"]).view(-1, 3, Hh, hd).unbind(1)
+            q = (q.float() * cos[:, None] + rotate_half(q.float()) * sin[:, None]).to(x.dtype)
+            k = (k.float() * cos[:, None] + rotate_half(k.float()) * sin[:, None]).to(x.dtype)
+            outs = []
+            for s0, s1 in segs:
+                o = F.scaled_dot_product_attention(q[s0:s1].transpose(0, 1)[None], k[s0:s1].transpose(0, 1)[None],
+                                                   v[s0:s1].transpose(0, 1)[None])
+                outs.append(o[0].transpose(0, 1).reshape(s1 - s0, E))
+            x = x + linear(torch.cat(outs), W[p + "attn.proj.weight"])
+            h2 = rms_norm(x, W[p + "norm2.weight"], self.v_eps)
+            x = x + linear(F.silu(linear(h2, W[p + "mlp.gate_proj.weight"])) * linear(h2, W[p + "mlp.up_proj.weight"]), W[p + "mlp.down_proj.weight"])
+        x = rms_norm(x, W["model.visual.post_layernorm.weight"], self.v_eps)
+        x = x.view(-1, m * m, E).transpose(1, 2).reshape(-1, E * m * m)          # each window in the kernel's (channel, row, column) order
+        x = linear(x, W["model.visual.downsample.weight"]) + W["model.visual.downsample.bias"]
+        x = linear(x, W["model.visual.merger.proj.weight"])
+        x = F.gelu(F.layer_norm(x, (self.vOut,), W["model.visual.merger.post_projection_norm.weight"],
+                                W["model.visual.merger.post_projection_norm.bias"], 1e-5))
+        return linear(F.silu(linear(x, W["model.visual.merger.gate_proj.weight"])) * linear(x, W["model.visual.merger.up_proj.weight"]),
+                      W["model.visual.merger.down_proj.weight"])
+
+    def layer(self, W, l, x, ctx):
+        T = x.shape[0]
+        h = rms_norm(x, self.P(W, l, "input_layernorm.weight"), self.eps)
+        cos, sin = self.rotary(ctx)
+        q = (linear(h, self.P(W, l, "self_attn.q_proj.weight")) + self.P(W, l, "self_attn.q_proj.bias")).view(T, self.nh, self.D)
+        k = (linear(h, self.P(W, l, "self_attn.k_proj.weight")) + self.P(W, l, "self_attn.k_proj.bias")).view(T, self.nkv, self.D)
+        v = (linear(h, self.P(W, l, "self_attn.v_proj.weight")) + self.P(W, l, "self_attn.v_proj.bias")).view(T, self.nkv, self.D)
+        o = attend(apply_rope(q, cos, sin, interleaved=True), apply_rope(k, cos, sin, interleaved=True), v, ctx, l, self.D ** -0.5)
+        a = linear(o.reshape(T, self.nh * self.D), self.P(W, l, "self_attn.o_proj.weight"))
+        x = x + rms_norm(a, self.P(W, l, "post_self_attn_layernorm.weight"), self.eps)
+        h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps)
+        gate, up = linear(h, self.P(W, l, "mlp.gate_up_proj.weight")).chunk(2, dim=-1)
+        mo = linear(F.silu(gate) * up, self.P(W, l, "mlp.down_proj.weight"))
+        return x + rms_norm(mo, self.P(W, l, "post_mlp_layernorm.weight"), self.eps)
+
+
+_SPECS = {"qwen2_vl": _Qwen2VL, "qwen2_5_vl": _Qwen25VL, "qwen3_vl": _Qwen3VL, "glm4v": _Glm4V, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
           "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen35, "qwen3_5_moe_text": _Qwen35}
 
 

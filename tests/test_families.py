@@ -576,3 +576,62 @@ def test_qwen3_vl_deepstack_and_interleaved_rotary_match_transformers():
                  "model.language_model.layers.2.self_attn.k_norm.weight", "model.visual.patch_embed.proj.bias"):
         a, b = m.params.grads[name], sd[name].grad.reshape(m.params.grads[name].shape)
         assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
+
+
+def test_glm4v_tower_and_partial_interleaved_rotary_match_transformers():
+    """GLM-4.1V: bicubically sampled position table, RMSNorm / SwiGLU tower with the strided-convolution merger,
+    sandwich-norm decoder with three-row rotary angles on interleaved pairs of half of each head - logits and
+    gradients (decoder and tower) against HF."""
+    try:
+        from transformers import Glm4vConfig, Glm4vForConditionalGeneration
+    except Exception:
+        pytest.skip("transformers has no GLM-4V")
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.dense import PackedBatch
+    from axon_b200.models.families import FamilyModel
+    torch.manual_seed(0)
+    cfg = Glm4vConfig(text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                       vocab_size=300, max_position_embeddings=512,
+                                       rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [2, 1, 1], "partial_rotary_factor": 0.5}),
+                      vision_config=dict(depth=2, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+                                         temporal_patch_size=2, spatial_merge_size=2, image_size=32),
+                      image_token_id=290, video_token_id=291, image_start_token_id=292, image_end_token_id=293)
+    ref = Glm4vForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in ref.named_parameters():          # norms away from one, biases away from zero
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    grid = torch.tensor([[1, 6, 8], [1, 2, 4]])
+    pix = torch.randn(56, 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 292] + [290] * 12 + [293, 44, 292] + [290] * 2 + [293, 9, 120, 33]])
+    types = (ids == 290).int()
+    with torch.no_grad():
+        want = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+        pos = ref.model.get_rope_index(ids, types, image_grid_thw=grid, attention_mask=torch.ones_like(ids))[0][:, 0]
+    m = FamilyModel(ModelConfig.from_hf_dict(cfg.to_dict()), device="cpu", dtype=torch.float32)
+    m.load_state_dict(ref.state_dict())
+    mm = {"pixel_values": pix, "image_grid_thw": grid, "mrope_positions": pos}
+    z = m.logits(ids[0].to(torch.int32), multimodal=mm)
+    assert (z - want).abs().max() < 2e-4, (z - want).abs().max()
+    assert torch.equal(m.rotary_rows(ids[0].tolist(), {"image_grid_thw": grid}).long(), pos.long())
+    t_ids = torch.randint(0, 280, (1, 12))
+    with torch.no_grad():
+        assert (m.logits(t_ids[0].to(torch.int32)) - ref(input_ids=t_ids).logits[0].float()).abs().max() < 2e-4
+    exported = m.params.to_hf_state_dict()           # the checkpoint's shapes: the strided convolution as a Conv2d kernel
+    assert tuple(exported["model.visual.downsample.weight"].shape) == (64, 32, 2, 2)
+    assert torch.equal(exported["model.visual.downsample.weight"], ref.state_dict()["model.visual.downsample.weight"])
+    batch = PackedBatch.from_sequences([ids[0]], "cpu")
+    batch.multimodal = mm
+    lp, _ = m.forward(batch, 1.0, save_for_backward=True)
+    g = torch.linspace(0.5, 1.5, lp.numel())
+    g[-1] = 0
+    m.backward(g)
+    out = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+    lp_ref = torch.log_softmax(out[:-1], -1).gather(1, ids[0, 1:, None])[:, 0]
+    (lp_ref * g[:-1]).sum().backward()
+    named = dict(ref.named_parameters())
+    for name in ("model.visual.embeddings.position_embedding.weight", "model.visual.downsample.weight", "model.visual.blocks.0.attn.qkv.weight",
+                 "model.visual.merger.post_projection_norm.bias", "model.language_model.layers.1.post_mlp_layernorm.weight",
+                 "model.language_model.layers.0.mlp.gate_up_proj.weight", "model.language_model.layers.0.self_attn.k_proj.bias"):
+        a, b = m.params.grads[name], named[name].grad.reshape(m.params.grads[name].shape)
+        assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
