@@ -19,6 +19,7 @@ against the HF implementation of the same architecture on CPU (tests/test_famili
 from __future__ import annotations
 
 import math
+import re
 from collections import OrderedDict
 
 import torch
@@ -29,8 +30,8 @@ from .config import ModelConfig
 from .params import FlatParams
 
 FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text",
-                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "glm4v")
-VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "glm4v")
+                "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v")
+VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v")
 
 
 # ------------------------------------------------------------------------------------------ small pieces
@@ -1731,12 +1732,52 @@ class _Qwen3VL(_Qwen2VL):
         v = linear(h, self.P(W, l, "self_attn.v_proj.weight")).view(T, self.nkv, self.D)
         o = attend(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, ctx, l, self.D ** -0.5)
         x = x + linear(o.reshape(T, self.nh * self.D), self.P(W, l, "self_attn.o_proj.weight"))
-        h = rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps)
-        x = x + linear(F.silu(linear(h, self.P(W, l, "mlp.gate_proj.weight"))) * linear(h, self.P(W, l, "mlp.up_proj.weight")),
-                       self.P(W, l, "mlp.down_proj.weight"))
+        x = x + self.mlp(W, l, rms_norm(x, self.P(W, l, "post_attention_layernorm.weight"), self.eps))
         if self._deepstack is not None and l < len(self._deepstack):
             x = x.index_add(0, self._visual_idx, self._deepstack[l])
         return x
+
+    def mlp(self, W, l, h):
+        return linear(F.silu(linear(h, self.P(W, l, "mlp.gate_proj.weight"))) * linear(h, self.P(W, l, "mlp.up_proj.weight")),
+                      self.P(W, l, "mlp.down_proj.weight"))
+
+
+class _Qwen3VLMoe(_Qwen3VL):
+    """Qwen3-VL with a sparse decoder: the layers named by ``decoder_sparse_step`` / ``mlp_only_layers`` replace the
+    MLP with top-k softmax routing (weights renormalised over the chosen experts) over stacked SwiGLU experts.
+    Reference: axon/models/transformers/qwen3_vl.py (its patch of the sparse block), HF modeling_qwen3_vl_moe.py."""
+
+    def __init__(self, hf):
+        super().__init__(hf)
+        self.E, self.k, self.Fm = int(hf.get("num_experts") or hf["num_local_experts"]), int(hf["num_experts_per_tok"]), int(hf["moe_intermediate_size"])
+        step, dense_only = int(hf.get("decoder_sparse_step", 1) or 1), set(hf.get("mlp_only_layers") or [])
+        self.sparse = [l not in dense_only and self.E > 0 and (l + 1) % step == 0 for l in range(self.L)]
+
+    def layout(self):
+        lay = OrderedDict()
+        for name, shape in super().layout().items():
+            m = re.match(r"model\.language_model\.layers\.(\d+)\.mlp\.(gate_proj|up_proj|down_proj)\.weight", name)
+            if m and self.sparse[int(m.group(1))]:
+                if m.group(2) == "gate_proj":
+                    p = f"model.language_model.layers.{m.group(1)}.mlp."
+                    lay[p + "experts.gate_up_proj"], lay[p + "experts.down_proj"] = (self.E, 2 * self.Fm, self.H), (self.E, self.H, self.Fm)
+                    lay[p + "gate.weight"] = (self.E, self.H)
+                continue
+            lay[name] = shape
+        return lay
+
+    def mlp(self, W, l, h):
+        if not self.sparse[l]:
+            return super().mlp(W, l, h)
+        probs = torch.softmax(F.linear(h, self.P(W, l, "mlp.gate.weight")), dim=-1, dtype=torch.float)
+        w, idx = probs.topk(self.k, dim=-1)
+        w = w / w.sum(-1, keepdim=True)
+        gu, dn = self.P(W, l, "mlp.experts.gate_up_proj"), self.P(W, l, "mlp.experts.down_proj")
+
+        def expert(e, rows):
+            g, u = F.linear(rows, gu[e]).chunk(2, dim=-1)
+            return F.linear(F.silu(g) * u, dn[e])
+        return experts_forward(h, idx, w.to(h.dtype), expert, self.E)
 
 
 class _Glm4V(_Qwen2VL):
@@ -1867,7 +1908,7 @@ class _Glm4V(_Qwen2VL):
         return x + rms_norm(mo, self.P(W, l, "post_mlp_layernorm.weight"), self.eps)
 
 
-_SPECS = {"qwen2_vl": _Qwen2VL, "qwen2_5_vl": _Qwen25VL, "qwen3_vl": _Qwen3VL, "glm4v": _Glm4V, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
+_SPECS = {"qwen2_vl": _Qwen2VL, "qwen2_5_vl": _Qwen25VL, "qwen3_vl": _Qwen3VL, "qwen3_vl_moe": _Qwen3VLMoe, "glm4v": _Glm4V, "deepseek_v3": _DeepseekV3, "glm4_moe_lite": _DeepseekV3, "glm_moe_dsa": _GlmMoeDsa, "gemma4_text": _Gemma4, "glm4_moe": _Glm4Moe, "gpt_oss": _GptOss,
           "gemma2": _Gemma, "gemma3_text": _Gemma, "qwen3_next": _Qwen3Next, "qwen3_5_text": _Qwen35, "qwen3_5_moe_text": _Qwen35}
 
 

@@ -635,3 +635,54 @@ def test_glm4v_tower_and_partial_interleaved_rotary_match_transformers():
                  "model.language_model.layers.0.mlp.gate_up_proj.weight", "model.language_model.layers.0.self_attn.k_proj.bias"):
         a, b = m.params.grads[name], named[name].grad.reshape(m.params.grads[name].shape)
         assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
+
+
+def test_qwen3_vl_moe_sparse_decoder_matches_transformers():
+    """Qwen3-VL-MoE: the Qwen3-VL tower and DeepStack in front of a decoder with routed experts."""
+    try:
+        from transformers import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+    except Exception:
+        pytest.skip("transformers has no Qwen3-VL-MoE")
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.dense import PackedBatch
+    from axon_b200.models.families import FamilyModel
+    torch.manual_seed(0)
+    cfg = Qwen3VLMoeConfig(text_config=dict(hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_experts=4, num_experts_per_tok=2,
+                                            num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16, vocab_size=300,
+                                            decoder_sparse_step=1, mlp_only_layers=[1], max_position_embeddings=512,
+                                            rope_scaling={"rope_type": "default", "mrope_section": [2, 3, 3], "mrope_interleaved": True}),
+                           vision_config=dict(depth=2, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+                                              temporal_patch_size=2, spatial_merge_size=2, num_position_embeddings=64, deepstack_visual_indexes=[0]),
+                           image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    ref = Qwen3VLMoeForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if "experts" in n or n.endswith("mlp.gate.weight"):
+                p.normal_(0, 0.2)
+    grid = torch.tensor([[1, 4, 4]])
+    pix = torch.randn(16, 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 292] + [290] * 4 + [293, 44, 9, 120, 33, 7]])
+    types = (ids == 290).int()
+    with torch.no_grad():
+        want = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+        pos = ref.model.get_rope_index(ids, types, image_grid_thw=grid, attention_mask=torch.ones_like(ids))[0][:, 0]
+    m = FamilyModel(ModelConfig.from_hf_dict(cfg.to_dict()), device="cpu", dtype=torch.float32)
+    assert m.cfg.num_experts == 4
+    m.load_state_dict(ref.state_dict())
+    mm = {"pixel_values": pix, "image_grid_thw": grid, "mrope_positions": pos}
+    z = m.logits(ids[0].to(torch.int32), multimodal=mm)
+    assert (z - want).abs().max() < 2e-4, (z - want).abs().max()
+    batch = PackedBatch.from_sequences([ids[0]], "cpu")
+    batch.multimodal = mm
+    lp, _ = m.forward(batch, 1.0, save_for_backward=True)
+    g = torch.linspace(0.5, 1.5, lp.numel())
+    g[-1] = 0
+    m.backward(g)
+    out = ref(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=types).logits[0].float()
+    lp_ref = torch.log_softmax(out[:-1], -1).gather(1, ids[0, 1:, None])[:, 0]
+    (lp_ref * g[:-1]).sum().backward()
+    named = dict(ref.named_parameters())
+    for name in ("model.language_model.layers.0.mlp.experts.gate_up_proj", "model.language_model.layers.2.mlp.gate.weight",
+                 "model.language_model.layers.1.mlp.up_proj.weight", "model.visual.deepstack_merger_list.0.linear_fc1.weight"):
+        a, b = m.params.grads[name], named[name].grad
+        assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
