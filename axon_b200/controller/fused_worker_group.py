@@ -28,6 +28,7 @@ def fuse_worker_cls(class_dict: dict[str, ClassWithInitArgs]) -> ClassWithInitAr
 
     class FusedWorker:
         _role_classes = {r: class_dict[r].cls for r in roles}
+        _fused_spec = class_dict          # how a worker process assembles this class again (``ClassWithInitArgs``)
 
         def __init__(self):
             self.role_objects = {r: class_dict[r]() for r in roles}

@@ -44,13 +44,21 @@ class ClassWithInitArgs:
         if spec is not None:
             state["cls"] = None
             state["_spec"] = spec
+        fused = getattr(self.cls, "_fused_spec", None)       # a colocated multi-role worker: its roles' recipes travel
+        if fused is not None:
+            state["cls"] = None
+            state["_fused"] = fused
         return state
 
     def __setstate__(self, state):
         spec = state.pop("_spec", None)
+        fused = state.pop("_fused", None)
         self.__dict__.update(state)
         if spec is not None:
             self.cls = synthesize_class(*spec)
+        if fused is not None:
+            from .fused_worker_group import fuse_worker_cls
+            self.cls = fuse_worker_cls(fused).cls
 
 
 def synthesize_class(name: str, base: type, mixins: tuple = ()) -> type:

@@ -310,7 +310,7 @@ class FamilyModel:
         self.device, self.dtype = torch.device(device), dtype
         self.spec = _SPECS[self.kind](self.hf)
         self.layout = self.spec.layout()
-        self.params = FamilyParams(cfg, self.device, dtype, self.layout, self.spec)
+        self.params = self._make_params()
         self.buffers: dict[str, torch.Tensor] = self.spec.buffers(self.device)      # non-trainable tensors of the checkpoint
         self.recompute = "full"
         self._saved = None
@@ -320,6 +320,14 @@ class FamilyModel:
         self.has_recurrent_state = any(t == "linear_attention" for t in getattr(self.spec, "types", [])) or self.kind == "glm_moe_dsa"
 
     # ---- parameters
+    def _make_params(self):
+        """Storage for ``self.layout`` (a model with parameter shards allocates its pieces instead)."""
+        return FamilyParams(self.cfg, self.device, self.dtype, self.layout, self.spec)
+
+    def _layer_call(self, W, l: int, h, ctx):
+        """Decoder layer ``l`` on the weights ``W`` (a model with parameter shards gathers the layer first)."""
+        return self.spec.layer(W, l, h, ctx)
+
     def init_random(self, std: float = 0.02, seed: int = 0) -> None:
         self.params.init_random(std, seed)
 
@@ -363,7 +371,7 @@ class FamilyModel:
             x = self.spec.embed(W, input_ids)
         ctx = {"positions": position_ids, "cu": cu, "model": self}
         for l in range(self.cfg.num_hidden_layers):
-            fn = lambda h, l=l: self.spec.layer(W, l, h, ctx)      # noqa: E731
+            fn = lambda h, l=l: self._layer_call(W, l, h, ctx)      # noqa: E731
             x = checkpoint(fn, x, use_reentrant=False) if ckpt else fn(x)
         return self.spec.final_norm(W, x)
 

@@ -63,6 +63,13 @@ class Zero3DenseModel(DenseModel):
             out[name] = (self.shard.all_gather_rows(v.detach()) if is_sharded(name) else v.detach()).cpu().clone()
         return out
 
+    serves_sampler = False       # a colocated sampler keeps a replica with whole parameters
+
+    def full_named_tensors(self):
+        """(name, whole tensor) of every parameter, gathered one at a time; a collective every rank iterates to the end."""
+        for name, v in self.params.views.items():
+            yield name, (self.shard.all_gather_rows(v.detach()) if is_sharded(name) else v.detach())
+
     def replicated_names(self) -> list[str]:
         return [n for n in self.params.layout if not is_sharded(n)]
 

@@ -31,7 +31,9 @@ class SyncSamplerMixin:
                 need = int(eng._num_pages) * PagedKVCache.bytes_per_page(eng.cfg, eng.model.params.flat.element_size())
             peer.rollout_mode(need)
             if not self.shares_trainer_weights:
-                self.server.update_weights(peer.model.params.views.items())
+                # a trainer with parameter shards gathers whole tensors layer by layer (every rank takes part)
+                gathered = getattr(peer.model, "full_named_tensors", None)
+                self.server.update_weights(gathered() if gathered is not None else peer.model.params.views.items())
         self.server.wake_up()
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)

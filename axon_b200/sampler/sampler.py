@@ -84,7 +84,13 @@ class SamplerWorker(Worker, DistProfilerExtension):
                 raise NotImplementedError("a tensor-parallel sampler owns its weights (disaggregated deployment); "
                                           "colocated samplers share the trainer's buffer and run one replica per GPU")
             lockstep = self._make_tp_groups()
-        if trainer is not None:
+        if trainer is not None and not getattr(trainer.model, "serves_sampler", True):
+            # the trainer keeps parameter shards: this sampler holds a replica with whole parameters of its own and is
+            # refreshed from the trainer's gathered tensors at every switch to rollout
+            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            self.model = build_model(_get(cfg, "model_path"), device=self.device, dtype=dtype, seed=int(_get(cfg, "seed", 42)),
+                                     load_weights=False)
+        elif trainer is not None:
             self.model = trainer.model                  # zero-copy: generation reads the trainer's live parameters
             self.shares_trainer_weights = True
         elif self.tp > 1:
@@ -164,15 +170,24 @@ class SamplerWorker(Worker, DistProfilerExtension):
 
     def _start_http(self) -> None:
         import socket
+        import time
 
         import uvicorn
-        with socket.socket() as s:
-            s.bind(("127.0.0.1", 0))
-            port = s.getsockname()[1]
+        # the listening socket is opened HERE and handed to the server: a port that was only probed could be taken by
+        # another worker process before the server binds it
+        sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+        sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
         cfg = uvicorn.Config(self.server.build_app(), host="127.0.0.1", port=port, log_level="warning")
         self._http_server = uvicorn.Server(cfg)
-        self._http_thread = threading.Thread(target=self._http_server.run, daemon=True, name="sampler-http")
+        self._http_thread = threading.Thread(target=self._http_server.run, kwargs={"sockets": [sock]}, daemon=True, name="sampler-http")
         self._http_thread.start()
+        deadline = time.monotonic() + 30.0
+        while not self._http_server.started and self._http_thread.is_alive() and time.monotonic() < deadline:
+            time.sleep(0.01)
+        if not self._http_server.started:
+            raise RuntimeError("the sampler's HTTP server did not start")
         self.address = f"http://127.0.0.1:{port}"
 
     def _kv_bytes_beside_optimizer(self, trainer, kv_bytes: int) -> int:

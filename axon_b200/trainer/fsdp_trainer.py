@@ -171,6 +171,10 @@ class TrainerWorker(Worker, DistProfilerExtension):
 
     def _make_state_manager(self):
         from ..utils.state import FSDPStateManager
+        if hasattr(self.model, "full_named_tensors") and hasattr(self.model, "layer_offsets"):      # a family model cut layer by layer
+            from ..utils.state.fsdp_state_manager import ShardedFamilyStateManager
+            return ShardedFamilyStateManager(self.model, self.engine, group=self._mp_group, processing_class=self.tokenizer,
+                                             rank=self.rank, world_size=self.world_size)
         if getattr(self.model, "shard", None) is not None:      # parameter shards: per-rank files + gathered HF export
             from ..utils.state.megatron_state_manager import MegatronStateManager
             return MegatronStateManager(self.model, self.engine, mp_group=self._mp_group, dp_rank=0, processing_class=self.tokenizer,
@@ -202,10 +206,12 @@ class TrainerWorker(Worker, DistProfilerExtension):
         if bool(_get(self.config, "fsdp.param_sharding", False)) and self.world_size > 1:
             # ZeRO-3 / FSDP-style parameter shards over all ranks: the optimizer works on this rank's shards only
             # (a group of its own), replicated parameters are summed by the model's hook
+            from ..models.families import FAMILY_TYPES
             from ..models.zero3_dense import Zero3DenseModel
             from ..parallel.zero3 import ShardContext
-            assert mcfg.num_experts == 0 and not self.model_kind.value_head and self.ulysses_sequence_parallel_size == 1, \
-                "parameter sharding is available on dense causal-LM models without sequence parallelism"
+            family = mcfg.model_type in FAMILY_TYPES
+            assert (family or mcfg.num_experts == 0) and not self.model_kind.value_head and self.ulysses_sequence_parallel_size == 1, \
+                "parameter sharding is available on dense causal-LM models and on the family toolkit's models, without sequence parallelism"
             own = None
             for r in range(self.world_size):
                 g = dist.new_group([r])
@@ -214,6 +220,15 @@ class TrainerWorker(Worker, DistProfilerExtension):
             world_group = self.pg
             self.pg = own
             self._mp_group = world_group
+            if family:
+                # one piece of every decoder layer per rank; a layer is gathered for its forward and again for its backward
+                from ..models.sharded_family import ShardedFamilyModel
+                model = ShardedFamilyModel(mcfg, ShardContext(world_group, self.device, fused=False), device=self.device, dtype=dtype)
+                if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+                    model.load_hf_checkpoint(model_path)
+                else:
+                    model.init_random(seed=seed)
+                return model
             model = Zero3DenseModel(mcfg, ShardContext(world_group, self.device), device=self.device, dtype=dtype)
             model.recompute = str(_get(self.config, "recompute", "selective"))
             if os.path.isdir(str(model_path)) and has_hf_weights(model_path):

@@ -33,6 +33,8 @@ class FSDPStateManager(BaseStateManager):
     """``model`` is the policy model (flat parameters), ``optimizer`` the PolicyEngine that owns the
     sharded optimizer state."""
 
+    layout_tag = "zero1-flat"
+
     def __init__(self, model, optimizer, lr_scheduler=None, processing_class=None, rank=None, world_size=None,
                  process_group=None):
         super().__init__(model, optimizer, lr_scheduler, processing_class, rank, world_size)
@@ -62,6 +64,12 @@ class FSDPStateManager(BaseStateManager):
         out.copy_(t, non_blocking=True)
         return out
 
+    def _export_state_dict(self, want_hf: bool, pin: bool):
+        """HF-named whole tensors on the host for the export (rank 0 only; None elsewhere)."""
+        if want_hf and self.rank == 0:
+            return {k: self._to_host(v, pin) for k, v in self.model.params.to_hf_state_dict().items()}
+        return None
+
     # -- save ----------------------------------------------------------------------------------
     def save_state(self, local_path: str, global_step: int = 0, max_ckpt_to_keep: int | None = None,
                    save_mode: str | None = None, async_save: bool | None = None):
@@ -87,9 +95,7 @@ class FSDPStateManager(BaseStateManager):
                                       "exp_avg_sq": self._to_host(eng.exp_avg_sq, pin), "step": eng.opt_step, "range": (lo, hi)}
         files[self._name("extra_state")] = {"lr_scheduler": {"opt_step": eng.opt_step, "sched_step": getattr(eng, "sched_step", eng.opt_step)},
                                             "rng": self.get_rng_state(), "global_step": global_step}
-        hf_sd = None
-        if want_hf and self.rank == 0:
-            hf_sd = {k: self._to_host(v, pin) for k, v in params.to_hf_state_dict().items()}
+        hf_sd = self._export_state_dict(want_hf, pin)
         if torch.cuda.is_available() and params.flat.is_cuda:
             torch.cuda.current_stream().synchronize()
 
@@ -100,7 +106,7 @@ class FSDPStateManager(BaseStateManager):
                 os.replace(tmp, os.path.join(local_path, name))
             if self.rank == 0:
                 with open(os.path.join(local_path, "fsdp_config.json"), "w") as f:
-                    json.dump({"FSDP_version": "zero1-flat", "world_size": self.world_size}, f, indent=4)
+                    json.dump({"FSDP_version": self.layout_tag, "world_size": self.world_size}, f, indent=4)
                 from ..hf_model import save_hf_model
                 if hf_sd is not None:
                     save_hf_model(params, hf_dir, cfg=params.cfg, tokenizer=self.processing_class, state_dict=hf_sd)
@@ -171,3 +177,27 @@ class FSDPStateManager(BaseStateManager):
         if hasattr(eng, "sched_step"):
             eng.sched_step = int(sched.get("sched_step", eng.opt_step))
         _barrier(self.pg)
+
+
+class ShardedFamilyStateManager(FSDPStateManager):
+    """Checkpoints of a family model with parameter shards (``models/sharded_family.py``): every rank writes its own
+    pieces and optimizer state (the files of the flat layout, with the rank's whole local buffer as its range), the HF
+    export gathers one layer at a time and is written by rank 0. Resuming needs the writing world size; any other
+    layout starts from the HF export."""
+    layout_tag = "layer-pieces"
+
+    def __init__(self, model, optimizer, group=None, **kw):
+        super().__init__(model, optimizer, process_group=group, **kw)
+
+    def _export_state_dict(self, want_hf: bool, pin: bool):
+        if not want_hf:
+            return None
+        out = {} if self.rank == 0 else None
+        shape_of = getattr(self.model.spec, "checkpoint_shape", lambda n: None)
+        for name, t in self.model.full_named_tensors():       # a collective: every rank walks all layers
+            if out is not None:
+                t = t if shape_of(name) is None else t.reshape(shape_of(name))
+                out[name] = self._to_host(t, False)
+        if torch.cuda.is_available() and self.model.params.flat.is_cuda:
+            torch.cuda.current_stream().synchronize()
+        return out

@@ -111,3 +111,23 @@ def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
     assert [r["step"] for r in logs] == [1, 2]
     for r in logs:
         assert abs(r["data"]["batch/sampler_logprobs_diff_max"]) < 0.02 and abs(r["data"]["batch/sampler_logprobs_diff_min"]) < 0.02, r["data"]
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("model,shards", [("tiny-gemma3", True), ("tiny-qwen3", True), ("tiny-qwen3", False)])
+def test_colocated_run_on_two_worker_processes(tmp_path, model, shards):
+    """Two colocated ranks, each a worker process that holds the trainer and the sampler role. With parameter shards (a
+    family model cut layer by layer / the dense model cut by rows) each sampler holds a whole replica that is refreshed
+    from the gathered tensors before every rollout; without, it reads the trainer's buffer. Either way what it samples
+    has the trainer's log-probs."""
+    extra = ["num_gpus_per_node=2", "total_training_steps=2", "save_steps=-1", f"model_path={model}",
+             f"actor.fsdp.param_sharding={'true' if shards else 'false'}"]
+    drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
+    try:
+        assert drv.global_steps == 3
+    finally:
+        drv.shutdown()
+    logs = _logged_steps(tmp_path)
+    assert [r["step"] for r in logs] == [1, 2]
+    for r in logs:
+        assert abs(r["data"]["batch/sampler_logprobs_diff_max"]) < 0.02 and abs(r["data"]["batch/sampler_logprobs_diff_min"]) < 0.02, r["data"]
