@@ -161,19 +161,28 @@ class _ShardedInference:
                 dist.broadcast(v, src=src, group=self.shard.group)
 
 
+def _own_or_shared_params(cfg: ModelConfig, lc: ModelConfig, shard: Shard, device, dtype, share):
+    """Storage of one rank's part. ``share``: the ``FlatParams`` of a tensor-parallel TRAINER model of the same group
+    size (``tp_dense.TPDenseModel`` / ``tp_moe.TPMoEModel`` use the very same per-rank layout): the sampler then reads
+    the trainer's live shards - also after the trainer moved them to another buffer - and a weight update moves nothing."""
+    if share is not None:
+        assert dict(share.layout) == dict(local_layout(cfg, shard.world, shard.rank)), \
+            "trainer and sampler disagree about the per-rank parameter layout"
+        return share
+    return FlatParams(lc, torch.device(device), dtype, layout=local_layout(cfg, shard.world, shard.rank))
+
+
 class ShardedDenseModel(_ShardedInference, DenseModel):
-    def __init__(self, cfg: ModelConfig, shard: Shard, device="cuda", dtype=torch.bfloat16):
+    def __init__(self, cfg: ModelConfig, shard: Shard, device="cuda", dtype=torch.bfloat16, share=None):
         lc = local_config(cfg, shard.world)
-        params = FlatParams(lc, torch.device(device), dtype, layout=local_layout(cfg, shard.world, shard.rank))
-        DenseModel.__init__(self, lc, device, dtype, params)
+        DenseModel.__init__(self, lc, device, dtype, _own_or_shared_params(cfg, lc, shard, device, dtype, share))
         self._bind(cfg, shard)
 
 
 class ShardedMoEModel(_ShardedInference, MoEModel):
-    def __init__(self, cfg: ModelConfig, shard: Shard, device="cuda", dtype=torch.bfloat16):
+    def __init__(self, cfg: ModelConfig, shard: Shard, device="cuda", dtype=torch.bfloat16, share=None):
         lc = local_config(cfg, shard.world)
-        params = FlatParams(lc, torch.device(device), dtype, layout=local_layout(cfg, shard.world, shard.rank))
-        MoEModel.__init__(self, lc, device, dtype, params)
+        MoEModel.__init__(self, lc, device, dtype, _own_or_shared_params(cfg, lc, shard, device, dtype, share))
         self._bind(cfg, shard)
 
     def mlp_infer(self, l: int, h2):
@@ -195,6 +204,20 @@ class ShardedMoEModel(_ShardedInference, MoEModel):
 
     def mlp_fwd(self, *a, **k):
         raise NotImplementedError("a sharded sampler model has no training pass")
+
+
+def share_trainer_shards(trainer_model, shard: Shard):
+    """The sampler-side model of one rank over the SAME storage as a tensor-parallel trainer model of the same group
+    (zero-copy colocated deployment); None when the trainer's layout is not the sampler's."""
+    inner = getattr(trainer_model, "inner", trainer_model)
+    tp = getattr(inner, "tp", None)
+    if tp is None or not hasattr(inner, "hq") or tp.world != shard.world or tp.rank != shard.rank or getattr(inner, "shard_head", False):
+        return None
+    cfg = inner.cfg
+    if cfg.num_experts > 0 and getattr(inner, "ep_world", 1) != shard.world:
+        return None
+    cls = ShardedMoEModel if cfg.num_experts > 0 else ShardedDenseModel
+    return cls(cfg, shard, device=inner.device, dtype=inner.dtype, share=inner.params)
 
 
 def build_sharded_model(model_path, shard: Shard, device="cuda", dtype=torch.bfloat16, seed: int = 0, load_weights: bool = True):

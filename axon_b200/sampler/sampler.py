@@ -80,11 +80,20 @@ class SamplerWorker(Worker, DistProfilerExtension):
         if self.tp * self.pp > 1:
             if self.pp > 1:
                 raise NotImplementedError("the sampler shards a model over tensor-parallel groups; pipeline stages are not built")
-            if trainer is not None:
-                raise NotImplementedError("a tensor-parallel sampler owns its weights (disaggregated deployment); "
-                                          "colocated samplers share the trainer's buffer and run one replica per GPU")
             lockstep = self._make_tp_groups()
-        if trainer is not None and not getattr(trainer.model, "serves_sampler", True):
+        shared = None
+        if trainer is not None and self.tp > 1:
+            # colocated with a tensor- (and expert-) parallel trainer of the same group size: read its shards in place
+            from ..models.tp_infer import Shard, share_trainer_shards
+            shared = share_trainer_shards(trainer.model, Shard.create(self.tp_group, self.device))
+            if shared is None:
+                raise NotImplementedError("a colocated tensor-parallel sampler reads the shards of a trainer with the same "
+                                          "tensor-parallel (and expert-parallel) group size and a whole output head; other "
+                                          "layouts need the disaggregated deployment")
+        if shared is not None:
+            self.model = shared
+            self.shares_trainer_weights = True
+        elif trainer is not None and not getattr(trainer.model, "serves_sampler", True):
             # the trainer keeps parameter shards: this sampler holds a replica with whole parameters of its own and is
             # refreshed from the trainer's gathered tensors at every switch to rollout
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32

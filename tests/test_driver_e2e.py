@@ -131,3 +131,25 @@ def test_colocated_run_on_two_worker_processes(tmp_path, model, shards):
     assert [r["step"] for r in logs] == [1, 2]
     for r in logs:
         assert abs(r["data"]["batch/sampler_logprobs_diff_max"]) < 0.02 and abs(r["data"]["batch/sampler_logprobs_diff_min"]) < 0.02, r["data"]
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("model", ["dense", "moe"])
+def test_colocated_tensor_parallel_trainer_and_sampler_share_their_shards(tmp_path, model):
+    """Two colocated ranks form ONE tensor-parallel group for both roles (sparse model: it also divides the experts):
+    the sampler group reads the trainer's shards in place, generates in lockstep behind its first rank, and what it
+    samples has the trainer's log-probs - also after the optimizer step."""
+    extra = ["num_gpus_per_node=2", "total_training_steps=2", "save_steps=-1", "strategy=megatron",
+             "actor.megatron.tensor_model_parallel_size=2", "sampler.tensor_model_parallel_size=2"]
+    if model == "moe":
+        extra += ["model_path=tiny-moe", "actor.megatron.expert_model_parallel_size=2", "moe_replay=true"]
+    drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
+    try:
+        assert drv.global_steps == 3
+        assert len(drv.server_addresses) == 1
+    finally:
+        drv.shutdown()
+    logs = _logged_steps(tmp_path)
+    assert [r["step"] for r in logs] == [1, 2]
+    for r in logs:
+        assert abs(r["data"]["batch/sampler_logprobs_diff_max"]) < 0.02 and abs(r["data"]["batch/sampler_logprobs_diff_min"]) < 0.02, r["data"]
