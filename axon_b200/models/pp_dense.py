@@ -37,9 +37,76 @@ def stage_layers(num_layers: int, stages: int, stage: int) -> range:
     return range(lo, lo + base + (1 if stage < rem else 0))
 
 
-def stage_keeps(cfg: ModelConfig, stages: int, stage: int):
+def chunk_layers(num_layers: int, stages: int, stage: int, virtual: int = 1) -> list[range]:
+    """Layer ranges of the ``virtual`` model chunks of ``stage``: chunk c is virtual stage ``c * stages + stage`` of
+    a pipeline of ``stages * virtual`` virtual stages (interleaved assignment)."""
+    return [stage_layers(num_layers, stages * virtual, c * stages + stage) for c in range(virtual)]
+
+
+def virtual_schedule(stages: int, virtual: int, micro: int, train: bool = True, backward_only: bool = False) -> list[list[tuple]]:
+    """The interleaved one-forward-one-backward schedule of every rank as lock-step ticks.
+
+    Forwards visit the micro-batches in groups of ``stages`` and, inside a group, chunk after chunk; backwards visit the
+    chunks in reverse (reference: the interleaved schedule behind ``virtual_pipeline_model_parallel_size``,
+    axon/utils/megatron/pipeline_parallel.py). A rank prefers a backward whose upstream gradient has arrived; else it
+    runs its next forward whose input has arrived, as long as it holds the activations of fewer than
+    ``2 (stages - 1 - rank) + (virtual - 1) stages + 1`` forwards (``stages - rank`` with one chunk) - the warm-up depth
+    of that schedule, which bounds activation memory. "Arrived" means produced in an EARLIER tick: everything produced
+    in a tick is exchanged at the end of that tick, so the send of one rank and the receive of its neighbour always sit
+    in the same batch of point-to-point operations. If the bound ever blocks every rank (micro-batch counts that are
+    not a multiple of ``stages``), it is lifted for that tick.
+
+    Returns ``ticks[t][rank] = (kind, micro-batch, chunk) | None``; every rank computes the same table."""
+    P, v, M = stages, virtual, micro
+    K = P * v
+    fwd = [(m, c) for g0 in range(0, M, P) for c in range(v) for m in range(g0, min(g0 + P, M))]
+    bwd = [(m, c) for g0 in range(0, M, P) for c in reversed(range(v)) for m in range(g0, min(g0 + P, M))]
+    want_f = not backward_only
+    want_b = train or backward_only
+    done_f = set() if want_f else {(m, k) for m in range(M) for k in range(K)}
+    done_b: set = set()
+    todo_f = [list(fwd) if want_f else [] for _ in range(P)]
+    todo_b = [list(bwd) if want_b else [] for _ in range(P)]
+    held = [0] * P
+    cap = [((P - r - 1) * 2 + (v - 1) * P if v > 1 else P - 1 - r) + 1 for r in range(P)]
+    ticks = []
+
+    def pick(r, bounded):
+        for m, c in todo_b[r]:
+            k = c * P + r
+            if (m, k) in done_f and (k == K - 1 or (m, k + 1) in done_b):
+                return ("B", m, c)
+        if todo_f[r] and (not bounded or not want_b or held[r] < cap[r]):
+            m, c = todo_f[r][0]                  # forwards strictly in order: the receiver's inputs arrive in order too
+            k = c * P + r
+            if k == 0 or (m, k - 1) in done_f:
+                return ("F", m, c)
+        return None
+
+    while any(todo_f[r] or todo_b[r] for r in range(P)):
+        step = [pick(r, True) for r in range(P)]
+        if not any(step):
+            step = [pick(r, False) for r in range(P)]
+        assert any(step), f"pipeline schedule stalls (stages={P}, virtual={v}, micro-batches={M})"
+        for r, op in enumerate(step):
+            if op is None:
+                continue
+            kind, m, c = op
+            if kind == "F":
+                done_f.add((m, c * P + r))
+                todo_f[r].remove((m, c))
+                held[r] += 1
+            else:
+                done_b.add((m, c * P + r))
+                todo_b[r].remove((m, c))
+                held[r] -= 1
+        ticks.append(step)
+    return ticks
+
+
+def stage_keeps(cfg: ModelConfig, stages: int, stage: int, virtual: int = 1):
     """Predicate over parameter names: does ``stage`` hold this parameter?"""
-    keep = tuple(f"model.layers.{l}." for l in stage_layers(cfg.num_hidden_layers, stages, stage))
+    keep = tuple(f"model.layers.{l}." for rng in chunk_layers(cfg.num_hidden_layers, stages, stage, virtual) for l in rng)
 
     def holds(name: str) -> bool:
         if name.startswith("model.layers."):
@@ -50,9 +117,9 @@ def stage_keeps(cfg: ModelConfig, stages: int, stage: int):
     return holds
 
 
-def stage_layout(cfg: ModelConfig, stages: int, stage: int):
+def stage_layout(cfg: ModelConfig, stages: int, stage: int, virtual: int = 1):
     lay = param_layout(cfg)
-    holds = stage_keeps(cfg, stages, stage)
+    holds = stage_keeps(cfg, stages, stage, virtual)
     out = type(lay)()
     for name, shape in lay.items():
         if holds(name):
@@ -118,6 +185,8 @@ class PipelineSchedule:
     (logprob, entropy)`` over the whole micro-batch (last stage), ``_state_bwd(state, upstream) -> d(stream) | None`` and
     ``_stream_shape(batch)``; plus ``pp`` (PipelineContext), ``stage``, ``stages``, ``params``, ``device``, ``dtype``."""
 
+    vpp = 1          # model chunks per rank (interleaved / virtual pipeline stages); > 1 runs the tick engine below
+
     @property
     def first(self) -> bool:
         return self.stage == 0
@@ -136,8 +205,72 @@ class PipelineSchedule:
         if not self.last:
             self.pp.exchange([(x, self.stage + 1), (delta, self.stage + 1)], [])
 
+    # ------------------------------------------------------------------ interleaved (virtual) stages
+    def _run_ticks(self, batches, ticks, temperature: float, loss_cb=None, save: bool = True, states: dict | None = None,
+                   collect: dict | None = None) -> dict:
+        """Execute this rank's column of a ``virtual_schedule`` table. A forward of virtual stage k hands (x, delta) to
+        the rank after this one (the last rank wraps around to the first, whose next chunk continues), a backward hands
+        d(stream) to the rank before; both travel in the ONE batch of point-to-point operations that ends the tick, in
+        which the receiving rank has posted the matching receive. ``states``: (micro-batch, chunk) -> saved forward
+        state; ``collect``: micro-batch -> (log-prob, entropy) on the rank that holds the head."""
+        P, r, v = self.stages, self.stage, self.vpp
+        K = P * v
+        inbox: dict = {}
+        states = {} if states is None else states
+        for step in ticks:
+            sends, op = [], step[r]
+            if op is not None:
+                kind, m, c = op
+                k = c * P + r
+                if kind == "F":
+                    x, delta, st = self._layers_fwd(batches[m], None if k == 0 else inbox.pop(("F", m, k)), save, chunk=c)
+                    if k == K - 1:
+                        lp, ent = self._head_fwd(x, delta, batches[m], temperature, st)
+                        if loss_cb is not None:
+                            st["upstream"] = loss_cb(m, lp, ent)
+                        if collect is not None:
+                            collect[m] = (lp, ent)
+                    else:
+                        sends += [(x, (r + 1) % P), (delta, (r + 1) % P)]
+                    if save:
+                        states[(m, c)] = st
+                else:
+                    st = states.pop((m, c))
+                    dx = self._state_bwd(st, st.pop("upstream") if k == K - 1 else inbox.pop(("B", m, k)))
+                    if k > 0:
+                        sends.append((dx, (r - 1) % P))
+            recvs, keys = [], []
+            for q, oq in enumerate(step):              # what the other ranks produced for this one in this tick
+                if oq is None or q == r:
+                    continue
+                kind, m, c = oq
+                k = c * P + q
+                shape = self._stream_shape(batches[m])
+                if kind == "F" and k < K - 1 and (q + 1) % P == r:
+                    recvs += [(shape, self.dtype, q)] * 2
+                    keys.append(("F", m, k + 1, 2))
+                elif kind == "B" and k > 0 and (q - 1) % P == r:
+                    recvs.append((shape, self.dtype, q))
+                    keys.append(("B", m, k - 1, 1))
+            got = self.pp.exchange(sends, recvs) if (sends or recvs) else []
+            at = 0
+            for kind, m, k, n in keys:
+                inbox[(kind, m, k)] = tuple(got[at:at + n]) if n == 2 else got[at]
+                at += n
+        assert not inbox, "activations or gradients were left undelivered"
+        return states
+
     # ------------------------------------------------------------------ one micro-batch (stages take turns)
     def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
+        if self.vpp > 1:
+            T, got = batch.input_ids.numel(), {}
+            states = self._run_ticks([batch], virtual_schedule(self.stages, self.vpp, 1, train=False), temperature,
+                                     save=save_for_backward, collect=got)
+            both = torch.stack([got[0][0].float(), got[0][1].float()]) if self.last else torch.empty(2, T, dtype=torch.float32, device=self.device)
+            self.pp.broadcast_from_last(both)
+            if save_for_backward:
+                self._saved = {"kind": "lm", "states": states, "batch": batch}
+            return both[0], both[1]
         x, delta, state = self._layers_fwd(batch, self._recv_fwd(batch), save_for_backward)
         T = batch.input_ids.numel()
         if self.last:
@@ -157,6 +290,11 @@ class PipelineSchedule:
         assert s is not None and s.get("kind") == "lm", "call forward(save_for_backward=True) first"
         self._saved = None
         self.params.alloc_grads()
+        if self.vpp > 1:
+            if self.last:
+                s["states"][(0, self.vpp - 1)]["upstream"] = (g_logprob, g_entropy)
+            self._run_ticks([s["batch"]], virtual_schedule(self.stages, self.vpp, 1, backward_only=True), 1.0, states=s["states"])
+            return
         if self.last:
             dx = self._state_bwd(s, (g_logprob, g_entropy))
         else:
@@ -170,6 +308,14 @@ class PipelineSchedule:
         """Forward only: micro-batches stream through the stages (stage s works on micro-batch i while
         stage s + 1 works on i - 1); the last stage's per-token results reach every stage in one broadcast."""
         outs = []
+        if self.vpp > 1:
+            got: dict = {}
+            self._run_ticks(batches, virtual_schedule(self.stages, self.vpp, len(batches), train=False), temperature, save=False, collect=got)
+            sizes = [b.input_ids.numel() for b in batches]
+            both = torch.cat([torch.stack([got[i][0].float(), got[i][1].float()]) for i in range(len(batches))], dim=1) if self.last \
+                else torch.empty(2, sum(sizes), dtype=torch.float32, device=self.device)
+            self.pp.broadcast_from_last(both)
+            return [(part[0], part[1]) for part in both.split(sizes, dim=1)]
         for b in batches:
             x, delta, state = self._layers_fwd(b, self._recv_fwd(b), save=False)
             if self.last:
@@ -190,6 +336,10 @@ class PipelineSchedule:
         the last stage only, right after the forward of micro-batch i."""
         from collections import deque
         self.params.alloc_grads()
+        if self.vpp > 1:
+            left = self._run_ticks(batches, virtual_schedule(self.stages, self.vpp, len(batches)), temperature, loss_cb=loss_cb)
+            assert not left
+            return
         P, s, M = self.stages, self.stage, len(batches)
         warm = min(P - 1 - s, M)
         rest = M - warm
@@ -238,16 +388,21 @@ class PipelineSchedule:
 
 
 class PPDenseModel(PipelineSchedule, DenseModel):
-    def __init__(self, cfg: ModelConfig, pp: PipelineContext, device="cuda", dtype=torch.bfloat16):
+    def __init__(self, cfg: ModelConfig, pp: PipelineContext, device="cuda", dtype=torch.bfloat16, virtual: int = 1):
+        """``virtual``: model chunks per rank. With v > 1 rank r holds the layers of virtual stages r, P + r, 2 P + r, ...
+        of a pipeline of P v virtual stages and the schedule interleaves them (a smaller pipeline bubble for the same
+        number of micro-batches, more point-to-point traffic)."""
         assert cfg.num_experts == 0, "pipeline stages are built for dense models"
+        assert virtual == 1 or pp.world > 1, "virtual stages need at least two pipeline ranks"
         if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
             assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
-        assert pp.world <= cfg.num_hidden_layers
+        assert pp.world * virtual <= cfg.num_hidden_layers, "every (virtual) stage needs at least one layer"
         self.pp = pp
-        self.stage, self.stages = pp.rank, pp.world
-        params = FlatParams(cfg, torch.device(device), dtype, layout=stage_layout(cfg, self.stages, self.stage))
+        self.stage, self.stages, self.vpp = pp.rank, pp.world, int(virtual)
+        params = FlatParams(cfg, torch.device(device), dtype, layout=stage_layout(cfg, self.stages, self.stage, self.vpp))
         super().__init__(cfg, device, dtype, params=params)
-        self.layers = stage_layers(cfg.num_hidden_layers, self.stages, self.stage)
+        self.chunks = chunk_layers(cfg.num_hidden_layers, self.stages, self.stage, self.vpp)
+        self.layers = self.chunks[0]
 
     def load_full_state(self, full_views: dict) -> None:
         for name, dst in self.params.views.items():
@@ -278,21 +433,23 @@ class PPDenseModel(PipelineSchedule, DenseModel):
         return []
 
     # ------------------------------------------------------------------ the pieces of one micro-batch
-    def _layers_fwd(self, batch: PackedBatch, inp, save: bool):
-        """``inp`` = (x, delta) from the previous stage, None on the first. Returns (x, delta, state)."""
+    def _layers_fwd(self, batch: PackedBatch, inp, save: bool, chunk: int = 0):
+        """``inp`` = (x, delta) from the previous (virtual) stage, None on the very first. Returns (x, delta, state)."""
         from ..ops import activation as A
         c = self.cfg
         tables = self._tables(int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
-        if self.first:
+        very_first, very_last = self.first and chunk == 0, self.last and chunk == self.vpp - 1
+        if very_first:
             x, delta = A.embedding_fwd(batch.input_ids, self.weights["model.embed_tokens.weight"]), None
         else:
             x, delta = inp
         kept = []
-        for l in self.layers:
+        for l in self.chunks[chunk]:
             x, delta, saved = self.layer_fwd(l, x, delta, batch, tables, keep=save)
             if save:
                 kept.append(saved)
-        return x, delta, dict(batch=batch, tables=tables, layer_inputs=kept)
+        return x, delta, dict(batch=batch, tables=tables, layer_inputs=kept, layers=self.chunks[chunk], very_first=very_first,
+                              very_last=very_last)
 
     def _head_fwd(self, x, delta, batch: PackedBatch, temperature: float, state: dict):
         hf, rstd_f, xf = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], self.cfg.rms_norm_eps, delta=delta)
@@ -304,7 +461,7 @@ class PPDenseModel(PipelineSchedule, DenseModel):
         """``upstream``: (g_logprob, g_entropy) on the last stage, d(stream) from the next stage otherwise.
         Returns d(stream) for the previous stage (None on the first, which ends in the embedding)."""
         batch, tables = s["batch"], s["tables"]
-        if self.last:
+        if s["very_last"]:
             g_logprob, g_entropy = upstream
             g_lp = None if g_logprob is None else g_logprob.float().contiguous()
             g_ent = None if g_entropy is None else g_entropy.float().contiguous()
@@ -314,9 +471,9 @@ class PPDenseModel(PipelineSchedule, DenseModel):
         else:
             dx = upstream
         kept = s["layer_inputs"]
-        for l in reversed(self.layers):
+        for l in reversed(s["layers"]):
             dx = self.layer_bwd(l, kept.pop(), dx, batch, tables)
-        if self.first:
+        if s["very_first"]:
             self._embed_bwd(batch, dx)
             return None
         return dx

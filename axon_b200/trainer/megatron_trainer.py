@@ -38,6 +38,10 @@ class TrainerWorker(_Base):
             raise NotImplementedError("tensor and expert parallelism together divide the experts over the tensor-parallel group's own "
                                       f"ranks: set expert_model_parallel_size == tensor_model_parallel_size (got ep={self.ep_size}, tp={self.tp_size})")
         self.pp_size = int(_get(m, "pipeline_model_parallel_size", 1) or 1)
+        self.vpp_size = int(_get(m, "virtual_pipeline_model_parallel_size", 1) or 1)
+        if self.vpp_size > 1 and (self.pp_size < 2 or self.tp_size > 1):
+            raise NotImplementedError("virtual pipeline stages interleave the chunks of a plain pipeline (pipeline_model_parallel_size "
+                                      ">= 2, no tensor parallelism inside the stages)")
         if self.pp_size > 1 and self.ep_size > 1:
             raise NotImplementedError("pipeline parallelism together with expert parallelism is not available in this trainer "
                                       "yet; tensor x pipeline is, or use one of the two")
@@ -98,7 +102,8 @@ class TrainerWorker(_Base):
                 g = dist.new_group(ranks)
                 if self.rank in ranks:
                     ends_group = g
-        model = PPDenseModel(mcfg, PipelineContext(pp_group, self.device, ends_group), device=self.device, dtype=dtype)
+        model = PPDenseModel(mcfg, PipelineContext(pp_group, self.device, ends_group), device=self.device, dtype=dtype,
+                             virtual=self.vpp_size)
         ref = FlatParams(mcfg, "cpu", dtype)                 # full model on the host, cut down to this stage
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
             ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))

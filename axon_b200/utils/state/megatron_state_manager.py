@@ -83,7 +83,8 @@ class MegatronStateManager(FSDPStateManager):
         return getattr(self.model, "inner", self.model)
 
     def _layout_tag(self) -> str:
-        return f"tp{self.tp}_ep{self.ep}_pp{self.pp}_mp{self._mp_rank()}"
+        v = int(getattr(self._inner(), "vpp", 1) or 1)        # interleaved chunks change which layers a pipeline rank holds
+        return f"tp{self.tp}_ep{self.ep}_pp{self.pp}{f'v{v}' if v > 1 else ''}_mp{self._mp_rank()}"
 
     def _param_entries(self) -> dict:
         """key -> ShardedTensor for the parameters this rank holds, in full-model coordinates."""

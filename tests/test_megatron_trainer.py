@@ -8,10 +8,11 @@ from axon_b200.core.resource_pool import ResourcePool
 from axon_b200.protocol import DataProto
 
 
-def _cfg(tp, model="tiny-qwen3", ep=1, pp=1):
+def _cfg(tp, model="tiny-qwen3", ep=1, pp=1, vpp=1):
     return {"model_path": model, "force_cpu": True, "seed": 7, "max_token_len_per_gpu": 512,
             "optimizer_args": {"lr": 1e-3, "weight_decay": 0.0, "betas": [0.9, 0.95], "eps": 1e-8}, "grad_clip": 1.0,
-            "megatron": {"tensor_model_parallel_size": tp, "expert_model_parallel_size": ep, "pipeline_model_parallel_size": pp}, "recompute": "full"}
+            "megatron": {"tensor_model_parallel_size": tp, "expert_model_parallel_size": ep, "pipeline_model_parallel_size": pp,
+                         "virtual_pipeline_model_parallel_size": vpp}, "recompute": "full"}
 
 
 def _batch(n_rows=4, T=48, vocab=4096):
@@ -98,7 +99,7 @@ def test_tensor_and_expert_parallel_over_one_group_matches_data_parallel_trainer
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp", "tp-ep"])
+@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp", "tp-ep", "vpp"])
 def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
     run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
@@ -109,7 +110,9 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     from axon_b200.models.moe import build_model_for
     from axon_b200.utils.hf_model import load_hf_weights
     preset, vocab = ("tiny-moe", 2048) if kind.endswith("ep") else (("tiny-qwen2" if kind == "tp-bias" else "tiny-qwen3-untied"), 4096)
-    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind.endswith("ep") else 1, 2 if kind.endswith("pp") else 1)
+    if kind == "vpp":
+        preset = "tiny-qwen3-untied-5l"
+    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind.endswith("ep") else 1, 2 if kind.endswith("pp") else 1, 2 if kind == "vpp" else 1)
     world = 4 if kind == "tp-pp" else 2
     d = str(tmp_path / "ck")
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, world, vocab=vocab, save_dir=d)
@@ -136,6 +139,9 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     again = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, world, vocab=vocab, load_dir=d)
     torch.testing.assert_close(again[0], got[3], rtol=1e-5, atol=1e-5)
     if kind == "tp-pp":          # written by tp 2 x pp 2, resumed by two pipeline stages without tensor parallelism
+        other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, pp=2), 2, vocab=vocab, load_dir=d)
+        torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
+    if kind == "vpp":           # written by two ranks with two interleaved chunks each, resumed by two plain pipeline stages
         other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, pp=2), 2, vocab=vocab, load_dir=d)
         torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
     if kind == "tp-ep":         # written by one tp = ep = 2 group, resumed by two expert-parallel ranks without tensor parallelism
@@ -216,6 +222,57 @@ def test_pipeline_stages_share_a_tied_embedding(world, pp, model, cap):
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, world)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+def test_virtual_stage_schedule_runs_every_operation_once_in_dependency_order():
+    """The tick table of the interleaved schedule: every (micro-batch, virtual stage) forward and backward exactly once, a
+    forward only after the previous virtual stage's forward of an earlier tick, a backward only after the next virtual
+    stage's backward of an earlier tick; activation memory stays within the warm-up depth when the counts divide."""
+    from axon_b200.models.pp_dense import virtual_schedule
+    for P, v, M in [(2, 2, 4), (2, 2, 3), (3, 2, 6), (4, 3, 5), (4, 2, 8), (2, 3, 1), (4, 1, 8)]:
+        ticks = virtual_schedule(P, v, M)
+        K, seen = P * v, {}
+        for t, step in enumerate(ticks):
+            for r, op in enumerate(step):
+                if op is not None:
+                    key = (op[0], op[1], op[2] * P + r)
+                    assert key not in seen
+                    seen[key] = t
+        assert len(seen) == 2 * M * K
+        for (kind, m, k), t in seen.items():
+            if kind == "F" and k > 0:
+                assert seen[("F", m, k - 1)] < t
+            if kind == "B":
+                assert seen[("F", m, k)] < t and (k == K - 1 or seen[("B", m, k + 1)] < t)
+        if M % P == 0:
+            for r in range(P):
+                held = peak = 0
+                for step in ticks:
+                    if step[r] is not None:
+                        held += 1 if step[r][0] == "F" else -1
+                        peak = max(peak, held)
+                assert peak <= ((P - r - 1) * 2 + (v - 1) * P if v > 1 else P - 1 - r) + 1
+        fwd_only = virtual_schedule(P, v, M, train=False)
+        assert sum(op is not None for step in fwd_only for op in step) == M * K and all(op is None or op[0] == "F" for step in fwd_only for op in step)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world,pp,vpp,cap,model", [(2, 2, 2, 64, "tiny-qwen3-untied-5l"), (2, 2, 2, 512, "tiny-qwen3-5l"), (3, 3, 1, 64, "tiny-qwen3-untied-5l")])
+def test_interleaved_pipeline_chunks_match_single_process(world, pp, vpp, cap, model):
+    """Two ranks with two model chunks each (virtual stages 0, 2 on the first rank and 1, 3 on the second; with a token cap
+    of 64 every row is its own micro-batch, with 512 there is one): log-probs, loss, gradient norm and the update equal the
+    single-process trainer, also with the embedding tied between the first rank's first chunk and the last rank's last."""
+    import numpy as np
+    ref_cfg, got_cfg = _cfg(1, model), _cfg(1, model, pp=pp, vpp=vpp)
+    ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = cap
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, world)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(np.mean(got[1]["actor/loss"]), np.mean(ref[1]["actor/loss"]), rtol=1e-3, atol=1e-5)
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
