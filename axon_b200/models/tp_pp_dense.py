@@ -133,4 +133,45 @@ class TPPPDenseModel(PipelineSchedule, TPDenseModel):
         return dx
 
     def flops_per_token(self, seqlen: int) -> float:
-        return DenseModel.flops_per_token(self, seqlen) / (self.stages * self.tp.world)
+        from .moe import MoEModel
+        return (MoEModel if self.cfg.num_experts > 0 else DenseModel).flops_per_token(self, seqlen) / (self.stages * self.tp.world)
+
+
+class TPPPMoEModel(TPPPDenseModel):
+    """Sparse decoder with tensor + expert parallelism over one group INSIDE pipeline stages (``world = dp x pp x tp``,
+    ``ep == tp``): the stage model above with the MLP of ``tp_moe.TPMoEModel`` - every rank routes its own T / tp rows of
+    the stream through the expert-parallel dispatch of its stage's group. The expert choice of a micro-batch is kept
+    with its saved state, because several micro-batches are in flight between a forward and its backward.
+    (reference: the Qwen3-30B-A3B recipe trains with pipeline 2 x tensor 4 x expert 4,
+    recipes/math/train_polaris_qwen_30b_a3b.sh.)"""
+    SPARSE = True
+
+    def __init__(self, cfg: ModelConfig, tp: TPContext, ep, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16):
+        assert ep.world == tp.world and ep.rank == tp.rank, "experts are divided over the tensor-parallel group's own ranks"
+        assert cfg.num_experts % tp.world == 0, f"{cfg.num_experts} experts do not divide over {tp.world} ranks"
+        self.ep = ep if ep.world > 1 else None
+        self.ep_world = ep.world
+        super().__init__(cfg, tp, pp, block_group, device=device, dtype=dtype)
+        self.params.expert_offset = tp.rank * (cfg.num_experts // tp.world)
+        self.capture_routing, self.last_routing = False, None
+        self._ids: dict = {}
+
+    def _layers_fwd(self, batch: PackedBatch, inp, save: bool):
+        self._ids = {}
+        x, delta, state = super()._layers_fwd(batch, inp, save)
+        if save:
+            state["moe_ids"] = self._ids
+        return x, delta, state
+
+    def _state_bwd(self, s: dict, upstream):
+        self._ids = s["moe_ids"]
+        return super()._state_bwd(s, upstream)
+
+
+def _borrow_sparse_mlp() -> None:
+    from .tp_moe import TPMoEModel
+    for name in ("_route", "_experts", "_combine", "_moe_rebuild", "_moe_bwd", "_replay_local", "_mlp_fwd", "_mlp_bwd"):
+        setattr(TPPPMoEModel, name, getattr(TPMoEModel, name))
+
+
+_borrow_sparse_mlp()

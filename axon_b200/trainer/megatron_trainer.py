@@ -42,9 +42,9 @@ class TrainerWorker(_Base):
         if self.vpp_size > 1 and (self.pp_size < 2 or self.tp_size > 1):
             raise NotImplementedError("virtual pipeline stages interleave the chunks of a plain pipeline (pipeline_model_parallel_size "
                                       ">= 2, no tensor parallelism inside the stages)")
-        if self.pp_size > 1 and self.ep_size > 1:
-            raise NotImplementedError("pipeline parallelism together with expert parallelism is not available in this trainer "
-                                      "yet; tensor x pipeline is, or use one of the two")
+        if self.pp_size > 1 and self.ep_size > 1 and self.tp_size != self.ep_size:
+            raise NotImplementedError("pipeline stages of a sparse model divide their experts over the stage's tensor-parallel "
+                                      "group: set expert_model_parallel_size == tensor_model_parallel_size > 1")
         self.cp_size = int(_get(m, "context_parallel_size", 1) or 1)
         if self.cp_size > 1 and (self.tp_size > 1 or self.ep_size > 1 or self.pp_size > 1):
             raise NotImplementedError("context parallelism together with tensor / expert / pipeline parallelism is not available "
@@ -130,7 +130,7 @@ class TrainerWorker(_Base):
         from ..models.config import get_config
         from ..models.params import FlatParams
         from ..models.pp_dense import PipelineContext
-        from ..models.tp_pp_dense import TPPPDenseModel
+        from ..models.tp_pp_dense import TPPPDenseModel, TPPPMoEModel
         from ..parallel.tp import TPContext
         from ..utils.hf_model import has_hf_weights, iter_hf_weights
         mcfg = get_config(model_path)
@@ -157,10 +157,18 @@ class TrainerWorker(_Base):
         self.pg, self._mp_group = dp_group, block_group
         rows = int(_get(self.config, "max_token_len_per_gpu", 16384))
         rows = (rows // tp + 127) // 128 * 128 + 128
-        width = max(mcfg.qkv_size, 2 * mcfg.intermediate_size, mcfg.hidden_size)
+        sparse = mcfg.num_experts > 0
+        assert sparse == (self.ep_size > 1), "expert_model_parallel_size goes with a mixture-of-experts model (and only with one)"
+        width = max(mcfg.qkv_size, mcfg.hidden_size) if sparse else max(mcfg.qkv_size, 2 * mcfg.intermediate_size, mcfg.hidden_size)
         ctx = TPContext(tp_group, self.device, max_rows_per_rank=rows, max_width=width)
-        model = TPPPDenseModel(mcfg, ctx, PipelineContext(pp_group, self.device, ends_group=ends_group), block_group,
-                               device=self.device, dtype=dtype)
+        stage_ctx = PipelineContext(pp_group, self.device, ends_group=ends_group)
+        if sparse:
+            from ..parallel.ep import EPContext
+            ep = EPContext(tp_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, max_tokens=rows,
+                           top_k=mcfg.num_experts_per_tok)
+            model = TPPPMoEModel(mcfg, ctx, ep, stage_ctx, block_group, device=self.device, dtype=dtype)
+        else:
+            model = TPPPDenseModel(mcfg, ctx, stage_ctx, block_group, device=self.device, dtype=dtype)
         ref = FlatParams(mcfg, "cpu", dtype)
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
             ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))

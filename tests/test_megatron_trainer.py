@@ -99,7 +99,7 @@ def test_tensor_and_expert_parallel_over_one_group_matches_data_parallel_trainer
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp", "tp-ep", "vpp"])
+@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp", "tp-ep", "vpp", "tp-ep-pp"])
 def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
     run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
@@ -109,11 +109,11 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     from axon_b200.models.dense import PackedBatch
     from axon_b200.models.moe import build_model_for
     from axon_b200.utils.hf_model import load_hf_weights
-    preset, vocab = ("tiny-moe", 2048) if kind.endswith("ep") else (("tiny-qwen2" if kind == "tp-bias" else "tiny-qwen3-untied"), 4096)
+    preset, vocab = ("tiny-moe", 2048) if "ep" in kind else (("tiny-qwen2" if kind == "tp-bias" else "tiny-qwen3-untied"), 4096)
     if kind == "vpp":
         preset = "tiny-qwen3-untied-5l"
-    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if kind.endswith("ep") else 1, 2 if kind.endswith("pp") else 1, 2 if kind == "vpp" else 1)
-    world = 4 if kind == "tp-pp" else 2
+    cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if "ep" in kind else 1, 2 if kind.endswith("pp") else 1, 2 if kind == "vpp" else 1)
+    world = 4 if kind in ("tp-pp", "tp-ep-pp") else 2
     d = str(tmp_path / "ck")
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, world, vocab=vocab, save_dir=d)
     assert json.load(open(os.path.join(d, "model_parallel_config.json")))["world_size"] == world
@@ -143,6 +143,9 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
         torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
     if kind == "vpp":           # written by two ranks with two interleaved chunks each, resumed by two plain pipeline stages
         other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, pp=2), 2, vocab=vocab, load_dir=d)
+        torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
+    if kind == "tp-ep-pp":      # written by pipeline 2 x (tensor = expert = 2), resumed by one tensor + expert group without stages
+        other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, preset, 2), 2, vocab=vocab, load_dir=d)
         torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
     if kind == "tp-ep":         # written by one tp = ep = 2 group, resumed by two expert-parallel ranks without tensor parallelism
         other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, 2), 2, vocab=vocab, load_dir=d)
@@ -271,6 +274,23 @@ def test_interleaved_pipeline_chunks_match_single_process(world, pp, vpp, cap, m
     ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = cap
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, world)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(np.mean(got[1]["actor/loss"]), np.mean(ref[1]["actor/loss"]), rtol=1e-3, atol=1e-5)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+def test_sparse_model_with_tensor_and_expert_parallel_pipeline_stages_matches_single_process():
+    """world = 4 as pipeline 2 x (tensor = expert = 2), token cap 64 so that every row is its own micro-batch and several
+    are in flight: log-probs, loss, gradient norm and update equal the single-process trainer."""
+    import numpy as np
+    ref_cfg, got_cfg = _cfg(1, "tiny-moe"), _cfg(2, "tiny-moe", ep=2, pp=2)
+    ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = 64
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1, vocab=2048)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 4, vocab=2048)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(np.mean(got[1]["actor/loss"]), np.mean(ref[1]["actor/loss"]), rtol=1e-3, atol=1e-5)
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
