@@ -388,6 +388,8 @@ class PipelineSchedule:
 
 
 class PPDenseModel(PipelineSchedule, DenseModel):
+    serves_sampler = False       # a stage holds a slice of the layers: a colocated sampler keeps weights of its own
+
     def __init__(self, cfg: ModelConfig, pp: PipelineContext, device="cuda", dtype=torch.bfloat16, virtual: int = 1):
         """``virtual``: model chunks per rank. With v > 1 rank r holds the layers of virtual stages r, P + r, 2 P + r, ...
         of a pipeline of P v virtual stages and the schedule interleaves them (a smaller pipeline bubble for the same

@@ -3,7 +3,8 @@
 Every rank of the group sees the SAME tokens (the engines of the group run in lockstep) and holds
 
   * the query / key / value rows of its share of the heads and the matching columns of the attention
-    output projection, hence also only its heads' pages of the KV cache,
+    output projection, hence also only its heads' pages of the KV cache (a group with more ranks than the
+    model has key / value heads gives each rank ONE such head, which several ranks then hold alike),
   * dense MLP: its share of the gate / up rows and of the down-projection columns,
   * sparse MLP: ALL of the router and the whole weights of ``num_experts / world`` experts (expert
     parallelism inside the group): a rank runs the grouped GEMMs over the assignments to its own experts
@@ -63,9 +64,11 @@ class Shard:
 
 def local_config(cfg: ModelConfig, world: int) -> ModelConfig:
     """The configuration of one rank's part: heads (and the dense MLP width) divided by the group size."""
-    if cfg.num_attention_heads % world or cfg.num_key_value_heads % world:
-        raise ValueError(f"{cfg.num_attention_heads} query / {cfg.num_key_value_heads} key-value heads do not divide over {world} ranks")
-    kw = dict(num_attention_heads=cfg.num_attention_heads // world, num_key_value_heads=cfg.num_key_value_heads // world)
+    g = cfg.num_key_value_heads
+    if cfg.num_attention_heads % world or (g % world and world % g):
+        raise ValueError(f"{cfg.num_attention_heads} query / {g} key-value heads do not divide over {world} ranks")
+    # more ranks than key / value heads: world / g ranks hold the same head (and keep its cache pages) next to their own query heads
+    kw = dict(num_attention_heads=cfg.num_attention_heads // world, num_key_value_heads=max(1, g // world))
     if cfg.num_experts > 0:
         if cfg.num_experts % world:
             raise ValueError(f"{cfg.num_experts} experts do not divide over {world} ranks")
@@ -124,6 +127,9 @@ class _ShardedInference:
         if leaf == "q_proj":
             return rows(c.q_size)
         if leaf in ("k_proj", "v_proj"):
+            if c.num_key_value_heads % W:            # one head, shared with the neighbouring ranks
+                kv = r * c.num_key_value_heads // W
+                return t[kv * c.head_dim:(kv + 1) * c.head_dim]
             return rows(c.kv_size)
         if leaf == "o_proj":
             return t[:, r * c.q_size // W:(r + 1) * c.q_size // W]
@@ -216,6 +222,8 @@ def share_trainer_shards(trainer_model, shard: Shard):
     cfg = inner.cfg
     if cfg.num_experts > 0 and getattr(inner, "ep_world", 1) != shard.world:
         return None
+    if dict(inner.params.layout) != dict(local_layout(cfg, shard.world, shard.rank)):
+        return None                          # e.g. a pipeline stage: it holds a slice of the layers only
     cls = ShardedMoEModel if cfg.num_experts > 0 else ShardedDenseModel
     return cls(cfg, shard, device=inner.device, dtype=inner.dtype, share=inner.params)
 

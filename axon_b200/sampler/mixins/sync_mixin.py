@@ -33,6 +33,8 @@ class SyncSamplerMixin:
             if not self.shares_trainer_weights:
                 # a trainer with parameter shards gathers whole tensors layer by layer (every rank takes part)
                 gathered = getattr(peer.model, "full_named_tensors", None)
+                if gathered is None and getattr(getattr(peer, "state_manager", None), "mp_group", None) is not None:
+                    gathered = peer.state_manager.full_named_tensors       # tensor / expert / pipeline shards of a model-parallel trainer
                 self.server.update_weights(gathered() if gathered is not None else peer.model.params.views.items())
         self.server.wake_up()
 

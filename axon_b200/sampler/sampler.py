@@ -82,26 +82,29 @@ class SamplerWorker(Worker, DistProfilerExtension):
                 raise NotImplementedError("the sampler shards a model over tensor-parallel groups; pipeline stages are not built")
             lockstep = self._make_tp_groups()
         shared = None
+        dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         if trainer is not None and self.tp > 1:
             # colocated with a tensor- (and expert-) parallel trainer of the same group size: read its shards in place
             from ..models.tp_infer import Shard, share_trainer_shards
             shared = share_trainer_shards(trainer.model, Shard.create(self.tp_group, self.device))
-            if shared is None:
-                raise NotImplementedError("a colocated tensor-parallel sampler reads the shards of a trainer with the same "
-                                          "tensor-parallel (and expert-parallel) group size and a whole output head; other "
-                                          "layouts need the disaggregated deployment")
+        serves = trainer is not None and getattr(trainer.model, "serves_sampler", True) and hasattr(trainer.model, "prefill")
         if shared is not None:
             self.model = shared
             self.shares_trainer_weights = True
-        elif trainer is not None and not getattr(trainer.model, "serves_sampler", True):
-            # the trainer keeps parameter shards: this sampler holds a replica with whole parameters of its own and is
-            # refreshed from the trainer's gathered tensors at every switch to rollout
-            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
-            self.model = build_model(_get(cfg, "model_path"), device=self.device, dtype=dtype, seed=int(_get(cfg, "seed", 42)),
-                                     load_weights=False)
-        elif trainer is not None:
+        elif trainer is not None and self.tp == 1 and serves:
             self.model = trainer.model                  # zero-copy: generation reads the trainer's live parameters
             self.shares_trainer_weights = True
+        elif trainer is not None:
+            # the trainer's layout is not the sampler's (parameter shards, pipeline stages, another group size): this
+            # sampler holds weights of its own - whole, or its part of a tensor-parallel group - and is refreshed from the
+            # trainer's gathered tensors at every switch to rollout
+            if self.tp > 1:
+                from ..models.tp_infer import Shard, build_sharded_model
+                self.model = build_sharded_model(_get(cfg, "model_path"), Shard.create(self.tp_group, self.device), device=self.device,
+                                                 dtype=dtype, seed=int(_get(cfg, "seed", 42)), load_weights=False)
+            else:
+                self.model = build_model(_get(cfg, "model_path"), device=self.device, dtype=dtype, seed=int(_get(cfg, "seed", 42)),
+                                         load_weights=False)
         elif self.tp > 1:
             from ..models.tp_infer import Shard, build_sharded_model
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32

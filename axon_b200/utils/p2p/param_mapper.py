@@ -73,11 +73,17 @@ def shard_rows(cfg: ModelConfig, name: str, tp: int, tp_rank: int, ep: int = 1, 
         return [(0, shape[0], 0, shape[1] if len(shape) > 1 else 1)]
     if kind == "qkv":
         g = cfg.num_key_value_heads
-        assert g % tp == 0, f"kv heads {g} not divisible by tp {tp}"
-        rep = cfg.num_attention_heads // g
-        g0, g1 = tp_rank * g // tp, (tp_rank + 1) * g // tp
         qo, ko, vo = 0, cfg.q_size, cfg.q_size + cfg.kv_size
         H = shape[1] if len(shape) > 1 else 1
+        if g % tp != 0:
+            # more ranks than key / value heads (a sampler group): every rank takes its share of the query heads and
+            # the ONE key / value head they attend to, which tp / g ranks hold alike
+            assert tp % g == 0 and cfg.num_attention_heads % tp == 0, f"{cfg.num_attention_heads} query / {g} key-value heads do not divide over tp {tp}"
+            hq, kv = cfg.num_attention_heads // tp, tp_rank * g // tp
+            return [(qo + tp_rank * hq * D, qo + (tp_rank + 1) * hq * D, 0, H), (ko + kv * D, ko + (kv + 1) * D, 0, H),
+                    (vo + kv * D, vo + (kv + 1) * D, 0, H)]
+        rep = cfg.num_attention_heads // g
+        g0, g1 = tp_rank * g // tp, (tp_rank + 1) * g // tp
         return [(qo + g0 * rep * D, qo + g1 * rep * D, 0, H), (ko + g0 * D, ko + g1 * D, 0, H),
                 (vo + g0 * D, vo + g1 * D, 0, H)]
     if kind == "gate_up":

@@ -113,6 +113,50 @@ class MegatronStateManager(FSDPStateManager):
             out["model/" + name] = ShardedTensor("model/" + name, mine.detach(), g2, boxes, 0 if writer else 1)
         return out
 
+    def full_named_tensors(self):
+        """(name, whole tensor) of every parameter of the model, on EVERY rank of the model-parallel group, one tensor
+        at a time - for a colocated sampler that does not share the trainer's layout (the reference materialises every
+        parameter out of its sharded trainer the same way, axon/sampler/mixins/sync_mixin.py:86-168). Which rank holds
+        which box of which tensor is exchanged once; then every box travels in one broadcast from the rank that would
+        write it into a checkpoint. A collective: every rank of the group iterates it to the end."""
+        from ...models.params import param_layout
+        inner = self._inner()
+        full_layout = param_layout(inner.cfg)
+        mine = self._param_entries()
+        group = self.mp_group
+        world = dist.get_world_size(group) if group is not None else 1
+        if world == 1:
+            for name in full_layout:
+                yield name, inner.params[name].detach()
+            return
+        if getattr(self, "_gather_table", None) is None:
+            note = {k: (tuple(e.global_shape), [tuple(map(tuple, b)) for b in e.boxes], e.replica_id == 0) for k, e in mine.items()}
+            table = [None] * world
+            dist.all_gather_object(table, note, group=group)
+            self._gather_table = table
+        ranks = dist.get_process_group_ranks(group)
+        me = dist.get_rank(group)
+        dev, dtype = inner.params.flat.device, inner.params.flat.dtype
+        for name, shape in full_layout.items():
+            key = "model/" + name
+            full2d = None
+            for r, note in enumerate(self._gather_table):
+                ent = note.get(key)
+                if ent is None or not ent[2]:
+                    continue
+                g2, boxes, _ = ent
+                if full2d is None:
+                    full2d = torch.empty(g2, dtype=dtype, device=dev)
+                local = mine[key].data.detach().reshape(-1) if r == me else None
+                at = 0
+                for (r0, c0), (nr, nc) in boxes:
+                    piece = local[at:at + nr * nc].reshape(nr, nc).contiguous() if r == me else torch.empty(nr, nc, dtype=dtype, device=dev)
+                    dist.broadcast(piece, src=ranks[r], group=group)
+                    full2d[r0:r0 + nr, c0:c0 + nc] = piece
+                    at += nr * nc
+            assert full2d is not None, f"no rank of the group writes '{name}'"
+            yield name, full2d.reshape(shape)
+
     def _optim_entries(self) -> dict:
         eng = self.optimizer
         lo, hi = eng.shard

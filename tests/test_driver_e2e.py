@@ -92,13 +92,16 @@ def test_disaggregated_modes_push_weights(tmp_path, mode):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("model", ["dense", "moe"])
+@pytest.mark.parametrize("model", ["dense", "moe", "dense-4"])
 def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
     """1 trainer + a sampler group of 2 ranks that shard the model: the weight push re-slices every tensor for the
     group's ranks, the group generates in lockstep behind its first rank, and what it samples has the log-probs the
     trainer computes for the same tokens."""
     extra = ["num_gpus_per_node=3", "sampler_trainer_gpu_ratio=2", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
              "sampler.tensor_model_parallel_size=2"]
+    if model == "dense-4":      # a group of 4 for a model with 2 key / value heads: the push sends each head to the two ranks that hold it
+        extra = ["num_gpus_per_node=5", "sampler_trainer_gpu_ratio=4", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
+                 "sampler.tensor_model_parallel_size=4"]
     if model == "moe":          # the group also divides the experts; the routed experts it records are replayed by the trainer
         extra += ["model_path=tiny-moe", "strategy=megatron", "moe_replay=true"]
     drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
@@ -147,6 +150,36 @@ def test_colocated_tensor_parallel_trainer_and_sampler_share_their_shards(tmp_pa
     try:
         assert drv.global_steps == 3
         assert len(drv.server_addresses) == 1
+    finally:
+        drv.shutdown()
+    logs = _logged_steps(tmp_path)
+    assert [r["step"] for r in logs] == [1, 2]
+    for r in logs:
+        assert abs(r["data"]["batch/sampler_logprobs_diff_max"]) < 0.02 and abs(r["data"]["batch/sampler_logprobs_diff_min"]) < 0.02, r["data"]
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("layout", ["pp2-sampler-dp", "tp2-sampler-dp", "pp2-sampler-tp2", "pp2xtp2ep2-sampler-tp2"])
+def test_colocated_sampler_next_to_a_trainer_with_another_layout(tmp_path, layout):
+    """The trainer's shards are not what the sampler reads (pipeline stages; tensor-parallel shards next to whole-model
+    sampler replicas; a sparse pipeline x tensor x expert trainer next to tensor-parallel sampler groups): every sampler
+    keeps weights of its own, refreshed before each rollout from the tensors the trainer's model-parallel group gathers,
+    and what it samples has the trainer's log-probs."""
+    extra = ["total_training_steps=2", "save_steps=-1", "strategy=megatron", "model_path=tiny-qwen3-untied"]
+    if layout == "pp2-sampler-dp":
+        extra += ["num_gpus_per_node=2", "actor.megatron.pipeline_model_parallel_size=2"]
+    elif layout == "tp2-sampler-dp":
+        extra += ["num_gpus_per_node=2", "actor.megatron.tensor_model_parallel_size=2"]
+    elif layout == "pp2-sampler-tp2":
+        extra += ["num_gpus_per_node=2", "actor.megatron.pipeline_model_parallel_size=2", "sampler.tensor_model_parallel_size=2"]
+    else:
+        extra = [e for e in extra if not e.startswith("model_path")]
+        extra += ["num_gpus_per_node=4", "model_path=tiny-moe", "moe_replay=true", "actor.megatron.pipeline_model_parallel_size=2",
+                  "actor.megatron.tensor_model_parallel_size=2", "actor.megatron.expert_model_parallel_size=2",
+                  "sampler.tensor_model_parallel_size=2"]
+    drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
+    try:
+        assert drv.global_steps == 3
     finally:
         drv.shutdown()
     logs = _logged_steps(tmp_path)

@@ -39,10 +39,12 @@ def _check(res, presets, tol, exact):
 
 
 @pytest.mark.timeout(900)
-def test_tp2_sampler_group_matches_unsharded_model_cpu(tmp_path):
-    res = _run(tmp_path, 2, "cpu", 29671)
+@pytest.mark.parametrize("world", [2, 4])
+def test_sampler_group_matches_unsharded_model_cpu(tmp_path, world):
+    """Groups of 2 and of 4 ranks; the models have 2 key / value heads, so in the group of 4 two ranks each hold the same one."""
+    res = _run(tmp_path, world, "cpu", 29671 + world)
     _check(res, ("tiny-qwen3", "tiny-moe"), 1e-4, exact=True)
-    assert not res[0]["fused"]
+    assert not res[0]["fused"] and len(res) == world
 
 
 @pytest.mark.gpu
