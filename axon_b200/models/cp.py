@@ -35,10 +35,13 @@ class CPModelAdapter:
     on top of the context-parallel model: pads every sequence to a multiple of ``2 W`` tokens, hands the
     rank its zigzag chunks and puts the per-token results back into the order of the batch."""
 
-    def __init__(self, model: CPDenseModel):
+    def __init__(self, model, token_multiple: int = 128):
+        """``model``: a ``CPDenseModel`` - or the tensor-parallel adapter around a model whose attention is
+        context-parallel, with ``token_multiple = 128 tp`` so that the rank's tokens divide over its tensor-parallel group."""
         self.inner, self.cp = model, model.cp
         self.cfg, self.params, self.device, self.dtype = model.cfg, model.params, model.device, model.dtype
         self._maps = None
+        self._token_multiple = int(token_multiple)
 
     @property
     def recompute(self):
@@ -50,7 +53,7 @@ class CPModelAdapter:
 
     def _local(self, batch: PackedBatch) -> PackedBatch:
         W, me, dev = self.cp.world, self.cp.rank, batch.input_ids.device
-        new_cu, orig_pos, off = CP.pad_layout(batch.cu_seqlens, W)
+        new_cu, orig_pos, off = CP.pad_layout(batch.cu_seqlens, W, self._token_multiple)
         T_pad = int(new_cu[-1])
         idx_all = [CP.local_index(new_cu, r, W) for r in range(W)]
         orig_pos_d = orig_pos.to(dev)

@@ -172,8 +172,15 @@ class TPDenseModel:
         qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
         kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
         qkv_r = R.qknorm_rope_fwd(qkv, batch.position_ids, tables[0], tables[1], self.hq, self.hkv, c.head_dim, qw, kw, c.rms_norm_eps)
-        o, lse = AT.attn_fwd(qkv_r, batch.cu_seqlens, self.hq, self.hkv, c.head_dim, need_lse=need_lse)
+        o, lse = self._attn_kernel(qkv_r, batch, need_lse)
         return qkv_r, o, lse
+
+    def _attn_kernel(self, qkv_r, batch, need_lse):
+        return AT.attn_fwd(qkv_r, batch.cu_seqlens, self.hq, self.hkv, self.cfg.head_dim, need_lse=need_lse)
+
+    def _attn_bwd(self, do, qkv_r, o, lse, batch):
+        """Gradient of the attention kernel call of ``_attn`` w.r.t. the rotated q | k | v of this rank's heads."""
+        return AT.attn_bwd(do, qkv_r, o, lse, batch.cu_seqlens, self.hq, self.hkv, self.cfg.head_dim)
 
     def layer_fwd(self, l, x, delta, batch, tables):
         """x (+ delta): local rows [T/W, H] of the stream entering the layer -> (x1, mlp_out, xin), all local rows."""
@@ -229,7 +236,7 @@ class TPDenseModel:
         dao_full = tp.all_gather_rows(dx1)
         do = G.gemm_nn(dao_full, self._p(l, "self_attn.o_proj.weight"))
         G.gemm_tn(dao_full, o, out=self._g(l, "self_attn.o_proj.weight"), accumulate=True)
-        dqkv_r = AT.attn_bwd(do, qkv_r, o, lse, batch.cu_seqlens, self.hq, self.hkv, c.head_dim)
+        dqkv_r = self._attn_bwd(do, qkv_r, o, lse, batch)
         dqkv = R.qknorm_rope_bwd(dqkv_r, qkv, batch.position_ids, tables[0], tables[1], self.hq, self.hkv, c.head_dim, qw, kw,
                                  self._g(l, "self_attn.q_norm.weight") if c.qk_norm else None,
                                  self._g(l, "self_attn.k_norm.weight") if c.qk_norm else None, c.rms_norm_eps)

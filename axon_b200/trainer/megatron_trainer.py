@@ -46,9 +46,9 @@ class TrainerWorker(_Base):
             raise NotImplementedError("pipeline stages of a sparse model divide their experts over the stage's tensor-parallel "
                                       "group: set expert_model_parallel_size == tensor_model_parallel_size > 1")
         self.cp_size = int(_get(m, "context_parallel_size", 1) or 1)
-        if self.cp_size > 1 and (self.tp_size > 1 or self.ep_size > 1 or self.pp_size > 1):
-            raise NotImplementedError("context parallelism together with tensor / expert / pipeline parallelism is not available "
-                                      "in this trainer yet; use one model-parallel dimension")
+        if self.cp_size > 1 and (self.ep_size > 1 or self.pp_size > 1):
+            raise NotImplementedError("context parallelism combines with tensor parallelism (world = dp x cp x tp); together with "
+                                      "expert or pipeline parallelism it is not available in this trainer")
         self._pending_dispatch = True
         super().__init__(config, model=model, name=name, **kwargs)
         if self.cp_size > 1:
@@ -61,6 +61,8 @@ class TrainerWorker(_Base):
             self._pending_dispatch = False
             # ranks of one tensor- / pipeline- / context-parallel group (or tensor x pipeline block) see the same rows
             mp = self.tp_size * self.pp_size if (self.tp_size > 1 and self.pp_size > 1) else max(self.tp_size, self.pp_size, self.cp_size)
+            if self.tp_size > 1 and self.cp_size > 1:
+                mp = self.tp_size * self.cp_size          # a context-parallel rank is a whole tensor-parallel group
             assert self.world_size % mp == 0, f"world size {self.world_size} not divisible by the model-parallel size {mp}"
             return super()._register_dispatch_collect_info(mesh_name, self.rank // mp, self.rank % mp == 0)
         return super()._register_dispatch_collect_info(mesh_name, dp_rank, is_collect)
@@ -265,7 +267,50 @@ class TrainerWorker(_Base):
             inner.params.init_random(seed=seed)
         return CPModelAdapter(inner)
 
+    def _build_tensor_context_parallel(self, model_path, dtype, seed):
+        """world = dp x cp x tp, tensor-parallel ranks consecutive: the members with the same place in their tensor-parallel
+        group form the context-parallel groups (and, over all replicas, the optimizer's group)."""
+        import os
+        from ..models.config import get_config
+        from ..models.cp import CPModelAdapter
+        from ..models.params import FlatParams
+        from ..models.tp_cp_dense import TPCPDenseModel
+        from ..models.tp_dense import TPModelAdapter
+        from ..parallel.cp import ContextParallel
+        from ..parallel.tp import TPContext
+        from ..utils.hf_model import has_hf_weights, iter_hf_weights
+        mcfg = get_config(model_path)
+        tp, cp, world = self.tp_size, self.cp_size, self.world_size
+        assert mcfg.num_experts == 0 and not self.model_kind.value_head, "tensor x context parallelism is available on dense causal-LM models"
+        assert world % (tp * cp) == 0, f"world size {world} not divisible by cp x tp = {cp * tp}"
+        tp_group, dp_group = self._make_groups()
+        cp_group = None
+        for b in range(world // (tp * cp)):
+            for t in range(tp):
+                ranks = [b * tp * cp + c * tp + t for c in range(cp)]
+                g = dist.new_group(ranks)
+                if self.rank in ranks:
+                    cp_group = g
+        self.pg, self._mp_group = dp_group, tp_group
+        cap = int(_get(self.config, "max_token_len_per_gpu", 16384))
+        local = (cap + 127) // 128 * 128 + 1024 + 128 * tp           # the rank's tokens: padding per sequence and to 128 tp
+        rows = (local // tp + 127) // 128 * 128 + 128
+        ctx = TPContext(tp_group, self.device, max_rows_per_rank=rows, max_width=max(mcfg.qkv_size, 2 * mcfg.intermediate_size, mcfg.hidden_size))
+        ring = ContextParallel(cp_group, self.device, max_local_tokens=local, kv_width=2 * mcfg.kv_size // tp)
+        inner = TPCPDenseModel(mcfg, ctx, ring, device=self.device, dtype=dtype)
+        if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
+            ref = FlatParams(mcfg, "cpu", dtype)
+            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+            inner.load_full_state(ref.views)
+        else:
+            inner.init_random(seed=seed)
+        mid = TPModelAdapter(inner)
+        mid.cp = ring
+        return CPModelAdapter(mid, token_multiple=128 * tp)
+
     def _build(self, model_path, dtype, seed):
+        if self.cp_size > 1 and self.tp_size > 1:
+            return self._build_tensor_context_parallel(model_path, dtype, seed)
         if self.cp_size > 1:
             return self._build_context_parallel(model_path, dtype, seed)
         if self.pp_size > 1 and self.tp_size > 1:

@@ -8,11 +8,11 @@ from axon_b200.core.resource_pool import ResourcePool
 from axon_b200.protocol import DataProto
 
 
-def _cfg(tp, model="tiny-qwen3", ep=1, pp=1, vpp=1):
+def _cfg(tp, model="tiny-qwen3", ep=1, pp=1, vpp=1, cp=1):
     return {"model_path": model, "force_cpu": True, "seed": 7, "max_token_len_per_gpu": 512,
             "optimizer_args": {"lr": 1e-3, "weight_decay": 0.0, "betas": [0.9, 0.95], "eps": 1e-8}, "grad_clip": 1.0,
             "megatron": {"tensor_model_parallel_size": tp, "expert_model_parallel_size": ep, "pipeline_model_parallel_size": pp,
-                         "virtual_pipeline_model_parallel_size": vpp}, "recompute": "full"}
+                         "virtual_pipeline_model_parallel_size": vpp, "context_parallel_size": cp}, "recompute": "full"}
 
 
 def _batch(n_rows=4, T=48, vocab=4096):
@@ -293,6 +293,20 @@ def test_sparse_model_with_tensor_and_expert_parallel_pipeline_stages_matches_si
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 4, vocab=2048)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(np.mean(got[1]["actor/loss"]), np.mean(ref[1]["actor/loss"]), rtol=1e-3, atol=1e-5)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+def test_tensor_parallel_groups_as_context_parallel_ranks_match_single_process():
+    """world = 4 as context 2 x tensor 2: every sequence is cut into zigzag chunks over two tensor-parallel groups, whose
+    members exchange the K|V of their own heads; log-probs, gradient norm and update equal the single-process trainer."""
+    import numpy as np
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied"), 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, "tiny-qwen3-untied", cp=2), 4)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
