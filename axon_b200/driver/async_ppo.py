@@ -45,6 +45,11 @@ class AsyncPPO(PPODriverBase):
             raise ValueError("the asynchronous driver needs disaggregated pools (hybrid_engine=false)")
         self.channel = str(cfg_get(cfg, "sampler_channel", "nccl"))
         sp = int(cfg_get(cfg, "actor.fsdp.ulysses_sequence_parallel_size", 1))
+        if str(cfg_get(cfg, "strategy", "fsdp")) == "megatron":
+            # ranks of one tensor- / pipeline- / context-parallel block work on the same rows (expert-parallel ranks do not)
+            sp = 1
+            for key in ("tensor_model_parallel_size", "pipeline_model_parallel_size", "context_parallel_size"):
+                sp *= int(cfg_get(cfg, f"actor.megatron.{key}", 1) or 1)
         self.dp_rank_mapping = [r // sp for r in range(self.actor_wg.world_size)]
         plain = cfg.to_dict() if hasattr(cfg, "to_dict") else dict(cfg)
         addrs = self.server_addresses or [None] * self.sampler_wg.world_size

@@ -44,13 +44,17 @@ def _replicated(name: str, shard_head: bool) -> bool:
     return split_kind(name) in REPLICATED_KINDS
 
 
-def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = False, ep: int = 1) -> "OrderedDict[str, tuple[int, ...]]":
+def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = False, ep: int = 1, etp: int = 1) -> "OrderedDict[str, tuple[int, ...]]":
     """Parameter shapes of one rank, in the full model's parameter order. ``ep``: the stacked expert tensors keep
-    ``num_experts / ep`` whole experts (which ones does not change the shape)."""
+    ``num_experts / ep`` whole experts (which ones does not change the shape); ``etp``: every expert keeps 1 / etp of its
+    intermediate units (gate and up rows of ``w13``, columns of ``w2``)."""
     out: OrderedDict[str, tuple[int, ...]] = OrderedDict()
     for name, full in param_layout(cfg).items():
         if split_kind(name) == "expert":
-            out[name] = (full[0] // ep, *full[1:])
+            if name.endswith("w13_weight"):
+                out[name] = (full[0] // ep, full[1] // etp, full[2])
+            else:
+                out[name] = (full[0] // ep, full[1], full[2] // etp)
             continue
         if _replicated(name, shard_head) or tp == 1:
             out[name] = tuple(full)
@@ -62,10 +66,18 @@ def tp_param_layout(cfg: ModelConfig, tp: int, tp_rank: int, shard_head: bool = 
 
 
 def slice_full_param(cfg: ModelConfig, name: str, full: torch.Tensor, tp: int, tp_rank: int, shard_head: bool = False,
-                     ep: int = 1, ep_rank: int = 0) -> torch.Tensor:
+                     ep: int = 1, ep_rank: int = 0, etp: int = 1, etp_rank: int = 0) -> torch.Tensor:
     if split_kind(name) == "expert":
         n = full.shape[0] // ep
-        return full[ep_rank * n:(ep_rank + 1) * n]
+        part = full[ep_rank * n:(ep_rank + 1) * n]
+        if etp > 1 and name.endswith("w13_weight"):
+            F = part.shape[1] // 2
+            f0, f1 = etp_rank * F // etp, (etp_rank + 1) * F // etp
+            part = torch.cat([part[:, f0:f1], part[:, F + f0:F + f1]], dim=1)
+        elif etp > 1:
+            F = part.shape[2]
+            part = part[:, :, etp_rank * F // etp:(etp_rank + 1) * F // etp]
+        return part
     if _replicated(name, shard_head) or tp == 1:
         return full
     if full.dim() == 1:
@@ -94,6 +106,7 @@ def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, in
 class TPDenseModel:
     SPARSE = False           # the sparse subclass (tp_moe.TPMoEModel) replaces the MLP hooks
     ep_world = 1
+    etp_world = 1
 
     def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False,
                  holds=None):
@@ -105,7 +118,7 @@ class TPDenseModel:
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
         self.shard_head = bool(vocab_parallel_head) and not cfg.tie_word_embeddings and tp.world > 1
-        layout = tp_param_layout(cfg, tp.world, tp.rank, self.shard_head, ep=self.ep_world)
+        layout = tp_param_layout(cfg, tp.world, tp.rank, self.shard_head, ep=self.ep_world, etp=self.etp_world)
         if holds is not None:
             layout = OrderedDict((n, sh) for n, sh in layout.items() if holds(n))
         self.params = FlatParams(cfg, self.device, dtype, layout=layout)
@@ -120,7 +133,8 @@ class TPDenseModel:
     def load_full_state(self, full_views: dict) -> None:
         for name, dst in self.params.views.items():
             dst.copy_(slice_full_param(self.cfg, name, full_views[name], self.tp.world, self.tp.rank, self.shard_head,
-                                       ep=self.ep_world, ep_rank=self.tp.rank if self.ep_world > 1 else 0).to(dst.device).to(dst.dtype))
+                                       ep=self.ep_world, ep_rank=self.tp.rank if self.ep_world > 1 else 0,
+                                       etp=self.etp_world, etp_rank=self.tp.rank if self.etp_world > 1 else 0).to(dst.device).to(dst.dtype))
 
     def init_random(self, std: float = 0.02, seed: int = 0) -> None:
         """Same values as ``FlatParams.init_random`` of the unsharded model with this seed."""

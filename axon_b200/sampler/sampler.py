@@ -262,6 +262,13 @@ class SamplerWorker(Worker, DistProfilerExtension):
         return self.server.update_weights(named_tensors)
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def param_sums(self) -> dict:
+        """name -> (fp64 sum, shape, position-weighted fp64 sum) of every parameter tensor this rank holds (weight-sync
+        checks compare them; the weighted sum also notices rows that arrived in the wrong place)."""
+        from ..utils.state.utils import tensor_digest
+        return {n: tensor_digest(v) for n, v in self.model.params.views.items()}
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def params_checksum(self) -> float:
         return float(self.model.params.flat.double().sum().item())
 

@@ -394,6 +394,24 @@ class TrainerWorker(Worker, DistProfilerExtension):
                 "vocab_size": c.vocab_size, "world_size": self.world_size}
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def param_sums(self) -> dict:
+        """name -> (fp64 sum, shape, position-weighted fp64 sum) of every parameter tensor this rank holds (weight-sync
+        checks compare them; the weighted sum also notices rows that arrived in the wrong place)."""
+        from ..utils.state.utils import tensor_digest
+        return {n: tensor_digest(v) for n, v in self.model.params.views.items()}
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def full_param_sums(self) -> dict:
+        """``param_sums`` of the WHOLE tensors: a trainer with parameter shards or a model-parallel layout gathers them
+        (a collective over its ranks), so that the result compares with a sampler that holds whole tensors."""
+        from ..utils.state.utils import tensor_digest
+        gathered = getattr(self.model, "full_named_tensors", None)
+        if gathered is None and getattr(getattr(self, "state_manager", None), "mp_group", None) is not None:
+            gathered = self.state_manager.full_named_tensors
+        items = gathered() if gathered is not None else self.model.params.views.items()
+        return {n: tensor_digest(t) for n, t in items}
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def params_checksum(self) -> float:
         """Sum of all parameters in fp64 — replicas must agree; used by resume and sync tests."""
         return float(self.model.params.flat.double().sum().item())

@@ -34,6 +34,11 @@ class TrainerWorker(_Base):
         m = _get(config, "megatron", {}) or {}
         self.tp_size = int(_get(m, "tensor_model_parallel_size", 1) or 1)
         self.ep_size = int(_get(m, "expert_model_parallel_size", 1) or 1)
+        self.etp_size = int(_get(m, "expert_tensor_parallel_size", 1) or 1)
+        if self.etp_size > 1 and (self.etp_size != self.tp_size or self.ep_size > 1):
+            raise NotImplementedError("expert tensor parallelism divides every expert over the tensor-parallel group: set "
+                                      "expert_tensor_parallel_size == tensor_model_parallel_size with expert_model_parallel_size = 1 "
+                                      f"(got etp={self.etp_size}, tp={self.tp_size}, ep={self.ep_size})")
         if self.ep_size > 1 and self.tp_size > 1 and self.ep_size != self.tp_size:
             raise NotImplementedError("tensor and expert parallelism together divide the experts over the tensor-parallel group's own "
                                       f"ranks: set expert_model_parallel_size == tensor_model_parallel_size (got ep={self.ep_size}, tp={self.tp_size})")
@@ -51,9 +56,11 @@ class TrainerWorker(_Base):
                                       "expert or pipeline parallelism it is not available in this trainer")
         self._pending_dispatch = True
         super().__init__(config, model=model, name=name, **kwargs)
-        if self.cp_size > 1:
-            assert self.ulysses_sequence_parallel_size == 1, "choose one of Ulysses and context parallelism"
-            self.ulysses_sequence_parallel_size = self.cp_size      # the token caps count per group, as with Ulysses
+        rows_group = self.tp_size * self.pp_size * self.cp_size     # ranks that work on the same rows (expert-parallel ranks do not)
+        if rows_group > 1:
+            assert self.ulysses_sequence_parallel_size == 1, "choose one of Ulysses and the model-parallel layouts of this trainer"
+            # the token caps count per group and the asynchronous driver hands one shard of a batch to each group, as with Ulysses
+            self.ulysses_sequence_parallel_size = rows_group
 
     # the base class registers dp_rank = rank // sp; with TP the data shard is rank // tp
     def _register_dispatch_collect_info(self, mesh_name: str, dp_rank: int, is_collect: bool) -> None:
@@ -122,7 +129,7 @@ class TrainerWorker(_Base):
             return super()._make_state_manager()
         from ..utils.state.megatron_state_manager import MegatronStateManager
         return MegatronStateManager(self.model, self.engine, mp_group=getattr(self, "_mp_group", None), tp=self.tp_size, ep=self.ep_size,
-                                    pp=self.pp_size, dp_rank=self.rank // mp, tp_rank=(self.rank % self.tp_size) if both else None,
+                                    etp=self.etp_size, pp=self.pp_size, dp_rank=self.rank // mp, tp_rank=(self.rank % self.tp_size) if both else None,
                                     processing_class=self.tokenizer, rank=self.rank, world_size=self.world_size, process_group=self.pg)
 
     def _build_tensor_pipeline_parallel(self, model_path, dtype, seed):
@@ -220,15 +227,17 @@ class TrainerWorker(_Base):
         if self.model_kind.value_head:
             raise NotImplementedError("value-head models are not tensor-parallel yet; run the critic with tp=1")
         mcfg = get_config(model_path)
-        assert mcfg.num_experts > 0, f"expert_model_parallel_size={self.ep_size} needs a mixture-of-experts model"
+        assert mcfg.num_experts > 0, "expert_model_parallel_size / expert_tensor_parallel_size need a mixture-of-experts model"
         tp_group, dp_group = self._make_groups()
         self.pg = dp_group
         self._mp_group = tp_group
         rows = int(_get(self.config, "max_token_len_per_gpu", 16384))
         rows = (rows // self.tp_size + 127) // 128 * 128 + 128
         tp = TPContext(tp_group, self.device, max_rows_per_rank=rows, max_width=max(mcfg.qkv_size, mcfg.hidden_size))
-        ep = EPContext(tp_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, max_tokens=rows,
-                       top_k=mcfg.num_experts_per_tok)
+        ep = None                     # expert TENSOR parallelism: a slice of every expert per rank, no token exchange
+        if self.ep_size > 1:
+            ep = EPContext(tp_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, max_tokens=rows,
+                           top_k=mcfg.num_experts_per_tok)
         inner = TPMoEModel(mcfg, tp, ep, device=self.device, dtype=dtype)
         ref = FlatParams(mcfg, "cpu", dtype)                 # full model on the host, cut down to this rank's part
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
@@ -317,7 +326,7 @@ class TrainerWorker(_Base):
             return self._build_tensor_pipeline_parallel(model_path, dtype, seed)
         if self.pp_size > 1:
             return self._build_pipeline_parallel(model_path, dtype, seed)
-        if self.ep_size > 1 and self.tp_size > 1:
+        if (self.ep_size > 1 or self.etp_size > 1) and self.tp_size > 1 and self.pp_size == 1:
             return self._build_tensor_expert_parallel(model_path, dtype, seed)
         if self.ep_size > 1:
             return self._build_expert_parallel(model_path, dtype, seed)

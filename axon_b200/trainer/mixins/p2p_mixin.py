@@ -89,16 +89,22 @@ class TrainerP2PMixin:
     def get_parameter_mapping(self):
         # a tensor- or expert-parallel trainer describes its own slices; the routing table then matches
         # them against the sampler's slices box by box
-        tp, ep = getattr(self.model, "tp", None), getattr(self.model, "ep", None)
         inner = getattr(self.model, "inner", self.model)
+        tp, ep = getattr(self.model, "tp", None), getattr(self.model, "ep", None) or getattr(inner, "ep", None)
+        if getattr(inner, "etp_world", 1) > 1:
+            raise NotImplementedError("the trainer -> sampler push does not describe experts that are cut over the tensor-parallel "
+                                      "group (expert_tensor_parallel_size > 1); use the colocated deployment, which gathers whole tensors")
         rep = ()
         if tp is not None and tp.world > 1:
             from ...utils.p2p.param_mapper import split_kind
             rep = [n for n in inner.replicated_names() if split_kind(n) != "replicated"]
-        return get_param_metadata(self.model.cfg, rank=self.rank, dtype=self.model.params.dtype,
-                                  tp=tp.world if tp is not None else 1, tp_rank=tp.rank if tp is not None else 0,
-                                  ep=ep.world if ep is not None else 1, ep_rank=ep.rank if ep is not None else 0,
-                                  replicated_names=rep)
+        mapping = get_param_metadata(self.model.cfg, rank=self.rank, dtype=self.model.params.dtype,
+                                     tp=tp.world if tp is not None else 1, tp_rank=tp.rank if tp is not None else 0,
+                                     ep=ep.world if ep is not None else 1, ep_rank=ep.rank if ep is not None else 0,
+                                     replicated_names=rep)
+        held = self.model.params.layout                 # a pipeline stage holds (and sends) its own layers only
+        mapping.params = [m for m in mapping.params if m.param_name in held]
+        return mapping
 
     def _local_offsets(self) -> dict:
         return {n: o for n, (o, _) in self.model.params.offsets.items()}

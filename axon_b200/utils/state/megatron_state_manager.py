@@ -30,6 +30,33 @@ from .fsdp_state_manager import FSDPStateManager, _barrier
 from .utils import delete_oldest_checkpoints
 
 
+def view2d(name: str, shape) -> tuple[int, int]:
+    """The two-dimensional view in which a parameter's shards are boxes. Stacked down projections of the experts
+    ``[E, H, F]`` are seen as ``[E H, F]`` - whole experts AND column slices of every expert (expert tensor parallelism)
+    are then single boxes; everything else as ``[dim 0, the rest]``."""
+    if name.endswith("w2_weight") and len(shape) == 3:
+        return int(shape[0]) * int(shape[1]), int(shape[2])
+    return int(shape[0]), int(torch.Size(shape[1:]).numel()) if len(shape) > 1 else 1
+
+
+def expert_boxes(name: str, shape, ep: int, ep_rank: int, etp: int, etp_rank: int) -> list:
+    """Boxes ((row, column), (rows, columns)) in ``view2d`` coordinates of the part of a stacked expert tensor held by
+    one rank: experts ``[e0, e1)`` of the expert-parallel split, and of each of them the slice ``[f0, f1)`` of the
+    expert's intermediate units (rows of gate and of up in ``w13``, columns of ``w2``)."""
+    E = int(shape[0])
+    e0, e1 = ep_rank * E // ep, (ep_rank + 1) * E // ep
+    if name.endswith("w2_weight"):
+        H, F = int(shape[1]), int(shape[2])
+        f0, f1 = etp_rank * F // etp, (etp_rank + 1) * F // etp
+        return [((e0 * H, f0), ((e1 - e0) * H, f1 - f0))]
+    F2, H = int(shape[1]), int(shape[2])
+    if etp == 1:
+        return [((e0, 0), (e1 - e0, F2 * H))]
+    F = F2 // 2
+    f0, f1 = etp_rank * F // etp, (etp_rank + 1) * F // etp
+    return [b for e in range(e0, e1) for b in (((e, f0 * H), (1, (f1 - f0) * H)), ((e, (F + f0) * H), (1, (f1 - f0) * H)))]
+
+
 def gather_full_params(model, group, tp: int = 1, tp_rank: int = 0, ep: int = 1, ep_rank: int = 0, replicated_names=()):
     """Full (unsharded) tensors of every parameter on every rank of ``group`` (CPU, model dtype).
     ``model`` holds this rank's shards in ``model.params`` under the full model's names."""
@@ -61,11 +88,12 @@ def gather_full_params(model, group, tp: int = 1, tp_rank: int = 0, ep: int = 1,
 
 class MegatronStateManager(FSDPStateManager):
     def __init__(self, model, optimizer, mp_group=None, tp: int = 1, ep: int = 1, pp: int = 1, dp_rank: int = 0,
-                 tp_rank: int | None = None, **kw):
+                 tp_rank: int | None = None, etp: int = 1, **kw):
         """``tp_rank``: this rank's place in its tensor-parallel group when that differs from its place in ``mp_group``
         (tensor parallelism inside pipeline stages, where ``mp_group`` is the whole tensor x pipeline block)."""
         super().__init__(model, optimizer, **kw)
         self.mp_group, self.tp, self.ep, self.pp, self.dp_rank = mp_group, tp, ep, pp, dp_rank
+        self.etp = int(etp)           # ranks over which every expert's intermediate units are divided (the tensor-parallel group)
         self.tp_rank = tp_rank
         self._request: AsyncSaveRequest | None = None
 
@@ -84,7 +112,7 @@ class MegatronStateManager(FSDPStateManager):
 
     def _layout_tag(self) -> str:
         v = int(getattr(self._inner(), "vpp", 1) or 1)        # interleaved chunks change which layers a pipeline rank holds
-        return f"tp{self.tp}_ep{self.ep}_pp{self.pp}{f'v{v}' if v > 1 else ''}_mp{self._mp_rank()}"
+        return f"tp{self.tp}_ep{self.ep}{f'_etp{self.etp}' if self.etp > 1 else ''}_pp{self.pp}{f'v{v}' if v > 1 else ''}_mp{self._mp_rank()}"
 
     def _param_entries(self) -> dict:
         """key -> ShardedTensor for the parameters this rank holds, in full-model coordinates."""
@@ -97,9 +125,12 @@ class MegatronStateManager(FSDPStateManager):
         out = {}
         for name, mine in inner.params.views.items():
             shape = full[name]
-            g2 = (int(shape[0]), int(torch.Size(shape[1:]).numel()) if len(shape) > 1 else 1)
+            g2 = view2d(name, shape)
             zshard = getattr(self.model, "shard", None)
-            if tuple(mine.shape) == tuple(shape):          # whole tensor on this rank (a stage's own, or replicated in its group)
+            if name.endswith(("w13_weight", "w2_weight")) and len(shape) == 3:       # stacked experts: whole ones and / or slices of each
+                boxes = expert_boxes(name, shape, self.ep, r if self.ep > 1 else 0, self.etp, r if self.etp > 1 else 0)
+                writer = self.dp_rank == 0 and (self.ep > 1 or self.etp > 1 or ((self.pp > 1 and self.tp == 1) or r == 0))
+            elif tuple(mine.shape) == tuple(shape):          # whole tensor on this rank (a stage's own, or replicated in its group)
                 boxes = [((0, 0), g2)]
                 one_of_group = (self.pp > 1 and self.tp == 1) or (r == 0 and (zshard is None or zshard.rank == 0))
                 writer = self.dp_rank == 0 and one_of_group
@@ -201,7 +232,7 @@ class MegatronStateManager(FSDPStateManager):
             self._request = req            # finalized by wait(): before the next save, a load, or shutdown
         elif max_ckpt_to_keep and max_ckpt_to_keep > 0 and self.rank == 0:
             delete_oldest_checkpoints(os.path.dirname(os.path.dirname(os.path.abspath(local_path))), max_ckpt_to_keep)
-        if want_hf and self.tp > 1 and self.pp > 1:
+        if want_hf and ((self.tp > 1 and self.pp > 1) or self.etp > 1):
             # shards of two kinds: assemble the export from the array store just written (any layout reads back whole)
             req.finalize()
             self._request = None
@@ -210,8 +241,7 @@ class MegatronStateManager(FSDPStateManager):
                 from ..hf_model import save_hf_model
                 inner = self._inner()
                 host = FlatParams(inner.cfg, "cpu", inner.params.flat.dtype)
-                load_sharded({"model/" + n: ShardedTensor("model/" + n, v, (int(v.shape[0]), int(v[0].numel()) if v.dim() > 1 else 1),
-                                                          [((0, 0), (int(v.shape[0]), int(v[0].numel()) if v.dim() > 1 else 1))])
+                load_sharded({"model/" + n: ShardedTensor("model/" + n, v, view2d(n, v.shape), [((0, 0), view2d(n, v.shape))])
                               for n, v in host.views.items()}, os.path.join(local_path, "dist_ckpt"), group=False)
                 save_hf_model(host, os.path.join(local_path, "huggingface"), cfg=inner.cfg, tokenizer=self.processing_class)
             _barrier(None)

@@ -83,3 +83,12 @@ def find_latest_ckpt_path(path: str | None) -> str | None:
             return cand
         logger.warning("checkpoint %s is incomplete, skipping", cand)
     return None
+
+
+def tensor_digest(t) -> tuple:
+    """(fp64 sum, shape, position-weighted fp64 sum) of a tensor: equal tensors give equal digests, and rows that were
+    swapped or shifted change the third entry."""
+    import torch
+    flat = t.detach().double().reshape(-1).cpu()
+    w = 1.0 + (torch.arange(flat.numel(), dtype=torch.float64) % 1009) / 1009.0
+    return float(flat.sum().item()), tuple(t.shape), float((flat * w).sum().item())

@@ -9,7 +9,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def main(out_path: str, device_kind: str) -> None:
+def main(out_path: str, device_kind: str, how: str = "ep") -> None:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     if device_kind == "cuda":
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -44,8 +44,9 @@ def main(out_path: str, device_kind: str) -> None:
     full.capture_routing = False
     full.backward(glp, gent)
     tp = TPContext(dist.group.WORLD, dev, max_rows_per_rank=T // world, max_width=max(cfg.qkv_size, cfg.hidden_size))
+    # "ep": whole experts per rank, tokens travel; "etp": a slice of every expert per rank, all ranks see all tokens
     ep = EPContext(dist.group.WORLD, dev, cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size, max_tokens=T // world,
-                   top_k=cfg.num_experts_per_tok)
+                   top_k=cfg.num_experts_per_tok) if how == "ep" else None
     m = TPMoEModel(cfg, tp, ep, device=dev, dtype=dtype)
     m.load_full_state(full.params.views)
     m.params.alloc_grads()
@@ -58,10 +59,11 @@ def main(out_path: str, device_kind: str) -> None:
         torch.cuda.synchronize()
         from axon_b200.ops import _common as C
         C.check_status()
-    res = {"fused": tp.fused, "ep_fused": ep.fused, "lp_err": float((lp.float() - lp_f[sl].float()).abs().max()),
+    res = {"fused": tp.fused, "ep_fused": ep.fused if ep is not None else None, "lp_err": float((lp.float() - lp_f[sl].float()).abs().max()),
            "ent_err": float((ent.float() - ent_f[sl].float()).abs().max()), "grad_rel": {}}
     for name, gsh in m.params.grads.items():
-        ref = slice_full_param(cfg, name, full.params.grads[name], world, rank, False, ep=world, ep_rank=rank).float()
+        kw = dict(ep=world, ep_rank=rank) if how == "ep" else dict(etp=world, etp_rank=rank)
+        ref = slice_full_param(cfg, name, full.params.grads[name], world, rank, False, **kw).float()
         res["grad_rel"][name] = float((gsh.float() - ref).norm() / (ref.norm() + 1e-12))
     ss = m.grad_sumsq().reshape(1).to(dev)
     dist.all_reduce(ss)
@@ -80,4 +82,4 @@ def main(out_path: str, device_kind: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1], sys.argv[2])
+    main(sys.argv[1], sys.argv[2], sys.argv[3] if len(sys.argv) > 3 else "ep")

@@ -92,7 +92,7 @@ def test_disaggregated_modes_push_weights(tmp_path, mode):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("model", ["dense", "moe", "dense-4"])
+@pytest.mark.parametrize("model", ["dense", "moe", "dense-4", "moe-tp-ep-trainer", "dense-tp-trainer", "dense-pp-trainer"])
 def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
     """1 trainer + a sampler group of 2 ranks that shard the model: the weight push re-slices every tensor for the
     group's ranks, the group generates in lockstep behind its first rank, and what it samples has the log-probs the
@@ -102,7 +102,16 @@ def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
     if model == "dense-4":      # a group of 4 for a model with 2 key / value heads: the push sends each head to the two ranks that hold it
         extra = ["num_gpus_per_node=5", "sampler_trainer_gpu_ratio=4", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
                  "sampler.tensor_model_parallel_size=4"]
-    if model == "moe":          # the group also divides the experts; the routed experts it records are replayed by the trainer
+    if model == "moe-tp-ep-trainer":    # two trainer ranks as one tensor + expert parallel group push to one whole-model sampler
+        extra = ["num_gpus_per_node=3", "sampler_trainer_gpu_ratio=0.5", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
+                 "actor.megatron.tensor_model_parallel_size=2", "actor.megatron.expert_model_parallel_size=2"]
+    if model in ("dense-tp-trainer", "dense-pp-trainer"):
+        # two trainer ranks as one tensor-parallel group / as two pipeline stages feed one whole-model sampler; the asynchronous
+        # driver hands the SAME rows to the ranks of such a group and each stage pushes its own layers
+        dim = "tensor_model_parallel_size" if model == "dense-tp-trainer" else "pipeline_model_parallel_size"
+        extra = ["num_gpus_per_node=3", "sampler_trainer_gpu_ratio=0.5", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
+                 "strategy=megatron", f"actor.megatron.{dim}=2"]
+    if model.startswith("moe"):  # the group also divides the experts; the routed experts it records are replayed by the trainer
         extra += ["model_path=tiny-moe", "strategy=megatron", "moe_replay=true"]
     drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
     try:

@@ -8,11 +8,12 @@ from axon_b200.core.resource_pool import ResourcePool
 from axon_b200.protocol import DataProto
 
 
-def _cfg(tp, model="tiny-qwen3", ep=1, pp=1, vpp=1, cp=1):
+def _cfg(tp, model="tiny-qwen3", ep=1, pp=1, vpp=1, cp=1, etp=1):
     return {"model_path": model, "force_cpu": True, "seed": 7, "max_token_len_per_gpu": 512,
             "optimizer_args": {"lr": 1e-3, "weight_decay": 0.0, "betas": [0.9, 0.95], "eps": 1e-8}, "grad_clip": 1.0,
             "megatron": {"tensor_model_parallel_size": tp, "expert_model_parallel_size": ep, "pipeline_model_parallel_size": pp,
-                         "virtual_pipeline_model_parallel_size": vpp, "context_parallel_size": cp}, "recompute": "full"}
+                         "virtual_pipeline_model_parallel_size": vpp, "context_parallel_size": cp,
+                         "expert_tensor_parallel_size": etp}, "recompute": "full"}
 
 
 def _batch(n_rows=4, T=48, vocab=4096):
@@ -99,7 +100,7 @@ def test_tensor_and_expert_parallel_over_one_group_matches_data_parallel_trainer
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp", "tp-ep", "vpp", "tp-ep-pp"])
+@pytest.mark.parametrize("kind", ["tp", "tp-bias", "ep", "pp", "tp-pp", "tp-ep", "vpp", "tp-ep-pp", "tp-etp"])
 def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     """The HF export of a tp=2 / ep=2 run holds the full tensors: an unsharded model loaded from it gives the
     run's own post-update log-probs; the sharded files and the layout note are there for resuming."""
@@ -113,6 +114,9 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     if kind == "vpp":
         preset = "tiny-qwen3-untied-5l"
     cfg = _cfg(2 if kind.startswith("tp") else 1, preset, 2 if "ep" in kind else 1, 2 if kind.endswith("pp") else 1, 2 if kind == "vpp" else 1)
+    if kind == "tp-etp":
+        preset, vocab = "tiny-moe", 2048
+        cfg = _cfg(2, preset, etp=2)
     world = 4 if kind in ("tp-pp", "tp-ep-pp") else 2
     d = str(tmp_path / "ck")
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", cfg, world, vocab=vocab, save_dir=d)
@@ -124,8 +128,8 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
     meta = read_metadata(dist_dir)
     assert any(k.startswith("optimizer/") for k in meta["tensors"]) and "extra/common" in meta["objects"]
     host = FlatParams(get_config(preset), "cpu", torch.float32)
-    load_sharded({"model/" + n: ShardedTensor("model/" + n, v, (v.shape[0], v[0].numel() if v.dim() > 1 else 1),
-                                              [((0, 0), (v.shape[0], v[0].numel() if v.dim() > 1 else 1))]) for n, v in host.views.items()}, dist_dir)
+    from axon_b200.utils.state.megatron_state_manager import view2d       # the 2-D view in which shards are boxes
+    load_sharded({"model/" + n: ShardedTensor("model/" + n, v, view2d(n, v.shape), [((0, 0), view2d(n, v.shape))]) for n, v in host.views.items()}, dist_dir)
     m = build_model_for(get_config(preset), device="cpu", dtype=torch.float32)
     load_hf_weights(m, os.path.join(d, "huggingface"))
     for n, v in host.views.items():              # ... which an unsharded reader assembles to the exported tensors
@@ -145,6 +149,9 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
         other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, preset, pp=2), 2, vocab=vocab, load_dir=d)
         torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
     if kind == "tp-ep-pp":      # written by pipeline 2 x (tensor = expert = 2), resumed by one tensor + expert group without stages
+        other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, preset, 2), 2, vocab=vocab, load_dir=d)
+        torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
+    if kind == "tp-etp":        # every expert cut over two ranks when written; resumed by ranks that hold whole experts
         other = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, preset, 2), 2, vocab=vocab, load_dir=d)
         torch.testing.assert_close(other[0], got[3], rtol=1e-3, atol=1e-3)
     if kind == "tp-ep":         # written by one tp = ep = 2 group, resumed by two expert-parallel ranks without tensor parallelism
@@ -306,6 +313,21 @@ def test_tensor_parallel_groups_as_context_parallel_ranks_match_single_process()
     import numpy as np
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied"), 1)
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, "tiny-qwen3-untied", cp=2), 4)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_tensor_parallel_trainer_matches_data_parallel_trainer(world):
+    """tp = etp = 2 (x dp = 1 or 2): every rank holds a slice of the intermediate units of EVERY expert and works on all the
+    group's tokens; partial expert outputs are reduce-scattered back to the rows' owners."""
+    import numpy as np
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-moe"), 1, vocab=2048)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2, "tiny-moe", etp=2), world, vocab=2048)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
