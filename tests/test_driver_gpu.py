@@ -96,3 +96,24 @@ def test_disaggregated_driver_pushes_weights_with_the_peer_store_kernel(tmp_path
     logs = _logged_steps(tmp_path)
     assert [r["step"] for r in logs] == [1, 2]
     assert logs[0]["data"]["sync/peer_store_kernel"] == 1.0 and "timing_s/sync_weights" in logs[0]["data"]
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(900)
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_colocated_driver_on_two_gpus_as_worker_processes(tmp_path):
+    """Two worker processes, each holding the trainer AND the sampler role of its GPU: the optimizer state is sharded over
+    the two ranks, every sampler reads its trainer's parameter buffer in place, and the replicas stay equal."""
+    from axon_b200.driver.train_agent_ppo import train_agent
+    extra = ["num_gpus_per_node=2", "total_training_steps=2", "save_steps=-1"]
+    drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
+    try:
+        assert drv.global_steps == 3
+        sums = drv.actor_wg.params_checksum()
+        assert len(sums) == 2 and sums[0] == sums[1], sums
+        assert len(drv.server_addresses) == 2
+    finally:
+        drv.shutdown()
+    logs = _logged_steps(tmp_path)
+    assert [r["step"] for r in logs] == [1, 2]
+    assert logs[0]["data"]["batch/sampler_logprobs_diff_mean"] < 5e-3 and "actor/grad_norm" in logs[1]["data"]
