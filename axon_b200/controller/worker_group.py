@@ -149,8 +149,13 @@ class WorkerGroup:
             fns = mode if isinstance(mode, dict) else get_predefined_dispatch_fn(mode)
             execute_fn = getattr(self, get_predefined_execute_fn(info["execute_mode"])["execute_fn_name"])
             fn = generator(self, name, fns["dispatch_fn"], fns["collect_fn"], execute_fn, info["blocking"])
-            setattr(self, prefix + name, fn)
-            bound.append(prefix + name)
+            bind_as = prefix + name
+            if hasattr(type(self), bind_as):
+                # the group has a method of its own under this name (``shutdown`` tears the worker processes down): the
+                # workers' method of the same name stays reachable as ``worker_<name>`` and never shadows the group's
+                bind_as = "worker_" + bind_as
+            setattr(self, bind_as, fn)
+            bound.append(bind_as)
         return bound
 
     def _query_dispatch_info(self, mesh_name: str) -> list[int]:
@@ -389,7 +394,15 @@ class LocalWorkerGroup(WorkerGroup):
         return [self._call(r, method_name, args, kwargs) for r in (ranks if ranks is not None else range(self.world_size))]
 
     def shutdown(self) -> None:
+        """Tell the workers to wind down (their own ``shutdown``, where they have one: servers, threads), then end the
+        worker processes."""
         self.stop_worker_aliveness_check()
+        stop = getattr(self, "worker_shutdown", None)
+        if stop is not None and self._workers:
+            try:
+                stop()
+            except Exception:  # noqa: BLE001 - a worker that is already gone cannot wind down
+                pass
         if self.backend == "process":
             for w in self._workers:
                 w.shutdown()

@@ -56,11 +56,12 @@ class TrainerWorker(_Base):
                                       "expert or pipeline parallelism it is not available in this trainer")
         self._pending_dispatch = True
         super().__init__(config, model=model, name=name, **kwargs)
-        rows_group = self.tp_size * self.pp_size * self.cp_size     # ranks that work on the same rows (expert-parallel ranks do not)
-        if rows_group > 1:
-            assert self.ulysses_sequence_parallel_size == 1, "choose one of Ulysses and the model-parallel layouts of this trainer"
-            # the token caps count per group and the asynchronous driver hands one shard of a batch to each group, as with Ulysses
-            self.ulysses_sequence_parallel_size = rows_group
+        # ranks that work on the same rows (expert-parallel ranks do not): the asynchronous driver hands one shard of a batch to each such block
+        self.rows_group_size = self.tp_size * self.pp_size * self.cp_size
+        if self.cp_size > 1:
+            assert self.ulysses_sequence_parallel_size == 1, "choose one of Ulysses and context parallelism"
+            self.ulysses_sequence_parallel_size = self.cp_size      # the token caps count per group, as with Ulysses
+            self.rows_group_size = self.tp_size * self.pp_size      # ... and the row shards per (context-parallel x this) block
 
     # the base class registers dp_rank = rank // sp; with TP the data shard is rank // tp
     def _register_dispatch_collect_info(self, mesh_name: str, dp_rank: int, is_collect: bool) -> None:

@@ -22,12 +22,17 @@ from ...utils.metrics import append_to_dict, compute_data_metrics, compute_timin
 class AsyncTrainerMixin:
     active_batch: DataProto | None = None
 
+    def _rows_group(self) -> int:
+        """Ranks that work on the same rows of a batch: a sequence-parallel group, times the tensor- / pipeline- / context-
+        parallel block of a model-parallel trainer (expert-parallel ranks hold different rows)."""
+        return int(self.ulysses_sequence_parallel_size) * int(getattr(self, "rows_group_size", 1))
+
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
     def set_batch(self, batch: DataProto) -> bool:
         """Whole batch from the driver (host-channel mode): every rank keeps its own shard."""
-        dp = self.world_size // self.ulysses_sequence_parallel_size
+        dp = self.world_size // self._rows_group()
         shards = batch.chunk(dp)
-        self.active_batch = shards[self.rank // self.ulysses_sequence_parallel_size]
+        self.active_batch = shards[self.rank // self._rows_group()]
         self.active_batch.meta_info = dict(batch.meta_info)
         return True
 
@@ -75,7 +80,9 @@ class AsyncTrainerMixin:
             return value
         t = torch.tensor([value], dtype=torch.int64, device=self.device)
         dist.all_reduce(t, group=self.pg)
-        return int(t.item()) // self.ulysses_sequence_parallel_size
+        # inside the optimizer's group only sequence- / context-parallel peers count the same rows again (the ranks of a
+        # tensor- or pipeline-parallel block are not in it)
+        return int(t.item()) // int(self.ulysses_sequence_parallel_size)
 
     def _global_max(self, value: int) -> int:
         if self.world_size == 1:
@@ -91,7 +98,7 @@ class AsyncTrainerMixin:
         self.load_model(include_model=True, include_optimizer=True)
         try:
             data = self.active_batch
-            dp = self.world_size // self.ulysses_sequence_parallel_size
+            dp = self.world_size // self._rows_group()
             groups = _program_groups(data.non_tensor_batch["program_uids"])
             uids = list(groups)
             local_mbs = max(1, (mini_batch_size // dp) if mini_batch_size and mini_batch_size > 0 else len(uids))
