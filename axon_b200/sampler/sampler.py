@@ -47,6 +47,14 @@ class SamplerWorker(Worker, DistProfilerExtension):
         else:
             self.device = torch.device("cpu")
         self.tp = int(_get(scfg, "tensor_model_parallel_size", 1))
+        ep = int(_get(scfg, "expert_parallel_size", 1) or 1)
+        if ep > 1 and self.tp == 1:
+            # experts divided over a group of ranks: here that is the tensor-parallel group (which also divides the heads);
+            # a layout with whole attention replicas around shared experts is not built
+            self.tp = ep
+        elif ep > 1 and ep != self.tp:
+            raise NotImplementedError(f"sampler.expert_parallel_size ({ep}) must equal sampler.tensor_model_parallel_size ({self.tp}): "
+                                      "a sampler group divides its experts over its own ranks")
         self.pp = int(_get(scfg, "pipeline_model_parallel_size", 1))
         assert self.world_size % (self.tp * self.pp) == 0
         self.dp_rank = self.rank // (self.tp * self.pp)

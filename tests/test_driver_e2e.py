@@ -111,6 +111,8 @@ def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
         dim = "tensor_model_parallel_size" if model == "dense-tp-trainer" else "pipeline_model_parallel_size"
         extra = ["num_gpus_per_node=3", "sampler_trainer_gpu_ratio=0.5", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
                  "strategy=megatron", f"actor.megatron.{dim}=2"]
+    if model == "moe":          # asked for as an expert-parallel size alone: the same group of two
+        extra = [e for e in extra if not e.startswith("sampler.tensor_model_parallel_size")] + ["sampler.expert_parallel_size=2"]
     if model.startswith("moe"):  # the group also divides the experts; the routed experts it records are replayed by the trainer
         extra += ["model_path=tiny-moe", "strategy=megatron", "moe_replay=true"]
     drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
