@@ -265,9 +265,8 @@ class TPDenseModel:
         n = T // self.tp.world
         return slice(self.tp.rank * n, (self.tp.rank + 1) * n)
 
-    def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
-        """``batch`` is the full packed batch, its length a multiple of 128 * W (``pad_packed_batch``).
-        Returns (log-prob, entropy) of THIS rank's tokens [T/W]."""
+    def _trunk_fwd(self, batch: PackedBatch, save: bool):
+        """Embedding, layers and final norm on THIS rank's rows -> (hf [T/W, H], state)."""
         c = self.cfg
         self.tp.begin_pass()
         T = batch.input_ids.numel()
@@ -278,12 +277,25 @@ class TPDenseModel:
         delta, inputs = None, []
         for l in range(c.num_hidden_layers):
             x, delta, xin = self.layer_fwd(l, x, delta, batch, tables)
-            if save_for_backward:
+            if save:
                 inputs.append(xin)
         hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
+        return hf, dict(batch=batch, tables=tables, inputs=inputs, xf=xf, hf=hf, rstd_f=rstd_f, sl=sl)
+
+    def _trunk_bwd(self, s: dict, dhf) -> None:
+        c = self.cfg
+        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"])
+        for l in reversed(range(c.num_hidden_layers)):
+            dx = self.layer_bwd(l, s["inputs"].pop(), dx, s["batch"], s["tables"])
+        A.embedding_bwd(s["batch"].input_ids[s["sl"]].contiguous(), dx, self.params.grads["model.embed_tokens.weight"])
+
+    def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
+        """``batch`` is the full packed batch, its length a multiple of 128 * W (``pad_packed_batch``).
+        Returns (log-prob, entropy) of THIS rank's tokens [T/W]."""
+        hf, state = self._trunk_fwd(batch, save_for_backward)
         # the parameter gradient of a qk-norm weight is partial per rank (local heads); norms over the
         # hidden size see local tokens only — both are summed by sync_replicated_grads
-        labels = batch.labels[sl].contiguous()
+        labels = batch.labels[state["sl"]].contiguous()
         if self.vp_head is not None:
             lp, ent, head_ctx = self.vp_head.forward(hf, self.head_weight(), batch.labels, temperature)
             lse = None
@@ -291,15 +303,14 @@ class TPDenseModel:
             lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), labels, temperature)
             head_ctx = None
         if save_for_backward:
-            self._saved = dict(batch=batch, tables=tables, inputs=inputs, xf=xf, hf=hf, rstd_f=rstd_f, lse=lse, ent=ent,
-                               labels=labels, temperature=temperature, sl=sl, head_ctx=head_ctx)
+            state.update(kind="lm", lse=lse, ent=ent, labels=labels, temperature=temperature, head_ctx=head_ctx)
+            self._saved = state
         return lp, ent
 
     def backward(self, g_logprob, g_entropy=None) -> None:
         s = self._saved
-        assert s is not None
+        assert s is not None and s.get("kind") == "lm"
         self._saved = None
-        c = self.cfg
         self.tp.begin_pass()
         self.params.alloc_grads()
         g_lp = None if g_logprob is None else g_logprob.float().contiguous()
@@ -309,10 +320,28 @@ class TPDenseModel:
         else:
             dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
                                 dweight=self.head_grad())
-        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"])
-        for l in reversed(range(c.num_hidden_layers)):
-            dx = self.layer_bwd(l, s["inputs"].pop(), dx, s["batch"], s["tables"])
-        A.embedding_bwd(s["batch"].input_ids[s["sl"]].contiguous(), dx, self.params.grads["model.embed_tokens.weight"])
+        self._trunk_bwd(s, dhf)
+
+    def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
+        """Scalar value of THIS rank's tokens [T/W] from the value head (``value_head`` in the configuration: the head is
+        whole on every rank and its gradient, like a norm's, is partial over the rank's tokens)."""
+        hf, state = self._trunk_fwd(batch, save_for_backward)
+        values = (hf.float() @ self.params["v_head.weight"].float().t()).squeeze(-1)
+        if save_for_backward:
+            state["kind"] = "values"
+            self._saved = state
+        return values
+
+    def backward_values(self, g_values: torch.Tensor) -> None:
+        s = self._saved
+        assert s is not None and s.get("kind") == "values", "call forward_values(save_for_backward=True) first"
+        self._saved = None
+        self.tp.begin_pass()
+        self.params.alloc_grads()
+        g = g_values.float().contiguous()
+        w = self.params["v_head.weight"]
+        self.params.grads["v_head.weight"].add_(g[None, :] @ s["hf"].float())
+        self._trunk_bwd(s, (g[:, None] * w.float()).to(s["hf"].dtype))
 
 
 class TPModelAdapter:
@@ -344,6 +373,17 @@ class TPModelAdapter:
             full[: self._T_real] = g.float()
             return full[sl].contiguous()
         self.inner.backward(cut(g_logprob), cut(g_entropy))
+
+    def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
+        padded, self._T_real = pad_packed_batch(batch, 128 * self.tp.world)
+        self._T = padded.input_ids.numel()
+        v = self.inner.forward_values(padded, save_for_backward)
+        return self.tp.all_gather_rows(v.contiguous())[: self._T_real]
+
+    def backward_values(self, g_values: torch.Tensor) -> None:
+        full = torch.zeros(self._T, dtype=torch.float32, device=g_values.device)
+        full[: self._T_real] = g_values.float()
+        self.inner.backward_values(full[self.inner.local_slice(self._T)].contiguous())
 
     def sync_replicated_grads(self) -> None:
         self.inner.sync_replicated_grads()

@@ -333,12 +333,12 @@ class TrainerWorker(_Base):
             return self._build_expert_parallel(model_path, dtype, seed)
         if self.tp_size == 1:
             return super()._build(model_path, dtype, seed)
-        if self.model_kind.value_head:
-            raise NotImplementedError("value-head models are not tensor-parallel yet; run the critic with tp=1")
         from ..models.config import get_config
         from ..models.tp_dense import TPDenseModel, TPModelAdapter
         from ..parallel.tp import TPContext
         mcfg = get_config(model_path)
+        if self.model_kind.value_head:           # critic / reward model: a scalar head, whole on every rank
+            mcfg.extra = {**mcfg.extra, "value_head": True}
         tp_group, dp_group = self._make_groups()
         self.pg = dp_group                          # the optimizer shards over the data-parallel group
         self._mp_group = tp_group
@@ -352,7 +352,9 @@ class TrainerWorker(_Base):
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
             from ..models.params import FlatParams
             ref = FlatParams(mcfg, "cpu", dtype)
-            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))
+            ref.load_hf_state_dict(dict(iter_hf_weights(model_path)), strict=not self.model_kind.value_head)
+            if self.model_kind.value_head:           # the checkpoint of a language model has no value head: the same draw on every rank
+                torch.nn.init.normal_(ref["v_head.weight"], std=0.02, generator=torch.Generator().manual_seed(seed))
             inner.load_full_state(ref.views)
         else:
             inner.init_random(seed=seed)

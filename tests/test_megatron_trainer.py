@@ -333,3 +333,35 @@ def test_expert_tensor_parallel_trainer_matches_data_parallel_trainer(world):
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
     assert (got[3] - got[0]).abs().max() > 1e-4
+
+
+@pytest.mark.timeout(900)
+def test_tensor_parallel_critic_matches_single_process():
+    """A value-head model (critic) under tensor parallelism: values, the value-loss update and the values after it equal the
+    single-process critic."""
+    import importlib
+
+    def run(cls_path, cfg, world):
+        mod, name = cls_path.rsplit(".", 1)
+        from axon_b200.trainer.fsdp_trainer import ValueModel
+        wg = LocalWorkerGroup(ResourcePool([world]), ClassWithInitArgs(getattr(importlib.import_module(mod), name), config=cfg, name="critic",
+                                                                       model=ValueModel), backend="process", rpc_timeout=300)
+        try:
+            wg.init_model()
+            data = _batch()
+            v0 = wg.forward(data).batch["values"]
+            g = torch.Generator().manual_seed(5)
+            data.batch["values"] = v0
+            data.batch["returns"] = (v0 + torch.randn(v0.shape, generator=g) * 0.1) * data.batch["response_mask"]
+            from axon_b200.driver.driver_utils import process_mini_batch
+            process_mini_batch(data)
+            m = wg.forward_backward(data, loss_fn="value", loss_fn_args={"cliprange_value": 0.5})
+            opt = wg.optim_step(step_lr=True)
+            return v0, m.meta_info["metrics"], opt.meta_info["metrics"], wg.forward(data).batch["values"]
+        finally:
+            wg.shutdown()
+    ref = run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1), 1)
+    got = run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(2), 2)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    assert (got[3] - got[0]).abs().max() > 1e-5
