@@ -114,7 +114,8 @@ class TPDenseModel:
         assert (cfg.num_experts > 0) == self.SPARSE, "dense configurations use TPDenseModel, sparse ones TPMoEModel"
         assert cfg.num_key_value_heads % tp.world == 0 and (self.SPARSE or cfg.intermediate_size % tp.world == 0)
         assert not cfg.sandwich_norm, "sandwich-norm families (GLM-4) run under data / sequence / context / pipeline parallelism; the tensor-parallel layer code does not carry the extra norms yet"
-        assert cfg.num_nextn_predict_layers == 0, "the multi-token-prediction module is trained by the data-parallel trainer only"
+        assert cfg.num_nextn_predict_layers == 0 or type(self) is TPDenseModel, \
+            "the multi-token-prediction module is trained by the data-parallel and the plain tensor-parallel trainer"
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
         self.shard_head = bool(vocab_parallel_head) and not cfg.tie_word_embeddings and tp.world > 1
@@ -128,6 +129,8 @@ class TPDenseModel:
             self.vp_head = VocabParallelHead(tp, cfg.vocab_size)
         self.hq, self.hkv = cfg.num_attention_heads // tp.world, cfg.num_key_value_heads // tp.world
         self._saved = None
+        self.mtp_scale = 0.0          # weight of sum_t(-logprob) of the multi-token-prediction module in backward (0 = module idle)
+        self.mtp_last = None          # (sum of negative log-probs, positions) of the latest micro-batch, over the whole group
 
     # ------------------------------------------------------------------ parameters
     def load_full_state(self, full_views: dict) -> None:
@@ -282,9 +285,11 @@ class TPDenseModel:
         hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], c.rms_norm_eps, delta=delta)
         return hf, dict(batch=batch, tables=tables, inputs=inputs, xf=xf, hf=hf, rstd_f=rstd_f, sl=sl)
 
-    def _trunk_bwd(self, s: dict, dhf) -> None:
+    def _trunk_bwd(self, s: dict, dhf, extra_dx=None) -> None:
+        """``extra_dx``: a second gradient w.r.t. the stream before the final norm (the multi-token-prediction module's)."""
         c = self.cfg
-        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"])
+        dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"],
+                           dres=extra_dx)
         for l in reversed(range(c.num_hidden_layers)):
             dx = self.layer_bwd(l, s["inputs"].pop(), dx, s["batch"], s["tables"])
         A.embedding_bwd(s["batch"].input_ids[s["sl"]].contiguous(), dx, self.params.grads["model.embed_tokens.weight"])
@@ -304,8 +309,49 @@ class TPDenseModel:
             head_ctx = None
         if save_for_backward:
             state.update(kind="lm", lse=lse, ent=ent, labels=labels, temperature=temperature, head_ctx=head_ctx)
+            if self.cfg.num_nextn_predict_layers > 0 and self.mtp_scale:
+                self.mtp_last = self._mtp_fwd(state)
             self._saved = state
         return lp, ent
+
+    # ---- multi-token prediction (depth 1) on this rank's rows; the module's own layer is tensor-parallel like the others,
+    # its projection and norms are whole on every rank (``models/mtp.py`` is the data-parallel form and documents the math)
+    def _mtp_fwd(self, s: dict):
+        from .mtp import shifted_inputs
+        assert self.vp_head is None, "the multi-token-prediction module uses the whole output head"
+        c, batch, L, sl = self.cfg, s["batch"], self.cfg.num_hidden_layers, s["sl"]
+        p, w = f"model.layers.{L}.", self.params
+        nxt, lab2 = shifted_inputs(batch)
+        nxt, lab2 = nxt[sl].contiguous(), lab2[sl].contiguous()
+        e = A.embedding_fwd(nxt, w["model.embed_tokens.weight"])
+        en, rstd_e, _ = N.rmsnorm_fwd(e, w[p + "enorm.weight"], c.rms_norm_eps)
+        hn, rstd_h, _ = N.rmsnorm_fwd(s["xf"], w[p + "hnorm.weight"], c.rms_norm_eps)
+        cat = torch.cat([en, hn], dim=1)
+        z = G.gemm_nt(cat, w[p + "eh_proj.weight"])
+        x2, delta2, xin2 = self.layer_fwd(L, z, None, batch, s["tables"])
+        hf2, rstd2, xf2 = N.rmsnorm_fwd(x2, w[p + "shared_head.norm.weight"], c.rms_norm_eps, delta=delta2)
+        lp2, ent2, lse2 = LM.lmhead_fwd(hf2, self.head_weight(), lab2, 1.0)
+        valid = lab2 >= 0
+        s["mtp"] = dict(nxt=nxt, lab2=lab2, e=e, rstd_e=rstd_e, rstd_h=rstd_h, cat=cat, xin2=xin2, hf2=hf2, rstd2=rstd2, xf2=xf2,
+                        lse2=lse2, ent2=ent2, valid=valid)
+        both = torch.stack([-(lp2.float() * valid).sum(), valid.sum().float()])
+        self.tp.all_reduce_(both)                      # every rank reports the group's totals
+        return both[0], both[1]
+
+    def _mtp_bwd(self, s: dict, scale: float):
+        c, batch, L = self.cfg, s["batch"], self.cfg.num_hidden_layers
+        p, w, g, m = f"model.layers.{L}.", self.params, self.params.grads, s.pop("mtp")
+        H = c.hidden_size
+        dhf2 = LM.lmhead_bwd(m["hf2"], self.head_weight(), m["lab2"], m["lse2"], m["ent2"], (-scale) * m["valid"].float(), None, 1.0,
+                             dweight=self.head_grad())
+        dx2 = N.rmsnorm_bwd(dhf2, m["xf2"], w[p + "shared_head.norm.weight"], m["rstd2"], g[p + "shared_head.norm.weight"])
+        dz = self.layer_bwd(L, m["xin2"], dx2, batch, s["tables"])
+        dcat = G.gemm_nn(dz, w[p + "eh_proj.weight"])
+        G.gemm_tn(dz, m["cat"], out=g[p + "eh_proj.weight"], accumulate=True)
+        den, dhn = dcat[:, :H].contiguous(), dcat[:, H:].contiguous()
+        de = N.rmsnorm_bwd(den, m["e"], w[p + "enorm.weight"], m["rstd_e"], g[p + "enorm.weight"])
+        A.embedding_bwd(m["nxt"], de, g["model.embed_tokens.weight"])
+        return N.rmsnorm_bwd(dhn, s["xf"], w[p + "hnorm.weight"], m["rstd_h"], g[p + "hnorm.weight"])
 
     def backward(self, g_logprob, g_entropy=None) -> None:
         s = self._saved
@@ -320,7 +366,7 @@ class TPDenseModel:
         else:
             dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
                                 dweight=self.head_grad())
-        self._trunk_bwd(s, dhf)
+        self._trunk_bwd(s, dhf, self._mtp_bwd(s, float(self.mtp_scale)) if "mtp" in s else None)
 
     def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
         """Scalar value of THIS rank's tokens [T/W] from the value head (``value_head`` in the configuration: the head is
@@ -373,6 +419,18 @@ class TPModelAdapter:
             full[: self._T_real] = g.float()
             return full[sl].contiguous()
         self.inner.backward(cut(g_logprob), cut(g_entropy))
+
+    @property
+    def mtp_scale(self) -> float:
+        return self.inner.mtp_scale
+
+    @mtp_scale.setter
+    def mtp_scale(self, v: float) -> None:
+        self.inner.mtp_scale = v
+
+    @property
+    def mtp_last(self):
+        return self.inner.mtp_last
 
     def forward_values(self, batch: PackedBatch, save_for_backward: bool = False) -> torch.Tensor:
         padded, self._T_real = pad_packed_batch(batch, 128 * self.tp.world)

@@ -365,3 +365,19 @@ def test_tensor_parallel_critic_matches_single_process():
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
     assert (got[3] - got[0]).abs().max() > 1e-5
+
+
+@pytest.mark.timeout(900)
+def test_tensor_parallel_trainer_with_multi_token_prediction_matches_single_process():
+    """The depth-1 prediction module under tensor parallelism: its own decoder layer is cut like the others, its
+    projection and norms are whole on every rank; reported loss, gradient norm and update equal the single-process run."""
+    import numpy as np
+    ref_cfg, got_cfg = _cfg(1, "tiny-qwen3-mtp"), _cfg(2, "tiny-qwen3-mtp")
+    ref_cfg["mtp_loss_scaling_factor"] = got_cfg["mtp_loss_scaling_factor"] = 0.3
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 2)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    assert "actor/mtp_loss" in ref[1] and abs(np.mean(got[1]["actor/mtp_loss"]) - np.mean(ref[1]["actor/mtp_loss"])) < 1e-3
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
