@@ -368,10 +368,11 @@ def test_tensor_parallel_critic_matches_single_process():
 
 
 @pytest.mark.timeout(900)
-def test_tensor_parallel_trainer_with_multi_token_prediction_matches_single_process():
+def test_tensor_parallel_trainer_with_multi_token_prediction_matches_single_process(monkeypatch):
     """The depth-1 prediction module under tensor parallelism: its own decoder layer is cut like the others, its
     projection and norms are whole on every rank; reported loss, gradient norm and update equal the single-process run."""
     import numpy as np
+    monkeypatch.setenv("AXON_ENABLE_MTP", "1")       # the worker processes inherit it; another test may have switched the module off
     ref_cfg, got_cfg = _cfg(1, "tiny-qwen3-mtp"), _cfg(2, "tiny-qwen3-mtp")
     ref_cfg["mtp_loss_scaling_factor"] = got_cfg["mtp_loss_scaling_factor"] = 0.3
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
