@@ -399,7 +399,7 @@ class _DenseInference:
         max_pos = int(batch.position_ids.max().item()) + 1 if plan is not None else (int(batch.max_seqlen) if batch.max_seqlen else c.max_position_embeddings)
         tables = self._tables(max_pos)
         x = A.embedding_fwd(batch.input_ids, self.weights["model.embed_tokens.weight"])
-        delta = None
+        x, delta = self._stage_in(x)
         for l in range(c.num_hidden_layers):
             qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
             kw = self._p(l, "self_attn.k_norm.weight") if c.qk_norm else None
@@ -425,6 +425,7 @@ class _DenseInference:
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
             delta = self._post_norm(l, "post_mlp_layernorm.weight", self.mlp_infer(l, h2))
             x = x1
+        x, delta = self._stage_out(x, delta)
         xl = x[last_index]
         dl = delta[last_index]
         hf, _, _ = N.rmsnorm_fwd(xl, self.weights["model.norm.weight"], c.rms_norm_eps, delta=dl)
@@ -439,7 +440,7 @@ class _DenseInference:
         B = tokens.numel()
         tables = self._tables(c.max_position_embeddings)
         x = A.embedding_fwd(tokens, self.weights["model.embed_tokens.weight"])
-        delta = None
+        x, delta = self._stage_in(x)
         slots = cache.arange(B)
         for l in range(c.num_hidden_layers):
             qw = self._p(l, "self_attn.q_norm.weight") if c.qk_norm else None
@@ -459,10 +460,21 @@ class _DenseInference:
             h2, _, x1 = N.rmsnorm_fwd(xin, self._p(l, "post_attention_layernorm.weight"), c.rms_norm_eps, delta=ao)
             delta = self._post_norm(l, "post_mlp_layernorm.weight", self.mlp_infer(l, h2))
             x = x1
+        x, delta = self._stage_out(x, delta)
         hf, _, _ = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], c.rms_norm_eps, delta=delta)
         return G.gemm_nt(hf, self.head_weight(), out_dtype=torch.float32)
 
+    # A model that holds only a slice of the layers (a stage of a pipelined sampler group, ``models/pp_infer.py``) takes the
+    # stream from the stage before it here and hands it on there; a whole model passes it through.
+    def _stage_in(self, x):
+        return x, None
+
+    def _stage_out(self, x, delta):
+        return x, delta
+
 
 DenseModel.prefill = _DenseInference.prefill
+DenseModel._stage_in = _DenseInference._stage_in
+DenseModel._stage_out = _DenseInference._stage_out
 DenseModel.supports_cached_prefill = True
 DenseModel.decode = _DenseInference.decode

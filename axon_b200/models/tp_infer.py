@@ -56,10 +56,11 @@ class Shard:
     reduce: PeerAllReduce | None = None
 
     @staticmethod
-    def create(group, device) -> "Shard":
+    def create(group, device, reduce: bool = True) -> "Shard":
+        """``reduce``: also set up the group's activation sum (a tensor-parallel group needs it, pipeline stages do not)."""
         world = dist.get_world_size(group) if group is not None else 1
         rank = dist.get_rank(group) if group is not None else 0
-        return Shard(group, rank, world, PeerAllReduce(group, device))
+        return Shard(group, rank, world, PeerAllReduce(group, device) if reduce else None)
 
 
 def local_config(cfg: ModelConfig, world: int) -> ModelConfig:

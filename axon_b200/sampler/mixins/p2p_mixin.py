@@ -49,7 +49,7 @@ class SamplerP2PMixin:
         dist.all_reduce(self._bridge_token, group=self.bridge_pg)
         mine = {"role": "sampler", "rank": self.rank, "host": socket.gethostname(), "cuda": self.device.type == "cuda",
                 "tp": self.tp, "handle": None, "offsets": None}
-        if self.device.type == "cuda" and self.tp == 1 and not getattr(self, "shares_trainer_weights", False):
+        if self.device.type == "cuda" and self.tp == 1 and getattr(self, "pp", 1) == 1 and not getattr(self, "shares_trainer_weights", False):
             mine["handle"], mine["offsets"] = self._export_parameters()
         infos = exchange_peer_info(self.bridge_pg, mine)
         self._peer_path = peer_store_path_possible(infos)
@@ -75,10 +75,17 @@ class SamplerP2PMixin:
         cfg = getattr(self.model, "full_cfg", self.model.cfg)       # a sharded model computes on its local configuration
         ep = self.tp if getattr(cfg, "num_experts", 0) > 0 else 1   # experts are divided whole over the group
         whole = ("model.embed_tokens.weight", "lm_head.weight") if self.tp > 1 else ()      # every rank of a group holds these in full
-        return get_param_metadata(cfg, rank=self.rank, tp=self.tp, tp_rank=tp_rank, ep=ep, ep_rank=tp_rank if ep > 1 else 0,
-                                  dtype=self.model.params.dtype, replicated_names=whole)
+        mapping = get_param_metadata(cfg, rank=self.rank, tp=self.tp, tp_rank=tp_rank, ep=ep, ep_rank=tp_rank if ep > 1 else 0,
+                                     dtype=self.model.params.dtype, replicated_names=whole)
+        local_name = getattr(self.model, "local_name", None)
+        if local_name is not None:                      # a pipeline stage: its own layers (under the full model's names) only
+            mapping.params = [m for m in mapping.params if local_name(m.param_name) is not None]
+        return mapping
 
     def _shard_offsets(self, metas) -> dict:
+        local_name = getattr(self.model, "local_name", None)
+        if local_name is not None:                      # full-model names -> where the stage keeps the tensor
+            return {m.param_name: self.model.params.offsets[local_name(m.param_name)][0] for m in metas}
         if self.tp == 1:
             return {n: o for n, (o, _) in self.model.params.offsets.items()}
         off, table = 0, {}

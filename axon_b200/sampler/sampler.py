@@ -86,8 +86,11 @@ class SamplerWorker(Worker, DistProfilerExtension):
         lockstep = None
         self.tp_group = None
         if self.tp * self.pp > 1:
-            if self.pp > 1:
-                raise NotImplementedError("the sampler shards a model over tensor-parallel groups; pipeline stages are not built")
+            if self.pp > 1 and self.tp > 1:
+                raise NotImplementedError("a sampler group is either tensor-parallel or cut into pipeline stages, not both")
+            if self.pp > 1 and _get(cfg, "moe_replay", False):
+                raise NotImplementedError("routed-experts capture is not gathered over the stages of a pipelined sampler group; "
+                                          "use a tensor-parallel group with moe_replay")
             lockstep = self._make_tp_groups()
         shared = None
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
@@ -99,7 +102,7 @@ class SamplerWorker(Worker, DistProfilerExtension):
         if shared is not None:
             self.model = shared
             self.shares_trainer_weights = True
-        elif trainer is not None and self.tp == 1 and serves:
+        elif trainer is not None and self.tp == 1 and self.pp == 1 and serves:
             self.model = trainer.model                  # zero-copy: generation reads the trainer's live parameters
             self.shares_trainer_weights = True
         elif trainer is not None:
@@ -110,6 +113,11 @@ class SamplerWorker(Worker, DistProfilerExtension):
                 from ..models.tp_infer import Shard, build_sharded_model
                 self.model = build_sharded_model(_get(cfg, "model_path"), Shard.create(self.tp_group, self.device), device=self.device,
                                                  dtype=dtype, seed=int(_get(cfg, "seed", 42)), load_weights=False)
+            elif self.pp > 1:
+                from ..models.pp_infer import build_staged_model
+                from ..models.tp_infer import Shard
+                self.model = build_staged_model(_get(cfg, "model_path"), Shard.create(self.tp_group, self.device, reduce=False), device=self.device,
+                                                dtype=dtype, seed=int(_get(cfg, "seed", 42)), load_weights=False)
             else:
                 self.model = build_model(_get(cfg, "model_path"), device=self.device, dtype=dtype, seed=int(_get(cfg, "seed", 42)),
                                          load_weights=False)
@@ -118,6 +126,11 @@ class SamplerWorker(Worker, DistProfilerExtension):
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
             self.model = build_sharded_model(_get(cfg, "model_path"), Shard.create(self.tp_group, self.device), device=self.device,
                                              dtype=dtype, seed=int(_get(cfg, "seed", 42)), load_weights=True)
+        elif self.pp > 1:
+            from ..models.pp_infer import build_staged_model
+            from ..models.tp_infer import Shard
+            self.model = build_staged_model(_get(cfg, "model_path"), Shard.create(self.tp_group, self.device, reduce=False), device=self.device,
+                                            dtype=dtype, seed=int(_get(cfg, "seed", 42)), load_weights=True)
         else:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
             self.model = build_model(_get(cfg, "model_path"), device=self.device, dtype=dtype, seed=int(_get(cfg, "seed", 42)),
@@ -179,8 +192,9 @@ class SamplerWorker(Worker, DistProfilerExtension):
         from .server import Lockstep
         assert dist.is_initialized(), "a tensor-parallel sampler needs the worker group's process group"
         mine_data = mine_ctl = None
-        for g in range(self.world_size // self.tp):
-            ranks = list(range(g * self.tp, (g + 1) * self.tp))
+        size = self.tp * self.pp              # one of the two is 1
+        for g in range(self.world_size // size):
+            ranks = list(range(g * size, (g + 1) * size))
             data = dist.new_group(ranks)
             ctl = dist.new_group(ranks, backend="gloo", timeout=datetime.timedelta(hours=6))
             if g == self.dp_rank:

@@ -352,6 +352,8 @@ class SamplerServer:
                     t = localize(name, t)
                     if t is None:
                         continue
+                    if isinstance(t, tuple):          # a pipeline stage renumbers its layers: (its own name, tensor)
+                        name, t = t
                 dst = views.get(name)
                 if dst is None:
                     if hf_views is None:

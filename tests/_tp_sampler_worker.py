@@ -24,7 +24,7 @@ def _trainer_logprobs(model, prompt, out, temperature):
     return lp[len(prompt) - 1: len(prompt) - 1 + len(out_ids)].float().cpu()
 
 
-def main(out_path: str, device_kind: str) -> None:
+def main(out_path: str, device_kind: str, how: str = "tp") -> None:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     if device_kind == "cuda":
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -44,20 +44,24 @@ def main(out_path: str, device_kind: str) -> None:
     group = dist.new_group(list(range(world)))
     ctl = dist.new_group(list(range(world)), backend="gloo")       # the servers' lockstep messages, nothing else
     side = dist.new_group(list(range(world)), backend="gloo")      # this script's own barriers and gathers
-    shard = Shard.create(group, dev)
-    res = {"rank": rank, "fused": shard.reduce.fused}
+    shard = Shard.create(group, dev, reduce=how == "tp")       # "pp": the group is cut into pipeline stages instead
+    res = {"rank": rank, "fused": shard.reduce.fused if how == "tp" else False}
     g = torch.Generator().manual_seed(5)
     for preset in presets:
         cfg = get_config(preset)
         full = build_model_for(cfg, dev, dtype)
         full.params.init_random(std=0.08, seed=3)
-        part = (ShardedMoEModel if cfg.num_experts else ShardedDenseModel)(cfg, shard, device=dev, dtype=dtype)
+        if how == "tp":
+            part = (ShardedMoEModel if cfg.num_experts else ShardedDenseModel)(cfg, shard, device=dev, dtype=dtype)
+        else:
+            from axon_b200.models.pp_infer import StagedDenseModel, StagedMoEModel
+            part = (StagedMoEModel if cfg.num_experts else StagedDenseModel)(cfg, shard, device=dev, dtype=dtype)
         part.load_full_state(full.params.views)
         prompts = [torch.randint(2, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 130, 47, 260, 9, 33)]
         # ---------------- engines driven with the same calls on every rank
         sp = SamplingParams(temperature=0.8, max_tokens=24, ignore_eos=True)
         eng = GenerationEngine(part, num_pages=24, max_num_seqs=8, seed=7)
-        if cfg.num_experts:
+        if cfg.num_experts and how == "tp":
             eng.enable_routing_capture(True)
         outs = eng.generate(prompts, sp)
         worst = 0.0
@@ -75,7 +79,7 @@ def main(out_path: str, device_kind: str) -> None:
             res[key]["equals_unsharded"] = [o.token_ids for o in ref_eng.generate(prompts, sp)] == toks
         # ---------------- servers: requests and control on the first rank only
         eng2 = GenerationEngine(part, num_pages=24, max_num_seqs=8, seed=7)
-        if cfg.num_experts:
+        if cfg.num_experts and how == "tp":
             eng2.enable_routing_capture(True)
         srv = SamplerServer(eng2, name=f"s{rank}", lockstep=Lockstep(ctl)).start()
         greedy = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
@@ -113,7 +117,7 @@ def main(out_path: str, device_kind: str) -> None:
             res[key]["follower_done"] = not srv._thread.is_alive()
             res[key]["follower_error"] = repr(srv.error) if srv.error else None
         dist.barrier(group=side)
-    res["reduce_calls"] = dict(shard.reduce.calls)
+    res["reduce_calls"] = dict(shard.reduce.calls) if how == "tp" else {}
     if device_kind == "cuda":
         from axon_b200.ops import _common as C
         torch.cuda.synchronize()
@@ -127,4 +131,4 @@ def main(out_path: str, device_kind: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1], sys.argv[2])
+    main(sys.argv[1], sys.argv[2], sys.argv[3] if len(sys.argv) > 3 else "tp")

@@ -92,7 +92,7 @@ def test_disaggregated_modes_push_weights(tmp_path, mode):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("model", ["dense", "moe", "dense-4", "moe-tp-ep-trainer", "dense-tp-trainer", "dense-pp-trainer"])
+@pytest.mark.parametrize("model", ["dense", "moe", "dense-4", "moe-tp-ep-trainer", "dense-tp-trainer", "dense-pp-trainer", "dense-pp-sampler"])
 def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
     """1 trainer + a sampler group of 2 ranks that shard the model: the weight push re-slices every tensor for the
     group's ranks, the group generates in lockstep behind its first rank, and what it samples has the log-probs the
@@ -105,6 +105,8 @@ def test_disaggregated_with_a_tensor_parallel_sampler_group(tmp_path, model):
     if model == "moe-tp-ep-trainer":    # two trainer ranks as one tensor + expert parallel group push to one whole-model sampler
         extra = ["num_gpus_per_node=3", "sampler_trainer_gpu_ratio=0.5", "hybrid_engine=false", "total_training_steps=2", "save_steps=-1",
                  "actor.megatron.tensor_model_parallel_size=2", "actor.megatron.expert_model_parallel_size=2"]
+    if model == "dense-pp-sampler":     # the sampler group is cut into two pipeline stages: each receives its own layers
+        extra = [e for e in extra if not e.startswith("sampler.tensor_model_parallel_size")] + ["sampler.pipeline_model_parallel_size=2"]
     if model in ("dense-tp-trainer", "dense-pp-trainer"):
         # two trainer ranks as one tensor-parallel group / as two pipeline stages feed one whole-model sampler; the asynchronous
         # driver hands the SAME rows to the ranks of such a group and each stage pushes its own layers
@@ -170,7 +172,7 @@ def test_colocated_tensor_parallel_trainer_and_sampler_share_their_shards(tmp_pa
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("layout", ["pp2-sampler-dp", "tp2-sampler-dp", "pp2-sampler-tp2", "pp2xtp2ep2-sampler-tp2"])
+@pytest.mark.parametrize("layout", ["pp2-sampler-dp", "tp2-sampler-dp", "pp2-sampler-tp2", "pp2xtp2ep2-sampler-tp2", "dp2-sampler-pp2"])
 def test_colocated_sampler_next_to_a_trainer_with_another_layout(tmp_path, layout):
     """The trainer's shards are not what the sampler reads (pipeline stages; tensor-parallel shards next to whole-model
     sampler replicas; a sparse pipeline x tensor x expert trainer next to tensor-parallel sampler groups): every sampler
@@ -181,6 +183,8 @@ def test_colocated_sampler_next_to_a_trainer_with_another_layout(tmp_path, layou
         extra += ["num_gpus_per_node=2", "actor.megatron.pipeline_model_parallel_size=2"]
     elif layout == "tp2-sampler-dp":
         extra += ["num_gpus_per_node=2", "actor.megatron.tensor_model_parallel_size=2"]
+    elif layout == "dp2-sampler-pp2":           # a data-parallel trainer next to a sampler group cut into two pipeline stages
+        extra = [e for e in extra if e != "strategy=megatron"] + ["num_gpus_per_node=2", "sampler.pipeline_model_parallel_size=2"]
     elif layout == "pp2-sampler-tp2":
         extra += ["num_gpus_per_node=2", "actor.megatron.pipeline_model_parallel_size=2", "sampler.tensor_model_parallel_size=2"]
     else:

@@ -12,17 +12,17 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(tmp_path, n, kind, port):
+def _run(tmp_path, n, kind, port, how="tp"):
     out = tmp_path / "tps.json"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_sampler_worker.py"), str(out), kind]
+           "--master-port", str(port), os.path.join(ROOT, "tests", "_tp_sampler_worker.py"), str(out), kind, how]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.loads(out.read_text())
 
 
-def _check(res, presets, tol, exact):
+def _check(res, presets, tol, exact, routed=True):
     for x in res:
         for p in presets:
             y = x[p]
@@ -35,7 +35,7 @@ def _check(res, presets, tol, exact):
                 assert y["server_first_err"] < tol, (p, y)
             else:
                 assert y["follower_done"] and y["follower_error"] is None, (p, y)
-        assert x["tiny-moe" if exact else "tiny-moe-gpu"]["routed"]
+        assert x["tiny-moe" if exact else "tiny-moe-gpu"]["routed"] or not routed
 
 
 @pytest.mark.timeout(900)
@@ -45,6 +45,15 @@ def test_sampler_group_matches_unsharded_model_cpu(tmp_path, world):
     res = _run(tmp_path, world, "cpu", 29671 + world)
     _check(res, ("tiny-qwen3", "tiny-moe"), 1e-4, exact=True)
     assert not res[0]["fused"] and len(res) == world
+
+
+@pytest.mark.timeout(900)
+def test_pipelined_sampler_group_matches_unsharded_model_cpu(tmp_path):
+    """A group of 2 ranks that holds the model by layers (each rank its slice and its share of the KV cache): the stream
+    crosses the stage boundary inside every prefill / decode call, every rank computes the same logits, and the group's
+    servers run in lockstep like a tensor-parallel group's (requests, sleep / wake, weight updates, reset)."""
+    res = _run(tmp_path, 2, "cpu", 29679, how="pp")
+    _check(res, ("tiny-qwen3", "tiny-moe"), 1e-4, exact=True, routed=False)
 
 
 @pytest.mark.gpu
