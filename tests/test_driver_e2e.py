@@ -150,7 +150,7 @@ def test_colocated_run_on_two_worker_processes(tmp_path, model, shards):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("model", ["dense", "moe"])
+@pytest.mark.parametrize("model", ["dense", "moe", "dense-critic"])
 def test_colocated_tensor_parallel_trainer_and_sampler_share_their_shards(tmp_path, model):
     """Two colocated ranks form ONE tensor-parallel group for both roles (sparse model: it also divides the experts):
     the sampler group reads the trainer's shards in place, generates in lockstep behind its first rank, and what it
@@ -159,6 +159,8 @@ def test_colocated_tensor_parallel_trainer_and_sampler_share_their_shards(tmp_pa
              "actor.megatron.tensor_model_parallel_size=2", "sampler.tensor_model_parallel_size=2"]
     if model == "moe":
         extra += ["model_path=tiny-moe", "actor.megatron.expert_model_parallel_size=2", "moe_replay=true"]
+    if model == "dense-critic":         # PPO with a value model that is tensor-parallel too
+        extra += ["critic.enable=true", "advantage=gae", "critic.megatron.tensor_model_parallel_size=2"]
     drv = train_agent(_config(tmp_path, extra), backend="process", keep_alive=True)
     try:
         assert drv.global_steps == 3
@@ -169,6 +171,7 @@ def test_colocated_tensor_parallel_trainer_and_sampler_share_their_shards(tmp_pa
     assert [r["step"] for r in logs] == [1, 2]
     for r in logs:
         assert abs(r["data"]["batch/sampler_logprobs_diff_max"]) < 0.02 and abs(r["data"]["batch/sampler_logprobs_diff_min"]) < 0.02, r["data"]
+        assert model != "dense-critic" or "critic/vf_loss" in r["data"] or any(k.startswith("critic/") for k in r["data"]), sorted(r["data"])[:40]
 
 
 @pytest.mark.timeout(900)
