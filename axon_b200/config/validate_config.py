@@ -191,6 +191,16 @@ def validate_sampler_config(cfg) -> None:
         raise ValueError(f"Invalid sampler_channel: {_get(cfg, 'sampler_channel')}")
     if (s.get("max_model_len") or 0) and s["max_model_len"] < _get(cfg, "max_seq_length", 0):
         raise ValueError("sampler.max_model_len must be >= max_seq_length.")
+    tp, pp, ep = (int(s.get(k, 1) or 1) for k in ("tensor_model_parallel_size", "pipeline_model_parallel_size", "expert_parallel_size"))
+    if tp > 1 and pp > 1:
+        raise ValueError("a sampler group is tensor-parallel or cut into pipeline stages, not both "
+                         f"(sampler.tensor_model_parallel_size={tp}, sampler.pipeline_model_parallel_size={pp}).")
+    if ep > 1 and tp > 1 and ep != tp:
+        raise ValueError(f"sampler.expert_parallel_size ({ep}) must equal sampler.tensor_model_parallel_size ({tp}): a group divides "
+                         "its experts over its own ranks.")
+    if pp > 1 and _get(cfg, "moe_replay", False):
+        raise ValueError("moe_replay needs a tensor-parallel sampler group or whole replicas: routed experts are not gathered over "
+                         "the stages of a pipelined group.")
 
 
 def _validate_cross_section_consistency(cfg) -> None:

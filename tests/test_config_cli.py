@@ -56,6 +56,9 @@ def test_dataclass_conversion():
     (["mini_batch_size=128"], "mini_batch_size"), (["strategy=deepspeed"], "strategy"),
     (["strategy=megatron", "actor.megatron.tensor_model_parallel_size=3"], "tp*pp*cp"),
     (["hybrid_engine=false", "driver_mode=async", "advantage=gae"], "critic"),
+    (["sampler.tensor_model_parallel_size=2", "sampler.pipeline_model_parallel_size=2"], "not both"),
+    (["sampler.tensor_model_parallel_size=2", "sampler.expert_parallel_size=4"], "expert_parallel_size"),
+    (["moe_replay=true", "strategy=megatron", "sampler.pipeline_model_parallel_size=2"], "pipelined group"),
 ])
 def test_validation_rejects(ov, msg):
     with pytest.raises(ValueError, match=msg.replace("*", r"\*")):
