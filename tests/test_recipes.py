@@ -95,3 +95,19 @@ def test_react_program_runs_an_episode_of_each_recipe(recipe):
     res = asyncio.run(prog.run())
     assert res.reward == 1.0 and res.done
     assert script.calls[0][-1]["role"] == "user" and not script.replies
+
+
+def test_launch_files_compose_and_pass_the_configuration_check():
+    """Every shell launch file hands ``axon train`` a list of overrides that composes and validates."""
+    import glob
+    import re
+    from axon_b200.config.validate_config import validate_axon_config
+    from axon_b200.utils.config import compose_config
+    files = sorted(glob.glob(os.path.join(ROOT, "recipes", "*", "*.sh")))
+    assert len(files) >= 4
+    for f in files:
+        txt = open(f).read()
+        body = txt[txt.index("axon train --fg --") + len("axon train --fg --"):]
+        body = body.replace("\\\n", " ").replace('"$@"', "").replace("${ROOT}", ROOT)
+        overrides = [t.strip('"') for t in re.findall(r'(?:"[^"]*"|\S+)', body) if "=" in t]
+        validate_axon_config(compose_config(overrides))
