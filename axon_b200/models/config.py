@@ -83,8 +83,8 @@ class ModelConfig:
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
-        from .families import FAMILY_TYPES, family_config
-        if d.get("model_type") in FAMILY_TYPES:
+        from .families import FAMILY_TYPES, TEXT_ONLY_OF, family_config
+        if d.get("model_type") in FAMILY_TYPES or (d.get("model_type") in TEXT_ONLY_OF and "text_config" in d):
             return family_config(d)
         known = {f for f in cls.__dataclass_fields__ if f != "extra"}
         kw = {k: v for k, v in d.items() if k in known}

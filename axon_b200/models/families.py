@@ -32,6 +32,10 @@ from .params import FlatParams
 FAMILY_TYPES = ("deepseek_v3", "glm4_moe", "glm4_moe_lite", "gpt_oss", "gemma2", "gemma3_text", "qwen3_next", "qwen3_5_text",
                 "qwen3_5_moe_text", "glm_moe_dsa", "gemma4_text", "qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v")
 VISION_LANGUAGE_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe", "glm4v")
+# Multimodal checkpoints whose decoder is one of the text families above: they are trained text-only, as the reference does
+# for Gemma-4 (axon/models/transformers/gemma4.py: ``patch_gemma4_for_text_only_training``) - the decoder's configuration
+# and weights are taken, the towers are left alone.
+TEXT_ONLY_OF = {"gemma3": "gemma3_text", "gemma4": "gemma4_text", "qwen3_5": "qwen3_5_text", "qwen3_5_moe": "qwen3_5_moe_text"}
 
 
 # ------------------------------------------------------------------------------------------ small pieces
@@ -274,6 +278,10 @@ class FamilyParams(FlatParams):
         """Copies tensors by name. Checkpoints that store every expert separately
         (``mlp.experts.<e>.{gate,up,down}_proj.weight``) are stacked into the ``[E, ...]`` tensors used here."""
         sd = dict(sd)
+        if not any(".language_model." in n for n in self.layout):
+            # a multimodal checkpoint read by its text family: the decoder's tensors sit under ``...language_model.``
+            for k in [k for k in sd if ".language_model." in k]:
+                sd.setdefault(k.replace("language_model.", "", 1), sd[k])
         missing = []
         for name in self.layout:
             t = sd.get(name)
@@ -1925,6 +1933,14 @@ def family_config(hf: dict) -> ModelConfig:
     """The ``ModelConfig`` view of a family's HF config: the fields the engines read (cache geometry, vocabulary,
     special tokens); everything else stays in ``extra['hf_config']`` for the family's spec."""
     mt = hf["model_type"]
+    if mt in TEXT_ONLY_OF and "text_config" in hf:
+        # the decoder of a multimodal checkpoint: its own configuration (special tokens of the wrapper are kept when it has none)
+        text = dict(hf["text_config"])
+        for k in ("eos_token_id", "pad_token_id", "bos_token_id", "tie_word_embeddings"):
+            if text.get(k) is None and hf.get(k) is not None:
+                text[k] = hf[k]
+        text["model_type"] = mt = TEXT_ONLY_OF[mt]
+        hf = text
     if mt in VISION_LANGUAGE_TYPES and "text_config" in hf:
         # vision-language checkpoints nest the decoder's fields: lift them, keep the nested form for export
         nested = dict(hf)

@@ -686,3 +686,30 @@ def test_qwen3_vl_moe_sparse_decoder_matches_transformers():
                  "model.language_model.layers.1.mlp.up_proj.weight", "model.visual.deepstack_merger_list.0.linear_fc1.weight"):
         a, b = m.params.grads[name], named[name].grad
         assert (a - b).abs().max() < 2e-4 * max(1.0, b.abs().max().item()), name
+
+
+def test_multimodal_checkpoint_of_a_text_family_is_read_text_only():
+    """A multimodal wrapper (``gemma3`` around ``gemma3_text``): the configuration is the nested decoder's, its tensors are
+    found under ``model.language_model.``, tower tensors are ignored, and the logits are the text model's."""
+    from axon_b200.models.config import ModelConfig
+    from axon_b200.models.families import FamilyModel
+    text = dict(_HF["gemma3_text"]) if "gemma3_text" in globals().get("_HF", {}) else None
+    if text is None:
+        text = dict(model_type="gemma3_text", vocab_size=160, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                    head_dim=16, intermediate_size=96, sliding_window=8, query_pre_attn_scalar=16, rms_norm_eps=1e-6, rope_theta=10000.0,
+                    rope_local_base_freq=10000.0, layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"],
+                    max_position_embeddings=256, tie_word_embeddings=True)
+    plain = FamilyModel(ModelConfig.from_hf_dict(text), device="cpu", dtype=torch.float32)
+    plain.init_random(std=0.05, seed=2)
+    wrapper = {"model_type": "gemma3", "text_config": {k: v for k, v in text.items() if k != "tie_word_embeddings"}, "tie_word_embeddings": True,
+               "vision_config": {"model_type": "siglip_vision_model", "hidden_size": 32}, "eos_token_id": 1}
+    cfg = ModelConfig.from_hf_dict(wrapper)
+    assert cfg.model_type == "gemma3_text" and cfg.num_hidden_layers == 4 and cfg.eos_token_id == 1
+    m = FamilyModel(cfg, device="cpu", dtype=torch.float32)
+    sd = {k.replace("model.", "model.language_model.", 1): v for k, v in plain.state_dict().items()}
+    sd["model.vision_tower.vision_model.embeddings.patch_embedding.weight"] = torch.zeros(32, 3, 4, 4)
+    sd["model.multi_modal_projector.mm_input_projection_weight"] = torch.zeros(32, 64)
+    m.load_state_dict(sd)
+    ids = torch.randint(0, 150, (23,), dtype=torch.int32)
+    assert torch.equal(m.logits(ids), plain.logits(ids))
+    assert m.cfg.to_hf_dict()["model_type"] == "gemma3_text"          # what is exported is the text model
