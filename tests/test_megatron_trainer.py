@@ -271,7 +271,7 @@ def test_virtual_stage_schedule_runs_every_operation_once_in_dependency_order():
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("world,pp,vpp,cap,model", [(2, 2, 2, 64, "tiny-qwen3-untied-5l"), (2, 2, 2, 512, "tiny-qwen3-5l"), (3, 3, 1, 64, "tiny-qwen3-untied-5l")])
+@pytest.mark.parametrize("world,pp,vpp,cap,model", [(2, 2, 2, 64, "tiny-qwen3-untied-5l"), (2, 2, 2, 512, "tiny-qwen3-5l")])
 def test_interleaved_pipeline_chunks_match_single_process(world, pp, vpp, cap, model):
     """Two ranks with two model chunks each (virtual stages 0, 2 on the first rank and 1, 3 on the second; with a token cap
     of 64 every row is its own micro-batch, with 512 there is one): log-probs, loss, gradient norm and the update equal the
@@ -321,9 +321,9 @@ def test_tensor_parallel_groups_as_context_parallel_ranks_match_single_process()
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2])
 def test_expert_tensor_parallel_trainer_matches_data_parallel_trainer(world):
-    """tp = etp = 2 (x dp = 1 or 2): every rank holds a slice of the intermediate units of EVERY expert and works on all the
+    """tp = etp = 2: every rank holds a slice of the intermediate units of EVERY expert and works on all the
     group's tokens; partial expert outputs are reduce-scattered back to the rows' owners."""
     import numpy as np
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-moe"), 1, vocab=2048)
