@@ -329,6 +329,10 @@ class Engine:
         dt = time.time() - t0
         state.metrics.llm_time += dt
         state.metrics.total_time += dt
+        if out.spec_decode_metrics is not None:
+            state.metrics.spec_draft_tokens += out.spec_decode_metrics.num_draft_tokens
+            state.metrics.spec_accepted_tokens += out.spec_decode_metrics.num_accepted_tokens
+            state.metrics.spec_verify_count += out.spec_decode_metrics.num_completions
         if (state.enable_partial_rollout and out.stop_reason == ModelStopReason.LENGTH
                 and step.token_len + len(step.partial_tokens) < self.max_seq_length):
             raise StopPartialProgram(f"Program {state.uid} preempted due to partial sampler limit.")
@@ -377,9 +381,13 @@ class Engine:
         else:
             rm = []
         fin = res["finish_reasons"][0]
+        spec = (res.get("spec_decode_metrics") or [None])[0]
+        if spec:
+            from ..sampler.params import SpecDecodeMetrics
+            spec = SpecDecodeMetrics(**{k: int(v) for k, v in spec.items()})
         return ModelOutput.from_token_strs(token_ids=ids, token_strs=strs, logprobs=lps,
                                            stop_reason=ModelStopReason.LENGTH if fin == "length" else ModelStopReason.STOP,
-                                           moe_routermap=rm)
+                                           moe_routermap=rm, spec_decode_metrics=spec or None)
 
     # ------------------------------------------------------------------ termination checks
     def check_prompt_truncation_termination(self, step: Step) -> None:

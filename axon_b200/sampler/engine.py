@@ -640,6 +640,13 @@ class GenerationEngine:
             off += n
             self.stats["spec_draft_tokens"] = self.stats.get("spec_draft_tokens", 0) + len(d)
             self.stats["spec_accepted_tokens"] = self.stats.get("spec_accepted_tokens", 0) + accepted
+            m = s.out.spec_decode_metrics
+            if m is None:
+                from .params import SpecDecodeMetrics
+                m = s.out.spec_decode_metrics = SpecDecodeMetrics()
+            m.num_draft_tokens += len(d)
+            m.num_accepted_tokens += accepted
+            m.num_completions += 1
             self.stats["decode_tokens"] += accepted + 1
         self.stats["spec_verify_steps"] = self.stats.get("spec_verify_steps", 0) + 1
         return {id(s) for s, _ in work}

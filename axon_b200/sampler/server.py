@@ -406,7 +406,8 @@ class SamplerServer:
                 choices.append({"index": i, "text": text, "token_ids": o.token_ids, "finish_reason": o.finish_reason,
                                 "stop_reason": o.stop_reason,
                                 "logprobs": {"token_logprobs": o.logprobs, "tokens": strs},
-                                "routed_experts": encode_routed_experts(o.moe_routermap)})
+                                "routed_experts": encode_routed_experts(o.moe_routermap),
+                                "spec_decode_metrics": o.spec_decode_metrics.to_dict() if o.spec_decode_metrics is not None else None})
             return {"object": "text_completion", "model": server.name, "choices": choices,
                     "usage": {"prompt_tokens": len(prompt), "completion_tokens": sum(len(o.token_ids) for o in outs)}}
 

@@ -72,14 +72,16 @@ class SamplingClient:
             ch = r.json()["choices"][0]
             return {"token_ids": ch["token_ids"], "logprobs": ch["logprobs"]["token_logprobs"],
                     "token_strs": ch["logprobs"].get("tokens") or [], "finish_reason": ch.get("finish_reason"),
-                    "stop_reason": ch.get("stop_reason"), "moe_routermap": decode_routed_experts(ch.get("routed_experts"))}
+                    "stop_reason": ch.get("stop_reason"), "moe_routermap": decode_routed_experts(ch.get("routed_experts")),
+                    "spec_decode_metrics": ch.get("spec_decode_metrics")}
         out = await (addr.generate(prompt_ids, params, image_data) if image_data else addr.generate(prompt_ids, params))
         strs = []
         tok = self.tokenizer or getattr(addr, "tokenizer", None)
         if tok is not None:
             strs = tok.token_strs(out.token_ids) if hasattr(tok, "token_strs") else [tok.decode([t]) for t in out.token_ids]
         return {"token_ids": out.token_ids, "logprobs": out.logprobs, "token_strs": strs,
-                "finish_reason": out.finish_reason, "stop_reason": out.stop_reason, "moe_routermap": out.moe_routermap}
+                "finish_reason": out.finish_reason, "stop_reason": out.stop_reason, "moe_routermap": out.moe_routermap,
+                "spec_decode_metrics": out.spec_decode_metrics.to_dict() if getattr(out, "spec_decode_metrics", None) is not None else None}
 
     async def sample(self, prompt_token_ids, sampling_params: dict | None = None, session_id: str | None = None,
                      image_data=None) -> dict:
@@ -90,7 +92,7 @@ class SamplingClient:
         addr = self.addresses[idx]
 
         async def run_one():
-            acc = {"token_ids": [], "logprobs": [], "token_strs": [], "moe_routermap": None}
+            acc = {"token_ids": [], "logprobs": [], "token_strs": [], "moe_routermap": None, "spec_decode_metrics": None}
             prompt, p = list(prompt_token_ids), dict(params)
             for _ in range(self.max_retries + 1):
                 async with self._sem(idx):
@@ -105,6 +107,8 @@ class SamplingClient:
                 if r["moe_routermap"] is not None:
                     acc["moe_routermap"] = r["moe_routermap"] if acc["moe_routermap"] is None else \
                         __import__("numpy").concatenate([acc["moe_routermap"], r["moe_routermap"]], 0)
+                if r.get("spec_decode_metrics"):
+                    acc["spec_decode_metrics"] = {k: (acc["spec_decode_metrics"] or {}).get(k, 0) + int(v) for k, v in r["spec_decode_metrics"].items()}
                 if r["finish_reason"] != "abort":
                     return {**acc, "finish_reason": r["finish_reason"], "stop_reason": r["stop_reason"]}
                 # aborted by a pause(reset): continue from what was generated, with the remaining budget
@@ -118,7 +122,8 @@ class SamplingClient:
         outs = await asyncio.gather(*(run_one() for _ in range(n)))
         return {"token_ids": [o["token_ids"] for o in outs], "logprobs": [o["logprobs"] for o in outs],
                 "token_strs": [o["token_strs"] for o in outs], "finish_reasons": [o["finish_reason"] for o in outs],
-                "stop_reasons": [o["stop_reason"] for o in outs], "moe_routermap": [o["moe_routermap"] for o in outs]}
+                "stop_reasons": [o["stop_reason"] for o in outs], "moe_routermap": [o["moe_routermap"] for o in outs],
+                "spec_decode_metrics": [o.get("spec_decode_metrics") for o in outs]}
 
     # ------------------------------------------------------------------ fleet control
     async def _fanout(self, local_call: str, http_path: str, payload: dict | None = None, **kw) -> None:

@@ -19,6 +19,7 @@ class ScriptedSampler:
 
     def __init__(self, tok, replies, with_routing=False):
         self.tok, self.replies, self.calls, self.with_routing = tok, list(replies), [], with_routing
+        self.spec = None          # what the sampler says about speculative rounds of every completion
 
     async def sample(self, prompt_ids, params, session_id=None, image_data=None):
         self.calls.append((list(prompt_ids), dict(params)))
@@ -34,7 +35,7 @@ class ScriptedSampler:
             n = len(prompt_ids) + len(ids) - 1          # the sampler never routes its last sampled token
             rm = (np.arange(n * 2 * 2).reshape(n, 2, 2) % 8).astype("int16")
         return {"token_ids": [ids], "logprobs": [[-0.5] * len(ids)], "token_strs": [strs], "finish_reasons": [fin],
-                "stop_reasons": [None], "moe_routermap": [rm]}
+                "stop_reasons": [None], "moe_routermap": [rm], "spec_decode_metrics": [self.spec]}
 
 
 def make_engine(replies, **kw):
@@ -99,6 +100,23 @@ def test_multi_turn_session_reuses_recorded_tokens():
     n_resp = len(resp1) + len(tok.encode("second<|im_end|>"))
     assert sum(step.masks) == n_resp and step.tokens[: len(p1)] == p1
     assert [lp for lp, m in zip(step.logprobs, step.masks) if m] == [-0.5] * n_resp
+    assert (p.metrics.spec_draft_tokens, p.metrics.spec_verify_count) == (0, 0)
+
+
+def test_speculative_decoding_counts_reach_the_program_metrics():
+    eng, samp, tok = make_engine(["one<|im_end|>", "two<|im_end|>"])
+    samp.spec = {"num_draft_tokens": 8, "num_accepted_tokens": 5, "num_completions": 3}
+
+    async def go():
+        sid = await eng.init_session("g1", {})
+        m = [{"role": "user", "content": "q"}]
+        a1, _, _ = await eng.generate(m, sid)
+        await eng.generate(m + [{"role": "assistant", "content": a1}, {"role": "user", "content": "more"}], sid)
+        await eng.end_session(sid, reward=0.0)
+        return await eng.get_finished_programs()
+
+    (p,) = eng.run_in_engine_loop(go())
+    assert (p.metrics.spec_draft_tokens, p.metrics.spec_accepted_tokens, p.metrics.spec_verify_count) == (16, 10, 6)
 
 
 def test_truncation_and_prompt_limits():

@@ -268,6 +268,12 @@ def _speculative_run(device, dtype, exact):
                 assert a.token_ids == b.token_ids, temp
                 assert (torch.tensor(a.logprobs) - torch.tensor(b.logprobs)).abs().max().item() < 1e-4
         assert 0 <= spec.stats["spec_accepted_tokens"] <= spec.stats["spec_draft_tokens"]
+        # every request reports its own rounds; together they are the engine's totals, and plain decoding reports none
+        per = [o.spec_decode_metrics for o in got if o.spec_decode_metrics is not None]
+        assert per and all(o.spec_decode_metrics is None for o in want)
+        assert sum(m.num_draft_tokens for m in per) == spec.stats["spec_draft_tokens"]
+        assert sum(m.num_accepted_tokens for m in per) == spec.stats["spec_accepted_tokens"]
+        assert all(m.num_completions > 0 and 0.0 <= m.accept_rate <= 1.0 and m.accept_length >= 1.0 for m in per)
     return spec
 
 
