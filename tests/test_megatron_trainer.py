@@ -1,4 +1,4 @@
-"""Model-parallel trainer worker: tp=2 (x dp=1) and tp=2 x dp=2 worker groups on CPU (gloo) give the same
+"""Model-parallel trainer worker: tp=2 x dp=2 worker groups (and the other layouts below) on CPU (gloo) give the same
 losses, gradient norms and updated parameters as the single-process data-parallel trainer."""
 import pytest
 import torch
@@ -73,7 +73,7 @@ def test_tensor_parallel_trainer_matches_data_parallel_trainer(world, tp):
 @pytest.mark.timeout(900)
 @pytest.mark.parametrize("world,ep", [(4, 2)])
 def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
-    """ep=2 (x edp=1 or 2): every rank trains on its own rows, experts are split over the group."""
+    """ep=2 x edp=2: every rank trains on its own rows, experts are split over the group."""
     import numpy as np
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-moe"), 1, vocab=2048)
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, "tiny-moe", ep), world, vocab=2048)
@@ -87,7 +87,7 @@ def test_expert_parallel_trainer_matches_data_parallel_trainer(world, ep):
 @pytest.mark.timeout(900)
 @pytest.mark.parametrize("world", [4])
 def test_tensor_and_expert_parallel_over_one_group_matches_data_parallel_trainer(world):
-    """tp = ep = 2 (x dp = 1 or 2): the group divides the attention heads AND the experts; the ranks of a group see the
+    """tp = ep = 2 x dp = 2: the group divides the attention heads AND the experts; the ranks of a group see the
     same rows, each routes its own share of the tokens to the experts' owners."""
     import numpy as np
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-moe"), 1, vocab=2048)
@@ -165,7 +165,7 @@ def test_model_parallel_checkpoint_exports_full_hf_model(tmp_path, kind):
 @pytest.mark.timeout(900)
 @pytest.mark.parametrize("world,pp", [(4, 2)])
 def test_pipeline_parallel_trainer_matches_data_parallel_trainer(world, pp):
-    """Two pipeline stages (x dp=1 or 2): same log-probs, gradient norm and update as the single-process trainer."""
+    """Two pipeline stages x dp=2: same log-probs, gradient norm and update as the single-process trainer."""
     import numpy as np
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied"), 1)
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, "tiny-qwen3-untied", pp=pp), world)
