@@ -147,12 +147,19 @@ class TPPPMoEModel(TPPPDenseModel):
     SPARSE = True
 
     def __init__(self, cfg: ModelConfig, tp: TPContext, ep, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16):
-        assert ep.world == tp.world and ep.rank == tp.rank, "experts are divided over the tensor-parallel group's own ranks"
-        assert cfg.num_experts % tp.world == 0, f"{cfg.num_experts} experts do not divide over {tp.world} ranks"
-        self.ep = ep if ep.world > 1 else None
-        self.ep_world = ep.world
+        """``ep``: an ``EPContext`` over the stage's tensor-parallel ranks, or None for expert TENSOR parallelism (every rank
+        of the stage keeps a slice of every expert of the stage's layers)."""
+        if ep is not None:
+            assert ep.world == tp.world and ep.rank == tp.rank, "experts are divided over the tensor-parallel group's own ranks"
+            assert cfg.num_experts % tp.world == 0, f"{cfg.num_experts} experts do not divide over {tp.world} ranks"
+            self.ep = ep if ep.world > 1 else None
+            self.ep_world = ep.world
+        else:
+            assert cfg.moe_intermediate_size % tp.world == 0, f"expert width {cfg.moe_intermediate_size} does not divide over {tp.world} ranks"
+            self.ep = None
+            self.etp_world = tp.world
         super().__init__(cfg, tp, pp, block_group, device=device, dtype=dtype)
-        self.params.expert_offset = tp.rank * (cfg.num_experts // tp.world)
+        self.params.expert_offset = tp.rank * (cfg.num_experts // tp.world) if self.ep_world > 1 else 0
         self.capture_routing, self.last_routing = False, None
         self._ids: dict = {}
 
@@ -170,7 +177,8 @@ class TPPPMoEModel(TPPPDenseModel):
 
 def _borrow_sparse_mlp() -> None:
     from .tp_moe import TPMoEModel
-    for name in ("_route", "_experts", "_combine", "_moe_rebuild", "_moe_bwd", "_replay_local", "_mlp_fwd", "_mlp_bwd"):
+    for name in ("_route", "_experts", "_combine", "_moe_rebuild", "_moe_bwd", "_replay_local", "_mlp_fwd", "_mlp_bwd",
+                 "_etp_experts", "_etp_fwd", "_etp_bwd"):
         setattr(TPPPMoEModel, name, getattr(TPMoEModel, name))
 
 

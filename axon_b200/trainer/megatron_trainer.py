@@ -168,14 +168,17 @@ class TrainerWorker(_Base):
         rows = int(_get(self.config, "max_token_len_per_gpu", 16384))
         rows = (rows // tp + 127) // 128 * 128 + 128
         sparse = mcfg.num_experts > 0
-        assert sparse == (self.ep_size > 1), "expert_model_parallel_size goes with a mixture-of-experts model (and only with one)"
+        assert sparse == (self.ep_size > 1 or self.etp_size > 1), \
+            "expert_model_parallel_size / expert_tensor_parallel_size go with a mixture-of-experts model (and only with one)"
         width = max(mcfg.qkv_size, mcfg.hidden_size) if sparse else max(mcfg.qkv_size, 2 * mcfg.intermediate_size, mcfg.hidden_size)
         ctx = TPContext(tp_group, self.device, max_rows_per_rank=rows, max_width=width)
         stage_ctx = PipelineContext(pp_group, self.device, ends_group=ends_group)
         if sparse:
-            from ..parallel.ep import EPContext
-            ep = EPContext(tp_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, max_tokens=rows,
-                           top_k=mcfg.num_experts_per_tok)
+            ep = None                 # expert TENSOR parallelism: a slice of every expert per rank of the stage
+            if self.ep_size > 1:
+                from ..parallel.ep import EPContext
+                ep = EPContext(tp_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, max_tokens=rows,
+                               top_k=mcfg.num_experts_per_tok)
             model = TPPPMoEModel(mcfg, ctx, ep, stage_ctx, block_group, device=self.device, dtype=dtype)
         else:
             model = TPPPDenseModel(mcfg, ctx, stage_ctx, block_group, device=self.device, dtype=dtype)

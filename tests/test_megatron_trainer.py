@@ -290,11 +290,13 @@ def test_interleaved_pipeline_chunks_match_single_process(world, pp, vpp, cap, m
 
 
 @pytest.mark.timeout(900)
-def test_sparse_model_with_tensor_and_expert_parallel_pipeline_stages_matches_single_process():
-    """world = 4 as pipeline 2 x (tensor = expert = 2), token cap 64 so that every row is its own micro-batch and several
-    are in flight: log-probs, loss, gradient norm and update equal the single-process trainer."""
+@pytest.mark.parametrize("how", ["ep", "etp"])
+def test_sparse_model_with_tensor_and_expert_parallel_pipeline_stages_matches_single_process(how):
+    """world = 4 as pipeline 2 x (tensor = expert = 2) - whole experts per rank, or a slice of every expert per rank (expert
+    tensor parallelism) - token cap 64 so that every row is its own micro-batch and several are in flight: log-probs,
+    loss, gradient norm and update equal the single-process trainer."""
     import numpy as np
-    ref_cfg, got_cfg = _cfg(1, "tiny-moe"), _cfg(2, "tiny-moe", ep=2, pp=2)
+    ref_cfg, got_cfg = _cfg(1, "tiny-moe"), (_cfg(2, "tiny-moe", ep=2, pp=2) if how == "ep" else _cfg(2, "tiny-moe", etp=2, pp=2))
     ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = 64
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1, vocab=2048)
     got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 4, vocab=2048)
