@@ -21,7 +21,7 @@ from ..ops import rope as R
 from ..parallel.tp import TPContext
 from .config import ModelConfig
 from .dense import DenseModel, PackedBatch
-from .pp_dense import PipelineContext, PipelineSchedule, stage_keeps, stage_layers
+from .pp_dense import PipelineContext, PipelineSchedule, chunk_layers, stage_keeps
 from .tp_dense import TPDenseModel, pad_packed_batch
 
 
@@ -40,15 +40,19 @@ class BlockContext:
 
 
 class TPPPDenseModel(PipelineSchedule, TPDenseModel):
-    def __init__(self, cfg: ModelConfig, tp: TPContext, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16):
-        assert pp.world <= cfg.num_hidden_layers
+    def __init__(self, cfg: ModelConfig, tp: TPContext, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16,
+                 virtual: int = 1):
+        """``virtual``: model chunks per pipeline rank (interleaved stages, as in ``pp_dense.PPDenseModel``)."""
+        assert pp.world * virtual <= cfg.num_hidden_layers, "every (virtual) stage needs at least one layer"
+        assert virtual == 1 or pp.world > 1
         if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
             assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
         self.pp = pp
-        self.stage, self.stages = pp.rank, pp.world
+        self.stage, self.stages, self.vpp = pp.rank, pp.world, int(virtual)
         TPDenseModel.__init__(self, cfg, tp, device=device, dtype=dtype, vocab_parallel_head=False,
-                              holds=stage_keeps(cfg, self.stages, self.stage))
-        self.layers = stage_layers(cfg.num_hidden_layers, self.stages, self.stage)
+                              holds=stage_keeps(cfg, self.stages, self.stage, self.vpp))
+        self.chunks = chunk_layers(cfg.num_hidden_layers, self.stages, self.stage, self.vpp)
+        self.layers = self.chunks[0]
         self.mp_ctx = BlockContext(block_group, tp.world * pp.world, tp.world)
         self.recompute = "full"
 
@@ -81,23 +85,25 @@ class TPPPDenseModel(PipelineSchedule, TPDenseModel):
     def _stream_shape(self, batch: PackedBatch):
         return (self._padded_len(batch) // self.tp.world, self.cfg.hidden_size)
 
-    def _layers_fwd(self, batch: PackedBatch, inp, save: bool):
+    def _layers_fwd(self, batch: PackedBatch, inp, save: bool, chunk: int = 0):
         c = self.cfg
         self.tp.begin_pass()
+        very_first, very_last = self.first and chunk == 0, self.last and chunk == self.vpp - 1
         padded, t_real = pad_packed_batch(batch, 128 * self.tp.world)
         T = padded.input_ids.numel()
         sl = self.local_slice(T)
         tables = R.rope_tables(max(int(padded.max_seqlen) or c.max_position_embeddings, 8), c.head_dim, c.rope_theta, self.device, c.rotary_dim)
-        if self.first:
+        if very_first:
             x, delta = A.embedding_fwd(padded.input_ids[sl].contiguous(), self.params["model.embed_tokens.weight"]), None
         else:
             x, delta = inp
         inputs = []
-        for l in self.layers:
+        for l in self.chunks[chunk]:
             x, delta, xin = self.layer_fwd(l, x, delta, padded, tables)
             if save:
                 inputs.append(xin)
-        return x, delta, dict(batch=padded, tables=tables, inputs=inputs, sl=sl, T=T, T_real=t_real)
+        return x, delta, dict(batch=padded, tables=tables, inputs=inputs, sl=sl, T=T, T_real=t_real, layers=self.chunks[chunk],
+                              very_first=very_first, very_last=very_last)
 
     def _head_fwd(self, x, delta, batch: PackedBatch, temperature: float, state: dict):
         hf, rstd_f, xf = N.rmsnorm_fwd(x, self.params["model.norm.weight"], self.cfg.rms_norm_eps, delta=delta)
@@ -117,7 +123,7 @@ class TPPPDenseModel(PipelineSchedule, TPDenseModel):
     def _state_bwd(self, s: dict, upstream):
         self.tp.begin_pass()
         batch, tables = s["batch"], s["tables"]
-        if self.last:
+        if s["very_last"]:
             g_lp, g_ent = self._cut(upstream[0], s), self._cut(upstream[1], s)
             dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
                                 dweight=self.head_grad())
@@ -125,9 +131,9 @@ class TPPPDenseModel(PipelineSchedule, TPDenseModel):
         else:
             dx = upstream
         kept = s["inputs"]
-        for l in reversed(self.layers):
+        for l in reversed(s["layers"]):
             dx = self.layer_bwd(l, kept.pop(), dx, batch, tables)
-        if self.first:
+        if s["very_first"]:
             A.embedding_bwd(batch.input_ids[s["sl"]].contiguous(), dx, self.params.grads["model.embed_tokens.weight"])
             return None
         return dx
@@ -146,7 +152,8 @@ class TPPPMoEModel(TPPPDenseModel):
     recipes/math/train_polaris_qwen_30b_a3b.sh.)"""
     SPARSE = True
 
-    def __init__(self, cfg: ModelConfig, tp: TPContext, ep, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16):
+    def __init__(self, cfg: ModelConfig, tp: TPContext, ep, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16,
+                 virtual: int = 1):
         """``ep``: an ``EPContext`` over the stage's tensor-parallel ranks, or None for expert TENSOR parallelism (every rank
         of the stage keeps a slice of every expert of the stage's layers)."""
         if ep is not None:
@@ -158,14 +165,14 @@ class TPPPMoEModel(TPPPDenseModel):
             assert cfg.moe_intermediate_size % tp.world == 0, f"expert width {cfg.moe_intermediate_size} does not divide over {tp.world} ranks"
             self.ep = None
             self.etp_world = tp.world
-        super().__init__(cfg, tp, pp, block_group, device=device, dtype=dtype)
+        super().__init__(cfg, tp, pp, block_group, device=device, dtype=dtype, virtual=virtual)
         self.params.expert_offset = tp.rank * (cfg.num_experts // tp.world) if self.ep_world > 1 else 0
         self.capture_routing, self.last_routing = False, None
         self._ids: dict = {}
 
-    def _layers_fwd(self, batch: PackedBatch, inp, save: bool):
+    def _layers_fwd(self, batch: PackedBatch, inp, save: bool, chunk: int = 0):
         self._ids = {}
-        x, delta, state = super()._layers_fwd(batch, inp, save)
+        x, delta, state = super()._layers_fwd(batch, inp, save, chunk)
         if save:
             state["moe_ids"] = self._ids
         return x, delta, state

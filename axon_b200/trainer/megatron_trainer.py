@@ -44,9 +44,8 @@ class TrainerWorker(_Base):
                                       f"ranks: set expert_model_parallel_size == tensor_model_parallel_size (got ep={self.ep_size}, tp={self.tp_size})")
         self.pp_size = int(_get(m, "pipeline_model_parallel_size", 1) or 1)
         self.vpp_size = int(_get(m, "virtual_pipeline_model_parallel_size", 1) or 1)
-        if self.vpp_size > 1 and (self.pp_size < 2 or self.tp_size > 1):
-            raise NotImplementedError("virtual pipeline stages interleave the chunks of a plain pipeline (pipeline_model_parallel_size "
-                                      ">= 2, no tensor parallelism inside the stages)")
+        if self.vpp_size > 1 and self.pp_size < 2:
+            raise NotImplementedError("virtual pipeline stages interleave the chunks of a pipeline: pipeline_model_parallel_size >= 2")
         if self.pp_size > 1 and self.ep_size > 1 and self.tp_size != self.ep_size:
             raise NotImplementedError("pipeline stages of a sparse model divide their experts over the stage's tensor-parallel "
                                       "group: set expert_model_parallel_size == tensor_model_parallel_size > 1")
@@ -179,9 +178,9 @@ class TrainerWorker(_Base):
                 from ..parallel.ep import EPContext
                 ep = EPContext(tp_group, self.device, mcfg.num_experts, mcfg.hidden_size, mcfg.moe_intermediate_size, max_tokens=rows,
                                top_k=mcfg.num_experts_per_tok)
-            model = TPPPMoEModel(mcfg, ctx, ep, stage_ctx, block_group, device=self.device, dtype=dtype)
+            model = TPPPMoEModel(mcfg, ctx, ep, stage_ctx, block_group, device=self.device, dtype=dtype, virtual=self.vpp_size)
         else:
-            model = TPPPDenseModel(mcfg, ctx, stage_ctx, block_group, device=self.device, dtype=dtype)
+            model = TPPPDenseModel(mcfg, ctx, stage_ctx, block_group, device=self.device, dtype=dtype, virtual=self.vpp_size)
         ref = FlatParams(mcfg, "cpu", dtype)
         if os.path.isdir(str(model_path)) and has_hf_weights(model_path):
             ref.load_hf_state_dict(dict(iter_hf_weights(model_path)))

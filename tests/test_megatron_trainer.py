@@ -384,3 +384,20 @@ def test_tensor_parallel_trainer_with_multi_token_prediction_matches_single_proc
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.timeout(900)
+def test_tensor_parallel_inside_interleaved_pipeline_chunks_matches_single_process():
+    """world = 4 as pipeline 2 x tensor 2 with two model chunks per pipeline rank, every row its own micro-batch: equals the
+    single-process trainer."""
+    import numpy as np
+    name = "tiny-qwen3-untied-5l"
+    ref_cfg, got_cfg = _cfg(1, name), _cfg(2, name, pp=2, vpp=2)
+    ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = 64
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 4)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(np.mean(got[1]["actor/loss"]), np.mean(ref[1]["actor/loss"]), rtol=1e-3, atol=1e-5)
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
