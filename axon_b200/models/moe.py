@@ -31,6 +31,8 @@ from .dense import DenseModel, PackedBatch
 
 
 class MoEModel(DenseModel):
+    ROWS_DIFFER_IN_GROUP = True       # the ranks of an expert-parallel group train on different rows (unlike tensor-parallel peers)
+
     def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params=None, ep=None):
         """``ep``: an ``EPContext`` — every rank then holds only its E/W experts (``w13`` / ``w2`` have a
         leading dimension of E/W) and tokens reach their experts through peer memory."""
@@ -111,7 +113,7 @@ class MoEModel(DenseModel):
 
     def _replay_for(self, l: int, batch):
         rm = getattr(batch, "routermap", None) if batch is not None else None
-        if rm is None:
+        if rm is None or l >= rm.shape[1]:          # the record covers the decoder layers, not a prediction module behind them
             return None
         return rm[:, l, :].contiguous()
 

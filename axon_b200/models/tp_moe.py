@@ -62,7 +62,7 @@ class TPMoEModel(TPDenseModel):
 
     def _replay_local(self, l: int, batch):
         rm = getattr(batch, "routermap", None)
-        if rm is None:
+        if rm is None or l >= rm.shape[1]:
             return None
         return rm[self.local_slice(batch.input_ids.numel()), l, :].contiguous()
 
@@ -80,7 +80,7 @@ class TPMoEModel(TPDenseModel):
         from ..ops import moe as M
         hf = self.tp.all_gather_rows(h2)
         rm = getattr(batch, "routermap", None)
-        logits, ids, w = self._route(l, hf, None if rm is None else rm[:, l, :].contiguous())
+        logits, ids, w = self._route(l, hf, None if rm is None or l >= rm.shape[1] else rm[:, l, :].contiguous())
         lay, _, _, _, ys = self._etp_experts(l, hf, ids)
         self._ids[l] = ids
         if self.capture_routing:

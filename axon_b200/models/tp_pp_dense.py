@@ -40,6 +40,8 @@ class BlockContext:
 
 
 class TPPPDenseModel(PipelineSchedule, TPDenseModel):
+    MTP_OK = False
+
     def __init__(self, cfg: ModelConfig, tp: TPContext, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16,
                  virtual: int = 1):
         """``virtual``: model chunks per pipeline rank (interleaved stages, as in ``pp_dense.PPDenseModel``)."""

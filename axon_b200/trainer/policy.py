@@ -365,6 +365,8 @@ class PolicyEngine:
             cnt = sum((mb.batch["attention_mask"].sum(1) - 2).clamp_min(0).sum() for mb in mbs).float().reshape(1)
             if self.world > 1:
                 dist.all_reduce(cnt, group=self.pg)
+            if getattr(self.model, "ROWS_DIFFER_IN_GROUP", False) and getattr(self.model, "ep", None) is not None:
+                self.model.ep.all_reduce_(cnt)          # expert-parallel peers are outside the optimizer's group and bring rows of their own
             self.model.mtp_scale = self.mtp_loss_coef / max(float(cnt), 1.0)
         packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device, mb) for mb in mbs]
         if hasattr(self.model, "train_many"):

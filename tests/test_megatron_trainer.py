@@ -401,3 +401,24 @@ def test_tensor_parallel_inside_interleaved_pipeline_chunks_matches_single_proce
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("kind", ["ep", "tp-ep", "tp-etp"])
+def test_sparse_model_with_multi_token_prediction_matches_single_process(monkeypatch, kind):
+    """The prediction module of a sparse model is a sparse layer of its own: under expert parallelism, tensor + expert
+    parallelism and expert tensor parallelism its experts are divided like the decoder's; reported loss, gradient norm and
+    update equal the single-process run."""
+    import numpy as np
+    monkeypatch.setenv("AXON_ENABLE_MTP", "1")
+    name = "tiny-moe-mtp"
+    got_cfg = {"ep": _cfg(1, name, ep=2), "tp-ep": _cfg(2, name, ep=2), "tp-etp": _cfg(2, name, etp=2)}[kind]
+    ref_cfg = _cfg(1, name)
+    ref_cfg["mtp_loss_scaling_factor"] = got_cfg["mtp_loss_scaling_factor"] = 0.3
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1, vocab=2048)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 2, vocab=2048)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    assert "actor/mtp_loss" in ref[1] and abs(np.mean(got[1]["actor/mtp_loss"]) - np.mean(ref[1]["actor/mtp_loss"])) < 1e-3
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)

@@ -153,3 +153,31 @@ def test_mtp_weights_round_trip_through_hf_names(tmp_path):
     m2 = DenseModel(cfg2, device="cpu", dtype=torch.float32)
     load_hf_weights(m2, str(tmp_path / "hf"))
     torch.testing.assert_close(m2.params.flat, m.params.flat, rtol=0, atol=4e-3)
+
+
+def test_sparse_model_replays_the_decoder_layers_and_routes_the_module_itself():
+    """A routing record from the sampler covers the decoder layers only; the prediction module behind them is a sparse
+    layer too and picks its own experts while the decoder layers replay theirs."""
+    from axon_b200.models.moe import MoEModel
+    cfg = get_config("tiny-moe-mtp")
+    model = MoEModel(cfg, device="cpu", dtype=torch.float32)
+    model.params.init_random(std=0.05, seed=1)
+    batch = PackedBatch.from_sequences([torch.randint(0, cfg.vocab_size, (n,)) for n in (19, 6)], "cpu")
+    T = batch.input_ids.numel()
+    g = torch.Generator().manual_seed(2)
+    rm = torch.stack([torch.stack([torch.randperm(cfg.num_experts, generator=g)[:cfg.num_experts_per_tok] for _ in range(cfg.num_hidden_layers)])
+                      for _ in range(T)])                                   # [T, decoder layers, top-k]
+    batch.routermap = rm
+    model.mtp_scale = 0.3
+    model.capture_routing, model.last_routing = True, None
+    model.params.alloc_grads()
+    model.params.zero_grads()
+    lp, _ = model.forward(batch, 1.0, save_for_backward=True)
+    routed = model.last_routing
+    assert len(routed) == cfg.num_hidden_layers + 1
+    for l in range(cfg.num_hidden_layers):
+        assert torch.equal(routed[l].sort(1).values.long(), rm[:, l].sort(1).values)
+    model.backward(torch.ones_like(lp), None)
+    L = cfg.num_hidden_layers
+    assert float(model.params.grads[f"model.layers.{L}.mlp.experts.w13_weight"].abs().max()) > 0
+    assert float(model.params.grads[f"model.layers.{L}.mlp.gate.weight"].abs().max()) > 0
