@@ -179,6 +179,7 @@ PRESETS = {"qwen3-8b": qwen3_8b, "llama3-8b": llama3_8b, "qwen2.5-7b": qwen2_5_7
            "tiny-glm4": lambda: _with(tiny_qwen3(), model_type="glm4", qk_norm=False, attention_bias=True, partial_rotary_factor=0.5,
                                     rope_interleaved=True, sandwich_norm=True, tie_word_embeddings=False),
            "tiny-qwen3-mtp": lambda: _with(tiny_qwen3(), num_nextn_predict_layers=1),
+           "tiny-qwen3-untied-mtp": lambda: _with(_untied(tiny_qwen3()), num_nextn_predict_layers=1),
            "tiny-moe-mtp": lambda: _with(tiny_moe(), num_nextn_predict_layers=1),
            "tiny-qwen3-5l": lambda: _with(tiny_qwen3(), num_hidden_layers=5),
            "tiny-qwen3-untied-5l": lambda: _with(_untied(tiny_qwen3()), num_hidden_layers=5), "tiny-gpu": tiny_gpu, "tiny-moe": tiny_moe, "tiny-moe-gpu": tiny_moe_gpu}

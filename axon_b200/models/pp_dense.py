@@ -107,12 +107,17 @@ def virtual_schedule(stages: int, virtual: int, micro: int, train: bool = True, 
 def stage_keeps(cfg: ModelConfig, stages: int, stage: int, virtual: int = 1):
     """Predicate over parameter names: does ``stage`` hold this parameter?"""
     keep = tuple(f"model.layers.{l}." for rng in chunk_layers(cfg.num_hidden_layers, stages, stage, virtual) for l in rng)
+    L = cfg.num_hidden_layers
+    after = tuple(f"model.layers.{l}." for l in range(L, L + cfg.num_nextn_predict_layers))      # multi-token-prediction modules
 
     def holds(name: str) -> bool:
         if name.startswith("model.layers."):
+            if after and name.startswith(after):
+                return stage == stages - 1         # they read the stream that enters the final norm
             return name.startswith(keep) if keep else False
         if name == "model.embed_tokens.weight":
-            return stage == 0 or (cfg.tie_word_embeddings and stage == stages - 1)      # tied: the last stage's head reads it too
+            # tied: the last stage's head reads it too; so does a prediction module, which embeds the next token
+            return stage == 0 or ((cfg.tie_word_embeddings or bool(after)) and stage == stages - 1)
         return stage == stages - 1         # final norm, head, value head
     return holds
 
@@ -396,10 +401,11 @@ class PPDenseModel(PipelineSchedule, DenseModel):
         number of micro-batches, more point-to-point traffic)."""
         assert cfg.num_experts == 0, "pipeline stages are built for dense models"
         assert virtual == 1 or pp.world > 1, "virtual stages need at least two pipeline ranks"
-        if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
-            assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
+        if (cfg.tie_word_embeddings or cfg.num_nextn_predict_layers > 0) and pp.world > 2 and pp.rank in (0, pp.world - 1):
+            assert pp.ends_group is not None, "an embedding held by the first and the last of more than two stages needs the group of the two"
         assert pp.world * virtual <= cfg.num_hidden_layers, "every (virtual) stage needs at least one layer"
         self.pp = pp
+        self.mtp_records: list = []       # (sum of negative log-probs, targets) of the prediction module per micro-batch, last stage
         self.stage, self.stages, self.vpp = pp.rank, pp.world, int(virtual)
         params = FlatParams(cfg, torch.device(device), dtype, layout=stage_layout(cfg, self.stages, self.stage, self.vpp))
         super().__init__(cfg, device, dtype, params=params)
@@ -417,9 +423,11 @@ class PPDenseModel(PipelineSchedule, DenseModel):
         return []
 
     # Tied embeddings: the table lives on the first stage (lookup) and on the last (output head). Both copies start
-    # equal, their gradients are summed over the two stages before the optimizer, so they stay equal.
+    # equal, their gradients are summed over the two stages before the optimizer, so they stay equal. A multi-token-
+    # prediction module (on the last stage) looks the next token up in the same table, tied or not.
     def _shares_embedding(self) -> bool:
-        return self.cfg.tie_word_embeddings and self.stages > 1 and (self.first or self.last)
+        c = self.cfg
+        return (c.tie_word_embeddings or c.num_nextn_predict_layers > 0) and self.stages > 1 and (self.first or self.last)
 
     def sync_replicated_grads(self) -> None:
         if self._shares_embedding() and self.params.grad_flat is not None:
@@ -457,6 +465,10 @@ class PPDenseModel(PipelineSchedule, DenseModel):
         hf, rstd_f, xf = N.rmsnorm_fwd(x, self.weights["model.norm.weight"], self.cfg.rms_norm_eps, delta=delta)
         lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), batch.labels, temperature)
         state.update(hf=hf, rstd_f=rstd_f, xf=xf, lse=lse, ent=ent, temperature=temperature)
+        if self.cfg.num_nextn_predict_layers > 0 and self.mtp_scale:       # the engine sets the scale for training passes only
+            from .mtp import mtp_fwd
+            self.mtp_last = mtp_fwd(self, state)
+            self.mtp_records.append(self.mtp_last)
         return lp, ent
 
     def _state_bwd(self, s: dict, upstream):
@@ -469,7 +481,11 @@ class PPDenseModel(PipelineSchedule, DenseModel):
             g_ent = None if g_entropy is None else g_entropy.float().contiguous()
             dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), batch.labels, s["lse"], s["ent"], g_lp, g_ent,
                                 s["temperature"], dweight=self.head_grad())
-            dx = N.rmsnorm_bwd(dhf, s["xf"], self.weights["model.norm.weight"], s["rstd_f"], self._wgrad("model.norm.weight"))
+            extra = None
+            if "mtp" in s:
+                from .mtp import mtp_bwd
+                extra = mtp_bwd(self, s, float(self.mtp_scale))
+            dx = N.rmsnorm_bwd(dhf, s["xf"], self.weights["model.norm.weight"], s["rstd_f"], self._wgrad("model.norm.weight"), dres=extra)
         else:
             dx = upstream
         kept = s["layer_inputs"]

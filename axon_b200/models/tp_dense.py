@@ -107,7 +107,7 @@ class TPDenseModel:
     SPARSE = False           # the sparse subclass (tp_moe.TPMoEModel) replaces the MLP hooks
     ep_world = 1
     etp_world = 1
-    MTP_OK = True           # pipeline stages and context-parallel ranks switch it off
+    MTP_OK = True           # context-parallel ranks switch it off
 
     def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False,
                  holds=None):
@@ -116,7 +116,7 @@ class TPDenseModel:
         assert cfg.num_key_value_heads % tp.world == 0 and (self.SPARSE or cfg.intermediate_size % tp.world == 0)
         assert not cfg.sandwich_norm, "sandwich-norm families (GLM-4) run under data / sequence / context / pipeline parallelism; the tensor-parallel layer code does not carry the extra norms yet"
         assert cfg.num_nextn_predict_layers == 0 or self.MTP_OK, \
-            "the multi-token-prediction module is trained by the data-parallel, the tensor-parallel and the tensor + expert parallel trainer"
+            "the multi-token-prediction module is not built for context-parallel ranks"
         self.cfg, self.tp = cfg, tp
         self.device, self.dtype = torch.device(device), dtype
         self.shard_head = bool(vocab_parallel_head) and not cfg.tie_word_embeddings and tp.world > 1

@@ -40,16 +40,15 @@ class BlockContext:
 
 
 class TPPPDenseModel(PipelineSchedule, TPDenseModel):
-    MTP_OK = False
-
     def __init__(self, cfg: ModelConfig, tp: TPContext, pp: PipelineContext, block_group=None, device="cuda", dtype=torch.bfloat16,
                  virtual: int = 1):
         """``virtual``: model chunks per pipeline rank (interleaved stages, as in ``pp_dense.PPDenseModel``)."""
         assert pp.world * virtual <= cfg.num_hidden_layers, "every (virtual) stage needs at least one layer"
         assert virtual == 1 or pp.world > 1
-        if cfg.tie_word_embeddings and pp.world > 2 and pp.rank in (0, pp.world - 1):
-            assert pp.ends_group is not None, "tied embeddings over more than two stages need the group of the first and the last stage"
+        if (cfg.tie_word_embeddings or cfg.num_nextn_predict_layers > 0) and pp.world > 2 and pp.rank in (0, pp.world - 1):
+            assert pp.ends_group is not None, "an embedding held by the first and the last of more than two stages needs the group of the two"
         self.pp = pp
+        self.mtp_records: list = []       # (sum of negative log-probs, targets) of the prediction module per micro-batch, last stage
         self.stage, self.stages, self.vpp = pp.rank, pp.world, int(virtual)
         TPDenseModel.__init__(self, cfg, tp, device=device, dtype=dtype, vocab_parallel_head=False,
                               holds=stage_keeps(cfg, self.stages, self.stage, self.vpp))
@@ -60,7 +59,8 @@ class TPPPDenseModel(PipelineSchedule, TPDenseModel):
 
     # ------------------------------------------------------------------ parameters shared between ranks
     def _shares_embedding(self) -> bool:
-        return self.cfg.tie_word_embeddings and self.stages > 1 and (self.first or self.last)
+        c = self.cfg             # tied head, or a multi-token-prediction module: both read the table on the last stage
+        return (c.tie_word_embeddings or c.num_nextn_predict_layers > 0) and self.stages > 1 and (self.first or self.last)
 
     def sync_replicated_grads(self) -> None:
         TPDenseModel.sync_replicated_grads(self)            # norms / embedding / head: partial per tensor-parallel rank
@@ -112,6 +112,9 @@ class TPPPDenseModel(PipelineSchedule, TPDenseModel):
         labels = state["batch"].labels[state["sl"]].contiguous()
         lp, ent, lse = LM.lmhead_fwd(hf, self.head_weight(), labels, temperature)
         state.update(hf=hf, rstd_f=rstd_f, xf=xf, lse=lse, ent=ent, labels=labels, temperature=temperature)
+        if self.cfg.num_nextn_predict_layers > 0 and self.mtp_scale:       # the engine sets the scale for training passes only
+            self.mtp_last = self._mtp_fwd(state)
+            self.mtp_records.append(self.mtp_last)
         n = state["T_real"]
         return self.tp.all_gather_rows(lp.contiguous())[:n], self.tp.all_gather_rows(ent.contiguous())[:n]
 
@@ -129,7 +132,9 @@ class TPPPDenseModel(PipelineSchedule, TPDenseModel):
             g_lp, g_ent = self._cut(upstream[0], s), self._cut(upstream[1], s)
             dhf = LM.lmhead_bwd(s["hf"], self.head_weight(), s["labels"], s["lse"], s["ent"], g_lp, g_ent, s["temperature"],
                                 dweight=self.head_grad())
-            dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"])
+            extra = self._mtp_bwd(s, float(self.mtp_scale)) if "mtp" in s else None
+            dx = N.rmsnorm_bwd(dhf, s["xf"], self.params["model.norm.weight"], s["rstd_f"], self.params.grads["model.norm.weight"],
+                               dres=extra)
         else:
             dx = upstream
         kept = s["inputs"]

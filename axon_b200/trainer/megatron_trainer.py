@@ -105,7 +105,7 @@ class TrainerWorker(_Base):
         pp_group, dp_group = self._make_groups(self.pp_size)
         self.pg, self._mp_group = dp_group, pp_group
         ends_group = None
-        if mcfg.tie_word_embeddings and self.pp_size > 2:      # first and last stage of every pipeline share the embedding
+        if (mcfg.tie_word_embeddings or mcfg.num_nextn_predict_layers > 0) and self.pp_size > 2:      # first and last stage of every pipeline share the embedding
             for i in range(self.world_size // self.pp_size):
                 ranks = [i * self.pp_size, (i + 1) * self.pp_size - 1]
                 g = dist.new_group(ranks)
@@ -161,7 +161,7 @@ class TrainerWorker(_Base):
         dp_group = make([[b * block + j for b in range(n_rep)] for j in range(block)])
         block_group = make([list(range(b * block, (b + 1) * block)) for b in range(n_rep)])
         ends_group = None
-        if mcfg.tie_word_embeddings and pp > 2:
+        if (mcfg.tie_word_embeddings or mcfg.num_nextn_predict_layers > 0) and pp > 2:
             ends_group = make([[b * block + t, b * block + (pp - 1) * tp + t] for b in range(n_rep) for t in range(tp)])
         self.pg, self._mp_group = dp_group, block_group
         rows = int(_get(self.config, "max_token_len_per_gpu", 16384))

@@ -373,6 +373,11 @@ class PolicyEngine:
             # pipeline stages: the model orders forwards and backwards of the micro-batches (1F1B) and calls
             # the loss on the last stage only; its metrics are then handed to the other stages
             self.model.train_many([pk.batch for pk in packs], temp, lambda i, lp, ent: loss_step(mbs[i], packs[i], lp, ent))
+            if mtp:
+                for nll, n in getattr(self.model, "mtp_records", []):           # filled on the stage that holds the module
+                    metrics.setdefault("mtp_loss", []).append(float(nll) / max(float(n), 1.0))
+                self.model.mtp_records = []
+                self.model.mtp_scale = 0.0
             return self.model.share_from_last(metrics)
         for mb, pk in zip(mbs, packs):
             lp_packed, ent_packed = self.model.forward(pk.batch, temp, save_for_backward=True)

@@ -422,3 +422,48 @@ def test_sparse_model_with_multi_token_prediction_matches_single_process(monkeyp
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("kind", ["tied", "untied-micro"])
+def test_pipeline_trainer_with_multi_token_prediction_matches_single_process(monkeypatch, tmp_path, kind):
+    """The prediction module sits on the last stage and embeds the next token there, so the table lives on both ends of
+    the pipeline (tied or not) with its gradients summed; one micro-batch and one per row both equal the single process."""
+    import numpy as np
+    monkeypatch.setenv("AXON_ENABLE_MTP", "1")
+    name = "tiny-qwen3-mtp" if kind == "tied" else "tiny-qwen3-untied-mtp"
+    ref_cfg, got_cfg = _cfg(1, name), _cfg(1, name, pp=2)
+    ref_cfg["mtp_loss_scaling_factor"] = got_cfg["mtp_loss_scaling_factor"] = 0.3
+    if kind == "untied-micro":
+        ref_cfg["max_token_len_per_gpu"] = got_cfg["max_token_len_per_gpu"] = 64
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
+    d = str(tmp_path / "ck") if kind == "untied-micro" else None
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 2, save_dir=d)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    assert "actor/mtp_loss" in got[1] and abs(np.mean(got[1]["actor/mtp_loss"]) - np.mean(ref[1]["actor/mtp_loss"])) < 1e-3
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
+    if d is not None:          # the table is written once although both ends hold it; a single process reads the checkpoint back
+        single = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", _cfg(1, name), 1, load_dir=d)
+        torch.testing.assert_close(single[0], got[3], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("kind", ["dense", "sparse"])
+def test_tensor_parallel_pipeline_stages_with_multi_token_prediction_match_single_process(monkeypatch, kind):
+    """world = 4 as pipeline 2 x tensor 2 (the sparse model with tensor = expert 2), every row its own micro-batch: the
+    prediction module runs on the last stage's tensor-parallel group."""
+    import numpy as np
+    monkeypatch.setenv("AXON_ENABLE_MTP", "1")
+    name, vocab = ("tiny-qwen3-untied-mtp", 4096) if kind == "dense" else ("tiny-moe-mtp", 2048)
+    ref_cfg, got_cfg = _cfg(1, name), (_cfg(2, name, pp=2) if kind == "dense" else _cfg(2, name, ep=2, pp=2))
+    for c in (ref_cfg, got_cfg):
+        c["mtp_loss_scaling_factor"], c["max_token_len_per_gpu"] = 0.3, 64
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1, vocab=vocab)
+    got = _run("axon_b200.trainer.megatron_trainer.TrainerWorker", got_cfg, 4, vocab=vocab)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    assert "actor/mtp_loss" in got[1] and abs(np.mean(got[1]["actor/mtp_loss"]) - np.mean(ref[1]["actor/mtp_loss"])) < 1e-3
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
