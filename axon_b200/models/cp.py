@@ -14,6 +14,7 @@ import torch
 from ..parallel import cp as CP
 from .config import ModelConfig
 from .dense import DenseModel, PackedBatch
+from .mtp import SlicedModuleMixin, shifted_inputs
 
 
 class CPDenseModel(DenseModel):
@@ -30,7 +31,7 @@ class CPDenseModel(DenseModel):
         return CP.attn_bwd(self.cp, do, qkv_r, o, lse, batch.cu_seqlens, c.num_attention_heads, c.num_key_value_heads, c.head_dim)
 
 
-class CPModelAdapter:
+class CPModelAdapter(SlicedModuleMixin):
     """The interface of ``DenseModel`` (full packed batch in, full log-probs out, full-batch gradients in)
     on top of the context-parallel model: pads every sequence to a multiple of ``2 W`` tokens, hands the
     rank its zigzag chunks and puts the per-token results back into the order of the batch."""
@@ -42,6 +43,10 @@ class CPModelAdapter:
         self.cfg, self.params, self.device, self.dtype = model.cfg, model.params, model.device, model.dtype
         self._maps = None
         self._token_multiple = int(token_multiple)
+        self.same_rows_ranks = self.cp.world
+
+    def _mtp_group(self):
+        return self.cp.group if self.cp.world > 1 else None
 
     @property
     def recompute(self):
@@ -69,8 +74,12 @@ class CPModelAdapter:
         # positions of real tokens come from the batch (they need not start at 0), pads count on from 0
         pos[orig_pos_d] = batch.position_ids
         longest = int((new_cu[1:] - new_cu[:-1]).max())
-        return PackedBatch(padded(batch.input_ids, 0)[mine].contiguous(), pos[mine].contiguous(), cu_half,
-                           padded(batch.labels, -100)[mine].contiguous(), max(int(batch.max_seqlen or 0), longest))
+        local = PackedBatch(padded(batch.input_ids, 0)[mine].contiguous(), pos[mine].contiguous(), cu_half,
+                            padded(batch.labels, -100)[mine].contiguous(), max(int(batch.max_seqlen or 0), longest))
+        if self._wants_mtp():          # shifted within the whole sequences of the batch, then laid out like the ids
+            nxt, lab2 = shifted_inputs(batch)
+            local.mtp_inputs = (padded(nxt, 0)[mine].contiguous(), padded(lab2, -100)[mine].contiguous())
+        return local
 
     def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
         lp, ent = self.inner.forward(self._local(batch), temperature, save_for_backward)

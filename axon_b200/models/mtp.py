@@ -26,6 +26,39 @@ from ..ops import norm as N
 from .dense import PackedBatch
 
 
+class SlicedModuleMixin:
+    """For the adapters of models whose ranks hold a slice of every batch's tokens: the engine's switch reaches the
+    wrapped model, and the module's (sum of negative log-probs, targets) is summed over the ranks of the group."""
+
+    same_rows_ranks = 1          # ranks of the optimizer's group that train on the same rows (the engine counts targets once)
+
+    @property
+    def mtp_scale(self):
+        return self.inner.mtp_scale
+
+    @mtp_scale.setter
+    def mtp_scale(self, v):
+        self.inner.mtp_scale = v
+
+    def _wants_mtp(self) -> bool:
+        return self.cfg.num_nextn_predict_layers > 0 and bool(self.inner.mtp_scale)
+
+    def _mtp_group(self):
+        raise NotImplementedError
+
+    @property
+    def mtp_last(self):
+        import torch.distributed as dist
+        last = self.inner.mtp_last
+        if last is None:
+            return None
+        both = torch.stack([last[0].float(), last[1].float()])
+        group = self._mtp_group()
+        if group is not None:
+            dist.all_reduce(both, group=group)
+        return both[0], both[1]
+
+
 def shifted_inputs(batch: PackedBatch):
     """(ids of token t+1, labels = token t+2 or -100) per packed position."""
     labels = batch.labels
@@ -43,7 +76,8 @@ def mtp_fwd(model, s: dict) -> torch.Tensor:
     c, batch, L = model.cfg, s["batch"], model.cfg.num_hidden_layers
     p = f"model.layers.{L}."
     w = model.weights
-    nxt, lab2 = shifted_inputs(batch)
+    # a rank that holds a slice of the tokens (sequence- / context-parallel) gets the slice of the shifted ids with its batch
+    nxt, lab2 = getattr(batch, "mtp_inputs", None) or shifted_inputs(batch)
     e = A.embedding_fwd(nxt, w["model.embed_tokens.weight"])
     en, rstd_e, _ = N.rmsnorm_fwd(e, w[p + "enorm.weight"], c.rms_norm_eps)
     hn, rstd_h, _ = N.rmsnorm_fwd(s["xf"], w[p + "hnorm.weight"], c.rms_norm_eps)

@@ -16,6 +16,7 @@ from ..ops import attention as AT
 from ..parallel.ulysses import UlyssesContext
 from .config import ModelConfig
 from .dense import DenseModel, PackedBatch
+from .mtp import SlicedModuleMixin, shifted_inputs
 from .tp_dense import pad_packed_batch
 
 
@@ -54,7 +55,7 @@ class UlyssesDenseModel(DenseModel):
         return self.sp.scatter_rows(dqkv_h, self.seg_qkv_back, self.cfg.qkv_size)
 
 
-class UlyssesModelAdapter:
+class UlyssesModelAdapter(SlicedModuleMixin):
     """The interface of ``DenseModel`` (full packed batch in, full log-probs out, full-batch gradients in)
     on top of the sequence-parallel model: pads the batch to a multiple of 128 tokens per rank, hands
     the local slice to the model and gathers the per-token results."""
@@ -63,6 +64,10 @@ class UlyssesModelAdapter:
         self.inner, self.sp = model, model.sp
         self.cfg, self.params, self.device, self.dtype = model.cfg, model.params, model.device, model.dtype
         self._T = self._T_real = 0
+        self.same_rows_ranks = self.sp.world
+
+    def _mtp_group(self):
+        return self.sp.group if self.sp.world > 1 else None
 
     @property
     def recompute(self):
@@ -77,8 +82,12 @@ class UlyssesModelAdapter:
         self._T = padded.input_ids.numel()
         n = self._T // self.sp.world
         sl = slice(self.sp.rank * n, (self.sp.rank + 1) * n)
-        return PackedBatch(padded.input_ids[sl].contiguous(), padded.position_ids[sl].contiguous(), padded.cu_seqlens,
-                           padded.labels[sl].contiguous(), padded.max_seqlen)
+        local = PackedBatch(padded.input_ids[sl].contiguous(), padded.position_ids[sl].contiguous(), padded.cu_seqlens,
+                            padded.labels[sl].contiguous(), padded.max_seqlen)
+        if self._wants_mtp():          # next tokens and second-next labels are shifted within whole sequences, then cut
+            nxt, lab2 = shifted_inputs(padded)
+            local.mtp_inputs = (nxt[sl].contiguous(), lab2[sl].contiguous())
+        return local
 
     def forward(self, batch: PackedBatch, temperature: float = 1.0, save_for_backward: bool = False):
         lp, ent = self.inner.forward(self._local(batch), temperature, save_for_backward)

@@ -367,6 +367,7 @@ class PolicyEngine:
                 dist.all_reduce(cnt, group=self.pg)
             if getattr(self.model, "ROWS_DIFFER_IN_GROUP", False) and getattr(self.model, "ep", None) is not None:
                 self.model.ep.all_reduce_(cnt)          # expert-parallel peers are outside the optimizer's group and bring rows of their own
+            cnt = cnt / float(getattr(self.model, "same_rows_ranks", 1))     # sequence- / context-parallel peers counted the same rows
             self.model.mtp_scale = self.mtp_loss_coef / max(float(cnt), 1.0)
         packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device, mb) for mb in mbs]
         if hasattr(self.model, "train_many"):
@@ -382,8 +383,9 @@ class PolicyEngine:
         for mb, pk in zip(mbs, packs):
             lp_packed, ent_packed = self.model.forward(pk.batch, temp, save_for_backward=True)
             g_lp, g_ent = loss_step(mb, pk, lp_packed, ent_packed)
-            if mtp and self.model.mtp_last is not None:
-                nll, n = self.model.mtp_last
+            last = self.model.mtp_last if mtp else None        # read once: an adapter sums it over its group
+            if last is not None:
+                nll, n = last
                 metrics.setdefault("mtp_loss", []).append(float(nll) / max(float(n), 1.0))
             self.model.backward(g_lp, g_ent)
         if mtp:

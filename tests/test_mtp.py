@@ -2,6 +2,7 @@
 against an autograd implementation; the engine reports the loss and scales it by mini-batch counts."""
 import math
 
+import pytest
 import torch
 import torch.nn.functional as F
 
@@ -181,3 +182,29 @@ def test_sparse_model_replays_the_decoder_layers_and_routes_the_module_itself():
     L = cfg.num_hidden_layers
     assert float(model.params.grads[f"model.layers.{L}.mlp.experts.w13_weight"].abs().max()) > 0
     assert float(model.params.grads[f"model.layers.{L}.mlp.gate.weight"].abs().max()) > 0
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("kind", ["ulysses", "context"])
+def test_module_on_ranks_that_hold_a_slice_of_the_tokens_matches_single_process(monkeypatch, kind):
+    """Sequence-parallel (Ulysses) and context-parallel (zigzag) ranks hold a slice of every sequence: the next tokens and
+    the second-next labels are shifted within whole sequences before the cut, the module's attention is the group's, its
+    targets are counted once; reported loss, gradient norm and update equal the single-process trainer."""
+    import numpy as np
+    from test_megatron_trainer import _cfg, _run
+    monkeypatch.setenv("AXON_ENABLE_MTP", "1")
+    name = "tiny-qwen3-mtp"
+    ref_cfg = _cfg(1, name)
+    if kind == "ulysses":
+        got_cfg, cls = _cfg(1, name), "axon_b200.trainer.fsdp_trainer.TrainerWorker"
+        got_cfg["fsdp"] = {"ulysses_sequence_parallel_size": 2}
+    else:
+        got_cfg, cls = _cfg(1, name, cp=2), "axon_b200.trainer.megatron_trainer.TrainerWorker"
+    ref_cfg["mtp_loss_scaling_factor"] = got_cfg["mtp_loss_scaling_factor"] = 0.3
+    ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
+    got = _run(cls, got_cfg, 2)
+    torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
+    assert "actor/mtp_loss" in got[1] and abs(np.mean(got[1]["actor/mtp_loss"]) - np.mean(ref[1]["actor/mtp_loss"])) < 1e-3
+    gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
+    assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
+    torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
