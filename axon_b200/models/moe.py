@@ -31,8 +31,6 @@ from .dense import DenseModel, PackedBatch
 
 
 class MoEModel(DenseModel):
-    ROWS_DIFFER_IN_GROUP = True       # the ranks of an expert-parallel group train on different rows (unlike tensor-parallel peers)
-
     def __init__(self, cfg: ModelConfig, device="cuda", dtype=torch.bfloat16, params=None, ep=None):
         """``ep``: an ``EPContext`` — every rank then holds only its E/W experts (``w13`` / ``w2`` have a
         leading dimension of E/W) and tokens reach their experts through peer memory."""
@@ -75,6 +73,11 @@ class MoEModel(DenseModel):
             else:
                 out.append([a, b])
         return [(a, b) for a, b in out]
+
+    def sum_over_row_peers(self, t: torch.Tensor) -> torch.Tensor:
+        """The ranks of an expert-parallel group train on different rows (unlike tensor-parallel peers) and are not in the
+        optimizer's group: a count over the rows of a mini-batch is completed here."""
+        return self.ep.all_reduce_(t) if self.ep is not None else t
 
     def sync_replicated_grads(self) -> None:
         """Sum the gradients of the replicated parameters over the expert-parallel group (each rank saw

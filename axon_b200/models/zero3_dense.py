@@ -70,6 +70,11 @@ class Zero3DenseModel(DenseModel):
         for name, v in self.params.views.items():
             yield name, (self.shard.all_gather_rows(v.detach()) if is_sharded(name) else v.detach())
 
+    def sum_over_row_peers(self, t: torch.Tensor) -> torch.Tensor:
+        """The ranks of the shard group are data-parallel peers outside the optimizer's (single-rank) group: a count over the
+        rows of a mini-batch is completed here."""
+        return self.shard.all_reduce_(t)
+
     def replicated_names(self) -> list[str]:
         return [n for n in self.params.layout if not is_sharded(n)]
 

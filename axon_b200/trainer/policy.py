@@ -365,8 +365,9 @@ class PolicyEngine:
             cnt = sum((mb.batch["attention_mask"].sum(1) - 2).clamp_min(0).sum() for mb in mbs).float().reshape(1)
             if self.world > 1:
                 dist.all_reduce(cnt, group=self.pg)
-            if getattr(self.model, "ROWS_DIFFER_IN_GROUP", False) and getattr(self.model, "ep", None) is not None:
-                self.model.ep.all_reduce_(cnt)          # expert-parallel peers are outside the optimizer's group and bring rows of their own
+            peers = getattr(self.model, "sum_over_row_peers", None)
+            if peers is not None:
+                peers(cnt)          # ranks outside the optimizer's group that bring rows of their own (expert-parallel, parameter-sharding peers)
             cnt = cnt / float(getattr(self.model, "same_rows_ranks", 1))     # sequence- / context-parallel peers counted the same rows
             self.model.mtp_scale = self.mtp_loss_coef / max(float(cnt), 1.0)
         packs = [_Packing(mb.batch["input_ids"], mb.batch["attention_mask"], self.device, mb) for mb in mbs]

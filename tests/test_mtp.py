@@ -185,11 +185,12 @@ def test_sparse_model_replays_the_decoder_layers_and_routes_the_module_itself():
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["ulysses", "context"])
+@pytest.mark.parametrize("kind", ["ulysses", "context", "param-shards"])
 def test_module_on_ranks_that_hold_a_slice_of_the_tokens_matches_single_process(monkeypatch, kind):
     """Sequence-parallel (Ulysses) and context-parallel (zigzag) ranks hold a slice of every sequence: the next tokens and
     the second-next labels are shifted within whole sequences before the cut, the module's attention is the group's, its
-    targets are counted once; reported loss, gradient norm and update equal the single-process trainer."""
+    targets are counted once; reported loss, gradient norm and update equal the single-process trainer. Parameter-sharding
+    ranks are the opposite case: data-parallel peers outside the optimizer's group, whose targets have to be added."""
     import numpy as np
     from test_megatron_trainer import _cfg, _run
     monkeypatch.setenv("AXON_ENABLE_MTP", "1")
@@ -198,13 +199,18 @@ def test_module_on_ranks_that_hold_a_slice_of_the_tokens_matches_single_process(
     if kind == "ulysses":
         got_cfg, cls = _cfg(1, name), "axon_b200.trainer.fsdp_trainer.TrainerWorker"
         got_cfg["fsdp"] = {"ulysses_sequence_parallel_size": 2}
+    elif kind == "param-shards":
+        got_cfg, cls = _cfg(1, name), "axon_b200.trainer.fsdp_trainer.TrainerWorker"
+        got_cfg["fsdp"] = {"param_sharding": True}
     else:
         got_cfg, cls = _cfg(1, name, cp=2), "axon_b200.trainer.megatron_trainer.TrainerWorker"
     ref_cfg["mtp_loss_scaling_factor"] = got_cfg["mtp_loss_scaling_factor"] = 0.3
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
     got = _run(cls, got_cfg, 2)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
-    assert "actor/mtp_loss" in got[1] and abs(np.mean(got[1]["actor/mtp_loss"]) - np.mean(ref[1]["actor/mtp_loss"])) < 1e-3
+    # data-parallel ranks report the mean over their own micro-batches: close to, not equal to, the single process's
+    tol = 5e-3 if kind == "param-shards" else 1e-3
+    assert "actor/mtp_loss" in got[1] and abs(np.mean(got[1]["actor/mtp_loss"]) - np.mean(ref[1]["actor/mtp_loss"])) < tol
     gn, gr = float(np.mean(got[2]["actor/grad_norm"])), float(np.mean(ref[2]["actor/grad_norm"]))
     assert abs(gn - gr) < 1e-3 * max(1.0, gr), (gn, gr)
     torch.testing.assert_close(got[3], ref[3], rtol=1e-3, atol=1e-3)
