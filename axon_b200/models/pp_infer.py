@@ -101,8 +101,8 @@ class _StagedInference:
 def _stage_config(cfg: ModelConfig, stage) -> ModelConfig:
     n = len(stage_layers(cfg.num_hidden_layers, stage.world, stage.rank))
     assert n >= 1, f"{cfg.num_hidden_layers} layers do not give every one of {stage.world} stages a layer"
-    assert cfg.num_nextn_predict_layers == 0, "a multi-token-prediction module is not part of a sampler stage"
-    return dataclasses.replace(cfg, num_hidden_layers=n, extra=dict(cfg.extra))
+    # a multi-token-prediction module behind the decoder is a training device: no stage holds it (``local_name`` -> None)
+    return dataclasses.replace(cfg, num_hidden_layers=n, num_nextn_predict_layers=0, extra=dict(cfg.extra))
 
 
 class StagedDenseModel(_StagedInference, DenseModel):

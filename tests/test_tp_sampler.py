@@ -64,3 +64,40 @@ def test_tp2_sampler_group_sums_through_peer_memory_gpu(tmp_path):
     for x in res:
         assert x["fused"] and x["reduce_calls"]["fused"] > 0 and x["status"] == 0, x
         assert x["tiny-gpu"]["graphs"] > 0, x          # the decode graph replays the peer-memory sums
+
+
+def test_sampler_group_models_accept_a_checkpoint_with_a_prediction_module():
+    """A multi-token-prediction module behind the decoder is a training device. A sampler stage holds none of it (its
+    tensors are skipped when weights arrive); a tensor-parallel member keeps its cut like any layer's and never runs it.
+    Both generate what the whole model generates."""
+    import torch
+    from axon_b200.models.config import get_config
+    from axon_b200.models.moe import build_model_for
+    from axon_b200.models.pp_infer import StagedDenseModel
+    from axon_b200.models.tp_infer import Shard, ShardedDenseModel, ShardedMoEModel
+    from axon_b200.sampler.engine import GenerationEngine
+    from axon_b200.sampler.params import SamplingParams
+
+    class _Alone:                     # a group of one: nothing to sum
+        calls: dict = {}
+
+        def begin_step(self):
+            pass
+
+        def __call__(self, y):
+            return y
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    prompt = [[5, 6, 7, 8, 9]]
+    for preset, kinds in (("tiny-qwen3-mtp", (StagedDenseModel, ShardedDenseModel)), ("tiny-moe-mtp", (ShardedMoEModel,))):
+        cfg = get_config(preset)
+        full = build_model_for(cfg, "cpu", torch.float32)
+        full.params.init_random(std=0.08, seed=3)
+        want = GenerationEngine(full, num_pages=8, max_num_seqs=4, seed=1).generate(prompt, sp)[0].token_ids
+        for cls in kinds:
+            part = cls(cfg, Shard(None, 0, 1, _Alone()), device="cpu", dtype=torch.float32)
+            part.load_full_state(full.params.views)
+            assert GenerationEngine(part, num_pages=8, max_num_seqs=4, seed=1).generate(prompt, sp)[0].token_ids == want
+            if cls is StagedDenseModel:
+                L = cfg.num_hidden_layers
+                assert part.localize(f"model.layers.{L}.eh_proj.weight", torch.zeros(1)) is None
+                assert part.localize("model.layers.0.input_layernorm.weight", torch.zeros(1))[0] == "model.layers.0.input_layernorm.weight"
