@@ -28,8 +28,6 @@ from .tp_dense import TPDenseModel
 
 
 class TPCPDenseModel(TPDenseModel):
-    MTP_OK = False
-
     def __init__(self, cfg: ModelConfig, tp: TPContext, cp: CP.ContextParallel, device="cuda", dtype=torch.bfloat16):
         super().__init__(cfg, tp, device=device, dtype=dtype)
         self.cp = cp

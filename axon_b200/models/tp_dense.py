@@ -96,18 +96,22 @@ def pad_packed_batch(batch: PackedBatch, multiple: int) -> tuple[PackedBatch, in
     rm = getattr(batch, "routermap", None)
     if rm is not None:                       # padding rows replay nothing
         rm = torch.cat([rm, torch.full((pad, *rm.shape[1:]), -1, dtype=rm.dtype, device=rm.device)])
-    return PackedBatch(torch.cat([batch.input_ids, z(pad, 0, batch.input_ids.dtype)]),
-                       torch.cat([batch.position_ids, torch.arange(pad, dtype=batch.position_ids.dtype, device=dev)]),
-                       torch.cat([batch.cu_seqlens, torch.tensor([T + pad], dtype=batch.cu_seqlens.dtype, device=dev)]),
-                       torch.cat([batch.labels, z(pad, -100, batch.labels.dtype)]),
-                       max(batch.max_seqlen, pad), routermap=rm), T
+    out = PackedBatch(torch.cat([batch.input_ids, z(pad, 0, batch.input_ids.dtype)]),
+                      torch.cat([batch.position_ids, torch.arange(pad, dtype=batch.position_ids.dtype, device=dev)]),
+                      torch.cat([batch.cu_seqlens, torch.tensor([T + pad], dtype=batch.cu_seqlens.dtype, device=dev)]),
+                      torch.cat([batch.labels, z(pad, -100, batch.labels.dtype)]),
+                      max(batch.max_seqlen, pad), routermap=rm)
+    pre = getattr(batch, "mtp_inputs", None)         # shifted ids / labels that an outer adapter cut for this rank
+    if pre is not None:
+        out.mtp_inputs = (torch.cat([pre[0], z(pad, 0, pre[0].dtype)]), torch.cat([pre[1], z(pad, -100, pre[1].dtype)]))
+    return out, T
 
 
 class TPDenseModel:
     SPARSE = False           # the sparse subclass (tp_moe.TPMoEModel) replaces the MLP hooks
     ep_world = 1
     etp_world = 1
-    MTP_OK = True           # context-parallel ranks switch it off
+    MTP_OK = True
 
     def __init__(self, cfg: ModelConfig, tp: TPContext, device="cuda", dtype=torch.bfloat16, vocab_parallel_head: bool = False,
                  holds=None):
@@ -322,7 +326,8 @@ class TPDenseModel:
         assert self.vp_head is None, "the multi-token-prediction module uses the whole output head"
         c, batch, L, sl = self.cfg, s["batch"], self.cfg.num_hidden_layers, s["sl"]
         p, w = f"model.layers.{L}.", self.params
-        nxt, lab2 = shifted_inputs(batch)
+        pre = getattr(batch, "mtp_inputs", None)         # context-parallel ranks: shifted within whole sequences before the cut
+        nxt, lab2 = pre if pre is not None else shifted_inputs(batch)
         nxt, lab2 = nxt[sl].contiguous(), lab2[sl].contiguous()
         e = A.embedding_fwd(nxt, w["model.embed_tokens.weight"])
         en, rstd_e, _ = N.rmsnorm_fwd(e, w[p + "enorm.weight"], c.rms_norm_eps)

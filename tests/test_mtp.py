@@ -185,7 +185,7 @@ def test_sparse_model_replays_the_decoder_layers_and_routes_the_module_itself():
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("kind", ["ulysses", "context", "param-shards"])
+@pytest.mark.parametrize("kind", ["ulysses", "context", "param-shards", "tensor-context"])
 def test_module_on_ranks_that_hold_a_slice_of_the_tokens_matches_single_process(monkeypatch, kind):
     """Sequence-parallel (Ulysses) and context-parallel (zigzag) ranks hold a slice of every sequence: the next tokens and
     the second-next labels are shifted within whole sequences before the cut, the module's attention is the group's, its
@@ -199,6 +199,8 @@ def test_module_on_ranks_that_hold_a_slice_of_the_tokens_matches_single_process(
     if kind == "ulysses":
         got_cfg, cls = _cfg(1, name), "axon_b200.trainer.fsdp_trainer.TrainerWorker"
         got_cfg["fsdp"] = {"ulysses_sequence_parallel_size": 2}
+    elif kind == "tensor-context":          # world = 4: two context-parallel members, each a tensor-parallel pair
+        got_cfg, cls = _cfg(2, name, cp=2), "axon_b200.trainer.megatron_trainer.TrainerWorker"
     elif kind == "param-shards":
         got_cfg, cls = _cfg(1, name), "axon_b200.trainer.fsdp_trainer.TrainerWorker"
         got_cfg["fsdp"] = {"param_sharding": True}
@@ -206,7 +208,7 @@ def test_module_on_ranks_that_hold_a_slice_of_the_tokens_matches_single_process(
         got_cfg, cls = _cfg(1, name, cp=2), "axon_b200.trainer.megatron_trainer.TrainerWorker"
     ref_cfg["mtp_loss_scaling_factor"] = got_cfg["mtp_loss_scaling_factor"] = 0.3
     ref = _run("axon_b200.trainer.fsdp_trainer.TrainerWorker", ref_cfg, 1)
-    got = _run(cls, got_cfg, 2)
+    got = _run(cls, got_cfg, 4 if kind == "tensor-context" else 2)
     torch.testing.assert_close(got[0], ref[0], rtol=1e-4, atol=1e-4)
     # data-parallel ranks report the mean over their own micro-batches: close to, not equal to, the single process's
     tol = 5e-3 if kind == "param-shards" else 1e-3
